@@ -1,0 +1,182 @@
+/*
+ * lyraq — C ABI of the B200 (sm_100a) quantized-linear path.
+ *
+ * Every entry point takes plain device pointers and sizes, is asynchronous on the CUDA
+ * stream it is given (passed as void*, i.e. a cudaStream_t; NULL = the default stream),
+ * allocates nothing, never throws and returns a lyraq_status_t.  Unsupported shapes are
+ * refused with an error code before anything is launched; nothing is silently skipped.
+ * Tensor element types are named by lyraq_dtype_t.  "rows" is batch*sequence, flattened.
+ *
+ * Each declaration names the reference interface (file:line within lyraDiff's source
+ * tree) that it replaces.
+ */
+#ifndef LYRAQ_H_
+#define LYRAQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define LYRAQ_API __attribute__((visibility("default")))
+#else
+#define LYRAQ_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    LYRAQ_OK = 0,
+    LYRAQ_ERR_INVALID_ARG = 1,    /* null pointer, bad enum, misaligned pointer */
+    LYRAQ_ERR_UNSUPPORTED = 2,    /* shape outside what the kernels cover */
+    LYRAQ_ERR_CUDA = 3,           /* a CUDA runtime/driver call failed */
+    LYRAQ_ERR_DEVICE_TIMEOUT = 4, /* a bounded wait inside a kernel ran out (see lyraq_last_status) */
+    LYRAQ_ERR_WORKSPACE = 5       /* workspace missing or too small */
+} lyraq_status_t;
+
+typedef enum {
+    LYRAQ_F16 = 0,
+    LYRAQ_BF16 = 1,
+    LYRAQ_F32 = 2,
+    LYRAQ_S32 = 3
+} lyraq_dtype_t;
+
+/* How the activation scale of an INT8 quantize / GEMM is given. */
+typedef enum {
+    LYRAQ_SCALE_PER_TENSOR = 0,       /* one fp32 scalar on the device */
+    LYRAQ_SCALE_PER_TOKEN = 1,        /* fp32 [rows], precomputed */
+    LYRAQ_SCALE_PER_TOKEN_DYNAMIC = 2 /* fp32 [rows], computed by the kernel as amax/127 and written out */
+} lyraq_scale_mode_t;
+
+/* Epilogue flags of the GEMMs (bit set). */
+enum {
+    LYRAQ_EPI_NONE = 0,
+    LYRAQ_EPI_GELU_TANH = 1 /* tanh-GELU after bias (and after beta*residual, as cuBLASLt orders it) */
+};
+
+LYRAQ_API const char* lyraq_version(void);
+LYRAQ_API const char* lyraq_status_string(int status);
+
+/* Reads (and clears) the device-side status word of the current device after synchronising
+ * `stream`: LYRAQ_OK, or LYRAQ_ERR_DEVICE_TIMEOUT with *detail (may be NULL) = which wait gave up.
+ * The reference has no counterpart: its kernels have no bounded waits. */
+LYRAQ_API int lyraq_last_status(void* stream, uint32_t* detail);
+
+/* ------------------------------------------------------------------ activation quantizers */
+
+/* INT8 SmoothQuant activation quantize: q = sat_s8(rne(float(x)*pre[c] / s)).
+ * Replaces invokeSqInputQuant<T> (src/lyradiff/kernels/quant_kernels/quant_kernels.h:9-17;
+ * kernels quant_kernels.cu:51-115).  pre_quant_scale may be NULL (= ones).
+ * scale_mode PER_TENSOR / PER_TOKEN read `scale`; PER_TOKEN_DYNAMIC writes `scale` [rows].
+ * dim must be a multiple of 8 and at most 16384. */
+LYRAQ_API int lyraq_quant_int8(int8_t* dst, const void* src, int src_dtype, const float* pre_quant_scale,
+                     float* scale, int scale_mode, size_t rows, size_t dim, void* stream);
+
+/* Per-tensor static-scale conversion to e4m3: dst = e4m3_rne_satfinite(float(src) * r),
+ * r = 1/scale[0] if invert_scale else scale[0].
+ * Replaces invokeCudaD2DScaleCpyConvert<Tin, __nv_fp8_e4m3> (src/lyradiff/utils/memory_utils.h:74;
+ * kernel memory_utils.cu:431-446). */
+LYRAQ_API int lyraq_quant_fp8(uint8_t* dst, const void* src, int src_dtype, const float* scale, int invert_scale,
+                    size_t n, void* stream);
+
+/* scale[0] = max(scale[0], max|w| / 448).  The caller zeroes scale[0] first, as the reference does.
+ * Replaces invokeGetFP8WeightScale (src/lyradiff/kernels/lora/load_lora.cu:49-54,109-113). */
+LYRAQ_API int lyraq_fp8_amax_scale(float* scale, const void* w, int w_dtype, size_t n, void* stream);
+
+/* INT4 activation quantize, groups of 64 along K: v = float(x)/smooth[c]; s = max|v|/7; q = sat_s4(rne(v/s)).
+ * q: packed [m, k/2] bytes (even element in the low nibble), q_scale: fp32 [m, k/64].
+ * Replaces the quantize half of invokeFusedQuantizeAndLoraDownSimple
+ * (src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.h:6-17; kernel w4a4_gemm.cu:769-954).
+ * smooth may be NULL (= ones).  If lora_down (bf16/f16 [32, k], same type as x) and lora_act
+ * (fp32 [m, 32]) are both non-NULL, lora_act = x * lora_down^T is also produced (deterministic,
+ * overwritten not accumulated).  k must be a multiple of 64. */
+LYRAQ_API int lyraq_quant_int4_g64(uint8_t* q, float* q_scale, float* lora_act, const void* x, int x_dtype,
+                         const float* smooth, const void* lora_down, size_t m, size_t k, void* stream);
+
+/* ------------------------------------------------------------------ load-time weight quantizers */
+
+/* Per-output-channel INT8 weight quantize: w' = w/pre[c]; s_w[n] = amax_n/127; q = sat_s8(rne(w'/s_w)).
+ * Replaces invokeGetINT8WeightScale<T> (src/lyradiff/kernels/quant_kernels/quant_kernels.cu:173-223,270-312).
+ * pre_quant_scale may be NULL. */
+LYRAQ_API int lyraq_weight_quant_int8(float* w_scale, int8_t* qw, const void* w, int w_dtype, const float* pre_quant_scale,
+                            size_t d_out, size_t d_in, void* stream);
+
+/* INT4 group-64 weight quantize into the layout W4A4GemmWeight holds
+ * (src/lyradiff/layers/w4a4_gemm_block/W4A4GemmWeight.h:8-45): packed [n, k/2], scales [n, k/64]
+ * of scale_dtype (LYRAQ_F32 or LYRAQ_F16).  The reference has no device quantizer for this format. */
+LYRAQ_API int lyraq_weight_quant_int4_g64(uint8_t* qw, void* w_scale, int scale_dtype, const void* w, int w_dtype,
+                                size_t n, size_t k, void* stream);
+
+/* ------------------------------------------------------------------ fused producers */
+
+/* AdaLN-Zero modulation y = LN(x)*(1+scale_b)+shift_b (eps, no affine), x [B,S,D], scale/shift [B,D].
+ * Replaces invokeLayerNormWithShiftAndScale<T> (src/lyradiff/kernels/norms/layer_norm.h:19; kernel
+ * layer_norm.cu:405-484), fused with the quantize pass that follows it in the reference
+ * (memory_utils.cu:431-446 / quant_kernels.cu:93-115).  Any of the three outputs may be NULL:
+ *   y     [B*S, D] of dtype                       (the un-quantized result)
+ *   q8    int8 [B*S, D] with q8_scale fp32 [B*S]  (dynamic per-token, amax/127; pre_quant_scale optional)
+ *   qf8   e4m3 [B*S, D] with f8_scale fp32 [1]    (static per-tensor, dst = y / f8_scale[0])
+ * D must be a multiple of 8 and at most 16384. */
+LYRAQ_API int lyraq_adaln_quant(void* y, int8_t* q8, float* q8_scale, uint8_t* qf8, const float* f8_scale,
+                      const void* x, const void* scale, const void* shift, int dtype,
+                      const float* pre_quant_scale, size_t B, size_t S, size_t D, double eps, void* stream);
+
+/* (residual + bias +) LayerNorm(gamma, beta) -> int8 with a static scalar scale.
+ * Replaces invokeLayerNormInt8O<T> and invokeFusedResidualBiasLayerNormInt8O<T>
+ * (src/lyradiff/kernels/quant_kernels/layer_norm_int8.h:9-38; launchers layer_norm_int8.cu:558-679).
+ * residual/bias may be NULL; when residual is given, sum_out (dtype [rows, dim], may alias x) receives x+residual+bias. */
+LYRAQ_API int lyraq_ln_quant_int8(int8_t* dst, void* sum_out, const void* x, const void* residual, const void* bias,
+                        const void* gamma, const void* beta, int dtype, const float* pre_quant_scale,
+                        const float* input_quant_scale, size_t rows, size_t dim, double eps, void* stream);
+
+/* bias + GEGLU (tanh-GELU) -> int8: h [rows, 2*dim] -> dst [rows, dim], static scalar scale.
+ * Replaces invokeFusedAddBiasGegluInt8O<T> (src/lyradiff/kernels/quant_kernels/ffn_kernels_int8.h:13-21;
+ * kernels ffn_kernels_int8.cu:15-187).  bias ([2*dim]) may be NULL. */
+LYRAQ_API int lyraq_geglu_quant_int8(int8_t* dst, const void* h, const void* bias, int dtype, const float* pre_quant_scale,
+                           const float* input_quant_scale, size_t rows, size_t dim, void* stream);
+
+/* ------------------------------------------------------------------ GEMMs (tcgen05, accumulators in TMEM) */
+
+/* Bytes of workspace a GEMM call needs for (m, n, k); currently 0 for every op (no split-K), kept so that
+ * callers written against the reference's getWorkspaceSize (int8_gemm_template.h:683-692) keep working. */
+LYRAQ_API size_t lyraq_workspace_bytes(int op, int m, int n, int k);
+
+/* INT8 W8A8: C[m,n] = T( T(float(sum_k A[m,k]*B[n,k]) * (alpha_col[n]*alpha_row)) + bias[n] ).
+ * A int8 [m,k] row-major, B int8 [n,k] (K contiguous), int32 accumulation (exact), alpha_col fp32 [n],
+ * alpha_row fp32 [1] or [m] (row_scale_mode PER_TENSOR / PER_TOKEN), bias of c_dtype [n] or NULL.
+ * c_dtype F16/BF16/F32, or S32 to get the raw accumulators (scales and bias ignored).
+ * Replaces cublasMMWrapper::runGemmInt8 (src/lyradiff/utils/cublasMMWrapper.h:368-385) ->
+ * SmoothQuantGemmPlugin<T>::RunGemm (layers/gemm_utils/SmoothQuantGemm.cc:108-163) ->
+ * CutlassInt8GemmRunner<T>::gemm (kernels/cutlass_kernels/int8_gemm/int8_gemm_template.h:643-672).
+ * k must be a multiple of 16; A and B 16-byte aligned; C 16-byte aligned. */
+LYRAQ_API int lyraq_gemm_int8(const int8_t* A, const int8_t* B, const float* alpha_col, const float* alpha_row,
+                    int row_scale_mode, void* C, int c_dtype, const void* bias, int m, int n, int k,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* FP8 e4m3: Y[m,n] = T( epi( alpha*s_x[0]*s_w[0] * sum_k X[m,k]*W[n,k] + beta*R[m,n] + bias[n] ) ),
+ * fp32 accumulation, epi = identity or tanh-GELU (epilogue flags), bias/R of c_dtype or NULL.
+ * Replaces cublasMMWrapper::GemmWithResidualAndBias for __nv_fp8_e4m3
+ * (src/lyradiff/utils/cublasMMWrapper.h:300-317, .cc:1104-1276), in its only calling form
+ * (OP_T, OP_N, n, m, k, W, k, s_w, X, k, s_x, Y, n, bias, R, alpha, beta, is_gelu). */
+LYRAQ_API int lyraq_gemm_fp8(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, void* Y, int c_dtype,
+                   const void* bias, const void* residual, float alpha, float beta, int epilogue,
+                   int m, int n, int k, void* workspace, size_t workspace_bytes, void* stream);
+
+/* W4A4, groups of 64 along K: D[m,n] = T( epi( sum_g (float(sum_{k in g} a*b) * sa[m,g]) * sb[n,g]
+ *                                              + lora_act[m,:] . lora_up[n,:] + bias[n] ) + R[m,n] ).
+ * A packed int4 [m,k/2], B packed int4 [n,k/2], sa fp32 [m,k/64], sb [n,k/64] of sb_dtype (F32 or F16),
+ * exact int32 per group, fp32 across groups in order g = 0..k/64-1.  lora_act fp32 [m,32] and
+ * lora_up (c_dtype, [n,32]) may both be NULL.  bias, R of c_dtype or NULL.
+ * Replaces invokeFusedW4A4GemmAndLoraUp (src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.h:19-30; kernels
+ * w4a4_gemm.cu:227-767) and the bias/GELU/residual kernels that follow it
+ * (kernels/flux_single_transformer_block/flux_single_transformer_kernels.cu:68-134). */
+LYRAQ_API int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* sa, const void* sb, int sb_dtype,
+                    void* D, int c_dtype, const float* lora_act, const void* lora_up, const void* bias,
+                    const void* residual, int epilogue, int m, int n, int k,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LYRAQ_H_ */

@@ -1,0 +1,80 @@
+// Library-level entry points: version, status strings, the per-device status word.
+#include "common.cuh"
+
+namespace lyraq {
+
+// Word 0: status code written by the first kernel wait that gave up; word 1: which wait.
+__device__ unsigned int g_status_words[4];
+
+static unsigned int* g_status_addr[64];  // per device ordinal, filled on first use
+
+unsigned int* status_word_ptr()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        return nullptr;
+    }
+    if (g_status_addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_words) != cudaSuccess) {
+            return nullptr;
+        }
+        g_status_addr[dev] = static_cast<unsigned int*>(p);
+    }
+    return g_status_addr[dev];
+}
+
+}  // namespace lyraq
+
+extern "C" {
+
+const char* lyraq_version(void) { return "lyraq 0.1 (sm_100a)"; }
+
+const char* lyraq_status_string(int status)
+{
+    switch (status) {
+        case LYRAQ_OK: return "ok";
+        case LYRAQ_ERR_INVALID_ARG: return "invalid argument (null, misaligned or bad enum)";
+        case LYRAQ_ERR_UNSUPPORTED: return "shape or type not supported by the sm_100a kernels";
+        case LYRAQ_ERR_CUDA: return "CUDA call failed";
+        case LYRAQ_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
+        case LYRAQ_ERR_WORKSPACE: return "workspace missing or too small";
+        default: return "unknown status";
+    }
+}
+
+int lyraq_last_status(void* stream, uint32_t* detail)
+{
+    unsigned int* dptr = lyraq::status_word_ptr();
+    if (dptr == nullptr) {
+        return LYRAQ_ERR_CUDA;
+    }
+    cudaStream_t s = (cudaStream_t)stream;
+    unsigned int host[2] = {0u, 0u};
+    if (cudaMemcpyAsync(host, dptr, sizeof(host), cudaMemcpyDeviceToHost, s) != cudaSuccess) {
+        return LYRAQ_ERR_CUDA;
+    }
+    if (cudaStreamSynchronize(s) != cudaSuccess) {
+        return LYRAQ_ERR_CUDA;
+    }
+    if (host[0] != 0u) {
+        if (cudaMemsetAsync(dptr, 0, 2 * sizeof(unsigned int), s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+            return LYRAQ_ERR_CUDA;
+        }
+    }
+    if (detail != nullptr) {
+        *detail = host[1];
+    }
+    return (int)host[0];
+}
+
+size_t lyraq_workspace_bytes(int op, int m, int n, int k)
+{
+    (void)op;
+    (void)m;
+    (void)n;
+    (void)k;
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,162 @@
+// Shared helpers of the lyraq kernels: dtype dispatch, 16-byte vector access, conversions with the
+// reference's rounding, the device status word, and argument checks used by every C entry point.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/lyraq.h"
+
+namespace lyraq {
+
+// ---------------------------------------------------------------------------------------------
+// Device status word.  Kernels with bounded waits record the first wait that gave up in a small
+// per-device array (word 0: code, 0 = ok; word 1: detail); the host reads it through
+// lyraq_last_status().  The array lives in the library's own device memory (api.cu); kernels get
+// its device address as a parameter.
+unsigned int* status_word_ptr();  // device address for the current device, NULL on failure
+
+__device__ __forceinline__ void report_timeout(unsigned int* status, unsigned int detail)
+{
+    if (atomicCAS(&status[0], 0u, (unsigned int)LYRAQ_ERR_DEVICE_TIMEOUT) == 0u) {
+        status[1] = detail;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+template<typename T> struct TypeTag;
+template<> struct TypeTag<__half> { static constexpr int value = LYRAQ_F16; };
+template<> struct TypeTag<__nv_bfloat16> { static constexpr int value = LYRAQ_BF16; };
+template<> struct TypeTag<float> { static constexpr int value = LYRAQ_F32; };
+
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(float v) { return v; }
+
+template<typename T> __device__ __forceinline__ T from_f32(float v);
+template<> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template<> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template<> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+
+// One arithmetic step "in T": the fp32 result of an operation on T operands, rounded to T.
+// For 16-bit T an fp32 add or multiply of two T values followed by this rounding equals the
+// native single-rounding T operation (products are exact in fp32; a sum that is inexact in fp32
+// is far from any T rounding boundary).
+template<typename T> __device__ __forceinline__ float round_t(float v) { return to_f32(from_f32<T>(v)); }
+
+// q = sat_s8(rne(v)): cvt.rni.sat.s8.f32, NaN -> 0 (reference: kernels/quant_kernels/int8_utils.cuh:23-28).
+__device__ __forceinline__ int f32_to_s8(float v)
+{
+    int r;
+    asm("cvt.rni.sat.s8.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return r;
+}
+
+__device__ __forceinline__ uint32_t pack4_s8(int a, int b, int c, int d)
+{
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+}
+
+// Two floats -> two e4m3 codes (RNE, saturate to +-448), low byte = first.
+__device__ __forceinline__ uint32_t f32x2_to_e4m3x2(float lo, float hi)
+{
+    uint16_t r;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(r) : "f"(hi), "f"(lo));
+    return (uint32_t)r;
+}
+
+__device__ __forceinline__ float tanh_approx(float x)
+{
+    float r;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// tanh-GELU in fp32 (reference: kernels/activation_kernels.h:56-68).
+__device__ __forceinline__ float gelu_tanh_f32(float v)
+{
+    const float cdf = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v * cdf;
+}
+
+// ---------------------------------------------------------------------------------------------
+// 16-byte vectors of 8 sixteen-bit values or 4 floats.
+struct alignas(16) Vec16 {
+    uint32_t w[4];
+};
+
+__device__ __forceinline__ Vec16 ld_nc_16(const void* p)
+{
+    Vec16 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void st_16(void* p, const Vec16& v)
+{
+    asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3])
+                 : "memory");
+}
+
+__device__ __forceinline__ void st_8(void* p, uint32_t a, uint32_t b)
+{
+    asm volatile("st.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+
+// Unpack 8 sixteen-bit values held in a Vec16 to fp32.
+template<typename T> __device__ __forceinline__ void unpack8(const Vec16& v, float* out);
+template<> __device__ __forceinline__ void unpack8<__half>(const Vec16& v, float* out)
+{
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2 h = *reinterpret_cast<const __half2*>(&v.w[i]);
+        float2  f = __half22float2(h);
+        out[2 * i]     = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+template<> __device__ __forceinline__ void unpack8<__nv_bfloat16>(const Vec16& v, float* out)
+{
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        out[2 * i]     = __uint_as_float(v.w[i] << 16);
+        out[2 * i + 1] = __uint_as_float(v.w[i] & 0xffff0000u);
+    }
+}
+
+template<typename T> __device__ __forceinline__ Vec16 pack8(const float* in);
+template<> __device__ __forceinline__ Vec16 pack8<__half>(const float* in)
+{
+    Vec16 v;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2 h = __floats2half2_rn(in[2 * i], in[2 * i + 1]);
+        v.w[i]    = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return v;
+}
+template<> __device__ __forceinline__ Vec16 pack8<__nv_bfloat16>(const float* in)
+{
+    Vec16 v;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(in[2 * i], in[2 * i + 1]);
+        v.w[i]           = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return v;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host-side checks.
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? LYRAQ_OK : LYRAQ_ERR_CUDA; }
+
+inline int launch_status() { return cuda_status(cudaGetLastError()); }
+
+}  // namespace lyraq

@@ -1,0 +1,547 @@
+// W4A4 GEMM, groups of 64 along K, for sm_100a.
+//
+//   D[m,n] = T( epi( sum_g (float(sum_{k in g} a[m,k]*b[n,k]) * sa[m,g]) * sb[n,g] + bias[n] ) + R[m,n] )
+//
+// Blackwell's tensor cores have no 4-bit integer MMA, so the packed nibbles are expanded to signed
+// bytes in shared memory and multiplied with tcgen05.mma kind::i8.  The expansion keeps each nibble in
+// the HIGH four bits of its byte (value * 16): that needs one AND (odd elements) or one shift + AND
+// (even elements) per four values and no sign fix-up; the factor 16 * 16 = 256 on every integer dot
+// product is an exact power of two and is folded into the activation scale (sa / 256), so the fp32
+// result is bit-identical.  Even and odd elements of a 32-nibble chunk land in two separate 16-byte
+// pieces; A and B use the same permutation, so dot products are unchanged and a group of 64 still
+// occupies exactly 64 consecutive bytes (two K = 32 MMA steps).
+//
+// Each group's int32 partial must be rescaled in fp32 before the next group is added, so the
+// accumulator leaves tensor memory once per group: four partial buffers (128 columns each) are
+// cycled, the MMA warp runs up to four groups ahead, and eight drain warps convert / scale /
+// accumulate in registers.  That CUDA-core work, not the tensor pipe, bounds this kernel.
+//
+// 384 threads per CTA, one persistent CTA per SM:
+//   warp 0      TMA producer: packed A (128 x 64 B) and packed B (128 x 64 B) tiles, ring of 4 stages
+//   warp 1      MMA issuer
+//   warps 2-3   expand nibbles -> swizzled int8 operand tiles (ring of 4 stages) and stage the scales
+//               of the two groups of the K block in shared memory; warp 2 also owns tensor memory
+//   warps 4-11  drain: warp w reads TMEM lanes 32*(w%4).., columns 64*((w-4)/4)..; final epilogue
+// All waits are bounded (see sm100_ptx.cuh); a timeout sets the status word and every role exits.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace lyraq {
+
+using namespace sm100;
+
+// defined in gemm_dense.cu
+int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k_bytes, uint64_t row_stride_bytes,
+                       uint32_t box_rows, uint32_t box_bytes, bool swizzle128);
+int device_sm_count();
+
+namespace w4 {
+
+constexpr int kBM          = 128;
+constexpr int kBN          = 128;
+constexpr int kKBlock      = 128;            // K elements per block = 2 groups
+constexpr int kPackedRowB  = kKBlock / 2;    // 64 bytes
+constexpr int kThreads     = 384;
+constexpr int kPStages     = 4;
+constexpr int kUStages     = 4;
+constexpr int kPBufs       = 4;              // partial accumulator buffers in tensor memory
+constexpr int kPackedTile  = kBM * kPackedRowB;   // 8 KB (A) ; B the same with kBN rows
+constexpr int kPackedStage = 2 * kPackedTile;     // 16 KB
+constexpr int kOperandTile = kBM * kKBlock;       // 16 KB
+constexpr int kScaleBytes  = 2 * (kBM + kBN) * 4; // two groups x (128 sa + 128 sb) fp32 = 2 KB
+constexpr int kUStage      = 2 * kOperandTile + kScaleBytes;
+constexpr int kBarOffset   = kPStages * kPackedStage + kUStages * kUStage;
+constexpr int kSmemTotal   = kBarOffset + 512 + 1024;
+
+struct Params {
+    int           M, N, K, G;  // G = K / 64
+    int           m_tiles, n_tiles;
+    const float*  sa;
+    const void*   sb;
+    int           sb_is_f16;
+    void*         D;
+    int           c_dtype;
+    const void*   bias;
+    const void*   residual;
+    int           gelu;
+    unsigned int* status;
+};
+
+template<typename T>
+__device__ __forceinline__ void final_store32(const Params& p, const float* acc, int row, int col0, int valid, bool vec_ok)
+{
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        v[i] = acc[i];
+    }
+    if (p.bias != nullptr) {
+        const T* b = reinterpret_cast<const T*>(p.bias) + col0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (i < valid) {
+                v[i] += to_f32(b[i]);
+            }
+        }
+    }
+    if (p.gelu) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            v[i] = gelu_tanh_f32(v[i]);
+        }
+    }
+    T* drow = reinterpret_cast<T*>(p.D) + (size_t)row * p.N + col0;
+    if (p.residual != nullptr) {
+        const T* r = reinterpret_cast<const T*>(p.residual) + (size_t)row * p.N + col0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (i < valid) {
+                v[i] += to_f32(r[i]);
+            }
+        }
+    }
+    if (vec_ok && valid >= 32) {
+        if (sizeof(T) == 2) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float tmp[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    tmp[j] = v[8 * i + j];
+                }
+                Vec16 w;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    T lo = from_f32<T>(tmp[2 * j]);
+                    T hi = from_f32<T>(tmp[2 * j + 1]);
+                    w.w[j] = (uint32_t)(*reinterpret_cast<uint16_t*>(&lo)) | ((uint32_t)(*reinterpret_cast<uint16_t*>(&hi)) << 16);
+                }
+                st_16(drow + 8 * i, w);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                Vec16 w;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    w.w[j] = __float_as_uint(v[4 * i + j]);
+                }
+                st_16(drow + 4 * i, w);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (i < valid) {
+                drow[i] = from_f32<T>(v[i]);
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p)
+{
+    constexpr uint32_t kTmemCols = kPBufs * kBN;  // 512
+    constexpr uint32_t kIdesc    = umma_idesc(2u, 1u, kBM, kBN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t*       gen_base  = smem_raw + (smem_base - smem_u32(smem_raw));
+    // [packed ring][operand ring: A int8 | B int8 | scales][barriers]
+    const uint32_t packed0 = smem_base;
+    const uint32_t ustage0 = smem_base + kPStages * kPackedStage;
+    const uint32_t bars    = smem_base + kBarOffset;
+    auto full_p    = [&](int s) { return bars + 8u * s; };
+    auto empty_p   = [&](int s) { return bars + 8u * (kPStages + s); };
+    auto full_u    = [&](int s) { return bars + 8u * (2 * kPStages + s); };
+    auto empty_u   = [&](int s) { return bars + 8u * (2 * kPStages + kUStages + s); };
+    auto part_full = [&](int b) { return bars + 8u * (2 * kPStages + 2 * kUStages + b); };
+    auto part_empty = [&](int b) { return bars + 8u * (2 * kPStages + 2 * kUStages + kPBufs + b); };
+    constexpr int kNumBars  = 2 * kPStages + 2 * kUStages + 2 * kPBufs;
+    uint32_t*     tmem_slot  = reinterpret_cast<uint32_t*>(gen_base + kBarOffset + 8 * kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPStages; ++s) {
+            mbar_init(full_p(s), 1);
+            mbar_init(empty_p(s), 2);   // the two expanding warps
+        }
+        for (int s = 0; s < kUStages; ++s) {
+            mbar_init(full_u(s), 2);    // the two expanding warps
+            mbar_init(empty_u(s), 1 + 8);  // MMA commit + eight drain warps
+        }
+        for (int b = 0; b < kPBufs; ++b) {
+            mbar_init(part_full(b), 1);
+            mbar_init(part_empty(b), 8);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 2) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_tiles = p.m_tiles * p.n_tiles;
+    const int num_kb    = (p.K + kKBlock - 1) / kKBlock;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // -------------------------------------------------------------- TMA producer
+            int      stage = 0, issued = 0;
+            uint32_t phase = 0;
+            bool     ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                const int m_blk = tile % p.m_tiles;
+                const int n_blk = tile / p.m_tiles;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(empty_p(stage), phase ^ 1u, abort_flag)) {
+                        report_timeout(p.status, 0x1100u | (unsigned)stage);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t dst = packed0 + stage * kPackedStage;
+                    mbar_arrive_expect_tx(full_p(stage), (uint32_t)kPackedStage);
+                    tma_load_2d(dst, &tmap_a, full_p(stage), kb * kPackedRowB, m_blk * kBM);
+                    tma_load_2d(dst + kPackedTile, &tmap_b, full_p(stage), kb * kPackedRowB, n_blk * kBN);
+                    ++issued;
+                    if (++stage == kPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+            int      s  = stage;
+            uint32_t ph = phase;
+            for (int i = 0; i < kPStages && i < issued; ++i) {
+                if (s == 0) {
+                    s = kPStages;
+                    ph ^= 1u;
+                }
+                --s;
+                const uint64_t t0 = global_timer_ns();
+                while (!mbar_try_wait(full_p(s), ph)) {
+                    if (global_timer_ns() - t0 > kWaitLimitNs) {
+                        report_timeout(p.status, 0x1500u | (unsigned)s);
+                        break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // -------------------------------------------------------------- MMA issuer
+            int      ustage = 0;
+            uint32_t uphase = 0;
+            uint32_t gi = 0;
+            bool     ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                for (int kb = 0; ok && kb < num_kb; ++kb) {
+                    if (!mbar_wait(full_u(ustage), uphase, abort_flag)) {
+                        report_timeout(p.status, 0x1200u | (unsigned)ustage);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = ustage0 + ustage * kUStage;
+                    const uint64_t adesc  = umma_desc_k_sw128(a_addr);
+                    const uint64_t bdesc  = umma_desc_k_sw128(a_addr + kOperandTile);
+                    const int      groups = min(2, p.G - 2 * kb);
+                    for (int g = 0; g < groups; ++g, ++gi) {
+                        const int pb = (int)(gi % kPBufs);
+                        if (!mbar_wait(part_empty(pb), ((gi / kPBufs) & 1u) ^ 1u, abort_flag)) {
+                            report_timeout(p.status, 0x1300u | (unsigned)pb);
+                            *abort_flag = 1;
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t d_tmem = tmem_base + (uint32_t)(pb * kBN);
+#pragma unroll
+                        for (int k = 0; k < 2; ++k) {
+                            const uint64_t koff = (uint64_t)((g * 2 + k) * 2);  // 32-byte K steps, in 16-byte units
+                            mma_i8(d_tmem, adesc + koff, bdesc + koff, kIdesc, (uint32_t)k);
+                        }
+                        tc_commit(part_full(pb));
+                    }
+                    if (ok) {
+                        tc_commit(empty_u(ustage));
+                    }
+                    if (++ustage == kUStages) {
+                        ustage = 0;
+                        uphase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 2 || warp == 3) {
+        // ------------------------------------------------------------------ nibble expansion + scale staging
+        const int tu     = threadIdx.x - 64;  // 0..63
+        int       pstage = 0, ustage = 0;
+        uint32_t  pphase = 0, uphase = 0;
+        bool      ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            const int m_blk = tile % p.m_tiles;
+            const int n_blk = tile / p.m_tiles;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                bool w = mbar_wait(full_p(pstage), pphase, abort_flag);
+                w      = w && mbar_wait(empty_u(ustage), uphase ^ 1u, abort_flag);
+                if (!__all_sync(0xffffffffu, w)) {
+                    if (lane == 0) {
+                        report_timeout(p.status, 0x1400u | (unsigned)(pstage * 16 + ustage));
+                    }
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                const uint8_t* src = gen_base + (packed0 - smem_base) + pstage * kPackedStage;
+                uint8_t*       dst = gen_base + (ustage0 - smem_base) + ustage * kUStage;
+                // 2 tiles x 128 rows x 4 packed 16-byte chunks = 1024 tasks over 64 threads
+#pragma unroll 4
+                for (int it = 0; it < 16; ++it) {
+                    const int   task = it * 64 + tu;        // 0..1023
+                    const int   mat  = task >> 9;           // 0 = A, 1 = B
+                    const int   idx  = task & 511;
+                    const int   r    = idx >> 2;
+                    const int   c    = idx & 3;
+                    const uint4 w4   = *reinterpret_cast<const uint4*>(src + mat * kPackedTile + r * kPackedRowB + c * 16);
+                    uint4       ev, od;
+                    ev.x = (w4.x << 4) & 0xF0F0F0F0u; od.x = w4.x & 0xF0F0F0F0u;
+                    ev.y = (w4.y << 4) & 0xF0F0F0F0u; od.y = w4.y & 0xF0F0F0F0u;
+                    ev.z = (w4.z << 4) & 0xF0F0F0F0u; od.z = w4.z & 0xF0F0F0F0u;
+                    ev.w = (w4.w << 4) & 0xF0F0F0F0u; od.w = w4.w & 0xF0F0F0F0u;
+                    uint8_t*  rowp = dst + mat * kOperandTile + (r >> 3) * 1024 + (r & 7) * 128;
+                    const int sw   = r & 7;
+                    *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ sw) << 4))     = ev;
+                    *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ sw) << 4)) = od;
+                }
+                // scales of the (up to) two groups of this K block: sas[g][row] = sa / 256, sbs[g][col] = sb
+                float* sas = reinterpret_cast<float*>(dst + 2 * kOperandTile);
+                float* sbs = sas + 2 * kBM;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int r    = tu + 64 * h;
+                    const int grow = m_blk * kBM + r;
+                    const int gcol = n_blk * kBN + r;
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        const int gg = 2 * kb + g;
+                        float     a = 0.0f, b = 0.0f;
+                        if (gg < p.G) {
+                            if (grow < p.M) {
+                                a = __ldg(p.sa + (size_t)grow * p.G + gg) * (1.0f / 256.0f);
+                            }
+                            if (gcol < p.N) {
+                                b = p.sb_is_f16 ? __half2float(reinterpret_cast<const __half*>(p.sb)[(size_t)gcol * p.G + gg])
+                                                : __ldg(reinterpret_cast<const float*>(p.sb) + (size_t)gcol * p.G + gg);
+                            }
+                        }
+                        sas[g * kBM + r] = a;
+                        sbs[g * kBN + r] = b;
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(full_u(ustage));
+                    mbar_arrive(empty_p(pstage));
+                }
+                if (++pstage == kPStages) {
+                    pstage = 0;
+                    pphase ^= 1u;
+                }
+                if (++ustage == kUStages) {
+                    ustage = 0;
+                    uphase ^= 1u;
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ drain + epilogue
+        const int      quad      = warp & 3;
+        const int      half      = (warp - 4) >> 2;
+        const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+        const int      trow      = quad * 32 + lane;
+        const bool     vec_ok    = (p.c_dtype == LYRAQ_F32) ? ((p.N & 3) == 0) : ((p.N & 7) == 0);
+        int            ustage = 0;
+        uint32_t       uphase = 0;
+        uint32_t       gi = 0;
+        bool           ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            const int m_blk = tile % p.m_tiles;
+            const int n_blk = tile / p.m_tiles;
+            float     acc[64];
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                acc[i] = 0.0f;
+            }
+            for (int kb = 0; ok && kb < num_kb; ++kb) {
+                if (!__all_sync(0xffffffffu, mbar_wait(full_u(ustage), uphase, abort_flag))) {
+                    if (lane == 0) {
+                        report_timeout(p.status, 0x1600u | (unsigned)ustage);
+                    }
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                const float* sas    = reinterpret_cast<const float*>(gen_base + (ustage0 - smem_base) + ustage * kUStage + 2 * kOperandTile);
+                const float* sbs    = sas + 2 * kBM;
+                const int    groups = min(2, p.G - 2 * kb);
+                for (int g = 0; g < groups; ++g, ++gi) {
+                    const int pb = (int)(gi % kPBufs);
+                    if (!__all_sync(0xffffffffu, mbar_wait(part_full(pb), (gi / kPBufs) & 1u, abort_flag))) {
+                        if (lane == 0) {
+                            report_timeout(p.status, 0x1700u | (unsigned)pb);
+                        }
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const float sa_v = sas[g * kBM + trow];
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t part[32];
+                        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64 + c * 32), part);
+                        tmem_ld_wait();
+                        const float4* sb4 = reinterpret_cast<const float4*>(sbs + g * kBN + half * 64 + c * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const float4 s = sb4[j];
+                            // acc = fma(float(p) * sa, sb, acc): the contraction the reference's compiler makes of
+                            // `acc += float(p) * sa * sb` (w4a4_gemm.cu:504-507)
+                            acc[c * 32 + 4 * j]     = fmaf((float)(int)part[4 * j] * sa_v, s.x, acc[c * 32 + 4 * j]);
+                            acc[c * 32 + 4 * j + 1] = fmaf((float)(int)part[4 * j + 1] * sa_v, s.y, acc[c * 32 + 4 * j + 1]);
+                            acc[c * 32 + 4 * j + 2] = fmaf((float)(int)part[4 * j + 2] * sa_v, s.z, acc[c * 32 + 4 * j + 2]);
+                            acc[c * 32 + 4 * j + 3] = fmaf((float)(int)part[4 * j + 3] * sa_v, s.w, acc[c * 32 + 4 * j + 3]);
+                        }
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(part_empty(pb));
+                    }
+                }
+                __syncwarp();
+                if (ok && lane == 0) {
+                    mbar_arrive(empty_u(ustage));
+                }
+                if (++ustage == kUStages) {
+                    ustage = 0;
+                    uphase ^= 1u;
+                }
+            }
+            if (!ok) {
+                break;
+            }
+            const int row = m_blk * kBM + trow;
+            if (row < p.M) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int col0  = n_blk * kBN + half * 64 + c * 32;
+                    const int valid = p.N - col0;
+                    if (valid > 0) {
+                        if (p.c_dtype == LYRAQ_BF16) {
+                            final_store32<__nv_bfloat16>(p, acc + c * 32, row, col0, valid, vec_ok);
+                        } else if (p.c_dtype == LYRAQ_F16) {
+                            final_store32<__half>(p, acc + c * 32, row, col0, valid, vec_ok);
+                        } else {
+                            final_store32<float>(p, acc + c * 32, row, col0, valid, vec_ok);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 2) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace w4
+}  // namespace lyraq
+
+using namespace lyraq;
+
+extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* sa, const void* sb, int sb_dtype, void* D,
+                               int c_dtype, const float* lora_act, const void* lora_up, const void* bias,
+                               const void* residual, int epilogue, int m, int n, int k, void* workspace,
+                               size_t workspace_bytes, void* stream)
+{
+    (void)workspace;
+    (void)workspace_bytes;
+    if (A == nullptr || B == nullptr || sa == nullptr || sb == nullptr || D == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (c_dtype < LYRAQ_F16 || c_dtype > LYRAQ_F32 || (sb_dtype != LYRAQ_F32 && sb_dtype != LYRAQ_F16) ||
+        (epilogue & ~LYRAQ_EPI_GELU_TANH) != 0 || m < 0 || n < 0 || k < 0) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (lora_act != nullptr || lora_up != nullptr) {
+        return LYRAQ_ERR_UNSUPPORTED;  // low-rank side branch: not built yet
+    }
+    if (m == 0 || n == 0) {
+        return LYRAQ_OK;
+    }
+    if (k == 0 || (k & 63) != 0) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    if (!aligned16(A) || !aligned16(B) || !aligned16(D) || (residual != nullptr && !aligned16(residual))) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    w4::Params p{};
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.G = k / 64;
+    p.m_tiles   = (m + w4::kBM - 1) / w4::kBM;
+    p.n_tiles   = (n + w4::kBN - 1) / w4::kBN;
+    p.sa        = sa;
+    p.sb        = sb;
+    p.sb_is_f16 = (sb_dtype == LYRAQ_F16) ? 1 : 0;
+    p.D         = D;
+    p.c_dtype   = c_dtype;
+    p.bias      = bias;
+    p.residual  = residual;
+    p.gelu      = (epilogue & LYRAQ_EPI_GELU_TANH) ? 1 : 0;
+    p.status    = status_word_ptr();
+    if (p.status == nullptr) {
+        return LYRAQ_ERR_CUDA;
+    }
+    const int sms = device_sm_count();
+    if (sms <= 0) {
+        return LYRAQ_ERR_CUDA;
+    }
+    CUtensorMap ta, tb;
+    int st = make_tmap_bytes_2d(&ta, A, (uint64_t)m, (uint64_t)k / 2, (uint64_t)k / 2, w4::kBM, w4::kPackedRowB, false);
+    if (st != LYRAQ_OK) {
+        return st;
+    }
+    st = make_tmap_bytes_2d(&tb, B, (uint64_t)n, (uint64_t)k / 2, (uint64_t)k / 2, w4::kBN, w4::kPackedRowB, false);
+    if (st != LYRAQ_OK) {
+        return st;
+    }
+    const long tiles = (long)p.m_tiles * p.n_tiles;
+    const int  grid  = (int)(tiles < sms ? tiles : sms);
+    if (cudaFuncSetAttribute(w4::gemm_w4a4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, w4::kSmemTotal) != cudaSuccess) {
+        return LYRAQ_ERR_CUDA;
+    }
+    w4::gemm_w4a4_kernel<<<grid, w4::kThreads, w4::kSmemTotal, (cudaStream_t)stream>>>(ta, tb, p);
+    return launch_status();
+}

@@ -1,0 +1,712 @@
+// Activation / weight quantizers and the fused LayerNorm, AdaLN and GEGLU producers.
+//
+// All of them are HBM-bound row kernels: a team of 32..256 threads owns one row, reads it once
+// with 16-byte loads into registers, reduces what it must (sum, sum of squares, amax) with warp
+// shuffles (plus one shared-memory hop when the team spans several warps), and writes the
+// quantized row once with 8- or 16-byte stores.  Nothing is staged through global memory.
+#include "common.cuh"
+
+namespace lyraq {
+
+enum RowMode { ROW_PLAIN = 0, ROW_ADALN = 1, ROW_LN = 2, ROW_GEGLU = 3 };
+
+struct RowParams {
+    // inputs
+    const void*  x;            // [rows, in_cols]
+    const void*  residual;     // LN: [rows, dim] or null
+    const void*  bias;         // LN: [dim]; GEGLU: [2*dim]; or null
+    const void*  gamma;        // LN
+    const void*  beta;         // LN
+    const void*  ada_scale;    // AdaLN: [B, dim]
+    const void*  ada_shift;    // AdaLN: [B, dim]
+    const float* pre;          // [dim] or null
+    const float* f8_scale;     // [1]
+    // outputs
+    void*    y;                // [rows, dim] of T or null
+    void*    sum_out;          // LN with residual: [rows, dim] of T or null
+    int8_t*  q8;               // [rows, dim] or null
+    float*   q8_scale;         // in (static/per-token) or out (dynamic)
+    uint8_t* qf8;              // [rows, dim] or null
+    int      scale_mode;
+    int      f8_invert;
+    size_t   rows;
+    int      dim;
+    int      in_cols;
+    int      rows_per_batch;   // AdaLN: S
+    float    eps;
+    int      tpr;              // threads per row (32, 64, 128 or 256)
+};
+
+template<bool IS_MAX> __device__ __forceinline__ float warp_reduce(float v)
+{
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        const float o = __shfl_xor_sync(0xffffffffu, v, m);
+        v             = IS_MAX ? fmaxf(v, o) : v + o;
+    }
+    return v;
+}
+
+// Reduction over the tpr threads of a team (tpr is a multiple of 32; a warp belongs to one team).
+// Every thread of the block must call it.
+template<bool IS_MAX> __device__ __forceinline__ float team_reduce(float v, int tpr, float* red)
+{
+    v = warp_reduce<IS_MAX>(v);
+    if (tpr == 32) {
+        return v;
+    }
+    const int warp = threadIdx.x >> 5;
+    if ((threadIdx.x & 31) == 0) {
+        red[warp] = v;
+    }
+    __syncthreads();
+    const int wpt   = tpr >> 5;
+    const int first = (warp / wpt) * wpt;
+    float     r     = red[first];
+    for (int i = 1; i < wpt; ++i) {
+        r = IS_MAX ? fmaxf(r, red[first + i]) : r + red[first + i];
+    }
+    __syncthreads();
+    return r;
+}
+
+template<typename T, int VPT, int MODE> __global__ void __launch_bounds__(256) row_quant_kernel(const RowParams p)
+{
+    __shared__ float red[8];
+
+    const int    tpr   = p.tpr;
+    const int    team  = threadIdx.x / tpr;
+    const int    tlane = threadIdx.x - team * tpr;
+    const size_t row   = (size_t)blockIdx.x * (256 / tpr) + team;
+    const bool   live  = row < p.rows;
+    const int    nvec  = p.dim >> 3;
+
+    float v[VPT][8];
+
+    const T* xrow = reinterpret_cast<const T*>(p.x) + row * (size_t)p.in_cols;
+
+    // ---- load (and, per mode, pre-combine) the row
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int vi = tlane + i * tpr;
+        if (live && vi < nvec) {
+            const int c = vi << 3;
+            unpack8<T>(ld_nc_16(xrow + c), v[i]);
+            if (MODE == ROW_LN && p.residual != nullptr) {
+                float r[8];
+                unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.residual) + row * (size_t)p.dim + c), r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[i][j] = round_t<T>(v[i][j] + r[j]);
+                }
+                if (p.bias != nullptr) {
+                    float b[8];
+                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.bias) + c), b);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        v[i][j] = round_t<T>(v[i][j] + b[j]);
+                    }
+                }
+                if (p.sum_out != nullptr) {
+                    st_16(reinterpret_cast<T*>(p.sum_out) + row * (size_t)p.dim + c, pack8<T>(v[i]));
+                }
+            }
+            if (MODE == ROW_GEGLU) {
+                float g[8];
+                unpack8<T>(ld_nc_16(xrow + p.dim + c), g);
+                if (p.bias != nullptr) {
+                    float bh[8], bg[8];
+                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.bias) + c), bh);
+                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.bias) + p.dim + c), bg);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        v[i][j] = round_t<T>(v[i][j] + bh[j]);
+                        g[j]    = round_t<T>(g[j] + bg[j]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    // GeluActivation<half2>: cube and final product in T, cdf in fp32 then rounded to T.
+                    const float cube = round_t<T>(g[j] * round_t<T>(g[j] * g[j]));
+                    const float cdf  = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (g[j] + 0.044715f * cube)));
+                    const float act  = round_t<T>(g[j] * round_t<T>(cdf));
+                    v[i][j]          = round_t<T>(v[i][j] * act);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[i][j] = 0.0f;
+            }
+        }
+    }
+
+    // ---- row statistics and normalisation
+    if (MODE == ROW_ADALN || MODE == ROW_LN) {
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                s += v[i][j];
+            }
+        }
+        s                = team_reduce<false>(s, tpr, red);
+        const float mean = s / (float)p.dim;
+        float       m2   = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vi = tlane + i * tpr;
+            if (vi < nvec) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float d = v[i][j] - mean;
+                    m2 += d * d;
+                }
+            }
+        }
+        m2               = team_reduce<false>(m2, tpr, red);
+        const float var  = fmaxf(m2 / (float)p.dim, 0.0f);
+        const float rstd = (float)(1.0 / sqrt((double)var + (double)p.eps));
+
+        const size_t brow = (MODE == ROW_ADALN) ? (row / (size_t)p.rows_per_batch) : 0;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vi = tlane + i * tpr;
+            if (live && vi < nvec) {
+                const int c = vi << 3;
+                float     a[8], b[8];
+                if (MODE == ROW_ADALN) {
+                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.ada_scale) + brow * (size_t)p.dim + c), a);
+                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.ada_shift) + brow * (size_t)p.dim + c), b);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float xh  = round_t<T>((v[i][j] - mean) * rstd);
+                        const float sp1 = round_t<T>(a[j] + 1.0f);
+                        v[i][j]         = round_t<T>(round_t<T>(sp1 * xh) + b[j]);
+                    }
+                } else {
+                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.gamma) + c), a);
+                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.beta) + c), b);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float xh = round_t<T>((v[i][j] - mean) * rstd);
+                        v[i][j]        = round_t<T>(round_t<T>(a[j] * xh) + b[j]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- un-quantized copy
+    if (p.y != nullptr) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vi = tlane + i * tpr;
+            if (live && vi < nvec) {
+                st_16(reinterpret_cast<T*>(p.y) + row * (size_t)p.dim + (vi << 3), pack8<T>(v[i]));
+            }
+        }
+    }
+
+    // ---- e4m3, static per-tensor scale
+    if (p.qf8 != nullptr) {
+        const float s = __ldg(p.f8_scale);
+        const float r = p.f8_invert ? 1.0f / s : s;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vi = tlane + i * tpr;
+            if (live && vi < nvec) {
+                uint32_t w[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const uint32_t lo = f32x2_to_e4m3x2(v[i][4 * h] * r, v[i][4 * h + 1] * r);
+                    const uint32_t hi = f32x2_to_e4m3x2(v[i][4 * h + 2] * r, v[i][4 * h + 3] * r);
+                    w[h]              = lo | (hi << 16);
+                }
+                st_8(p.qf8 + row * (size_t)p.dim + (vi << 3), w[0], w[1]);
+            }
+        }
+    }
+
+    // ---- int8
+    if (p.q8 != nullptr) {
+        // apply the SmoothQuant per-channel factor first: (float(x) * pre[c]) / s
+        if (p.pre != nullptr) {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int vi = tlane + i * tpr;
+                if (live && vi < nvec) {
+                    const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
+                    const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
+                    v[i][0] *= p0.x; v[i][1] *= p0.y; v[i][2] *= p0.z; v[i][3] *= p0.w;
+                    v[i][4] *= p1.x; v[i][5] *= p1.y; v[i][6] *= p1.z; v[i][7] *= p1.w;
+                }
+            }
+        }
+        float s;
+        if (p.scale_mode == LYRAQ_SCALE_PER_TOKEN_DYNAMIC) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    amax = fmaxf(amax, fabsf(v[i][j]));
+                }
+            }
+            amax = team_reduce<true>(amax, tpr, red);
+            s    = (amax == 0.0f) ? 1.0f : amax / 127.0f;
+            if (live && tlane == 0) {
+                p.q8_scale[row] = s;
+            }
+        } else if (p.scale_mode == LYRAQ_SCALE_PER_TOKEN) {
+            s = live ? __ldg(p.q8_scale + row) : 1.0f;
+        } else {
+            s = __ldg(p.q8_scale);
+        }
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vi = tlane + i * tpr;
+            if (live && vi < nvec) {
+                int q[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    q[j] = f32_to_s8(v[i][j] / s);
+                }
+                st_8(p.q8 + row * (size_t)p.dim + (vi << 3), pack4_s8(q[0], q[1], q[2], q[3]),
+                     pack4_s8(q[4], q[5], q[6], q[7]));
+            }
+        }
+    }
+}
+
+// Picks the team size and launches.  dim is a multiple of 8 and <= 16384.
+template<typename T, int MODE> static int launch_row(RowParams p, cudaStream_t stream)
+{
+    const int nvec = p.dim >> 3;
+    int       tpr  = 32;
+    while (tpr < 256 && (nvec + tpr - 1) / tpr > 4) {
+        tpr <<= 1;
+    }
+    p.tpr                = tpr;
+    const int    vpt     = (nvec + tpr - 1) / tpr;
+    const size_t per_cta = 256 / tpr;
+    const size_t grid    = (p.rows + per_cta - 1) / per_cta;
+    if (grid == 0) {
+        return LYRAQ_OK;
+    }
+    if (grid > 0x7fffffffu) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    if (vpt <= 4) {
+        row_quant_kernel<T, 4, MODE><<<(unsigned)grid, 256, 0, stream>>>(p);
+    } else if (vpt <= 8) {
+        row_quant_kernel<T, 8, MODE><<<(unsigned)grid, 256, 0, stream>>>(p);
+    } else {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    return launch_status();
+}
+
+template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaStream_t stream)
+{
+    if (p.dim <= 0 || (p.dim & 7) != 0 || p.dim > 16384) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    if (dtype == LYRAQ_F16) {
+        return launch_row<__half, MODE>(p, stream);
+    }
+    if (dtype == LYRAQ_BF16) {
+        return launch_row<__nv_bfloat16, MODE>(p, stream);
+    }
+    return LYRAQ_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Flat per-tensor e4m3 conversion (no row structure): 8 elements per thread per step.
+template<typename T>
+__global__ void __launch_bounds__(256) fp8_cast_kernel(uint8_t* dst, const T* src, const float* scale, int invert, size_t n)
+{
+    const float  s      = __ldg(scale);
+    const float  r      = invert ? 1.0f / s : s;
+    const size_t nvec   = n >> 3;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t vi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; vi < nvec; vi += stride) {
+        float v[8];
+        unpack8<T>(ld_nc_16(src + (vi << 3)), v);
+        const uint32_t w0 = f32x2_to_e4m3x2(v[0] * r, v[1] * r) | (f32x2_to_e4m3x2(v[2] * r, v[3] * r) << 16);
+        const uint32_t w1 = f32x2_to_e4m3x2(v[4] * r, v[5] * r) | (f32x2_to_e4m3x2(v[6] * r, v[7] * r) << 16);
+        st_8(dst + (vi << 3), w0, w1);
+    }
+    // tail (n not a multiple of 8)
+    if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+        const size_t i = (nvec << 3) + threadIdx.x;
+        dst[i]         = (uint8_t)(f32x2_to_e4m3x2(to_f32(src[i]) * r, 0.0f) & 0xff);
+    }
+}
+
+// max|w|/448 folded into scale[0] with an integer atomicMax on the (non-negative) float bits.
+template<typename T> __global__ void __launch_bounds__(256) fp8_amax_kernel(float* scale, const T* src, size_t n)
+{
+    __shared__ float red[8];
+    const size_t     nvec   = n >> 3;
+    const size_t     stride = (size_t)gridDim.x * blockDim.x;
+    float            amax   = 0.0f;
+    for (size_t vi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; vi < nvec; vi += stride) {
+        float v[8];
+        unpack8<T>(ld_nc_16(src + (vi << 3)), v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            amax = fmaxf(amax, fabsf(v[j]));
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
+        amax = fmaxf(amax, fabsf(to_f32(src[(nvec << 3) + threadIdx.x])));
+    }
+    amax = team_reduce<true>(amax, 256, red);
+    if (threadIdx.x == 0) {
+        // |w|/448 is monotone in |w|, so dividing the block maximum equals the maximum of the quotients.
+        atomicMax(reinterpret_cast<int*>(scale), __float_as_int(amax / 448.0f));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// INT4 group-64 quantize: 8 consecutive threads own one group of 64 values, 8 values each.
+template<typename T, typename ST>
+__global__ void __launch_bounds__(256)
+int4_g64_kernel(uint32_t* q, ST* q_scale, const T* x, const float* smooth, size_t rows, int k)
+{
+    const size_t nvec_total = rows * (size_t)(k >> 3);
+    const size_t stride     = (size_t)gridDim.x * blockDim.x;
+    const int    vec_per_row = k >> 3;
+    // the loop bound is rounded up to a multiple of 8 threads so that shuffles stay converged
+    for (size_t base = (size_t)blockIdx.x * blockDim.x; base < nvec_total; base += stride) {
+        const size_t vi   = base + threadIdx.x;
+        const bool   live = vi < nvec_total;
+        float        v[8];
+        if (live) {
+            unpack8<T>(ld_nc_16(x + (vi << 3)), v);
+            if (smooth != nullptr) {
+                const int    c  = (int)(vi % vec_per_row) << 3;
+                const float4 s0 = __ldg(reinterpret_cast<const float4*>(smooth + c));
+                const float4 s1 = __ldg(reinterpret_cast<const float4*>(smooth + c + 4));
+                v[0] /= s0.x; v[1] /= s0.y; v[2] /= s0.z; v[3] /= s0.w;
+                v[4] /= s1.x; v[5] /= s1.y; v[6] /= s1.z; v[7] /= s1.w;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                v[j] = 0.0f;
+            }
+        }
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            amax = fmaxf(amax, fabsf(v[j]));
+        }
+#pragma unroll
+        for (int m = 1; m < 8; m <<= 1) {
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+        }
+        const float s = amax / 7.0f;
+        uint32_t    w = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int qi;
+            // v/s with s == 0 is NaN (or inf); cvt.rni.s32.f32 maps NaN to 0 exactly as the reference's does.
+            asm("cvt.rni.s32.f32 %0, %1;" : "=r"(qi) : "f"(v[j] / s));
+            qi = max(-8, min(7, qi));
+            w |= (uint32_t)(qi & 0xf) << (4 * j);
+        }
+        if (live) {
+            q[vi] = w;
+            if ((threadIdx.x & 7) == 0) {
+                q_scale[vi >> 3] = ST(s);
+            }
+        }
+    }
+}
+
+// INT8 per-output-channel weight quantize: one 128-thread block per row, row kept in registers/re-read.
+template<typename T>
+__global__ void __launch_bounds__(256)
+int8_weight_quant_kernel(float* w_scale, int8_t* qw, const T* w, const float* pre, size_t d_in)
+{
+    __shared__ float red[8];
+    const size_t     row  = blockIdx.x;
+    const T*         wrow = w + row * d_in;
+    float            amax = 0.0f;
+    for (size_t c = threadIdx.x; c < d_in; c += blockDim.x) {
+        float v = to_f32(wrow[c]);
+        if (pre != nullptr) {
+            v = v / __ldg(pre + c);
+        }
+        amax = fmaxf(amax, fabsf(v));
+    }
+    amax          = team_reduce<true>(amax, 256, red);
+    const float s = (float)((double)amax / 127.0);
+    if (threadIdx.x == 0) {
+        w_scale[row] = s;
+    }
+    for (size_t c = threadIdx.x; c < d_in; c += blockDim.x) {
+        float v = to_f32(wrow[c]);
+        if (pre != nullptr) {
+            v = v / __ldg(pre + c);
+        }
+        qw[row * d_in + c] = (int8_t)f32_to_s8(v / s);
+    }
+}
+
+static unsigned flat_grid(size_t nvec)
+{
+    size_t g = (nvec + 255) / 256;
+    // enough blocks to fill 148 SMs eight times over; the kernels are grid-stride
+    const size_t cap = 148 * 8;
+    if (g > cap) {
+        g = cap;
+    }
+    return g == 0 ? 1u : (unsigned)g;
+}
+
+}  // namespace lyraq
+
+using namespace lyraq;
+
+extern "C" {
+
+int lyraq_quant_int8(int8_t* dst, const void* src, int src_dtype, const float* pre_quant_scale, float* scale,
+                     int scale_mode, size_t rows, size_t dim, void* stream)
+{
+    if (dst == nullptr || src == nullptr || scale == nullptr || scale_mode < 0 || scale_mode > 2) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (!aligned16(src) || (reinterpret_cast<uintptr_t>(dst) & 7u) != 0 ||
+        (pre_quant_scale != nullptr && !aligned16(pre_quant_scale))) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (dim > 16384) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    RowParams p{};
+    p.x          = src;
+    p.pre        = pre_quant_scale;
+    p.q8         = dst;
+    p.q8_scale   = scale;
+    p.scale_mode = scale_mode;
+    p.rows       = rows;
+    p.dim        = (int)dim;
+    p.in_cols    = (int)dim;
+    return dispatch_row<ROW_PLAIN>(src_dtype, p, (cudaStream_t)stream);
+}
+
+int lyraq_quant_fp8(uint8_t* dst, const void* src, int src_dtype, const float* scale, int invert_scale, size_t n,
+                    void* stream)
+{
+    if (dst == nullptr || src == nullptr || scale == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (!aligned16(src) || (reinterpret_cast<uintptr_t>(dst) & 7u) != 0) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (n == 0) {
+        return LYRAQ_OK;
+    }
+    const unsigned grid = flat_grid(n >> 3);
+    if (src_dtype == LYRAQ_F16) {
+        fp8_cast_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>(dst, (const __half*)src, scale, invert_scale, n);
+    } else if (src_dtype == LYRAQ_BF16) {
+        fp8_cast_kernel<__nv_bfloat16>
+            <<<grid, 256, 0, (cudaStream_t)stream>>>(dst, (const __nv_bfloat16*)src, scale, invert_scale, n);
+    } else {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    return launch_status();
+}
+
+int lyraq_fp8_amax_scale(float* scale, const void* w, int w_dtype, size_t n, void* stream)
+{
+    if (scale == nullptr || w == nullptr || !aligned16(w)) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (n == 0) {
+        return LYRAQ_OK;
+    }
+    const unsigned grid = flat_grid(n >> 3);
+    if (w_dtype == LYRAQ_F16) {
+        fp8_amax_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>(scale, (const __half*)w, n);
+    } else if (w_dtype == LYRAQ_BF16) {
+        fp8_amax_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(scale, (const __nv_bfloat16*)w, n);
+    } else {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    return launch_status();
+}
+
+int lyraq_weight_quant_int8(float* w_scale, int8_t* qw, const void* w, int w_dtype, const float* pre_quant_scale,
+                            size_t d_out, size_t d_in, void* stream)
+{
+    if (w_scale == nullptr || qw == nullptr || w == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (d_out == 0 || d_in == 0) {
+        return LYRAQ_OK;
+    }
+    if (d_out > 0x7fffffffu) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    if (w_dtype == LYRAQ_F16) {
+        int8_weight_quant_kernel<__half>
+            <<<(unsigned)d_out, 256, 0, (cudaStream_t)stream>>>(w_scale, qw, (const __half*)w, pre_quant_scale, d_in);
+    } else if (w_dtype == LYRAQ_BF16) {
+        int8_weight_quant_kernel<__nv_bfloat16><<<(unsigned)d_out, 256, 0, (cudaStream_t)stream>>>(
+            w_scale, qw, (const __nv_bfloat16*)w, pre_quant_scale, d_in);
+    } else {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    return launch_status();
+}
+
+static int int4_g64_dispatch(uint8_t* q, void* q_scale, int scale_dtype, const void* x, int x_dtype, const float* smooth,
+                             size_t rows, size_t k, cudaStream_t stream)
+{
+    if (q == nullptr || q_scale == nullptr || x == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (!aligned16(x) || (reinterpret_cast<uintptr_t>(q) & 3u) != 0 || (smooth != nullptr && !aligned16(smooth))) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (k == 0 || (k & 63) != 0 || k > 0x7fffffffu) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    if (rows == 0) {
+        return LYRAQ_OK;
+    }
+    const unsigned grid = flat_grid(rows * (k >> 3));
+    uint32_t*      qo   = reinterpret_cast<uint32_t*>(q);
+    if (x_dtype == LYRAQ_BF16 && scale_dtype == LYRAQ_F32) {
+        int4_g64_kernel<__nv_bfloat16, float>
+            <<<grid, 256, 0, stream>>>(qo, (float*)q_scale, (const __nv_bfloat16*)x, smooth, rows, (int)k);
+    } else if (x_dtype == LYRAQ_F16 && scale_dtype == LYRAQ_F32) {
+        int4_g64_kernel<__half, float><<<grid, 256, 0, stream>>>(qo, (float*)q_scale, (const __half*)x, smooth, rows, (int)k);
+    } else if (x_dtype == LYRAQ_BF16 && scale_dtype == LYRAQ_F16) {
+        int4_g64_kernel<__nv_bfloat16, __half>
+            <<<grid, 256, 0, stream>>>(qo, (__half*)q_scale, (const __nv_bfloat16*)x, smooth, rows, (int)k);
+    } else if (x_dtype == LYRAQ_F16 && scale_dtype == LYRAQ_F16) {
+        int4_g64_kernel<__half, __half><<<grid, 256, 0, stream>>>(qo, (__half*)q_scale, (const __half*)x, smooth, rows, (int)k);
+    } else {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    return launch_status();
+}
+
+int lyraq_quant_int4_g64(uint8_t* q, float* q_scale, float* lora_act, const void* x, int x_dtype, const float* smooth,
+                         const void* lora_down, size_t m, size_t k, void* stream)
+{
+    if (lora_act != nullptr || lora_down != nullptr) {
+        return LYRAQ_ERR_UNSUPPORTED;  // low-rank side branch: not built yet
+    }
+    return int4_g64_dispatch(q, q_scale, LYRAQ_F32, x, x_dtype, smooth, m, k, (cudaStream_t)stream);
+}
+
+int lyraq_weight_quant_int4_g64(uint8_t* qw, void* w_scale, int scale_dtype, const void* w, int w_dtype, size_t n,
+                                size_t k, void* stream)
+{
+    return int4_g64_dispatch(qw, w_scale, scale_dtype, w, w_dtype, nullptr, n, k, (cudaStream_t)stream);
+}
+
+int lyraq_adaln_quant(void* y, int8_t* q8, float* q8_scale, uint8_t* qf8, const float* f8_scale, const void* x,
+                      const void* scale, const void* shift, int dtype, const float* pre_quant_scale, size_t B, size_t S,
+                      size_t D, double eps, void* stream)
+{
+    if (x == nullptr || scale == nullptr || shift == nullptr || (q8 != nullptr && q8_scale == nullptr) ||
+        (qf8 != nullptr && f8_scale == nullptr) || (y == nullptr && q8 == nullptr && qf8 == nullptr)) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (!aligned16(x) || !aligned16(scale) || !aligned16(shift) || (y != nullptr && !aligned16(y)) ||
+        (reinterpret_cast<uintptr_t>(q8) & 7u) != 0 || (reinterpret_cast<uintptr_t>(qf8) & 7u) != 0 ||
+        (pre_quant_scale != nullptr && !aligned16(pre_quant_scale))) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (D > 16384 || S == 0 || S > 0x7fffffffu) {
+        return (B * S == 0) ? LYRAQ_OK : LYRAQ_ERR_UNSUPPORTED;
+    }
+    RowParams p{};
+    p.x              = x;
+    p.ada_scale      = scale;
+    p.ada_shift      = shift;
+    p.pre            = pre_quant_scale;
+    p.y              = y;
+    p.q8             = q8;
+    p.q8_scale       = q8_scale;
+    p.scale_mode     = LYRAQ_SCALE_PER_TOKEN_DYNAMIC;
+    p.qf8            = qf8;
+    p.f8_scale       = f8_scale;
+    p.f8_invert      = 1;
+    p.rows           = B * S;
+    p.dim            = (int)D;
+    p.in_cols        = (int)D;
+    p.rows_per_batch = (int)S;
+    p.eps            = (float)eps;
+    return dispatch_row<ROW_ADALN>(dtype, p, (cudaStream_t)stream);
+}
+
+int lyraq_ln_quant_int8(int8_t* dst, void* sum_out, const void* x, const void* residual, const void* bias,
+                        const void* gamma, const void* beta, int dtype, const float* pre_quant_scale,
+                        const float* input_quant_scale, size_t rows, size_t dim, double eps, void* stream)
+{
+    if (dst == nullptr || x == nullptr || gamma == nullptr || beta == nullptr || input_quant_scale == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (!aligned16(x) || !aligned16(gamma) || !aligned16(beta) || (residual != nullptr && !aligned16(residual)) ||
+        (bias != nullptr && !aligned16(bias)) || (sum_out != nullptr && !aligned16(sum_out)) ||
+        (reinterpret_cast<uintptr_t>(dst) & 7u) != 0 || (pre_quant_scale != nullptr && !aligned16(pre_quant_scale))) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (dim > 16384) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    RowParams p{};
+    p.x          = x;
+    p.residual   = residual;
+    p.bias       = bias;
+    p.gamma      = gamma;
+    p.beta       = beta;
+    p.pre        = pre_quant_scale;
+    p.sum_out    = sum_out;
+    p.q8         = dst;
+    p.q8_scale   = const_cast<float*>(input_quant_scale);
+    p.scale_mode = LYRAQ_SCALE_PER_TENSOR;
+    p.rows       = rows;
+    p.dim        = (int)dim;
+    p.in_cols    = (int)dim;
+    p.eps        = (float)eps;
+    return dispatch_row<ROW_LN>(dtype, p, (cudaStream_t)stream);
+}
+
+int lyraq_geglu_quant_int8(int8_t* dst, const void* h, const void* bias, int dtype, const float* pre_quant_scale,
+                           const float* input_quant_scale, size_t rows, size_t dim, void* stream)
+{
+    if (dst == nullptr || h == nullptr || input_quant_scale == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (!aligned16(h) || (bias != nullptr && !aligned16(bias)) || (reinterpret_cast<uintptr_t>(dst) & 7u) != 0 ||
+        (pre_quant_scale != nullptr && !aligned16(pre_quant_scale))) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (dim > 16384) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    RowParams p{};
+    p.x          = h;
+    p.bias       = bias;
+    p.pre        = pre_quant_scale;
+    p.q8         = dst;
+    p.q8_scale   = const_cast<float*>(input_quant_scale);
+    p.scale_mode = LYRAQ_SCALE_PER_TENSOR;
+    p.rows       = rows;
+    p.dim        = (int)dim;
+    p.in_cols    = (int)(2 * dim);
+    return dispatch_row<ROW_GEGLU>(dtype, p, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,92 @@
+"""CPU tests of the drop-in boundary: the C-ABI library loads, exports every symbol the header
+declares, and refuses bad arguments before touching a device (no compute call is made here)."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+from lyradiff_b200 import _lib, build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "lyraq.h")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return _lib.lib()
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    return sorted(set(re.findall(r"LYRAQ_API[^;(]*?\b(lyraq_\w+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_symbols()
+    for required in ("lyraq_quant_int8", "lyraq_quant_fp8", "lyraq_quant_int4_g64", "lyraq_adaln_quant",
+                     "lyraq_ln_quant_int8", "lyraq_geglu_quant_int8", "lyraq_gemm_int8", "lyraq_gemm_fp8",
+                     "lyraq_gemm_w4a4", "lyraq_weight_quant_int8", "lyraq_weight_quant_int4_g64",
+                     "lyraq_fp8_amax_scale", "lyraq_workspace_bytes", "lyraq_last_status"):
+        assert required in names
+
+
+def test_library_exports_every_declared_symbol(lib):
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in declared_symbols():
+        assert hasattr(raw, name), name
+
+
+def test_python_signatures_cover_the_header(lib):
+    assert sorted(_lib.SIGNATURES) == declared_symbols()
+
+
+def test_every_declaration_cites_the_reference():
+    text = open(HEADER).read()
+    # each entry point's comment either names a reference file:line or says there is no counterpart
+    blocks = re.findall(r"/\*((?:(?!\*/).)*?)\*/\s*LYRAQ_API[^;]*?\b(lyraq_\w+)\s*\(", text, flags=re.S)
+    assert len(blocks) >= 14
+    for comment, name in blocks:
+        assert ("src/lyradiff" in comment or "lyradiff/" in comment or "no counterpart" in comment
+                or "int8_gemm_template.h" in comment), name
+
+
+def test_status_strings_and_version(lib):
+    assert lib.lyraq_version().decode().startswith("lyraq")
+    assert lib.lyraq_status_string(0) == b"ok"
+    assert b"unknown" in lib.lyraq_status_string(99)
+    assert lib.lyraq_workspace_bytes(0, 128, 128, 128) == 0
+
+
+def test_bad_arguments_are_refused_without_a_device(lib):
+    INVALID, UNSUPPORTED = 1, 2
+    # null pointers
+    assert lib.lyraq_quant_int8(None, None, 0, None, None, 0, 4, 64, None) == INVALID
+    assert lib.lyraq_quant_fp8(None, None, 1, None, 1, 64, None) == INVALID
+    assert lib.lyraq_gemm_int8(None, None, None, None, 0, None, 0, None, 128, 128, 128, None, 0, None) == INVALID
+    assert lib.lyraq_gemm_fp8(None, None, None, None, None, 1, None, None, 1.0, 0.0, 0, 128, 128, 128, None, 0, None) == INVALID
+    assert lib.lyraq_gemm_w4a4(None, None, None, None, 2, None, 1, None, None, None, None, 0, 128, 128, 128, None, 0, None) == INVALID
+    # fake but well-aligned addresses: shape checks come before any launch
+    p = 0x1000
+    assert lib.lyraq_quant_int8(p, p, 0, None, p, 0, 4, 60, None) == UNSUPPORTED       # dim % 8
+    assert lib.lyraq_quant_int8(p, p, 0, None, p, 0, 4, 32768, None) == UNSUPPORTED    # dim too large
+    assert lib.lyraq_quant_int8(p, p, 2, None, p, 0, 4, 64, None) == UNSUPPORTED       # fp32 source
+    assert lib.lyraq_quant_int8(p, p + 2, 0, None, p, 0, 4, 64, None) == INVALID       # misaligned source
+    assert lib.lyraq_quant_int8(p, p, 0, None, p, 7, 4, 64, None) == INVALID           # bad scale mode
+    assert lib.lyraq_quant_int4_g64(p, p, None, p, 1, None, None, 4, 96, None) == UNSUPPORTED  # k % 64
+    assert lib.lyraq_gemm_int8(p, p, p, p, 0, p, 0, None, 128, 128, 120, None, 0, None) == UNSUPPORTED  # k % 16
+    assert lib.lyraq_gemm_int8(p, p, p, p, 5, p, 0, None, 128, 128, 128, None, 0, None) == INVALID
+    assert lib.lyraq_gemm_fp8(p, p, p, p, p, 3, None, None, 1.0, 0.0, 0, 128, 128, 128, None, 0, None) == INVALID
+    assert lib.lyraq_gemm_w4a4(p, p, p, p, 2, p, 1, None, None, None, None, 0, 128, 128, 96, None, 0, None) == UNSUPPORTED
+    # empty problems are a no-op
+    assert lib.lyraq_gemm_int8(p, p, p, p, 0, p, 0, None, 0, 128, 128, None, 0, None) == 0
+    assert lib.lyraq_quant_fp8(p, p, 1, p, 1, 0, None) == 0
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(ImportError):
+        _lib.lib()

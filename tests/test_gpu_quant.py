@@ -1,0 +1,259 @@
+"""GPU parity tests of the quantize / fused-producer kernels against the CPU oracle, through the C ABI."""
+
+import pytest
+import torch
+
+from oracle import norms, quant, workloads
+from tests.util import assert_bit_equal, check_status, cu, mismatch_fraction
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from lyradiff_b200 import ops as _ops
+    return _ops
+
+
+def _x(rows, dim, dtype, seed, outliers=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, dim, generator=g)
+    if outliers and dim >= 20:
+        x[:, torch.randperm(dim, generator=g)[: dim // 20]] *= 20.0
+    pre = (0.25 + torch.rand(dim, generator=g)).float()
+    return x.to(dtype), pre
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,dim", [(1, 8), (7, 64), (129, 640), (33, 3072), (5, 5120), (3, 16384), (260, 1280)])
+def test_int8_quant_all_scale_modes_bit_exact(ops, dtype, rows, dim):
+    x, pre = _x(rows, dim, dtype, seed=rows * 31 + dim)
+    xd, pred = cu(x), cu(pre)
+    # static per-tensor scale (the reference's sqInputQuant)
+    s = torch.tensor([0.043], dtype=torch.float32)
+    q = torch.empty(rows, dim, dtype=torch.int8, device="cuda")
+    ops.invoke_sq_input_quant(q, xd, pred, cu(s))
+    assert_bit_equal(q, quant.sq_input_quant(x, pre, s), "static")
+    # precomputed per-token scales (sqPerTokenInputQuant)
+    st = (0.01 + torch.rand(rows)).float()
+    ops.invoke_sq_input_quant(q, xd, pred, cu(st), per_token=True)
+    assert_bit_equal(q, quant.sq_input_quant(x, pre, st, per_token=True), "per-token")
+    # dynamic per-token
+    sd = torch.empty(rows, dtype=torch.float32, device="cuda")
+    ops.invoke_sq_input_quant(q, xd, pred, sd, dynamic=True)
+    q_ref, s_ref = quant.sq_input_quant_dynamic(x, pre)
+    assert_bit_equal(sd, s_ref, "dynamic scale")
+    assert_bit_equal(q, q_ref, "dynamic q")
+    # without the smoothing vector
+    ops.invoke_sq_input_quant(q, xd, None, sd, dynamic=True)
+    q_ref, s_ref = quant.sq_input_quant_dynamic(x, None)
+    assert_bit_equal(sd, s_ref, "dynamic scale, no pre")
+    assert_bit_equal(q, q_ref, "dynamic q, no pre")
+
+
+def test_int8_quant_zero_rows_and_empty(ops):
+    x = torch.zeros(4, 64, dtype=torch.float16)
+    x[2] = torch.linspace(-2, 2, 64).half()
+    q = torch.full((4, 64), 99, dtype=torch.int8, device="cuda")
+    s = torch.empty(4, dtype=torch.float32, device="cuda")
+    ops.invoke_sq_input_quant(q, cu(x), None, s, dynamic=True)
+    q_ref, s_ref = quant.sq_input_quant_dynamic(x, None)
+    assert_bit_equal(q, q_ref)
+    assert_bit_equal(s, s_ref)
+    assert s.cpu()[0].item() == 1.0
+    # zero rows: nothing is launched, nothing fails
+    ops.invoke_sq_input_quant(torch.empty(0, 64, dtype=torch.int8, device="cuda"),
+                              torch.empty(0, 64, dtype=torch.float16, device="cuda"), None, s, dynamic=True)
+    with pytest.raises(Exception):
+        ops.invoke_sq_input_quant(q, cu(torch.zeros(4, 60, dtype=torch.float16)), None, s, dynamic=True)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n", [8, 1000, 4608 * 64 + 3, 1 << 20])
+def test_fp8_quant_bit_exact(ops, dtype, n):
+    g = torch.Generator().manual_seed(n)
+    x = (torch.randn(n, generator=g) * 3.0).to(dtype)
+    x[:: 97] *= 200.0  # exercise saturation to +-448
+    s = torch.tensor([0.0371], dtype=torch.float32)
+    q = torch.empty(n, dtype=torch.uint8, device="cuda")
+    ops.invoke_cuda_d2d_scale_cpy_convert(q, cu(x), cu(s), invert_scale=True)
+    assert_bit_equal(q, quant.fp8_quant(x, s, True), "invert")
+    ops.invoke_cuda_d2d_scale_cpy_convert(q, cu(x), cu(s), invert_scale=False)
+    assert_bit_equal(q, quant.fp8_quant(x, s, False), "direct")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fp8_weight_amax_scale_exact(ops, dtype):
+    g = torch.Generator().manual_seed(5)
+    w = (torch.randn(3072 * 96 + 5, generator=g) * 0.02).to(dtype)
+    s = torch.zeros(1, dtype=torch.float32, device="cuda")
+    ops.invoke_get_fp8_weight_scale(s, cu(w))
+    assert_bit_equal(s, quant.fp8_amax_scale(w))
+    # a second, smaller tensor leaves the running maximum alone
+    ops.invoke_get_fp8_weight_scale(s, cu((w * 0.5).to(dtype)))
+    assert_bit_equal(s, quant.fp8_amax_scale(w))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,k", [(1, 64), (24, 128), (130, 3072), (5, 12288)])
+def test_int4_g64_quant_bit_exact(ops, dtype, m, k):
+    g = torch.Generator().manual_seed(m * 7 + k)
+    x = torch.randn(m, k, generator=g).to(dtype)
+    x[0, :64] = 0  # an all-zero group
+    smooth = (0.5 + torch.rand(k, generator=g)).float()
+    for sm in (smooth, None):
+        q = torch.empty(m, k // 2, dtype=torch.uint8, device="cuda")
+        s = torch.empty(m, k // 64, dtype=torch.float32, device="cuda")
+        ops.invoke_fused_quantize_and_lora_down_simple(None, q, s, cu(x), None, cu(sm))
+        p_ref, s_ref, _ = quant.int4_quant_g64(x, sm)
+        assert_bit_equal(s, s_ref, "scales")
+        assert_bit_equal(q, p_ref, "packed nibbles")
+
+
+@pytest.mark.parametrize("scale_dtype", [torch.float32, torch.float16])
+def test_int4_weight_quant_bit_exact(ops, scale_dtype):
+    w = workloads.w4a4_linear(m=8, k=256, n=72, seed=3)["w"]
+    q = torch.empty(72, 128, dtype=torch.uint8, device="cuda")
+    s = torch.empty(72, 4, dtype=scale_dtype, device="cuda")
+    ops.weight_quant_int4_g64(q, s, cu(w))
+    p_ref, s_ref, _ = quant.int4_weight_quant_g64(w)
+    assert_bit_equal(q, p_ref)
+    assert_bit_equal(s, s_ref.to(scale_dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_int8_weight_quant_bit_exact(ops, dtype):
+    g = torch.Generator().manual_seed(9)
+    w = (torch.randn(70, 650, generator=g) * 0.02).to(dtype)
+    w[3] = 0
+    pre = (0.25 + torch.rand(650, generator=g)).float()
+    for p in (pre, None):
+        qw = torch.empty(70, 650, dtype=torch.int8, device="cuda")
+        sw = torch.empty(70, dtype=torch.float32, device="cuda")
+        ops.invoke_get_int8_weight_scale(sw, qw, cu(w), cu(p))
+        q_ref, s_ref = quant.int8_weight_quant_device(w, p)
+        assert_bit_equal(sw, s_ref)
+        assert_bit_equal(qw, q_ref)
+
+
+# Row statistics are summed in a different order on the device (fp32 shuffles) than in the oracle
+# (fp64), so a value sitting on a rounding boundary may land one step away.  Stated tolerance:
+# at most 1 LSB (int8) / 1 code (e4m3) / 1 ulp (16-bit y) on at most 0.1 % of the outputs.
+def _close(got, want, frac=1e-3):
+    got = got.cpu()
+    d = (got.to(torch.int32) - want.to(torch.int32)).abs()
+    assert int(d.max()) <= 1, int(d.max())
+    assert float((d != 0).float().mean()) <= frac
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,s,d", [(1, 37, 3072), (3, 11, 128), (2, 130, 1536), (8, 16, 3072)])
+def test_adaln_quant_against_oracle(ops, dtype, b, s, d):
+    a = workloads.adaln_input(b=b, s=s, d=d, seed=b * 100 + s, dtype=dtype)
+    f8 = torch.tensor([0.02], dtype=torch.float32)
+    ref = norms.adaln_quant(a["x"], a["scale"], a["shift"], fp8_scale=f8)
+    y = torch.empty(b, s, d, dtype=dtype, device="cuda")
+    q8 = torch.empty(b * s, d, dtype=torch.int8, device="cuda")
+    s8 = torch.empty(b * s, dtype=torch.float32, device="cuda")
+    qf8 = torch.empty(b * s, d, dtype=torch.uint8, device="cuda")
+    ops.invoke_layer_norm_with_shift_and_scale(y, cu(a["x"]), cu(a["scale"]), cu(a["shift"]), 1e-6, q8=q8, q8_scale=s8,
+                                               qf8=qf8, f8_scale=cu(f8))
+    _close(y.view(torch.int16), ref["y"].view(torch.int16))
+    # rows whose dynamic scale agrees bit for bit must agree on q8 up to the same slack
+    same = (s8.cpu().view(torch.int32) == ref["s8"].view(torch.int32))
+    assert float(same.float().mean()) >= 0.99
+    _close(q8.cpu()[same], ref["q8"][same])
+    # e4m3 codes: compare as sign-magnitude integers
+    got = qf8.cpu().to(torch.int32)
+    want = ref["qf8"].to(torch.int32)
+    d_ = ((got & 0x7F) - (want & 0x7F)).abs()
+    assert int(d_.max()) <= 1 and float((got != want).float().mean()) <= 1e-3
+    # quantized-only call (no y) gives the same bytes
+    q8b = torch.empty_like(q8)
+    s8b = torch.empty_like(s8)
+    ops.invoke_layer_norm_with_shift_and_scale(None, cu(a["x"]), cu(a["scale"]), cu(a["shift"]), 1e-6, q8=q8b, q8_scale=s8b)
+    assert torch.equal(q8b, q8) and torch.equal(s8b, s8)
+
+
+def test_adaln_golden(ops, golden):
+    z = golden("adaln")
+    b, s, d = z["x"].shape
+    y = torch.empty(b, s, d, dtype=torch.bfloat16, device="cuda")
+    q8 = torch.empty(b * s, d, dtype=torch.int8, device="cuda")
+    s8 = torch.empty(b * s, dtype=torch.float32, device="cuda")
+    qf8 = torch.empty(b * s, d, dtype=torch.uint8, device="cuda")
+    ops.invoke_layer_norm_with_shift_and_scale(y, cu(z["x"]), cu(z["scale"]), cu(z["shift"]), 1e-6, q8=q8, q8_scale=s8,
+                                               qf8=qf8, f8_scale=cu(z["f8_scale"]))
+    _close(y.view(torch.int16), z["y"].view(torch.int16), frac=5e-3)
+    _close(q8, z["q8"], frac=5e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,dim", [(9, 64), (130, 320), (64, 640), (17, 1280), (5, 1024)])
+def test_layernorm_int8_against_oracle(ops, dtype, rows, dim):
+    g = torch.Generator().manual_seed(rows + dim)
+    x = torch.randn(rows, dim, generator=g).to(dtype)
+    res = torch.randn(rows, dim, generator=g).to(dtype)
+    bias = (torch.randn(dim, generator=g) * 0.1).to(dtype)
+    gamma = (1.0 + 0.1 * torch.randn(dim, generator=g)).to(dtype)
+    beta = (0.1 * torch.randn(dim, generator=g)).to(dtype)
+    pre = (0.5 + torch.rand(dim, generator=g)).float()
+    s = torch.tensor([0.03], dtype=torch.float32)
+    q = torch.empty(rows, dim, dtype=torch.int8, device="cuda")
+    ops.invoke_layer_norm_int8o(q, cu(x), cu(gamma), cu(beta), cu(pre), cu(s), 1e-5)
+    _close(q, norms.layernorm_int8(x, gamma, beta, pre, s)[0])
+    hsum = torch.empty(rows, dim, dtype=dtype, device="cuda")
+    ops.invoke_layer_norm_int8o(q, cu(x), cu(gamma), cu(beta), cu(pre), cu(s), 1e-5, residual=cu(res), bias=cu(bias),
+                                sum_out=hsum)
+    q_ref, h_ref = norms.layernorm_int8(x, gamma, beta, pre, s, residual=res, bias=bias)
+    assert_bit_equal(hsum, h_ref, "x + residual + bias")
+    _close(q, q_ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,dim", [(9, 64), (33, 1280), (8, 2560), (3, 5120)])
+def test_geglu_int8_against_oracle(ops, dtype, rows, dim):
+    g = torch.Generator().manual_seed(rows * 3 + dim)
+    h = torch.randn(rows, 2 * dim, generator=g).to(dtype)
+    b2 = (torch.randn(2 * dim, generator=g) * 0.1).to(dtype)
+    pre = (0.5 + torch.rand(dim, generator=g)).float()
+    s = torch.tensor([0.02], dtype=torch.float32)
+    q = torch.empty(rows, dim, dtype=torch.int8, device="cuda")
+    ops.invoke_fused_add_bias_geglu_int8o(q, cu(h), cu(b2), cu(pre), cu(s))
+    # the device tanh is tanh.approx.f32 (as in the reference): 1 LSB on a small fraction
+    _close(q, norms.geglu_int8(h, b2, pre, s), frac=2e-2)
+    ops.invoke_fused_add_bias_geglu_int8o(q, cu(h), None, cu(pre), cu(s))
+    _close(q, norms.geglu_int8(h, None, pre, s), frac=2e-2)
+
+
+def test_ln_geglu_golden(ops, golden):
+    z = golden("ln_geglu")
+    rows, dim = z["x"].shape
+    q = torch.empty(rows, dim, dtype=torch.int8, device="cuda")
+    ops.invoke_layer_norm_int8o(q, cu(z["x"]), cu(z["gamma"]), cu(z["beta"]), cu(z["pre"]), cu(z["scale"]), 1e-5)
+    _close(q, z["q_ln"], frac=1e-2)
+    ops.invoke_fused_add_bias_geglu_int8o(q, cu(z["h"]), cu(z["b2"]), cu(z["pre"]), cu(z["scale"]))
+    _close(q, z["q_geglu"], frac=3e-2)
+
+
+def test_adaln_full_size_properties(ops):
+    """BASELINE configuration 4 at full size: dequantized int8 reproduces y within half a step per token,
+    and the e4m3 output decodes to y within e4m3 spacing."""
+    a = workloads.adaln_input(b=1, s=4608, d=3072, seed=0)
+    xd, sc, sh = cu(a["x"]), cu(a["scale"]), cu(a["shift"])
+    y = torch.empty(1, 4608, 3072, dtype=torch.bfloat16, device="cuda")
+    q8 = torch.empty(4608, 3072, dtype=torch.int8, device="cuda")
+    s8 = torch.empty(4608, dtype=torch.float32, device="cuda")
+    qf8 = torch.empty(4608, 3072, dtype=torch.uint8, device="cuda")
+    f8 = torch.tensor([8.0 / 448.0], dtype=torch.float32)
+    ops.invoke_layer_norm_with_shift_and_scale(y, xd, sc, sh, 1e-6, q8=q8, q8_scale=s8, qf8=qf8, f8_scale=cu(f8))
+    yf = y.view(4608, 3072).float()
+    assert float((q8.float() * s8[:, None] - yf).abs().max() / s8.max()) <= 0.5 + 1e-3
+    assert torch.equal(s8, yf.abs().amax(dim=1) / 127.0)
+    dec = qf8.view(torch.float8_e4m3fn).float() * f8.cuda()
+    assert float(((dec - yf).abs() / yf.abs().clamp_min(0.05)).max()) <= 0.0626 + 1e-3
+    # oracle on a sample of rows
+    rows = torch.arange(0, 4608, 97)
+    ref = norms.adaln_quant(a["x"][:, rows], a["scale"], a["shift"], fp8_scale=f8)
+    _close(q8.cpu()[rows], ref["q8"], frac=2e-3)
+    check_status()
