@@ -1,17 +1,21 @@
 #!/usr/bin/env python
 """Benchmark of the quantized-linear hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--case NAME] [--tokens M]
 
-Workload (N=1 and per rank at N>1): the four FP8 e4m3 FLUX.1-dev-shaped linears at M = 4608 tokens
-(QKV 3072->9216, out-proj 3072->3072, MLP-up 3072->12288 + tanh-GELU, MLP-down 12288->3072 + residual).
-One step = for each linear: per-tensor e4m3 activation quantize (bf16 -> e4m3) + the tcgen05 FP8 GEMM with
-its fused epilogue.  Synthetic seeded inputs, random weights.  Prints ONE JSON line (rank 0).
+Default case `flux_fp8` (the headline; N=1 and per rank at N>1): the four FP8 e4m3 FLUX.1-dev-shaped linears at
+M = 4608 tokens (QKV 3072->9216, out-proj 3072->3072, MLP-up 3072->12288 + tanh-GELU, MLP-down 12288->3072 +
+residual).  One step = for each linear: per-tensor e4m3 activation quantize (bf16 -> e4m3) + the tcgen05 FP8 GEMM
+with its fused epilogue.  Other cases time the remaining configurations with the same harness:
+    int8_sdxl    SDXL GEGLU-FF INT8 SmoothQuant linear, M=8192 K=640 N=5120 (dynamic per-token quantize + GEMM)
+    w4a4         FLUX fused W4A4 linear, M=4608 K=3072 N=21504 (int4 group-64 quantize + GEMM)
+    adaln_quant  fused AdaLN-modulation + int8 and e4m3 quantize of [4608, 3072] bf16
+`--tokens` shrinks M (for profiler captures).  Synthetic seeded inputs, random weights.  Rank 0 prints ONE JSON line.
 
-`value` is whole-job TFLOP/s with inputs resident in HBM; `e2e` is the same metric through the public
-API from pinned HOST buffers (H2D of the step's activations and D2H of its result inside the timed region).
-`--impl reference` times the CPU restatement of the reference's arithmetic (the oracle port, torch on all
-host cores) on a bounded row sample of the same workload.
+`value` is whole-job throughput with inputs resident in HBM; `e2e` is the same metric through the public API from
+pinned HOST buffers (H2D of the step's activations and D2H of its result inside the timed region).
+`--impl reference` times the CPU restatement of the reference's arithmetic (the oracle port, torch on all host
+cores) on a bounded row sample of the same workload.
 """
 
 import argparse
@@ -25,21 +29,6 @@ import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
-
-TOKENS = 4608
-HIDDEN = 3072
-LINEARS = (
-    # name, K, N, gelu, residual
-    ("qkv", 3072, 9216, False, False),
-    ("out_proj", 3072, 3072, False, False),
-    ("mlp_up_gelu", 3072, 12288, True, False),
-    ("mlp_down_residual", 12288, 3072, False, True),
-)
-FLOP_PER_STEP = sum(2.0 * TOKENS * k * n for _, k, n, _, _ in LINEARS)
-WORKLOAD = ("configs[1]: FP8 e4m3 FLUX.1-dev linears, M=4608 tokens, hidden 3072: QKV 3072->9216, out-proj 3072->3072, "
-            "MLP-up 3072->12288 +GELU-tanh, MLP-down 12288->3072 +residual; per-tensor e4m3 activation quantize before each")
-METRIC = "fp8_flux_linears_throughput"
-UNIT = "TFLOP/s"
 
 
 def load_peaks():
@@ -58,7 +47,6 @@ class ClockSampler(threading.Thread):
 
     def __init__(self, index):
         super().__init__(daemon=True)
-        self.index = index
         self.samples = []
         self.reasons = set()
         self.max_mhz = None
@@ -78,12 +66,7 @@ class ClockSampler(threading.Thread):
         if not self.ok:
             return
         nv = self.nv
-        names = {
-            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
-            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
-            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
-            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
-        }
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
         while not self.stop_flag.is_set():
             try:
                 self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
@@ -96,99 +79,50 @@ class ClockSampler(threading.Thread):
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.02)
+            time.sleep(0.001)
 
     def result(self):
         self.stop_flag.set()
         if not self.ok or not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
         s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+        return {"sm_mhz": s[len(s) // 2], "sm_min_mhz": s[0], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
 
 
-# ------------------------------------------------------------------------------------------------ CPU baseline
-def cpu_reference_step(state):
-    """One pass of the reference arithmetic on the host over the row sample: quantize + e4m3 GEMM (fp32 upcast matmul)
-    + epilogue, for each of the four linears."""
-    from oracle import gemm as ogemm
-    from oracle import quant as oquant
-    outs = {}
-    for name, k, n, gelu, residual in LINEARS:
-        lin = state[name]
-        x = outs["mlp_up_gelu"] if name == "mlp_down_residual" else lin["x"]
-        qx = oquant.fp8_quant(x, lin["s_x"])
-        xf = oquant.fp8_dequant(qx)
-        acc = xf @ lin["w_f32_t"]
-        v = acc * (float(lin["s_x"]) * float(lin["s_w"]))
-        if residual:
-            v = v + lin["residual"].float()
-        v = v + lin["bias"].float()
-        if gelu:
-            v = ogemm.gelu_tanh(v)
-        outs[name] = v.to(torch.bfloat16)
-    return outs
+def _gen(seed=0):
+    return torch.Generator().manual_seed(seed)
 
 
-def make_cpu_state(rows, seed=0):
-    from oracle import quant as oquant
-    g = torch.Generator().manual_seed(seed)
-    state = {}
-    for name, k, n, gelu, residual in LINEARS:
-        x = torch.randn(rows, k, generator=g).bfloat16()
-        w = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
-        s_w = oquant.fp8_amax_scale(w)
-        qw = oquant.fp8_quant(w, s_w)
-        state[name] = {
-            "x": x, "s_x": torch.tensor([6.0 / 448.0]), "s_w": s_w,
-            "w_f32_t": oquant.fp8_dequant(qw).t().contiguous(),
-            "bias": (torch.randn(n, generator=g) * 0.02).bfloat16(),
-            "residual": torch.randn(rows, n, generator=g).bfloat16() if residual else None,
-        }
-    return state
+# =================================================================================================== cases
+class FluxFp8:
+    """configs[1]: the four FP8 FLUX linears."""
+    name = "flux_fp8"
+    metric = "fp8_flux_linears_throughput"
+    unit = "TFLOP/s"
+    dtype = "f8e4m3 (fp32 accumulate in TMEM)"
+    LINEARS = (("qkv", 3072, 9216, False, False), ("out_proj", 3072, 3072, False, False),
+               ("mlp_up_gelu", 3072, 12288, True, False), ("mlp_down_residual", 12288, 3072, False, True))
 
+    def __init__(self, tokens):
+        self.tokens = tokens or 4608
+        self.work_per_step = sum(2.0 * self.tokens * k * n for _, k, n, _, _ in self.LINEARS)  # FLOP
+        self.scale = 1e12
+        self.workload = ("configs[1]: FP8 e4m3 FLUX.1-dev linears, M=%d tokens, hidden 3072: QKV 3072->9216, out-proj "
+                         "3072->3072, MLP-up 3072->12288 +GELU-tanh, MLP-down 12288->3072 +residual; per-tensor e4m3 "
+                         "activation quantize before each" % self.tokens)
+        self.launches_per_step = 2 * len(self.LINEARS)
+        self.timed_names = [l[0] for l in self.LINEARS]
+        self.timed_work = [2.0 * self.tokens * k * n for _, k, n, _, _ in self.LINEARS]
+        self.roof = {"bound": "tensor", "unit": "TFLOP/s", "kernel": "gemm_tcgen05_kernel<f8f6f4> (4 launches per step, one per linear)"}
 
-def time_cpu_reference(rows, steps, warmup):
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    state = make_cpu_state(rows)
-    for _ in range(warmup):
-        cpu_reference_step(state)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        cpu_reference_step(state)
-    dt = (time.perf_counter() - t0) / steps
-    flop = FLOP_PER_STEP * rows / TOKENS
-    return {"value": flop / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": "%d of %d token rows through all four linears per step (quantize + e4m3 GEMM as fp32 upcast matmul "
-                      "+ epilogue), torch on %d threads, %d timed steps" % (rows, TOKENS, cores, steps),
-            "ms_per_step_sample": dt * 1e3}
-
-
-def run_reference(args, rank, world):
-    if rank != 0:
-        return
-    rows = 512
-    base = time_cpu_reference(rows, max(1, args.steps), max(1, min(args.warmup, 3)))
-    line = {
-        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": base["ms_per_step_sample"] * TOKENS / rows, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f8e4m3 (fp32 accumulate) on CPU", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "note": "CPU restatement of the reference arithmetic on a bounded row sample; "
-                   "ms_per_step is the sample time scaled to all 4608 rows"},
-        "cpu_baseline": base,
-        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }
-    print(json.dumps(line), flush=True)
-
-
-# ------------------------------------------------------------------------------------------------ GPU arm
-class GpuState:
-    def __init__(self, dev, seed=0):
+    def setup_gpu(self, dev):
         from lyradiff_b200 import ops
         self.ops = ops
-        g = torch.Generator().manual_seed(seed)
+        g = _gen()
+        T = self.tokens
         self.lin = {}
-        for name, k, n, gelu, residual in LINEARS:
+        for name, k, n, gelu, residual in self.LINEARS:
             w = (torch.randn(n, k, generator=g) * 0.02).bfloat16().to(dev)
             s_w = torch.zeros(1, dtype=torch.float32, device=dev)
             ops.invoke_get_fp8_weight_scale(s_w, w)
@@ -196,41 +130,340 @@ class GpuState:
             ops.invoke_cuda_d2d_scale_cpy_convert(qw, w, s_w)
             del w
             self.lin[name] = {
-                "k": k, "n": n, "gelu": gelu,
-                "x": torch.randn(TOKENS, k, generator=g).bfloat16().to(dev) if name != "mlp_down_residual" else None,
-                "qx": torch.empty(TOKENS, k, dtype=torch.uint8, device=dev),
+                "x": torch.randn(T, k, generator=g).bfloat16().to(dev) if name != "mlp_down_residual" else None,
+                "qx": torch.empty(T, k, dtype=torch.uint8, device=dev),
                 "s_x": torch.tensor([6.0 / 448.0], dtype=torch.float32, device=dev),
                 "qw": qw, "s_w": s_w,
                 "bias": (torch.randn(n, generator=g) * 0.02).bfloat16().to(dev),
-                "residual": torch.randn(TOKENS, n, generator=g).bfloat16().to(dev) if residual else None,
-                "y": torch.empty(TOKENS, n, dtype=torch.bfloat16, device=dev),
+                "residual": torch.randn(T, n, generator=g).bfloat16().to(dev) if residual else None,
+                "y": torch.empty(T, n, dtype=torch.bfloat16, device=dev),
             }
-        self.launches_per_step = 2 * len(LINEARS)
-        # host side of the end-to-end path
-        self.h_x = torch.randn(TOKENS, HIDDEN, generator=g).bfloat16().pin_memory()
-        self.h_y = torch.empty(TOKENS, HIDDEN, dtype=torch.bfloat16).pin_memory()
+        self.h_in = torch.randn(T, 3072, generator=g).bfloat16().pin_memory()
+        self.h_out = torch.empty(T, 3072, dtype=torch.bfloat16).pin_memory()
 
-    def step(self, gemm_events=None):
+    def step(self, events=None):
         ops = self.ops
-        for i, (name, k, n, gelu, residual) in enumerate(LINEARS):
+        for i, (name, k, n, gelu, residual) in enumerate(self.LINEARS):
             L = self.lin[name]
             x = self.lin["mlp_up_gelu"]["y"] if name == "mlp_down_residual" else L["x"]
             ops.invoke_cuda_d2d_scale_cpy_convert(L["qx"], x, L["s_x"])
-            if gemm_events is not None:
-                gemm_events[i][0].record()
+            if events is not None:
+                events[i][0].record()
             ops.gemm_with_residual_and_bias_fp8(L["qw"], L["s_w"], L["qx"], L["s_x"], L["y"], bias=L["bias"],
                                                 residual=L["residual"], is_gelu=gelu)
-            if gemm_events is not None:
-                gemm_events[i][1].record()
+            if events is not None:
+                events[i][1].record()
 
     def step_e2e(self):
-        # the step's activations arrive from the host, its result goes back to the host
-        self.lin["qkv"]["x"].copy_(self.h_x, non_blocking=True)
+        self.lin["qkv"]["x"].copy_(self.h_in, non_blocking=True)
         self.step()
-        self.h_y.copy_(self.lin["mlp_down_residual"]["y"], non_blocking=True)
+        self.h_out.copy_(self.lin["mlp_down_residual"]["y"], non_blocking=True)
+
+    def peak(self, peaks):
+        return 2.0 * peaks["bf16_sustained"], ("2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s): dense FP8 runs at "
+                                               "twice the bf16 rate; nominal dense FP8 is 4500" % peaks["source"]), 4500.0
+
+    # ---- CPU restatement on a row sample
+    def setup_cpu(self, rows):
+        from oracle import quant as oq
+        g = _gen()
+        self.cpu = {}
+        for name, k, n, gelu, residual in self.LINEARS:
+            w = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+            s_w = oq.fp8_amax_scale(w)
+            self.cpu[name] = {"x": torch.randn(rows, k, generator=g).bfloat16(), "s_x": torch.tensor([6.0 / 448.0]), "s_w": s_w,
+                              "w_t": oq.fp8_dequant(oq.fp8_quant(w, s_w)).t().contiguous(),
+                              "bias": (torch.randn(n, generator=g) * 0.02).bfloat16(),
+                              "residual": torch.randn(rows, n, generator=g).bfloat16() if residual else None}
+        self.cpu_rows = rows
+
+    def step_cpu(self):
+        from oracle import gemm as og
+        from oracle import quant as oq
+        outs = {}
+        for name, k, n, gelu, residual in self.LINEARS:
+            L = self.cpu[name]
+            x = outs["mlp_up_gelu"] if name == "mlp_down_residual" else L["x"]
+            xf = oq.fp8_dequant(oq.fp8_quant(x, L["s_x"]))
+            v = (xf @ L["w_t"]) * (float(L["s_x"]) * float(L["s_w"]))
+            if residual:
+                v = v + L["residual"].float()
+            v = v + L["bias"].float()
+            if gelu:
+                v = og.gelu_tanh(v)
+            outs[name] = v.to(torch.bfloat16)
+        return outs
+
+    cpu_note = "quantize + e4m3 GEMM as fp32 upcast matmul + epilogue, all four linears"
 
 
-def run_ours(args, rank, world, local_rank):
+class Int8Sdxl:
+    """configs[0]: SDXL GEGLU-FF INT8 SmoothQuant linear."""
+    name = "int8_sdxl"
+    metric = "int8_smoothquant_linear_throughput"
+    unit = "TOP/s"
+    dtype = "s8 (s32 accumulate in TMEM)"
+    K, N = 640, 5120
+
+    def __init__(self, tokens):
+        self.tokens = tokens or 8192
+        T = self.tokens
+        self.work_per_step = 2.0 * T * self.K * self.N
+        self.scale = 1e12
+        self.workload = ("configs[0]: INT8 SmoothQuant W8A8 linear, SDXL GEGLU-FF shape M=%d K=640 N=5120: dynamic per-token "
+                         "int8 quantize of fp16 X (with smoothing vector) + INT8 GEMM + dequant + bias -> fp16" % T)
+        self.launches_per_step = 2
+        self.timed_names = ["int8_gemm"]
+        # the GEMM is bound by its fp16 output store: algorithmic bytes A + W + out + scales
+        self.gemm_bytes = T * self.K + self.N * self.K + 2.0 * T * self.N + 4.0 * (T + self.N) + 2.0 * self.N
+        self.timed_work = [self.gemm_bytes]
+        self.roof = {"bound": "hbm", "unit": "GB/s", "kernel": "gemm_tcgen05_kernel<i8> (1 launch per step)"}
+
+    def setup_gpu(self, dev):
+        from lyradiff_b200 import ops
+        from oracle import workloads
+        self.ops = ops
+        wl = workloads.int8_smoothquant_linear(m=self.tokens, k=self.K, n=self.N, seed=0)
+        self.x = wl["x"].to(dev)
+        self.pre = wl["pre"].to(dev)
+        self.qw = wl["qw"].to(dev)
+        self.s_w = wl["s_w"].to(dev)
+        self.bias = wl["bias"].to(dev)
+        self.qa = torch.empty(self.tokens, self.K, dtype=torch.int8, device=dev)
+        self.sa = torch.empty(self.tokens, dtype=torch.float32, device=dev)
+        self.y = torch.empty(self.tokens, self.N, dtype=torch.float16, device=dev)
+        # a second output buffer alternates with the first so that consecutive steps do not rewrite lines still in L2
+        self.y2 = torch.empty_like(self.y)
+        self.h_in = wl["x"].pin_memory()
+        self.h_out = torch.empty(self.tokens, self.N, dtype=torch.float16).pin_memory()
+        self.flip = False
+
+    def step(self, events=None):
+        ops = self.ops
+        self.flip = not self.flip
+        y = self.y if self.flip else self.y2
+        ops.invoke_sq_input_quant(self.qa, self.x, self.pre, self.sa, dynamic=True)
+        if events is not None:
+            events[0][0].record()
+        ops.run_gemm_int8(self.qa, self.qw, self.s_w, self.sa, y, bias=self.bias, per_token=True)
+        if events is not None:
+            events[0][1].record()
+        return y
+
+    def step_e2e(self):
+        self.x.copy_(self.h_in, non_blocking=True)
+        y = self.step()
+        self.h_out.copy_(y, non_blocking=True)
+
+    def peak(self, peaks):
+        return peaks["hbm_gbs"], "hbm_gbs of MEASURED_PEAKS.json (%s); the fp16 output store bounds this shape" % peaks["source"], 7700.0
+
+    def setup_cpu(self, rows):
+        from oracle import workloads
+        self.cpu = workloads.int8_smoothquant_linear(m=rows, k=self.K, n=self.N, seed=0)
+        self.cpu["qw_t"] = self.cpu["qw"].t().contiguous()
+        self.cpu_rows = rows
+
+    def step_cpu(self):
+        from oracle import quant as oq
+        c = self.cpu
+        qa, sa = oq.sq_input_quant_dynamic(c["x"], c["pre"])
+        acc = torch._int_mm(qa, c["qw_t"])
+        y = (acc.float() * (c["s_w"][None, :] * sa[:, None])).half()
+        return (y.float() + c["bias"].float()).half()
+
+    cpu_note = "dynamic per-token int8 quantize + torch._int_mm + dequant + bias"
+
+
+class W4A4:
+    """configs[2]: FLUX fused W4A4 linear."""
+    name = "w4a4"
+    metric = "w4a4_g64_linear_throughput"
+    unit = "TOP/s"
+    dtype = "s4 expanded to s8 (s32 per group in TMEM, fp32 across groups)"
+    K, N = 3072, 21504
+
+    def __init__(self, tokens):
+        self.tokens = tokens or 4608
+        self.work_per_step = 2.0 * self.tokens * self.K * self.N
+        self.scale = 1e12
+        self.workload = ("configs[2]: W4A4 group-64 linear M=%d K=3072 N=21504: int4 per-(token, group) quantize of bf16 X + "
+                         "grouped GEMM with fp16 weight group scales -> bf16" % self.tokens)
+        self.launches_per_step = 2
+        self.timed_names = ["w4a4_gemm"]
+        self.timed_work = [self.work_per_step]
+        self.roof = {"bound": "tensor", "unit": "TOP/s", "kernel": "gemm_w4a4_kernel (1 launch per step)"}
+
+    def setup_gpu(self, dev):
+        from lyradiff_b200 import ops
+        self.ops = ops
+        g = _gen()
+        T, K, N = self.tokens, self.K, self.N
+        self.x = torch.randn(T, K, generator=g).bfloat16().to(dev)
+        w = (torch.randn(N, K, generator=g) * 0.02).bfloat16().to(dev)
+        self.qw = torch.empty(N, K // 2, dtype=torch.uint8, device=dev)
+        self.sw = torch.empty(N, K // 64, dtype=torch.float16, device=dev)
+        ops.weight_quant_int4_g64(self.qw, self.sw, w)
+        del w
+        self.smooth = torch.ones(K, dtype=torch.float32, device=dev)
+        self.q = torch.empty(T, K // 2, dtype=torch.uint8, device=dev)
+        self.s = torch.empty(T, K // 64, dtype=torch.float32, device=dev)
+        self.y = torch.empty(T, N, dtype=torch.bfloat16, device=dev)
+        self.h_in = self.x.cpu().pin_memory()
+        self.h_out = torch.empty(T, N, dtype=torch.bfloat16).pin_memory()
+
+    def step(self, events=None):
+        ops = self.ops
+        ops.invoke_fused_quantize_and_lora_down_simple(None, self.q, self.s, self.x, None, self.smooth)
+        if events is not None:
+            events[0][0].record()
+        ops.invoke_fused_w4a4_gemm_and_lora_up(self.y, self.q, self.qw, None, None, self.s, self.sw)
+        if events is not None:
+            events[0][1].record()
+
+    def step_e2e(self):
+        self.x.copy_(self.h_in, non_blocking=True)
+        self.step()
+        self.h_out.copy_(self.y, non_blocking=True)
+
+    def peak(self, peaks):
+        return 2.0 * peaks["bf16_sustained"], ("2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s) as the dense INT8 tensor "
+                                               "rate; this kernel is bound by the per-group fp32 rescale on the CUDA cores, "
+                                               "not by the tensor pipe" % peaks["source"]), 4500.0
+
+    def setup_cpu(self, rows):
+        from oracle import quant as oq
+        g = _gen()
+        self.cpu = {"x": torch.randn(rows, self.K, generator=g).bfloat16()}
+        w = (torch.randn(self.N, self.K, generator=g) * 0.02).bfloat16()
+        _, sw, qw = oq.int4_weight_quant_g64(w)
+        self.cpu["qw"], self.cpu["sw"] = qw, sw.half()
+        self.cpu_rows = rows
+
+    def step_cpu(self):
+        from oracle import gemm as og
+        from oracle import quant as oq
+        _, sa, qa = oq.int4_quant_g64(self.cpu["x"], None)
+        return og.w4a4_gemm(qa, self.cpu["qw"], sa, self.cpu["sw"], fma=False)
+
+    cpu_note = "int4 group-64 quantize + per-group exact contraction + fp32 rescale"
+
+
+class AdalnQuant:
+    """configs[3]: fused AdaLN-modulation + quantize."""
+    name = "adaln_quant"
+    metric = "adaln_quant_bandwidth"
+    unit = "GB/s"
+    dtype = "bf16 in, fp32 statistics, int8 + f8e4m3 out"
+    D = 3072
+
+    def __init__(self, tokens):
+        self.tokens = tokens or 4608
+        T, D = self.tokens, self.D
+        # read X, write int8 + per-token scales + e4m3 (scale/shift rows are negligible and L2-resident)
+        self.work_per_step = 2.0 * T * D + T * D + 4.0 * T + T * D + 2 * 2.0 * D
+        self.scale = 1e9
+        self.workload = ("configs[3]: fused AdaLN-modulation + quantize, X bf16 [%d, 3072], LayerNorm eps 1e-6 no affine, "
+                         "y = LN(x)(1+scale)+shift; emits int8 with per-token scales and e4m3 with a per-tensor scale in one "
+                         "pass" % T)
+        self.launches_per_step = 1
+        self.timed_names = ["adaln_quant"]
+        self.timed_work = [self.work_per_step]
+        self.roof = {"bound": "hbm", "unit": "GB/s", "kernel": "row_quant_kernel<bf16, ROW_ADALN> (1 launch per step)"}
+
+    def setup_gpu(self, dev):
+        from lyradiff_b200 import ops
+        self.ops = ops
+        g = _gen()
+        T, D = self.tokens, self.D
+        # several independent input/output sets (> 126 MB L2 in total) are rotated so that no step finds its data in L2
+        self.nset = 4
+        self.x = [torch.randn(1, T, D, generator=g).bfloat16().to(dev) for _ in range(self.nset)]
+        self.sc = (torch.randn(1, D, generator=g) * 0.1).bfloat16().to(dev)
+        self.sh = (torch.randn(1, D, generator=g) * 0.1).bfloat16().to(dev)
+        self.q8 = [torch.empty(T, D, dtype=torch.int8, device=dev) for _ in range(self.nset)]
+        self.s8 = torch.empty(T, dtype=torch.float32, device=dev)
+        self.qf8 = [torch.empty(T, D, dtype=torch.uint8, device=dev) for _ in range(self.nset)]
+        self.f8s = torch.tensor([8.0 / 448.0], dtype=torch.float32, device=dev)
+        self.h_in = self.x[0].cpu().pin_memory()
+        self.h_out = torch.empty(T, D, dtype=torch.int8).pin_memory()
+        self.i = 0
+
+    def step(self, events=None):
+        i = self.i = (self.i + 1) % self.nset
+        if events is not None:
+            events[0][0].record()
+        self.ops.invoke_layer_norm_with_shift_and_scale(None, self.x[i], self.sc, self.sh, 1e-6, q8=self.q8[i], q8_scale=self.s8,
+                                                        qf8=self.qf8[i], f8_scale=self.f8s)
+        if events is not None:
+            events[0][1].record()
+        return i
+
+    def step_e2e(self):
+        nxt = (self.i + 1) % self.nset
+        self.x[nxt].copy_(self.h_in, non_blocking=True)
+        i = self.step()
+        self.h_out.copy_(self.q8[i], non_blocking=True)
+
+    def peak(self, peaks):
+        return peaks["hbm_gbs"], "hbm_gbs of MEASURED_PEAKS.json (%s)" % peaks["source"], 7700.0
+
+    def setup_cpu(self, rows):
+        g = _gen()
+        self.cpu = {"x": torch.randn(1, rows, self.D, generator=g).bfloat16(), "sc": (torch.randn(1, self.D, generator=g) * 0.1).bfloat16(),
+                    "sh": (torch.randn(1, self.D, generator=g) * 0.1).bfloat16(), "f8": torch.tensor([8.0 / 448.0])}
+        self.cpu_rows = rows
+
+    def step_cpu(self):
+        from oracle import norms
+        c = self.cpu
+        return norms.adaln_quant(c["x"], c["sc"], c["sh"], fp8_scale=c["f8"])
+
+    cpu_note = "LayerNorm + modulation + int8 and e4m3 quantize"
+
+
+CASES = {c.name: c for c in (FluxFp8, Int8Sdxl, W4A4, AdalnQuant)}
+
+
+# =================================================================================================== CPU arm
+def time_cpu(case, rows, steps, warmup):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    case.setup_cpu(rows)
+    for _ in range(warmup):
+        case.step_cpu()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        case.step_cpu()
+    dt = (time.perf_counter() - t0) / steps
+    work = case.work_per_step * rows / case.tokens
+    return {"value": work / dt / case.scale, "unit": case.unit, "cores": cores, "kind": "port",
+            "sample": "%d of %d token rows per step (%s), torch on %d threads, %d timed steps" % (
+                rows, case.tokens, case.cpu_note, cores, steps),
+            "ms_per_step_sample": dt * 1e3}
+
+
+def run_reference(case, args, rank, world):
+    if rank != 0:
+        return
+    # exactly K timed steps; the row sample shrinks as K grows so that the whole run stays within a few minutes
+    rows = min(case.tokens, max(64, min(512, (512 * 20) // max(1, args.steps))))
+    base = time_cpu(case, rows, max(1, args.steps), max(1, min(args.warmup, 3)))
+    line = {
+        "impl": "reference", "metric": case.metric, "value": base["value"], "unit": case.unit, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step_sample"] * case.tokens / rows,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": case.dtype + " restated on CPU",
+        "data": "synthetic",
+        "config": {"workload": case.workload, "note": "CPU restatement of the reference arithmetic (the reference's CUDA sources "
+                   "cannot be built or run on host cores) on a bounded row sample; ms_per_step is the sample time scaled to all rows"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": case.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# =================================================================================================== GPU arm
+def run_ours(case, args, rank, world, local_rank):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the GPU arm has no CPU fallback")
     dev = torch.device("cuda", local_rank)
@@ -247,45 +480,47 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    st = GpuState(dev)
+    def check_device():
+        status, detail = ops.last_status()
+        if status != 0:
+            raise SystemExit("bench.py: device status %d (detail 0x%x)" % (status, detail))
+
+    case.setup_gpu(dev)
     peaks = load_peaks()
-    for _ in range(max(args.warmup, 3)):
-        st.step()
-    torch.cuda.synchronize()
-    status, detail = ops.last_status()
-    if status != 0:
-        raise SystemExit("bench.py: device status %d (detail 0x%x) after warm-up" % (status, detail))
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        case.step()
+    check_device()
 
     # ---- timed region 1: kernels only, inputs resident
-    sampler = ClockSampler(local_rank)
-    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in LINEARS]
+    nt = len(case.timed_names)
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nt)]
           for _ in range(args.steps)]
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
     barrier()
     sampler.start()
     t_begin.record()
     for s in range(args.steps):
-        st.step(ev[s])
+        case.step(ev[s])
     t_end.record()
     barrier()
     clocks = sampler.result()
     ms_total = t_begin.elapsed_time(t_end)
-    gemm_ms = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps)) / args.steps for i in range(len(LINEARS))]
+    timed_ms = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps)) / args.steps for i in range(nt)]
 
     # ---- timed region 2: end to end from pinned host buffers
     for _ in range(2):
-        st.step_e2e()
+        case.step_e2e()
     e_begin, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e_begin.record()
     for _ in range(args.steps):
-        st.step_e2e()
+        case.step_e2e()
     e_end.record()
     barrier()
     ms_e2e = e_begin.elapsed_time(e_end)
-    status, detail = ops.last_status()
-    if status != 0:
-        raise SystemExit("bench.py: device status %d (detail 0x%x)" % (status, detail))
+    check_device()
 
     times = torch.tensor([ms_total, ms_e2e], dtype=torch.float64, device=dev)
     if dist is not None:
@@ -294,32 +529,27 @@ def run_ours(args, rank, world, local_rank):
 
     if rank == 0:
         ms_step = ms_total / args.steps
-        value = world * FLOP_PER_STEP / (ms_step * 1e-3) / 1e12
-        e2e_value = world * FLOP_PER_STEP / (ms_e2e / args.steps * 1e-3) / 1e12
-        gemm_flop = [2.0 * TOKENS * k * n for _, k, n, _, _ in LINEARS]
-        achieved = sum(gemm_flop) / (sum(gemm_ms) * 1e-3) / 1e12
-        peak = 2.0 * peaks["bf16_sustained"]
-        cpu = time_cpu_reference(256, 3, 1)
+        value = world * case.work_per_step / (ms_step * 1e-3) / case.scale
+        e2e_value = world * case.work_per_step / (ms_e2e / args.steps * 1e-3) / case.scale
+        achieved = sum(case.timed_work) / (sum(timed_ms) * 1e-3) / case.scale
+        peak, peak_source, nominal = case.peak(peaks)
+        cpu = time_cpu(case, min(case.tokens, 256), 3, 1)
+        roof = dict(case.roof)
+        roof.update({"achieved": achieved, "peak": peak, "frac": achieved / peak, "traffic": None, "peak_source": peak_source,
+                     "frac_of_nominal": achieved / nominal, "nominal": nominal,
+                     "per_launch_ms": dict(zip(case.timed_names, timed_ms)),
+                     "per_launch_achieved": dict(zip(case.timed_names,
+                                                     [w / (t * 1e-3) / case.scale for w, t in zip(case.timed_work, timed_ms)]))})
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f8e4m3 (fp32 accumulate in TMEM)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "parallelism": "replicas x%d, one workload copy per GPU, no collective" % world,
-                       "l2": "no explicit flush: each step streams ~0.6 GB of distinct tensors (> 126 MB L2) between reuses"},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": st.h_x.numel() * 2,
-                    "d2h_bytes_per_step": st.h_y.numel() * 2, "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": args.steps * st.launches_per_step,
-            "clocks": clocks,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None,
-                         "kernel": "gemm_tcgen05_kernel<f8f6f4> (4 launches per step, one per linear)",
-                         "peak_source": "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s); dense FP8 runs at twice the "
-                                        "bf16 rate" % peaks["source"],
-                         "frac_of_nominal_4500": achieved / 4500.0,
-                         "per_linear_ms": dict(zip([l[0] for l in LINEARS], gemm_ms)),
-                         "per_linear_tflops": dict(zip([l[0] for l in LINEARS],
-                                                       [f / (t * 1e-3) / 1e12 for f, t in zip(gemm_flop, gemm_ms)]))},
-            "cpu_baseline": cpu,
+            "metric": case.metric, "value": value, "unit": case.unit, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": case.dtype,
+            "data": "synthetic",
+            "config": {"workload": case.workload, "parallelism": "replicas x%d: one copy of the workload per GPU, no collective" % world,
+                       "l2": "no explicit flush: every step streams distinct tensors larger than the 126 MB L2 between reuses"},
+            "e2e": {"value": e2e_value, "unit": case.unit, "h2d_bytes_per_step": case.h_in.numel() * case.h_in.element_size(),
+                    "d2h_bytes_per_step": case.h_out.numel() * case.h_out.element_size(), "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": args.steps * case.launches_per_step,
+            "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -329,18 +559,21 @@ def run_ours(args, rank, world, local_rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--case", default="flux_fp8", choices=sorted(CASES))
+    ap.add_argument("--tokens", type=int, default=0, help="override the number of token rows (0 = the configuration's own)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    case = CASES[args.case](args.tokens)
     if args.impl == "reference":
-        run_reference(args, rank, world)
+        run_reference(case, args, rank, world)
     else:
-        run_ours(args, rank, world, local_rank)
+        run_ours(case, args, rank, world, local_rank)
 
 
 if __name__ == "__main__":

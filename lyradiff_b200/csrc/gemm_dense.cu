@@ -508,14 +508,14 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
 
 template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams p, cudaStream_t stream)
 {
-    if (A == nullptr || B == nullptr || p.epi.C == nullptr) {
-        return LYRAQ_ERR_INVALID_ARG;
-    }
     if (p.M < 0 || p.N < 0 || p.K < 0) {
         return LYRAQ_ERR_INVALID_ARG;
     }
     if (p.M == 0 || p.N == 0) {
         return LYRAQ_OK;
+    }
+    if (A == nullptr || B == nullptr || p.epi.C == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
     }
     if (p.K == 0 || (p.K & 15) != 0) {
         return LYRAQ_ERR_UNSUPPORTED;  // TMA needs 16-byte row pitch

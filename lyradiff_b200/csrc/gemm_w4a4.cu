@@ -486,6 +486,9 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
 {
     (void)workspace;
     (void)workspace_bytes;
+    if (m == 0 || n == 0) {
+        return LYRAQ_OK;
+    }
     if (A == nullptr || B == nullptr || sa == nullptr || sb == nullptr || D == nullptr) {
         return LYRAQ_ERR_INVALID_ARG;
     }
@@ -495,9 +498,6 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     }
     if (lora_act != nullptr || lora_up != nullptr) {
         return LYRAQ_ERR_UNSUPPORTED;  // low-rank side branch: not built yet
-    }
-    if (m == 0 || n == 0) {
-        return LYRAQ_OK;
     }
     if (k == 0 || (k & 63) != 0) {
         return LYRAQ_ERR_UNSUPPORTED;

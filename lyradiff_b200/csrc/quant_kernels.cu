@@ -477,6 +477,9 @@ extern "C" {
 int lyraq_quant_int8(int8_t* dst, const void* src, int src_dtype, const float* pre_quant_scale, float* scale,
                      int scale_mode, size_t rows, size_t dim, void* stream)
 {
+    if (rows == 0 && scale_mode >= 0 && scale_mode <= 2) {
+        return LYRAQ_OK;
+    }
     if (dst == nullptr || src == nullptr || scale == nullptr || scale_mode < 0 || scale_mode > 2) {
         return LYRAQ_ERR_INVALID_ARG;
     }
@@ -502,14 +505,14 @@ int lyraq_quant_int8(int8_t* dst, const void* src, int src_dtype, const float* p
 int lyraq_quant_fp8(uint8_t* dst, const void* src, int src_dtype, const float* scale, int invert_scale, size_t n,
                     void* stream)
 {
+    if (n == 0) {
+        return LYRAQ_OK;
+    }
     if (dst == nullptr || src == nullptr || scale == nullptr) {
         return LYRAQ_ERR_INVALID_ARG;
     }
     if (!aligned16(src) || (reinterpret_cast<uintptr_t>(dst) & 7u) != 0) {
         return LYRAQ_ERR_INVALID_ARG;
-    }
-    if (n == 0) {
-        return LYRAQ_OK;
     }
     const unsigned grid = flat_grid(n >> 3);
     if (src_dtype == LYRAQ_F16) {
@@ -525,11 +528,11 @@ int lyraq_quant_fp8(uint8_t* dst, const void* src, int src_dtype, const float* s
 
 int lyraq_fp8_amax_scale(float* scale, const void* w, int w_dtype, size_t n, void* stream)
 {
-    if (scale == nullptr || w == nullptr || !aligned16(w)) {
-        return LYRAQ_ERR_INVALID_ARG;
-    }
     if (n == 0) {
         return LYRAQ_OK;
+    }
+    if (scale == nullptr || w == nullptr || !aligned16(w)) {
+        return LYRAQ_ERR_INVALID_ARG;
     }
     const unsigned grid = flat_grid(n >> 3);
     if (w_dtype == LYRAQ_F16) {
@@ -545,11 +548,11 @@ int lyraq_fp8_amax_scale(float* scale, const void* w, int w_dtype, size_t n, voi
 int lyraq_weight_quant_int8(float* w_scale, int8_t* qw, const void* w, int w_dtype, const float* pre_quant_scale,
                             size_t d_out, size_t d_in, void* stream)
 {
-    if (w_scale == nullptr || qw == nullptr || w == nullptr) {
-        return LYRAQ_ERR_INVALID_ARG;
-    }
     if (d_out == 0 || d_in == 0) {
         return LYRAQ_OK;
+    }
+    if (w_scale == nullptr || qw == nullptr || w == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
     }
     if (d_out > 0x7fffffffu) {
         return LYRAQ_ERR_UNSUPPORTED;
@@ -569,6 +572,9 @@ int lyraq_weight_quant_int8(float* w_scale, int8_t* qw, const void* w, int w_dty
 static int int4_g64_dispatch(uint8_t* q, void* q_scale, int scale_dtype, const void* x, int x_dtype, const float* smooth,
                              size_t rows, size_t k, cudaStream_t stream)
 {
+    if (rows == 0 && k != 0 && (k & 63) == 0) {
+        return LYRAQ_OK;
+    }
     if (q == nullptr || q_scale == nullptr || x == nullptr) {
         return LYRAQ_ERR_INVALID_ARG;
     }
@@ -618,6 +624,9 @@ int lyraq_adaln_quant(void* y, int8_t* q8, float* q8_scale, uint8_t* qf8, const 
                       const void* scale, const void* shift, int dtype, const float* pre_quant_scale, size_t B, size_t S,
                       size_t D, double eps, void* stream)
 {
+    if (B * S == 0) {
+        return LYRAQ_OK;
+    }
     if (x == nullptr || scale == nullptr || shift == nullptr || (q8 != nullptr && q8_scale == nullptr) ||
         (qf8 != nullptr && f8_scale == nullptr) || (y == nullptr && q8 == nullptr && qf8 == nullptr)) {
         return LYRAQ_ERR_INVALID_ARG;
@@ -627,8 +636,8 @@ int lyraq_adaln_quant(void* y, int8_t* q8, float* q8_scale, uint8_t* qf8, const 
         (pre_quant_scale != nullptr && !aligned16(pre_quant_scale))) {
         return LYRAQ_ERR_INVALID_ARG;
     }
-    if (D > 16384 || S == 0 || S > 0x7fffffffu) {
-        return (B * S == 0) ? LYRAQ_OK : LYRAQ_ERR_UNSUPPORTED;
+    if (D > 16384 || S > 0x7fffffffu) {
+        return LYRAQ_ERR_UNSUPPORTED;
     }
     RowParams p{};
     p.x              = x;
@@ -654,6 +663,9 @@ int lyraq_ln_quant_int8(int8_t* dst, void* sum_out, const void* x, const void* r
                         const void* gamma, const void* beta, int dtype, const float* pre_quant_scale,
                         const float* input_quant_scale, size_t rows, size_t dim, double eps, void* stream)
 {
+    if (rows == 0) {
+        return LYRAQ_OK;
+    }
     if (dst == nullptr || x == nullptr || gamma == nullptr || beta == nullptr || input_quant_scale == nullptr) {
         return LYRAQ_ERR_INVALID_ARG;
     }
@@ -686,6 +698,9 @@ int lyraq_ln_quant_int8(int8_t* dst, void* sum_out, const void* x, const void* r
 int lyraq_geglu_quant_int8(int8_t* dst, const void* h, const void* bias, int dtype, const float* pre_quant_scale,
                            const float* input_quant_scale, size_t rows, size_t dim, void* stream)
 {
+    if (rows == 0) {
+        return LYRAQ_OK;
+    }
     if (dst == nullptr || h == nullptr || input_quant_scale == nullptr) {
         return LYRAQ_ERR_INVALID_ARG;
     }

@@ -90,3 +90,17 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(ImportError):
         _lib.lib()
+
+
+def test_cpp_shim_compiles_against_the_reference_call_forms():
+    """include/lyradiff_shim.h keeps the reference's function names and argument lists: a translation unit that calls
+    them the way the reference's layers do must compile (syntax check only, nothing is linked or run)."""
+    import shutil
+    import subprocess
+    cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+    if shutil.which("g++") is None or not os.path.exists(os.path.join(cuda_inc, "cuda_runtime.h")):
+        pytest.skip("g++ or CUDA headers not present")
+    src = os.path.join(ROOT, "tests", "shim_compile_check.cpp")
+    r = subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-I", os.path.join(ROOT, "include"), "-I", cuda_inc, src],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
