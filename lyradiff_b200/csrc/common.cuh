@@ -152,6 +152,68 @@ template<> __device__ __forceinline__ Vec16 pack8<__nv_bfloat16>(const float* in
 }
 
 // ---------------------------------------------------------------------------------------------
+// Arithmetic "in T" on packed pairs (two 16-bit values in one 32-bit register), using the native
+// single-rounding add / multiply of the type.  `_rn` intrinsics are never contracted into an fma,
+// so each step is rounded to T exactly as the reference's T-typed expressions are.
+template<typename T> struct Pair;
+template<> struct Pair<__half> {
+    static __device__ __forceinline__ float2 to_f32(uint32_t w) { return __half22float2(*reinterpret_cast<const __half2*>(&w)); }
+    static __device__ __forceinline__ uint32_t from_f32(float a, float b)
+    {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b)
+    {
+        __half2 r = __hadd2_rn(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+    static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b)
+    {
+        __half2 r = __hmul2_rn(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+    static __device__ __forceinline__ uint32_t one() { return 0x3C003C00u; }
+};
+template<> struct Pair<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 to_f32(uint32_t w)
+    {
+        return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+    }
+    static __device__ __forceinline__ uint32_t from_f32(float a, float b)
+    {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t*>(&h);
+    }
+    static __device__ __forceinline__ uint32_t add(uint32_t a, uint32_t b)
+    {
+        __nv_bfloat162 r = __hadd2_rn(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+    static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b)
+    {
+        __nv_bfloat162 r = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+        return *reinterpret_cast<uint32_t*>(&r);
+    }
+    static __device__ __forceinline__ uint32_t one() { return 0x3F803F80u; }
+};
+
+// sat_s8(rne(v)) without the conversion unit: NaN -> 0 (as cvt.rni.sat.s8.f32 does), clamp to
+// [-128, 127] (also catches +-inf), then add 1.5 * 2^23: at that magnitude one ulp is 1, so the
+// fp32 add rounds v to the nearest integer, ties to even, and the low byte of the sum's bit
+// pattern is the two's-complement int8.  Returns the byte in bits [0, 8).
+__device__ __forceinline__ uint32_t f32_to_s8_bits(float v)
+{
+    v = (v != v) ? 0.0f : v;
+    v = fminf(fmaxf(v, -128.0f), 127.0f);
+    return __float_as_uint(v + 12582912.0f);
+}
+__device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host-side checks.
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -16,12 +16,13 @@
 // cycled, the MMA warp runs up to four groups ahead, and eight drain warps convert / scale /
 // accumulate in registers.  That CUDA-core work, not the tensor pipe, bounds this kernel.
 //
-// 384 threads per CTA, one persistent CTA per SM:
-//   warp 0      TMA producer: packed A (128 x 64 B) and packed B (128 x 64 B) tiles, ring of 4 stages
-//   warp 1      MMA issuer
-//   warps 2-3   expand nibbles -> swizzled int8 operand tiles (ring of 4 stages) and stage the scales
-//               of the two groups of the K block in shared memory; warp 2 also owns tensor memory
-//   warps 4-11  drain: warp w reads TMEM lanes 32*(w%4).., columns 64*((w-4)/4)..; final epilogue
+// 416 threads per CTA, one persistent CTA per SM:
+//   warp 0       TMA producer: packed A (128 x 64 B) and packed B (128 x 64 B) tiles, ring of 4 stages
+//   warp 1       MMA issuer
+//   warp 2       scale loader: every four K blocks (8 groups) it transposes sa[m, g] and sb[n, g] of the tile into
+//                shared memory as [g][row] (ring of 3 slots), running ahead of the drain; also owns tensor memory
+//   warps 3, 12  expand nibbles -> swizzled int8 operand tiles (ring of 4 stages)
+//   warps 4-11   drain: warp w reads TMEM lanes 32*(w%4).., columns 64*((w-4)/4)..; final epilogue
 // All waits are bounded (see sm100_ptx.cuh); a timeout sets the status word and every role exits.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -41,16 +42,19 @@ constexpr int kBM          = 128;
 constexpr int kBN          = 128;
 constexpr int kKBlock      = 128;            // K elements per block = 2 groups
 constexpr int kPackedRowB  = kKBlock / 2;    // 64 bytes
-constexpr int kThreads     = 384;
+constexpr int kThreads     = 416;
 constexpr int kPStages     = 4;
 constexpr int kUStages     = 4;
 constexpr int kPBufs       = 4;              // partial accumulator buffers in tensor memory
+constexpr int kSSlots      = 3;              // scale ring
+constexpr int kSlotGroups  = 8;              // groups per scale slot = 4 K blocks
 constexpr int kPackedTile  = kBM * kPackedRowB;   // 8 KB (A) ; B the same with kBN rows
 constexpr int kPackedStage = 2 * kPackedTile;     // 16 KB
 constexpr int kOperandTile = kBM * kKBlock;       // 16 KB
-constexpr int kScaleBytes  = 2 * (kBM + kBN) * 4; // two groups x (128 sa + 128 sb) fp32 = 2 KB
-constexpr int kUStage      = 2 * kOperandTile + kScaleBytes;
-constexpr int kBarOffset   = kPStages * kPackedStage + kUStages * kUStage;
+constexpr int kUStage      = 2 * kOperandTile;    // 32 KB
+constexpr int kScaleSlot   = kSlotGroups * (kBM + kBN) * 4;  // 8 KB: sas[8][128] then sbs[8][128], fp32
+constexpr int kScaleOffset = kPStages * kPackedStage + kUStages * kUStage;
+constexpr int kBarOffset   = kScaleOffset + kSSlots * kScaleSlot;
 constexpr int kSmemTotal   = kBarOffset + 512 + 1024;
 
 struct Params {
@@ -59,6 +63,7 @@ struct Params {
     const float*  sa;
     const void*   sb;
     int           sb_is_f16;
+    int           scale_vec_ok;  // G % 4 == 0 and 16-byte aligned scale arrays: 16-byte scale loads are legal
     void*         D;
     int           c_dtype;
     const void*   bias;
@@ -139,7 +144,7 @@ __device__ __forceinline__ void final_store32(const Params& p, const float* acc,
     }
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __maxnreg__(152)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p)
 {
     constexpr uint32_t kTmemCols = kPBufs * kBN;  // 512
@@ -148,17 +153,19 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t*       gen_base  = smem_raw + (smem_base - smem_u32(smem_raw));
-    // [packed ring][operand ring: A int8 | B int8 | scales][barriers]
+    // [packed ring][operand ring: A int8 | B int8][scale ring][barriers]
     const uint32_t packed0 = smem_base;
     const uint32_t ustage0 = smem_base + kPStages * kPackedStage;
     const uint32_t bars    = smem_base + kBarOffset;
-    auto full_p    = [&](int s) { return bars + 8u * s; };
-    auto empty_p   = [&](int s) { return bars + 8u * (kPStages + s); };
-    auto full_u    = [&](int s) { return bars + 8u * (2 * kPStages + s); };
-    auto empty_u   = [&](int s) { return bars + 8u * (2 * kPStages + kUStages + s); };
-    auto part_full = [&](int b) { return bars + 8u * (2 * kPStages + 2 * kUStages + b); };
+    auto full_p     = [&](int s) { return bars + 8u * s; };
+    auto empty_p    = [&](int s) { return bars + 8u * (kPStages + s); };
+    auto full_u     = [&](int s) { return bars + 8u * (2 * kPStages + s); };
+    auto empty_u    = [&](int s) { return bars + 8u * (2 * kPStages + kUStages + s); };
+    auto part_full  = [&](int b) { return bars + 8u * (2 * kPStages + 2 * kUStages + b); };
     auto part_empty = [&](int b) { return bars + 8u * (2 * kPStages + 2 * kUStages + kPBufs + b); };
-    constexpr int kNumBars  = 2 * kPStages + 2 * kUStages + 2 * kPBufs;
+    auto sc_full    = [&](int s) { return bars + 8u * (2 * kPStages + 2 * kUStages + 2 * kPBufs + s); };
+    auto sc_empty   = [&](int s) { return bars + 8u * (2 * kPStages + 2 * kUStages + 2 * kPBufs + kSSlots + s); };
+    constexpr int kNumBars   = 2 * kPStages + 2 * kUStages + 2 * kPBufs + 2 * kSSlots;
     uint32_t*     tmem_slot  = reinterpret_cast<uint32_t*>(gen_base + kBarOffset + 8 * kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -172,11 +179,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         for (int s = 0; s < kUStages; ++s) {
             mbar_init(full_u(s), 2);    // the two expanding warps
-            mbar_init(empty_u(s), 1 + 8);  // MMA commit + eight drain warps
+            mbar_init(empty_u(s), 1);   // MMA commit
         }
         for (int b = 0; b < kPBufs; ++b) {
             mbar_init(part_full(b), 1);
             mbar_init(part_empty(b), 8);
+        }
+        for (int s = 0; s < kSSlots; ++s) {
+            mbar_init(sc_full(s), 1);
+            mbar_init(sc_empty(s), 8);  // eight drain warps
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -194,6 +205,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
     const int num_tiles = p.m_tiles * p.n_tiles;
     const int num_kb    = (p.K + kKBlock - 1) / kKBlock;
+    const int num_slots = (num_kb + 3) / 4;  // scale slots per tile
 
     if (warp == 0) {
         if (lane == 0) {
@@ -286,15 +298,109 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
-    } else if (warp == 2 || warp == 3) {
-        // ------------------------------------------------------------------ nibble expansion + scale staging
-        const int tu     = threadIdx.x - 64;  // 0..63
+    } else if (warp == 2) {
+        // ------------------------------------------------------------------ scale loader
+        int      slot = 0;
+        uint32_t sphase = 0;
+        bool     ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            const int m_blk = tile % p.m_tiles;
+            const int n_blk = tile / p.m_tiles;
+            for (int sl = 0; sl < num_slots; ++sl) {
+                if (!__all_sync(0xffffffffu, mbar_wait(sc_empty(slot), sphase ^ 1u, abort_flag))) {
+                    if (lane == 0) {
+                        report_timeout(p.status, 0x1800u | (unsigned)slot);
+                    }
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                float*     sas  = reinterpret_cast<float*>(gen_base + kScaleOffset + slot * kScaleSlot);
+                float*     sbs  = sas + kSlotGroups * kBM;
+                const int  g0   = sl * kSlotGroups;
+                const bool full = p.scale_vec_ok && (g0 + kSlotGroups <= p.G);
+                float      va[4][8], vb[4][8];
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) {
+                    const int    r    = lane + 32 * rr;
+                    const int    grow = m_blk * kBM + r;
+                    const int    gcol = n_blk * kBN + r;
+                    const float* pa   = p.sa + (size_t)grow * p.G + g0;
+                    if (full && grow < p.M) {
+                        const float4 x0 = __ldg(reinterpret_cast<const float4*>(pa));
+                        const float4 x1 = __ldg(reinterpret_cast<const float4*>(pa) + 1);
+                        va[rr][0] = x0.x; va[rr][1] = x0.y; va[rr][2] = x0.z; va[rr][3] = x0.w;
+                        va[rr][4] = x1.x; va[rr][5] = x1.y; va[rr][6] = x1.z; va[rr][7] = x1.w;
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            va[rr][g] = (grow < p.M && g0 + g < p.G) ? __ldg(pa + g) : 0.0f;
+                        }
+                    }
+                    if (p.sb_is_f16) {
+                        const __half* pb = reinterpret_cast<const __half*>(p.sb) + (size_t)gcol * p.G + g0;
+                        if (full && gcol < p.N) {
+                            float tmp[8];
+                            unpack8<__half>(ld_nc_16(pb), tmp);
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                vb[rr][g] = tmp[g];
+                            }
+                        } else {
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                vb[rr][g] = (gcol < p.N && g0 + g < p.G) ? __half2float(pb[g]) : 0.0f;
+                            }
+                        }
+                    } else {
+                        const float* pb = reinterpret_cast<const float*>(p.sb) + (size_t)gcol * p.G + g0;
+                        if (full && gcol < p.N) {
+                            const float4 x0 = __ldg(reinterpret_cast<const float4*>(pb));
+                            const float4 x1 = __ldg(reinterpret_cast<const float4*>(pb) + 1);
+                            vb[rr][0] = x0.x; vb[rr][1] = x0.y; vb[rr][2] = x0.z; vb[rr][3] = x0.w;
+                            vb[rr][4] = x1.x; vb[rr][5] = x1.y; vb[rr][6] = x1.z; vb[rr][7] = x1.w;
+                        } else {
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                vb[rr][g] = (gcol < p.N && g0 + g < p.G) ? __ldg(pb + g) : 0.0f;
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int rr = 0; rr < 4; ++rr) {
+                    const int r = lane + 32 * rr;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        sas[g * kBM + r] = va[rr][g] * (1.0f / 256.0f);  // the 16 * 16 of the nibble expansion, exactly
+                        sbs[g * kBN + r] = vb[rr][g];
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(sc_full(slot));
+                }
+                if (++slot == kSSlots) {
+                    slot = 0;
+                    sphase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 3 || warp == 12) {
+        // ------------------------------------------------------------------ nibble expansion
+        // 2 tiles x 128 rows x 4 packed 16-byte chunks = 1024 tasks over 64 threads; thread tu owns chunk (tu & 3) of
+        // rows (tu >> 2) + 16 * it, it = 0..15 (it < 8: A, it >= 8: B), so every address is a base plus it * constant.
+        const int tu     = (warp == 3 ? 0 : 32) + lane;
+        const int c      = tu & 3;
+        const int r0     = tu >> 2;       // 0..15
+        const int sw     = r0 & 7;        // (r0 + 16 * it) & 7 == r0 & 7
+        const int src_o  = r0 * kPackedRowB + c * 16;
+        const int dst_ev = (r0 >> 3) * 1024 + (r0 & 7) * 128 + (((2 * c) ^ sw) << 4);
+        const int dst_od = (r0 >> 3) * 1024 + (r0 & 7) * 128 + (((2 * c + 1) ^ sw) << 4);
         int       pstage = 0, ustage = 0;
         uint32_t  pphase = 0, uphase = 0;
         bool      ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-            const int m_blk = tile % p.m_tiles;
-            const int n_blk = tile / p.m_tiles;
             for (int kb = 0; kb < num_kb; ++kb) {
                 bool w = mbar_wait(full_p(pstage), pphase, abort_flag);
                 w      = w && mbar_wait(empty_u(ustage), uphase ^ 1u, abort_flag);
@@ -306,51 +412,20 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     ok = false;
                     break;
                 }
-                const uint8_t* src = gen_base + (packed0 - smem_base) + pstage * kPackedStage;
+                const uint8_t* src = gen_base + (packed0 - smem_base) + pstage * kPackedStage + src_o;
                 uint8_t*       dst = gen_base + (ustage0 - smem_base) + ustage * kUStage;
-                // 2 tiles x 128 rows x 4 packed 16-byte chunks = 1024 tasks over 64 threads
-#pragma unroll 4
+#pragma unroll
                 for (int it = 0; it < 16; ++it) {
-                    const int   task = it * 64 + tu;        // 0..1023
-                    const int   mat  = task >> 9;           // 0 = A, 1 = B
-                    const int   idx  = task & 511;
-                    const int   r    = idx >> 2;
-                    const int   c    = idx & 3;
-                    const uint4 w4   = *reinterpret_cast<const uint4*>(src + mat * kPackedTile + r * kPackedRowB + c * 16);
+                    // 16 rows further per step: 16 * 64 B in the packed tile, 2 * 1024 B in the operand tile;
+                    // it >= 8 switches to the B tile (its packed and operand tiles follow A's contiguously)
+                    const uint4 w4 = *reinterpret_cast<const uint4*>(src + it * 16 * kPackedRowB);
                     uint4       ev, od;
                     ev.x = (w4.x << 4) & 0xF0F0F0F0u; od.x = w4.x & 0xF0F0F0F0u;
                     ev.y = (w4.y << 4) & 0xF0F0F0F0u; od.y = w4.y & 0xF0F0F0F0u;
                     ev.z = (w4.z << 4) & 0xF0F0F0F0u; od.z = w4.z & 0xF0F0F0F0u;
                     ev.w = (w4.w << 4) & 0xF0F0F0F0u; od.w = w4.w & 0xF0F0F0F0u;
-                    uint8_t*  rowp = dst + mat * kOperandTile + (r >> 3) * 1024 + (r & 7) * 128;
-                    const int sw   = r & 7;
-                    *reinterpret_cast<uint4*>(rowp + (((2 * c) ^ sw) << 4))     = ev;
-                    *reinterpret_cast<uint4*>(rowp + (((2 * c + 1) ^ sw) << 4)) = od;
-                }
-                // scales of the (up to) two groups of this K block: sas[g][row] = sa / 256, sbs[g][col] = sb
-                float* sas = reinterpret_cast<float*>(dst + 2 * kOperandTile);
-                float* sbs = sas + 2 * kBM;
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int r    = tu + 64 * h;
-                    const int grow = m_blk * kBM + r;
-                    const int gcol = n_blk * kBN + r;
-#pragma unroll
-                    for (int g = 0; g < 2; ++g) {
-                        const int gg = 2 * kb + g;
-                        float     a = 0.0f, b = 0.0f;
-                        if (gg < p.G) {
-                            if (grow < p.M) {
-                                a = __ldg(p.sa + (size_t)grow * p.G + gg) * (1.0f / 256.0f);
-                            }
-                            if (gcol < p.N) {
-                                b = p.sb_is_f16 ? __half2float(reinterpret_cast<const __half*>(p.sb)[(size_t)gcol * p.G + gg])
-                                                : __ldg(reinterpret_cast<const float*>(p.sb) + (size_t)gcol * p.G + gg);
-                            }
-                        }
-                        sas[g * kBM + r] = a;
-                        sbs[g * kBN + r] = b;
-                    }
+                    *reinterpret_cast<uint4*>(dst + it * 2048 + dst_ev) = ev;
+                    *reinterpret_cast<uint4*>(dst + it * 2048 + dst_od) = od;
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -369,14 +444,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
         }
     } else {
-        // ------------------------------------------------------------------ drain + epilogue
+        // ------------------------------------------------------------------ drain + epilogue (warps 4..11)
         const int      quad      = warp & 3;
         const int      half      = (warp - 4) >> 2;
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         const int      trow      = quad * 32 + lane;
         const bool     vec_ok    = (p.c_dtype == LYRAQ_F32) ? ((p.N & 3) == 0) : ((p.N & 7) == 0);
-        int            ustage = 0;
-        uint32_t       uphase = 0;
+        int            slot = 0;
+        uint32_t       sphase = 0;
         uint32_t       gi = 0;
         bool           ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
@@ -388,19 +463,22 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 acc[i] = 0.0f;
             }
             for (int kb = 0; ok && kb < num_kb; ++kb) {
-                if (!__all_sync(0xffffffffu, mbar_wait(full_u(ustage), uphase, abort_flag))) {
-                    if (lane == 0) {
-                        report_timeout(p.status, 0x1600u | (unsigned)ustage);
+                if ((kb & 3) == 0) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(sc_full(slot), sphase, abort_flag))) {
+                        if (lane == 0) {
+                            report_timeout(p.status, 0x1600u | (unsigned)slot);
+                        }
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
                     }
-                    *abort_flag = 1;
-                    ok = false;
-                    break;
                 }
-                const float* sas    = reinterpret_cast<const float*>(gen_base + (ustage0 - smem_base) + ustage * kUStage + 2 * kOperandTile);
-                const float* sbs    = sas + 2 * kBM;
+                const float* sas    = reinterpret_cast<const float*>(gen_base + kScaleOffset + slot * kScaleSlot);
+                const float* sbs    = sas + kSlotGroups * kBM;
                 const int    groups = min(2, p.G - 2 * kb);
                 for (int g = 0; g < groups; ++g, ++gi) {
                     const int pb = (int)(gi % kPBufs);
+                    const int gs = (kb & 3) * 2 + g;  // group index inside the scale slot
                     if (!__all_sync(0xffffffffu, mbar_wait(part_full(pb), (gi / kPBufs) & 1u, abort_flag))) {
                         if (lane == 0) {
                             report_timeout(p.status, 0x1700u | (unsigned)pb);
@@ -410,13 +488,13 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         break;
                     }
                     tc_fence_after_sync();
-                    const float sa_v = sas[g * kBM + trow];
+                    const float sa_v = sas[gs * kBM + trow];
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         uint32_t part[32];
                         tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64 + c * 32), part);
                         tmem_ld_wait();
-                        const float4* sb4 = reinterpret_cast<const float4*>(sbs + g * kBN + half * 64 + c * 32);
+                        const float4* sb4 = reinterpret_cast<const float4*>(sbs + gs * kBN + half * 64 + c * 32);
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const float4 s = sb4[j];
@@ -434,13 +512,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         mbar_arrive(part_empty(pb));
                     }
                 }
-                __syncwarp();
-                if (ok && lane == 0) {
-                    mbar_arrive(empty_u(ustage));
-                }
-                if (++ustage == kUStages) {
-                    ustage = 0;
-                    uphase ^= 1u;
+                if (ok && ((kb & 3) == 3 || kb == num_kb - 1)) {
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(sc_empty(slot));
+                    }
+                    if (++slot == kSSlots) {
+                        slot = 0;
+                        sphase ^= 1u;
+                    }
                 }
             }
             if (!ok) {
@@ -515,6 +595,7 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     p.sa        = sa;
     p.sb        = sb;
     p.sb_is_f16 = (sb_dtype == LYRAQ_F16) ? 1 : 0;
+    p.scale_vec_ok = ((p.G & 7) == 0 || ((p.G & 3) == 0 && sb_dtype == LYRAQ_F32)) && aligned16(sa) && aligned16(sb) ? 1 : 0;
     p.D         = D;
     p.c_dtype   = c_dtype;
     p.bias      = bias;

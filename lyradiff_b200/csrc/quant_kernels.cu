@@ -48,30 +48,34 @@ template<bool IS_MAX> __device__ __forceinline__ float warp_reduce(float v)
 }
 
 // Reduction over the tpr threads of a team (tpr is a multiple of 32; a warp belongs to one team).
-// Every thread of the block must call it.
+// Every thread of the team must call it.
 template<bool IS_MAX> __device__ __forceinline__ float team_reduce(float v, int tpr, float* red)
 {
     v = warp_reduce<IS_MAX>(v);
     if (tpr == 32) {
         return v;
     }
-    const int warp = threadIdx.x >> 5;
+    const int warp  = threadIdx.x >> 5;
+    const int wpt   = tpr >> 5;
+    const int first = (warp / wpt) * wpt;
     if ((threadIdx.x & 31) == 0) {
         red[warp] = v;
     }
-    __syncthreads();
-    const int wpt   = tpr >> 5;
-    const int first = (warp / wpt) * wpt;
-    float     r     = red[first];
+    // only the warps of this team meet: named barrier 1 + team index, tpr participants
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + first / wpt), "r"(tpr) : "memory");
+    float r = red[first];
     for (int i = 1; i < wpt; ++i) {
         r = IS_MAX ? fmaxf(r, red[first + i]) : r + red[first + i];
     }
-    __syncthreads();
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + first / wpt), "r"(tpr) : "memory");
     return r;
 }
 
-template<typename T, int VPT, int MODE> __global__ void __launch_bounds__(256) row_quant_kernel(const RowParams p)
+// Row data lives in registers as packed pairs of T (h[i][0..3] = the i-th 16-byte vector of this thread).
+template<typename T, int VPT, int MODE>
+__global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(const RowParams p)
 {
+    using P2 = Pair<T>;
     __shared__ float red[8];
 
     const int    tpr   = p.tpr;
@@ -81,74 +85,84 @@ template<typename T, int VPT, int MODE> __global__ void __launch_bounds__(256) r
     const bool   live  = row < p.rows;
     const int    nvec  = p.dim >> 3;
 
-    float v[VPT][8];
+    uint32_t h[VPT][4];
 
     const T* xrow = reinterpret_cast<const T*>(p.x) + row * (size_t)p.in_cols;
 
-    // ---- load (and, per mode, pre-combine) the row
+    // ---- load (and, per mode, pre-combine in T arithmetic) the row
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int vi = tlane + i * tpr;
         if (live && vi < nvec) {
-            const int c = vi << 3;
-            unpack8<T>(ld_nc_16(xrow + c), v[i]);
-            if (MODE == ROW_LN && p.residual != nullptr) {
-                float r[8];
-                unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.residual) + row * (size_t)p.dim + c), r);
+            const int   c = vi << 3;
+            const Vec16 x = ld_nc_16(xrow + c);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    v[i][j] = round_t<T>(v[i][j] + r[j]);
+            for (int j = 0; j < 4; ++j) {
+                h[i][j] = x.w[j];
+            }
+            if (MODE == ROW_LN && p.residual != nullptr) {
+                // h = T(T(x + residual) + bias)
+                const Vec16 r = ld_nc_16(reinterpret_cast<const T*>(p.residual) + row * (size_t)p.dim + c);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    h[i][j] = P2::add(h[i][j], r.w[j]);
                 }
                 if (p.bias != nullptr) {
-                    float b[8];
-                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.bias) + c), b);
+                    const Vec16 b = ld_nc_16(reinterpret_cast<const T*>(p.bias) + c);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        v[i][j] = round_t<T>(v[i][j] + b[j]);
+                    for (int j = 0; j < 4; ++j) {
+                        h[i][j] = P2::add(h[i][j], b.w[j]);
                     }
                 }
                 if (p.sum_out != nullptr) {
-                    st_16(reinterpret_cast<T*>(p.sum_out) + row * (size_t)p.dim + c, pack8<T>(v[i]));
+                    Vec16 o;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        o.w[j] = h[i][j];
+                    }
+                    st_16(reinterpret_cast<T*>(p.sum_out) + row * (size_t)p.dim + c, o);
                 }
             }
             if (MODE == ROW_GEGLU) {
-                float g[8];
-                unpack8<T>(ld_nc_16(xrow + p.dim + c), g);
+                Vec16 g = ld_nc_16(xrow + p.dim + c);
                 if (p.bias != nullptr) {
-                    float bh[8], bg[8];
-                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.bias) + c), bh);
-                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.bias) + p.dim + c), bg);
+                    const Vec16 bh = ld_nc_16(reinterpret_cast<const T*>(p.bias) + c);
+                    const Vec16 bg = ld_nc_16(reinterpret_cast<const T*>(p.bias) + p.dim + c);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        v[i][j] = round_t<T>(v[i][j] + bh[j]);
-                        g[j]    = round_t<T>(g[j] + bg[j]);
+                    for (int j = 0; j < 4; ++j) {
+                        h[i][j] = P2::add(h[i][j], bh.w[j]);
+                        g.w[j]  = P2::add(g.w[j], bg.w[j]);
                     }
                 }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    // GeluActivation<half2>: cube and final product in T, cdf in fp32 then rounded to T.
-                    const float cube = round_t<T>(g[j] * round_t<T>(g[j] * g[j]));
-                    const float cdf  = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (g[j] + 0.044715f * cube)));
-                    const float act  = round_t<T>(g[j] * round_t<T>(cdf));
-                    v[i][j]          = round_t<T>(v[i][j] * act);
+                for (int j = 0; j < 4; ++j) {
+                    // GeluActivation<half2>: cube and products in T, the cdf in fp32 and rounded to T
+                    const uint32_t cube = P2::mul(g.w[j], P2::mul(g.w[j], g.w[j]));
+                    const float2   gf   = P2::to_f32(g.w[j]);
+                    const float2   cf   = P2::to_f32(cube);
+                    const float    c0   = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (gf.x + 0.044715f * cf.x)));
+                    const float    c1   = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (gf.y + 0.044715f * cf.y)));
+                    const uint32_t act  = P2::mul(g.w[j], P2::from_f32(c0, c1));
+                    h[i][j]             = P2::mul(h[i][j], act);
                 }
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                v[i][j] = 0.0f;
+            for (int j = 0; j < 4; ++j) {
+                h[i][j] = 0u;
             }
         }
     }
 
-    // ---- row statistics and normalisation
+    // ---- row statistics (fp32) and normalisation + modulation (T arithmetic)
     if (MODE == ROW_ADALN || MODE == ROW_LN) {
         float s = 0.0f;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                s += v[i][j];
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = P2::to_f32(h[i][j]);
+                s += f.x + f.y;
             }
         }
         s                = team_reduce<false>(s, tpr, red);
@@ -159,9 +173,10 @@ template<typename T, int VPT, int MODE> __global__ void __launch_bounds__(256) r
             const int vi = tlane + i * tpr;
             if (vi < nvec) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float d = v[i][j] - mean;
-                    m2 += d * d;
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f  = P2::to_f32(h[i][j]);
+                    const float  d0 = f.x - mean, d1 = f.y - mean;
+                    m2 += d0 * d0 + d1 * d1;
                 }
             }
         }
@@ -170,29 +185,23 @@ template<typename T, int VPT, int MODE> __global__ void __launch_bounds__(256) r
         const float rstd = (float)(1.0 / sqrt((double)var + (double)p.eps));
 
         const size_t brow = (MODE == ROW_ADALN) ? (row / (size_t)p.rows_per_batch) : 0;
+        const T*     mul_v = (MODE == ROW_ADALN) ? reinterpret_cast<const T*>(p.ada_scale) + brow * (size_t)p.dim
+                                                 : reinterpret_cast<const T*>(p.gamma);
+        const T*     add_v = (MODE == ROW_ADALN) ? reinterpret_cast<const T*>(p.ada_shift) + brow * (size_t)p.dim
+                                                 : reinterpret_cast<const T*>(p.beta);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int vi = tlane + i * tpr;
             if (live && vi < nvec) {
-                const int c = vi << 3;
-                float     a[8], b[8];
-                if (MODE == ROW_ADALN) {
-                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.ada_scale) + brow * (size_t)p.dim + c), a);
-                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.ada_shift) + brow * (size_t)p.dim + c), b);
+                const int   c = vi << 3;
+                const Vec16 a = ld_nc_16(mul_v + c);
+                const Vec16 b = ld_nc_16(add_v + c);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float xh  = round_t<T>((v[i][j] - mean) * rstd);
-                        const float sp1 = round_t<T>(a[j] + 1.0f);
-                        v[i][j]         = round_t<T>(round_t<T>(sp1 * xh) + b[j]);
-                    }
-                } else {
-                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.gamma) + c), a);
-                    unpack8<T>(ld_nc_16(reinterpret_cast<const T*>(p.beta) + c), b);
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float xh = round_t<T>((v[i][j] - mean) * rstd);
-                        v[i][j]        = round_t<T>(round_t<T>(a[j] * xh) + b[j]);
-                    }
+                for (int j = 0; j < 4; ++j) {
+                    const float2   f  = P2::to_f32(h[i][j]);
+                    const uint32_t xh = P2::from_f32((f.x - mean) * rstd, (f.y - mean) * rstd);  // x_hat rounded to T
+                    const uint32_t m  = (MODE == ROW_ADALN) ? P2::add(a.w[j], P2::one()) : a.w[j];  // T(scale + 1) | gamma
+                    h[i][j]           = P2::add(P2::mul(m, xh), b.w[j]);                            // T(T(m * x_hat) + shift)
                 }
             }
         }
@@ -204,7 +213,12 @@ template<typename T, int VPT, int MODE> __global__ void __launch_bounds__(256) r
         for (int i = 0; i < VPT; ++i) {
             const int vi = tlane + i * tpr;
             if (live && vi < nvec) {
-                st_16(reinterpret_cast<T*>(p.y) + row * (size_t)p.dim + (vi << 3), pack8<T>(v[i]));
+                Vec16 o;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    o.w[j] = h[i][j];
+                }
+                st_16(reinterpret_cast<T*>(p.y) + row * (size_t)p.dim + (vi << 3), o);
             }
         }
     }
@@ -219,39 +233,43 @@ template<typename T, int VPT, int MODE> __global__ void __launch_bounds__(256) r
             if (live && vi < nvec) {
                 uint32_t w[2];
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const uint32_t lo = f32x2_to_e4m3x2(v[i][4 * h] * r, v[i][4 * h + 1] * r);
-                    const uint32_t hi = f32x2_to_e4m3x2(v[i][4 * h + 2] * r, v[i][4 * h + 3] * r);
-                    w[h]              = lo | (hi << 16);
+                for (int k = 0; k < 2; ++k) {
+                    const float2   f0 = P2::to_f32(h[i][2 * k]);
+                    const float2   f1 = P2::to_f32(h[i][2 * k + 1]);
+                    const uint32_t lo = f32x2_to_e4m3x2(f0.x * r, f0.y * r);
+                    const uint32_t hi = f32x2_to_e4m3x2(f1.x * r, f1.y * r);
+                    w[k]              = lo | (hi << 16);
                 }
                 st_8(p.qf8 + row * (size_t)p.dim + (vi << 3), w[0], w[1]);
             }
         }
     }
 
-    // ---- int8
+    // ---- int8: q = sat_s8(rne((float(y) * pre[c]) / s))
     if (p.q8 != nullptr) {
-        // apply the SmoothQuant per-channel factor first: (float(x) * pre[c]) / s
-        if (p.pre != nullptr) {
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int vi = tlane + i * tpr;
-                if (live && vi < nvec) {
-                    const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
-                    const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
-                    v[i][0] *= p0.x; v[i][1] *= p0.y; v[i][2] *= p0.z; v[i][3] *= p0.w;
-                    v[i][4] *= p1.x; v[i][5] *= p1.y; v[i][6] *= p1.z; v[i][7] *= p1.w;
-                }
-            }
-        }
         float s;
         if (p.scale_mode == LYRAQ_SCALE_PER_TOKEN_DYNAMIC) {
             float amax = 0.0f;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
+                const int vi = tlane + i * tpr;
+                if (live && vi < nvec) {
+                    float pre[8];
+                    if (p.pre != nullptr) {
+                        const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
+                        const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
+                        pre[0] = p0.x; pre[1] = p0.y; pre[2] = p0.z; pre[3] = p0.w;
+                        pre[4] = p1.x; pre[5] = p1.y; pre[6] = p1.z; pre[7] = p1.w;
+                    }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    amax = fmaxf(amax, fabsf(v[i][j]));
+                    for (int j = 0; j < 4; ++j) {
+                        float2 f = P2::to_f32(h[i][j]);
+                        if (p.pre != nullptr) {
+                            f.x *= pre[2 * j];
+                            f.y *= pre[2 * j + 1];
+                        }
+                        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+                    }
                 }
             }
             amax = team_reduce<true>(amax, tpr, red);
@@ -268,24 +286,39 @@ template<typename T, int VPT, int MODE> __global__ void __launch_bounds__(256) r
         for (int i = 0; i < VPT; ++i) {
             const int vi = tlane + i * tpr;
             if (live && vi < nvec) {
-                int q[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    q[j] = f32_to_s8(v[i][j] / s);
+                float pre[8];
+                if (p.pre != nullptr) {
+                    const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
+                    const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
+                    pre[0] = p0.x; pre[1] = p0.y; pre[2] = p0.z; pre[3] = p0.w;
+                    pre[4] = p1.x; pre[5] = p1.y; pre[6] = p1.z; pre[7] = p1.w;
                 }
-                st_8(p.q8 + row * (size_t)p.dim + (vi << 3), pack4_s8(q[0], q[1], q[2], q[3]),
-                     pack4_s8(q[4], q[5], q[6], q[7]));
+                uint32_t q[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float2 f = P2::to_f32(h[i][j]);
+                    if (p.pre != nullptr) {
+                        f.x *= pre[2 * j];
+                        f.y *= pre[2 * j + 1];
+                    }
+                    q[2 * j]     = f32_to_s8_bits(f.x / s);
+                    q[2 * j + 1] = f32_to_s8_bits(f.y / s);
+                }
+                st_8(p.q8 + row * (size_t)p.dim + (vi << 3), pack4_low_bytes(q[0], q[1], q[2], q[3]),
+                     pack4_low_bytes(q[4], q[5], q[6], q[7]));
             }
         }
     }
 }
 
-// Picks the team size and launches.  dim is a multiple of 8 and <= 16384.
+// Picks the team size and launches.  dim is a multiple of 8 and <= 16384.  The smallest team (32..256 threads) that
+// keeps at most six 16-byte vectors per thread is used, so narrow rows need no cross-warp reduction and every thread
+// has several independent loads in flight; only rows wider than 12288 elements use eight vectors per thread.
 template<typename T, int MODE> static int launch_row(RowParams p, cudaStream_t stream)
 {
     const int nvec = p.dim >> 3;
     int       tpr  = 32;
-    while (tpr < 256 && (nvec + tpr - 1) / tpr > 4) {
+    while (tpr < 256 && (nvec + tpr - 1) / tpr > 6) {
         tpr <<= 1;
     }
     p.tpr                = tpr;
@@ -300,6 +333,8 @@ template<typename T, int MODE> static int launch_row(RowParams p, cudaStream_t s
     }
     if (vpt <= 4) {
         row_quant_kernel<T, 4, MODE><<<(unsigned)grid, 256, 0, stream>>>(p);
+    } else if (vpt <= 6) {
+        row_quant_kernel<T, 6, MODE><<<(unsigned)grid, 256, 0, stream>>>(p);
     } else if (vpt <= 8) {
         row_quant_kernel<T, 8, MODE><<<(unsigned)grid, 256, 0, stream>>>(p);
     } else {
