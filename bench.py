@@ -204,6 +204,7 @@ class Int8Sdxl:
     unit = "TOP/s"
     dtype = "s8 (s32 accumulate in TMEM)"
     K, N = 640, 5120
+    roof_scale = 1e9  # the roofline of this case is in GB/s while the metric is in TOP/s
 
     def __init__(self, tokens):
         self.tokens = tokens or 8192
@@ -485,6 +486,9 @@ def run_ours(case, args, rank, world, local_rank):
         if status != 0:
             raise SystemExit("bench.py: device status %d (detail 0x%x)" % (status, detail))
 
+    if args.tile:
+        from lyradiff_b200 import _lib
+        _lib.check(_lib.lib().lyraq_debug_force_gemm_tile(args.tile), "lyraq_debug_force_gemm_tile")
     case.setup_gpu(dev)
     peaks = load_peaks()
     warmup = max(args.warmup, 3)
@@ -531,7 +535,8 @@ def run_ours(case, args, rank, world, local_rank):
         ms_step = ms_total / args.steps
         value = world * case.work_per_step / (ms_step * 1e-3) / case.scale
         e2e_value = world * case.work_per_step / (ms_e2e / args.steps * 1e-3) / case.scale
-        achieved = sum(case.timed_work) / (sum(timed_ms) * 1e-3) / case.scale
+        rscale = getattr(case, "roof_scale", case.scale)
+        achieved = sum(case.timed_work) / (sum(timed_ms) * 1e-3) / rscale
         peak, peak_source, nominal = case.peak(peaks)
         cpu = time_cpu(case, min(case.tokens, 256), 3, 1)
         roof = dict(case.roof)
@@ -539,7 +544,7 @@ def run_ours(case, args, rank, world, local_rank):
                      "frac_of_nominal": achieved / nominal, "nominal": nominal,
                      "per_launch_ms": dict(zip(case.timed_names, timed_ms)),
                      "per_launch_achieved": dict(zip(case.timed_names,
-                                                     [w / (t * 1e-3) / case.scale for w, t in zip(case.timed_work, timed_ms)]))})
+                                                     [w / (t * 1e-3) / rscale for w, t in zip(case.timed_work, timed_ms)]))})
         line = {
             "metric": case.metric, "value": value, "unit": case.unit, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": case.dtype,
@@ -564,6 +569,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--case", default="flux_fp8", choices=sorted(CASES))
     ap.add_argument("--tokens", type=int, default=0, help="override the number of token rows (0 = the configuration's own)")
+    ap.add_argument("--tile", type=int, default=0, choices=[0, 2561, 1281, 2562],
+                    help="force the dense-GEMM tile configuration (0 = automatic; see lyraq_debug_force_gemm_tile)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

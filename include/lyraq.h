@@ -63,6 +63,12 @@ LYRAQ_API const char* lyraq_status_string(int status);
  * The reference has no counterpart: its kernels have no bounded waits. */
 LYRAQ_API int lyraq_last_status(void* stream, uint32_t* detail);
 
+/* Test / sweep hook: force the tile configuration of the dense GEMMs.  0 = automatic (default); 2561 = one CTA,
+ * 128 x 256 tile; 1281 = one CTA, 128 x 128; 2562 = CTA pair, 256 x 256.  Process-wide, not thread-safe.
+ * No counterpart in the reference API; it plays the role of choosing a tactic by hand, which the reference does
+ * through CutlassGemmConfig (src/lyradiff/kernels/cutlass_extensions/include/cutlass_extensions/gemm_configs.h:101-130). */
+LYRAQ_API int lyraq_debug_force_gemm_tile(int code);
+
 /* ------------------------------------------------------------------ activation quantizers */
 
 /* INT8 SmoothQuant activation quantize: q = sat_s8(rne(float(x)*pre[c] / s)).

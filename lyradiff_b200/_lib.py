@@ -18,6 +18,7 @@ SIGNATURES = {
     "lyraq_version": (ctypes.c_char_p, []),
     "lyraq_status_string": (ctypes.c_char_p, [c_int]),
     "lyraq_last_status": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint32)]),
+    "lyraq_debug_force_gemm_tile": (c_int, [c_int]),
     "lyraq_quant_int8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_void_p]),
     "lyraq_quant_fp8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p]),
     "lyraq_fp8_amax_scale": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p]),

@@ -198,19 +198,36 @@ template<> struct Pair<__nv_bfloat16> {
     static __device__ __forceinline__ uint32_t one() { return 0x3F803F80u; }
 };
 
-// sat_s8(rne(v)) without the conversion unit: NaN -> 0 (as cvt.rni.sat.s8.f32 does), clamp to
-// [-128, 127] (also catches +-inf), then add 1.5 * 2^23: at that magnitude one ulp is 1, so the
-// fp32 add rounds v to the nearest integer, ties to even, and the low byte of the sum's bit
-// pattern is the two's-complement int8.  Returns the byte in bits [0, 8).
-__device__ __forceinline__ uint32_t f32_to_s8_bits(float v)
+// Eight quotients v[j] / s quantized exactly as the reference does, q = sat_s8(rne(fl32(v / s))), without a
+// division or a conversion per element.  r = fl32(1 / s) is computed once per row by the caller.
+//   t  = fma(v, r, 1.5 * 2^23)   one rounding: v*r to the nearest integer, ties to even (one ulp is 1 up there)
+//   tc = clamp(t, magic - 128, magic + 127); the low byte of tc's bit pattern is the two's-complement int8
+//   d  = fma(v, r, -(tc - magic)) the distance of v*r from that integer
+// v*r and fl32(v/s) both lie within |q| * 2^-24 <= 7.7e-6 of the true quotient, so they round to the same
+// integer unless the quotient is within 1.6e-5 of a half-integer.  If any of the eight is within 6.1e-5 of one
+// (or is NaN: 0/0, NaN input), the whole vector is redone with the IEEE divide and cvt.rni.sat.s8.f32, which
+// also gives NaN -> 0.  That happens for about one vector in a thousand.
+__device__ __forceinline__ void quant8_s8(const float* v, float s, float r, uint32_t& w0, uint32_t& w1)
 {
-    v = (v != v) ? 0.0f : v;
-    v = fminf(fmaxf(v, -128.0f), 127.0f);
-    return __float_as_uint(v + 12582912.0f);
-}
-__device__ __forceinline__ uint32_t pack4_low_bytes(uint32_t a, uint32_t b, uint32_t c, uint32_t d)
-{
-    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+    const float magic = 12582912.0f;
+    uint32_t    b[8];
+    bool        redo = false;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float t  = fmaf(v[j], r, magic);
+        const float tc = fminf(fmaxf(t, magic - 128.0f), magic + 127.0f);
+        const float d  = fmaf(v[j], r, magic - tc);
+        redo |= !(fabsf(fabsf(d) - 0.5f) >= 6.1e-5f);
+        b[j] = __float_as_uint(tc);
+    }
+    if (redo) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            b[j] = (uint32_t)f32_to_s8(v[j] / s);
+        }
+    }
+    w0 = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+    w1 = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
 }
 
 // ---------------------------------------------------------------------------------------------

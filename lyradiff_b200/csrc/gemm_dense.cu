@@ -2,7 +2,10 @@
 //
 //   Y[M,N] = epilogue( sum_k A[M,k] * B[N,k] ),  A and B both K-contiguous 8-bit.
 //
-// One persistent CTA per SM, 256 threads, warp-specialised:
+// One persistent CTA per SM, 256 threads, warp-specialised.  Large problems run as CTA PAIRS (a cluster of two):
+// tcgen05.mma.cta_group::2 computes a 256 x 256 tile across the two SMs, each CTA loading only its half of the A
+// rows and its half of the B rows, which cuts the operand traffic from L2 per flop by a third against a single
+// CTA's 128 x 256 tile.  Roles per CTA:
 //   warp 0   : TMA producer   - streams 128x128-byte A tiles and BLOCK_N x128-byte B tiles into a ring of
 //                               shared-memory stages (128-byte swizzle), one mbarrier per stage.
 //   warp 1   : MMA issuer     - one thread issues four tcgen05.mma (K = 32 bytes each) per stage into one of
@@ -54,11 +57,13 @@ struct GemmParams {
     EpilogueParams epi;
 };
 
-template<int BLOCK_N> struct GemmSmem {
+// BLOCK_N is the width of the output tile; CTAS = 1: one CTA computes 128 x BLOCK_N; CTAS = 2: a pair of CTAs
+// computes 256 x BLOCK_N with cta_group::2 MMAs, each CTA staging 128 A rows and BLOCK_N / 2 B rows per K block.
+template<int BLOCK_N, int CTAS> struct GemmSmem {
     static constexpr int kABytes     = kBlockM * kBlockK;
-    static constexpr int kBBytes     = BLOCK_N * kBlockK;
+    static constexpr int kBBytes     = (BLOCK_N / CTAS) * kBlockK;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages     = (kSmemBudget - 2048) / kStageBytes;  // 4 for BLOCK_N=256, 6 for 128
+    static constexpr int kStages     = (kSmemBudget - 2048) / kStageBytes;  // 4 (1 x 256), 7 (1 x 128), 7 (2 x 256)
     static constexpr int kBarBytes   = 256;
     static constexpr int kTotal      = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
 };
@@ -190,17 +195,19 @@ __device__ __forceinline__ void epilogue_chunk(const EpilogueParams& e, const ui
     store_row32<T>(crow, valid, vec_ok, v);
 }
 
-template<int KIND, int BLOCK_N>
+template<int KIND, int BLOCK_N, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p)
 {
-    using S = GemmSmem<BLOCK_N>;
+    using S = GemmSmem<BLOCK_N, CTAS>;
     constexpr int      kStages   = S::kStages;
+    constexpr int      kTileM    = kBlockM * CTAS;
     constexpr uint32_t kTmemCols = 2 * BLOCK_N;  // two accumulator buffers (power of two: 256 or 512)
-    constexpr uint32_t kIdesc    = (KIND == KIND_I8) ? umma_idesc(2u, 1u, kBlockM, BLOCK_N) : umma_idesc(1u, 0u, kBlockM, BLOCK_N);
+    constexpr uint32_t kIdesc    = (KIND == KIND_I8) ? umma_idesc(2u, 1u, kTileM, BLOCK_N) : umma_idesc(1u, 0u, kTileM, BLOCK_N);
 
     extern __shared__ uint8_t smem_raw[];
-    // 1024-byte alignment is what the 128-byte swizzle pattern of TMA and UMMA is anchored to.
+    // 1024-byte alignment is what the 128-byte swizzle pattern of TMA and UMMA is anchored to.  The dynamic shared
+    // window starts at the same offset in every CTA of the kernel, so both CTAs of a pair get the same layout.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t smem_a    = smem_base;
     const uint32_t smem_b    = smem_base + kStages * S::kABytes;
@@ -214,8 +221,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     uint32_t*      tmem_slot  = reinterpret_cast<uint32_t*>(gen_base + kStages * S::kStageBytes + 8 * (2 * kStages + 4));
     volatile int*  abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int warp = threadIdx.x >> 5;
-    const int lane = threadIdx.x & 31;
+    const int      warp    = threadIdx.x >> 5;
+    const int      lane    = threadIdx.x & 31;
+    const uint32_t rank    = (CTAS == 2) ? cluster_ctarank() : 0u;  // position in the pair; 0 = leader
+    const bool     leader  = (rank == 0);
+    const int      unit    = (CTAS == 2) ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;  // CTA or CTA pair
+    const int      n_units = (CTAS == 2) ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -224,7 +235,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar(b), 1);
-            mbar_init(tmem_empty_bar(b), 128);
+            mbar_init(tmem_empty_bar(b), 4 * CTAS);  // one arrival per epilogue warp of every CTA of the unit
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -232,11 +243,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         prefetch_tensormap(&tmap_b);
     }
     if (warp == 2) {
-        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-        tmem_relinquish();
+        if (CTAS == 2) {
+            tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if (CTAS == 2) {
+        cluster_sync_all();  // the peer's barriers are initialised before anything is signalled across the pair
+    } else {
+        __syncthreads();
+    }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -244,14 +264,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int num_kb    = (p.K + kBlockK - 1) / kBlockK;
 
     if (warp == 0 && lane == 0) {
-        // ------------------------------------------------------------------ TMA producer
+        // ------------------------------------------------------------------ TMA producer (every CTA loads its own halves)
         int      stage = 0;
         uint32_t phase = 0;
         int      issued = 0;
         bool     ok = true;
-        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+        for (int tile = unit; ok && tile < num_tiles; tile += n_units) {
             const int m_blk = tile % p.m_tiles;
             const int n_blk = tile / p.m_tiles;
+            const int a_row = m_blk * kTileM + (int)rank * kBlockM;
+            const int b_row = n_blk * BLOCK_N + (int)rank * (BLOCK_N / CTAS);
             for (int kb = 0; kb < num_kb; ++kb) {
                 if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                     report_timeout(p.status, 0x100u | (unsigned)stage);
@@ -259,9 +281,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     ok = false;
                     break;
                 }
-                mbar_arrive_expect_tx(full_bar(stage), (uint32_t)S::kStageBytes);
-                tma_load_2d(smem_a + stage * S::kABytes, &tmap_a, full_bar(stage), kb * kBlockK, m_blk * kBlockM);
-                tma_load_2d(smem_b + stage * S::kBBytes, &tmap_b, full_bar(stage), kb * kBlockK, n_blk * BLOCK_N);
+                if (CTAS == 2) {
+                    // both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair
+                    const uint32_t lbar = map_to_cta(full_bar(stage), 0u);
+                    if (leader) {
+                        mbar_arrive_expect_tx(full_bar(stage), 2u * (uint32_t)S::kStageBytes);
+                    }
+                    tma_load_2d_pair(smem_a + stage * S::kABytes, &tmap_a, lbar, kb * kBlockK, a_row);
+                    tma_load_2d_pair(smem_b + stage * S::kBBytes, &tmap_b, lbar, kb * kBlockK, b_row);
+                } else {
+                    mbar_arrive_expect_tx(full_bar(stage), (uint32_t)S::kStageBytes);
+                    tma_load_2d(smem_a + stage * S::kABytes, &tmap_a, full_bar(stage), kb * kBlockK, a_row);
+                    tma_load_2d(smem_b + stage * S::kBBytes, &tmap_b, full_bar(stage), kb * kBlockK, b_row);
+                }
                 ++issued;
                 if (++stage == kStages) {
                     stage = 0;
@@ -269,31 +301,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
         }
-        // Drain: every load this thread issued must have landed before the block may exit.
-        // (stage, phase) now name the next slot to fill; walk back over the last min(issued, kStages) slots.
-        int      s  = stage;
-        uint32_t ph = phase;
-        for (int i = 0; i < kStages && i < issued; ++i) {
-            if (s == 0) {
-                s = kStages;
-                ph ^= 1u;
-            }
-            --s;
-            uint64_t t0 = global_timer_ns();
-            while (!mbar_try_wait(full_bar(s), ph)) {
-                if (global_timer_ns() - t0 > kWaitLimitNs) {
-                    report_timeout(p.status, 0x500u | (unsigned)s);
-                    break;
+        if (CTAS == 1 || leader) {
+            // Drain: every load counted on this CTA's barriers must have landed before the block may exit.
+            // (stage, phase) now name the next slot to fill; walk back over the last min(issued, kStages) slots.
+            int      s  = stage;
+            uint32_t ph = phase;
+            for (int i = 0; i < kStages && i < issued; ++i) {
+                if (s == 0) {
+                    s = kStages;
+                    ph ^= 1u;
+                }
+                --s;
+                uint64_t t0 = global_timer_ns();
+                while (!mbar_try_wait(full_bar(s), ph)) {
+                    if (global_timer_ns() - t0 > kWaitLimitNs) {
+                        report_timeout(p.status, 0x500u | (unsigned)s);
+                        break;
+                    }
                 }
             }
         }
-    } else if (warp == 1 && lane == 0) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp == 1 && lane == 0 && leader) {
+        // ------------------------------------------------------------------ MMA issuer (the leader CTA only)
         int      stage = 0;
         uint32_t phase = 0;
         int      local = 0;
         bool     ok = true;
-        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++local) {
+        // cluster addresses of the peer's barriers (same offsets): its producer and epilogue wait on those
+        const uint32_t peer = (CTAS == 2) ? 1u : 0u;
+        for (int tile = unit; ok && tile < num_tiles; tile += n_units, ++local) {
             const int      buf       = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             if (!mbar_wait(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag)) {
@@ -318,20 +354,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     // advancing K by 32 bytes inside the swizzled 128-byte row: +2 in 16-byte units
                     const uint64_t koff = (uint64_t)(k * (kUmmaK >> 4));
                     const uint32_t acc  = (kb > 0 || k > 0) ? 1u : 0u;
-                    if (KIND == KIND_I8) {
-                        mma_i8(d_tmem, adesc + koff, bdesc + koff, kIdesc, acc);
+                    if (CTAS == 2) {
+                        if (KIND == KIND_I8) {
+                            mma_i8_pair(d_tmem, adesc + koff, bdesc + koff, kIdesc, acc);
+                        } else {
+                            mma_f8f6f4_pair(d_tmem, adesc + koff, bdesc + koff, kIdesc, acc);
+                        }
                     } else {
-                        mma_f8f6f4(d_tmem, adesc + koff, bdesc + koff, kIdesc, acc);
+                        if (KIND == KIND_I8) {
+                            mma_i8(d_tmem, adesc + koff, bdesc + koff, kIdesc, acc);
+                        } else {
+                            mma_f8f6f4(d_tmem, adesc + koff, bdesc + koff, kIdesc, acc);
+                        }
                     }
                 }
-                tc_commit(empty_bar(stage));  // the stage is free once these MMAs have read it
+                // the stage is free, in both CTAs, once these MMAs have read it
+                if (CTAS == 2) {
+                    tc_commit_pair(empty_bar(stage));
+                    tc_commit_pair(map_to_cta(empty_bar(stage), peer));
+                } else {
+                    tc_commit(empty_bar(stage));
+                }
                 if (++stage == kStages) {
                     stage = 0;
                     phase ^= 1u;
                 }
             }
             if (ok) {
-                tc_commit(tmem_full_bar(buf));  // accumulator complete
+                // accumulator complete: each CTA's epilogue reads its own half of the rows
+                if (CTAS == 2) {
+                    tc_commit_pair(tmem_full_bar(buf));
+                    tc_commit_pair(map_to_cta(tmem_full_bar(buf), peer));
+                } else {
+                    tc_commit(tmem_full_bar(buf));
+                }
             }
         }
     } else if (warp >= kEpiWarp0) {
@@ -345,7 +401,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         const bool vec_ok = (e.c_dtype == LYRAQ_F32 || e.c_dtype == LYRAQ_S32) ? ((e.ldc & 3) == 0) : ((e.ldc & 7) == 0);
         int local = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+        for (int tile = unit; tile < num_tiles; tile += n_units, ++local) {
             const int      buf       = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             const int      m_blk     = tile % p.m_tiles;
@@ -359,7 +415,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 break;
             }
             tc_fence_after_sync();
-            const int row = m_blk * kBlockM + quad * 32 + lane;
+            const int row = m_blk * kTileM + (int)rank * kBlockM + quad * 32 + lane;
             float     row_scale = 1.0f;
             if (KIND == KIND_I8 && e.c_dtype != LYRAQ_S32) {
                 row_scale = e.row_scale_per_token ? ((row < p.M) ? __ldg(e.row_scale + row) : 0.0f) : __ldg(e.row_scale);
@@ -399,17 +455,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                 }
             }
+            // this warp is done with the accumulator buffer: tell the MMA issuer (in the leader CTA)
             tc_fence_before_sync();
-            mbar_arrive(tmem_empty_bar(buf));
+            __syncwarp();
+            if (lane == 0) {
+                if (CTAS == 2 && !leader) {
+                    mbar_arrive_cluster(map_to_cta(tmem_empty_bar(buf), 0u));
+                } else {
+                    mbar_arrive(tmem_empty_bar(buf));
+                }
+            }
         }
     }
 
     // ---------------------------------------------------------------------- common exit
     tc_fence_before_sync();
-    __syncthreads();
+    if (CTAS == 2) {
+        cluster_sync_all();  // neither CTA may leave while its peer can still touch its shared or tensor memory
+    } else {
+        __syncthreads();
+    }
     if (warp == 2) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if (CTAS == 2) {
+            tmem_dealloc_pair(tmem_base, kTmemCols);
+        } else {
+            tmem_dealloc(tmem_base, kTmemCols);
+        }
     }
 }
 
@@ -470,41 +542,73 @@ int device_sm_count()
     return cached[dev];
 }
 
-// Cost model for the N tile: waves of (tiles / SMs) times the tile's width.
-static int pick_block_n(int m, int n, int sms)
+// Tile choice.  Cost of a configuration = waves (tiles / units that run at once) x work per tile.  A CTA pair with a
+// 256 x 256 tile moves a third less operand traffic per flop than a single CTA with 128 x 256, so it is preferred
+// (10 % bonus) whenever its wave quantisation is not worse; small or narrow problems fall back to one CTA.
+struct TileChoice {
+    int block_n;
+    int ctas;
+};
+
+static TileChoice pick_tile(int m, int n, int sms)
 {
-    const long m_tiles = (m + kBlockM - 1) / kBlockM;
-    const long t256    = m_tiles * ((n + 255) / 256);
-    const long t128    = m_tiles * ((n + 127) / 128);
-    const long c256    = ((t256 + sms - 1) / sms) * 256;
-    const long c128    = ((t128 + sms - 1) / sms) * 128;
-    return (c128 < c256) ? 128 : 256;
+    const long m128 = (m + 127) / 128, m256 = (m + 255) / 256;
+    const long n128 = (n + 127) / 128, n256 = (n + 255) / 256;
+    const long pairs = sms / 2;
+    const double c1_256 = (double)((m128 * n256 + sms - 1) / sms) * 256.0;
+    const double c1_128 = (double)((m128 * n128 + sms - 1) / sms) * 128.0;
+    const double c2_256 = (pairs > 0) ? (double)((m256 * n256 + pairs - 1) / pairs) * 256.0 * 0.9 : 1e30;
+    TileChoice best{256, 1};
+    double     cost = c1_256;
+    if (c1_128 < cost) {
+        best = TileChoice{128, 1};
+        cost = c1_128;
+    }
+    if (c2_256 <= cost) {
+        best = TileChoice{256, 2};
+    }
+    return best;
 }
 
-template<int KIND, int BLOCK_N>
+template<int KIND, int BLOCK_N, int CTAS>
 static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cudaStream_t stream)
 {
-    using S = GemmSmem<BLOCK_N>;
+    using S = GemmSmem<BLOCK_N, CTAS>;
     CUtensorMap ta, tb;
     int         st = make_tmap_bytes_2d(&ta, A, (uint64_t)p.M, (uint64_t)p.K, (uint64_t)p.K, kBlockM, kBlockK, true);
     if (st != LYRAQ_OK) {
         return st;
     }
-    st = make_tmap_bytes_2d(&tb, B, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.K, BLOCK_N, kBlockK, true);
+    st = make_tmap_bytes_2d(&tb, B, (uint64_t)p.N, (uint64_t)p.K, (uint64_t)p.K, BLOCK_N / CTAS, kBlockK, true);
     if (st != LYRAQ_OK) {
         return st;
     }
-    p.m_tiles = (p.M + kBlockM - 1) / kBlockM;
+    p.m_tiles = (p.M + kBlockM * CTAS - 1) / (kBlockM * CTAS);
     p.n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
     const long tiles = (long)p.m_tiles * p.n_tiles;
-    const int  grid  = (int)(tiles < sms ? tiles : sms);
-    auto       kern  = gemm_tcgen05_kernel<KIND, BLOCK_N>;
+    const long units = sms / CTAS;
+    const int  grid  = (int)(tiles < units ? tiles : units) * CTAS;
+    auto       kern  = gemm_tcgen05_kernel<KIND, BLOCK_N, CTAS>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) {
         return LYRAQ_ERR_CUDA;
     }
-    kern<<<grid, kThreads, S::kTotal, stream>>>(ta, tb, p);
-    return launch_status();
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim          = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim         = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = S::kTotal;
+    cfg.stream           = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTAS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs    = attr;
+    cfg.numAttrs = (CTAS > 1) ? 1 : 0;
+    return cuda_status(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
 }
+
+// forced tile configuration for tests and sweeps: 0 = automatic, else block_n * 10 + ctas (2561, 1281, 2562)
+static int g_forced_tile = 0;
 
 template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams p, cudaStream_t stream)
 {
@@ -533,10 +637,17 @@ template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams 
         return LYRAQ_ERR_CUDA;
     }
     p.epi.ldc = p.N;
-    if (pick_block_n(p.M, p.N, sms) == 128) {
-        return launch_gemm<KIND, 128>(A, B, p, sms, stream);
+    TileChoice t = pick_tile(p.M, p.N, sms);
+    if (g_forced_tile != 0) {
+        t = TileChoice{g_forced_tile / 10, g_forced_tile % 10};
     }
-    return launch_gemm<KIND, 256>(A, B, p, sms, stream);
+    if (t.ctas == 2) {
+        return launch_gemm<KIND, 256, 2>(A, B, p, sms, stream);
+    }
+    if (t.block_n == 128) {
+        return launch_gemm<KIND, 128, 1>(A, B, p, sms, stream);
+    }
+    return launch_gemm<KIND, 256, 1>(A, B, p, sms, stream);
 }
 
 }  // namespace lyraq
@@ -544,6 +655,15 @@ template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams 
 using namespace lyraq;
 
 extern "C" {
+
+int lyraq_debug_force_gemm_tile(int code)
+{
+    if (code != 0 && code != 2561 && code != 1281 && code != 2562) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    g_forced_tile = code;
+    return LYRAQ_OK;
+}
 
 int lyraq_gemm_int8(const int8_t* A, const int8_t* B, const float* alpha_col, const float* alpha_row, int row_scale_mode,
                     void* C, int c_dtype, const void* bias, int m, int n, int k, void* workspace, size_t workspace_bytes,

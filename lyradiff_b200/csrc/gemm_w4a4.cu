@@ -144,7 +144,8 @@ __device__ __forceinline__ void final_store32(const Params& p, const float* acc,
     }
 }
 
-__global__ void __maxnreg__(152)
+// 13 warps x 32 lanes x 144 registers = 59904 of the 65536 registers of an SM (allocation is per warp, in units of 512)
+__global__ void __maxnreg__(144)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p)
 {
     constexpr uint32_t kTmemCols = kPBufs * kBN;  // 512

@@ -71,7 +71,8 @@ template<bool IS_MAX> __device__ __forceinline__ float team_reduce(float v, int 
     return r;
 }
 
-// Row data lives in registers as packed pairs of T (h[i][0..3] = the i-th 16-byte vector of this thread).
+// The row lives in registers as fp32 (f[i][0..7] = the i-th 16-byte vector of this thread); every step the
+// reference evaluates in T is done on packed pairs with the type's native single-rounding add / multiply.
 template<typename T, int VPT, int MODE>
 __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(const RowParams p)
 {
@@ -85,7 +86,7 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
     const bool   live  = row < p.rows;
     const int    nvec  = p.dim >> 3;
 
-    uint32_t h[VPT][4];
+    float f[VPT][8];
 
     const T* xrow = reinterpret_cast<const T*>(p.x) + row * (size_t)p.in_cols;
 
@@ -94,33 +95,24 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
     for (int i = 0; i < VPT; ++i) {
         const int vi = tlane + i * tpr;
         if (live && vi < nvec) {
-            const int   c = vi << 3;
-            const Vec16 x = ld_nc_16(xrow + c);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                h[i][j] = x.w[j];
-            }
+            const int c = vi << 3;
+            Vec16     h = ld_nc_16(xrow + c);
             if (MODE == ROW_LN && p.residual != nullptr) {
                 // h = T(T(x + residual) + bias)
                 const Vec16 r = ld_nc_16(reinterpret_cast<const T*>(p.residual) + row * (size_t)p.dim + c);
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    h[i][j] = P2::add(h[i][j], r.w[j]);
+                    h.w[j] = P2::add(h.w[j], r.w[j]);
                 }
                 if (p.bias != nullptr) {
                     const Vec16 b = ld_nc_16(reinterpret_cast<const T*>(p.bias) + c);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        h[i][j] = P2::add(h[i][j], b.w[j]);
+                        h.w[j] = P2::add(h.w[j], b.w[j]);
                     }
                 }
                 if (p.sum_out != nullptr) {
-                    Vec16 o;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        o.w[j] = h[i][j];
-                    }
-                    st_16(reinterpret_cast<T*>(p.sum_out) + row * (size_t)p.dim + c, o);
+                    st_16(reinterpret_cast<T*>(p.sum_out) + row * (size_t)p.dim + c, h);
                 }
             }
             if (MODE == ROW_GEGLU) {
@@ -130,8 +122,8 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
                     const Vec16 bg = ld_nc_16(reinterpret_cast<const T*>(p.bias) + p.dim + c);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        h[i][j] = P2::add(h[i][j], bh.w[j]);
-                        g.w[j]  = P2::add(g.w[j], bg.w[j]);
+                        h.w[j] = P2::add(h.w[j], bh.w[j]);
+                        g.w[j] = P2::add(g.w[j], bg.w[j]);
                     }
                 }
 #pragma unroll
@@ -143,26 +135,34 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
                     const float    c0   = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (gf.x + 0.044715f * cf.x)));
                     const float    c1   = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (gf.y + 0.044715f * cf.y)));
                     const uint32_t act  = P2::mul(g.w[j], P2::from_f32(c0, c1));
-                    h[i][j]             = P2::mul(h[i][j], act);
+                    h.w[j]              = P2::mul(h.w[j], act);
                 }
+            }
+            if ((MODE == ROW_PLAIN || MODE == ROW_GEGLU) && p.y != nullptr) {
+                st_16(reinterpret_cast<T*>(p.y) + row * (size_t)p.dim + c, h);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 t = P2::to_f32(h.w[j]);
+                f[i][2 * j]     = t.x;
+                f[i][2 * j + 1] = t.y;
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                h[i][j] = 0u;
+            for (int j = 0; j < 8; ++j) {
+                f[i][j] = 0.0f;
             }
         }
     }
 
-    // ---- row statistics (fp32) and normalisation + modulation (T arithmetic)
+    // ---- row statistics (fp32), then normalise and modulate (T arithmetic)
     if (MODE == ROW_ADALN || MODE == ROW_LN) {
         float s = 0.0f;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float2 f = P2::to_f32(h[i][j]);
-                s += f.x + f.y;
+            for (int j = 0; j < 8; ++j) {
+                s += f[i][j];
             }
         }
         s                = team_reduce<false>(s, tpr, red);
@@ -173,10 +173,9 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
             const int vi = tlane + i * tpr;
             if (vi < nvec) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float2 f  = P2::to_f32(h[i][j]);
-                    const float  d0 = f.x - mean, d1 = f.y - mean;
-                    m2 += d0 * d0 + d1 * d1;
+                for (int j = 0; j < 8; ++j) {
+                    const float d = f[i][j] - mean;
+                    m2            = fmaf(d, d, m2);
                 }
             }
         }
@@ -184,7 +183,7 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
         const float var  = fmaxf(m2 / (float)p.dim, 0.0f);
         const float rstd = (float)(1.0 / sqrt((double)var + (double)p.eps));
 
-        const size_t brow = (MODE == ROW_ADALN) ? (row / (size_t)p.rows_per_batch) : 0;
+        const size_t brow  = (MODE == ROW_ADALN) ? (row / (size_t)p.rows_per_batch) : 0;
         const T*     mul_v = (MODE == ROW_ADALN) ? reinterpret_cast<const T*>(p.ada_scale) + brow * (size_t)p.dim
                                                  : reinterpret_cast<const T*>(p.gamma);
         const T*     add_v = (MODE == ROW_ADALN) ? reinterpret_cast<const T*>(p.ada_shift) + brow * (size_t)p.dim
@@ -196,29 +195,20 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
                 const int   c = vi << 3;
                 const Vec16 a = ld_nc_16(mul_v + c);
                 const Vec16 b = ld_nc_16(add_v + c);
+                Vec16       y;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float2   f  = P2::to_f32(h[i][j]);
-                    const uint32_t xh = P2::from_f32((f.x - mean) * rstd, (f.y - mean) * rstd);  // x_hat rounded to T
-                    const uint32_t m  = (MODE == ROW_ADALN) ? P2::add(a.w[j], P2::one()) : a.w[j];  // T(scale + 1) | gamma
-                    h[i][j]           = P2::add(P2::mul(m, xh), b.w[j]);                            // T(T(m * x_hat) + shift)
+                    // x_hat rounded to T; m = T(scale + 1) | gamma; y = T(T(m * x_hat) + shift)
+                    const uint32_t xh = P2::from_f32((f[i][2 * j] - mean) * rstd, (f[i][2 * j + 1] - mean) * rstd);
+                    const uint32_t m  = (MODE == ROW_ADALN) ? P2::add(a.w[j], P2::one()) : a.w[j];
+                    y.w[j]            = P2::add(P2::mul(m, xh), b.w[j]);
+                    const float2 t    = P2::to_f32(y.w[j]);
+                    f[i][2 * j]       = t.x;
+                    f[i][2 * j + 1]   = t.y;
                 }
-            }
-        }
-    }
-
-    // ---- un-quantized copy
-    if (p.y != nullptr) {
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int vi = tlane + i * tpr;
-            if (live && vi < nvec) {
-                Vec16 o;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    o.w[j] = h[i][j];
+                if (p.y != nullptr) {
+                    st_16(reinterpret_cast<T*>(p.y) + row * (size_t)p.dim + c, y);
                 }
-                st_16(reinterpret_cast<T*>(p.y) + row * (size_t)p.dim + (vi << 3), o);
             }
         }
     }
@@ -231,45 +221,35 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
         for (int i = 0; i < VPT; ++i) {
             const int vi = tlane + i * tpr;
             if (live && vi < nvec) {
-                uint32_t w[2];
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const float2   f0 = P2::to_f32(h[i][2 * k]);
-                    const float2   f1 = P2::to_f32(h[i][2 * k + 1]);
-                    const uint32_t lo = f32x2_to_e4m3x2(f0.x * r, f0.y * r);
-                    const uint32_t hi = f32x2_to_e4m3x2(f1.x * r, f1.y * r);
-                    w[k]              = lo | (hi << 16);
-                }
-                st_8(p.qf8 + row * (size_t)p.dim + (vi << 3), w[0], w[1]);
+                const uint32_t w0 = f32x2_to_e4m3x2(f[i][0] * r, f[i][1] * r) | (f32x2_to_e4m3x2(f[i][2] * r, f[i][3] * r) << 16);
+                const uint32_t w1 = f32x2_to_e4m3x2(f[i][4] * r, f[i][5] * r) | (f32x2_to_e4m3x2(f[i][6] * r, f[i][7] * r) << 16);
+                st_8(p.qf8 + row * (size_t)p.dim + (vi << 3), w0, w1);
             }
         }
     }
 
     // ---- int8: q = sat_s8(rne((float(y) * pre[c]) / s))
     if (p.q8 != nullptr) {
+        if (p.pre != nullptr) {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int vi = tlane + i * tpr;
+                if (live && vi < nvec) {
+                    const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
+                    const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
+                    f[i][0] *= p0.x; f[i][1] *= p0.y; f[i][2] *= p0.z; f[i][3] *= p0.w;
+                    f[i][4] *= p1.x; f[i][5] *= p1.y; f[i][6] *= p1.z; f[i][7] *= p1.w;
+                }
+            }
+        }
         float s;
         if (p.scale_mode == LYRAQ_SCALE_PER_TOKEN_DYNAMIC) {
             float amax = 0.0f;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
-                const int vi = tlane + i * tpr;
-                if (live && vi < nvec) {
-                    float pre[8];
-                    if (p.pre != nullptr) {
-                        const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
-                        const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
-                        pre[0] = p0.x; pre[1] = p0.y; pre[2] = p0.z; pre[3] = p0.w;
-                        pre[4] = p1.x; pre[5] = p1.y; pre[6] = p1.z; pre[7] = p1.w;
-                    }
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float2 f = P2::to_f32(h[i][j]);
-                        if (p.pre != nullptr) {
-                            f.x *= pre[2 * j];
-                            f.y *= pre[2 * j + 1];
-                        }
-                        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
-                    }
+                for (int j = 0; j < 8; ++j) {
+                    amax = fmaxf(amax, fabsf(f[i][j]));
                 }
             }
             amax = team_reduce<true>(amax, tpr, red);
@@ -282,30 +262,14 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
         } else {
             s = __ldg(p.q8_scale);
         }
+        const float r = 1.0f / s;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int vi = tlane + i * tpr;
             if (live && vi < nvec) {
-                float pre[8];
-                if (p.pre != nullptr) {
-                    const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
-                    const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
-                    pre[0] = p0.x; pre[1] = p0.y; pre[2] = p0.z; pre[3] = p0.w;
-                    pre[4] = p1.x; pre[5] = p1.y; pre[6] = p1.z; pre[7] = p1.w;
-                }
-                uint32_t q[8];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float2 f = P2::to_f32(h[i][j]);
-                    if (p.pre != nullptr) {
-                        f.x *= pre[2 * j];
-                        f.y *= pre[2 * j + 1];
-                    }
-                    q[2 * j]     = f32_to_s8_bits(f.x / s);
-                    q[2 * j + 1] = f32_to_s8_bits(f.y / s);
-                }
-                st_8(p.q8 + row * (size_t)p.dim + (vi << 3), pack4_low_bytes(q[0], q[1], q[2], q[3]),
-                     pack4_low_bytes(q[4], q[5], q[6], q[7]));
+                uint32_t w0, w1;
+                quant8_s8(f[i], s, r, w0, w1);
+                st_8(p.q8 + row * (size_t)p.dim + (vi << 3), w0, w1);
             }
         }
     }

@@ -19,6 +19,14 @@ def ops():
     return _ops
 
 
+@pytest.fixture(params=[0, 2561, 1281, 2562], ids=["auto", "1cta_n256", "1cta_n128", "pair_n256"])
+def tile(request):
+    from lyradiff_b200 import _lib
+    assert _lib.lib().lyraq_debug_force_gemm_tile(request.param) == 0
+    yield request.param
+    _lib.lib().lyraq_debug_force_gemm_tile(0)
+
+
 def _run(ops, f, dtype, bias=True, residual=False, gelu=False, alpha=1.0, beta=1.0):
     m, k = f["qx"].shape
     n = f["qw"].shape[0]
@@ -43,7 +51,7 @@ def _check(y, want, dtype):
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 128, 256), (130, 72, 144), (1, 8, 16), (300, 1000, 3072),
                                    (256, 384, 12288)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_plain_and_bias(ops, m, n, k, dtype):
+def test_plain_and_bias(ops, tile, m, n, k, dtype):
     f = workloads.fp8_linear(m, k, n, seed=m + n, with_residual=True)
     for bias in (False, True):
         y, want = _run(ops, f, dtype, bias=bias)
@@ -51,7 +59,7 @@ def test_plain_and_bias(ops, m, n, k, dtype):
     check_status()
 
 
-def test_exact_on_small_integers(ops):
+def test_exact_on_small_integers(ops, tile):
     """Operands that are small integers in e4m3 and unit scales give integer sums below 2**24: fp32 accumulation
     must then be exact, whatever the order."""
     g = torch.Generator().manual_seed(4)
@@ -65,7 +73,7 @@ def test_exact_on_small_integers(ops):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
-def test_gelu_and_residual_epilogues(ops, dtype):
+def test_gelu_and_residual_epilogues(ops, tile, dtype):
     f = workloads.fp8_linear(260, 512, 392, seed=21, with_residual=True)
     for kw in ({"gelu": True}, {"gelu": True, "bias": False}, {"residual": True}, {"residual": True, "beta": 0.5, "alpha": 2.0}):
         y, want = _run(ops, f, dtype, **kw)

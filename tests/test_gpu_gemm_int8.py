@@ -17,6 +17,15 @@ def ops():
     return _ops
 
 
+@pytest.fixture(params=[0, 2561, 1281, 2562], ids=["auto", "1cta_n256", "1cta_n128", "pair_n256"])
+def tile(request):
+    """Runs a test once per tile configuration of the dense GEMM (automatic choice, and each kernel variant forced)."""
+    from lyradiff_b200 import _lib
+    assert _lib.lib().lyraq_debug_force_gemm_tile(request.param) == 0
+    yield request.param
+    _lib.lib().lyraq_debug_force_gemm_tile(0)
+
+
 def _rand_int8(m, n, k, seed):
     g = torch.Generator().manual_seed(seed)
     a = torch.randint(-128, 128, (m, k), generator=g, dtype=torch.int8)
@@ -37,7 +46,7 @@ SHAPES = [
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)
-def test_int32_accumulators_bit_exact(ops, m, n, k):
+def test_int32_accumulators_bit_exact(ops, tile, m, n, k):
     a, b = _rand_int8(m, n, k, seed=m + n + k)
     c = torch.full((m, n), -7, dtype=torch.int32, device="cuda")
     ops.run_gemm_int8(cu(a), cu(b), None, None, c)
@@ -47,7 +56,7 @@ def test_int32_accumulators_bit_exact(ops, m, n, k):
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (130, 72, 144), (700, 1280, 640)])
-def test_dequant_epilogue_bit_exact(ops, dtype, m, n, k):
+def test_dequant_epilogue_bit_exact(ops, tile, dtype, m, n, k):
     a, b = _rand_int8(m, n, k, seed=3 * m + n)
     g = torch.Generator().manual_seed(m)
     alpha_col = (torch.rand(n, generator=g) * 1e-3 + 1e-4).float()
