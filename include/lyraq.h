@@ -63,6 +63,11 @@ LYRAQ_API const char* lyraq_status_string(int status);
  * The reference has no counterpart: its kernels have no bounded waits. */
 LYRAQ_API int lyraq_last_status(void* stream, uint32_t* detail);
 
+/* Text of the last CUDA runtime / driver error that made an entry point return LYRAQ_ERR_CUDA (which call, the
+ * error string and name).  Process-wide, for diagnostics.  The reference prints such errors to its log
+ * (check_cuda_error, src/lyradiff/utils/cuda_utils.h:62-90); this is the same information as a string. */
+LYRAQ_API const char* lyraq_last_cuda_error(void);
+
 /* Test / sweep hook: force the tile configuration of the dense GEMMs.  0 = automatic (default); 2561 = one CTA,
  * 128 x 256 tile; 1281 = one CTA, 128 x 128; 2562 = CTA pair, 256 x 256.  Process-wide, not thread-safe.
  * No counterpart in the reference API; it plays the role of choosing a tactic by hand, which the reference does

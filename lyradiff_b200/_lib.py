@@ -19,6 +19,7 @@ SIGNATURES = {
     "lyraq_status_string": (ctypes.c_char_p, [c_int]),
     "lyraq_last_status": (c_int, [c_void_p, ctypes.POINTER(ctypes.c_uint32)]),
     "lyraq_debug_force_gemm_tile": (c_int, [c_int]),
+    "lyraq_last_cuda_error": (ctypes.c_char_p, []),
     "lyraq_quant_int8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_void_p]),
     "lyraq_quant_fp8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p]),
     "lyraq_fp8_amax_scale": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p]),
@@ -48,6 +49,8 @@ class LyraqError(RuntimeError):
     def __init__(self, status, where):
         self.status = status
         msg = lib().lyraq_status_string(status).decode() if _lib is not None else str(status)
+        if status == 3 and _lib is not None:
+            msg += " [" + lib().lyraq_last_cuda_error().decode() + "]"
         super().__init__("%s failed: %s (status %d)" % (where, msg, status))
 
 

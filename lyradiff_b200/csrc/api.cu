@@ -1,6 +1,8 @@
 // Library-level entry points: version, status strings, the per-device status word.
 #include "common.cuh"
 
+#include <cstdio>
+
 namespace lyraq {
 
 // Word 0: status code written by the first kernel wait that gave up; word 1: which wait.
@@ -24,9 +26,18 @@ unsigned int* status_word_ptr()
     return g_status_addr[dev];
 }
 
+static char g_last_error[256] = "no CUDA error recorded";
+
+void record_cuda_error(cudaError_t e, const char* where)
+{
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", where, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
 }  // namespace lyraq
 
 extern "C" {
+
+const char* lyraq_last_cuda_error(void) { return lyraq::g_last_error; }
 
 const char* lyraq_version(void) { return "lyraq 0.1 (sm_100a)"; }
 

@@ -207,6 +207,30 @@ template<> struct Pair<__nv_bfloat16> {
 // integer unless the quotient is within 1.6e-5 of a half-integer.  If any of the eight is within 6.1e-5 of one
 // (or is NaN: 0/0, NaN input), the whole vector is redone with the IEEE divide and cvt.rni.sat.s8.f32, which
 // also gives NaN -> 0.  That happens for about one vector in a thousand.
+// Variant for scales computed from the row itself (s = amax / 127): the quotient cannot exceed 127 * (1 + 2^-23)
+// in magnitude, so no clamp is needed, d always lies in [-0.5, 0.5], and the near-tie test reduces to one maximum.
+__device__ __forceinline__ void quant8_s8_inrange(const float* v, float s, float r, uint32_t& w0, uint32_t& w1)
+{
+    const float magic = 12582912.0f;
+    uint32_t    b[8];
+    float       dmax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float t = fmaf(v[j], r, magic);
+        const float d = fmaf(v[j], r, magic - t);
+        dmax          = fmaxf(dmax, fabsf(d));
+        b[j]          = __float_as_uint(t);
+    }
+    if (dmax > 0.5f - 6.1e-5f) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            b[j] = (uint32_t)f32_to_s8(v[j] / s);
+        }
+    }
+    w0 = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+    w1 = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
+}
+
 __device__ __forceinline__ void quant8_s8(const float* v, float s, float r, uint32_t& w0, uint32_t& w1)
 {
     const float magic = 12582912.0f;
@@ -234,8 +258,18 @@ __device__ __forceinline__ void quant8_s8(const float* v, float s, float r, uint
 // Host-side checks.
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? LYRAQ_OK : LYRAQ_ERR_CUDA; }
+// The last CUDA error any entry point saw (process-wide), readable through lyraq_last_cuda_error().
+void record_cuda_error(cudaError_t e, const char* where);
 
-inline int launch_status() { return cuda_status(cudaGetLastError()); }
+inline int cuda_status(cudaError_t e, const char* where = "cuda call")
+{
+    if (e == cudaSuccess) {
+        return LYRAQ_OK;
+    }
+    record_cuda_error(e, where);
+    return LYRAQ_ERR_CUDA;
+}
+
+inline int launch_status() { return cuda_status(cudaGetLastError(), "kernel launch"); }
 
 }  // namespace lyraq

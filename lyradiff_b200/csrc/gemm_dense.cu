@@ -2,17 +2,21 @@
 //
 //   Y[M,N] = epilogue( sum_k A[M,k] * B[N,k] ),  A and B both K-contiguous 8-bit.
 //
-// One persistent CTA per SM, 256 threads, warp-specialised.  Large problems run as CTA PAIRS (a cluster of two):
+// One persistent CTA per SM, 384 threads, warp-specialised.  Large problems run as CTA PAIRS (a cluster of two):
 // tcgen05.mma.cta_group::2 computes a 256 x 256 tile across the two SMs, each CTA loading only its half of the A
 // rows and its half of the B rows, which cuts the operand traffic from L2 per flop by a third against a single
 // CTA's 128 x 256 tile.  Roles per CTA:
-//   warp 0   : TMA producer   - streams 128x128-byte A tiles and BLOCK_N x128-byte B tiles into a ring of
-//                               shared-memory stages (128-byte swizzle), one mbarrier per stage.
-//   warp 1   : MMA issuer     - one thread issues four tcgen05.mma (K = 32 bytes each) per stage into one of
-//                               two accumulator buffers in tensor memory, and commits to free the stage.
-//   warp 2   : allocates / frees tensor memory.
-//   warps 4-7: epilogue       - tcgen05.ld the finished accumulator (warp w reads TMEM lanes 32(w-4)..),
-//                               apply dequant scales / bias / GELU / residual in registers, store.
+//   warp 0    : TMA producer  - streams 128 x 128-byte A tiles and B tiles into a ring of shared-memory stages
+//                               (128-byte swizzle), one mbarrier per stage.
+//   warp 1    : MMA issuer    - one thread issues four tcgen05.mma (K = 32 bytes each) per stage into one of two
+//                               accumulator buffers in tensor memory, and commits to free the stage.
+//   warp 2    : allocates / frees tensor memory.
+//   warps 4-11: epilogue      - warp w reads TMEM lanes 32 (w % 4).. and the column half (w - 4) / 4.  Per tile the
+//                               eight warps first stage the tile's column scales and bias in shared memory (one
+//                               coalesced load, one named barrier), then stream 32-column chunks: tcgen05.ld of chunk
+//                               c+1 is in flight while chunk c gets its scales / bias / GELU / residual in registers;
+//                               16-bit results go through a 64-byte-swizzled shared-memory box and leave with one TMA
+//                               store per chunk (full 64-byte row segments, rows and columns clipped by the hardware).
 // The two accumulator buffers let the epilogue of tile i overlap the main loop of tile i+1.
 // Every mbarrier wait is bounded; on a timeout the role records it in the status word, raises the
 // block's abort flag and all roles fall through to the common exit, where tensor memory is freed.
@@ -23,12 +27,16 @@ namespace lyraq {
 
 using namespace sm100;
 
-constexpr int kBlockM     = 128;
-constexpr int kBlockK     = 128;  // bytes == elements for 8-bit operands
-constexpr int kUmmaK      = 32;
-constexpr int kThreads    = 256;
-constexpr int kEpiWarp0   = 4;
-constexpr int kSmemBudget = 227 * 1024;
+constexpr int kBlockM      = 128;
+constexpr int kBlockK      = 128;  // bytes == elements for 8-bit operands
+constexpr int kUmmaK       = 32;
+constexpr int kThreads     = 384;
+constexpr int kEpiWarp0    = 4;
+constexpr int kEpiWarps    = 8;
+constexpr int kSmemBudget  = 227 * 1024;
+constexpr int kStoreBox    = 32 * 64;                       // one warp's staging box: 32 rows x 64 bytes
+constexpr int kEpiSmem     = kEpiWarps * kStoreBox + 2 * 256 * 8;  // boxes + two parities of 256 (scale, bias) pairs
+constexpr int kBarBytes    = 256;
 
 enum GemmKind { KIND_I8 = 0, KIND_F8 = 1 };
 
@@ -36,6 +44,7 @@ struct EpilogueParams {
     void*        C;
     int          c_dtype;
     int          ldc;
+    int          tma_store;  // 16-bit output whose row pitch allows TMA stores
     // int8: y = T(float(acc) * (col_scale[n] * row_scale)), then T(y + bias)
     const float* col_scale;
     const float* row_scale;
@@ -63,36 +72,23 @@ template<int BLOCK_N, int CTAS> struct GemmSmem {
     static constexpr int kABytes     = kBlockM * kBlockK;
     static constexpr int kBBytes     = (BLOCK_N / CTAS) * kBlockK;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages     = (kSmemBudget - 2048) / kStageBytes;  // 4 (1 x 256), 7 (1 x 128), 7 (2 x 256)
-    static constexpr int kBarBytes   = 256;
-    static constexpr int kTotal      = kStages * kStageBytes + kBarBytes + 1024;  // + alignment slack
+    static constexpr int kStages     = (kSmemBudget - 1024 - kBarBytes - kEpiSmem) / kStageBytes;  // 4 (1 x 256) or 6
+    static constexpr int kEpiOffset  = kStages * kStageBytes;           // 1024-aligned: stage sizes are multiples of 16 KB
+    static constexpr int kBarOffset  = kEpiOffset + kEpiSmem;
+    static constexpr int kTotal      = kBarOffset + kBarBytes + 1024;   // + alignment slack
 };
 
-// Load 32 values of a T row (or a scalar-predicated tail) to fp32.
-template<typename T>
-__device__ __forceinline__ void load_row32(const T* p, int valid, bool vec_ok, float* out)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t smem_src, int x, int y)
 {
-    if (vec_ok && valid >= 32) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            unpack8<T>(ld_nc_16(p + 8 * i), out + 8 * i);
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            out[i] = (i < valid) ? to_f32(p[i]) : 0.0f;
-        }
-    }
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(smem_src), "r"(x), "r"(y)
+                 : "memory");
 }
-template<>
-__device__ __forceinline__ void load_row32<float>(const float* p, int valid, bool vec_ok, float* out)
-{
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        out[i] = (i < valid) ? p[i] : 0.0f;
-    }
-}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all of this thread's committed stores have finished READING shared memory (the box may be overwritten)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
+// 32 values of one output row -> global memory, directly (fp32 / int32 outputs, or rows whose pitch rules out TMA).
 template<typename T> __device__ __forceinline__ void store_row32(T* p, int valid, bool vec_ok, const float* v)
 {
     if (vec_ok && valid >= 32) {
@@ -131,77 +127,65 @@ template<> __device__ __forceinline__ void store_row32<float>(float* p, int vali
     }
 }
 
-// Epilogue for one 32-column chunk of one row.  acc holds raw accumulator bits (s32 or f32).
-template<int KIND, typename T>
-__device__ __forceinline__ void epilogue_chunk(const EpilogueParams& e, const uint32_t* acc, int row, int col0, int valid,
-                                               float row_scale, float fp8_scale, bool vec_ok)
+// 64 bytes of a residual row (32 values of a 16-bit type), or a predicated tail.
+template<typename T> __device__ __forceinline__ void load_res32(const T* p, int valid, bool vec_ok, float* out)
 {
-    float v[32];
-    T*    crow = reinterpret_cast<T*>(e.C) + (size_t)row * e.ldc + col0;
-    if (KIND == KIND_I8) {
-        float cs[32];
-        if (valid >= 32) {
+    if (sizeof(T) == 2 && vec_ok && valid >= 32) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 f = __ldg(reinterpret_cast<const float4*>(e.col_scale + col0) + i);
-                cs[4 * i] = f.x; cs[4 * i + 1] = f.y; cs[4 * i + 2] = f.z; cs[4 * i + 3] = f.w;
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                cs[i] = (i < valid) ? __ldg(e.col_scale + col0 + i) : 0.0f;
-            }
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            v[i] = round_t<T>((float)(int)acc[i] * (cs[i] * row_scale));
-        }
-        if (e.bias != nullptr) {
-            float b[32];
-            load_row32<T>(reinterpret_cast<const T*>(e.bias) + col0, valid, vec_ok, b);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                v[i] = v[i] + b[i];  // rounded to T by the store: T(T(acc*scale) + bias)
-            }
+        for (int i = 0; i < 4; ++i) {
+            unpack8<T>(ld_nc_16(p + 8 * i), out + 8 * i);
         }
     } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            v[i] = __uint_as_float(acc[i]) * fp8_scale;
-        }
-        if (e.residual != nullptr) {
-            float r[32];
-            load_row32<T>(reinterpret_cast<const T*>(e.residual) + (size_t)row * e.ldc + col0, valid, vec_ok, r);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                v[i] = fmaf(e.beta, r[i], v[i]);
-            }
-        }
-        if (e.bias != nullptr) {
-            float b[32];
-            load_row32<T>(reinterpret_cast<const T*>(e.bias) + col0, valid, vec_ok, b);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                v[i] += b[i];
-            }
-        }
-        if (e.gelu) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                v[i] = gelu_tanh_f32(v[i]);
-            }
+            out[i] = (i < valid) ? to_f32(p[i]) : 0.0f;
         }
     }
-    store_row32<T>(crow, valid, vec_ok, v);
+}
+template<> __device__ __forceinline__ void load_res32<float>(const float* p, int valid, bool vec_ok, float* out)
+{
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        out[i] = (i < valid) ? p[i] : 0.0f;
+    }
+}
+
+// The arithmetic of one 32-column chunk of one row: raw accumulator bits -> fp32 results (not yet rounded to T,
+// except where the reference's sequence rounds in between).  colp holds (column scale, bias) pairs of the chunk.
+template<int KIND, typename T>
+__device__ __forceinline__ void epilogue_math(const EpilogueParams& e, const uint32_t* acc, const float2* colp, float row_scale,
+                                              float fp8_scale, bool has_res, const float* res, float* v)
+{
+    if (KIND == KIND_I8) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const float2 cp = colp[i];  // same address in every lane: a shared-memory broadcast
+            // T(T(acc * (s_w * s_a)) + bias): the first rounding here, the second when the value is stored as T
+            v[i] = round_t<T>((float)(int)acc[i] * (cp.x * row_scale)) + cp.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            float t = __uint_as_float(acc[i]) * fp8_scale;
+            if (has_res) {
+                t = fmaf(e.beta, res[i], t);
+            }
+            t += colp[i].y;
+            v[i] = e.gelu ? gelu_tanh_f32(t) : t;
+        }
+    }
 }
 
 template<int KIND, int BLOCK_N, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const GemmParams p)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_c, const GemmParams p)
 {
     using S = GemmSmem<BLOCK_N, CTAS>;
     constexpr int      kStages   = S::kStages;
     constexpr int      kTileM    = kBlockM * CTAS;
+    constexpr int      kHalfN    = BLOCK_N / 2;            // columns per epilogue warp
+    constexpr int      kChunks   = kHalfN / 32;            // 4 or 2, always even
     constexpr uint32_t kTmemCols = 2 * BLOCK_N;  // two accumulator buffers (power of two: 256 or 512)
     constexpr uint32_t kIdesc    = (KIND == KIND_I8) ? umma_idesc(2u, 1u, kTileM, BLOCK_N) : umma_idesc(1u, 0u, kTileM, BLOCK_N);
 
@@ -209,16 +193,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     // 1024-byte alignment is what the 128-byte swizzle pattern of TMA and UMMA is anchored to.  The dynamic shared
     // window starts at the same offset in every CTA of the kernel, so both CTAs of a pair get the same layout.
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t*       gen_base  = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t smem_a    = smem_base;
     const uint32_t smem_b    = smem_base + kStages * S::kABytes;
-    const uint32_t bars      = smem_base + kStages * S::kStageBytes;
+    const uint32_t bars      = smem_base + S::kBarOffset;
     // barrier slots (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
     auto full_bar       = [&](int s) { return bars + 8u * s; };
     auto empty_bar      = [&](int s) { return bars + 8u * (kStages + s); };
     auto tmem_full_bar  = [&](int b) { return bars + 8u * (2 * kStages + b); };
     auto tmem_empty_bar = [&](int b) { return bars + 8u * (2 * kStages + 2 + b); };
-    uint8_t*       gen_base   = smem_raw + (smem_base - smem_u32(smem_raw));
-    uint32_t*      tmem_slot  = reinterpret_cast<uint32_t*>(gen_base + kStages * S::kStageBytes + 8 * (2 * kStages + 4));
+    uint32_t*      tmem_slot  = reinterpret_cast<uint32_t*>(gen_base + S::kBarOffset + 8 * (2 * kStages + 4));
     volatile int*  abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int      warp    = threadIdx.x >> 5;
@@ -235,12 +219,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tmem_full_bar(b), 1);
-            mbar_init(tmem_empty_bar(b), 4 * CTAS);  // one arrival per epilogue warp of every CTA of the unit
+            mbar_init(tmem_empty_bar(b), kEpiWarps * CTAS);  // one arrival per epilogue warp of every CTA of the unit
         }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmap_a);
         prefetch_tensormap(&tmap_b);
+        prefetch_tensormap(&tmap_c);
     }
     if (warp == 2) {
         if (CTAS == 2) {
@@ -391,10 +376,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
         }
     } else if (warp >= kEpiWarp0) {
-        // ------------------------------------------------------------------ epilogue
-        const int      quad      = warp - kEpiWarp0;  // == warp % 4: the TMEM lane quadrant this warp may read
+        // ------------------------------------------------------------------ epilogue (warps 4..11)
+        const int      quad      = warp & 3;                 // the TMEM lane quadrant this warp may read
+        const int      half      = (warp - kEpiWarp0) >> 2;  // which half of the tile's columns
+        const int      et        = threadIdx.x - kEpiWarp0 * 32;  // 0..255
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         const EpilogueParams& e  = p.epi;
+        float2*        colp      = reinterpret_cast<float2*>(gen_base + S::kEpiOffset + kEpiWarps * kStoreBox);  // [2][256]
+        uint8_t*       box       = gen_base + S::kEpiOffset + (warp - kEpiWarp0) * kStoreBox;
+        const uint32_t box_addr  = smem_base + S::kEpiOffset + (warp - kEpiWarp0) * kStoreBox;
         float fp8_scale = 0.0f;
         if (KIND == KIND_F8) {
             fp8_scale = e.alpha * __ldg(e.s_a) * __ldg(e.s_b);
@@ -406,6 +396,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             const int      m_blk     = tile % p.m_tiles;
             const int      n_blk     = tile / p.m_tiles;
+            // column parameters of the tile, staged while the main loop of this tile may still be running
+            float2* cp_tile = colp + (local & 1) * 256;
+            if (et < BLOCK_N) {
+                const int col = n_blk * BLOCK_N + et;
+                float2    v   = make_float2(0.0f, 0.0f);
+                if (col < p.N) {
+                    if (KIND == KIND_I8 && e.col_scale != nullptr) {
+                        v.x = __ldg(e.col_scale + col);
+                    }
+                    if (e.bias != nullptr) {
+                        v.y = (e.c_dtype == LYRAQ_BF16)  ? to_f32(reinterpret_cast<const __nv_bfloat16*>(e.bias)[col])
+                              : (e.c_dtype == LYRAQ_F16) ? to_f32(reinterpret_cast<const __half*>(e.bias)[col])
+                                                         : reinterpret_cast<const float*>(e.bias)[col];
+                    }
+                }
+                cp_tile[et] = v;
+            }
+            // the eight epilogue warps meet: named barrier 1, 256 threads
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             // the verdict is made warp-uniform: the tensor-memory loads below need the whole warp
             if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag))) {
                 if (lane == 0) {
@@ -415,43 +424,94 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 break;
             }
             tc_fence_after_sync();
-            const int row = m_blk * kTileM + (int)rank * kBlockM + quad * 32 + lane;
+            const int row0 = m_blk * kTileM + (int)rank * kBlockM + quad * 32;  // first row of this warp
+            const int row  = row0 + lane;
             float     row_scale = 1.0f;
             if (KIND == KIND_I8 && e.c_dtype != LYRAQ_S32) {
                 row_scale = e.row_scale_per_token ? ((row < p.M) ? __ldg(e.row_scale + row) : 0.0f) : __ldg(e.row_scale);
             }
-#pragma unroll 1
-            for (int c = 0; c < BLOCK_N / 32; ++c) {
-                uint32_t acc[32];
-                tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(buf * BLOCK_N + c * 32), acc);
+            const uint32_t t_addr = tmem_base + lane_addr + (uint32_t)(buf * BLOCK_N + half * kHalfN);
+
+            uint32_t acc[2][32];
+            tmem_ld_32x32(t_addr, acc[0]);
+#pragma unroll
+            for (int c = 0; c < kChunks; ++c) {
                 tmem_ld_wait();
-                const int col0  = n_blk * BLOCK_N + c * 32;
-                const int valid = p.N - col0;
-                if (row < p.M && valid > 0) {
-                    if (e.c_dtype == LYRAQ_BF16) {
-                        epilogue_chunk<KIND, __nv_bfloat16>(e, acc, row, col0, valid, row_scale, fp8_scale, vec_ok);
-                    } else if (e.c_dtype == LYRAQ_F16) {
-                        epilogue_chunk<KIND, __half>(e, acc, row, col0, valid, row_scale, fp8_scale, vec_ok);
-                    } else if (e.c_dtype == LYRAQ_F32) {
-                        epilogue_chunk<KIND, float>(e, acc, row, col0, valid, row_scale, fp8_scale, vec_ok);
-                    } else {
-                        // raw s32 accumulators
+                if (c + 1 < kChunks) {
+                    tmem_ld_32x32(t_addr + (uint32_t)((c + 1) * 32), acc[(c + 1) & 1]);
+                }
+                const uint32_t* a     = acc[c & 1];
+                const int       ccol  = half * kHalfN + c * 32;        // column of the chunk inside the tile
+                const int       col0  = n_blk * BLOCK_N + ccol;
+                const int       valid = p.N - col0;
+                if (e.c_dtype == LYRAQ_S32) {
+                    if (row < p.M && valid > 0) {
                         int32_t* crow = reinterpret_cast<int32_t*>(e.C) + (size_t)row * e.ldc + col0;
                         if (vec_ok && valid >= 32) {
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
                                 Vec16 w;
-                                w.w[0] = acc[4 * i]; w.w[1] = acc[4 * i + 1]; w.w[2] = acc[4 * i + 2]; w.w[3] = acc[4 * i + 3];
+                                w.w[0] = a[4 * i]; w.w[1] = a[4 * i + 1]; w.w[2] = a[4 * i + 2]; w.w[3] = a[4 * i + 3];
                                 st_16(crow + 4 * i, w);
                             }
                         } else {
 #pragma unroll
                             for (int i = 0; i < 32; ++i) {
                                 if (i < valid) {
-                                    crow[i] = (int32_t)acc[i];
+                                    crow[i] = (int32_t)a[i];
                                 }
                             }
                         }
+                    }
+                    continue;
+                }
+                float v[32];
+                float res[32];
+                const bool has_res = (KIND == KIND_F8) && e.residual != nullptr;
+                const bool in_range = row < p.M && valid > 0;
+                if (e.c_dtype == LYRAQ_BF16) {
+                    if (has_res && in_range) {
+                        load_res32<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(e.residual) + (size_t)row * e.ldc + col0, valid, vec_ok, res);
+                    }
+                    epilogue_math<KIND, __nv_bfloat16>(e, a, cp_tile + ccol, row_scale, fp8_scale, has_res && in_range, res, v);
+                } else if (e.c_dtype == LYRAQ_F16) {
+                    if (has_res && in_range) {
+                        load_res32<__half>(reinterpret_cast<const __half*>(e.residual) + (size_t)row * e.ldc + col0, valid, vec_ok, res);
+                    }
+                    epilogue_math<KIND, __half>(e, a, cp_tile + ccol, row_scale, fp8_scale, has_res && in_range, res, v);
+                } else {
+                    if (has_res && in_range) {
+                        load_res32<float>(reinterpret_cast<const float*>(e.residual) + (size_t)row * e.ldc + col0, valid, vec_ok, res);
+                    }
+                    epilogue_math<KIND, float>(e, a, cp_tile + ccol, row_scale, fp8_scale, has_res && in_range, res, v);
+                }
+                if (e.tma_store) {
+                    // 32 rows x 64 bytes through this warp's box, 16-byte pieces XOR-swizzled by (row >> 1) & 3 as the
+                    // 64-byte TMA swizzle expects (conflict-free for the 16-byte shared stores of a quarter warp)
+                    if (lane == 0) {
+                        tma_store_wait_read();  // the previous chunk's store has drained the box
+                    }
+                    __syncwarp();
+                    uint8_t* brow = box + lane * 64;
+                    const int sw  = (lane >> 1) & 3;
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        Vec16 w = (e.c_dtype == LYRAQ_BF16) ? pack8<__nv_bfloat16>(v + 8 * q) : pack8<__half>(v + 8 * q);
+                        *reinterpret_cast<Vec16*>(brow + ((q ^ sw) << 4)) = w;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row0 < p.M && valid > 0) {
+                        tma_store_2d(&tmap_c, box_addr, col0, row0);
+                        tma_store_commit();
+                    }
+                } else if (in_range) {
+                    if (e.c_dtype == LYRAQ_BF16) {
+                        store_row32<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(e.C) + (size_t)row * e.ldc + col0, valid, vec_ok, v);
+                    } else if (e.c_dtype == LYRAQ_F16) {
+                        store_row32<__half>(reinterpret_cast<__half*>(e.C) + (size_t)row * e.ldc + col0, valid, vec_ok, v);
+                    } else {
+                        store_row32<float>(reinterpret_cast<float*>(e.C) + (size_t)row * e.ldc + col0, valid, vec_ok, v);
                     }
                 }
             }
@@ -465,6 +525,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     mbar_arrive(tmem_empty_bar(buf));
                 }
             }
+        }
+        if (lane == 0) {
+            tma_store_wait_read();  // shared memory must outlive the last store's read of it
         }
     }
 
@@ -522,7 +585,33 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
     const CUresult   r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
                             CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? LYRAQ_OK : LYRAQ_ERR_CUDA;
+    if (r != CUDA_SUCCESS) {
+        record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled refused the tensor map");
+        return LYRAQ_ERR_CUDA;
+    }
+    return LYRAQ_OK;
+}
+
+// Tensor map of a row-major [rows, cols] matrix of 16-bit elements for TMA stores of 32 x 32 boxes whose shared-memory
+// image uses the 64-byte swizzle.
+int make_tmap_store_16bit(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols)
+{
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) {
+        return LYRAQ_ERR_CUDA;
+    }
+    const cuuint64_t dims[2]    = {cols, rows};
+    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint32_t box[2]     = {32, 32};
+    const cuuint32_t estr[2]    = {1, 1};
+    const CUresult   r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled refused the output tensor map");
+        return LYRAQ_ERR_CUDA;
+    }
+    return LYRAQ_OK;
 }
 
 int device_sm_count()
@@ -583,14 +672,27 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
     if (st != LYRAQ_OK) {
         return st;
     }
+    // output map for TMA stores: 16-bit elements, boxes of 32 rows x 32 columns (64 bytes), 64-byte swizzle.
+    // When the output does not qualify (fp32 / int32, or a row pitch that is not a multiple of 16 bytes) the kernel
+    // stores directly and this map is a never-used copy of A's.
+    CUtensorMap tc = ta;
+    p.epi.tma_store = 0;
+    if ((p.epi.c_dtype == LYRAQ_BF16 || p.epi.c_dtype == LYRAQ_F16) && (p.N & 7) == 0) {
+        st = make_tmap_store_16bit(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N);
+        if (st != LYRAQ_OK) {
+            return st;
+        }
+        p.epi.tma_store = 1;
+    }
     p.m_tiles = (p.M + kBlockM * CTAS - 1) / (kBlockM * CTAS);
     p.n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
     const long tiles = (long)p.m_tiles * p.n_tiles;
     const long units = sms / CTAS;
     const int  grid  = (int)(tiles < units ? tiles : units) * CTAS;
     auto       kern  = gemm_tcgen05_kernel<KIND, BLOCK_N, CTAS>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal) != cudaSuccess) {
-        return LYRAQ_ERR_CUDA;
+    const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (attr_err != cudaSuccess) {
+        return cuda_status(attr_err, "cudaFuncSetAttribute(gemm_tcgen05_kernel, dynamic shared memory)");
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim          = dim3((unsigned)grid, 1, 1);
@@ -604,7 +706,7 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
     attr[0].val.clusterDim.z = 1;
     cfg.attrs    = attr;
     cfg.numAttrs = (CTAS > 1) ? 1 : 0;
-    return cuda_status(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
+    return cuda_status(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p), "cudaLaunchKernelEx(gemm_tcgen05_kernel)");
 }
 
 // forced tile configuration for tests and sweeps: 0 = automatic, else block_n * 10 + ctas (2561, 1281, 2562)

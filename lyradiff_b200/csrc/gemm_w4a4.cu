@@ -16,12 +16,13 @@
 // cycled, the MMA warp runs up to four groups ahead, and eight drain warps convert / scale /
 // accumulate in registers.  That CUDA-core work, not the tensor pipe, bounds this kernel.
 //
-// 416 threads per CTA, one persistent CTA per SM:
+// 512 threads per CTA (sixteen warps, four per scheduler, hence at most 128 registers per thread), one persistent
+// CTA per SM:
 //   warp 0       TMA producer: packed A (128 x 64 B) and packed B (128 x 64 B) tiles, ring of 4 stages
 //   warp 1       MMA issuer
 //   warp 2       scale loader: every four K blocks (8 groups) it transposes sa[m, g] and sb[n, g] of the tile into
 //                shared memory as [g][row] (ring of 3 slots), running ahead of the drain; also owns tensor memory
-//   warps 3, 12  expand nibbles -> swizzled int8 operand tiles (ring of 4 stages)
+//   warps 3, 12-14  expand nibbles -> swizzled int8 operand tiles (ring of 4 stages); warp 15 idles
 //   warps 4-11   drain: warp w reads TMEM lanes 32*(w%4).., columns 64*((w-4)/4)..; final epilogue
 // All waits are bounded (see sm100_ptx.cuh); a timeout sets the status word and every role exits.
 #include "common.cuh"
@@ -42,7 +43,8 @@ constexpr int kBM          = 128;
 constexpr int kBN          = 128;
 constexpr int kKBlock      = 128;            // K elements per block = 2 groups
 constexpr int kPackedRowB  = kKBlock / 2;    // 64 bytes
-constexpr int kThreads     = 416;
+constexpr int kThreads     = 512;
+constexpr int kExpandWarps = 4;
 constexpr int kPStages     = 4;
 constexpr int kUStages     = 4;
 constexpr int kPBufs       = 4;              // partial accumulator buffers in tensor memory
@@ -144,8 +146,7 @@ __device__ __forceinline__ void final_store32(const Params& p, const float* acc,
     }
 }
 
-// 13 warps x 32 lanes x 144 registers = 59904 of the 65536 registers of an SM (allocation is per warp, in units of 512)
-__global__ void __maxnreg__(144)
+__global__ void __launch_bounds__(kThreads, 1)
 gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p)
 {
     constexpr uint32_t kTmemCols = kPBufs * kBN;  // 512
@@ -176,10 +177,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPStages; ++s) {
             mbar_init(full_p(s), 1);
-            mbar_init(empty_p(s), 2);   // the two expanding warps
+            mbar_init(empty_p(s), kExpandWarps);
         }
         for (int s = 0; s < kUStages; ++s) {
-            mbar_init(full_u(s), 2);    // the two expanding warps
+            mbar_init(full_u(s), kExpandWarps);
             mbar_init(empty_u(s), 1);   // MMA commit
         }
         for (int b = 0; b < kPBufs; ++b) {
@@ -387,14 +388,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
-    } else if (warp == 3 || warp == 12) {
+    } else if (warp == 3 || (warp >= 12 && warp <= 14)) {
         // ------------------------------------------------------------------ nibble expansion
-        // 2 tiles x 128 rows x 4 packed 16-byte chunks = 1024 tasks over 64 threads; thread tu owns chunk (tu & 3) of
-        // rows (tu >> 2) + 16 * it, it = 0..15 (it < 8: A, it >= 8: B), so every address is a base plus it * constant.
-        const int tu     = (warp == 3 ? 0 : 32) + lane;
+        // 2 tiles x 128 rows x 4 packed 16-byte chunks = 1024 tasks over 128 threads; thread tu owns chunk (tu & 3) of
+        // rows (tu >> 2) + 32 * it, it = 0..7 (it < 4: A, it >= 4: B), so every address is a base plus it * constant.
+        const int tu     = (warp == 3 ? 0 : (warp - 11) * 32) + lane;  // 0..127
         const int c      = tu & 3;
-        const int r0     = tu >> 2;       // 0..15
-        const int sw     = r0 & 7;        // (r0 + 16 * it) & 7 == r0 & 7
+        const int r0     = tu >> 2;       // 0..31
+        const int sw     = r0 & 7;        // (r0 + 32 * it) & 7 == r0 & 7
         const int src_o  = r0 * kPackedRowB + c * 16;
         const int dst_ev = (r0 >> 3) * 1024 + (r0 & 7) * 128 + (((2 * c) ^ sw) << 4);
         const int dst_od = (r0 >> 3) * 1024 + (r0 & 7) * 128 + (((2 * c + 1) ^ sw) << 4);
@@ -416,17 +417,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const uint8_t* src = gen_base + (packed0 - smem_base) + pstage * kPackedStage + src_o;
                 uint8_t*       dst = gen_base + (ustage0 - smem_base) + ustage * kUStage;
 #pragma unroll
-                for (int it = 0; it < 16; ++it) {
-                    // 16 rows further per step: 16 * 64 B in the packed tile, 2 * 1024 B in the operand tile;
-                    // it >= 8 switches to the B tile (its packed and operand tiles follow A's contiguously)
-                    const uint4 w4 = *reinterpret_cast<const uint4*>(src + it * 16 * kPackedRowB);
+                for (int it = 0; it < 8; ++it) {
+                    // 32 rows further per step: 32 * 64 B in the packed tile, 4 * 1024 B in the operand tile;
+                    // it >= 4 switches to the B tile (its packed and operand tiles follow A's contiguously)
+                    const uint4 w4 = *reinterpret_cast<const uint4*>(src + it * 32 * kPackedRowB);
                     uint4       ev, od;
                     ev.x = (w4.x << 4) & 0xF0F0F0F0u; od.x = w4.x & 0xF0F0F0F0u;
                     ev.y = (w4.y << 4) & 0xF0F0F0F0u; od.y = w4.y & 0xF0F0F0F0u;
                     ev.z = (w4.z << 4) & 0xF0F0F0F0u; od.z = w4.z & 0xF0F0F0F0u;
                     ev.w = (w4.w << 4) & 0xF0F0F0F0u; od.w = w4.w & 0xF0F0F0F0u;
-                    *reinterpret_cast<uint4*>(dst + it * 2048 + dst_ev) = ev;
-                    *reinterpret_cast<uint4*>(dst + it * 2048 + dst_od) = od;
+                    *reinterpret_cast<uint4*>(dst + it * 4096 + dst_ev) = ev;
+                    *reinterpret_cast<uint4*>(dst + it * 4096 + dst_od) = od;
                 }
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -444,7 +445,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
-    } else {
+    } else if (warp >= 4 && warp <= 11) {
         // ------------------------------------------------------------------ drain + epilogue (warps 4..11)
         const int      quad      = warp & 3;
         const int      half      = (warp - 4) >> 2;
@@ -491,20 +492,20 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     tc_fence_after_sync();
                     const float sa_v = sas[gs * kBM + trow];
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
-                        uint32_t part[32];
-                        tmem_ld_32x32(tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64 + c * 32), part);
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t part[16];
+                        tmem_ld_32x16(tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64 + c * 16), part);
                         tmem_ld_wait();
-                        const float4* sb4 = reinterpret_cast<const float4*>(sbs + gs * kBN + half * 64 + c * 32);
+                        const float4* sb4 = reinterpret_cast<const float4*>(sbs + gs * kBN + half * 64 + c * 16);
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) {
+                        for (int j = 0; j < 4; ++j) {
                             const float4 s = sb4[j];
                             // acc = fma(float(p) * sa, sb, acc): the contraction the reference's compiler makes of
                             // `acc += float(p) * sa * sb` (w4a4_gemm.cu:504-507)
-                            acc[c * 32 + 4 * j]     = fmaf((float)(int)part[4 * j] * sa_v, s.x, acc[c * 32 + 4 * j]);
-                            acc[c * 32 + 4 * j + 1] = fmaf((float)(int)part[4 * j + 1] * sa_v, s.y, acc[c * 32 + 4 * j + 1]);
-                            acc[c * 32 + 4 * j + 2] = fmaf((float)(int)part[4 * j + 2] * sa_v, s.z, acc[c * 32 + 4 * j + 2]);
-                            acc[c * 32 + 4 * j + 3] = fmaf((float)(int)part[4 * j + 3] * sa_v, s.w, acc[c * 32 + 4 * j + 3]);
+                            acc[c * 16 + 4 * j]     = fmaf((float)(int)part[4 * j] * sa_v, s.x, acc[c * 16 + 4 * j]);
+                            acc[c * 16 + 4 * j + 1] = fmaf((float)(int)part[4 * j + 1] * sa_v, s.y, acc[c * 16 + 4 * j + 1]);
+                            acc[c * 16 + 4 * j + 2] = fmaf((float)(int)part[4 * j + 2] * sa_v, s.z, acc[c * 16 + 4 * j + 2]);
+                            acc[c * 16 + 4 * j + 3] = fmaf((float)(int)part[4 * j + 3] * sa_v, s.w, acc[c * 16 + 4 * j + 3]);
                         }
                     }
                     tc_fence_before_sync();
@@ -621,8 +622,10 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     }
     const long tiles = (long)p.m_tiles * p.n_tiles;
     const int  grid  = (int)(tiles < sms ? tiles : sms);
-    if (cudaFuncSetAttribute(w4::gemm_w4a4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, w4::kSmemTotal) != cudaSuccess) {
-        return LYRAQ_ERR_CUDA;
+    const cudaError_t attr_err =
+        cudaFuncSetAttribute(w4::gemm_w4a4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, w4::kSmemTotal);
+    if (attr_err != cudaSuccess) {
+        return cuda_status(attr_err, "cudaFuncSetAttribute(gemm_w4a4_kernel, dynamic shared memory)");
     }
     w4::gemm_w4a4_kernel<<<grid, w4::kThreads, w4::kSmemTotal, (cudaStream_t)stream>>>(ta, tb, p);
     return launch_status();

@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
         }
         m2               = team_reduce<false>(m2, tpr, red);
         const float var  = fmaxf(m2 / (float)p.dim, 0.0f);
-        const float rstd = (float)(1.0 / sqrt((double)var + (double)p.eps));
+        const float rstd = 1.0f / sqrtf(var + p.eps);  // IEEE sqrt and divide: within one ulp of the exact value
 
         const size_t brow  = (MODE == ROW_ADALN) ? (row / (size_t)p.rows_per_batch) : 0;
         const T*     mul_v = (MODE == ROW_ADALN) ? reinterpret_cast<const T*>(p.ada_scale) + brow * (size_t)p.dim
@@ -213,63 +213,72 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
         }
     }
 
-    // ---- e4m3, static per-tensor scale
+    // ---- int8 scale: q = sat_s8(rne((float(y) * pre[c]) / s)); the e4m3 output uses y before the pre factor
+    float s8 = 1.0f;
+    float f8r = 0.0f;
     if (p.qf8 != nullptr) {
         const float s = __ldg(p.f8_scale);
-        const float r = p.f8_invert ? 1.0f / s : s;
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int vi = tlane + i * tpr;
-            if (live && vi < nvec) {
-                const uint32_t w0 = f32x2_to_e4m3x2(f[i][0] * r, f[i][1] * r) | (f32x2_to_e4m3x2(f[i][2] * r, f[i][3] * r) << 16);
-                const uint32_t w1 = f32x2_to_e4m3x2(f[i][4] * r, f[i][5] * r) | (f32x2_to_e4m3x2(f[i][6] * r, f[i][7] * r) << 16);
-                st_8(p.qf8 + row * (size_t)p.dim + (vi << 3), w0, w1);
-            }
-        }
+        f8r           = p.f8_invert ? 1.0f / s : s;
     }
-
-    // ---- int8: q = sat_s8(rne((float(y) * pre[c]) / s))
+    const bool dynamic = (p.scale_mode == LYRAQ_SCALE_PER_TOKEN_DYNAMIC);
     if (p.q8 != nullptr) {
-        if (p.pre != nullptr) {
+        if (dynamic) {
+            float amax = 0.0f;
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int vi = tlane + i * tpr;
-                if (live && vi < nvec) {
+                if (p.pre != nullptr && live && vi < nvec) {
+                    const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
+                    const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f[i][0] * p0.x), fabsf(f[i][1] * p0.y)),
+                                             fmaxf(fabsf(f[i][2] * p0.z), fabsf(f[i][3] * p0.w))));
+                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f[i][4] * p1.x), fabsf(f[i][5] * p1.y)),
+                                             fmaxf(fabsf(f[i][6] * p1.z), fabsf(f[i][7] * p1.w))));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        amax = fmaxf(amax, fabsf(f[i][j]));
+                    }
+                }
+            }
+            amax = team_reduce<true>(amax, tpr, red);
+            s8   = (amax == 0.0f) ? 1.0f : amax / 127.0f;
+            if (live && tlane == 0) {
+                p.q8_scale[row] = s8;
+            }
+        } else if (p.scale_mode == LYRAQ_SCALE_PER_TOKEN) {
+            s8 = live ? __ldg(p.q8_scale + row) : 1.0f;
+        } else {
+            s8 = __ldg(p.q8_scale);
+        }
+    }
+    const float r8 = 1.0f / s8;
+
+    // ---- quantized outputs, one 16-byte vector of the row at a time
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int vi = tlane + i * tpr;
+        if (live && vi < nvec) {
+            const size_t off = row * (size_t)p.dim + (vi << 3);
+            if (p.qf8 != nullptr) {
+                const uint32_t w0 = f32x2_to_e4m3x2(f[i][0] * f8r, f[i][1] * f8r) | (f32x2_to_e4m3x2(f[i][2] * f8r, f[i][3] * f8r) << 16);
+                const uint32_t w1 = f32x2_to_e4m3x2(f[i][4] * f8r, f[i][5] * f8r) | (f32x2_to_e4m3x2(f[i][6] * f8r, f[i][7] * f8r) << 16);
+                st_8(p.qf8 + off, w0, w1);
+            }
+            if (p.q8 != nullptr) {
+                if (p.pre != nullptr) {
                     const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
                     const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
                     f[i][0] *= p0.x; f[i][1] *= p0.y; f[i][2] *= p0.z; f[i][3] *= p0.w;
                     f[i][4] *= p1.x; f[i][5] *= p1.y; f[i][6] *= p1.z; f[i][7] *= p1.w;
                 }
-            }
-        }
-        float s;
-        if (p.scale_mode == LYRAQ_SCALE_PER_TOKEN_DYNAMIC) {
-            float amax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    amax = fmaxf(amax, fabsf(f[i][j]));
-                }
-            }
-            amax = team_reduce<true>(amax, tpr, red);
-            s    = (amax == 0.0f) ? 1.0f : amax / 127.0f;
-            if (live && tlane == 0) {
-                p.q8_scale[row] = s;
-            }
-        } else if (p.scale_mode == LYRAQ_SCALE_PER_TOKEN) {
-            s = live ? __ldg(p.q8_scale + row) : 1.0f;
-        } else {
-            s = __ldg(p.q8_scale);
-        }
-        const float r = 1.0f / s;
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int vi = tlane + i * tpr;
-            if (live && vi < nvec) {
                 uint32_t w0, w1;
-                quant8_s8(f[i], s, r, w0, w1);
-                st_8(p.q8 + row * (size_t)p.dim + (vi << 3), w0, w1);
+                if (dynamic) {
+                    quant8_s8_inrange(f[i], s8, r8, w0, w1);
+                } else {
+                    quant8_s8(f[i], s8, r8, w0, w1);
+                }
+                st_8(p.q8 + off, w0, w1);
             }
         }
     }
