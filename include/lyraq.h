@@ -74,6 +74,12 @@ LYRAQ_API const char* lyraq_last_cuda_error(void);
  * through CutlassGemmConfig (src/lyradiff/kernels/cutlass_extensions/include/cutlass_extensions/gemm_configs.h:101-130). */
 LYRAQ_API int lyraq_debug_force_gemm_tile(int code);
 
+/* Test / sweep hook for the row kernels (quantize, LayerNorm, AdaLN, GEGLU): the most 16-byte vectors one thread
+ * holds (4 or 6, default 6) before a row is given to a team twice as large.  Process-wide, not thread-safe.
+ * No counterpart in the reference, whose kernels fix columns-per-thread per supported width
+ * (src/lyradiff/kernels/quant_kernels/layer_norm_int8.cu:558-617). */
+LYRAQ_API int lyraq_debug_set_row_vectors_per_thread(int max_vpt);
+
 /* ------------------------------------------------------------------ activation quantizers */
 
 /* INT8 SmoothQuant activation quantize: q = sat_s8(rne(float(x)*pre[c] / s)).

@@ -83,6 +83,26 @@ __device__ __forceinline__ float gelu_tanh_f32(float v)
 }
 
 // ---------------------------------------------------------------------------------------------
+// Packed fp32 pairs (sm_100: one instruction, two IEEE-rounded results; lane-wise identical to the scalar op).
+__device__ __forceinline__ float2 mul_f32x2(float2 a, float2 b)
+{
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)));
+    return d;
+}
+__device__ __forceinline__ float2 fma_f32x2(float2 a, float2 b, float2 c)
+{
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)),
+          "l"(reinterpret_cast<const unsigned long long&>(c)));
+    return d;
+}
+
+// ---------------------------------------------------------------------------------------------
 // 16-byte vectors of 8 sixteen-bit values or 4 floats.
 struct alignas(16) Vec16 {
     uint32_t w[4];
@@ -92,6 +112,16 @@ __device__ __forceinline__ Vec16 ld_nc_16(const void* p)
 {
     Vec16 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+                 : "l"(p));
+    return v;
+}
+
+// Same, for vectors that every row re-reads (modulation scale / shift, gamma / beta, bias): kept in L1.
+__device__ __forceinline__ Vec16 ld_nc_16_keep(const void* p)
+{
+    Vec16 v;
+    asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
                  : "l"(p));
     return v;
@@ -213,14 +243,14 @@ __device__ __forceinline__ void quant8_s8_inrange(const float* v, float s, float
 {
     const float magic = 12582912.0f;
     uint32_t    b[8];
-    float       dmax = 0.0f;
+    float       d[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const float t = fmaf(v[j], r, magic);
-        const float d = fmaf(v[j], r, magic - t);
-        dmax          = fmaxf(dmax, fabsf(d));
+        d[j]          = fabsf(fmaf(v[j], r, magic - t));
         b[j]          = __float_as_uint(t);
     }
+    const float dmax = fmaxf(fmaxf(fmaxf(d[0], d[1]), fmaxf(d[2], d[3])), fmaxf(fmaxf(d[4], d[5]), fmaxf(d[6], d[7])));
     if (dmax > 0.5f - 6.1e-5f) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {

@@ -40,6 +40,22 @@ constexpr int kBarBytes    = 256;
 
 enum GemmKind { KIND_I8 = 0, KIND_F8 = 1 };
 
+// Optional instrumentation (compile with -DLYRAQ_PROFILE_WAITS): per CTA, the cycles each role spends waiting on
+// its barriers and in total.  Slots: 0 producer wait-empty, 1 producer total, 2 MMA wait-full, 3 MMA wait-tmem,
+// 4 MMA total, 5 epilogue (warp 4) wait-full-accumulator, 6 epilogue total, 7 MMA total in nanoseconds.
+#ifdef LYRAQ_PROFILE_WAITS
+__device__ unsigned long long g_wait_prof[296 * 8];
+#define PROF_DECL(name) long long name = 0
+#define PROF_T0(t) const long long t = clock64()
+#define PROF_ADD(acc, t) acc += clock64() - (t)
+#define PROF_STORE(slot, v) g_wait_prof[blockIdx.x * 8 + (slot)] = (unsigned long long)(v)
+#else
+#define PROF_DECL(name)
+#define PROF_T0(t)
+#define PROF_ADD(acc, t)
+#define PROF_STORE(slot, v)
+#endif
+
 struct EpilogueParams {
     void*        C;
     int          c_dtype;
@@ -161,7 +177,8 @@ __device__ __forceinline__ void epilogue_math(const EpilogueParams& e, const uin
         for (int i = 0; i < 32; ++i) {
             const float2 cp = colp[i];  // same address in every lane: a shared-memory broadcast
             // T(T(acc * (s_w * s_a)) + bias): the first rounding here, the second when the value is stored as T
-            v[i] = round_t<T>((float)(int)acc[i] * (cp.x * row_scale)) + cp.y;
+            // (explicitly rounded multiply: for T = float nothing sits between it and the add, and it must not fuse)
+            v[i] = round_t<T>(__fmul_rn((float)(int)acc[i], cp.x * row_scale)) + cp.y;
         }
     } else {
 #pragma unroll
@@ -254,18 +271,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint32_t phase = 0;
         int      issued = 0;
         bool     ok = true;
+        PROF_DECL(w_empty);
+        PROF_T0(t_all);
         for (int tile = unit; ok && tile < num_tiles; tile += n_units) {
             const int m_blk = tile % p.m_tiles;
             const int n_blk = tile / p.m_tiles;
             const int a_row = m_blk * kTileM + (int)rank * kBlockM;
             const int b_row = n_blk * BLOCK_N + (int)rank * (BLOCK_N / CTAS);
             for (int kb = 0; kb < num_kb; ++kb) {
+                PROF_T0(t_w);
                 if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                     report_timeout(p.status, 0x100u | (unsigned)stage);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
+                PROF_ADD(w_empty, t_w);
                 if (CTAS == 2) {
                     // both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair
                     const uint32_t lbar = map_to_cta(full_bar(stage), 0u);
@@ -286,6 +307,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
         }
+#ifdef LYRAQ_PROFILE_WAITS
+        PROF_STORE(0, w_empty);
+        PROF_STORE(1, clock64() - t_all);
+#endif
         if (CTAS == 1 || leader) {
             // Drain: every load counted on this CTA's barriers must have landed before the block may exit.
             // (stage, phase) now name the next slot to fill; walk back over the last min(issued, kStages) slots.
@@ -314,23 +339,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool     ok = true;
         // cluster addresses of the peer's barriers (same offsets): its producer and epilogue wait on those
         const uint32_t peer = (CTAS == 2) ? 1u : 0u;
+        PROF_DECL(w_full);
+        PROF_DECL(w_tmem);
+        PROF_T0(t_all);
+#ifdef LYRAQ_PROFILE_WAITS
+        const uint64_t ns0 = global_timer_ns();
+#endif
         for (int tile = unit; ok && tile < num_tiles; tile += n_units, ++local) {
             const int      buf       = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
+            PROF_T0(t_w0);
             if (!mbar_wait(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag)) {
                 report_timeout(p.status, 0x200u | (unsigned)buf);
                 *abort_flag = 1;
                 break;
             }
+            PROF_ADD(w_tmem, t_w0);
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BLOCK_N);
             for (int kb = 0; kb < num_kb; ++kb) {
+                PROF_T0(t_w1);
                 if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                     report_timeout(p.status, 0x300u | (unsigned)stage);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
+                PROF_ADD(w_full, t_w1);
                 tc_fence_after_sync();
                 const uint64_t adesc = umma_desc_k_sw128(smem_a + stage * S::kABytes);
                 const uint64_t bdesc = umma_desc_k_sw128(smem_b + stage * S::kBBytes);
@@ -375,6 +410,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
         }
+#ifdef LYRAQ_PROFILE_WAITS
+        PROF_STORE(2, w_full);
+        PROF_STORE(3, w_tmem);
+        PROF_STORE(4, clock64() - t_all);
+        PROF_STORE(7, global_timer_ns() - ns0);  // wall time of the same span: cycles / ns = the SM clock under load
+#endif
     } else if (warp >= kEpiWarp0) {
         // ------------------------------------------------------------------ epilogue (warps 4..11)
         const int      quad      = warp & 3;                 // the TMEM lane quadrant this warp may read
@@ -391,6 +432,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         const bool vec_ok = (e.c_dtype == LYRAQ_F32 || e.c_dtype == LYRAQ_S32) ? ((e.ldc & 3) == 0) : ((e.ldc & 7) == 0);
         int local = 0;
+        PROF_DECL(w_acc);
+        PROF_T0(t_all);
         for (int tile = unit; tile < num_tiles; tile += n_units, ++local) {
             const int      buf       = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
@@ -416,6 +459,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             // the eight epilogue warps meet: named barrier 1, 256 threads
             asm volatile("bar.sync 1, 256;" ::: "memory");
             // the verdict is made warp-uniform: the tensor-memory loads below need the whole warp
+            PROF_T0(t_w2);
             if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag))) {
                 if (lane == 0) {
                     report_timeout(p.status, 0x400u | (unsigned)buf);
@@ -423,6 +467,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 *abort_flag = 1;
                 break;
             }
+            PROF_ADD(w_acc, t_w2);
             tc_fence_after_sync();
             const int row0 = m_blk * kTileM + (int)rank * kBlockM + quad * 32;  // first row of this warp
             const int row  = row0 + lane;
@@ -529,6 +574,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0) {
             tma_store_wait_read();  // shared memory must outlive the last store's read of it
         }
+#ifdef LYRAQ_PROFILE_WAITS
+        if (threadIdx.x == kEpiWarp0 * 32) {
+            PROF_STORE(5, w_acc);
+            PROF_STORE(6, clock64() - t_all);
+        }
+#endif
     }
 
     // ---------------------------------------------------------------------- common exit
@@ -757,6 +808,13 @@ template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams 
 using namespace lyraq;
 
 extern "C" {
+
+#ifdef LYRAQ_PROFILE_WAITS
+__attribute__((visibility("default"))) int lyraq_debug_read_wait_profile(unsigned long long* host, int n_words)
+{
+    return cuda_status(cudaMemcpyFromSymbol(host, g_wait_prof, sizeof(unsigned long long) * (size_t)n_words), "read wait profile");
+}
+#endif
 
 int lyraq_debug_force_gemm_tile(int code)
 {

@@ -459,10 +459,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
             const int m_blk = tile % p.m_tiles;
             const int n_blk = tile / p.m_tiles;
-            float     acc[64];
+            float2    acc[32];  // 64 columns of this thread's row, as packed pairs
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                acc[i] = 0.0f;
+            for (int i = 0; i < 32; ++i) {
+                acc[i] = make_float2(0.0f, 0.0f);
             }
             for (int kb = 0; ok && kb < num_kb; ++kb) {
                 if ((kb & 3) == 0) {
@@ -490,7 +490,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         break;
                     }
                     tc_fence_after_sync();
-                    const float sa_v = sas[gs * kBM + trow];
+                    const float  sa_s = sas[gs * kBM + trow];
+                    const float2 sa_v = make_float2(sa_s, sa_s);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t part[16];
@@ -501,11 +502,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         for (int j = 0; j < 4; ++j) {
                             const float4 s = sb4[j];
                             // acc = fma(float(p) * sa, sb, acc): the contraction the reference's compiler makes of
-                            // `acc += float(p) * sa * sb` (w4a4_gemm.cu:504-507)
-                            acc[c * 16 + 4 * j]     = fmaf((float)(int)part[4 * j] * sa_v, s.x, acc[c * 16 + 4 * j]);
-                            acc[c * 16 + 4 * j + 1] = fmaf((float)(int)part[4 * j + 1] * sa_v, s.y, acc[c * 16 + 4 * j + 1]);
-                            acc[c * 16 + 4 * j + 2] = fmaf((float)(int)part[4 * j + 2] * sa_v, s.z, acc[c * 16 + 4 * j + 2]);
-                            acc[c * 16 + 4 * j + 3] = fmaf((float)(int)part[4 * j + 3] * sa_v, s.w, acc[c * 16 + 4 * j + 3]);
+                            // `acc += float(p) * sa * sb` (w4a4_gemm.cu:504-507); two columns per instruction
+                            const float2 p0 = make_float2((float)(int)part[4 * j], (float)(int)part[4 * j + 1]);
+                            const float2 p1 = make_float2((float)(int)part[4 * j + 2], (float)(int)part[4 * j + 3]);
+                            acc[c * 8 + 2 * j]     = fma_f32x2(mul_f32x2(p0, sa_v), make_float2(s.x, s.y), acc[c * 8 + 2 * j]);
+                            acc[c * 8 + 2 * j + 1] = fma_f32x2(mul_f32x2(p1, sa_v), make_float2(s.z, s.w), acc[c * 8 + 2 * j + 1]);
                         }
                     }
                     tc_fence_before_sync();
@@ -536,11 +537,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const int valid = p.N - col0;
                     if (valid > 0) {
                         if (p.c_dtype == LYRAQ_BF16) {
-                            final_store32<__nv_bfloat16>(p, acc + c * 32, row, col0, valid, vec_ok);
+                            final_store32<__nv_bfloat16>(p, reinterpret_cast<const float*>(acc) + c * 32, row, col0, valid, vec_ok);
                         } else if (p.c_dtype == LYRAQ_F16) {
-                            final_store32<__half>(p, acc + c * 32, row, col0, valid, vec_ok);
+                            final_store32<__half>(p, reinterpret_cast<const float*>(acc) + c * 32, row, col0, valid, vec_ok);
                         } else {
-                            final_store32<float>(p, acc + c * 32, row, col0, valid, vec_ok);
+                            final_store32<float>(p, reinterpret_cast<const float*>(acc) + c * 32, row, col0, valid, vec_ok);
                         }
                     }
                 }

@@ -8,6 +8,8 @@
 
 namespace lyraq {
 
+int device_sm_count();  // gemm_dense.cu
+
 enum RowMode { ROW_PLAIN = 0, ROW_ADALN = 1, ROW_LN = 2, ROW_GEGLU = 3 };
 
 struct RowParams {
@@ -74,38 +76,76 @@ template<bool IS_MAX> __device__ __forceinline__ float team_reduce(float v, int 
 // The row lives in registers as fp32 (f[i][0..7] = the i-th 16-byte vector of this thread); every step the
 // reference evaluates in T is done on packed pairs with the type's native single-rounding add / multiply.
 template<typename T, int VPT, int MODE>
-__global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(const RowParams p)
+__global__ void __launch_bounds__(256, (VPT <= 4) ? 3 : (VPT <= 6) ? 2 : 1) row_quant_kernel(const RowParams p)
 {
     using P2 = Pair<T>;
     __shared__ float red[8];
 
-    const int    tpr   = p.tpr;
-    const int    team  = threadIdx.x / tpr;
-    const int    tlane = threadIdx.x - team * tpr;
-    const size_t row   = (size_t)blockIdx.x * (256 / tpr) + team;
-    const bool   live  = row < p.rows;
-    const int    nvec  = p.dim >> 3;
+    const int    tpr    = p.tpr;
+    const int    team   = threadIdx.x / tpr;
+    const int    tlane  = threadIdx.x - team * tpr;
+    const int    nvec   = p.dim >> 3;
+    const size_t stride = (size_t)gridDim.x * (256 / tpr);  // rows advance by the number of teams in the grid
 
-    float f[VPT][8];
+    // The grid is sized to what is resident at once; every team walks over rows row0, row0 + stride, ... and
+    // fetches the next row's vectors (and, for LayerNorm + residual or GEGLU, the second operand's) before it
+    // starts on the current one, so the load latency is spent computing.
+    constexpr bool kSecond = (MODE == ROW_LN || MODE == ROW_GEGLU);
+    Vec16 nx[VPT];
+    Vec16 nx2[kSecond ? VPT : 1];
+    auto prefetch = [&](size_t r) {
+        const T* xr = reinterpret_cast<const T*>(p.x) + r * (size_t)p.in_cols;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int vi = tlane + i * tpr;
+            if (vi < nvec) {
+                nx[i] = ld_nc_16(xr + (vi << 3));
+                if (MODE == ROW_GEGLU) {
+                    nx2[kSecond ? i : 0] = ld_nc_16(xr + p.dim + (vi << 3));
+                }
+                if (MODE == ROW_LN && p.residual != nullptr) {
+                    nx2[kSecond ? i : 0] = ld_nc_16(reinterpret_cast<const T*>(p.residual) + r * (size_t)p.dim + (vi << 3));
+                }
+            }
+        }
+    };
 
-    const T* xrow = reinterpret_cast<const T*>(p.x) + row * (size_t)p.in_cols;
+    size_t row = (size_t)blockIdx.x * (256 / tpr) + team;
+    if (row < p.rows) {
+        prefetch(row);
+    }
+    for (; row < p.rows; row += stride) {
+    const bool live = true;
+    float      f[VPT][8];
 
-    // ---- load (and, per mode, pre-combine in T arithmetic) the row
+    // ---- take the prefetched row (and, per mode, pre-combine in T arithmetic); start fetching the next one
+    Vec16 cur[VPT];
+    Vec16 cur2[kSecond ? VPT : 1];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        cur[i] = nx[i];
+        if (kSecond) {
+            cur2[kSecond ? i : 0] = nx2[kSecond ? i : 0];
+        }
+    }
+    if (row + stride < p.rows) {
+        prefetch(row + stride);
+    }
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int vi = tlane + i * tpr;
         if (live && vi < nvec) {
             const int c = vi << 3;
-            Vec16     h = ld_nc_16(xrow + c);
+            Vec16     h = cur[i];
             if (MODE == ROW_LN && p.residual != nullptr) {
                 // h = T(T(x + residual) + bias)
-                const Vec16 r = ld_nc_16(reinterpret_cast<const T*>(p.residual) + row * (size_t)p.dim + c);
+                const Vec16 r = cur2[kSecond ? i : 0];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     h.w[j] = P2::add(h.w[j], r.w[j]);
                 }
                 if (p.bias != nullptr) {
-                    const Vec16 b = ld_nc_16(reinterpret_cast<const T*>(p.bias) + c);
+                    const Vec16 b = ld_nc_16_keep(reinterpret_cast<const T*>(p.bias) + c);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         h.w[j] = P2::add(h.w[j], b.w[j]);
@@ -116,10 +156,10 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
                 }
             }
             if (MODE == ROW_GEGLU) {
-                Vec16 g = ld_nc_16(xrow + p.dim + c);
+                Vec16 g = cur2[kSecond ? i : 0];
                 if (p.bias != nullptr) {
-                    const Vec16 bh = ld_nc_16(reinterpret_cast<const T*>(p.bias) + c);
-                    const Vec16 bg = ld_nc_16(reinterpret_cast<const T*>(p.bias) + p.dim + c);
+                    const Vec16 bh = ld_nc_16_keep(reinterpret_cast<const T*>(p.bias) + c);
+                    const Vec16 bg = ld_nc_16_keep(reinterpret_cast<const T*>(p.bias) + p.dim + c);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         h.w[j] = P2::add(h.w[j], bh.w[j]);
@@ -157,29 +197,30 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
 
     // ---- row statistics (fp32), then normalise and modulate (T arithmetic)
     if (MODE == ROW_ADALN || MODE == ROW_LN) {
-        float s = 0.0f;
+        // four independent partial sums per pass: a single running sum would be one long dependency chain
+        float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                s += f[i][j];
+            for (int j = 0; j < 4; ++j) {
+                s4[j] += f[i][j] + f[i][j + 4];
             }
         }
-        s                = team_reduce<false>(s, tpr, red);
+        float s          = team_reduce<false>((s4[0] + s4[1]) + (s4[2] + s4[3]), tpr, red);
         const float mean = s / (float)p.dim;
-        float       m2   = 0.0f;
+        float       q4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int vi = tlane + i * tpr;
             if (vi < nvec) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const float d = f[i][j] - mean;
-                    m2            = fmaf(d, d, m2);
+                for (int j = 0; j < 4; ++j) {
+                    const float d0 = f[i][j] - mean, d1 = f[i][j + 4] - mean;
+                    q4[j]          = fmaf(d0, d0, fmaf(d1, d1, q4[j]));
                 }
             }
         }
-        m2               = team_reduce<false>(m2, tpr, red);
+        float m2         = team_reduce<false>((q4[0] + q4[1]) + (q4[2] + q4[3]), tpr, red);
         const float var  = fmaxf(m2 / (float)p.dim, 0.0f);
         const float rstd = 1.0f / sqrtf(var + p.eps);  // IEEE sqrt and divide: within one ulp of the exact value
 
@@ -193,8 +234,8 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
             const int vi = tlane + i * tpr;
             if (live && vi < nvec) {
                 const int   c = vi << 3;
-                const Vec16 a = ld_nc_16(mul_v + c);
-                const Vec16 b = ld_nc_16(add_v + c);
+                const Vec16 a = ld_nc_16_keep(mul_v + c);
+                const Vec16 b = ld_nc_16_keep(add_v + c);
                 Vec16       y;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -235,10 +276,8 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
                     amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f[i][4] * p1.x), fabsf(f[i][5] * p1.y)),
                                              fmaxf(fabsf(f[i][6] * p1.z), fabsf(f[i][7] * p1.w))));
                 } else {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        amax = fmaxf(amax, fabsf(f[i][j]));
-                    }
+                    amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(f[i][0]), fabsf(f[i][1])), fmaxf(fabsf(f[i][2]), fabsf(f[i][3]))),
+                                             fmaxf(fmaxf(fabsf(f[i][4]), fabsf(f[i][5])), fmaxf(fabsf(f[i][6]), fabsf(f[i][7])))));
                 }
             }
             amax = team_reduce<true>(amax, tpr, red);
@@ -282,7 +321,28 @@ __global__ void __launch_bounds__(256, (VPT <= 6) ? 3 : 2) row_quant_kernel(cons
             }
         }
     }
+    }  // rows of this team
 }
+
+// Grid = the blocks that are resident at once (occupancy x SMs), or fewer when the rows do not fill them.
+template<typename K> static int launch_row_variant(K kernel, const RowParams& p, size_t needed, cudaStream_t stream)
+{
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess || per_sm <= 0) {
+        return cuda_status(cudaGetLastError(), "cudaOccupancyMaxActiveBlocksPerMultiprocessor(row_quant_kernel)");
+    }
+    const int sms = device_sm_count();
+    if (sms <= 0) {
+        return LYRAQ_ERR_CUDA;
+    }
+    const size_t resident = (size_t)per_sm * (size_t)sms;
+    const size_t grid     = needed < resident ? needed : resident;
+    kernel<<<(unsigned)grid, 256, 0, stream>>>(p);
+    return launch_status();
+}
+
+// Most 16-byte vectors a thread may hold before the team is doubled (4 or 6; sweepable through the debug hook).
+static int g_row_max_vpt = 6;
 
 // Picks the team size and launches.  dim is a multiple of 8 and <= 16384.  The smallest team (32..256 threads) that
 // keeps at most six 16-byte vectors per thread is used, so narrow rows need no cross-warp reduction and every thread
@@ -291,29 +351,26 @@ template<typename T, int MODE> static int launch_row(RowParams p, cudaStream_t s
 {
     const int nvec = p.dim >> 3;
     int       tpr  = 32;
-    while (tpr < 256 && (nvec + tpr - 1) / tpr > 6) {
+    while (tpr < 256 && (nvec + tpr - 1) / tpr > g_row_max_vpt) {
         tpr <<= 1;
     }
     p.tpr                = tpr;
     const int    vpt     = (nvec + tpr - 1) / tpr;
     const size_t per_cta = 256 / tpr;
-    const size_t grid    = (p.rows + per_cta - 1) / per_cta;
-    if (grid == 0) {
+    const size_t needed  = (p.rows + per_cta - 1) / per_cta;
+    if (needed == 0) {
         return LYRAQ_OK;
     }
-    if (grid > 0x7fffffffu) {
-        return LYRAQ_ERR_UNSUPPORTED;
-    }
     if (vpt <= 4) {
-        row_quant_kernel<T, 4, MODE><<<(unsigned)grid, 256, 0, stream>>>(p);
-    } else if (vpt <= 6) {
-        row_quant_kernel<T, 6, MODE><<<(unsigned)grid, 256, 0, stream>>>(p);
-    } else if (vpt <= 8) {
-        row_quant_kernel<T, 8, MODE><<<(unsigned)grid, 256, 0, stream>>>(p);
-    } else {
-        return LYRAQ_ERR_UNSUPPORTED;
+        return launch_row_variant(row_quant_kernel<T, 4, MODE>, p, needed, stream);
     }
-    return launch_status();
+    if (vpt <= 6) {
+        return launch_row_variant(row_quant_kernel<T, 6, MODE>, p, needed, stream);
+    }
+    if (vpt <= 8) {
+        return launch_row_variant(row_quant_kernel<T, 8, MODE>, p, needed, stream);
+    }
+    return LYRAQ_ERR_UNSUPPORTED;
 }
 
 template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaStream_t stream)
@@ -481,6 +538,15 @@ static unsigned flat_grid(size_t nvec)
 using namespace lyraq;
 
 extern "C" {
+
+int lyraq_debug_set_row_vectors_per_thread(int max_vpt)
+{
+    if (max_vpt != 4 && max_vpt != 6) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    g_row_max_vpt = max_vpt;
+    return LYRAQ_OK;
+}
 
 int lyraq_quant_int8(int8_t* dst, const void* src, int src_dtype, const float* pre_quant_scale, float* scale,
                      int scale_mode, size_t rows, size_t dim, void* stream)
