@@ -155,8 +155,19 @@ LYRAQ_API int lyraq_geglu_quant_int8(int8_t* dst, const void* h, const void* bia
 
 /* ------------------------------------------------------------------ GEMMs (tcgen05, accumulators in TMEM) */
 
-/* Bytes of workspace a GEMM call needs for (m, n, k); currently 0 for every op (no split-K), kept so that
- * callers written against the reference's getWorkspaceSize (int8_gemm_template.h:683-692) keep working. */
+/* Operation codes for lyraq_workspace_bytes. */
+enum {
+    LYRAQ_OP_GEMM_INT8 = 0,
+    LYRAQ_OP_GEMM_FP8 = 1,
+    LYRAQ_OP_GEMM_W4A4 = 2,
+    LYRAQ_OP_LINEAR_INT8 = 3,
+    LYRAQ_OP_LINEAR_FP8 = 4,
+    LYRAQ_OP_LINEAR_W4A4 = 5
+};
+
+/* Bytes of workspace an operation needs for (m, n, k).  0 for the bare GEMMs (no split-K; the call is kept so that
+ * callers written against the reference's getWorkspaceSize, int8_gemm_template.h:683-692, keep working); for the
+ * LINEAR_* layer forwards below, the size of the quantized activation plus its scales. */
 LYRAQ_API size_t lyraq_workspace_bytes(int op, int m, int n, int k);
 
 /* INT8 W8A8: C[m,n] = T( T(float(sum_k A[m,k]*B[n,k]) * (alpha_col[n]*alpha_row)) + bias[n] ).
@@ -192,6 +203,31 @@ LYRAQ_API int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* s
                     void* D, int c_dtype, const float* lora_act, const void* lora_up, const void* bias,
                     const void* residual, int epilogue, int m, int n, int k,
                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ quantized-Linear layer forwards
+ * Activation quantize + GEMM of one linear on `stream`; the quantized activation lives in `workspace`
+ * (lyraq_workspace_bytes(LYRAQ_OP_LINEAR_*, m, n, k) bytes, 16-byte aligned, owned by the caller, free for reuse
+ * once the call's work on `stream` has finished).  x, Y, bias and residual all have element type `dtype`. */
+
+/* FP8 linear: x -> e4m3 with the static per-tensor scale x_scale[0], then lyraq_gemm_fp8 (alpha = 1).
+ * Replaces the invokeCudaD2DScaleCpyConvert + GemmWithResidualAndBias pair the FLUX FP8 blocks run per linear
+ * (src/lyradiff/layers/flux_single_transformer_block/FluxSingleTransformerFP8Block.cc:216-243, :254-281). */
+LYRAQ_API int lyraq_linear_fp8_forward(void* Y, const void* x, int dtype, const float* x_scale, const uint8_t* W,
+                                       const float* w_scale, const void* bias, const void* residual, float beta, int epilogue,
+                                       int m, int n, int k, void* workspace, size_t workspace_bytes, void* stream);
+
+/* INT8 SmoothQuant linear: x -> int8 (scale_mode as in lyraq_quant_int8; PER_TOKEN_DYNAMIC keeps the computed scales in
+ * the workspace), then lyraq_gemm_int8 with bias.  Replaces the invokeSqInputQuant + runGemmInt8 pair of the SDXL INT8
+ * block (src/lyradiff/layers/basic_transformer/BasicTransformerInt8Block.cc:427-441). */
+LYRAQ_API int lyraq_linear_int8_forward(void* Y, const void* x, int dtype, const float* pre_quant_scale, const float* input_scale,
+                                        int scale_mode, const int8_t* W, const float* w_scale, const void* bias, int m, int n,
+                                        int k, void* workspace, size_t workspace_bytes, void* stream);
+
+/* W4A4 linear: x -> int4 group-64 (with the smoothing vector), then lyraq_gemm_w4a4 with bias / GELU / residual.
+ * Replaces W4A4Gemm<T>::forward (src/lyradiff/layers/w4a4_gemm_block/W4A4Gemm.cc:113-169) without its low-rank branch. */
+LYRAQ_API int lyraq_w4a4_forward(void* D, const void* x, int dtype, const float* smooth, const uint8_t* W, const void* w_scale,
+                                 int w_scale_dtype, const void* bias, const void* residual, int epilogue, int m, int n, int k,
+                                 void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

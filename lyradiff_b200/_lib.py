@@ -41,6 +41,12 @@ SIGNATURES = {
                                c_float, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_gemm_w4a4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "lyraq_linear_fp8_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
+                                         c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "lyraq_linear_int8_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "lyraq_w4a4_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                   c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
 }
 
 _lib = None

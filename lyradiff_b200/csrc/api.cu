@@ -79,13 +79,5 @@ int lyraq_last_status(void* stream, uint32_t* detail)
     return (int)host[0];
 }
 
-size_t lyraq_workspace_bytes(int op, int m, int n, int k)
-{
-    (void)op;
-    (void)m;
-    (void)n;
-    (void)k;
-    return 0;
-}
 
 }  // extern "C"

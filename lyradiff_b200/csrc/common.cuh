@@ -92,6 +92,14 @@ __device__ __forceinline__ float2 mul_f32x2(float2 a, float2 b)
         : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)));
     return d;
 }
+__device__ __forceinline__ float2 add_f32x2(float2 a, float2 b)
+{
+    float2 d;
+    asm("add.rn.f32x2 %0, %1, %2;"
+        : "=l"(reinterpret_cast<unsigned long long&>(d))
+        : "l"(reinterpret_cast<const unsigned long long&>(a)), "l"(reinterpret_cast<const unsigned long long&>(b)));
+    return d;
+}
 __device__ __forceinline__ float2 fma_f32x2(float2 a, float2 b, float2 c)
 {
     float2 d;

@@ -35,7 +35,8 @@ constexpr int kEpiWarp0    = 4;
 constexpr int kEpiWarps    = 8;
 constexpr int kSmemBudget  = 227 * 1024;
 constexpr int kStoreBox    = 32 * 64;                       // one warp's staging box: 32 rows x 64 bytes
-constexpr int kEpiSmem     = kEpiWarps * kStoreBox + 2 * 256 * 8;  // boxes + two parities of 256 (scale, bias) pairs
+// boxes + two parities of 256 (column scale, bias as fp32) pairs + two parities of 256 bias values as stored (16-bit)
+constexpr int kEpiSmem     = kEpiWarps * kStoreBox + 2 * 256 * 8 + 2 * 256 * 2;
 constexpr int kBarBytes    = 256;
 
 enum GemmKind { KIND_I8 = 0, KIND_F8 = 1 };
@@ -189,6 +190,47 @@ __device__ __forceinline__ void epilogue_math(const EpilogueParams& e, const uin
             }
             t += colp[i].y;
             v[i] = e.gelu ? gelu_tanh_f32(t) : t;
+        }
+    }
+}
+
+// The same chunk for 16-bit outputs, in packed arithmetic throughout: two columns per instruction (fp32 pairs with
+// IEEE rounding per lane, then the output type's native paired add), result as 16 words of two T values.
+// bias2: the chunk's bias as stored (pairs of T); res: the chunk's residual row segment (four 16-byte vectors).
+template<int KIND, typename T>
+__device__ __forceinline__ void epilogue_math16(const EpilogueParams& e, const uint32_t* acc, const float2* colp, const uint32_t* bias2,
+                                                float row_scale, float fp8_scale, bool has_res, const Vec16* res, uint32_t* o)
+{
+    using P2 = Pair<T>;
+    if (KIND == KIND_I8) {
+        const float2 rs2 = make_float2(row_scale, row_scale);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float4 c   = *reinterpret_cast<const float4*>(colp + 2 * i);  // (s_w, bias, s_w, bias) of two columns
+            const float2 sc2 = mul_f32x2(make_float2(c.x, c.z), rs2);          // s_w * s_a first, as the reference does
+            const float2 y2  = mul_f32x2(make_float2((float)(int)acc[2 * i], (float)(int)acc[2 * i + 1]), sc2);
+            uint32_t     h   = P2::from_f32(y2.x, y2.y);                       // T(acc * scale)
+            if (e.bias != nullptr) {
+                h = P2::add(h, bias2[i]);                                      // T(T(acc * scale) + bias)
+            }
+            o[i] = h;
+        }
+    } else {
+        const float2 fs2 = make_float2(fp8_scale, fp8_scale);
+        const float2 be2 = make_float2(e.beta, e.beta);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float4 c = *reinterpret_cast<const float4*>(colp + 2 * i);
+            float2       t = mul_f32x2(make_float2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1])), fs2);
+            if (has_res) {
+                t = fma_f32x2(be2, P2::to_f32(res[i >> 2].w[i & 3]), t);
+            }
+            t = add_f32x2(t, make_float2(c.y, c.w));
+            if (e.gelu) {
+                t.x = gelu_tanh_f32(t.x);
+                t.y = gelu_tanh_f32(t.y);
+            }
+            o[i] = P2::from_f32(t.x, t.y);
         }
     }
 }
@@ -424,6 +466,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         const EpilogueParams& e  = p.epi;
         float2*        colp      = reinterpret_cast<float2*>(gen_base + S::kEpiOffset + kEpiWarps * kStoreBox);  // [2][256]
+        uint16_t*      bias16    = reinterpret_cast<uint16_t*>(colp + 2 * 256);                                   // [2][256]
         uint8_t*       box       = gen_base + S::kEpiOffset + (warp - kEpiWarp0) * kStoreBox;
         const uint32_t box_addr  = smem_base + S::kEpiOffset + (warp - kEpiWarp0) * kStoreBox;
         float fp8_scale = 0.0f;
@@ -440,21 +483,27 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int      m_blk     = tile % p.m_tiles;
             const int      n_blk     = tile / p.m_tiles;
             // column parameters of the tile, staged while the main loop of this tile may still be running
-            float2* cp_tile = colp + (local & 1) * 256;
+            float2*   cp_tile = colp + (local & 1) * 256;
+            uint16_t* b16     = bias16 + (local & 1) * 256;
             if (et < BLOCK_N) {
                 const int col = n_blk * BLOCK_N + et;
                 float2    v   = make_float2(0.0f, 0.0f);
+                uint16_t  raw = 0;
                 if (col < p.N) {
                     if (KIND == KIND_I8 && e.col_scale != nullptr) {
                         v.x = __ldg(e.col_scale + col);
                     }
                     if (e.bias != nullptr) {
-                        v.y = (e.c_dtype == LYRAQ_BF16)  ? to_f32(reinterpret_cast<const __nv_bfloat16*>(e.bias)[col])
-                              : (e.c_dtype == LYRAQ_F16) ? to_f32(reinterpret_cast<const __half*>(e.bias)[col])
-                                                         : reinterpret_cast<const float*>(e.bias)[col];
+                        if (e.c_dtype == LYRAQ_F32) {
+                            v.y = reinterpret_cast<const float*>(e.bias)[col];
+                        } else {
+                            raw = reinterpret_cast<const uint16_t*>(e.bias)[col];
+                            v.y = (e.c_dtype == LYRAQ_BF16) ? __uint_as_float((uint32_t)raw << 16) : __half2float(__ushort_as_half(raw));
+                        }
                     }
                 }
                 cp_tile[et] = v;
+                b16[et]     = raw;
             }
             // the eight epilogue warps meet: named barrier 1, 256 threads
             asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -510,25 +559,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     continue;
                 }
-                float v[32];
-                float res[32];
-                const bool has_res = (KIND == KIND_F8) && e.residual != nullptr;
+                const bool has_res  = (KIND == KIND_F8) && e.residual != nullptr;
                 const bool in_range = row < p.M && valid > 0;
-                if (e.c_dtype == LYRAQ_BF16) {
-                    if (has_res && in_range) {
-                        load_res32<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(e.residual) + (size_t)row * e.ldc + col0, valid, vec_ok, res);
-                    }
-                    epilogue_math<KIND, __nv_bfloat16>(e, a, cp_tile + ccol, row_scale, fp8_scale, has_res && in_range, res, v);
-                } else if (e.c_dtype == LYRAQ_F16) {
-                    if (has_res && in_range) {
-                        load_res32<__half>(reinterpret_cast<const __half*>(e.residual) + (size_t)row * e.ldc + col0, valid, vec_ok, res);
-                    }
-                    epilogue_math<KIND, __half>(e, a, cp_tile + ccol, row_scale, fp8_scale, has_res && in_range, res, v);
-                } else {
+                if (e.c_dtype == LYRAQ_F32) {
+                    float v[32];
+                    float res[32];
                     if (has_res && in_range) {
                         load_res32<float>(reinterpret_cast<const float*>(e.residual) + (size_t)row * e.ldc + col0, valid, vec_ok, res);
                     }
                     epilogue_math<KIND, float>(e, a, cp_tile + ccol, row_scale, fp8_scale, has_res && in_range, res, v);
+                    if (in_range) {
+                        store_row32<float>(reinterpret_cast<float*>(e.C) + (size_t)row * e.ldc + col0, valid, vec_ok, v);
+                    }
+                    continue;
+                }
+                // 16-bit outputs: packed arithmetic, 16 words of two values each
+                uint32_t        o[16];
+                Vec16           res[4];
+                const bool      res_vec = has_res && in_range && vec_ok && valid >= 32;
+                const uint16_t* rrow    = reinterpret_cast<const uint16_t*>(e.residual) + (size_t)row * e.ldc + col0;
+                if (has_res && in_range) {
+                    if (res_vec) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            res[q] = ld_nc_16(rrow + 8 * q);
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int      i0 = 8 * q + 2 * j;
+                                const uint32_t lo = (i0 < valid) ? rrow[i0] : 0u;
+                                const uint32_t hi = (i0 + 1 < valid) ? rrow[i0 + 1] : 0u;
+                                res[q].w[j]       = lo | (hi << 16);
+                            }
+                        }
+                    }
+                }
+                const uint32_t* bias2 = reinterpret_cast<const uint32_t*>(b16 + ccol);
+                if (e.c_dtype == LYRAQ_BF16) {
+                    epilogue_math16<KIND, __nv_bfloat16>(e, a, cp_tile + ccol, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
+                } else {
+                    epilogue_math16<KIND, __half>(e, a, cp_tile + ccol, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
                 }
                 if (e.tma_store) {
                     // 32 rows x 64 bytes through this warp's box, 16-byte pieces XOR-swizzled by (row >> 1) & 3 as the
@@ -537,11 +610,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         tma_store_wait_read();  // the previous chunk's store has drained the box
                     }
                     __syncwarp();
-                    uint8_t* brow = box + lane * 64;
-                    const int sw  = (lane >> 1) & 3;
+                    uint8_t*  brow = box + lane * 64;
+                    const int sw   = (lane >> 1) & 3;
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
-                        Vec16 w = (e.c_dtype == LYRAQ_BF16) ? pack8<__nv_bfloat16>(v + 8 * q) : pack8<__half>(v + 8 * q);
+                        Vec16 w;
+                        w.w[0] = o[4 * q]; w.w[1] = o[4 * q + 1]; w.w[2] = o[4 * q + 2]; w.w[3] = o[4 * q + 3];
                         *reinterpret_cast<Vec16*>(brow + ((q ^ sw) << 4)) = w;
                     }
                     fence_proxy_async_smem();
@@ -551,12 +625,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         tma_store_commit();
                     }
                 } else if (in_range) {
-                    if (e.c_dtype == LYRAQ_BF16) {
-                        store_row32<__nv_bfloat16>(reinterpret_cast<__nv_bfloat16*>(e.C) + (size_t)row * e.ldc + col0, valid, vec_ok, v);
-                    } else if (e.c_dtype == LYRAQ_F16) {
-                        store_row32<__half>(reinterpret_cast<__half*>(e.C) + (size_t)row * e.ldc + col0, valid, vec_ok, v);
+                    uint16_t* crow = reinterpret_cast<uint16_t*>(e.C) + (size_t)row * e.ldc + col0;
+                    if (vec_ok && valid >= 32) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            Vec16 w;
+                            w.w[0] = o[4 * q]; w.w[1] = o[4 * q + 1]; w.w[2] = o[4 * q + 2]; w.w[3] = o[4 * q + 3];
+                            st_16(crow + 8 * q, w);
+                        }
                     } else {
-                        store_row32<float>(reinterpret_cast<float*>(e.C) + (size_t)row * e.ldc + col0, valid, vec_ok, v);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            if (2 * i < valid) {
+                                crow[2 * i] = (uint16_t)(o[i] & 0xffffu);
+                            }
+                            if (2 * i + 1 < valid) {
+                                crow[2 * i + 1] = (uint16_t)(o[i] >> 16);
+                            }
+                        }
                     }
                 }
             }

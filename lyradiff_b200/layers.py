@@ -1,0 +1,114 @@
+"""Quantized-Linear layers over the C ABI: the host-side mirror of the reference's layer objects for this path.
+
+Each class holds quantized weights and scales the way the reference's *Weight classes do, quantizes on load with the
+device quantizers, owns a workspace for the quantized activation, and its forward() is one C-ABI call
+(lyraq_*_forward).  torch supplies device memory and the stream; nothing is computed in torch.
+"""
+
+import torch
+
+from . import _lib, ops
+
+OP_LINEAR_INT8, OP_LINEAR_FP8, OP_LINEAR_W4A4 = 3, 4, 5
+
+
+def _workspace(op, m, n, k, device, current):
+    need = _lib.lib().lyraq_workspace_bytes(op, m, n, k)
+    if current is None or current.numel() < need or current.device != device:
+        current = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+    return current
+
+
+class Fp8Linear:
+    """FP8 e4m3 linear of the FLUX blocks: weight quantized on load with a per-tensor amax/448 scale
+    (MACROLoadFP8WeightFromCache, src/lyradiff/utils/common_macro_def.h:76-92), static activation scale,
+    bias / GELU-tanh / residual fused into the GEMM epilogue."""
+
+    def __init__(self, weight, bias, input_scale, gelu=False):
+        n, k = weight.shape
+        dev = weight.device
+        self.n, self.k, self.gelu = n, k, gelu
+        self.w_scale = torch.zeros(1, dtype=torch.float32, device=dev)
+        ops.invoke_get_fp8_weight_scale(self.w_scale, weight.contiguous())
+        self.qweight = torch.empty(n, k, dtype=torch.uint8, device=dev)
+        ops.invoke_cuda_d2d_scale_cpy_convert(self.qweight, weight.contiguous(), self.w_scale)
+        self.bias = None if bias is None else bias.contiguous()
+        self.input_scale = input_scale.to(device=dev, dtype=torch.float32).reshape(1).contiguous()
+        self._ws = None
+
+    def forward(self, x, residual=None, beta=1.0, out=None):
+        m = x.numel() // self.k
+        x2 = x.reshape(m, self.k)
+        y = out if out is not None else torch.empty(m, self.n, dtype=x.dtype, device=x.device)
+        self._ws = _workspace(OP_LINEAR_FP8, m, self.n, self.k, x.device, self._ws)
+        st = _lib.lib().lyraq_linear_fp8_forward(
+            ops._p(y), ops._p(x2), ops._dt(x2), ops._p(self.input_scale), ops._p(self.qweight), ops._p(self.w_scale),
+            ops._p(self.bias), ops._p(residual), float(beta), ops.EPI_GELU_TANH if self.gelu else ops.EPI_NONE, m, self.n,
+            self.k, ops._p(self._ws), self._ws.numel(), ops._stream())
+        _lib.check(st, "lyraq_linear_fp8_forward")
+        return y.reshape(*x.shape[:-1], self.n)
+
+
+class SmoothQuantLinear:
+    """INT8 SmoothQuant W8A8 linear of the SDXL INT8 block: int8 weight + per-channel scale + smoothing vector
+    (.weight_int8 / .weight_quant_scale / .pre_quant_scale / .input_quant_scale,
+    src/lyradiff/layers/basic_transformer/BasicTransformerInt8BlockWeight.cc:249-288).  input_scale=None selects
+    dynamic per-token activation scales."""
+
+    def __init__(self, qweight, weight_scale, pre_quant_scale, bias=None, input_scale=None):
+        self.n, self.k = qweight.shape
+        self.qweight, self.w_scale, self.pre = qweight.contiguous(), weight_scale.contiguous(), pre_quant_scale
+        self.bias, self.input_scale = bias, input_scale
+        self._ws = None
+
+    @classmethod
+    def from_float(cls, weight, pre_quant_scale, bias=None, input_scale=None):
+        """Quantizes a floating-point weight on the device as invokeGetINT8WeightScale does
+        (src/lyradiff/kernels/quant_kernels/quant_kernels.cu:270-312)."""
+        n, k = weight.shape
+        qw = torch.empty(n, k, dtype=torch.int8, device=weight.device)
+        sw = torch.empty(n, dtype=torch.float32, device=weight.device)
+        ops.invoke_get_int8_weight_scale(sw, qw, weight.contiguous(), pre_quant_scale)
+        return cls(qw, sw, pre_quant_scale, bias, input_scale)
+
+    def forward(self, x, out=None):
+        m = x.numel() // self.k
+        x2 = x.reshape(m, self.k)
+        y = out if out is not None else torch.empty(m, self.n, dtype=x.dtype, device=x.device)
+        self._ws = _workspace(OP_LINEAR_INT8, m, self.n, self.k, x.device, self._ws)
+        mode = ops.SCALE_PER_TOKEN_DYNAMIC if self.input_scale is None else ops.SCALE_PER_TENSOR
+        st = _lib.lib().lyraq_linear_int8_forward(
+            ops._p(y), ops._p(x2), ops._dt(x2), ops._p(self.pre), ops._p(self.input_scale), mode, ops._p(self.qweight),
+            ops._p(self.w_scale), ops._p(self.bias), m, self.n, self.k, ops._p(self._ws), self._ws.numel(), ops._stream())
+        _lib.check(st, "lyraq_linear_int8_forward")
+        return y.reshape(*x.shape[:-1], self.n)
+
+
+class W4A4Gemm:
+    """W4A4 group-64 linear: W4A4Gemm<T> / W4A4GemmWeight<T> (src/lyradiff/layers/w4a4_gemm_block/W4A4Gemm.cc:113-169,
+    W4A4GemmWeight.h:8-45): packed int4 weight [n, k/2], group scales [n, k/64], smoothing vector, optional bias."""
+
+    def __init__(self, packed_weight, weight_scale, smooth=None, bias=None, gelu=False):
+        self.n, self.k = packed_weight.shape[0], packed_weight.shape[1] * 2
+        self.qweight, self.w_scale, self.smooth, self.bias, self.gelu = packed_weight, weight_scale, smooth, bias, gelu
+        self._ws = None
+
+    @classmethod
+    def from_float(cls, weight, smooth=None, bias=None, gelu=False, scale_dtype=torch.float16):
+        n, k = weight.shape
+        qw = torch.empty(n, k // 2, dtype=torch.uint8, device=weight.device)
+        sw = torch.empty(n, k // 64, dtype=scale_dtype, device=weight.device)
+        ops.weight_quant_int4_g64(qw, sw, weight.contiguous())
+        return cls(qw, sw, smooth, bias, gelu)
+
+    def forward(self, x, residual=None, out=None):
+        m = x.numel() // self.k
+        x2 = x.reshape(m, self.k)
+        y = out if out is not None else torch.empty(m, self.n, dtype=x.dtype, device=x.device)
+        self._ws = _workspace(OP_LINEAR_W4A4, m, self.n, self.k, x.device, self._ws)
+        st = _lib.lib().lyraq_w4a4_forward(
+            ops._p(y), ops._p(x2), ops._dt(x2), ops._p(self.smooth), ops._p(self.qweight), ops._p(self.w_scale),
+            ops._dt(self.w_scale), ops._p(self.bias), ops._p(residual), ops.EPI_GELU_TANH if self.gelu else ops.EPI_NONE, m,
+            self.n, self.k, ops._p(self._ws), self._ws.numel(), ops._stream())
+        _lib.check(st, "lyraq_w4a4_forward")
+        return y.reshape(*x.shape[:-1], self.n)

@@ -1,0 +1,74 @@
+"""GPU tests of the quantized-Linear layer forwards (quantize into caller workspace + GEMM in one C-ABI call):
+bit-identical to calling the quantizer and the GEMM separately, and checked against the oracle chain."""
+
+import pytest
+import torch
+
+from oracle import gemm, quant, workloads
+from tests.util import assert_bit_equal, check_status, cu, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def layers():
+    from lyradiff_b200 import layers as _layers
+    return _layers
+
+
+def test_fp8_linear_layer(layers):
+    f = workloads.fp8_linear(300, 512, 392, seed=31, with_residual=True)
+    lin = layers.Fp8Linear(cu(f["w"]), cu(f["bias"]), f["s_x"], gelu=False)
+    assert torch.equal(lin.qweight.cpu(), f["qw"]) and torch.equal(lin.w_scale.cpu(), f["s_w"])
+    y = lin.forward(cu(f["x"]), residual=cu(f["residual"]))
+    want = gemm.fp8_gemm(f["qx"], f["qw"], f["s_x"], f["s_w"], bias=f["bias"], residual=f["residual"])
+    assert rel_err(y, want) < 1e-2
+    lin_g = layers.Fp8Linear(cu(f["w"]), cu(f["bias"]), f["s_x"], gelu=True)
+    yg = lin_g.forward(cu(f["x"]).view(3, 100, 512))
+    assert yg.shape == (3, 100, 392)
+    assert rel_err(yg.view(300, 392), gemm.fp8_gemm(f["qx"], f["qw"], f["s_x"], f["s_w"], bias=f["bias"], gelu=True)) < 1e-2
+    check_status()
+
+
+def test_int8_linear_layer_dynamic_and_static(layers):
+    wl = workloads.int8_smoothquant_linear(m=260, k=640, n=520, seed=32)
+    lin = layers.SmoothQuantLinear.from_float(cu(wl["w"]), cu(wl["pre"]), bias=cu(wl["bias"]))
+    assert torch.equal(lin.qweight.cpu(), wl["qw"])
+    y = lin.forward(cu(wl["x"]))
+    qa, sa = quant.sq_input_quant_dynamic(wl["x"], wl["pre"])
+    assert_bit_equal(y, gemm.int8_gemm(qa, wl["qw"], wl["s_w"], sa, torch.float16, per_token=True, bias=wl["bias"]))
+    s = torch.tensor([0.37], dtype=torch.float32)
+    lin_s = layers.SmoothQuantLinear(cu(wl["qw"]), cu(wl["s_w"]), cu(wl["pre"]), bias=cu(wl["bias"]), input_scale=cu(s))
+    ys = lin_s.forward(cu(wl["x"]))
+    qs = quant.sq_input_quant(wl["x"], wl["pre"], s)
+    assert_bit_equal(ys, gemm.int8_gemm(qs, wl["qw"], wl["s_w"], s, torch.float16, bias=wl["bias"]))
+    check_status()
+
+
+def test_w4a4_layer(layers):
+    w = workloads.w4a4_linear(m=200, k=512, n=264, seed=33, smooth_nontrivial=True)
+    g = torch.Generator().manual_seed(33)
+    bias = (torch.randn(264, generator=g) * 0.1).bfloat16()
+    res = torch.randn(200, 264, generator=g).bfloat16()
+    lin = layers.W4A4Gemm.from_float(cu(w["w"]), smooth=cu(w["smooth"]), bias=cu(bias))
+    assert torch.equal(lin.qweight.cpu(), w["packed_w"])
+    y = lin.forward(cu(w["x"]), residual=cu(res))
+    _, sa, qa = quant.int4_quant_g64(w["x"], w["smooth"])
+    assert_bit_equal(y, gemm.w4a4_gemm(qa, w["qw"], sa, w["s_w"], bias=bias, residual=res))
+    check_status()
+
+
+def test_workspace_is_checked(layers):
+    from lyradiff_b200 import _lib, ops
+    L = _lib.lib()
+    assert L.lyraq_workspace_bytes(4, 128, 256, 512) == 128 * 512
+    assert L.lyraq_workspace_bytes(3, 100, 256, 640) == 100 * 640 + 512
+    assert L.lyraq_workspace_bytes(5, 128, 256, 512) == 128 * 256 + 128 * 8 * 4
+    x = torch.zeros(128, 512, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(256, 512, dtype=torch.uint8, device="cuda")
+    y = torch.empty(128, 256, dtype=torch.bfloat16, device="cuda")
+    s = torch.ones(1, device="cuda")
+    small = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    st = L.lyraq_linear_fp8_forward(y.data_ptr(), x.data_ptr(), 1, s.data_ptr(), w.data_ptr(), s.data_ptr(), None, None, 0.0, 0,
+                                    128, 256, 512, small.data_ptr(), small.numel(), None)
+    assert st == 5  # LYRAQ_ERR_WORKSPACE
