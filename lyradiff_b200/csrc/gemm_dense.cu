@@ -35,8 +35,10 @@ constexpr int kEpiWarp0    = 4;
 constexpr int kEpiWarps    = 8;
 constexpr int kSmemBudget  = 227 * 1024;
 constexpr int kStoreBox    = 32 * 64;                       // one warp's staging box: 32 rows x 64 bytes
-// boxes + two parities of 256 (column scale, bias as fp32) pairs + two parities of 256 bias values as stored (16-bit)
-constexpr int kEpiSmem     = kEpiWarps * kStoreBox + 2 * 256 * 8 + 2 * 256 * 2;
+// per epilogue warp: one store box, then the (column scale, bias as fp32) pairs and the bias as stored (16-bit) of
+// the 128 columns the warp covers
+constexpr int kColParams   = 128 * 8 + 128 * 2;
+constexpr int kEpiSmem     = kEpiWarps * (kStoreBox + kColParams);
 constexpr int kBarBytes    = 256;
 
 enum GemmKind { KIND_I8 = 0, KIND_F8 = 1 };
@@ -462,11 +464,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // ------------------------------------------------------------------ epilogue (warps 4..11)
         const int      quad      = warp & 3;                 // the TMEM lane quadrant this warp may read
         const int      half      = (warp - kEpiWarp0) >> 2;  // which half of the tile's columns
-        const int      et        = threadIdx.x - kEpiWarp0 * 32;  // 0..255
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         const EpilogueParams& e  = p.epi;
-        float2*        colp      = reinterpret_cast<float2*>(gen_base + S::kEpiOffset + kEpiWarps * kStoreBox);  // [2][256]
-        uint16_t*      bias16    = reinterpret_cast<uint16_t*>(colp + 2 * 256);                                   // [2][256]
+        // this warp's private column parameters: no other warp reads or writes them, so __syncwarp is all they need
+        float2*        cp_tile   = reinterpret_cast<float2*>(gen_base + S::kEpiOffset + kEpiWarps * kStoreBox +
+                                                             (warp - kEpiWarp0) * kColParams);  // [128]
+        uint16_t*      b16       = reinterpret_cast<uint16_t*>(cp_tile + 128);                  // [128]
         uint8_t*       box       = gen_base + S::kEpiOffset + (warp - kEpiWarp0) * kStoreBox;
         const uint32_t box_addr  = smem_base + S::kEpiOffset + (warp - kEpiWarp0) * kStoreBox;
         float fp8_scale = 0.0f;
@@ -483,10 +486,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int      m_blk     = tile % p.m_tiles;
             const int      n_blk     = tile / p.m_tiles;
             // column parameters of the tile, staged while the main loop of this tile may still be running
-            float2*   cp_tile = colp + (local & 1) * 256;
-            uint16_t* b16     = bias16 + (local & 1) * 256;
-            if (et < BLOCK_N) {
-                const int col = n_blk * BLOCK_N + et;
+            // column parameters of this warp's half of the tile, staged while the main loop of the tile may still run
+            __syncwarp();
+#pragma unroll
+            for (int cc = lane; cc < kHalfN; cc += 32) {
+                const int col = n_blk * BLOCK_N + half * kHalfN + cc;
                 float2    v   = make_float2(0.0f, 0.0f);
                 uint16_t  raw = 0;
                 if (col < p.N) {
@@ -502,11 +506,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         }
                     }
                 }
-                cp_tile[et] = v;
-                b16[et]     = raw;
+                cp_tile[cc] = v;
+                b16[cc]     = raw;
             }
-            // the eight epilogue warps meet: named barrier 1, 256 threads
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            __syncwarp();
             // the verdict is made warp-uniform: the tensor-memory loads below need the whole warp
             PROF_T0(t_w2);
             if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag))) {
@@ -567,7 +570,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (has_res && in_range) {
                         load_res32<float>(reinterpret_cast<const float*>(e.residual) + (size_t)row * e.ldc + col0, valid, vec_ok, res);
                     }
-                    epilogue_math<KIND, float>(e, a, cp_tile + ccol, row_scale, fp8_scale, has_res && in_range, res, v);
+                    epilogue_math<KIND, float>(e, a, cp_tile + c * 32, row_scale, fp8_scale, has_res && in_range, res, v);
                     if (in_range) {
                         store_row32<float>(reinterpret_cast<float*>(e.C) + (size_t)row * e.ldc + col0, valid, vec_ok, v);
                     }
@@ -597,11 +600,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         }
                     }
                 }
-                const uint32_t* bias2 = reinterpret_cast<const uint32_t*>(b16 + ccol);
+                const uint32_t* bias2 = reinterpret_cast<const uint32_t*>(b16 + c * 32);
                 if (e.c_dtype == LYRAQ_BF16) {
-                    epilogue_math16<KIND, __nv_bfloat16>(e, a, cp_tile + ccol, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
+                    epilogue_math16<KIND, __nv_bfloat16>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
                 } else {
-                    epilogue_math16<KIND, __half>(e, a, cp_tile + ccol, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
+                    epilogue_math16<KIND, __half>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
                 }
                 if (e.tma_store) {
                     // 32 rows x 64 bytes through this warp's box, 16-byte pieces XOR-swizzled by (row >> 1) & 3 as the
@@ -776,14 +779,15 @@ struct TileChoice {
     int ctas;
 };
 
-static TileChoice pick_tile(int m, int n, int sms)
+static TileChoice pick_tile(int m, int n, int k, int sms)
 {
     const long m128 = (m + 127) / 128, m256 = (m + 255) / 256;
     const long n128 = (n + 127) / 128, n256 = (n + 255) / 256;
     const long pairs = sms / 2;
     const double c1_256 = (double)((m128 * n256 + sms - 1) / sms) * 256.0;
     const double c1_128 = (double)((m128 * n128 + sms - 1) / sms) * 128.0;
-    const double c2_256 = (pairs > 0) ? (double)((m256 * n256 + pairs - 1) / pairs) * 256.0 * 0.9 : 1e30;
+    // with a shallow K the epilogue, not operand traffic, bounds the kernel, and a single CTA's smaller tile wins
+    const double c2_256 = (pairs > 0 && k >= 2048) ? (double)((m256 * n256 + pairs - 1) / pairs) * 256.0 * 0.9 : 1e30;
     TileChoice best{256, 1};
     double     cost = c1_256;
     if (c1_128 < cost) {
@@ -876,7 +880,7 @@ template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams 
         return LYRAQ_ERR_CUDA;
     }
     p.epi.ldc = p.N;
-    TileChoice t = pick_tile(p.M, p.N, sms);
+    TileChoice t = pick_tile(p.M, p.N, p.K, sms);
     if (g_forced_tile != 0) {
         t = TileChoice{g_forced_tile / 10, g_forced_tile % 10};
     }
