@@ -229,6 +229,27 @@ LYRAQ_API int lyraq_w4a4_forward(void* D, const void* x, int dtype, const float*
                                  int w_scale_dtype, const void* bias, const void* residual, int epilogue, int m, int n, int k,
                                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* lyraq_w4a4_forward without a workspace argument and without any allocation: the packed activation and its group
+ * scales are kept in a fixed 16 MiB array inside the library's device image (lyraq_static_scratch_bytes()), present on
+ * every GPU that loads the library until the process exits.  Meant for hosts that may not allocate device memory and
+ * have no scratch pointer to pass (an asynchronous enqueue hook, a plug-in interface with inputs and outputs only, a
+ * process whose memory pool belongs to another framework).  It has no counterpart in the reference, whose layers
+ * always draw their buffers from the context's allocator.
+ *   - m * k / 2 + 4 * m * (k / 64) (each rounded up to 256) must fit in the array; larger problems get
+ *     LYRAQ_ERR_WORKSPACE and nothing is launched.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
+ *     outside any stream capture.  No call allocates or frees anything.
+ *   - Every call reuses the same array, which keeps the previous call's contents; nothing in it needs clearing
+ *     because the quantizer rewrites all of it that the GEMM reads.  Calls whose GPU work overlaps race on it:
+ *     issue them on one stream.
+ * Arguments and results are those of lyraq_w4a4_forward. */
+LYRAQ_API int lyraq_w4a4_forward_static(void* D, const void* x, int dtype, const float* smooth, const uint8_t* W,
+                                        const void* w_scale, int w_scale_dtype, const void* bias, const void* residual,
+                                        int epilogue, int m, int n, int k, void* stream);
+
+/* Size in bytes of the fixed scratch array behind lyraq_w4a4_forward_static (no counterpart in the reference). */
+LYRAQ_API size_t lyraq_static_scratch_bytes(void);
+
 #ifdef __cplusplus
 }
 #endif
