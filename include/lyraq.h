@@ -191,6 +191,17 @@ LYRAQ_API int lyraq_gemm_fp8(const uint8_t* X, const float* s_x, const uint8_t* 
                    const void* bias, const void* residual, float alpha, float beta, int epilogue,
                    int m, int n, int k, void* workspace, size_t workspace_bytes, void* stream);
 
+/* lyraq_gemm_fp8 with the activation quantize of the NEXT FP8 linear fused into the epilogue:
+ * Yq[m,n] = e4m3_rne_satfinite( float( T( epi(...) ) ) / y_scale[0] ), T = dtype (the type of bias and residual, and the
+ * type the reference would have stored Y in).  Replaces the sequence GemmWithResidualAndBias -> (GELU kernel) ->
+ * invokeCudaD2DScaleCpyConvert that the FLUX FP8 blocks run between two chained linears
+ * (src/lyradiff/layers/flux_single_transformer_block/FluxSingleTransformerFP8Block.cc:227-281,
+ * src/lyradiff/layers/flux_attn_post_processor/FluxAttnPostFP8Processor.cc:146-195): the 16-bit Y never goes to memory. */
+LYRAQ_API int lyraq_gemm_fp8_quant(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, uint8_t* Yq,
+                                   const float* y_scale, int dtype, const void* bias, const void* residual, float alpha,
+                                   float beta, int epilogue, int m, int n, int k, void* workspace, size_t workspace_bytes,
+                                   void* stream);
+
 /* W4A4, groups of 64 along K: D[m,n] = T( epi( sum_g (float(sum_{k in g} a*b) * sa[m,g]) * sb[n,g]
  *                                              + lora_act[m,:] . lora_up[n,:] + bias[n] ) + R[m,n] ).
  * A packed int4 [m,k/2], B packed int4 [n,k/2], sa fp32 [m,k/64], sb [n,k/64] of sb_dtype (F32 or F16),

@@ -76,6 +76,8 @@ struct EpilogueParams {
     const void*  bias;
     const void*  residual;
     int          gelu;
+    // optional fused output quantize: C receives e4m3 codes of T(result) / out_q_scale[0] instead of T values
+    const float* out_q_scale;
 };
 
 struct GemmParams {
@@ -167,6 +169,21 @@ template<> __device__ __forceinline__ void load_res32<float>(const float* p, int
     for (int i = 0; i < 32; ++i) {
         out[i] = (i < valid) ? p[i] : 0.0f;
     }
+}
+
+// Tile order.  Tiles are numbered so that the tiles running at the same time (consecutive numbers) form bands of
+// kGroupM tile rows swept along N: a wave then touches about as many A rows as B rows, and both operands of a
+// deep-K problem stay in L2 between waves instead of one of them being re-read from HBM every wave.
+constexpr int kGroupM = 8;
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int& m_blk, int& n_blk)
+{
+    const int per_group = kGroupM * n_tiles;
+    const int group     = tile / per_group;
+    const int first_m   = group * kGroupM;
+    const int rows      = min(kGroupM, m_tiles - first_m);
+    const int in_group  = tile - group * per_group;
+    m_blk               = first_m + in_group % rows;
+    n_blk               = in_group / rows;
 }
 
 // The arithmetic of one 32-column chunk of one row: raw accumulator bits -> fp32 results (not yet rounded to T,
@@ -318,8 +335,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         PROF_DECL(w_empty);
         PROF_T0(t_all);
         for (int tile = unit; ok && tile < num_tiles; tile += n_units) {
-            const int m_blk = tile % p.m_tiles;
-            const int n_blk = tile / p.m_tiles;
+            int m_blk, n_blk;
+            tile_coords(tile, p.m_tiles, p.n_tiles, m_blk, n_blk);
             const int a_row = m_blk * kTileM + (int)rank * kBlockM;
             const int b_row = n_blk * BLOCK_N + (int)rank * (BLOCK_N / CTAS);
             for (int kb = 0; kb < num_kb; ++kb) {
@@ -483,8 +500,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         for (int tile = unit; tile < num_tiles; tile += n_units, ++local) {
             const int      buf       = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-            const int      m_blk     = tile % p.m_tiles;
-            const int      n_blk     = tile / p.m_tiles;
+            int m_blk, n_blk;
+            tile_coords(tile, p.m_tiles, p.n_tiles, m_blk, n_blk);
             // column parameters of the tile, staged while the main loop of this tile may still be running
             // column parameters of this warp's half of the tile, staged while the main loop of the tile may still run
             __syncwarp();
@@ -605,6 +622,66 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     epilogue_math16<KIND, __nv_bfloat16>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
                 } else {
                     epilogue_math16<KIND, __half>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
+                }
+                if (e.out_q_scale != nullptr) {
+                    // fused activation quantize for the next FP8 linear: the T-rounded result times 1/s, e4m3 RNE satfinite
+                    if (in_range) {
+                        const float r  = 1.0f / __ldg(e.out_q_scale);
+                        uint32_t    w[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 f0 = (e.c_dtype == LYRAQ_BF16) ? Pair<__nv_bfloat16>::to_f32(o[2 * i]) : Pair<__half>::to_f32(o[2 * i]);
+                            const float2 f1 = (e.c_dtype == LYRAQ_BF16) ? Pair<__nv_bfloat16>::to_f32(o[2 * i + 1]) : Pair<__half>::to_f32(o[2 * i + 1]);
+                            w[i] = f32x2_to_e4m3x2(f0.x * r, f0.y * r) | (f32x2_to_e4m3x2(f1.x * r, f1.y * r) << 16);
+                        }
+                        uint8_t* qrow = reinterpret_cast<uint8_t*>(e.C) + (size_t)row * e.ldc + col0;
+                        if (e.tma_store) {
+                            // handled below, by the whole warp
+                        } else if ((e.ldc & 15) == 0 && valid >= 32) {
+                            Vec16 a0, a1;
+                            a0.w[0] = w[0]; a0.w[1] = w[1]; a0.w[2] = w[2]; a0.w[3] = w[3];
+                            a1.w[0] = w[4]; a1.w[1] = w[5]; a1.w[2] = w[6]; a1.w[3] = w[7];
+                            st_16(qrow, a0);
+                            st_16(qrow + 16, a1);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                if (i < valid) {
+                                    qrow[i] = (uint8_t)((w[i >> 2] >> (8 * (i & 3))) & 0xffu);
+                                }
+                            }
+                        }
+                        if (e.tma_store) {
+                            // stash for the warp-wide store below (rows out of range never get here, TMA clips them)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                o[i] = w[i];
+                            }
+                        }
+                    }
+                    if (e.tma_store) {
+                        // 32 rows x 32 bytes through this warp's box; the two 16-byte halves of a row swap places in rows
+                        // 4-7 of every eight, which is the 32-byte TMA swizzle (and keeps the shared stores conflict-free)
+                        if (lane == 0) {
+                            tma_store_wait_read();
+                        }
+                        __syncwarp();
+                        uint8_t*  brow = box + lane * 32;
+                        const int sw   = (lane >> 2) & 1;
+#pragma unroll
+                        for (int q = 0; q < 2; ++q) {
+                            Vec16 v16;
+                            v16.w[0] = o[4 * q]; v16.w[1] = o[4 * q + 1]; v16.w[2] = o[4 * q + 2]; v16.w[3] = o[4 * q + 3];
+                            *reinterpret_cast<Vec16*>(brow + ((q ^ sw) << 4)) = v16;
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && row0 < p.M && valid > 0) {
+                            tma_store_2d(&tmap_c, box_addr, col0, row0);
+                            tma_store_commit();
+                        }
+                    }
+                    continue;
                 }
                 if (e.tma_store) {
                     // 32 rows x 64 bytes through this warp's box, 16-byte pieces XOR-swizzled by (row >> 1) & 3 as the
@@ -732,21 +809,22 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
     return LYRAQ_OK;
 }
 
-// Tensor map of a row-major [rows, cols] matrix of 16-bit elements for TMA stores of 32 x 32 boxes whose shared-memory
-// image uses the 64-byte swizzle.
-int make_tmap_store_16bit(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols)
+// Tensor map of a row-major [rows, cols] matrix of 1- or 2-byte elements for TMA stores of 32 x 32 boxes whose
+// shared-memory image uses the swizzle that matches the box's row size (32 or 64 bytes).
+int make_tmap_store(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, int elem_bytes)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) {
         return LYRAQ_ERR_CUDA;
     }
     const cuuint64_t dims[2]    = {cols, rows};
-    const cuuint64_t strides[1] = {cols * 2};
+    const cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
     const cuuint32_t box[2]     = {32, 32};
     const cuuint32_t estr[2]    = {1, 1};
-    const CUresult   r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult   r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
+                            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                            elem_bytes == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B,
+                            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled refused the output tensor map");
         return LYRAQ_ERR_CUDA;
@@ -818,8 +896,16 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
     // stores directly and this map is a never-used copy of A's.
     CUtensorMap tc = ta;
     p.epi.tma_store = 0;
-    if ((p.epi.c_dtype == LYRAQ_BF16 || p.epi.c_dtype == LYRAQ_F16) && (p.N & 7) == 0) {
-        st = make_tmap_store_16bit(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N);
+    if (p.epi.out_q_scale != nullptr) {
+        if ((p.N & 15) == 0) {
+            st = make_tmap_store(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N, 1);
+            if (st != LYRAQ_OK) {
+                return st;
+            }
+            p.epi.tma_store = 1;
+        }
+    } else if ((p.epi.c_dtype == LYRAQ_BF16 || p.epi.c_dtype == LYRAQ_F16) && (p.N & 7) == 0) {
+        st = make_tmap_store(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N, 2);
         if (st != LYRAQ_OK) {
             return st;
         }
@@ -968,6 +1054,35 @@ int lyraq_gemm_fp8(const uint8_t* X, const float* s_x, const uint8_t* W, const f
     p.epi.bias     = bias;
     p.epi.residual = residual;
     p.epi.gelu     = (epilogue & LYRAQ_EPI_GELU_TANH) ? 1 : 0;
+    return run_gemm<KIND_F8>(X, W, p, (cudaStream_t)stream);
+}
+
+int lyraq_gemm_fp8_quant(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, uint8_t* Yq, const float* y_scale,
+                         int dtype, const void* bias, const void* residual, float alpha, float beta, int epilogue, int m, int n, int k,
+                         void* workspace, size_t workspace_bytes, void* stream)
+{
+    (void)workspace;
+    (void)workspace_bytes;
+    if ((dtype != LYRAQ_F16 && dtype != LYRAQ_BF16) || s_x == nullptr || s_w == nullptr || y_scale == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if ((epilogue & ~LYRAQ_EPI_GELU_TANH) != 0) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    GemmParams p{};
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.epi.C           = Yq;
+    p.epi.c_dtype     = dtype;
+    p.epi.s_a         = s_x;
+    p.epi.s_b         = s_w;
+    p.epi.alpha       = alpha;
+    p.epi.beta        = (residual == nullptr) ? 0.0f : beta;
+    p.epi.bias        = bias;
+    p.epi.residual    = residual;
+    p.epi.gelu        = (epilogue & LYRAQ_EPI_GELU_TANH) ? 1 : 0;
+    p.epi.out_q_scale = y_scale;
     return run_gemm<KIND_F8>(X, W, p, (cudaStream_t)stream);
 }
 

@@ -396,7 +396,24 @@ __global__ void __launch_bounds__(256) fp8_cast_kernel(uint8_t* dst, const T* sr
     const float  r      = invert ? 1.0f / s : s;
     const size_t nvec   = n >> 3;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t vi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; vi < nvec; vi += stride) {
+    // four independent 16-byte loads in flight per thread and step
+    size_t vi = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; vi + 3 * stride < nvec; vi += 4 * stride) {
+        Vec16 x[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            x[u] = ld_nc_16(src + ((vi + u * stride) << 3));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            float v[8];
+            unpack8<T>(x[u], v);
+            const uint32_t w0 = f32x2_to_e4m3x2(v[0] * r, v[1] * r) | (f32x2_to_e4m3x2(v[2] * r, v[3] * r) << 16);
+            const uint32_t w1 = f32x2_to_e4m3x2(v[4] * r, v[5] * r) | (f32x2_to_e4m3x2(v[6] * r, v[7] * r) << 16);
+            st_8(dst + ((vi + u * stride) << 3), w0, w1);
+        }
+    }
+    for (; vi < nvec; vi += stride) {
         float v[8];
         unpack8<T>(ld_nc_16(src + (vi << 3)), v);
         const uint32_t w0 = f32x2_to_e4m3x2(v[0] * r, v[1] * r) | (f32x2_to_e4m3x2(v[2] * r, v[3] * r) << 16);

@@ -168,6 +168,21 @@ def gemm_with_residual_and_bias_fp8(W, w_scale, X, x_scale, Y, bias=None, residu
     return Y
 
 
+def gemm_fp8_quant_out(W, w_scale, X, x_scale, Yq, y_scale, dtype, bias=None, residual=None, alpha=1.0, beta=1.0, is_gelu=False):
+    """FP8 GEMM whose epilogue also quantizes the result for the next FP8 linear (lyraq_gemm_fp8_quant): Yq uint8 e4m3 codes of
+    T(epi(...)) / y_scale; `dtype` is the torch dtype T of bias / residual.  Fuses GemmWithResidualAndBias + GELU kernel +
+    invokeCudaD2DScaleCpyConvert (FluxSingleTransformerFP8Block.cc:227-281)."""
+    m, k = X.shape
+    n = W.shape[0]
+    if W.shape[1] != k or tuple(Yq.shape) != (m, n):
+        raise ValueError("shape mismatch")
+    st = _lib.lib().lyraq_gemm_fp8_quant(_p(X), _p(x_scale), _p(W), _p(w_scale), _p(Yq), _p(y_scale), _dt(dtype), _p(bias),
+                                         _p(residual), float(alpha), float(beta), EPI_GELU_TANH if is_gelu else EPI_NONE, m, n, k,
+                                         None, 0, _stream())
+    _lib.check(st, "lyraq_gemm_fp8_quant")
+    return Yq
+
+
 def invoke_fused_w4a4_gemm_and_lora_up(D, A, B, lora_act, lora_up, sa, sb, bias=None, residual=None, is_gelu=False):
     """invokeFusedW4A4GemmAndLoraUp (src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.h:19-30) with the bias / GELU / residual
     kernels that follow it fused in.  A uint8 [m,k/2], B uint8 [n,k/2], sa fp32 [m,k/64], sb fp32|fp16 [n,k/64]."""
