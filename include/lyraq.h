@@ -162,7 +162,8 @@ enum {
     LYRAQ_OP_GEMM_W4A4 = 2,
     LYRAQ_OP_LINEAR_INT8 = 3,
     LYRAQ_OP_LINEAR_FP8 = 4,
-    LYRAQ_OP_LINEAR_W4A4 = 5
+    LYRAQ_OP_LINEAR_W4A4 = 5,
+    LYRAQ_OP_LINEAR_W4A4_LORA = 6
 };
 
 /* Bytes of workspace an operation needs for (m, n, k).  0 for the bare GEMMs (no split-K; the call is kept so that
@@ -235,10 +236,20 @@ LYRAQ_API int lyraq_linear_int8_forward(void* Y, const void* x, int dtype, const
                                         int k, void* workspace, size_t workspace_bytes, void* stream);
 
 /* W4A4 linear: x -> int4 group-64 (with the smoothing vector), then lyraq_gemm_w4a4 with bias / GELU / residual.
- * Replaces W4A4Gemm<T>::forward (src/lyradiff/layers/w4a4_gemm_block/W4A4Gemm.cc:113-169) without its low-rank branch. */
+ * Replaces W4A4Gemm<T>::forward (src/lyradiff/layers/w4a4_gemm_block/W4A4Gemm.cc:113-169) without its low-rank branch
+ * (lyraq_w4a4_lora_forward has it). */
 LYRAQ_API int lyraq_w4a4_forward(void* D, const void* x, int dtype, const float* smooth, const uint8_t* W, const void* w_scale,
                                  int w_scale_dtype, const void* bias, const void* residual, int epilogue, int m, int n, int k,
                                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* The whole of W4A4Gemm<T>::forward (src/lyradiff/layers/w4a4_gemm_block/W4A4Gemm.cc:113-169), low-rank branch
+ * included: int4 group-64 quantize of x plus act = x * lora_down^T (fp32, [m, 32]), then the W4A4 GEMM with
+ * T(act) * lora_up^T added after the last group, then bias / GELU / residual.  lora_down [32, k] and lora_up [n, 32] have
+ * the type of x and D.  Workspace: lyraq_workspace_bytes(LYRAQ_OP_LINEAR_W4A4_LORA, m, n, k). */
+LYRAQ_API int lyraq_w4a4_lora_forward(void* D, const void* x, int dtype, const float* smooth, const uint8_t* W,
+                                      const void* w_scale, int w_scale_dtype, const void* lora_down, const void* lora_up,
+                                      const void* bias, const void* residual, int epilogue, int m, int n, int k,
+                                      void* workspace, size_t workspace_bytes, void* stream);
 
 /* lyraq_w4a4_forward without a workspace argument and without any allocation: the packed activation and its group
  * scales are kept in a fixed 16 MiB array inside the library's device image (lyraq_static_scratch_bytes()), present on

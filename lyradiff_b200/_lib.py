@@ -49,6 +49,8 @@ SIGNATURES = {
                                           c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_w4a4_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                    c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "lyraq_w4a4_lora_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_w4a4_forward_static": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                           c_int, c_int, c_int, c_int, c_void_p]),
     "lyraq_static_scratch_bytes": (c_size_t, []),

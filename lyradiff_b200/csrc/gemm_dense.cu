@@ -85,6 +85,10 @@ struct GemmParams {
     int            m_tiles, n_tiles;
     unsigned int*  status;
     EpilogueParams epi;
+#ifdef LYRAQ_PROFILE_WAITS
+    int            skip;  // instrumentation only: bit 0 = the producer signals without loading, bit 1 = the epilogue frees
+                          // the accumulator without reading it
+#endif
 };
 
 // BLOCK_N is the width of the output tile; CTAS = 1: one CTA computes 128 x BLOCK_N; CTAS = 2: a pair of CTAs
@@ -334,6 +338,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool     ok = true;
         PROF_DECL(w_empty);
         PROF_T0(t_all);
+#ifdef LYRAQ_PROFILE_WAITS
+        if ((p.skip & 4) && !leader) {
+            ok = false;  // with bit 2 the peer gets no per-stage signal, so its producer must not wait for one
+        }
+#endif
         for (int tile = unit; ok && tile < num_tiles; tile += n_units) {
             int m_blk, n_blk;
             tile_coords(tile, p.m_tiles, p.n_tiles, m_blk, n_blk);
@@ -348,6 +357,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     break;
                 }
                 PROF_ADD(w_empty, t_w);
+#ifdef LYRAQ_PROFILE_WAITS
+                if (p.skip & 1) {
+                    if (leader) {
+                        mbar_arrive(full_bar(stage));
+                    }
+                } else
+#endif
                 if (CTAS == 2) {
                     // both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair
                     const uint32_t lbar = map_to_cta(full_bar(stage), 0u);
@@ -452,6 +468,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 // the stage is free, in both CTAs, once these MMAs have read it
                 if (CTAS == 2) {
                     tc_commit_pair(empty_bar(stage));
+#ifdef LYRAQ_PROFILE_WAITS
+                    if (!(p.skip & 4))
+#endif
                     tc_commit_pair(map_to_cta(empty_bar(stage), peer));
                 } else {
                     tc_commit(empty_bar(stage));
@@ -550,6 +569,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tmem_ld_32x32(t_addr, acc[0]);
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) {
+#ifdef LYRAQ_PROFILE_WAITS
+                if (p.skip & 2) {
+                    continue;
+                }
+#endif
                 tmem_ld_wait();
                 if (c + 1 < kChunks) {
                     tmem_ld_32x32(t_addr + (uint32_t)((c + 1) * 32), acc[(c + 1) & 1]);
@@ -938,6 +962,9 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
 
 // forced tile configuration for tests and sweeps: 0 = automatic, else block_n * 10 + ctas (2561, 1281, 2562)
 static int g_forced_tile = 0;
+#ifdef LYRAQ_PROFILE_WAITS
+static int g_prof_skip = 0;
+#endif
 
 template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams p, cudaStream_t stream)
 {
@@ -967,6 +994,9 @@ template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams 
     }
     p.epi.ldc = p.N;
     TileChoice t = pick_tile(p.M, p.N, p.K, sms);
+#ifdef LYRAQ_PROFILE_WAITS
+    p.skip = g_prof_skip;
+#endif
     if (g_forced_tile != 0) {
         t = TileChoice{g_forced_tile / 10, g_forced_tile % 10};
     }
@@ -986,6 +1016,11 @@ using namespace lyraq;
 extern "C" {
 
 #ifdef LYRAQ_PROFILE_WAITS
+__attribute__((visibility("default"))) int lyraq_debug_set_skip(int mask)
+{
+    lyraq::g_prof_skip = mask;
+    return LYRAQ_OK;
+}
 __attribute__((visibility("default"))) int lyraq_debug_read_wait_profile(unsigned long long* host, int n_words)
 {
     return cuda_status(cudaMemcpyFromSymbol(host, g_wait_prof, sizeof(unsigned long long) * (size_t)n_words), "read wait profile");

@@ -24,6 +24,11 @@
 //                shared memory as [g][row] (ring of 3 slots), running ahead of the drain; also owns tensor memory
 //   warps 3, 12-14  expand nibbles -> swizzled int8 operand tiles (ring of 4 stages); warp 15 idles
 //   warps 4-11   drain: warp w reads TMEM lanes 32*(w%4).., columns 64*((w-4)/4)..; final epilogue
+// The optional low-rank branch (D += T(act)[m, 32] * up[n, 32]^T, the reference's lora_up_gemm, w4a4_gemm.cu:515-663,
+// with the fp32 -> T conversion of act that W4A4Gemm.cc:143 runs as a separate kernel folded in) rides the same
+// pipeline as one more K block per tile: the expansion warps convert / copy the two 32-wide operands into an operand
+// stage, the MMA warp issues two kind::f16 steps into the next partial buffer, and the drain warps add that fp32
+// partial to their accumulators after the last group, as the reference does.
 // All waits are bounded (see sm100_ptx.cuh); a timeout sets the status word and every role exits.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -71,8 +76,12 @@ struct Params {
     const void*   bias;
     const void*   residual;
     int           gelu;
+    const float*  lora_act;      // [M, 32] fp32 or null
+    const void*   lora_up;       // [N, 32] of D's 16-bit type or null
     unsigned int* status;
 };
+
+constexpr int kLoraRank = 32;
 
 template<typename T>
 __device__ __forceinline__ void final_store32(const Params& p, const float* acc, int row, int col0, int valid, bool vec_ok)
@@ -298,6 +307,34 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         uphase ^= 1u;
                     }
                 }
+                if (ok && p.lora_act != nullptr) {
+                    // low-rank step: two K = 16 MMAs on 16-bit operands into the next partial buffer (fp32)
+                    const int pb = (int)(gi % kPBufs);
+                    if (!mbar_wait(full_u(ustage), uphase, abort_flag) ||
+                        !mbar_wait(part_empty(pb), ((gi / kPBufs) & 1u) ^ 1u, abort_flag)) {
+                        report_timeout(p.status, 0x1900u | (unsigned)ustage);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = ustage0 + ustage * kUStage;
+                    const uint64_t adesc  = umma_desc_k_sw128(a_addr);
+                    const uint64_t bdesc  = umma_desc_k_sw128(a_addr + kOperandTile);
+                    const uint32_t idesc  = umma_idesc(1u, p.c_dtype == LYRAQ_BF16 ? 1u : 0u, kBM, kBN);
+                    const uint32_t d_tmem = tmem_base + (uint32_t)(pb * kBN);
+#pragma unroll
+                    for (int k = 0; k < kLoraRank / 16; ++k) {
+                        mma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (uint32_t)k);
+                    }
+                    tc_commit(part_full(pb));
+                    tc_commit(empty_u(ustage));
+                    ++gi;
+                    if (++ustage == kUStages) {
+                        ustage = 0;
+                        uphase ^= 1u;
+                    }
+                }
             }
         }
     } else if (warp == 2) {
@@ -444,6 +481,54 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     uphase ^= 1u;
                 }
             }
+            if (ok && p.lora_act != nullptr) {
+                // low-rank operands: row tu of T(act) and of up, 64 bytes each, into the first four (swizzled) 16-byte
+                // pieces of the row's 128-byte line; the other four pieces are never read by the two K = 16 steps
+                if (!__all_sync(0xffffffffu, mbar_wait(empty_u(ustage), uphase ^ 1u, abort_flag))) {
+                    if (lane == 0) {
+                        report_timeout(p.status, 0x1a00u | (unsigned)ustage);
+                    }
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                const int m_blk = tile % p.m_tiles;
+                const int n_blk = tile / p.m_tiles;
+                uint8_t*  dst   = gen_base + (ustage0 - smem_base) + ustage * kUStage + (tu >> 3) * 1024 + (tu & 7) * 128;
+                const int arow  = m_blk * kBM + tu;
+                const int brow  = n_blk * kBN + tu;
+                const int swz   = tu & 7;
+                const float4* asrc = reinterpret_cast<const float4*>(p.lora_act + (size_t)arow * kLoraRank);
+                const uint4*  bsrc = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.lora_up) + (size_t)brow * kLoraRank);
+#pragma unroll
+                for (int cidx = 0; cidx < 4; ++cidx) {
+                    uint4 av = make_uint4(0u, 0u, 0u, 0u), bv = make_uint4(0u, 0u, 0u, 0u);
+                    if (arow < p.M) {
+                        const float4 f0 = __ldg(asrc + 2 * cidx), f1 = __ldg(asrc + 2 * cidx + 1);
+                        if (p.c_dtype == LYRAQ_BF16) {
+                            av.x = Pair<__nv_bfloat16>::from_f32(f0.x, f0.y); av.y = Pair<__nv_bfloat16>::from_f32(f0.z, f0.w);
+                            av.z = Pair<__nv_bfloat16>::from_f32(f1.x, f1.y); av.w = Pair<__nv_bfloat16>::from_f32(f1.z, f1.w);
+                        } else {
+                            av.x = Pair<__half>::from_f32(f0.x, f0.y); av.y = Pair<__half>::from_f32(f0.z, f0.w);
+                            av.z = Pair<__half>::from_f32(f1.x, f1.y); av.w = Pair<__half>::from_f32(f1.z, f1.w);
+                        }
+                    }
+                    if (brow < p.N) {
+                        bv = __ldg(bsrc + cidx);
+                    }
+                    *reinterpret_cast<uint4*>(dst + ((cidx ^ swz) << 4))                = av;
+                    *reinterpret_cast<uint4*>(dst + kOperandTile + ((cidx ^ swz) << 4)) = bv;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(full_u(ustage));
+                }
+                if (++ustage == kUStages) {
+                    ustage = 0;
+                    uphase ^= 1u;
+                }
+            }
         }
     } else if (warp >= 4 && warp <= 11) {
         // ------------------------------------------------------------------ drain + epilogue (warps 4..11)
@@ -526,6 +611,34 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                 }
             }
+            if (ok && p.lora_act != nullptr) {
+                const int pb = (int)(gi % kPBufs);
+                if (!__all_sync(0xffffffffu, mbar_wait(part_full(pb), (gi / kPBufs) & 1u, abort_flag))) {
+                    if (lane == 0) {
+                        report_timeout(p.status, 0x1b00u | (unsigned)pb);
+                    }
+                    *abort_flag = 1;
+                    ok = false;
+                } else {
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t part[16];
+                        tmem_ld_32x16(tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64 + c * 16), part);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            acc[c * 8 + j] = add_f32x2(acc[c * 8 + j], make_float2(__uint_as_float(part[2 * j]), __uint_as_float(part[2 * j + 1])));
+                        }
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(part_empty(pb));
+                    }
+                    ++gi;
+                }
+            }
             if (!ok) {
                 break;
             }
@@ -579,8 +692,16 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
         (epilogue & ~LYRAQ_EPI_GELU_TANH) != 0 || m < 0 || n < 0 || k < 0) {
         return LYRAQ_ERR_INVALID_ARG;
     }
-    if (lora_act != nullptr || lora_up != nullptr) {
-        return LYRAQ_ERR_UNSUPPORTED;  // low-rank side branch: not built yet
+    if ((lora_act == nullptr) != (lora_up == nullptr)) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (lora_act != nullptr) {
+        if (c_dtype == LYRAQ_F32) {
+            return LYRAQ_ERR_UNSUPPORTED;  // lora_up has D's type, which must be a 16-bit one
+        }
+        if (!aligned16(lora_act) || !aligned16(lora_up)) {
+            return LYRAQ_ERR_INVALID_ARG;
+        }
     }
     if (k == 0 || (k & 63) != 0) {
         return LYRAQ_ERR_UNSUPPORTED;
@@ -604,6 +725,8 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     p.bias      = bias;
     p.residual  = residual;
     p.gelu      = (epilogue & LYRAQ_EPI_GELU_TANH) ? 1 : 0;
+    p.lora_act  = lora_act;
+    p.lora_up   = lora_up;
     p.status    = status_word_ptr();
     if (p.status == nullptr) {
         return LYRAQ_ERR_CUDA;

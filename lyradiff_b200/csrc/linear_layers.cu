@@ -11,12 +11,15 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 //   LINEAR_FP8  : e4m3 activation [m, k]
 //   LINEAR_INT8 : int8 activation [m, k] | fp32 per-token scales [m]
 //   LINEAR_W4A4 : packed int4 activation [m, k/2] | fp32 group scales [m, k/64]
+//   LINEAR_W4A4_LORA : the same, then the fp32 low-rank activation [m, 32]
 size_t linear_workspace_bytes(int op, size_t m, size_t k)
 {
     switch (op) {
         case LYRAQ_OP_LINEAR_FP8: return align_up(m * k, 256);
         case LYRAQ_OP_LINEAR_INT8: return align_up(m * k, 256) + align_up(4 * m, 256);
         case LYRAQ_OP_LINEAR_W4A4: return align_up(m * k / 2, 256) + align_up(4 * m * (k / 64), 256);
+        case LYRAQ_OP_LINEAR_W4A4_LORA:
+            return align_up(m * k / 2, 256) + align_up(4 * m * (k / 64), 256) + align_up(4 * m * 32, 256);
         default: return 0;
     }
 }
@@ -111,6 +114,35 @@ int lyraq_w4a4_forward(void* D, const void* x, int dtype, const float* smooth, c
     }
     return lyraq_gemm_w4a4(q, W, qs, w_scale, w_scale_dtype, D, dtype, nullptr, nullptr, bias, residual, epilogue, m, n, k,
                            nullptr, 0, stream);
+}
+
+int lyraq_w4a4_lora_forward(void* D, const void* x, int dtype, const float* smooth, const uint8_t* W, const void* w_scale,
+                            int w_scale_dtype, const void* lora_down, const void* lora_up, const void* bias,
+                            const void* residual, int epilogue, int m, int n, int k, void* workspace, size_t workspace_bytes,
+                            void* stream)
+{
+    if (m < 0 || n < 0 || k < 0 || lora_down == nullptr || lora_up == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (m == 0 || n == 0) {
+        return LYRAQ_OK;
+    }
+    if (k == 0 || (k & 63) != 0) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    if (workspace == nullptr || workspace_bytes < linear_workspace_bytes(LYRAQ_OP_LINEAR_W4A4_LORA, (size_t)m, (size_t)k) ||
+        !aligned16(workspace)) {
+        return LYRAQ_ERR_WORKSPACE;
+    }
+    uint8_t* q   = static_cast<uint8_t*>(workspace);
+    float*   qs  = reinterpret_cast<float*>(q + align_up((size_t)m * (size_t)k / 2, 256));
+    float*   act = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(qs) + align_up(4 * (size_t)m * (size_t)(k / 64), 256));
+    int      st  = lyraq_quant_int4_g64(q, qs, act, x, dtype, smooth, lora_down, (size_t)m, (size_t)k, stream);
+    if (st != LYRAQ_OK) {
+        return st;
+    }
+    return lyraq_gemm_w4a4(q, W, qs, w_scale, w_scale_dtype, D, dtype, act, lora_up, bias, residual, epilogue, m, n, k, nullptr,
+                           0, stream);
 }
 
 }  // extern "C"

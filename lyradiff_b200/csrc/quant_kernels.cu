@@ -9,6 +9,7 @@
 namespace lyraq {
 
 int device_sm_count();  // gemm_dense.cu
+int launch_lora_down(float* act, const void* x, const void* down, int dtype, size_t m, size_t k, cudaStream_t stream);  // lora_down.cu
 
 enum RowMode { ROW_PLAIN = 0, ROW_ADALN = 1, ROW_LN = 2, ROW_GEGLU = 3 };
 
@@ -699,10 +700,15 @@ static int int4_g64_dispatch(uint8_t* q, void* q_scale, int scale_dtype, const v
 int lyraq_quant_int4_g64(uint8_t* q, float* q_scale, float* lora_act, const void* x, int x_dtype, const float* smooth,
                          const void* lora_down, size_t m, size_t k, void* stream)
 {
-    if (lora_act != nullptr || lora_down != nullptr) {
-        return LYRAQ_ERR_UNSUPPORTED;  // low-rank side branch: not built yet
+    if ((lora_act == nullptr) != (lora_down == nullptr)) {
+        return LYRAQ_ERR_INVALID_ARG;
     }
-    return int4_g64_dispatch(q, q_scale, LYRAQ_F32, x, x_dtype, smooth, m, k, (cudaStream_t)stream);
+    const int st = int4_g64_dispatch(q, q_scale, LYRAQ_F32, x, x_dtype, smooth, m, k, (cudaStream_t)stream);
+    if (st != LYRAQ_OK || lora_act == nullptr || m == 0) {
+        return st;
+    }
+    // the low-rank down projection reads the unsmoothed x once more (from L2 at these sizes) with its own kernel
+    return launch_lora_down(lora_act, x, lora_down, x_dtype, m, k, (cudaStream_t)stream);
 }
 
 int lyraq_weight_quant_int4_g64(uint8_t* qw, void* w_scale, int scale_dtype, const void* w, int w_dtype, size_t n,

@@ -150,6 +150,20 @@ __device__ __forceinline__ void mma_f8f6f4(uint32_t d_tmem, uint64_t adesc, uint
         : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem]^T for 16-bit floating-point operands (f16 or bf16, per the instruction descriptor),
+// fp32 accumulation; one instruction covers K = 16 elements (32 bytes of a K-major row).
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base_lane + t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t* r)
 {
@@ -274,8 +288,9 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr)
     return d;
 }
 
-// Instruction descriptor of tcgen05.mma kind::i8 / kind::f8f6f4, dense, both operands K-major.
-// c_format: 1 = f32, 2 = s32.  ab_format: kind::i8 -> 1 = signed 8-bit; kind::f8f6f4 -> 0 = e4m3.
+// Instruction descriptor of tcgen05.mma kind::i8 / kind::f8f6f4 / kind::f16, dense, both operands K-major.
+// c_format: 1 = f32, 2 = s32.  ab_format: kind::i8 -> 1 = signed 8-bit; kind::f8f6f4 -> 0 = e4m3;
+// kind::f16 -> 0 = f16, 1 = bf16.
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t c_format, uint32_t ab_format, uint32_t m, uint32_t n)
 {
     return (c_format << 4) | (ab_format << 7) | (ab_format << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);

@@ -9,7 +9,7 @@ import torch
 
 from . import _lib, ops
 
-OP_LINEAR_INT8, OP_LINEAR_FP8, OP_LINEAR_W4A4 = 3, 4, 5
+OP_LINEAR_INT8, OP_LINEAR_FP8, OP_LINEAR_W4A4, OP_LINEAR_W4A4_LORA = 3, 4, 5, 6
 
 
 def _workspace(op, m, n, k, device, current):
@@ -88,23 +88,35 @@ class W4A4Gemm:
     """W4A4 group-64 linear: W4A4Gemm<T> / W4A4GemmWeight<T> (src/lyradiff/layers/w4a4_gemm_block/W4A4Gemm.cc:113-169,
     W4A4GemmWeight.h:8-45): packed int4 weight [n, k/2], group scales [n, k/64], smoothing vector, optional bias."""
 
-    def __init__(self, packed_weight, weight_scale, smooth=None, bias=None, gelu=False):
+    def __init__(self, packed_weight, weight_scale, smooth=None, bias=None, gelu=False, lora_down=None, lora_up=None):
         self.n, self.k = packed_weight.shape[0], packed_weight.shape[1] * 2
         self.qweight, self.w_scale, self.smooth, self.bias, self.gelu = packed_weight, weight_scale, smooth, bias, gelu
+        if (lora_down is None) != (lora_up is None):
+            raise ValueError("lora_down [32, k] and lora_up [n, 32] come together")
+        self.lora_down, self.lora_up = lora_down, lora_up
         self._ws = None
 
     @classmethod
-    def from_float(cls, weight, smooth=None, bias=None, gelu=False, scale_dtype=torch.float16):
+    def from_float(cls, weight, smooth=None, bias=None, gelu=False, scale_dtype=torch.float16, lora_down=None, lora_up=None):
         n, k = weight.shape
         qw = torch.empty(n, k // 2, dtype=torch.uint8, device=weight.device)
         sw = torch.empty(n, k // 64, dtype=scale_dtype, device=weight.device)
         ops.weight_quant_int4_g64(qw, sw, weight.contiguous())
-        return cls(qw, sw, smooth, bias, gelu)
+        return cls(qw, sw, smooth, bias, gelu, lora_down, lora_up)
 
     def forward(self, x, residual=None, out=None):
         m = x.numel() // self.k
         x2 = x.reshape(m, self.k)
         y = out if out is not None else torch.empty(m, self.n, dtype=x.dtype, device=x.device)
+        if self.lora_down is not None:
+            self._ws = _workspace(OP_LINEAR_W4A4_LORA, m, self.n, self.k, x.device, self._ws)
+            st = _lib.lib().lyraq_w4a4_lora_forward(
+                ops._p(y), ops._p(x2), ops._dt(x2), ops._p(self.smooth), ops._p(self.qweight), ops._p(self.w_scale),
+                ops._dt(self.w_scale), ops._p(self.lora_down), ops._p(self.lora_up), ops._p(self.bias), ops._p(residual),
+                ops.EPI_GELU_TANH if self.gelu else ops.EPI_NONE, m, self.n, self.k, ops._p(self._ws), self._ws.numel(),
+                ops._stream())
+            _lib.check(st, "lyraq_w4a4_lora_forward")
+            return y.reshape(*x.shape[:-1], self.n)
         self._ws = _workspace(OP_LINEAR_W4A4, m, self.n, self.k, x.device, self._ws)
         st = _lib.lib().lyraq_w4a4_forward(
             ops._p(y), ops._p(x2), ops._dt(x2), ops._p(self.smooth), ops._p(self.qweight), ops._p(self.w_scale),

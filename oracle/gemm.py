@@ -138,7 +138,10 @@ def w4a4_gemm(qa, qw, sa, sb, out_dtype=torch.bfloat16, group=64, bias=None, gel
         else:
             acc = acc + t * sb[None, :, g]
     if lora_act is not None:
-        acc = acc + lora_act.to(F32) @ lora_up.to(F32).t()
+        # W4A4Gemm.cc:143 converts the fp32 down-projection to T before the low-rank MMA; the 32 products per
+        # output are summed here in fp64 and added to the fp32 accumulator in one step
+        a16 = lora_act.to(out_dtype if out_dtype != F32 else torch.bfloat16).double()
+        acc = (acc.double() + a16 @ lora_up.double().t()).to(F32)
     if bias is not None:
         acc = acc + bias.to(F32)[None, :]
     if gelu:

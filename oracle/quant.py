@@ -179,3 +179,11 @@ def int4_weight_quant_g64(w, group=64):
     (src/lyradiff/layers/w4a4_gemm_block/W4A4GemmWeight.h:21): [N, K/2] bytes, even k low.
     """
     return int4_quant_g64(w, None, group)
+
+
+def lora_down(x, down):
+    """Low-rank down projection computed next to the int4 quantize by fused_quantized_and_lora_down_simple
+    (src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.cu:769-954): act[m, r] = sum_k x[m, k] * down[r, k] on the
+    UNSMOOTHED 16-bit x, fp32 result.  The reference adds its 64-column partial sums with floating-point atomics in
+    no fixed order; the oracle sums in fp64 and rounds once, which every order agrees with to a few fp32 ulps."""
+    return (x.double() @ down.double().t()).to(F32)

@@ -114,3 +114,74 @@ def test_full_size_config3(ops):
     checksum = qa.to(torch.int64) @ w["qw"].to(torch.int64).sum(dim=0)
     assert torch.equal(d32.sum(dim=1, dtype=torch.float64).to(torch.int64).cpu(), checksum)
     check_status()
+
+
+@pytest.mark.parametrize("m,k", [(32, 64), (100, 192), (260, 3072), (4608, 3072)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_lora_down_next_to_the_quantize(ops, m, k, dt):
+    """act = x * lora_down^T in fp32 (tensor-core accumulation order is the hardware's: tolerance 2e-5 of the row's
+    absolute sum); q and scales are the same as without the low-rank branch."""
+    g = torch.Generator().manual_seed(m + k)
+    x = torch.randn(m, k, generator=g).to(dt)
+    down = (torch.randn(32, k, generator=g) * 0.05).to(dt)
+    smooth = (torch.rand(k, generator=g) + 0.5).float()
+    q = torch.empty(m, k // 2, dtype=torch.uint8, device="cuda")
+    s = torch.empty(m, k // 64, dtype=torch.float32, device="cuda")
+    act = torch.full((m, 32), float("nan"), dtype=torch.float32, device="cuda")
+    ops.invoke_fused_quantize_and_lora_down_simple(act, q, s, cu(x), cu(down), cu(smooth))
+    check_status()
+    want_q, want_s, _ = quant.int4_quant_g64(x, smooth)
+    assert_bit_equal(q, want_q, "packed int4")
+    assert_bit_equal(s, want_s, "group scales")
+    want = quant.lora_down(x, down)
+    bound = 2e-5 * (x.double().abs() @ down.double().abs().t()).float() + 1e-30
+    err = (act.cpu() - want).abs()
+    assert bool((err <= bound).all()), "lora_down: worst error / bound = %g" % float((err / bound).max())
+    # reproducible: a second run gives the same bits
+    act2 = torch.empty_like(act)
+    ops.invoke_fused_quantize_and_lora_down_simple(act2, q, s, cu(x), cu(down), cu(smooth))
+    assert_bit_equal(act2, act.cpu(), "second run")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 128), (130, 72, 192), (260, 520, 3072)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_lora_up_added_after_the_groups(ops, m, n, k, dt):
+    """D = T(groups + T(act) * up^T): the low-rank term is a 32-term fp32 tensor-core sum added to the accumulator once,
+    so the result may differ from the oracle's single rounding by an fp32 ulp before the rounding to T: at most one
+    T ulp (plus the fp32 rounding of terms that cancel) on at most 1 % of the outputs."""
+    qa, qw = _rand_int4(m, n, k, seed=m + n + k + 1)
+    g = torch.Generator().manual_seed(n)
+    sa = (torch.rand(m, k // 64, generator=g) * 0.5 + 0.1).float()
+    sb = (torch.rand(n, k // 64, generator=g) * 0.01 + 0.001).float()
+    act = torch.randn(m, 32, generator=g).float() * 3.0
+    up = (torch.randn(n, 32, generator=g) * 0.3).to(dt)
+    bias = (torch.randn(n, generator=g) * 0.1).to(dt)
+    d = torch.empty(m, n, dtype=dt, device="cuda")
+    ops.invoke_fused_w4a4_gemm_and_lora_up(d, cu(quant.pack_int4(qa)), cu(quant.pack_int4(qw)), cu(act), cu(up), cu(sa), cu(sb),
+                                           bias=cu(bias))
+    check_status()
+    want = gemm.w4a4_gemm(qa, qw, sa, sb, out_dtype=dt, lora_act=act, lora_up=up, bias=bias)
+    base = gemm.w4a4_gemm(qa, qw, sa, sb, out_dtype=dt, bias=bias)
+    assert not torch.equal(want, base)  # the low-rank term matters in this test
+    got = d.cpu()
+    diff = (got.float() - want.float()).abs()
+    # one ulp of T at the result, plus the fp32 rounding of the larger terms the result was summed from (they may cancel)
+    terms = (gemm.w4a4_gemm(qa, qw, sa, sb, out_dtype=torch.float32).abs() + bias.float().abs()[None, :] +
+             (act.to(dt).float() @ up.float().t()).abs())
+    bound = torch.finfo(dt).eps * want.float().abs() + 2.0 ** -22 * terms
+    assert bool((diff <= bound).all()), "worst = %g of the bound" % float((diff / bound).max())
+    assert float((diff > 0).float().mean()) <= 1e-2
+
+
+def test_lora_pointers_must_come_together(ops):
+    from lyradiff_b200 import _lib
+    d = torch.empty(128, 128, dtype=torch.bfloat16, device="cuda")
+    a = torch.zeros(128, 32, dtype=torch.uint8, device="cuda")
+    s = torch.ones(128, 1, dtype=torch.float32, device="cuda")
+    act = torch.zeros(128, 32, dtype=torch.float32, device="cuda")
+    with pytest.raises(_lib.LyraqError):
+        ops.invoke_fused_w4a4_gemm_and_lora_up(d, a, a, act, None, s, s)
+    d32 = torch.empty(128, 128, dtype=torch.float32, device="cuda")
+    up = torch.zeros(128, 32, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(_lib.LyraqError):
+        ops.invoke_fused_w4a4_gemm_and_lora_up(d32, a, a, act, up, s, s)  # fp32 output has no 16-bit type for lora_up

@@ -58,6 +58,28 @@ def test_w4a4_layer(layers):
     check_status()
 
 
+def test_w4a4_layer_with_low_rank_branch(layers):
+    """W4A4Gemm<T>::forward with lora_down / lora_up (W4A4Gemm.cc:137-163): compared with the oracle chain
+    quantize -> down projection -> GEMM + up projection at one T ulp (the two low-rank sums are tensor-core fp32 sums)."""
+    w = workloads.w4a4_linear(m=200, k=512, n=264, seed=34, smooth_nontrivial=True)
+    g = torch.Generator().manual_seed(34)
+    bias = (torch.randn(264, generator=g) * 0.1).bfloat16()
+    down = (torch.randn(32, 512, generator=g) * 0.05).bfloat16()
+    up = (torch.randn(264, 32, generator=g) * 0.2).bfloat16()
+    lin = layers.W4A4Gemm.from_float(cu(w["w"]), smooth=cu(w["smooth"]), bias=cu(bias), lora_down=cu(down), lora_up=cu(up))
+    y = lin.forward(cu(w["x"])).cpu()
+    _, sa, qa = quant.int4_quant_g64(w["x"], w["smooth"])
+    act = quant.lora_down(w["x"], down)
+    want = gemm.w4a4_gemm(qa, w["qw"], sa, w["s_w"], bias=bias, lora_act=act, lora_up=up)
+    plain = gemm.w4a4_gemm(qa, w["qw"], sa, w["s_w"], bias=bias)
+    assert not torch.equal(want, plain)
+    diff = (y.float() - want.float()).abs()
+    bound = 2.0 ** -7 * want.float().abs() + 1e-3
+    assert bool((diff <= bound).all()), float((diff / bound).max())
+    assert float((diff > 0).float().mean()) <= 2e-2
+    check_status()
+
+
 def test_workspace_is_checked(layers):
     from lyradiff_b200 import _lib, ops
     L = _lib.lib()
