@@ -193,7 +193,7 @@ inline void invokeFusedW4A4GemmAndLoraUp(void* Dptr, const void* Aptr, const voi
     (void)lora_k;
     (void)groups;
     lyraq_detail::check(lyraq_gemm_w4a4(static_cast<const uint8_t*>(Aptr), static_cast<const uint8_t*>(Bptr), AweightScale,
-                                        BweightScale, LYRAQ_F32, Dptr, LYRAQ_BF16, static_cast<const float*>(LoraAptr),
+                                        BweightScale, LYRAQ_F32, Dptr, LYRAQ_BF16, LoraAptr, LYRAQ_BF16,
                                         LoraBptr, nullptr, nullptr, LYRAQ_EPI_NONE, m, n, k, nullptr, 0, stream),
                         "invokeFusedW4A4GemmAndLoraUp");
 }
@@ -218,6 +218,18 @@ public:
                                             per_token ? LYRAQ_SCALE_PER_TOKEN : LYRAQ_SCALE_PER_TENSOR, C, c_dtype_, nullptr,
                                             m, n, k, workspace, 0, stream),
                             "runGemmInt8");
+    }
+
+    /* runGemmInt8 followed by invokeFusedBiasResidualAdd<T>(dst, gemm_out, residual, bias, ...) in one launch
+     * (BasicTransformerInt8Block.cc:824-845); C may be the residual buffer itself. */
+    void runGemmInt8BiasResidual(const int8_t* A, const int8_t* B, const float* alphaCol, const float* alphaRow, void* C,
+                                 const void* bias, const void* residual, int m, int n, int k, char* workspace,
+                                 cudaStream_t stream, bool per_token = false) const
+    {
+        lyraq_detail::check(lyraq_gemm_int8_residual(A, B, alphaCol, alphaRow,
+                                                     per_token ? LYRAQ_SCALE_PER_TOKEN : LYRAQ_SCALE_PER_TENSOR, C, c_dtype_,
+                                                     bias, residual, m, n, k, workspace, 0, stream),
+                            "runGemmInt8BiasResidual");
     }
 
     /* Called by the reference only as (OP_T, OP_N, n_out, m_tokens, k, W, k, s_w, X, k, s_x, Y, n_out, bias, R, alpha,

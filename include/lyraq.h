@@ -183,6 +183,15 @@ LYRAQ_API int lyraq_gemm_int8(const int8_t* A, const int8_t* B, const float* alp
                     int row_scale_mode, void* C, int c_dtype, const void* bias, int m, int n, int k,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* lyraq_gemm_int8 with the residual add that follows the feed-forward output linear of the SDXL INT8 blocks fused in:
+ * C[m,n] = T( T( T(acc * (alpha_col[n]*alpha_row)) + R[m,n] ) + bias[n] ), every step rounded to T as the reference's
+ * separate kernel does (fusedBiasResidualAdd, src/lyradiff/kernels/basic_transformer/basic_transformer_kernels.cu:183-215,
+ * called at layers/basic_transformer/BasicTransformerInt8Block.cc:824-845).  R of c_dtype [m,n] or NULL; C may alias R.
+ * c_dtype F16/BF16/F32. */
+LYRAQ_API int lyraq_gemm_int8_residual(const int8_t* A, const int8_t* B, const float* alpha_col, const float* alpha_row,
+                                       int row_scale_mode, void* C, int c_dtype, const void* bias, const void* residual,
+                                       int m, int n, int k, void* workspace, size_t workspace_bytes, void* stream);
+
 /* FP8 e4m3: Y[m,n] = T( epi( alpha*s_x[0]*s_w[0] * sum_k X[m,k]*W[n,k] + beta*R[m,n] + bias[n] ) ),
  * fp32 accumulation, epi = identity or tanh-GELU (epilogue flags), bias/R of c_dtype or NULL.
  * Replaces cublasMMWrapper::GemmWithResidualAndBias for __nv_fp8_e4m3
@@ -206,14 +215,16 @@ LYRAQ_API int lyraq_gemm_fp8_quant(const uint8_t* X, const float* s_x, const uin
 /* W4A4, groups of 64 along K: D[m,n] = T( epi( sum_g (float(sum_{k in g} a*b) * sa[m,g]) * sb[n,g]
  *                                              + lora_act[m,:] . lora_up[n,:] + bias[n] ) + R[m,n] ).
  * A packed int4 [m,k/2], B packed int4 [n,k/2], sa fp32 [m,k/64], sb [n,k/64] of sb_dtype (F32 or F16),
- * exact int32 per group, fp32 across groups in order g = 0..k/64-1.  lora_act fp32 [m,32] and
- * lora_up (c_dtype, [n,32]) may both be NULL.  bias, R of c_dtype or NULL.
+ * exact int32 per group, fp32 across groups in order g = 0..k/64-1.  lora_act [m,32] and lora_up (c_dtype, [n,32])
+ * may both be NULL; lora_act_dtype is F32 (the down projection as lyraq_quant_int4_g64 wrote it; it is rounded to
+ * c_dtype on the way in, which replaces the invokeCudaD2DcpyConvert of W4A4Gemm.cc:143) or c_dtype (already converted,
+ * as the reference's caller passes it).  bias, R of c_dtype or NULL.
  * Replaces invokeFusedW4A4GemmAndLoraUp (src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.h:19-30; kernels
  * w4a4_gemm.cu:227-767) and the bias/GELU/residual kernels that follow it
  * (kernels/flux_single_transformer_block/flux_single_transformer_kernels.cu:68-134). */
 LYRAQ_API int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* sa, const void* sb, int sb_dtype,
-                    void* D, int c_dtype, const float* lora_act, const void* lora_up, const void* bias,
-                    const void* residual, int epilogue, int m, int n, int k,
+                    void* D, int c_dtype, const void* lora_act, int lora_act_dtype, const void* lora_up,
+                    const void* bias, const void* residual, int epilogue, int m, int n, int k,
                     void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ quantized-Linear layer forwards

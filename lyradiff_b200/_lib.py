@@ -37,11 +37,13 @@ SIGNATURES = {
     "lyraq_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "lyraq_gemm_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
                                 c_int, c_void_p, c_size_t, c_void_p]),
+    "lyraq_gemm_int8_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                         c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_gemm_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float,
                                c_float, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_gemm_fp8_quant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_float, c_float, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
-    "lyraq_gemm_w4a4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+    "lyraq_gemm_w4a4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_linear_fp8_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float,
                                          c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),

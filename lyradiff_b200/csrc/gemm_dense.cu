@@ -202,7 +202,11 @@ __device__ __forceinline__ void epilogue_math(const EpilogueParams& e, const uin
             const float2 cp = colp[i];  // same address in every lane: a shared-memory broadcast
             // T(T(acc * (s_w * s_a)) + bias): the first rounding here, the second when the value is stored as T
             // (explicitly rounded multiply: for T = float nothing sits between it and the add, and it must not fuse)
-            v[i] = round_t<T>(__fmul_rn((float)(int)acc[i], cp.x * row_scale)) + cp.y;
+            float t = round_t<T>(__fmul_rn((float)(int)acc[i], cp.x * row_scale));
+            if (has_res) {
+                t = round_t<T>(t + res[i]);  // T(T(acc * scale) + R) before the bias, as fusedBiasResidualAdd orders it
+            }
+            v[i] = t + cp.y;
         }
     } else {
 #pragma unroll
@@ -233,6 +237,9 @@ __device__ __forceinline__ void epilogue_math16(const EpilogueParams& e, const u
             const float2 sc2 = mul_f32x2(make_float2(c.x, c.z), rs2);          // s_w * s_a first, as the reference does
             const float2 y2  = mul_f32x2(make_float2((float)(int)acc[2 * i], (float)(int)acc[2 * i + 1]), sc2);
             uint32_t     h   = P2::from_f32(y2.x, y2.y);                       // T(acc * scale)
+            if (has_res) {
+                h = P2::add(h, res[i >> 2].w[i & 3]);                          // T(T(acc * scale) + R)
+            }
             if (e.bias != nullptr) {
                 h = P2::add(h, bias2[i]);                                      // T(T(acc * scale) + bias)
             }
@@ -603,7 +610,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     continue;
                 }
-                const bool has_res  = (KIND == KIND_F8) && e.residual != nullptr;
+                const bool has_res  = e.residual != nullptr;
                 const bool in_range = row < p.M && valid > 0;
                 if (e.c_dtype == LYRAQ_F32) {
                     float v[32];
@@ -1061,6 +1068,32 @@ int lyraq_gemm_int8(const int8_t* A, const int8_t* B, const float* alpha_col, co
     p.epi.row_scale           = alpha_row;
     p.epi.row_scale_per_token = (row_scale_mode == LYRAQ_SCALE_PER_TOKEN) ? 1 : 0;
     p.epi.bias                = (c_dtype == LYRAQ_S32) ? nullptr : bias;
+    return run_gemm<KIND_I8>(A, B, p, (cudaStream_t)stream);
+}
+
+int lyraq_gemm_int8_residual(const int8_t* A, const int8_t* B, const float* alpha_col, const float* alpha_row,
+                             int row_scale_mode, void* C, int c_dtype, const void* bias, const void* residual, int m, int n,
+                             int k, void* workspace, size_t workspace_bytes, void* stream)
+{
+    (void)workspace;
+    (void)workspace_bytes;
+    if (c_dtype < LYRAQ_F16 || c_dtype > LYRAQ_F32 || alpha_col == nullptr || alpha_row == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (row_scale_mode != LYRAQ_SCALE_PER_TENSOR && row_scale_mode != LYRAQ_SCALE_PER_TOKEN) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    GemmParams p{};
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.epi.C                   = C;
+    p.epi.c_dtype             = c_dtype;
+    p.epi.col_scale           = alpha_col;
+    p.epi.row_scale           = alpha_row;
+    p.epi.row_scale_per_token = (row_scale_mode == LYRAQ_SCALE_PER_TOKEN) ? 1 : 0;
+    p.epi.bias                = bias;
+    p.epi.residual            = residual;
     return run_gemm<KIND_I8>(A, B, p, (cudaStream_t)stream);
 }
 

@@ -76,7 +76,8 @@ struct Params {
     const void*   bias;
     const void*   residual;
     int           gelu;
-    const float*  lora_act;      // [M, 32] fp32 or null
+    const void*   lora_act;      // [M, 32], fp32 or already of D's 16-bit type, or null
+    int           lora_act_is_f32;
     const void*   lora_up;       // [N, 32] of D's 16-bit type or null
     unsigned int* status;
 };
@@ -498,12 +499,15 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int arow  = m_blk * kBM + tu;
                 const int brow  = n_blk * kBN + tu;
                 const int swz   = tu & 7;
-                const float4* asrc = reinterpret_cast<const float4*>(p.lora_act + (size_t)arow * kLoraRank);
+                const float4* asrc = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.lora_act) + (size_t)arow * kLoraRank);
+                const uint4*  a16  = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.lora_act) + (size_t)arow * kLoraRank);
                 const uint4*  bsrc = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.lora_up) + (size_t)brow * kLoraRank);
 #pragma unroll
                 for (int cidx = 0; cidx < 4; ++cidx) {
                     uint4 av = make_uint4(0u, 0u, 0u, 0u), bv = make_uint4(0u, 0u, 0u, 0u);
-                    if (arow < p.M) {
+                    if (arow < p.M && !p.lora_act_is_f32) {
+                        av = __ldg(a16 + cidx);
+                    } else if (arow < p.M) {
                         const float4 f0 = __ldg(asrc + 2 * cidx), f1 = __ldg(asrc + 2 * cidx + 1);
                         if (p.c_dtype == LYRAQ_BF16) {
                             av.x = Pair<__nv_bfloat16>::from_f32(f0.x, f0.y); av.y = Pair<__nv_bfloat16>::from_f32(f0.z, f0.w);
@@ -676,7 +680,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 using namespace lyraq;
 
 extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* sa, const void* sb, int sb_dtype, void* D,
-                               int c_dtype, const float* lora_act, const void* lora_up, const void* bias,
+                               int c_dtype, const void* lora_act, int lora_act_dtype, const void* lora_up, const void* bias,
                                const void* residual, int epilogue, int m, int n, int k, void* workspace,
                                size_t workspace_bytes, void* stream)
 {
@@ -698,6 +702,9 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     if (lora_act != nullptr) {
         if (c_dtype == LYRAQ_F32) {
             return LYRAQ_ERR_UNSUPPORTED;  // lora_up has D's type, which must be a 16-bit one
+        }
+        if (lora_act_dtype != LYRAQ_F32 && lora_act_dtype != c_dtype) {
+            return LYRAQ_ERR_INVALID_ARG;
         }
         if (!aligned16(lora_act) || !aligned16(lora_up)) {
             return LYRAQ_ERR_INVALID_ARG;
@@ -726,6 +733,7 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     p.residual  = residual;
     p.gelu      = (epilogue & LYRAQ_EPI_GELU_TANH) ? 1 : 0;
     p.lora_act  = lora_act;
+    p.lora_act_is_f32 = (lora_act_dtype == LYRAQ_F32) ? 1 : 0;
     p.lora_up   = lora_up;
     p.status    = status_word_ptr();
     if (p.status == nullptr) {

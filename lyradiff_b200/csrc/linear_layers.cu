@@ -112,7 +112,7 @@ int lyraq_w4a4_forward(void* D, const void* x, int dtype, const float* smooth, c
     if (st != LYRAQ_OK) {
         return st;
     }
-    return lyraq_gemm_w4a4(q, W, qs, w_scale, w_scale_dtype, D, dtype, nullptr, nullptr, bias, residual, epilogue, m, n, k,
+    return lyraq_gemm_w4a4(q, W, qs, w_scale, w_scale_dtype, D, dtype, nullptr, LYRAQ_F32, nullptr, bias, residual, epilogue, m, n, k,
                            nullptr, 0, stream);
 }
 
@@ -141,7 +141,7 @@ int lyraq_w4a4_lora_forward(void* D, const void* x, int dtype, const float* smoo
     if (st != LYRAQ_OK) {
         return st;
     }
-    return lyraq_gemm_w4a4(q, W, qs, w_scale, w_scale_dtype, D, dtype, act, lora_up, bias, residual, epilogue, m, n, k, nullptr,
+    return lyraq_gemm_w4a4(q, W, qs, w_scale, w_scale_dtype, D, dtype, act, LYRAQ_F32, lora_up, bias, residual, epilogue, m, n, k, nullptr,
                            0, stream);
 }
 

@@ -138,14 +138,23 @@ def invoke_fused_add_bias_geglu_int8o(dst, hidden_states, bias, pre_quant_scale,
 
 
 # ----------------------------------------------------------------------------- GEMMs
-def run_gemm_int8(A, B, alpha_col, alpha_row, C, bias=None, per_token=False, workspace=None):
+def run_gemm_int8(A, B, alpha_col, alpha_row, C, bias=None, per_token=False, workspace=None, residual=None):
     """cublasMMWrapper::runGemmInt8 (src/lyradiff/utils/cublasMMWrapper.h:368-385): C[m,n] from A int8 [m,k], B int8 [n,k].
-    C dtype fp16/bf16/fp32 (dequantized) or int32 (raw accumulators)."""
+    C dtype fp16/bf16/fp32 (dequantized) or int32 (raw accumulators).  `residual` [m,n] fuses the invokeFusedBiasResidualAdd
+    that follows the SDXL feed-forward output linear (BasicTransformerInt8Block.cc:824-845)."""
     m, k = A.shape
     n = B.shape[0]
     if B.shape[1] != k or tuple(C.shape) != (m, n):
         raise ValueError("shape mismatch")
     ws = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    if residual is not None:
+        if tuple(residual.shape) != (m, n) or residual.dtype != C.dtype:
+            raise ValueError("residual must have the shape and dtype of C")
+        st = _lib.lib().lyraq_gemm_int8_residual(_p(A), _p(B), _p(alpha_col), _p(alpha_row),
+                                                 SCALE_PER_TOKEN if per_token else SCALE_PER_TENSOR, _p(C), _dt(C), _p(bias),
+                                                 _p(residual), m, n, k, _p(workspace), ws, _stream())
+        _lib.check(st, "lyraq_gemm_int8_residual")
+        return C
     st = _lib.lib().lyraq_gemm_int8(_p(A), _p(B), _p(alpha_col), _p(alpha_row),
                                     SCALE_PER_TOKEN if per_token else SCALE_PER_TENSOR, _p(C), _dt(C), _p(bias), m, n, k,
                                     _p(workspace), ws, _stream())
@@ -185,13 +194,15 @@ def gemm_fp8_quant_out(W, w_scale, X, x_scale, Yq, y_scale, dtype, bias=None, re
 
 def invoke_fused_w4a4_gemm_and_lora_up(D, A, B, lora_act, lora_up, sa, sb, bias=None, residual=None, is_gelu=False):
     """invokeFusedW4A4GemmAndLoraUp (src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.h:19-30) with the bias / GELU / residual
-    kernels that follow it fused in.  A uint8 [m,k/2], B uint8 [n,k/2], sa fp32 [m,k/64], sb fp32|fp16 [n,k/64]."""
+    kernels that follow it fused in.  A uint8 [m,k/2], B uint8 [n,k/2], sa fp32 [m,k/64], sb fp32|fp16 [n,k/64];
+    lora_act [m,32] fp32 (as the quantizer wrote it) or already of D's dtype, lora_up [n,32] of D's dtype."""
     m, kh = A.shape
     n = B.shape[0]
     k = kh * 2
     if B.shape[1] != kh or tuple(D.shape) != (m, n):
         raise ValueError("shape mismatch")
-    st = _lib.lib().lyraq_gemm_w4a4(_p(A), _p(B), _p(sa), _p(sb), _dt(sb), _p(D), _dt(D), _p(lora_act), _p(lora_up),
+    st = _lib.lib().lyraq_gemm_w4a4(_p(A), _p(B), _p(sa), _p(sb), _dt(sb), _p(D), _dt(D), _p(lora_act),
+                                    F32 if lora_act is None else _dt(lora_act), _p(lora_up),
                                     _p(bias), _p(residual), EPI_GELU_TANH if is_gelu else EPI_NONE, m, n, k, None, 0,
                                     _stream())
     _lib.check(st, "lyraq_gemm_w4a4")

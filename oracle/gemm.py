@@ -40,7 +40,7 @@ def int8_gemm_acc(qa, qw):
     return int_matmul_exact(qa, qw)
 
 
-def int8_gemm(qa, qw, alpha_col, alpha_row, out_dtype, per_token=False, bias=None, acc=None):
+def int8_gemm(qa, qw, alpha_col, alpha_row, out_dtype, per_token=False, bias=None, acc=None, residual=None):
     """C = T(float(acc) * (alpha_col[n] * alpha_row)), then bias added in T arithmetic.
 
     Scale order follows EpilogueVisitorPerRowPerCol
@@ -56,6 +56,10 @@ def int8_gemm(qa, qw, alpha_col, alpha_row, out_dtype, per_token=False, bias=Non
     ar = ar[:, None] if per_token else ar[0]
     scale = alpha_col.to(F32)[None, :] * ar
     y = _round_to(acc.to(F32) * scale, out_dtype)
+    if residual is not None:
+        # fusedBiasResidualAdd (src/lyradiff/kernels/basic_transformer/basic_transformer_kernels.cu:183-215):
+        # src + residual + bias in T arithmetic, left to right
+        y = _round_to(y.to(F32) + residual.to(F32), out_dtype)
     if bias is not None:
         y = _round_to(y.to(F32) + bias.to(F32)[None, :], out_dtype)
     return y

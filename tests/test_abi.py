@@ -67,7 +67,7 @@ def test_bad_arguments_are_refused_without_a_device(lib):
     assert lib.lyraq_quant_fp8(None, None, 1, None, 1, 64, None) == INVALID
     assert lib.lyraq_gemm_int8(None, None, None, None, 0, None, 0, None, 128, 128, 128, None, 0, None) == INVALID
     assert lib.lyraq_gemm_fp8(None, None, None, None, None, 1, None, None, 1.0, 0.0, 0, 128, 128, 128, None, 0, None) == INVALID
-    assert lib.lyraq_gemm_w4a4(None, None, None, None, 2, None, 1, None, None, None, None, 0, 128, 128, 128, None, 0, None) == INVALID
+    assert lib.lyraq_gemm_w4a4(None, None, None, None, 2, None, 1, None, 2, None, None, None, 0, 128, 128, 128, None, 0, None) == INVALID
     # fake but well-aligned addresses: shape checks come before any launch
     p = 0x1000
     assert lib.lyraq_quant_int8(p, p, 0, None, p, 0, 4, 60, None) == UNSUPPORTED       # dim % 8
@@ -79,7 +79,7 @@ def test_bad_arguments_are_refused_without_a_device(lib):
     assert lib.lyraq_gemm_int8(p, p, p, p, 0, p, 0, None, 128, 128, 120, None, 0, None) == UNSUPPORTED  # k % 16
     assert lib.lyraq_gemm_int8(p, p, p, p, 5, p, 0, None, 128, 128, 128, None, 0, None) == INVALID
     assert lib.lyraq_gemm_fp8(p, p, p, p, p, 3, None, None, 1.0, 0.0, 0, 128, 128, 128, None, 0, None) == INVALID
-    assert lib.lyraq_gemm_w4a4(p, p, p, p, 2, p, 1, None, None, None, None, 0, 128, 128, 96, None, 0, None) == UNSUPPORTED
+    assert lib.lyraq_gemm_w4a4(p, p, p, p, 2, p, 1, None, 2, None, None, None, 0, 128, 128, 96, None, 0, None) == UNSUPPORTED
     # empty problems are a no-op
     assert lib.lyraq_gemm_int8(p, p, p, p, 0, p, 0, None, 0, 128, 128, None, 0, None) == 0
     assert lib.lyraq_quant_fp8(p, p, 1, p, 1, 0, None) == 0

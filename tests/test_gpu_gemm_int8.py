@@ -73,6 +73,29 @@ def test_dequant_epilogue_bit_exact(ops, tile, dtype, m, n, k):
     check_status()
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (130, 72, 144), (520, 640, 2560)])
+def test_residual_epilogue_bit_exact(ops, tile, dtype, m, n, k):
+    """T(T(T(acc * scale) + R) + bias): the feed-forward output linear of the SDXL block with its residual add fused;
+    also in place (C aliases R), which is how the reference's block calls it."""
+    a, b = _rand_int8(m, n, k, seed=5 * m + n)
+    g = torch.Generator().manual_seed(n)
+    alpha_col = (torch.rand(n, generator=g) * 1e-3 + 1e-4).float()
+    alpha_one = torch.tensor([0.0045], dtype=torch.float32)
+    bias = (torch.randn(n, generator=g) * 0.05).to(dtype)
+    res = torch.randn(m, n, generator=g).to(dtype)
+    acc = gemm.int8_gemm_acc(a, b)
+    c = torch.empty(m, n, dtype=dtype, device="cuda")
+    for bi in (None, bias):
+        ops.run_gemm_int8(cu(a), cu(b), cu(alpha_col), cu(alpha_one), c, bias=cu(bi), residual=cu(res))
+        want = gemm.int8_gemm(a, b, alpha_col, alpha_one, dtype, bias=bi, acc=acc, residual=res)
+        assert_bit_equal(c, want, "bias=%s" % (bi is not None))
+    inplace = cu(res).clone()
+    ops.run_gemm_int8(cu(a), cu(b), cu(alpha_col), cu(alpha_one), inplace, bias=cu(bias), residual=inplace)
+    assert_bit_equal(inplace, gemm.int8_gemm(a, b, alpha_col, alpha_one, dtype, bias=bias, acc=acc, residual=res), "in place")
+    check_status()
+
+
 def test_golden_vectors(ops, golden):
     z = golden("int8")
     m, k = z["qa"].shape

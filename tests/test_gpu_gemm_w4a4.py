@@ -171,6 +171,11 @@ def test_lora_up_added_after_the_groups(ops, m, n, k, dt):
     bound = torch.finfo(dt).eps * want.float().abs() + 2.0 ** -22 * terms
     assert bool((diff <= bound).all()), "worst = %g of the bound" % float((diff / bound).max())
     assert float((diff > 0).float().mean()) <= 1e-2
+    # the reference's caller converts act to T first and passes that: same bits
+    d2 = torch.empty_like(d)
+    ops.invoke_fused_w4a4_gemm_and_lora_up(d2, cu(quant.pack_int4(qa)), cu(quant.pack_int4(qw)), cu(act.to(dt)), cu(up), cu(sa),
+                                           cu(sb), bias=cu(bias))
+    assert_bit_equal(d2, got, "act already of type T")
 
 
 def test_lora_pointers_must_come_together(ops):
