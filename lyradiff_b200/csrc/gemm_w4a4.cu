@@ -19,10 +19,10 @@
 // 512 threads per CTA (sixteen warps, four per scheduler, hence at most 128 registers per thread), one persistent
 // CTA per SM:
 //   warp 0       TMA producer: packed A (128 x 64 B) and packed B (128 x 64 B) tiles, ring of 4 stages
-//   warp 1       MMA issuer
+//   warps 1, 15  MMA issuers: warp 1 issues the first group of every K block, warp 15 the second
 //   warp 2       scale loader: every four K blocks (8 groups) it transposes sa[m, g] and sb[n, g] of the tile into
 //                shared memory as [g][row] (ring of 3 slots), running ahead of the drain; also owns tensor memory
-//   warps 3, 12-14  expand nibbles -> swizzled int8 operand tiles (ring of 4 stages); warp 15 idles
+//   warps 3, 12-14  expand nibbles -> swizzled int8 operand tiles (ring of 4 stages)
 //   warps 4-11   drain: warp w reads TMEM lanes 32*(w%4).., columns 64*((w-4)/4)..; final epilogue
 // The optional low-rank branch (D += T(act)[m, 32] * up[n, 32]^T, the reference's lora_up_gemm, w4a4_gemm.cu:515-663,
 // with the fp32 -> T conversion of act that W4A4Gemm.cc:143 runs as a separate kernel folded in) rides the same
@@ -43,6 +43,25 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
 int device_sm_count();
 
 namespace w4 {
+
+// Optional instrumentation (-DLYRAQ_PROFILE_WAITS -DLYRAQ_W4_TIMERS): cycles per CTA that a role spends in its waits and
+// in total.  Slots: 3 expand wait-packed, 4 expand wait-stage-free, 5 expand total, 11 expand copy loop, 6 drain
+// wait-partial, 7 drain wait-scales, 8 drain total.  (The clock reads themselves slow the kernel noticeably.)
+#ifdef LYRAQ_PROFILE_WAITS
+static int g_w4_skip = 0;
+__device__ unsigned long long g_w4_prof[148 * 16];
+#endif
+#if defined(LYRAQ_PROFILE_WAITS) && defined(LYRAQ_W4_TIMERS)
+#define W4_DECL(name) long long name = 0
+#define W4_T0(t) const long long t = clock64()
+#define W4_ADD(acc, t) acc += clock64() - (t)
+#define W4_STORE(slot, v) g_w4_prof[blockIdx.x * 16 + (slot)] = (unsigned long long)(v)
+#else
+#define W4_DECL(name)
+#define W4_T0(t)
+#define W4_ADD(acc, t)
+#define W4_STORE(slot, v)
+#endif
 
 constexpr int kBM          = 128;
 constexpr int kBN          = 128;
@@ -80,6 +99,10 @@ struct Params {
     int           lora_act_is_f32;
     const void*   lora_up;       // [N, 32] of D's 16-bit type or null
     unsigned int* status;
+#ifdef LYRAQ_PROFILE_WAITS
+    int           skip;          // instrumentation: bit 0 = no nibble expansion, bit 1 = no drain work, bit 2 = no MMAs,
+                                 // bit 3 = no TMA loads, bit 4 = no scale loads
+#endif
 };
 
 constexpr int kLoraRank = 32;
@@ -191,7 +214,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         for (int s = 0; s < kUStages; ++s) {
             mbar_init(full_u(s), kExpandWarps);
-            mbar_init(empty_u(s), 1);   // MMA commit
+            mbar_init(empty_u(s), 2);   // one commit per MMA issuer
         }
         for (int b = 0; b < kPBufs; ++b) {
             mbar_init(part_full(b), 1);
@@ -236,9 +259,16 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         break;
                     }
                     const uint32_t dst = packed0 + stage * kPackedStage;
-                    mbar_arrive_expect_tx(full_p(stage), (uint32_t)kPackedStage);
-                    tma_load_2d(dst, &tmap_a, full_p(stage), kb * kPackedRowB, m_blk * kBM);
-                    tma_load_2d(dst + kPackedTile, &tmap_b, full_p(stage), kb * kPackedRowB, n_blk * kBN);
+#ifdef LYRAQ_PROFILE_WAITS
+                    if (p.skip & 8) {
+                        mbar_arrive(full_p(stage));
+                    } else
+#endif
+                    {
+                        mbar_arrive_expect_tx(full_p(stage), (uint32_t)kPackedStage);
+                        tma_load_2d(dst, &tmap_a, full_p(stage), kb * kPackedRowB, m_blk * kBM);
+                        tma_load_2d(dst + kPackedTile, &tmap_b, full_p(stage), kb * kPackedRowB, n_blk * kBN);
+                    }
                     ++issued;
                     if (++stage == kPStages) {
                         stage = 0;
@@ -263,74 +293,64 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 15) {
         if (lane == 0) {
-            // -------------------------------------------------------------- MMA issuer
-            int      ustage = 0;
-            uint32_t uphase = 0;
-            uint32_t gi = 0;
-            bool     ok = true;
+            // -------------------------------------------------------------- MMA issuers
+            // Every tcgen05 instruction and barrier operation costs its issuing thread tens of cycles, and one group is
+            // only 128 cycles of tensor work, so a single issuer would bound the kernel.  Two threads share the work:
+            // issuer i takes group i of every K block and owns the partial buffers i and i + 2; each commits the
+            // operand stage when its own MMAs are done (the stage's barrier counts both).
+            const int iss    = (warp == 1) ? 0 : 1;
+            int       ustage = 0;
+            uint32_t  uphase = 0;
+            uint32_t  n      = 0;  // groups this issuer has issued
+            bool      ok     = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                for (int kb = 0; ok && kb < num_kb; ++kb) {
+                const int steps = num_kb + (p.lora_act != nullptr ? 1 : 0);  // the low-rank step is issuer 0's
+                for (int kb = 0; ok && kb < steps; ++kb) {
                     if (!mbar_wait(full_u(ustage), uphase, abort_flag)) {
                         report_timeout(p.status, 0x1200u | (unsigned)ustage);
                         *abort_flag = 1;
                         ok = false;
                         break;
                     }
-                    tc_fence_after_sync();
-                    const uint32_t a_addr = ustage0 + ustage * kUStage;
-                    const uint64_t adesc  = umma_desc_k_sw128(a_addr);
-                    const uint64_t bdesc  = umma_desc_k_sw128(a_addr + kOperandTile);
-                    const int      groups = min(2, p.G - 2 * kb);
-                    for (int g = 0; g < groups; ++g, ++gi) {
-                        const int pb = (int)(gi % kPBufs);
-                        if (!mbar_wait(part_empty(pb), ((gi / kPBufs) & 1u) ^ 1u, abort_flag)) {
+                    const bool lora_step = (kb == num_kb);
+                    const int  groups    = lora_step ? 1 : min(2, p.G - 2 * kb);
+                    if (iss < groups) {
+                        const int pb = iss + 2 * (int)(n & 1u);
+                        if (!mbar_wait(part_empty(pb), ((n >> 1) & 1u) ^ 1u, abort_flag)) {
                             report_timeout(p.status, 0x1300u | (unsigned)pb);
                             *abort_flag = 1;
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
+                        const uint32_t a_addr = ustage0 + ustage * kUStage;
+                        const uint64_t adesc  = umma_desc_k_sw128(a_addr);
+                        const uint64_t bdesc  = umma_desc_k_sw128(a_addr + kOperandTile);
                         const uint32_t d_tmem = tmem_base + (uint32_t)(pb * kBN);
+                        if (lora_step) {
+                            // two K = 16 MMAs on 16-bit operands: the fp32 low-rank product
+                            const uint32_t idesc = umma_idesc(1u, p.c_dtype == LYRAQ_BF16 ? 1u : 0u, kBM, kBN);
 #pragma unroll
-                        for (int k = 0; k < 2; ++k) {
-                            const uint64_t koff = (uint64_t)((g * 2 + k) * 2);  // 32-byte K steps, in 16-byte units
-                            mma_i8(d_tmem, adesc + koff, bdesc + koff, kIdesc, (uint32_t)k);
+                            for (int k = 0; k < kLoraRank / 16; ++k) {
+                                mma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (uint32_t)k);
+                            }
+                        } else
+#ifdef LYRAQ_PROFILE_WAITS
+                        if (!(p.skip & 4))
+#endif
+                        {
+#pragma unroll
+                            for (int k = 0; k < 2; ++k) {
+                                const uint64_t koff = (uint64_t)((iss * 2 + k) * 2);  // 32-byte K steps, in 16-byte units
+                                mma_i8(d_tmem, adesc + koff, bdesc + koff, kIdesc, (uint32_t)k);
+                            }
                         }
                         tc_commit(part_full(pb));
+                        ++n;
                     }
-                    if (ok) {
-                        tc_commit(empty_u(ustage));
-                    }
-                    if (++ustage == kUStages) {
-                        ustage = 0;
-                        uphase ^= 1u;
-                    }
-                }
-                if (ok && p.lora_act != nullptr) {
-                    // low-rank step: two K = 16 MMAs on 16-bit operands into the next partial buffer (fp32)
-                    const int pb = (int)(gi % kPBufs);
-                    if (!mbar_wait(full_u(ustage), uphase, abort_flag) ||
-                        !mbar_wait(part_empty(pb), ((gi / kPBufs) & 1u) ^ 1u, abort_flag)) {
-                        report_timeout(p.status, 0x1900u | (unsigned)ustage);
-                        *abort_flag = 1;
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t a_addr = ustage0 + ustage * kUStage;
-                    const uint64_t adesc  = umma_desc_k_sw128(a_addr);
-                    const uint64_t bdesc  = umma_desc_k_sw128(a_addr + kOperandTile);
-                    const uint32_t idesc  = umma_idesc(1u, p.c_dtype == LYRAQ_BF16 ? 1u : 0u, kBM, kBN);
-                    const uint32_t d_tmem = tmem_base + (uint32_t)(pb * kBN);
-#pragma unroll
-                    for (int k = 0; k < kLoraRank / 16; ++k) {
-                        mma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (uint32_t)k);
-                    }
-                    tc_commit(part_full(pb));
                     tc_commit(empty_u(ustage));
-                    ++gi;
                     if (++ustage == kUStages) {
                         ustage = 0;
                         uphase ^= 1u;
@@ -360,6 +380,18 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int  g0   = sl * kSlotGroups;
                 const bool full = p.scale_vec_ok && (g0 + kSlotGroups <= p.G);
                 float      va[4][8], vb[4][8];
+#ifdef LYRAQ_PROFILE_WAITS
+                if (p.skip & 16) {
+#pragma unroll
+                    for (int rr = 0; rr < 4; ++rr) {
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            va[rr][g] = 1.0f;
+                            vb[rr][g] = 1.0f;
+                        }
+                    }
+                } else
+#endif
 #pragma unroll
                 for (int rr = 0; rr < 4; ++rr) {
                     const int    r    = lane + 32 * rr;
@@ -440,10 +472,18 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int       pstage = 0, ustage = 0;
         uint32_t  pphase = 0, uphase = 0;
         bool      ok = true;
+        W4_DECL(w_p);
+        W4_DECL(w_u);
+        W4_DECL(w_x);
+        W4_T0(t_all);
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
             for (int kb = 0; kb < num_kb; ++kb) {
+                W4_T0(t_w);
                 bool w = mbar_wait(full_p(pstage), pphase, abort_flag);
+                W4_ADD(w_p, t_w);
+                W4_T0(t_w2);
                 w      = w && mbar_wait(empty_u(ustage), uphase ^ 1u, abort_flag);
+                W4_ADD(w_u, t_w2);
                 if (!__all_sync(0xffffffffu, w)) {
                     if (lane == 0) {
                         report_timeout(p.status, 0x1400u | (unsigned)(pstage * 16 + ustage));
@@ -452,8 +492,12 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     ok = false;
                     break;
                 }
+                W4_T0(t_x);
                 const uint8_t* src = gen_base + (packed0 - smem_base) + pstage * kPackedStage + src_o;
                 uint8_t*       dst = gen_base + (ustage0 - smem_base) + ustage * kUStage;
+#ifdef LYRAQ_PROFILE_WAITS
+                if (!(p.skip & 1))
+#endif
 #pragma unroll
                 for (int it = 0; it < 8; ++it) {
                     // 32 rows further per step: 32 * 64 B in the packed tile, 4 * 1024 B in the operand tile;
@@ -467,6 +511,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     *reinterpret_cast<uint4*>(dst + it * 4096 + dst_ev) = ev;
                     *reinterpret_cast<uint4*>(dst + it * 4096 + dst_od) = od;
                 }
+                W4_ADD(w_x, t_x);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
@@ -534,6 +579,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
+#if defined(LYRAQ_PROFILE_WAITS) && defined(LYRAQ_W4_TIMERS)
+        if (tu == 0) {
+            W4_STORE(3, w_p);
+            W4_STORE(4, w_u);
+            W4_STORE(5, clock64() - t_all);
+            W4_STORE(11, w_x);
+        }
+#endif
     } else if (warp >= 4 && warp <= 11) {
         // ------------------------------------------------------------------ drain + epilogue (warps 4..11)
         const int      quad      = warp & 3;
@@ -543,8 +596,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const bool     vec_ok    = (p.c_dtype == LYRAQ_F32) ? ((p.N & 3) == 0) : ((p.N & 7) == 0);
         int            slot = 0;
         uint32_t       sphase = 0;
-        uint32_t       gi = 0;
+        uint32_t       n0 = 0, n1 = 0;  // groups drained per MMA issuer (issuer i: group i of a K block, buffers i, i + 2)
         bool           ok = true;
+        W4_DECL(w_pf);
+        W4_DECL(w_sc);
+        W4_T0(t_all);
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
             const int m_blk = tile % p.m_tiles;
             const int n_blk = tile / p.m_tiles;
@@ -555,7 +611,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             for (int kb = 0; ok && kb < num_kb; ++kb) {
                 if ((kb & 3) == 0) {
-                    if (!__all_sync(0xffffffffu, mbar_wait(sc_full(slot), sphase, abort_flag))) {
+                    W4_T0(t_w);
+                    const bool got_s = mbar_wait(sc_full(slot), sphase, abort_flag);
+                    W4_ADD(w_sc, t_w);
+                    if (!__all_sync(0xffffffffu, got_s)) {
                         if (lane == 0) {
                             report_timeout(p.status, 0x1600u | (unsigned)slot);
                         }
@@ -567,10 +626,17 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const float* sas    = reinterpret_cast<const float*>(gen_base + kScaleOffset + slot * kScaleSlot);
                 const float* sbs    = sas + kSlotGroups * kBM;
                 const int    groups = min(2, p.G - 2 * kb);
-                for (int g = 0; g < groups; ++g, ++gi) {
-                    const int pb = (int)(gi % kPBufs);
-                    const int gs = (kb & 3) * 2 + g;  // group index inside the scale slot
-                    if (!__all_sync(0xffffffffu, mbar_wait(part_full(pb), (gi / kPBufs) & 1u, abort_flag))) {
+#pragma unroll 1
+                for (int g = 0; g < groups; ++g) {
+                    const uint32_t nsel = g ? n1 : n0;
+                    const int      pb   = g + 2 * (int)(nsel & 1u);
+                    const int      gs   = (kb & 3) * 2 + g;  // group index inside the scale slot
+                    W4_T0(t_w2);
+                    const bool got_p = mbar_wait(part_full(pb), (nsel >> 1) & 1u, abort_flag);
+                    n0 += (g == 0) ? 1u : 0u;
+                    n1 += (g == 1) ? 1u : 0u;
+                    W4_ADD(w_pf, t_w2);
+                    if (!__all_sync(0xffffffffu, got_p)) {
                         if (lane == 0) {
                             report_timeout(p.status, 0x1700u | (unsigned)pb);
                         }
@@ -581,19 +647,23 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     tc_fence_after_sync();
                     const float  sa_s = sas[gs * kBM + trow];
                     const float2 sa_v = make_float2(sa_s, sa_s);
+                    const uint32_t t_addr = tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64);
+#ifdef LYRAQ_PROFILE_WAITS
+                    if (!(p.skip & 2))
+#endif
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        uint32_t part[16];
-                        tmem_ld_32x16(tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64 + c * 16), part);
+                        uint32_t pc[16];
+                        tmem_ld_32x16(t_addr + (uint32_t)(c * 16), pc);
                         tmem_ld_wait();
-                        const float4* sb4 = reinterpret_cast<const float4*>(sbs + gs * kBN + half * 64 + c * 16);
+                        const float4*   sb4 = reinterpret_cast<const float4*>(sbs + gs * kBN + half * 64 + c * 16);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const float4 s = sb4[j];
                             // acc = fma(float(p) * sa, sb, acc): the contraction the reference's compiler makes of
                             // `acc += float(p) * sa * sb` (w4a4_gemm.cu:504-507); two columns per instruction
-                            const float2 p0 = make_float2((float)(int)part[4 * j], (float)(int)part[4 * j + 1]);
-                            const float2 p1 = make_float2((float)(int)part[4 * j + 2], (float)(int)part[4 * j + 3]);
+                            const float2 p0 = make_float2((float)(int)pc[4 * j], (float)(int)pc[4 * j + 1]);
+                            const float2 p1 = make_float2((float)(int)pc[4 * j + 2], (float)(int)pc[4 * j + 3]);
                             acc[c * 8 + 2 * j]     = fma_f32x2(mul_f32x2(p0, sa_v), make_float2(s.x, s.y), acc[c * 8 + 2 * j]);
                             acc[c * 8 + 2 * j + 1] = fma_f32x2(mul_f32x2(p1, sa_v), make_float2(s.z, s.w), acc[c * 8 + 2 * j + 1]);
                         }
@@ -616,8 +686,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
             if (ok && p.lora_act != nullptr) {
-                const int pb = (int)(gi % kPBufs);
-                if (!__all_sync(0xffffffffu, mbar_wait(part_full(pb), (gi / kPBufs) & 1u, abort_flag))) {
+                const int pb = 2 * (int)(n0 & 1u);
+                if (!__all_sync(0xffffffffu, mbar_wait(part_full(pb), (n0 >> 1) & 1u, abort_flag))) {
                     if (lane == 0) {
                         report_timeout(p.status, 0x1b00u | (unsigned)pb);
                     }
@@ -640,7 +710,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     if (lane == 0) {
                         mbar_arrive(part_empty(pb));
                     }
-                    ++gi;
+                    ++n0;
                 }
             }
             if (!ok) {
@@ -664,6 +734,13 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
+#if defined(LYRAQ_PROFILE_WAITS) && defined(LYRAQ_W4_TIMERS)
+        if (threadIdx.x == 128) {
+            W4_STORE(6, w_pf);
+            W4_STORE(7, w_sc);
+            W4_STORE(8, clock64() - t_all);
+        }
+#endif
     }
 
     tc_fence_before_sync();
@@ -678,6 +755,18 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }  // namespace lyraq
 
 using namespace lyraq;
+
+#ifdef LYRAQ_PROFILE_WAITS
+extern "C" __attribute__((visibility("default"))) int lyraq_debug_set_w4_skip(int mask)
+{
+    w4::g_w4_skip = mask;
+    return LYRAQ_OK;
+}
+extern "C" __attribute__((visibility("default"))) int lyraq_debug_read_w4_profile(unsigned long long* host, int n_words)
+{
+    return cuda_status(cudaMemcpyFromSymbol(host, w4::g_w4_prof, sizeof(unsigned long long) * (size_t)n_words), "read w4 profile");
+}
+#endif
 
 extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* sa, const void* sb, int sb_dtype, void* D,
                                int c_dtype, const void* lora_act, int lora_act_dtype, const void* lora_up, const void* bias,
@@ -735,6 +824,9 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     p.lora_act  = lora_act;
     p.lora_act_is_f32 = (lora_act_dtype == LYRAQ_F32) ? 1 : 0;
     p.lora_up   = lora_up;
+#ifdef LYRAQ_PROFILE_WAITS
+    p.skip      = w4::g_w4_skip;
+#endif
     p.status    = status_word_ptr();
     if (p.status == nullptr) {
         return LYRAQ_ERR_CUDA;

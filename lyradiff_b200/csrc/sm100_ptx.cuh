@@ -59,21 +59,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 // caller records the failure, raises the block's abort flag and leaves its loop, so that a
 // mis-programmed pipeline ends with an error status instead of holding the GPU.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr unsigned kPollSleepNs = 32;
 
 // Bounded wait on an mbarrier phase.  Returns false if the limit ran out or another role of the
 // block already gave up (abort flag in shared memory).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
 {
-    if (mbar_try_wait(bar, parity)) {
-        return true;
+    // The common case ends within the first polls.  Reading %globaltimer is slow, so the clock is first looked at
+    // only after a batch of failed polls (the limit then counts from that moment) and once per batch afterwards.
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+        if (mbar_try_wait(bar, parity)) {
+            return true;
+        }
+        __nanosleep(kPollSleepNs);  // a polling warp is always ready to issue and would take slots from the working warps
     }
     const uint64_t t0 = global_timer_ns();
     for (;;) {
 #pragma unroll 1
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < 256; ++i) {
             if (mbar_try_wait(bar, parity)) {
                 return true;
             }
+            __nanosleep(kPollSleepNs);
         }
         if (*abort_flag != 0) {
             return false;
