@@ -94,10 +94,16 @@ struct GemmParams {
 // BLOCK_N is the width of the output tile; CTAS = 1: one CTA computes 128 x BLOCK_N; CTAS = 2: a pair of CTAs
 // computes 256 x BLOCK_N with cta_group::2 MMAs, each CTA staging 128 A rows and BLOCK_N / 2 B rows per K block.
 template<int BLOCK_N, int CTAS> struct GemmSmem {
-    static constexpr int kABytes     = kBlockM * kBlockK;
-    static constexpr int kBBytes     = (BLOCK_N / CTAS) * kBlockK;
+    // A stage of a CTA pair, or of the 128-wide tile, holds two K blocks: issuing a tcgen05 instruction costs the single
+    // MMA thread about 50 cycles and a stage adds a barrier wait and one or two commits, so with stages of four MMAs the
+    // issue loop, not the tensor pipe, set the pace (86 % of the MMA rate for pairs); eight MMAs per stage hide it.
+    static constexpr int kSub        = (CTAS == 2 || BLOCK_N == 128) ? 2 : 1;
+    static constexpr int kASub       = kBlockM * kBlockK;
+    static constexpr int kBSub       = (BLOCK_N / CTAS) * kBlockK;
+    static constexpr int kABytes     = kASub * kSub;
+    static constexpr int kBBytes     = kBSub * kSub;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages     = (kSmemBudget - 1024 - kBarBytes - kEpiSmem) / kStageBytes;  // 4 (1 x 256) or 6
+    static constexpr int kStages     = (kSmemBudget - 1024 - kBarBytes - kEpiSmem) / kStageBytes;  // 4 (1 x 256), 6 (1 x 128) or 3 double stages (pair)
     static constexpr int kEpiOffset  = kStages * kStageBytes;           // 1024-aligned: stage sizes are multiples of 16 KB
     static constexpr int kBarOffset  = kEpiOffset + kEpiSmem;
     static constexpr int kTotal      = kBarOffset + kBarBytes + 1024;   // + alignment slack
@@ -355,7 +361,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tile_coords(tile, p.m_tiles, p.n_tiles, m_blk, n_blk);
             const int a_row = m_blk * kTileM + (int)rank * kBlockM;
             const int b_row = n_blk * BLOCK_N + (int)rank * (BLOCK_N / CTAS);
-            for (int kb = 0; kb < num_kb; ++kb) {
+            for (int kb = 0; kb < num_kb; kb += S::kSub) {
                 PROF_T0(t_w);
                 if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                     report_timeout(p.status, 0x100u | (unsigned)stage);
@@ -377,12 +383,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (leader) {
                         mbar_arrive_expect_tx(full_bar(stage), 2u * (uint32_t)S::kStageBytes);
                     }
-                    tma_load_2d_pair(smem_a + stage * S::kABytes, &tmap_a, lbar, kb * kBlockK, a_row);
-                    tma_load_2d_pair(smem_b + stage * S::kBBytes, &tmap_b, lbar, kb * kBlockK, b_row);
+#pragma unroll
+                    for (int sub = 0; sub < S::kSub; ++sub) {
+                        // a K block past the end of K is all zero fill (and still counts its bytes on the barrier)
+                        tma_load_2d_pair(smem_a + stage * S::kABytes + sub * S::kASub, &tmap_a, lbar, (kb + sub) * kBlockK, a_row);
+                        tma_load_2d_pair(smem_b + stage * S::kBBytes + sub * S::kBSub, &tmap_b, lbar, (kb + sub) * kBlockK, b_row);
+                    }
                 } else {
                     mbar_arrive_expect_tx(full_bar(stage), (uint32_t)S::kStageBytes);
-                    tma_load_2d(smem_a + stage * S::kABytes, &tmap_a, full_bar(stage), kb * kBlockK, a_row);
-                    tma_load_2d(smem_b + stage * S::kBBytes, &tmap_b, full_bar(stage), kb * kBlockK, b_row);
+#pragma unroll
+                    for (int sub = 0; sub < S::kSub; ++sub) {
+                        tma_load_2d(smem_a + stage * S::kABytes + sub * S::kASub, &tmap_a, full_bar(stage), (kb + sub) * kBlockK, a_row);
+                        tma_load_2d(smem_b + stage * S::kBBytes + sub * S::kBSub, &tmap_b, full_bar(stage), (kb + sub) * kBlockK, b_row);
+                    }
                 }
                 ++issued;
                 if (++stage == kStages) {
@@ -441,7 +454,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             PROF_ADD(w_tmem, t_w0);
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BLOCK_N);
-            for (int kb = 0; kb < num_kb; ++kb) {
+            for (int kb = 0; kb < num_kb; kb += S::kSub) {
                 PROF_T0(t_w1);
                 if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                     report_timeout(p.status, 0x300u | (unsigned)stage);
@@ -451,13 +464,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
                 PROF_ADD(w_full, t_w1);
                 tc_fence_after_sync();
-                const uint64_t adesc = umma_desc_k_sw128(smem_a + stage * S::kABytes);
-                const uint64_t bdesc = umma_desc_k_sw128(smem_b + stage * S::kBBytes);
 #pragma unroll
-                for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                for (int sk = 0; sk < S::kSub * (kBlockK / kUmmaK); ++sk) {
+                    const int      sub   = sk / (kBlockK / kUmmaK);
+                    const int      k     = sk % (kBlockK / kUmmaK);
+                    const uint64_t adesc = umma_desc_k_sw128(smem_a + stage * S::kABytes + sub * S::kASub);
+                    const uint64_t bdesc = umma_desc_k_sw128(smem_b + stage * S::kBBytes + sub * S::kBSub);
                     // advancing K by 32 bytes inside the swizzled 128-byte row: +2 in 16-byte units
                     const uint64_t koff = (uint64_t)(k * (kUmmaK >> 4));
-                    const uint32_t acc  = (kb > 0 || k > 0) ? 1u : 0u;
+                    const uint32_t acc  = (kb > 0 || sk > 0) ? 1u : 0u;
                     if (CTAS == 2) {
                         if (KIND == KIND_I8) {
                             mma_i8_pair(d_tmem, adesc + koff, bdesc + koff, kIdesc, acc);
