@@ -487,6 +487,9 @@ def run_ours(case, args, rank, world, local_rank):
         if status != 0:
             raise SystemExit("bench.py: device status %d (detail 0x%x)" % (status, detail))
 
+    if args.no_dependent_launch:
+        from lyradiff_b200 import _lib as _l
+        _l.check(_l.lib().lyraq_debug_set_dependent_launch(0), "lyraq_debug_set_dependent_launch")
     if args.tile:
         from lyradiff_b200 import _lib
         _lib.check(_lib.lib().lyraq_debug_force_gemm_tile(args.tile), "lyraq_debug_force_gemm_tile")
@@ -597,6 +600,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the number of token rows (0 = the configuration's own)")
     ap.add_argument("--tile", type=int, default=0, choices=[0, 2561, 1281, 2562],
                     help="force the dense-GEMM tile configuration (0 = automatic; see lyraq_debug_force_gemm_tile)")
+    ap.add_argument("--no-dependent-launch", action="store_true",
+                    help="launch the kernels as ordinary stream-ordered kernels (see lyraq_debug_set_dependent_launch)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

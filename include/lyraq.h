@@ -68,6 +68,12 @@ LYRAQ_API int lyraq_last_status(void* stream, uint32_t* detail);
  * (check_cuda_error, src/lyradiff/utils/cuda_utils.h:62-90); this is the same information as a string. */
 LYRAQ_API const char* lyraq_last_cuda_error(void);
 
+/* Debug / measurement hook (no counterpart in the reference): every kernel of the library is launched so that it may
+ * begin while the kernel before it on the stream is still draining (programmatic dependent launch: the kernel's
+ * set-up overlaps its predecessor's tail, and it waits for the predecessor's completion before it first touches
+ * global memory).  on = 0 launches them as ordinary stream-ordered kernels instead; on = 1 (default) restores it. */
+LYRAQ_API int lyraq_debug_set_dependent_launch(int on);
+
 /* Test / sweep hook: force the tile configuration of the dense GEMMs.  0 = automatic (default); 2561 = one CTA,
  * 128 x 256 tile; 1281 = one CTA, 128 x 128; 2562 = CTA pair, 256 x 256.  Process-wide, not thread-safe.
  * No counterpart in the reference API; it plays the role of choosing a tactic by hand, which the reference does

@@ -33,9 +33,18 @@ void record_cuda_error(cudaError_t e, const char* where)
     snprintf(g_last_error, sizeof(g_last_error), "%s: %s (%s)", where, cudaGetErrorString(e), cudaGetErrorName(e));
 }
 
+static int g_dependent_launch = 1;
+bool dependent_launch_enabled() { return g_dependent_launch != 0; }
+
 }  // namespace lyraq
 
 extern "C" {
+
+int lyraq_debug_set_dependent_launch(int on)
+{
+    lyraq::g_dependent_launch = on ? 1 : 0;
+    return LYRAQ_OK;
+}
 
 const char* lyraq_last_cuda_error(void) { return lyraq::g_last_error; }
 

@@ -310,4 +310,44 @@ inline int cuda_status(cudaError_t e, const char* where = "cuda call")
 
 inline int launch_status() { return cuda_status(cudaGetLastError(), "kernel launch"); }
 
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of the library tells the scheduler at its start that the next kernel
+// of the stream may begin launching (grid_launch_dependents), and waits for the kernels before it to have completed,
+// with their writes visible, before its first access to global memory (grid_dependency_wait).  A kernel's set-up
+// (barrier initialisation, tensor-memory allocation, descriptor prefetch) and its launch latency then overlap the
+// tail of its predecessor instead of following it.  Both instructions do nothing when the launch carries no such
+// dependency.  lyraq_debug_set_dependent_launch(0) turns the launch attribute off.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool dependent_launch_enabled();  // api.cu
+
+template<typename Kernel, typename... Args>
+inline cudaError_t launch_kernel(Kernel kernel, unsigned grid, unsigned block, size_t smem, cudaStream_t stream,
+                                 unsigned cluster_x, Args... args)
+{
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim          = dim3(grid, 1, 1);
+    cfg.blockDim         = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream           = stream;
+    cudaLaunchAttribute attr[2];
+    unsigned            n = 0;
+    if (cluster_x > 1) {
+        attr[n].id               = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    if (dependent_launch_enabled()) {
+        attr[n].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    cfg.attrs    = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 }  // namespace lyraq

@@ -307,6 +307,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const int      unit    = (CTAS == 2) ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;  // CTA or CTA pair
     const int      n_units = (CTAS == 2) ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
+    grid_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full_bar(s), 1);
@@ -339,6 +340,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dependency_wait();  // everything above overlapped the previous kernel's tail; global memory is touched from here on
 
     const int num_tiles = p.m_tiles * p.n_tiles;
     const int num_kb    = (p.K + kBlockK - 1) / kBlockK;
@@ -967,19 +969,8 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
     if (attr_err != cudaSuccess) {
         return cuda_status(attr_err, "cudaFuncSetAttribute(gemm_tcgen05_kernel, dynamic shared memory)");
     }
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim          = dim3((unsigned)grid, 1, 1);
-    cfg.blockDim         = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = S::kTotal;
-    cfg.stream           = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id               = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = CTAS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs    = attr;
-    cfg.numAttrs = (CTAS > 1) ? 1 : 0;
-    return cuda_status(cudaLaunchKernelEx(&cfg, kern, ta, tb, tc, p), "cudaLaunchKernelEx(gemm_tcgen05_kernel)");
+    return cuda_status(launch_kernel(kern, (unsigned)grid, (unsigned)kThreads, (size_t)S::kTotal, stream, (unsigned)CTAS, ta, tb, tc, p),
+                       "cudaLaunchKernelEx(gemm_tcgen05_kernel)");
 }
 
 // forced tile configuration for tests and sweeps: 0 = automatic, else block_n * 10 + ctas (2561, 1281, 2562)

@@ -207,6 +207,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    grid_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPStages; ++s) {
             mbar_init(full_p(s), 1);
@@ -237,6 +238,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dependency_wait();
 
     const int num_tiles = p.m_tiles * p.n_tiles;
     const int num_kb    = (p.K + kKBlock - 1) / kKBlock;
@@ -851,6 +853,7 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     if (attr_err != cudaSuccess) {
         return cuda_status(attr_err, "cudaFuncSetAttribute(gemm_w4a4_kernel, dynamic shared memory)");
     }
-    w4::gemm_w4a4_kernel<<<grid, w4::kThreads, w4::kSmemTotal, (cudaStream_t)stream>>>(ta, tb, p);
-    return launch_status();
+    return cuda_status(launch_kernel(w4::gemm_w4a4_kernel, (unsigned)grid, (unsigned)w4::kThreads, (size_t)w4::kSmemTotal,
+                                     (cudaStream_t)stream, 1u, ta, tb, p),
+                       "cudaLaunchKernelEx(gemm_w4a4_kernel)");
 }

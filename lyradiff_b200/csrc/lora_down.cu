@@ -59,6 +59,7 @@ lora_down_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
+    grid_launch_dependents();
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full_bar(s), 1);
@@ -78,6 +79,7 @@ lora_down_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    grid_dependency_wait();
 
     const int num_kb = (p.k * 2 + kBlockKB - 1) / kBlockKB;
     const int row0   = blockIdx.x * kRows;
@@ -215,8 +217,9 @@ int launch_lora_down(float* act, const void* x, const void* down, int dtype, siz
         return cuda_status(attr_err, "cudaFuncSetAttribute(lora_down_kernel, dynamic shared memory)");
     }
     const unsigned grid = (unsigned)((m + lora::kRows - 1) / lora::kRows);
-    lora::lora_down_kernel<<<grid, lora::kThreads, lora::kSmemTotal, stream>>>(tx, td, p);
-    return launch_status();
+    return cuda_status(launch_kernel(lora::lora_down_kernel, grid, (unsigned)lora::kThreads, (size_t)lora::kSmemTotal, stream, 1u,
+                                     tx, td, p),
+                       "cudaLaunchKernelEx(lora_down_kernel)");
 }
 
 }  // namespace lyraq

@@ -82,6 +82,8 @@ __global__ void __launch_bounds__(256, (VPT <= 4) ? 3 : (VPT <= 6) ? 2 : 1) row_
     using P2 = Pair<T>;
     __shared__ float red[8];
 
+    grid_launch_dependents();
+    grid_dependency_wait();
     const int    tpr    = p.tpr;
     const int    team   = threadIdx.x / tpr;
     const int    tlane  = threadIdx.x - team * tpr;
@@ -338,8 +340,7 @@ template<typename K> static int launch_row_variant(K kernel, const RowParams& p,
     }
     const size_t resident = (size_t)per_sm * (size_t)sms;
     const size_t grid     = needed < resident ? needed : resident;
-    kernel<<<(unsigned)grid, 256, 0, stream>>>(p);
-    return launch_status();
+    return cuda_status(launch_kernel(kernel, (unsigned)grid, 256u, (size_t)0, stream, 1u, p), "cudaLaunchKernelEx(row_quant_kernel)");
 }
 
 // Most 16-byte vectors a thread may hold before the team is doubled (4 or 6; sweepable through the debug hook).
@@ -393,6 +394,8 @@ template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaSt
 template<typename T>
 __global__ void __launch_bounds__(256) fp8_cast_kernel(uint8_t* dst, const T* src, const float* scale, int invert, size_t n)
 {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const float  s      = __ldg(scale);
     const float  r      = invert ? 1.0f / s : s;
     const size_t nvec   = n >> 3;
@@ -432,6 +435,8 @@ __global__ void __launch_bounds__(256) fp8_cast_kernel(uint8_t* dst, const T* sr
 template<typename T> __global__ void __launch_bounds__(256) fp8_amax_kernel(float* scale, const T* src, size_t n)
 {
     __shared__ float red[8];
+    grid_launch_dependents();
+    grid_dependency_wait();
     const size_t     nvec   = n >> 3;
     const size_t     stride = (size_t)gridDim.x * blockDim.x;
     float            amax   = 0.0f;
@@ -459,6 +464,8 @@ template<typename T, typename ST>
 __global__ void __launch_bounds__(256)
 int4_g64_kernel(uint32_t* q, ST* q_scale, const T* x, const float* smooth, size_t rows, int k)
 {
+    grid_launch_dependents();
+    grid_dependency_wait();
     const size_t nvec_total = rows * (size_t)(k >> 3);
     const size_t stride     = (size_t)gridDim.x * blockDim.x;
     const int    vec_per_row = k >> 3;
@@ -516,6 +523,8 @@ __global__ void __launch_bounds__(256)
 int8_weight_quant_kernel(float* w_scale, int8_t* qw, const T* w, const float* pre, size_t d_in)
 {
     __shared__ float red[8];
+    grid_launch_dependents();
+    grid_dependency_wait();
     const size_t     row  = blockIdx.x;
     const T*         wrow = w + row * d_in;
     float            amax = 0.0f;
@@ -608,10 +617,9 @@ int lyraq_quant_fp8(uint8_t* dst, const void* src, int src_dtype, const float* s
     }
     const unsigned grid = flat_grid(n >> 3);
     if (src_dtype == LYRAQ_F16) {
-        fp8_cast_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>(dst, (const __half*)src, scale, invert_scale, n);
+        launch_kernel(fp8_cast_kernel<__half>, (unsigned)(grid), 256u, (size_t)0, (cudaStream_t)stream, 1u, dst, (const __half*)src, scale, invert_scale, n);
     } else if (src_dtype == LYRAQ_BF16) {
-        fp8_cast_kernel<__nv_bfloat16>
-            <<<grid, 256, 0, (cudaStream_t)stream>>>(dst, (const __nv_bfloat16*)src, scale, invert_scale, n);
+        launch_kernel(fp8_cast_kernel<__nv_bfloat16>, (unsigned)(grid), 256u, (size_t)0, (cudaStream_t)stream, 1u, dst, (const __nv_bfloat16*)src, scale, invert_scale, n);
     } else {
         return LYRAQ_ERR_UNSUPPORTED;
     }
@@ -628,9 +636,9 @@ int lyraq_fp8_amax_scale(float* scale, const void* w, int w_dtype, size_t n, voi
     }
     const unsigned grid = flat_grid(n >> 3);
     if (w_dtype == LYRAQ_F16) {
-        fp8_amax_kernel<__half><<<grid, 256, 0, (cudaStream_t)stream>>>(scale, (const __half*)w, n);
+        launch_kernel(fp8_amax_kernel<__half>, (unsigned)(grid), 256u, (size_t)0, (cudaStream_t)stream, 1u, scale, (const __half*)w, n);
     } else if (w_dtype == LYRAQ_BF16) {
-        fp8_amax_kernel<__nv_bfloat16><<<grid, 256, 0, (cudaStream_t)stream>>>(scale, (const __nv_bfloat16*)w, n);
+        launch_kernel(fp8_amax_kernel<__nv_bfloat16>, (unsigned)(grid), 256u, (size_t)0, (cudaStream_t)stream, 1u, scale, (const __nv_bfloat16*)w, n);
     } else {
         return LYRAQ_ERR_UNSUPPORTED;
     }
@@ -650,10 +658,9 @@ int lyraq_weight_quant_int8(float* w_scale, int8_t* qw, const void* w, int w_dty
         return LYRAQ_ERR_UNSUPPORTED;
     }
     if (w_dtype == LYRAQ_F16) {
-        int8_weight_quant_kernel<__half>
-            <<<(unsigned)d_out, 256, 0, (cudaStream_t)stream>>>(w_scale, qw, (const __half*)w, pre_quant_scale, d_in);
+        launch_kernel(int8_weight_quant_kernel<__half>, (unsigned)((unsigned)d_out), 256u, (size_t)0, (cudaStream_t)stream, 1u, w_scale, qw, (const __half*)w, pre_quant_scale, d_in);
     } else if (w_dtype == LYRAQ_BF16) {
-        int8_weight_quant_kernel<__nv_bfloat16><<<(unsigned)d_out, 256, 0, (cudaStream_t)stream>>>(
+        launch_kernel(int8_weight_quant_kernel<__nv_bfloat16>, (unsigned)((unsigned)d_out), 256u, (size_t)0, (cudaStream_t)stream, 1u, 
             w_scale, qw, (const __nv_bfloat16*)w, pre_quant_scale, d_in);
     } else {
         return LYRAQ_ERR_UNSUPPORTED;
@@ -682,15 +689,13 @@ static int int4_g64_dispatch(uint8_t* q, void* q_scale, int scale_dtype, const v
     const unsigned grid = flat_grid(rows * (k >> 3));
     uint32_t*      qo   = reinterpret_cast<uint32_t*>(q);
     if (x_dtype == LYRAQ_BF16 && scale_dtype == LYRAQ_F32) {
-        int4_g64_kernel<__nv_bfloat16, float>
-            <<<grid, 256, 0, stream>>>(qo, (float*)q_scale, (const __nv_bfloat16*)x, smooth, rows, (int)k);
+        launch_kernel(int4_g64_kernel<__nv_bfloat16, float>, (unsigned)(grid), 256u, (size_t)0, stream, 1u, qo, (float*)q_scale, (const __nv_bfloat16*)x, smooth, rows, (int)k);
     } else if (x_dtype == LYRAQ_F16 && scale_dtype == LYRAQ_F32) {
-        int4_g64_kernel<__half, float><<<grid, 256, 0, stream>>>(qo, (float*)q_scale, (const __half*)x, smooth, rows, (int)k);
+        launch_kernel(int4_g64_kernel<__half, float>, (unsigned)(grid), 256u, (size_t)0, stream, 1u, qo, (float*)q_scale, (const __half*)x, smooth, rows, (int)k);
     } else if (x_dtype == LYRAQ_BF16 && scale_dtype == LYRAQ_F16) {
-        int4_g64_kernel<__nv_bfloat16, __half>
-            <<<grid, 256, 0, stream>>>(qo, (__half*)q_scale, (const __nv_bfloat16*)x, smooth, rows, (int)k);
+        launch_kernel(int4_g64_kernel<__nv_bfloat16, __half>, (unsigned)(grid), 256u, (size_t)0, stream, 1u, qo, (__half*)q_scale, (const __nv_bfloat16*)x, smooth, rows, (int)k);
     } else if (x_dtype == LYRAQ_F16 && scale_dtype == LYRAQ_F16) {
-        int4_g64_kernel<__half, __half><<<grid, 256, 0, stream>>>(qo, (__half*)q_scale, (const __half*)x, smooth, rows, (int)k);
+        launch_kernel(int4_g64_kernel<__half, __half>, (unsigned)(grid), 256u, (size_t)0, stream, 1u, qo, (__half*)q_scale, (const __half*)x, smooth, rows, (int)k);
     } else {
         return LYRAQ_ERR_UNSUPPORTED;
     }
