@@ -107,6 +107,12 @@ LYRAQ_API int lyraq_quant_fp8(uint8_t* dst, const void* src, int src_dtype, cons
  * Replaces invokeGetFP8WeightScale (src/lyradiff/kernels/lora/load_lora.cu:49-54,109-113). */
 LYRAQ_API int lyraq_fp8_amax_scale(float* scale, const void* w, int w_dtype, size_t n, void* stream);
 
+/* FP8 weight quantize in one call, all on `stream` and without a host round trip: scale[0] = max|w| / 448, then
+ * qw = e4m3(w / scale[0]).  What MACROLoadFP8WeightFromCache does with a memset, invokeGetFP8WeightScale and
+ * invokeCudaD2DScaleCpyConvert (src/lyradiff/utils/common_macro_def.h:76-92), and what a LoRA swap repeats for every
+ * merged weight (src/lyradiff/interface/IFLoraWeight.h:80-128). */
+LYRAQ_API int lyraq_weight_quant_fp8(uint8_t* qw, float* scale, const void* w, int w_dtype, size_t n, void* stream);
+
 /* INT4 activation quantize, groups of 64 along K: v = float(x)/smooth[c]; s = max|v|/7; q = sat_s4(rne(v/s)).
  * q: packed [m, k/2] bytes (even element in the low nibble), q_scale: fp32 [m, k/64].
  * Replaces the quantize half of invokeFusedQuantizeAndLoraDownSimple

@@ -25,6 +25,7 @@ SIGNATURES = {
     "lyraq_quant_int8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_void_p]),
     "lyraq_quant_fp8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p]),
     "lyraq_fp8_amax_scale": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p]),
+    "lyraq_weight_quant_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_void_p]),
     "lyraq_quant_int4_g64": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t,
                                      c_size_t, c_void_p]),
     "lyraq_weight_quant_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t, c_size_t, c_void_p]),

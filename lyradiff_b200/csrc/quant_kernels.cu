@@ -645,6 +645,25 @@ int lyraq_fp8_amax_scale(float* scale, const void* w, int w_dtype, size_t n, voi
     return launch_status();
 }
 
+int lyraq_weight_quant_fp8(uint8_t* qw, float* scale, const void* w, int w_dtype, size_t n, void* stream)
+{
+    if (n == 0) {
+        return LYRAQ_OK;
+    }
+    if (qw == nullptr || scale == nullptr || w == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    const cudaError_t e = cudaMemsetAsync(scale, 0, sizeof(float), (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        return cuda_status(e, "cudaMemsetAsync(weight scale)");
+    }
+    const int st = lyraq_fp8_amax_scale(scale, w, w_dtype, n, stream);
+    if (st != LYRAQ_OK) {
+        return st;
+    }
+    return lyraq_quant_fp8(qw, w, w_dtype, scale, 1, n, stream);
+}
+
 int lyraq_weight_quant_int8(float* w_scale, int8_t* qw, const void* w, int w_dtype, const float* pre_quant_scale,
                             size_t d_out, size_t d_in, void* stream)
 {

@@ -28,10 +28,9 @@ class Fp8Linear:
         n, k = weight.shape
         dev = weight.device
         self.n, self.k, self.gelu = n, k, gelu
-        self.w_scale = torch.zeros(1, dtype=torch.float32, device=dev)
-        ops.invoke_get_fp8_weight_scale(self.w_scale, weight.contiguous())
+        self.w_scale = torch.empty(1, dtype=torch.float32, device=dev)
         self.qweight = torch.empty(n, k, dtype=torch.uint8, device=dev)
-        ops.invoke_cuda_d2d_scale_cpy_convert(self.qweight, weight.contiguous(), self.w_scale)
+        ops.weight_quant_fp8(self.qweight, self.w_scale, weight.contiguous())
         self.bias = None if bias is None else bias.contiguous()
         self.input_scale = input_scale.to(device=dev, dtype=torch.float32).reshape(1).contiguous()
         self._ws = None

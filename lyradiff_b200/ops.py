@@ -73,6 +73,14 @@ def invoke_get_fp8_weight_scale(scale, weight):
     return scale
 
 
+def weight_quant_fp8(qw, scale, weight):
+    """MACROLoadFP8WeightFromCache (src/lyradiff/utils/common_macro_def.h:76-92) in one call: scale = max|w|/448 and
+    qw = e4m3(w / scale), stream-ordered."""
+    st = _lib.lib().lyraq_weight_quant_fp8(_p(qw), _p(scale), _p(weight), _dt(weight), weight.numel(), _stream())
+    _lib.check(st, "lyraq_weight_quant_fp8")
+    return qw, scale
+
+
 def invoke_get_int8_weight_scale(new_weight_scale, quantized_weight, weight, pre_quant_scale):
     """invokeGetINT8WeightScale<T> (src/lyradiff/kernels/quant_kernels/quant_kernels.cu:270-312)."""
     d_out, d_in = weight.shape

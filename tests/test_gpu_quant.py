@@ -95,6 +95,19 @@ def test_fp8_weight_amax_scale_exact(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fp8_weight_quant_in_one_call(ops, dtype):
+    """scale = max|w|/448 and e4m3(w/scale) from a stale scale buffer and a stale output, with no host step between."""
+    g = torch.Generator().manual_seed(6)
+    w = (torch.randn(640, 1288, generator=g) * 0.02).to(dtype)
+    s = torch.full((1,), 123.0, dtype=torch.float32, device="cuda")
+    q = torch.full((640, 1288), 0x7F, dtype=torch.uint8, device="cuda")
+    ops.weight_quant_fp8(q, s, cu(w))
+    want_s = quant.fp8_amax_scale(w)
+    assert_bit_equal(s, want_s)
+    assert_bit_equal(q, quant.fp8_quant(w, want_s, invert_scale=True))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("m,k", [(1, 64), (24, 128), (130, 3072), (5, 12288)])
 def test_int4_g64_quant_bit_exact(ops, dtype, m, k):
     g = torch.Generator().manual_seed(m * 7 + k)
