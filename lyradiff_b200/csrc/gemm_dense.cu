@@ -358,12 +358,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             ok = false;  // with bit 2 the peer gets no per-stage signal, so its producer must not wait for one
         }
 #endif
-        for (int tile = unit; ok && tile < num_tiles; tile += n_units) {
+        // Every other tile of a CTA walks K from the far end: the K slices a wave touched last are the ones the next wave
+        // asks for first, so for a deep K they are still in L2 instead of being fetched from HBM once per wave.
+        const int kb_far = ((num_kb - 1) / S::kSub) * S::kSub;
+        bool      flip   = false;
+        for (int tile = unit; ok && tile < num_tiles; tile += n_units, flip = !flip) {
             int m_blk, n_blk;
             tile_coords(tile, p.m_tiles, p.n_tiles, m_blk, n_blk);
             const int a_row = m_blk * kTileM + (int)rank * kBlockM;
             const int b_row = n_blk * BLOCK_N + (int)rank * (BLOCK_N / CTAS);
-            for (int kb = 0; kb < num_kb; kb += S::kSub) {
+            for (int step = 0; step < num_kb; step += S::kSub) {
+                const int kb = flip ? kb_far - step : step;
                 PROF_T0(t_w);
                 if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                     report_timeout(p.status, 0x100u | (unsigned)stage);
