@@ -118,7 +118,7 @@ class FluxFp8:
         self.timed_work = [2.0 * self.tokens * k * n for _, k, n, _, _ in self.LINEARS]
         self.roof = {"bound": "tensor", "unit": "TFLOP/s", "kernel": "gemm_tcgen05_kernel<f8f6f4> (4 launches per step, one per linear)"}
         # dram__bytes_read + write per launch, mean of the four launches (profiles/gemm_tcgen05_fp8_flux_linears.md)
-        self.traffic = 123.0e6 if self.tokens == 4608 else None
+        self.traffic = 110.4e6 if self.tokens == 4608 else None
 
     def setup_gpu(self, dev):
         from lyradiff_b200 import ops
@@ -233,7 +233,7 @@ class Int8Sdxl:
         self.gemm_bytes = T * self.K + self.N * self.K + 2.0 * T * self.N + 4.0 * (T + self.N) + 2.0 * self.N
         self.timed_work = [self.gemm_bytes]
         self.roof = {"bound": "hbm", "unit": "GB/s", "kernel": "gemm_tcgen05_kernel<i8> (1 launch per step)"}
-        self.traffic = 40.5e6 if T == 8192 else None  # profiles/gemm_tcgen05_int8_sdxl.md (most of the output is still in L2)
+        self.traffic = 39.7e6 if T == 8192 else None  # profiles/gemm_tcgen05_int8_sdxl.md (most of the output is still in L2)
 
     def setup_gpu(self, dev):
         from lyradiff_b200 import ops

@@ -77,7 +77,8 @@ template<bool IS_MAX> __device__ __forceinline__ float team_reduce(float v, int 
 // The row lives in registers as fp32 (f[i][0..7] = the i-th 16-byte vector of this thread); every step the
 // reference evaluates in T is done on packed pairs with the type's native single-rounding add / multiply.
 template<typename T, int VPT, int MODE>
-__global__ void __launch_bounds__(256, (VPT <= 4) ? 3 : (VPT <= 6) ? 2 : 1) row_quant_kernel(const RowParams p)
+__global__ void __launch_bounds__(256, (VPT <= 4 && MODE != ROW_LN && MODE != ROW_GEGLU) ? 3 : (VPT <= 6) ? 2 : 1)
+row_quant_kernel(const RowParams p)
 {
     using P2 = Pair<T>;
     __shared__ float red[8];
