@@ -224,6 +224,17 @@ LYRAQ_API int lyraq_gemm_fp8_quant(const uint8_t* X, const float* s_x, const uin
                                    float beta, int epilogue, int m, int n, int k, void* workspace, size_t workspace_bytes,
                                    void* stream);
 
+/* lyraq_gemm_fp8_quant whose e4m3 output is a column window of a wider matrix: row m of the result starts at
+ * Yq + m * ldy (ldy >= n bytes, a multiple of 16 for the fast path).  This is how the MLP activation lands next to the
+ * attention output in the [tokens, 15360] input of proj_out without the 16-bit concat the reference builds
+ * (invokeFusedCatAndGelu + invokeCudaD2DScaleCpyConvert,
+ * src/lyradiff/layers/flux_single_transformer_block/FluxSingleTransformerFP8Block.cc:245-260).  residual must be
+ * NULL when ldy != n. */
+LYRAQ_API int lyraq_gemm_fp8_quant_ld(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, uint8_t* Yq,
+                                      size_t ldy, const float* y_scale, int dtype, const void* bias, const void* residual,
+                                      float alpha, float beta, int epilogue, int m, int n, int k, void* workspace,
+                                      size_t workspace_bytes, void* stream);
+
 /* W4A4, groups of 64 along K: D[m,n] = T( epi( sum_g (float(sum_{k in g} a*b) * sa[m,g]) * sb[n,g]
  *                                              + lora_act[m,:] . lora_up[n,:] + bias[n] ) + R[m,n] ).
  * A packed int4 [m,k/2], B packed int4 [n,k/2], sa fp32 [m,k/64], sb [n,k/64] of sb_dtype (F32 or F16),
@@ -238,6 +249,29 @@ LYRAQ_API int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* s
                     void* D, int c_dtype, const void* lora_act, int lora_act_dtype, const void* lora_up,
                     const void* bias, const void* residual, int epilogue, int m, int n, int k,
                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------ between the linears of a FLUX block
+ * (SURVEY "next" rows: the callers either side of the quantized-linear path) */
+
+/* QK RMSNorm + rotary embedding on the packed QKV projection: qkv [batch, seq, 3, heads, head_dim] (q heads, k heads,
+ * v heads), scale [2, head_dim] (q then k), rope [batch * seq, head_dim / 2, 2, 2]; q and k heads are normalised
+ * (fp32 statistics, eps), scaled and rotated with every step rounded to T as the reference does, v heads are copied
+ * (skipped when out == qkv).  head_dim 64 or 128.  Replaces invokeFusedRmsNormAndRope<T>
+ * (src/lyradiff/kernels/rope/flux_apply_rope.h:20-30; kernel flux_apply_rope.cu:8-76). */
+LYRAQ_API int lyraq_rmsnorm_rope(void* out, const void* qkv, const void* scale, const void* rope, int dtype, double eps,
+                                 size_t batch, size_t seq_len, int heads, int head_dim, void* stream);
+
+/* e4m3 quantize of src [rows, cols] (static per-tensor scale, 1/scale[0] applied) into a column window of an e4m3
+ * matrix with row pitch dst_ld bytes: the attention output's share of the proj_out input.  Same arithmetic as
+ * lyraq_quant_fp8 (invokeCudaD2DScaleCpyConvert, src/lyradiff/utils/memory_utils.h:74). */
+LYRAQ_API int lyraq_quant_fp8_2d(uint8_t* dst, size_t dst_ld, const void* src, int src_dtype, const float* scale, size_t rows,
+                                 size_t cols, void* stream);
+
+/* out = T(T(y * gate[b, :]) + x) with y, x, out [batch, seq, dim] and gate [batch, dim].  Replaces
+ * invokeFusedGateAndResidual<T> (src/lyradiff/kernels/flux_single_transformer_block/flux_single_transformer_kernels.cu:43-65,
+ * 152-160). */
+LYRAQ_API int lyraq_gate_residual(void* out, const void* y, const void* gate, const void* x, int dtype, size_t batch,
+                                  size_t seq_len, size_t dim, void* stream);
 
 /* ------------------------------------------------------------------ quantized-Linear layer forwards
  * Activation quantize + GEMM of one linear on `stream`; the quantized activation lives in `workspace`

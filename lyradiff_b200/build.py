@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblyraq.so")
 
-SOURCES = ["api.cu", "quant_kernels.cu", "gemm_dense.cu", "gemm_w4a4.cu", "lora_down.cu", "linear_layers.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "quant_kernels.cu", "gemm_dense.cu", "gemm_w4a4.cu", "lora_down.cu", "block_kernels.cu", "linear_layers.cu", "noalloc.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

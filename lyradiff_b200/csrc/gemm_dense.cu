@@ -864,14 +864,14 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
 
 // Tensor map of a row-major [rows, cols] matrix of 1- or 2-byte elements for TMA stores of 32 x 32 boxes whose
 // shared-memory image uses the swizzle that matches the box's row size (32 or 64 bytes).
-int make_tmap_store(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, int elem_bytes)
+int make_tmap_store(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int elem_bytes)
 {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) {
         return LYRAQ_ERR_CUDA;
     }
     const cuuint64_t dims[2]    = {cols, rows};
-    const cuuint64_t strides[1] = {cols * (uint64_t)elem_bytes};
+    const cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};  // row pitch: cols, or more when the output is a column window
     const cuuint32_t box[2]     = {32, 32};
     const cuuint32_t estr[2]    = {1, 1};
     const CUresult   r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
@@ -950,15 +950,15 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
     CUtensorMap tc = ta;
     p.epi.tma_store = 0;
     if (p.epi.out_q_scale != nullptr) {
-        if ((p.N & 15) == 0) {
-            st = make_tmap_store(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N, 1);
+        if ((p.N & 15) == 0 && (p.epi.ldc & 15) == 0) {
+            st = make_tmap_store(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N, (uint64_t)p.epi.ldc, 1);
             if (st != LYRAQ_OK) {
                 return st;
             }
             p.epi.tma_store = 1;
         }
     } else if ((p.epi.c_dtype == LYRAQ_BF16 || p.epi.c_dtype == LYRAQ_F16) && (p.N & 7) == 0) {
-        st = make_tmap_store(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N, 2);
+        st = make_tmap_store(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N, (uint64_t)p.epi.ldc, 2);
         if (st != LYRAQ_OK) {
             return st;
         }
@@ -1010,7 +1010,9 @@ template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams 
     if (sms <= 0) {
         return LYRAQ_ERR_CUDA;
     }
-    p.epi.ldc = p.N;
+    if (p.epi.ldc == 0) {
+        p.epi.ldc = p.N;
+    }
     TileChoice t = pick_tile(p.M, p.N, p.K, sms);
 #ifdef LYRAQ_PROFILE_WAITS
     p.skip = g_prof_skip;
@@ -1140,10 +1142,24 @@ int lyraq_gemm_fp8_quant(const uint8_t* X, const float* s_x, const uint8_t* W, c
                          int dtype, const void* bias, const void* residual, float alpha, float beta, int epilogue, int m, int n, int k,
                          void* workspace, size_t workspace_bytes, void* stream)
 {
+    return lyraq_gemm_fp8_quant_ld(X, s_x, W, s_w, Yq, (size_t)n, y_scale, dtype, bias, residual, alpha, beta, epilogue, m, n, k,
+                                   workspace, workspace_bytes, stream);
+}
+
+int lyraq_gemm_fp8_quant_ld(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, uint8_t* Yq, size_t ldy,
+                            const float* y_scale, int dtype, const void* bias, const void* residual, float alpha, float beta,
+                            int epilogue, int m, int n, int k, void* workspace, size_t workspace_bytes, void* stream)
+{
     (void)workspace;
     (void)workspace_bytes;
     if ((dtype != LYRAQ_F16 && dtype != LYRAQ_BF16) || s_x == nullptr || s_w == nullptr || y_scale == nullptr) {
         return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (ldy < (size_t)(n > 0 ? n : 0) || ldy > 0x7fffffffu) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (ldy != (size_t)n && residual != nullptr) {
+        return LYRAQ_ERR_UNSUPPORTED;  // the residual is read with the output's row pitch
     }
     if ((epilogue & ~LYRAQ_EPI_GELU_TANH) != 0) {
         return LYRAQ_ERR_INVALID_ARG;
@@ -1162,6 +1178,7 @@ int lyraq_gemm_fp8_quant(const uint8_t* X, const float* s_x, const uint8_t* W, c
     p.epi.residual    = residual;
     p.epi.gelu        = (epilogue & LYRAQ_EPI_GELU_TANH) ? 1 : 0;
     p.epi.out_q_scale = y_scale;
+    p.epi.ldc         = (int)ldy;
     return run_gemm<KIND_F8>(X, W, p, (cudaStream_t)stream);
 }
 

@@ -185,6 +185,46 @@ def gemm_with_residual_and_bias_fp8(W, w_scale, X, x_scale, Y, bias=None, residu
     return Y
 
 
+def invoke_fused_rmsnorm_and_rope(out, qkv, scale, rope_emb, eps, batch, seq_len, heads, head_dim):
+    """invokeFusedRmsNormAndRope<T> (src/lyradiff/kernels/rope/flux_apply_rope.h:20-30): qkv [batch, seq, 3*heads*head_dim]
+    packed q|k|v, scale [2*head_dim], rope_emb [batch, seq, head_dim/2, 2, 2]; out may be qkv itself."""
+    st = _lib.lib().lyraq_rmsnorm_rope(_p(out), _p(qkv), _p(scale), _p(rope_emb), _dt(qkv), float(eps), batch, seq_len, heads,
+                                       head_dim, _stream())
+    _lib.check(st, "lyraq_rmsnorm_rope")
+    return out
+
+
+def quant_fp8_into_columns(dst, col0, src, scale):
+    """e4m3 quantize of src [rows, cols] into dst[:, col0:col0+cols] (dst uint8 [rows, ld], contiguous)."""
+    rows, cols = src.shape
+    if dst.shape[0] != rows or col0 + cols > dst.shape[1]:
+        raise ValueError("shape mismatch")
+    st = _lib.lib().lyraq_quant_fp8_2d(dst.data_ptr() + col0, dst.shape[1], _p(src), _dt(src), _p(scale), rows, cols, _stream())
+    _lib.check(st, "lyraq_quant_fp8_2d")
+    return dst
+
+
+def invoke_fused_gate_and_residual(out, y, gate, residual):
+    """invokeFusedGateAndResidual<T> (flux_single_transformer_kernels.cu:152-160): out = y * gate[b] + residual."""
+    b, s, d = y.shape
+    st = _lib.lib().lyraq_gate_residual(_p(out), _p(y), _p(gate), _p(residual), _dt(y), b, s, d, _stream())
+    _lib.check(st, "lyraq_gate_residual")
+    return out
+
+
+def gemm_fp8_quant_into_columns(W, w_scale, X, x_scale, dst, col0, y_scale, dtype, bias=None, is_gelu=False):
+    """FP8 GEMM whose e4m3 result lands in dst[:, col0:col0+n] (lyraq_gemm_fp8_quant_ld)."""
+    m, k = X.shape
+    n = W.shape[0]
+    if W.shape[1] != k or dst.shape[0] != m or col0 + n > dst.shape[1]:
+        raise ValueError("shape mismatch")
+    st = _lib.lib().lyraq_gemm_fp8_quant_ld(_p(X), _p(x_scale), _p(W), _p(w_scale), dst.data_ptr() + col0, dst.shape[1],
+                                            _p(y_scale), _dt(dtype), _p(bias), None, 1.0, 0.0,
+                                            EPI_GELU_TANH if is_gelu else EPI_NONE, m, n, k, None, 0, _stream())
+    _lib.check(st, "lyraq_gemm_fp8_quant_ld")
+    return dst
+
+
 def gemm_fp8_quant_out(W, w_scale, X, x_scale, Yq, y_scale, dtype, bias=None, residual=None, alpha=1.0, beta=1.0, is_gelu=False):
     """FP8 GEMM whose epilogue also quantizes the result for the next FP8 linear (lyraq_gemm_fp8_quant): Yq uint8 e4m3 codes of
     T(epi(...)) / y_scale; `dtype` is the torch dtype T of bias / residual.  Fuses GemmWithResidualAndBias + GELU kernel +

@@ -123,3 +123,38 @@ def geglu_int8(h, bias, pre_quant_scale, input_quant_scale):
     gate = gelu_half_reference(gate, dt)
     prod = _t(hid * gate, dt)
     return _q.sq_input_quant(prod, pre_quant_scale, input_quant_scale, per_token=False)
+
+
+def rmsnorm_rope(qkv, scale, rope, heads, head_dim, eps=1e-6):
+    """QK RMSNorm + rotary embedding on the packed QKV projection.
+
+    Follows fuseRmsNormAndRope (src/lyradiff/kernels/rope/flux_apply_rope.cu:8-76).  qkv [tokens, 3*heads*head_dim]
+    (q heads, k heads, v heads); scale [2*head_dim] (q then k); rope [tokens, head_dim/2, 2, 2].  Per q/k head:
+    inv = rsqrt(mean(x^2) + eps) (exact here, rsqrtf on the device); t = T(x*inv); t = T(t*scale);
+    out[2i]   = T(T(t[2i]*r[i,0,0]) + T(t[2i+1]*r[i,0,1]));
+    out[2i+1] = T(T(t[2i]*r[i,1,0]) + T(t[2i+1]*r[i,1,1]));  v heads are copied.
+    """
+    dt = qkv.dtype
+    tokens = qkv.shape[0]
+    x = qkv.reshape(tokens, 3, heads, head_dim)
+    out = x.clone()
+    r = rope.reshape(tokens, head_dim // 2, 2, 2).to(F32)
+    for part in range(2):  # q, k
+        xf = x[:, part].to(F32)                                   # [tokens, heads, head_dim]
+        ms = (xf.double() ** 2).mean(dim=-1, keepdim=True)
+        inv = (1.0 / torch.sqrt(ms + eps)).to(F32)
+        t = _t(xf * inv, dt)
+        t = _t(t * scale[part * head_dim:(part + 1) * head_dim].to(F32)[None, None, :], dt)
+        te, to = t[..., 0::2], t[..., 1::2]                       # [tokens, heads, head_dim/2]
+        o_even = _t(_t(te * r[:, None, :, 0, 0], dt) + _t(to * r[:, None, :, 0, 1], dt), dt)
+        o_odd = _t(_t(te * r[:, None, :, 1, 0], dt) + _t(to * r[:, None, :, 1, 1], dt), dt)
+        o = torch.stack([o_even, o_odd], dim=-1).reshape(tokens, heads, head_dim)
+        out[:, part] = o.to(dt)
+    return out.reshape(tokens, 3 * heads * head_dim)
+
+
+def gate_residual(y, gate, x):
+    """fuseGateAndResidual (src/lyradiff/kernels/flux_single_transformer_block/flux_single_transformer_kernels.cu:43-65):
+    out = T(T(y * gate[b]) + x), y and x [B, S, D], gate [B, D]."""
+    dt = y.dtype
+    return _t(_t(y.to(F32) * gate.to(F32)[:, None, :], dt) + x.to(F32), dt).to(dt)

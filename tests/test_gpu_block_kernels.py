@@ -1,0 +1,85 @@
+"""GPU parity tests of the kernels between the quantized linears of a FLUX block (QK RMSNorm + RoPE, e4m3 quantize into
+a column window, gate + residual, GEMM with a strided e4m3 output) against the CPU oracle, through the C ABI."""
+
+import pytest
+import torch
+
+from oracle import gemm, norms, quant, workloads
+from tests.util import assert_bit_equal, check_status, cu
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from lyradiff_b200 import ops as _ops
+    return _ops
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("batch,seq,heads,head_dim", [(1, 7, 2, 128), (2, 33, 24, 128), (1, 50, 3, 64)])
+def test_rmsnorm_rope_against_oracle(ops, dtype, batch, seq, heads, head_dim):
+    """Device statistics are fp32 shuffle sums and rsqrtf (2 ulp): a result may sit on the other side of a rounding
+    boundary of T, so at most 0.5 % of the outputs may differ, by at most 2 ulp of T at the head's amplitude; V heads
+    and the out-of-place / in-place forms are bit-identical."""
+    g = torch.Generator().manual_seed(batch * 100 + seq + heads)
+    tokens = batch * seq
+    qkv = torch.randn(tokens, 3 * heads * head_dim, generator=g).to(dtype)
+    scale = (1.0 + 0.2 * torch.randn(2 * head_dim, generator=g)).to(dtype)
+    ang = torch.rand(tokens, head_dim // 2, generator=g) * 6.28
+    rope = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).to(dtype)
+    want = norms.rmsnorm_rope(qkv, scale, rope, heads, head_dim, eps=1e-6)
+    out = torch.full_like(qkv, float("nan"), device="cuda")
+    ops.invoke_fused_rmsnorm_and_rope(out, cu(qkv), cu(scale), cu(rope), 1e-6, batch, seq, heads, head_dim)
+    check_status()
+    got = out.cpu()
+    hd = heads * head_dim
+    assert_bit_equal(got[:, 2 * hd:], want[:, 2 * hd:], "v heads are copied")
+    diff = (got[:, :2 * hd].float() - want[:, :2 * hd].float()).abs()
+    assert float(diff.max()) <= 2 * torch.finfo(dtype).eps * 8.0
+    assert float((diff > 0).float().mean()) <= 5e-3
+    inplace = cu(qkv).clone()
+    ops.invoke_fused_rmsnorm_and_rope(inplace, inplace, cu(scale), cu(rope), 1e-6, batch, seq, heads, head_dim)
+    assert_bit_equal(inplace, got, "in place")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gate_residual_bit_exact(ops, dtype):
+    g = torch.Generator().manual_seed(3)
+    y = torch.randn(2, 37, 3072, generator=g).to(dtype)
+    x = torch.randn(2, 37, 3072, generator=g).to(dtype)
+    gate = torch.randn(2, 3072, generator=g).to(dtype)
+    out = torch.empty_like(y, device="cuda")
+    ops.invoke_fused_gate_and_residual(out, cu(y), cu(gate), cu(x))
+    check_status()
+    assert_bit_equal(out, norms.gate_residual(y, gate, x))
+
+
+def test_quantize_into_a_column_window(ops):
+    g = torch.Generator().manual_seed(4)
+    a = torch.randn(130, 256, generator=g).bfloat16()
+    s = torch.tensor([0.031], dtype=torch.float32)
+    dst = torch.full((130, 1024), 0x7F, dtype=torch.uint8, device="cuda")
+    ops.quant_fp8_into_columns(dst, 512, cu(a), cu(s))
+    check_status()
+    got = dst.cpu()
+    assert_bit_equal(got[:, 512:768], quant.fp8_quant(a, s, invert_scale=True))
+    assert bool((got[:, :512] == 0x7F).all()) and bool((got[:, 768:] == 0x7F).all())
+
+
+@pytest.mark.parametrize("m,n,k,ld,col0", [(128, 256, 128, 512, 256), (200, 1024, 384, 1280, 256), (130, 72, 144, 80, 0)])
+def test_gemm_with_strided_e4m3_output(ops, m, n, k, ld, col0):
+    """lyraq_gemm_fp8_quant_ld writes the same codes as the contiguous form, at the row pitch asked for, and nothing
+    outside its window (the last shape has a pitch that is not a multiple of 16: the direct-store path)."""
+    w = workloads.fp8_linear(m=m, k=k, n=n, seed=m + n)
+    ys = torch.tensor([0.05], dtype=torch.float32)
+    ref = torch.empty(m, n, dtype=torch.uint8, device="cuda")
+    ops.gemm_fp8_quant_out(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), ref, cu(ys), torch.bfloat16, bias=cu(w["bias"]),
+                           is_gelu=True)
+    dst = torch.full((m, ld), 0x55, dtype=torch.uint8, device="cuda")
+    ops.gemm_fp8_quant_into_columns(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), dst, col0, cu(ys), torch.bfloat16,
+                                    bias=cu(w["bias"]), is_gelu=True)
+    check_status()
+    got = dst.cpu()
+    assert_bit_equal(got[:, col0:col0 + n], ref.cpu())
+    assert bool((got[:, :col0] == 0x55).all()) and bool((got[:, col0 + n:] == 0x55).all())
