@@ -1,0 +1,55 @@
+"""CPU restatement of the FP8 FLUX single-stream block, for the parity test of lyradiff_b200.flux_blocks.
+
+TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).  PARITY UNPINNED: the reference has no test or golden vector for
+this block; the data flow follows FluxSingleTransformerFP8Block<T>::forward
+(src/lyradiff/layers/flux_single_transformer_block/FluxSingleTransformerFP8Block.cc:162-310), AdaFP8LayerNorm<T>::forward
+(src/lyradiff/layers/ada_layer_norm/AdaFP8LayerNorm.cc:96-205) and FluxSingleAttentionFP8Processor<T>::forward
+(src/lyradiff/layers/flux_single_attention_processor/FluxSingleAttentionFP8Processor.cc:134-230), with the kernels'
+arithmetic restated in oracle/quant.py, gemm.py and norms.py and an exact (fp64) softmax attention.
+"""
+
+import torch
+
+from . import gemm as _g
+from . import norms as _n
+from . import quant as _q
+
+F32 = torch.float32
+
+
+def _fp8_linear(x, w, bias, s_x, out_dtype, gelu=False):
+    s_w = _q.fp8_amax_scale(w)
+    return _g.fp8_gemm(_q.fp8_quant(x, s_x), _q.fp8_quant(w, s_w), s_x, s_w, out_dtype=out_dtype, bias=bias, gelu=gelu)
+
+
+def attention(q, k, v):
+    """softmax(q k^T / sqrt(d)) v per head in fp64; q, k, v [B, H, S, Dh]."""
+    d = q.shape[-1]
+    p = torch.softmax(q.double() @ k.double().transpose(-1, -2) / (d ** 0.5), dim=-1)
+    return p @ v.double()
+
+
+def flux_single_block(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_scale=4, quant_level=1):
+    """hidden [B, S, D], rope [B, S, head_dim/2, 2, 2], temb [B, D] (SiLU'd); sd: the state dict the block loads.
+    Returns (out [B, S, D], intermediates)."""
+    dt = hidden.dtype
+    B, S, D = hidden.shape
+    g = lambda name: sd[prefix + name]
+    if quant_level == 2:
+        msa = _fp8_linear(temb, g("norm.linear.weight").to(dt), g("norm.linear.bias").to(dt), g("norm.linear_input_scale"), dt)
+    else:
+        msa = (temb.double() @ g("norm.linear.weight").to(dt).double().t() + g("norm.linear.bias").to(dt).double()).to(dt)
+    shift, scale, gate = msa.chunk(3, dim=1)
+    norm = _n.adaln_modulate(hidden, scale, shift, eps=1e-6)                                  # [B, S, D] of dt
+    n2 = norm.reshape(B * S, D)
+    qkv = _fp8_linear(n2, g("attn.to_qkv.weight").to(dt), g("attn.to_qkv.bias").to(dt), g("attn.to_qkv_input_scale"), dt)
+    qk_scale = torch.cat([g("attn.norm_q.weight").reshape(-1), g("attn.norm_k.weight").reshape(-1)]).to(dt)
+    qkv = _n.rmsnorm_rope(qkv, qk_scale, rope.reshape(B * S, head_dim // 2, 2, 2), heads, head_dim, eps=1e-6)
+    v5 = qkv.reshape(B, S, 3, heads, head_dim)
+    q, k, v = (v5[:, :, i].transpose(1, 2) for i in range(3))
+    attn = attention(q, k, v).transpose(1, 2).reshape(B * S, D).to(dt)
+    mlp = _fp8_linear(n2, g("proj_mlp.weight").to(dt), g("proj_mlp.bias").to(dt), g("proj_mlp_input_scale"), dt, gelu=True)
+    cat = torch.cat([attn, mlp], dim=1)
+    y = _fp8_linear(cat, g("proj_out.weight").to(dt), g("proj_out.bias").to(dt), g("proj_out_input_scale"), dt)
+    out = _n.gate_residual(y.reshape(B, S, D), gate, hidden)
+    return out, {"msa": msa, "norm": norm, "qkv": qkv, "attn": attn, "mlp": mlp, "y": y}

@@ -1,0 +1,81 @@
+"""GPU parity test of the FLUX single-stream block mirror (lyradiff_b200.flux_blocks) against the CPU oracle block.
+
+Both sides quantize with the same static scales and the same e4m3 arithmetic, so what differs is rounding inside the
+block: bf16 library attention against an exact softmax, fp32 tensor-core sums against fp64, and the e4m3 codes that
+flip where those differences cross a rounding boundary.  The tolerance is stated against the output's own amplitude."""
+
+import pytest
+import torch
+
+from oracle import blocks
+from tests.util import check_status, cu
+
+pytestmark = pytest.mark.gpu
+
+
+def _state_dict(prefix, D, mlp_scale, head_dim, level, g):
+    sd = {}
+
+    def lin(name, n, k, std):
+        sd[prefix + name + ".weight"] = (torch.randn(n, k, generator=g) * std).bfloat16()
+        sd[prefix + name + ".bias"] = (torch.randn(n, generator=g) * 0.02).bfloat16()
+
+    lin("norm.linear", 3 * D, D, 0.03)
+    lin("attn.to_qkv", 3 * D, D, 0.05)
+    lin("proj_mlp", mlp_scale * D, D, 0.05)
+    lin("proj_out", D, (mlp_scale + 1) * D, 0.03)
+    sd[prefix + "attn.norm_q.weight"] = (1.0 + 0.1 * torch.randn(head_dim, generator=g)).bfloat16()
+    sd[prefix + "attn.norm_k.weight"] = (1.0 + 0.1 * torch.randn(head_dim, generator=g)).bfloat16()
+    sd[prefix + "attn.to_qkv_input_scale"] = torch.tensor([0.02])
+    sd[prefix + "proj_mlp_input_scale"] = torch.tensor([0.02])
+    sd[prefix + "proj_out_input_scale"] = torch.tensor([0.02])
+    if level == 2:
+        sd[prefix + "norm.linear_input_scale"] = torch.tensor([0.01])
+    return sd
+
+
+@pytest.mark.parametrize("level", [1, 2])
+@pytest.mark.parametrize("B,S", [(1, 160), (2, 96)])
+def test_single_block_against_oracle(level, B, S):
+    from lyradiff_b200 import flux_blocks
+    D, heads, head_dim, mlp_scale = 256, 2, 128, 4
+    g = torch.Generator().manual_seed(100 * level + S)
+    prefix = "single_transformer_blocks.0."
+    sd = _state_dict(prefix, D, mlp_scale, head_dim, level, g)
+    hidden = torch.randn(B, S, D, generator=g).bfloat16()
+    temb = torch.nn.functional.silu(torch.randn(B, D, generator=g)).bfloat16()
+    ang = torch.rand(B, S, head_dim // 2, generator=g) * 6.28
+    rope = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+        B, S, head_dim // 2, 2, 2).bfloat16()
+
+    op = flux_blocks.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    op.initialize(flux_blocks.LyraDiffCommonContext())
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    out = op.forward(cu(hidden), cu(rope), cu(temb))
+    out2 = op.forward(cu(hidden), cu(rope), cu(temb))
+    check_status()
+    assert tuple(out.shape) == (B, S, D) and out.dtype == torch.bfloat16
+    assert torch.equal(out, out2)  # same call, same bits
+
+    want, mid = blocks.flux_single_block(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_scale, level)
+    got = out.cpu().float()
+    delta = (got - hidden.float())            # the block's own contribution, without the residual
+    wdelta = (want.float() - hidden.float())
+    err = (delta - wdelta).abs()
+    amp = float(wdelta.abs().mean())
+    assert amp > 0.05                         # the block does something in this test
+    assert float(err.mean()) <= 0.02 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
+    assert float(err.max()) <= 0.25 * float(wdelta.abs().max()), float(err.max())
+
+
+def test_block_refuses_what_is_not_built():
+    from lyradiff_b200 import flux_blocks
+    with pytest.raises(NotImplementedError):
+        flux_blocks.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 7)
+    op = flux_blocks.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 1)
+    with pytest.raises(NotImplementedError):
+        op.reload_model_from_bin("/nowhere", "bf16")
+    with pytest.raises(RuntimeError):
+        op.forward(torch.zeros(1, 8, 256, dtype=torch.bfloat16, device="cuda"),
+                   torch.zeros(1, 8, 64, 2, 2, dtype=torch.bfloat16, device="cuda"),
+                   torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda"))
