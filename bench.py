@@ -9,6 +9,7 @@ residual).  One step = for each linear: per-tensor e4m3 activation quantize (bf1
 with its fused epilogue.  Other cases time the remaining configurations with the same harness:
     int8_sdxl    SDXL GEGLU-FF INT8 SmoothQuant linear, M=8192 K=640 N=5120 (dynamic per-token quantize + GEMM)
     w4a4         FLUX fused W4A4 linear, M=4608 K=3072 N=21504 (int4 group-64 quantize + GEMM)
+    flux_block   one FLUX single-stream block through FluxSingleTransformerBlockOp (FP8 linears + library attention)
     sdxl_ff      the whole SDXL GEGLU feed-forward block in INT8 (four launches)
     adaln_quant  fused AdaLN-modulation + int8 and e4m3 quantize of [4608, 3072] bf16
 `--tokens` shrinks M (for profiler captures).  Synthetic seeded inputs, random weights.  Rank 0 prints ONE JSON line.
@@ -387,6 +388,106 @@ class SdxlFF:
     cpu_note = "LayerNorm->int8 + torch._int_mm + bias/GEGLU->int8 + torch._int_mm + residual + bias"
 
 
+class FluxBlock:
+    """One FLUX.1-dev single-stream block through lyradiff_b200.flux_blocks.FluxSingleTransformerBlockOp (the per-block
+    unit of configs[4]): modulation, AdaLN + quantize, QKV, QK-norm + RoPE, attention (torch SDPA, library), MLP, proj_out,
+    gate + residual at 4608 tokens."""
+    name = "flux_block"
+    metric = "flux_single_block_throughput"
+    unit = "TFLOP/s"
+    dtype = "e4m3 linears (f32 accumulate in TMEM) + bf16 library attention"
+    D, H, DH, MLP = 3072, 24, 128, 4
+
+    def __init__(self, tokens):
+        self.tokens = tokens or 4608
+        T, D = self.tokens, self.D
+        self.lin_flops = 2.0 * T * D * (3 * D + self.MLP * D + (self.MLP + 1) * D)
+        self.attn_flops = 4.0 * T * T * D
+        self.work_per_step = self.lin_flops + self.attn_flops
+        self.scale = 1e12
+        self.workload = ("one FLUX.1-dev single-stream block (the unit configs[4] repeats 38 times), FP8_W8A8, batch 1, %d tokens, "
+                         "hidden 3072, 24 x 128 heads, random weights: %.3f TFLOP in FP8 linears + %.3f TFLOP in bf16 attention "
+                         "(torch SDPA)" % (T, self.lin_flops / 1e12, self.attn_flops / 1e12))
+        self.launches_per_step = 9
+        self.timed_names = ["block_forward"]
+        self.timed_work = [self.work_per_step]
+        self.roof = {"bound": "tensor", "unit": "TFLOP/s",
+                     "kernel": "whole block: 3 gemm_tcgen05_kernel<f8f6f4> launches + 6 element-wise kernels of this library, "
+                               "plus the library attention and one small library matmul"}
+        self.traffic = None
+
+    def _state_dict(self, g):
+        D, M = self.D, self.MLP
+        p = "single_transformer_blocks.0."
+        sd = {}
+        for name, n, k, std in (("norm.linear", 3 * D, D, 0.02), ("attn.to_qkv", 3 * D, D, 0.02), ("proj_mlp", M * D, D, 0.02),
+                                ("proj_out", D, (M + 1) * D, 0.02)):
+            sd[p + name + ".weight"] = (torch.randn(n, k, generator=g) * std).bfloat16()
+            sd[p + name + ".bias"] = (torch.randn(n, generator=g) * 0.02).bfloat16()
+        sd[p + "attn.norm_q.weight"] = torch.ones(self.DH).bfloat16()
+        sd[p + "attn.norm_k.weight"] = torch.ones(self.DH).bfloat16()
+        for name in ("attn.to_qkv_input_scale", "proj_mlp_input_scale", "proj_out_input_scale"):
+            sd[p + name] = torch.tensor([0.03])
+        return p, sd
+
+    def _inputs(self, g, rows):
+        x = torch.randn(1, rows, self.D, generator=g).bfloat16()
+        temb = torch.nn.functional.silu(torch.randn(1, self.D, generator=g)).bfloat16()
+        ang = torch.rand(1, rows, self.DH // 2, generator=g) * 6.28
+        rope = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+            1, rows, self.DH // 2, 2, 2).bfloat16()
+        return x, temb, rope
+
+    def setup_gpu(self, dev):
+        from lyradiff_b200 import flux_blocks
+        g = _gen()
+        prefix, sd = self._state_dict(g)
+        self.op = flux_blocks.FluxSingleTransformerBlockOp("bf16", self.D, self.H, self.DH, self.MLP, 1)
+        self.op.initialize(flux_blocks.LyraDiffCommonContext())
+        self.op.reload_model_from_state_dict(prefix, sd, dev)
+        x, temb, rope = self._inputs(g, self.tokens)
+        self.x, self.temb, self.rope = x.to(dev), temb.to(dev), rope.to(dev)
+        self.y = torch.empty_like(self.x)
+        self.h_in = x.pin_memory()
+        self.e2e_x = [self.x, torch.empty_like(self.x)]
+        self.e2e_y = [self.y, torch.empty_like(self.y)]
+
+    def step(self, events=None, io=None):
+        x = self.x if io is None else io[0]
+        if events is not None:
+            events[0][0].record()
+        out = self.op.forward(x, self.rope, self.temb)
+        if events is not None:
+            events[0][1].record()
+        if io is not None:
+            io[1].copy_(out)
+
+    def peak(self, peaks):
+        p8, p16 = 2.0 * peaks["bf16_sustained"], peaks["bf16_sustained"]
+        blend = self.work_per_step / (self.lin_flops / p8 + self.attn_flops / p16)
+        nominal = self.work_per_step / (self.lin_flops / 4500.0 + self.attn_flops / 2250.0)
+        return blend, ("FLOP-weighted blend of 2 x bf16_tflops_sustained (FP8 linears) and bf16_tflops_sustained (attention) of "
+                       "MEASURED_PEAKS.json (%s)" % peaks["source"]), nominal
+
+    def setup_cpu(self, rows):
+        g = _gen()
+        self.cpu_prefix, self.cpu_sd = self._state_dict(g)
+        self.cpu_in = self._inputs(g, rows)
+        self.cpu_rows = rows
+        self.cpu_cache = {}
+        self.step_cpu()  # quantizes the weights once, as loading the block does
+
+    def cpu_work(self, rows):
+        return 2.0 * rows * self.D * (3 * self.D + self.MLP * self.D + (self.MLP + 1) * self.D) + 4.0 * rows * rows * self.D
+
+    def step_cpu(self):
+        from oracle import blocks
+        x, temb, rope = self.cpu_in
+        return blocks.flux_single_block(x, rope, temb, self.cpu_sd, self.cpu_prefix, self.H, self.DH, self.MLP, 1, cache=self.cpu_cache)[0]
+
+    cpu_note = "oracle block with weights quantized once: fp64 contractions of the e4m3 operands and exact attention over the sample's own rows"
+
+
 class W4A4:
     """configs[2]: FLUX fused W4A4 linear."""
     name = "w4a4"
@@ -531,7 +632,7 @@ class AdalnQuant:
     cpu_note = "LayerNorm + modulation + int8 and e4m3 quantize"
 
 
-CASES = {c.name: c for c in (FluxFp8, Int8Sdxl, SdxlFF, W4A4, AdalnQuant)}
+CASES = {c.name: c for c in (FluxFp8, FluxBlock, Int8Sdxl, SdxlFF, W4A4, AdalnQuant)}
 
 
 # =================================================================================================== CPU arm
@@ -545,7 +646,7 @@ def time_cpu(case, rows, steps, warmup):
     for _ in range(steps):
         case.step_cpu()
     dt = (time.perf_counter() - t0) / steps
-    work = case.work_per_step * rows / case.tokens
+    work = case.cpu_work(rows) if hasattr(case, "cpu_work") else case.work_per_step * rows / case.tokens
     return {"value": work / dt / case.scale, "unit": case.unit, "cores": cores, "kind": "port",
             "sample": "%d of %d token rows per step (%s), torch on %d threads, %d timed steps" % (
                 rows, case.tokens, case.cpu_note, cores, steps),

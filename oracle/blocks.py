@@ -17,9 +17,17 @@ from . import quant as _q
 F32 = torch.float32
 
 
-def _fp8_linear(x, w, bias, s_x, out_dtype, gelu=False):
-    s_w = _q.fp8_amax_scale(w)
-    return _g.fp8_gemm(_q.fp8_quant(x, s_x), _q.fp8_quant(w, s_w), s_x, s_w, out_dtype=out_dtype, bias=bias, gelu=gelu)
+def _fp8_linear(x, w, bias, s_x, out_dtype, gelu=False, cache=None, key=None):
+    """Quantize-on-load weight (per-tensor amax / 448), static activation scale, FP8 GEMM.  `cache` keeps the quantized
+    weight between calls, as the loaded layer does."""
+    if cache is not None and key in cache:
+        qw, s_w = cache[key]
+    else:
+        s_w = _q.fp8_amax_scale(w)
+        qw = _q.fp8_quant(w, s_w)
+        if cache is not None:
+            cache[key] = (qw, s_w)
+    return _g.fp8_gemm(_q.fp8_quant(x, s_x), qw, s_x, s_w, out_dtype=out_dtype, bias=bias, gelu=gelu)
 
 
 def attention(q, k, v):
@@ -29,27 +37,27 @@ def attention(q, k, v):
     return p @ v.double()
 
 
-def flux_single_block(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_scale=4, quant_level=1):
-    """hidden [B, S, D], rope [B, S, head_dim/2, 2, 2], temb [B, D] (SiLU'd); sd: the state dict the block loads.
-    Returns (out [B, S, D], intermediates)."""
+def flux_single_block(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_scale=4, quant_level=1, cache=None):
+    """hidden [B, S, D], rope [B, S, head_dim/2, 2, 2], temb [B, D] (SiLU'd); sd: the state dict the block loads;
+    cache: optional dict that keeps the quantized weights between calls.  Returns (out [B, S, D], intermediates)."""
     dt = hidden.dtype
     B, S, D = hidden.shape
     g = lambda name: sd[prefix + name]
     if quant_level == 2:
-        msa = _fp8_linear(temb, g("norm.linear.weight").to(dt), g("norm.linear.bias").to(dt), g("norm.linear_input_scale"), dt)
+        msa = _fp8_linear(temb, g("norm.linear.weight").to(dt), g("norm.linear.bias").to(dt), g("norm.linear_input_scale"), dt, cache=cache, key="norm")
     else:
         msa = (temb.double() @ g("norm.linear.weight").to(dt).double().t() + g("norm.linear.bias").to(dt).double()).to(dt)
     shift, scale, gate = msa.chunk(3, dim=1)
     norm = _n.adaln_modulate(hidden, scale, shift, eps=1e-6)                                  # [B, S, D] of dt
     n2 = norm.reshape(B * S, D)
-    qkv = _fp8_linear(n2, g("attn.to_qkv.weight").to(dt), g("attn.to_qkv.bias").to(dt), g("attn.to_qkv_input_scale"), dt)
+    qkv = _fp8_linear(n2, g("attn.to_qkv.weight").to(dt), g("attn.to_qkv.bias").to(dt), g("attn.to_qkv_input_scale"), dt, cache=cache, key="qkv")
     qk_scale = torch.cat([g("attn.norm_q.weight").reshape(-1), g("attn.norm_k.weight").reshape(-1)]).to(dt)
     qkv = _n.rmsnorm_rope(qkv, qk_scale, rope.reshape(B * S, head_dim // 2, 2, 2), heads, head_dim, eps=1e-6)
     v5 = qkv.reshape(B, S, 3, heads, head_dim)
     q, k, v = (v5[:, :, i].transpose(1, 2) for i in range(3))
     attn = attention(q, k, v).transpose(1, 2).reshape(B * S, D).to(dt)
-    mlp = _fp8_linear(n2, g("proj_mlp.weight").to(dt), g("proj_mlp.bias").to(dt), g("proj_mlp_input_scale"), dt, gelu=True)
+    mlp = _fp8_linear(n2, g("proj_mlp.weight").to(dt), g("proj_mlp.bias").to(dt), g("proj_mlp_input_scale"), dt, gelu=True, cache=cache, key="mlp")
     cat = torch.cat([attn, mlp], dim=1)
-    y = _fp8_linear(cat, g("proj_out.weight").to(dt), g("proj_out.bias").to(dt), g("proj_out_input_scale"), dt)
+    y = _fp8_linear(cat, g("proj_out.weight").to(dt), g("proj_out.bias").to(dt), g("proj_out_input_scale"), dt, cache=cache, key="out")
     out = _n.gate_residual(y.reshape(B, S, D), gate, hidden)
     return out, {"msa": msa, "norm": norm, "qkv": qkv, "attn": attn, "mlp": mlp, "y": y}
