@@ -173,6 +173,26 @@ inline void invokeLayerNormWithShiftAndScaleFp8O(__nv_fp8_e4m3* dst_fp8, const f
                         "invokeLayerNormWithShiftAndScaleFp8O");
 }
 
+/* src/lyradiff/kernels/rope/flux_apply_rope.h:20-30 */
+template<typename T>
+inline void invokeFusedRmsNormAndRope(T* out, const T* input, const T* scale, const T* rope_emb, float eps, int batch_size,
+                                      int seq_len, int head_num, int head_dim, cudaStream_t stream)
+{
+    lyraq_detail::check(lyraq_rmsnorm_rope(out, input, scale, rope_emb, lyraq_detail::DType<T>::value, (double)eps,
+                                           (size_t)batch_size, (size_t)seq_len, head_num, head_dim, stream),
+                        "invokeFusedRmsNormAndRope");
+}
+
+/* src/lyradiff/kernels/flux_single_transformer_block/flux_single_transformer_kernels.cu:152-160 */
+template<typename T>
+inline void invokeFusedGateAndResidual(T* out, const T* input, const T* gate, const T* residual, int batch_size, int seq_len,
+                                       int dim, cudaStream_t stream)
+{
+    lyraq_detail::check(lyraq_gate_residual(out, input, gate, residual, lyraq_detail::DType<T>::value, (size_t)batch_size,
+                                            (size_t)seq_len, (size_t)dim, stream),
+                        "invokeFusedGateAndResidual");
+}
+
 /* src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.h:6-17.  A is bf16 [m,k]; B (lora_down) bf16 [32,k]; n is the LoRA rank. */
 inline void invokeFusedQuantizeAndLoraDownSimple(float* Cptr, uint32_t* quantized_input, float* quantized_scale,
                                                  const void* Aptr, const void* Bptr, const float* Smoothptr, int m, int n,

@@ -22,6 +22,8 @@ void flux_fp8_call_sites(__nv_fp8_e4m3* q8, __nv_bfloat16* b, const float* f, fl
     invokeGetFP8WeightScale<__nv_bfloat16>(fo, b, 9216 * 3072, s);
     invokeLayerNormWithShiftAndScale<__nv_bfloat16>(b, b, b, b, 1, 4608, 3072, s);
     invokeLayerNormWithShiftAndScaleFp8O<__nv_bfloat16>(q8, f, nullptr, b, b, b, 1, 4608, 3072, s);
+    invokeFusedRmsNormAndRope<__nv_bfloat16>(b, b, b, b, 1e-6f, 1, 4608, 24, 128, s);   // FluxSingleAttentionFP8Processor.cc:183
+    invokeFusedGateAndResidual<__nv_bfloat16>(b, b, b, b, 1, 4608, 3072, s);           // FluxSingleTransformerFP8Block.cc:296
     QuantGemmWrapper w(s, LYRAQ_BF16);
     w.GemmWithResidualAndBias(CUBLAS_OP_T, CUBLAS_OP_N, 12288, 4608, 3072, q8, 3072, f, q8, 3072, f, b, 12288, b, nullptr, 1.0f,
                               0.0f, true);
