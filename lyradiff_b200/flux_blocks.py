@@ -1,4 +1,7 @@
-"""Python mirror of the reference's block-level torch custom classes for the FLUX single-stream block.
+"""Python mirrors of the reference's block-level torch custom classes for the FLUX blocks.
+
+FluxTransformerBlockOp (double-stream, at the end of this file) follows the same conventions as the single-stream
+class described here.
 
 `torch.classes.lyradiff.FluxSingleTransformerBlockOp` (src/lyradiff/th_op/pybind.cc:82-96,
 th_op/flux_single_transformer_block/FluxSingleTransformerBlockOp.h:287-315) with the same constructor arguments,
@@ -167,5 +170,154 @@ class FluxSingleTransformerBlockOp:
         out = torch.empty_like(hidden_states)
         ops.invoke_fused_gate_and_residual(out, y.view(B, S, D), gate, hidden_states)
         return out
+
+    __call__ = forward
+
+
+def _modulation(op, w, temb, chunks):
+    """msa = linear(temb) -> `chunks` contiguous [B, D] tensors (AdaFP8LayerNorm<T>::forward,
+    src/lyradiff/layers/ada_layer_norm/AdaFP8LayerNorm.cc:96-160)."""
+    B, D = temb.shape
+    if op.quant_level == FP8_W8A8_FULL:
+        nw = w["fp8"]
+        tq = torch.empty(B, D, dtype=torch.uint8, device=temb.device)
+        ops.invoke_cuda_d2d_scale_cpy_convert(tq, temb, nw.input_scale)
+        msa = torch.empty(B, chunks * D, dtype=op.dtype, device=temb.device)
+        ops.gemm_with_residual_and_bias_fp8(nw.qweight, nw.w_scale, tq, nw.input_scale, msa, bias=nw.bias)
+    else:
+        msa = torch.addmm(w["b"], temb, w["w"].t())
+    return [c.contiguous() for c in msa.chunk(chunks, dim=1)]
+
+
+class FluxTransformerBlockOp:
+    """torch.classes.lyradiff.FluxTransformerBlockOp (src/lyradiff/th_op/pybind.cc:66-80,
+    th_op/flux_transformer_block/FluxTransformerBlockOp.h:187-237): the double-stream block.  Data flow of
+    FluxTransformerFP8Block<T>::forward (src/lyradiff/layers/flux_transformer_block/FluxTransformerFP8Block.cc:155-245),
+    FluxAttentionFP8Processor<T>::forward (layers/flux_attention_processor/FluxAttentionFP8Processor.cc:140-340) and
+    FluxAttnPostFP8Processor<T>::forward (layers/flux_attn_post_processor/FluxAttnPostFP8Processor.cc:90-205), per stream
+    (image tokens `hidden`, text tokens `encoder`):
+
+        shift, scale, gate, shift2, scale2, gate2 = linear(temb)
+        qkv  = FP8 GEMM(e4m3(LN(x)(1+scale)+shift), to_qkv) + bias        (AdaLN + quantize in one kernel)
+        both streams: QK RMSNorm + RoPE into one [B, S_txt + S_img] buffer (text first), joint attention (torch SDPA)
+        h    = x + gate * (FP8 GEMM(e4m3(attn), to_out) + bias)
+        ff   = FP8 GEMM(e4m3(gelu(FP8 GEMM(e4m3(LN(h)(1+scale2)+shift2), net.0.proj) + bias)), net.2) + bias
+        out  = h + gate2 * ff              (the quantize between the two FF linears is fused into the first GEMM's epilogue)
+    """
+
+    def __init__(self, inference_dtype="bf16", embedding_dim=3072, embedding_head_num=24, embedding_head_dim=128, mlp_scale=6,
+                 quant_level=0):
+        if inference_dtype not in _DTYPES:
+            raise RuntimeError("inference_dtype must be 'bf16' or 'fp16'")
+        if quant_level not in (FP8_W8A8, FP8_W8A8_FULL):
+            raise NotImplementedError("only quant_level 1 (FP8_W8A8) and 2 (FP8_W8A8_FULL) are built")
+        if embedding_head_num * embedding_head_dim != embedding_dim:
+            raise RuntimeError("embedding_dim must equal embedding_head_num * embedding_head_dim")
+        self.dtype = _DTYPES[inference_dtype]
+        self.dim, self.heads, self.head_dim, self.mlp_scale = embedding_dim, embedding_head_num, embedding_head_dim, mlp_scale
+        self.quant_level = quant_level
+        self._w = None
+
+    def initialize(self, ctx):
+        self._ctx = ctx
+
+    def reload_model_from_bin(self, path, dtype):
+        raise NotImplementedError("the .bin directory loader is not built; use reload_model_from_state_dict")
+
+    def load_lora_by_name(self, names, weight, scale):
+        raise NotImplementedError("LoRA hot-swap is not built")
+
+    def clear_lora(self):
+        raise NotImplementedError("LoRA hot-swap is not built")
+
+    def reload_model_from_state_dict(self, prefix, state_dict, device):
+        """Keys (FluxTransformerFP8BlockWeight.cc:104-108 and the loaders it calls): per stream
+        `norm1[_context].linear`, `attn.to_qkv | attn.to_added_qkv`, `attn.to_out.0 | attn.to_add_out`,
+        `attn.norm_q, norm_k | attn.norm_added_q, norm_added_k`, `ff[_context].net.0.proj`, `ff[_context].net.2`; every
+        quantized linear X has X.weight, X.bias and the fp32 scalar X_input_scale."""
+        dev = torch.device(device)
+        g = lambda name: state_dict[prefix + name]
+
+        def lin(name):
+            return _Fp8Weight(g(name + ".weight"), g(name + ".bias"), g(name + "_input_scale"), dev, self.dtype)
+
+        def stream(norm, qkv, out, nq, nk, ff):
+            w = {"qkv": lin(qkv), "out": lin(out), "ff1": lin(ff + ".net.0.proj"), "ff2": lin(ff + ".net.2")}
+            if self.quant_level == FP8_W8A8_FULL:
+                w["norm"] = {"fp8": lin(norm + ".linear")}
+            else:
+                w["norm"] = {"w": g(norm + ".linear.weight").to(device=dev, dtype=self.dtype).contiguous(),
+                             "b": g(norm + ".linear.bias").to(device=dev, dtype=self.dtype).contiguous()}
+            w["qk_scale"] = torch.cat([g(nq).reshape(-1), g(nk).reshape(-1)]).to(device=dev, dtype=self.dtype).contiguous()
+            return w
+
+        self._w = {
+            "img": stream("norm1", "attn.to_qkv", "attn.to_out.0", "attn.norm_q.weight", "attn.norm_k.weight", "ff"),
+            "txt": stream("norm1_context", "attn.to_added_qkv", "attn.to_add_out", "attn.norm_added_q.weight",
+                          "attn.norm_added_k.weight", "ff_context"),
+        }
+
+    def _pre_attention(self, w, x, temb):
+        B, S, D = x.shape
+        mod = _modulation(self, w["norm"], temb, 6)
+        norm_q = torch.empty(B * S, D, dtype=torch.uint8, device=x.device)
+        ops.invoke_layer_norm_with_shift_and_scale(None, x, mod[1], mod[0], eps=1e-6, qf8=norm_q, f8_scale=w["qkv"].input_scale)
+        qkv = torch.empty(B * S, 3 * D, dtype=self.dtype, device=x.device)
+        ops.gemm_with_residual_and_bias_fp8(w["qkv"].qweight, w["qkv"].w_scale, norm_q, w["qkv"].input_scale, qkv, bias=w["qkv"].bias)
+        return mod, qkv
+
+    def _post_attention(self, w, x, attn, mod):
+        B, S, D = x.shape
+        T = B * S
+        dev, dt = x.device, self.dtype
+        aq = torch.empty(T, D, dtype=torch.uint8, device=dev)
+        ops.invoke_cuda_d2d_scale_cpy_convert(aq, attn, w["out"].input_scale)
+        y = torch.empty(T, D, dtype=dt, device=dev)
+        ops.gemm_with_residual_and_bias_fp8(w["out"].qweight, w["out"].w_scale, aq, w["out"].input_scale, y, bias=w["out"].bias)
+        h = torch.empty_like(x)
+        ops.invoke_fused_gate_and_residual(h, y.view(B, S, D), mod[2], x)
+        nq = torch.empty(T, D, dtype=torch.uint8, device=dev)
+        ops.invoke_layer_norm_with_shift_and_scale(None, h, mod[4], mod[3], eps=1e-6, qf8=nq, f8_scale=w["ff1"].input_scale)
+        f1 = torch.empty(T, w["ff1"].n, dtype=torch.uint8, device=dev)
+        ops.gemm_fp8_quant_out(w["ff1"].qweight, w["ff1"].w_scale, nq, w["ff1"].input_scale, f1, w["ff2"].input_scale, dt,
+                               bias=w["ff1"].bias, is_gelu=True)
+        ops.gemm_with_residual_and_bias_fp8(w["ff2"].qweight, w["ff2"].w_scale, f1, w["ff2"].input_scale, y, bias=w["ff2"].bias)
+        out = torch.empty_like(x)
+        ops.invoke_fused_gate_and_residual(out, y.view(B, S, D), mod[5], h)
+        return out
+
+    def forward(self, hidden_states, encoder_hidden_states, rope_emb, temb):
+        """hidden_states [B, S_img, D], encoder_hidden_states [B, S_txt, D], rope_emb over the S_txt + S_img joint
+        sequence (text first) with B * (S_txt + S_img) * head_dim * 2 elements, temb [B, D] SiLU'd.
+        Returns [hidden_out, encoder_out]."""
+        if self._w is None:
+            raise RuntimeError("weights not loaded")
+        for t in (hidden_states, encoder_hidden_states, rope_emb, temb):
+            if not (t.is_cuda and t.is_contiguous() and t.dtype == self.dtype):
+                raise RuntimeError("inputs must be contiguous CUDA tensors of the inference dtype")
+        B, S, D = hidden_states.shape
+        E = encoder_hidden_states.shape[1]
+        if D != self.dim or encoder_hidden_states.shape[0] != B or encoder_hidden_states.shape[2] != D or \
+                tuple(temb.shape) != (B, D) or rope_emb.numel() != B * (S + E) * self.head_dim * 2:
+            raise RuntimeError("shape mismatch")
+        wi, wt = self._w["img"], self._w["txt"]
+        mod_i, qkv_i = self._pre_attention(wi, hidden_states, temb)
+        mod_t, qkv_t = self._pre_attention(wt, encoder_hidden_states, temb)
+        # joint sequence [B, E + S, 3, H, Dh], text first (invokeFusedRmsNormCatAndRope, flux_apply_rope.cu:78-156)
+        tot = E + S
+        joint = torch.empty(B, tot, 3 * D, dtype=self.dtype, device=hidden_states.device)
+        rope = rope_emb.view(B, tot, self.head_dim * 2)
+        qt, qi = qkv_t.view(B, E, 3 * D), qkv_i.view(B, S, 3 * D)
+        for b in range(B):
+            ops.invoke_fused_rmsnorm_and_rope(joint[b, :E], qt[b], wt["qk_scale"], rope[b, :E], 1e-6, 1, E, self.heads, self.head_dim)
+            ops.invoke_fused_rmsnorm_and_rope(joint[b, E:], qi[b], wi["qk_scale"], rope[b, E:], 1e-6, 1, S, self.heads, self.head_dim)
+        v5 = joint.view(B, tot, 3, self.heads, self.head_dim)
+        q, k, v = (v5[:, :, i].transpose(1, 2) for i in range(3))
+        attn = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, tot, D)
+        attn_t = attn[:, :E].reshape(B * E, D)
+        attn_i = attn[:, E:].reshape(B * S, D)
+        out_i = self._post_attention(wi, hidden_states, attn_i.contiguous(), mod_i)
+        out_t = self._post_attention(wt, encoder_hidden_states, attn_t.contiguous(), mod_t)
+        return [out_i, out_t]
 
     __call__ = forward

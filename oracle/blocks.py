@@ -61,3 +61,57 @@ def flux_single_block(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_scale
     y = _fp8_linear(cat, g("proj_out.weight").to(dt), g("proj_out.bias").to(dt), g("proj_out_input_scale"), dt, cache=cache, key="out")
     out = _n.gate_residual(y.reshape(B, S, D), gate, hidden)
     return out, {"msa": msa, "norm": norm, "qkv": qkv, "attn": attn, "mlp": mlp, "y": y}
+
+
+def flux_double_block(hidden, encoder, rope, temb, sd, prefix, heads, head_dim, quant_level=1, cache=None):
+    """Double-stream block: FluxTransformerFP8Block<T>::forward
+    (src/lyradiff/layers/flux_transformer_block/FluxTransformerFP8Block.cc:155-245) with FluxAttentionFP8Processor
+    (layers/flux_attention_processor/FluxAttentionFP8Processor.cc:140-340) and FluxAttnPostFP8Processor
+    (layers/flux_attn_post_processor/FluxAttnPostFP8Processor.cc:90-205).  hidden [B, S, D] (image), encoder [B, E, D]
+    (text), rope [B, E + S, head_dim/2, 2, 2] over the joint sequence with the text first.  Returns (hidden_out, encoder_out)."""
+    dt = hidden.dtype
+    B, S, D = hidden.shape
+    E = encoder.shape[1]
+    g = lambda name: sd[prefix + name]
+    cache = {} if cache is None else cache
+
+    def lin(x, name, gelu=False):
+        return _fp8_linear(x, g(name + ".weight").to(dt), g(name + ".bias").to(dt), g(name + "_input_scale"), dt, gelu=gelu,
+                           cache=cache, key=name)
+
+    def modulation(norm):
+        if quant_level == 2:
+            msa = lin(temb, norm + ".linear")
+        else:
+            msa = (temb.double() @ g(norm + ".linear.weight").to(dt).double().t() + g(norm + ".linear.bias").to(dt).double()).to(dt)
+        return msa.chunk(6, dim=1)
+
+    streams = {"img": (hidden, "norm1", "attn.to_qkv", "attn.to_out.0", "attn.norm_q.weight", "attn.norm_k.weight", "ff"),
+               "txt": (encoder, "norm1_context", "attn.to_added_qkv", "attn.to_add_out", "attn.norm_added_q.weight",
+                       "attn.norm_added_k.weight", "ff_context")}
+    mods, qkvs = {}, {}
+    rope_j = rope.reshape(B, E + S, head_dim // 2, 2, 2)
+    for key, (x, norm, qkv_name, _, nq, nk, _) in streams.items():
+        mod = modulation(norm)
+        n = _n.adaln_modulate(x, mod[1], mod[0], eps=1e-6).reshape(-1, D)
+        qkv = lin(n, qkv_name)
+        scale = torch.cat([g(nq).reshape(-1), g(nk).reshape(-1)]).to(dt)
+        L = x.shape[1]
+        r = (rope_j[:, :E] if key == "txt" else rope_j[:, E:]).reshape(B * L, head_dim // 2, 2, 2)
+        qkvs[key] = _n.rmsnorm_rope(qkv, scale, r, heads, head_dim, eps=1e-6).reshape(B, L, 3 * D)
+        mods[key] = mod
+    joint = torch.cat([qkvs["txt"], qkvs["img"]], dim=1).reshape(B, E + S, 3, heads, head_dim)
+    q, k, v = (joint[:, :, i].transpose(1, 2) for i in range(3))
+    attn = attention(q, k, v).transpose(1, 2).reshape(B, E + S, D).to(dt)
+    outs = {}
+    for key, (x, _, _, out_name, _, _, ff) in streams.items():
+        mod = mods[key]
+        a = (attn[:, :E] if key == "txt" else attn[:, E:]).reshape(-1, D)
+        L = x.shape[1]
+        y = lin(a, out_name).reshape(B, L, D)
+        h = _n.gate_residual(y, mod[2], x)
+        n2 = _n.adaln_modulate(h, mod[4], mod[3], eps=1e-6).reshape(-1, D)
+        f1 = lin(n2, ff + ".net.0.proj", gelu=True)
+        f2 = lin(f1, ff + ".net.2").reshape(B, L, D)
+        outs[key] = _n.gate_residual(f2, mod[5], h)
+    return outs["img"], outs["txt"]

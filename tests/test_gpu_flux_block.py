@@ -1,4 +1,4 @@
-"""GPU parity test of the FLUX single-stream block mirror (lyradiff_b200.flux_blocks) against the CPU oracle block.
+"""GPU parity tests of the FLUX single-stream and double-stream block mirrors (lyradiff_b200.flux_blocks) against the CPU oracle block.
 
 Both sides quantize with the same static scales and the same e4m3 arithmetic, so what differs is rounding inside the
 block: bf16 library attention against an exact softmax, fp32 tensor-core sums against fp64, and the e4m3 codes that
@@ -66,6 +66,62 @@ def test_single_block_against_oracle(level, B, S):
     assert amp > 0.05                         # the block does something in this test
     assert float(err.mean()) <= 0.02 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
     assert float(err.max()) <= 0.25 * float(wdelta.abs().max()), float(err.max())
+
+
+def _double_state_dict(prefix, D, head_dim, level, g):
+    sd = {}
+
+    def lin(name, n, k, std, scale):
+        sd[prefix + name + ".weight"] = (torch.randn(n, k, generator=g) * std).bfloat16()
+        sd[prefix + name + ".bias"] = (torch.randn(n, generator=g) * 0.02).bfloat16()
+        sd[prefix + name + "_input_scale"] = torch.tensor([scale])
+
+    for norm in ("norm1", "norm1_context"):
+        lin(norm + ".linear", 6 * D, D, 0.03, 0.01)
+    for qkv in ("attn.to_qkv", "attn.to_added_qkv"):
+        lin(qkv, 3 * D, D, 0.05, 0.02)
+    for out in ("attn.to_out.0", "attn.to_add_out"):
+        lin(out, D, D, 0.05, 0.01)
+    for ff in ("ff", "ff_context"):
+        lin(ff + ".net.0.proj", 4 * D, D, 0.05, 0.02)
+        lin(ff + ".net.2", D, 4 * D, 0.03, 0.02)
+    for n in ("attn.norm_q.weight", "attn.norm_k.weight", "attn.norm_added_q.weight", "attn.norm_added_k.weight"):
+        sd[prefix + n] = (1.0 + 0.1 * torch.randn(head_dim, generator=g)).bfloat16()
+    if level != 2:
+        for norm in ("norm1", "norm1_context"):
+            del sd[prefix + norm + ".linear_input_scale"]
+    return sd
+
+
+@pytest.mark.parametrize("level", [1, 2])
+@pytest.mark.parametrize("B,S,E", [(1, 128, 48), (2, 64, 24)])
+def test_double_block_against_oracle(level, B, S, E):
+    from lyradiff_b200 import flux_blocks
+    D, heads, head_dim = 256, 2, 128
+    g = torch.Generator().manual_seed(7 * level + S)
+    prefix = "transformer_blocks.3."
+    sd = _double_state_dict(prefix, D, head_dim, level, g)
+    hidden = torch.randn(B, S, D, generator=g).bfloat16()
+    encoder = torch.randn(B, E, D, generator=g).bfloat16()
+    temb = torch.nn.functional.silu(torch.randn(B, D, generator=g)).bfloat16()
+    ang = torch.rand(B, E + S, head_dim // 2, generator=g) * 6.28
+    rope = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+        B, E + S, head_dim // 2, 2, 2).bfloat16()
+
+    op = flux_blocks.FluxTransformerBlockOp("bf16", D, heads, head_dim, 4, level)
+    op.initialize(flux_blocks.LyraDiffCommonContext())
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    out_i, out_t = op.forward(cu(hidden), cu(encoder), cu(rope), cu(temb))
+    check_status()
+    want_i, want_t = blocks.flux_double_block(hidden, encoder, rope, temb, sd, prefix, heads, head_dim, level)
+    for got, want, x in ((out_i, want_i, hidden), (out_t, want_t, encoder)):
+        assert tuple(got.shape) == tuple(x.shape) and got.dtype == torch.bfloat16
+        delta, wdelta = got.cpu().float() - x.float(), want.float() - x.float()
+        err = (delta - wdelta).abs()
+        amp = float(wdelta.abs().mean())
+        assert amp > 0.02
+        assert float(err.mean()) <= 0.03 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
+        assert float(err.max()) <= 0.3 * float(wdelta.abs().max()), float(err.max())
 
 
 def test_block_refuses_what_is_not_built():
