@@ -10,6 +10,7 @@ with its fused epilogue.  Other cases time the remaining configurations with the
     int8_sdxl    SDXL GEGLU-FF INT8 SmoothQuant linear, M=8192 K=640 N=5120 (dynamic per-token quantize + GEMM)
     w4a4         FLUX fused W4A4 linear, M=4608 K=3072 N=21504 (int4 group-64 quantize + GEMM)
     flux_block   one FLUX single-stream block through FluxSingleTransformerBlockOp (FP8 linears + library attention)
+    flux_forward the FLUX.1-dev block stack (19 double + 38 single blocks, own weights each): ms per denoising step
     sdxl_ff      the whole SDXL GEGLU feed-forward block in INT8 (four launches)
     adaln_quant  fused AdaLN-modulation + int8 and e4m3 quantize of [4608, 3072] bf16
 `--tokens` shrinks M (for profiler captures).  Synthetic seeded inputs, random weights.  Rank 0 prints ONE JSON line.
@@ -488,6 +489,98 @@ class FluxBlock:
     cpu_note = "oracle block with weights quantized once: fp64 contractions of the e4m3 operands and exact attention over the sample's own rows"
 
 
+class FluxForward(FluxBlock):
+    """configs[4] without the embedders: the FLUX.1-dev block stack, 19 double-stream + 38 single-stream blocks, every
+    block with its own random FP8 weights, one image (4096 image + 512 text tokens) per GPU."""
+    name = "flux_forward"
+    metric = "flux_block_stack_throughput"
+    N_DOUBLE, N_SINGLE, TXT = 19, 38, 512
+
+    def __init__(self, tokens):
+        FluxBlock.__init__(self, tokens)
+        self.blocks = self.N_DOUBLE + self.N_SINGLE
+        self.lin_flops *= self.blocks
+        self.attn_flops *= self.blocks
+        self.work_per_step = self.lin_flops + self.attn_flops
+        self.workload = ("configs[4] block stack: FLUX.1-dev architecture, %d double-stream + %d single-stream blocks, FP8_W8A8, "
+                         "random weights (each block its own), 1 image per GPU = %d image + %d text tokens, hidden 3072, "
+                         "24 x 128 heads; one step = one pass through the stack = %.1f TFLOP (embedders and final layer left out); "
+                         "ms_per_step is the reference's denoising-step time for the stack"
+                         % (self.N_DOUBLE, self.N_SINGLE, self.tokens - self.TXT, self.TXT, self.work_per_step / 1e12))
+        self.launches_per_step = self.N_DOUBLE * 20 + self.N_SINGLE * 9
+        self.timed_names = ["stack_forward"]
+        self.timed_work = [self.work_per_step]
+        self.roof["kernel"] = "whole stack: 57 blocks, each 3 or 8 gemm_tcgen05_kernel<f8f6f4> launches + element-wise kernels of this " \
+                              "library, plus library attention and the small modulation matmuls"
+
+    def setup_gpu(self, dev):
+        from lyradiff_b200 import flux_blocks
+        D, M, DH = self.D, self.MLP, self.DH
+        g = torch.Generator(device=dev).manual_seed(0)
+
+        def lin(sd, name, n, k, scale=0.03):
+            sd[name + ".weight"] = (torch.randn(n, k, generator=g, device=dev, dtype=torch.float32) * 0.02).bfloat16()
+            sd[name + ".bias"] = (torch.randn(n, generator=g, device=dev, dtype=torch.float32) * 0.02).bfloat16()
+            sd[name + "_input_scale"] = torch.tensor([scale])
+
+        ctx = flux_blocks.LyraDiffCommonContext()
+        self.double, self.single = [], []
+        for i in range(self.N_DOUBLE):
+            sd = {}
+            for norm in ("norm1", "norm1_context"):
+                lin(sd, norm + ".linear", 6 * D, D)
+            for a, b in (("attn.to_qkv", "attn.to_out.0"), ("attn.to_added_qkv", "attn.to_add_out")):
+                lin(sd, a, 3 * D, D)
+                lin(sd, b, D, D)
+            for ff in ("ff", "ff_context"):
+                lin(sd, ff + ".net.0.proj", 4 * D, D)
+                lin(sd, ff + ".net.2", D, 4 * D)
+            for n in ("attn.norm_q.weight", "attn.norm_k.weight", "attn.norm_added_q.weight", "attn.norm_added_k.weight"):
+                sd[n] = torch.ones(DH, device=dev).bfloat16()
+            op = flux_blocks.FluxTransformerBlockOp("bf16", D, self.H, DH, 4, 1)
+            op.initialize(ctx)
+            op.reload_model_from_state_dict("", sd, dev)
+            self.double.append(op)
+            del sd
+        for i in range(self.N_SINGLE):
+            sd = {}
+            lin(sd, "norm.linear", 3 * D, D)
+            lin(sd, "attn.to_qkv", 3 * D, D)
+            lin(sd, "proj_mlp", M * D, D)
+            lin(sd, "proj_out", D, (M + 1) * D)
+            sd["attn.norm_q.weight"] = torch.ones(DH, device=dev).bfloat16()
+            sd["attn.norm_k.weight"] = torch.ones(DH, device=dev).bfloat16()
+            op = flux_blocks.FluxSingleTransformerBlockOp("bf16", D, self.H, DH, M, 1)
+            op.initialize(ctx)
+            op.reload_model_from_state_dict("", sd, dev)
+            self.single.append(op)
+            del sd
+        cg = _gen()
+        x, temb, rope = self._inputs(cg, self.tokens)
+        img = x[:, self.TXT:].contiguous()
+        self.txt = (torch.randn(1, self.TXT, D, generator=cg)).bfloat16().to(dev)
+        self.x, self.temb, self.rope = img.to(dev), temb.to(dev), rope.to(dev)
+        self.y = torch.empty(1, self.tokens, D, dtype=torch.bfloat16, device=dev)
+        self.h_in = img.pin_memory()
+        self.e2e_x = [self.x, torch.empty_like(self.x)]
+        self.e2e_y = [self.y, torch.empty_like(self.y)]
+
+    def step(self, events=None, io=None):
+        img = self.x if io is None else io[0]
+        if events is not None:
+            events[0][0].record()
+        txt = self.txt
+        for op in self.double:
+            img, txt = op.forward(img, txt, self.rope, self.temb)
+        h = torch.cat([txt, img], dim=1)
+        for op in self.single:
+            h = op.forward(h, self.rope, self.temb)
+        if events is not None:
+            events[0][1].record()
+        if io is not None:
+            io[1].copy_(h)
+
+
 class W4A4:
     """configs[2]: FLUX fused W4A4 linear."""
     name = "w4a4"
@@ -632,7 +725,7 @@ class AdalnQuant:
     cpu_note = "LayerNorm + modulation + int8 and e4m3 quantize"
 
 
-CASES = {c.name: c for c in (FluxFp8, FluxBlock, Int8Sdxl, SdxlFF, W4A4, AdalnQuant)}
+CASES = {c.name: c for c in (FluxFp8, FluxBlock, FluxForward, Int8Sdxl, SdxlFF, W4A4, AdalnQuant)}
 
 
 # =================================================================================================== CPU arm
