@@ -251,7 +251,7 @@ LYRAQ_API int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* s
                     void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------ between the linears of a FLUX block
- * (SURVEY "next" rows: the callers either side of the quantized-linear path) */
+ * (the callers either side of the quantized-linear path) */
 
 /* QK RMSNorm + rotary embedding on the packed QKV projection: qkv [batch, seq, 3, heads, head_dim] (q heads, k heads,
  * v heads), scale [2, head_dim] (q then k), rope [batch * seq, head_dim / 2, 2, 2]; q and k heads are normalised

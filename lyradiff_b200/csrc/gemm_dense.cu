@@ -8,12 +8,13 @@
 // CTA's 128 x 256 tile.  Roles per CTA:
 //   warp 0    : TMA producer  - streams 128 x 128-byte A tiles and B tiles into a ring of shared-memory stages
 //                               (128-byte swizzle), one mbarrier per stage.
-//   warp 1    : MMA issuer    - one thread issues four tcgen05.mma (K = 32 bytes each) per stage into one of two
-//                               accumulator buffers in tensor memory, and commits to free the stage.
+//   warp 1    : MMA issuer    - one thread issues the stage's tcgen05.mma (K = 32 bytes each; four per K block, and a
+//                               stage of a pair or of the 128-wide tile holds two K blocks) into one of two accumulator
+//                               buffers in tensor memory, and commits to free the stage.
 //   warp 2    : allocates / frees tensor memory.
 //   warps 4-11: epilogue      - warp w reads TMEM lanes 32 (w % 4).. and the column half (w - 4) / 4.  Per tile the
-//                               eight warps first stage the tile's column scales and bias in shared memory (one
-//                               coalesced load, one named barrier), then stream 32-column chunks: tcgen05.ld of chunk
+//                               each warp first stages its half-tile's column scales and bias in its own piece of
+//                               shared memory (no barrier across warps), then streams 32-column chunks: tcgen05.ld of chunk
 //                               c+1 is in flight while chunk c gets its scales / bias / GELU / residual in registers;
 //                               16-bit results go through a 64-byte-swizzled shared-memory box and leave with one TMA
 //                               store per chunk (full 64-byte row segments, rows and columns clipped by the hardware).
@@ -550,7 +551,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
             int m_blk, n_blk;
             tile_coords(tile, p.m_tiles, p.n_tiles, m_blk, n_blk);
-            // column parameters of the tile, staged while the main loop of this tile may still be running
             // column parameters of this warp's half of the tile, staged while the main loop of the tile may still run
             __syncwarp();
 #pragma unroll

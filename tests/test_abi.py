@@ -80,6 +80,19 @@ def test_bad_arguments_are_refused_without_a_device(lib):
     assert lib.lyraq_gemm_int8(p, p, p, p, 5, p, 0, None, 128, 128, 128, None, 0, None) == INVALID
     assert lib.lyraq_gemm_fp8(p, p, p, p, p, 3, None, None, 1.0, 0.0, 0, 128, 128, 128, None, 0, None) == INVALID
     assert lib.lyraq_gemm_w4a4(p, p, p, p, 2, p, 1, None, 2, None, None, None, 0, 128, 128, 96, None, 0, None) == UNSUPPORTED
+    # the kernels between the linears of a block
+    assert lib.lyraq_rmsnorm_rope(None, None, None, None, 1, 1e-6, 1, 8, 2, 128, None) == INVALID
+    assert lib.lyraq_rmsnorm_rope(p, p, p, p, 1, 1e-6, 1, 8, 2, 96, None) == UNSUPPORTED      # head_dim 64 or 128 only
+    assert lib.lyraq_rmsnorm_rope(p, p, p, p, 2, 1e-6, 1, 8, 2, 128, None) == UNSUPPORTED     # fp32
+    assert lib.lyraq_rmsnorm_rope(p, p, p, p, 1, 1e-6, 0, 8, 2, 128, None) == 0               # empty
+    assert lib.lyraq_quant_fp8_2d(p, 64, p, 1, p, 4, 128, None) == INVALID                    # row pitch below the width
+    assert lib.lyraq_quant_fp8_2d(p, 256, p, 1, p, 4, 100, None) == UNSUPPORTED               # cols % 8
+    assert lib.lyraq_gate_residual(p, p, None, p, 1, 1, 8, 256, None) == INVALID
+    assert lib.lyraq_gate_residual(p, p, p, p, 1, 1, 8, 100, None) == UNSUPPORTED             # dim % 8
+    assert lib.lyraq_gemm_fp8_quant_ld(p, p, p, p, p, 64, p, 1, None, None, 1.0, 0.0, 0, 128, 128, 128, None, 0, None) == INVALID
+    assert lib.lyraq_gemm_fp8_quant_ld(p, p, p, p, p, 256, p, 1, None, p, 1.0, 1.0, 0, 128, 128, 128, None, 0, None) == UNSUPPORTED
+    assert lib.lyraq_weight_quant_fp8(None, p, p, 1, 64, None) == INVALID
+    assert lib.lyraq_gemm_int8_residual(p, p, p, p, 0, p, 3, None, p, 128, 128, 128, None, 0, None) == INVALID  # no int32 form
     # empty problems are a no-op
     assert lib.lyraq_gemm_int8(p, p, p, p, 0, p, 0, None, 0, 128, 128, None, 0, None) == 0
     assert lib.lyraq_quant_fp8(p, p, 1, p, 1, 0, None) == 0
