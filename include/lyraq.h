@@ -151,6 +151,14 @@ LYRAQ_API int lyraq_adaln_quant(void* y, int8_t* q8, float* q8_scale, uint8_t* q
                       const void* x, const void* scale, const void* shift, int dtype,
                       const float* pre_quant_scale, size_t B, size_t S, size_t D, double eps, void* stream);
 
+/* lyraq_adaln_quant with two e4m3 outputs of the same modulated row, each with its own static scale: in the FLUX
+ * single-stream block the AdaLN output feeds both to_qkv and proj_mlp, whose calibrated input scales differ, and the
+ * reference quantizes it twice (FluxSingleAttentionFP8Processor.cc:155 and FluxSingleTransformerFP8Block.cc:216 of
+ * src/lyradiff/layers/...).  y (the 16-bit result) may be NULL. */
+LYRAQ_API int lyraq_adaln_quant_fp8x2(void* y, uint8_t* qa, const float* scale_a, uint8_t* qb, const float* scale_b,
+                                      const void* x, const void* scale, const void* shift, int dtype, size_t B, size_t S,
+                                      size_t D, double eps, void* stream);
+
 /* (residual + bias +) LayerNorm(gamma, beta) -> int8 with a static scalar scale.
  * Replaces invokeLayerNormInt8O<T> and invokeFusedResidualBiasLayerNormInt8O<T>
  * (src/lyradiff/kernels/quant_kernels/layer_norm_int8.h:9-38; launchers layer_norm_int8.cu:558-679).
@@ -212,6 +220,17 @@ LYRAQ_API int lyraq_gemm_int8_residual(const int8_t* A, const int8_t* B, const f
 LYRAQ_API int lyraq_gemm_fp8(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, void* Y, int c_dtype,
                    const void* bias, const void* residual, float alpha, float beta, int epilogue,
                    int m, int n, int k, void* workspace, size_t workspace_bytes, void* stream);
+
+/* FP8 GEMM with the block's gate and residual fused in: Y[m,n] = T( T( T(s_w*s_x*acc + bias[n]) * gate[b,n] ) + R[m,n] ),
+ * b = m / rows_per_batch, every step rounded to T as the reference's separate kernel does.  Replaces
+ * GemmWithResidualAndBias followed by invokeFusedGateAndResidual<T>
+ * (src/lyradiff/layers/flux_single_transformer_block/FluxSingleTransformerFP8Block.cc:262-303;
+ * kernel flux_single_transformer_kernels.cu:43-65).  gate of type T [batches, n]; R of type T [m,n] or NULL; Y may alias R.
+ * When m spans several batch entries rows_per_batch must be a multiple of 256 (LYRAQ_ERR_UNSUPPORTED otherwise: use
+ * lyraq_gemm_fp8 + lyraq_gate_residual). */
+LYRAQ_API int lyraq_gemm_fp8_gate(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, void* Y, int c_dtype,
+                                  const void* bias, const void* gate, const void* residual, int rows_per_batch, int m, int n,
+                                  int k, void* workspace, size_t workspace_bytes, void* stream);
 
 /* lyraq_gemm_fp8 with the activation quantize of the NEXT FP8 linear fused into the epilogue:
  * Yq[m,n] = e4m3_rne_satfinite( float( T( epi(...) ) ) / y_scale[0] ), T = dtype (the type of bias and residual, and the

@@ -32,6 +32,8 @@ SIGNATURES = {
     "lyraq_weight_quant_int4_g64": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_size_t, c_size_t, c_void_p]),
     "lyraq_adaln_quant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                   c_void_p, c_size_t, c_size_t, c_size_t, c_double, c_void_p]),
+    "lyraq_adaln_quant_fp8x2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_size_t, c_size_t, c_size_t, c_double, c_void_p]),
     "lyraq_ln_quant_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                     c_void_p, c_size_t, c_size_t, c_double, c_void_p]),
     "lyraq_geglu_quant_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t, c_size_t,
@@ -43,6 +45,8 @@ SIGNATURES = {
                                          c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_gemm_fp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float,
                                c_float, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "lyraq_gemm_fp8_gate": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                    c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_gemm_fp8_quant": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                      c_float, c_float, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_gemm_fp8_quant_ld": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_int, c_void_p,

@@ -126,6 +126,18 @@ __device__ __forceinline__ Vec16 ld_nc_16(const void* p)
 }
 
 // Same, for vectors that every row re-reads (modulation scale / shift, gamma / beta, bias): kept in L1.
+// A 16-byte load that stays where it is written (the compiler may not sink it towards its first use), for loads that
+// are issued ahead of time on purpose; and a prefetch of one 128-byte line into L2.
+__device__ __forceinline__ Vec16 ld_nc_16_here(const void* p)
+{
+    Vec16 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+                 : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
 __device__ __forceinline__ Vec16 ld_nc_16_keep(const void* p)
 {
     Vec16 v;

@@ -79,6 +79,9 @@ struct EpilogueParams {
     int          gelu;
     // optional fused output quantize: C receives e4m3 codes of T(result) / out_q_scale[0] instead of T values
     const float* out_q_scale;
+    // optional gate (fp8, 16-bit outputs): y = T(T(T(acc * scale + bias) * gate[batch, n]) + R), gate of type T [batches, N]
+    const void*  gate;
+    int          rows_per_batch;
 };
 
 struct GemmParams {
@@ -231,7 +234,7 @@ __device__ __forceinline__ void epilogue_math(const EpilogueParams& e, const uin
 // The same chunk for 16-bit outputs, in packed arithmetic throughout: two columns per instruction (fp32 pairs with
 // IEEE rounding per lane, then the output type's native paired add), result as 16 words of two T values.
 // bias2: the chunk's bias as stored (pairs of T); res: the chunk's residual row segment (four 16-byte vectors).
-template<int KIND, typename T>
+template<int KIND, typename T, bool RES>
 __device__ __forceinline__ void epilogue_math16(const EpilogueParams& e, const uint32_t* acc, const float2* colp, const uint32_t* bias2,
                                                 float row_scale, float fp8_scale, bool has_res, const Vec16* res, uint32_t* o)
 {
@@ -244,7 +247,7 @@ __device__ __forceinline__ void epilogue_math16(const EpilogueParams& e, const u
             const float2 sc2 = mul_f32x2(make_float2(c.x, c.z), rs2);          // s_w * s_a first, as the reference does
             const float2 y2  = mul_f32x2(make_float2((float)(int)acc[2 * i], (float)(int)acc[2 * i + 1]), sc2);
             uint32_t     h   = P2::from_f32(y2.x, y2.y);                       // T(acc * scale)
-            if (has_res) {
+            if (RES && has_res) {
                 h = P2::add(h, res[i >> 2].w[i & 3]);                          // T(T(acc * scale) + R)
             }
             if (e.bias != nullptr) {
@@ -259,7 +262,19 @@ __device__ __forceinline__ void epilogue_math16(const EpilogueParams& e, const u
         for (int i = 0; i < 16; ++i) {
             const float4 c = *reinterpret_cast<const float4*>(colp + 2 * i);
             float2       t = mul_f32x2(make_float2(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1])), fs2);
-            if (has_res) {
+            if (RES && e.gate != nullptr) {
+                // the linear's own 16-bit result, then the gate and the residual in T arithmetic, as the reference's
+                // separate kernel applies them: T(T(y * gate) + R); c.x / c.z hold the gate of the two columns
+                const uint32_t y = P2::from_f32(t.x + c.y, t.y + c.w);
+                const float2   g = mul_f32x2(P2::to_f32(y), make_float2(c.x, c.z));  // exact product of two T values
+                uint32_t       h = P2::from_f32(g.x, g.y);
+                if (has_res) {
+                    h = P2::add(h, res[i >> 2].w[i & 3]);
+                }
+                o[i] = h;
+                continue;
+            }
+            if (RES && has_res) {
                 t = fma_f32x2(be2, P2::to_f32(res[i >> 2].w[i & 3]), t);
             }
             t = add_f32x2(t, make_float2(c.y, c.w));
@@ -272,7 +287,9 @@ __device__ __forceinline__ void epilogue_math16(const EpilogueParams& e, const u
     }
 }
 
-template<int KIND, int BLOCK_N, int CTAS>
+// RES: the instance carries the residual / gate code of the epilogue.  Problems without a residual run an instance
+// without it: the extra registers and branches cost the GELU + quantize epilogue of the MLP linear 15-20 %.
+template<int KIND, int BLOCK_N, int CTAS, bool RES>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const GemmParams p)
@@ -562,6 +579,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     if (KIND == KIND_I8 && e.col_scale != nullptr) {
                         v.x = __ldg(e.col_scale + col);
                     }
+                    if (RES && KIND == KIND_F8 && e.gate != nullptr) {
+                        // all rows of a tile belong to one batch entry (checked on the host)
+                        const size_t   gi = (size_t)((m_blk * kTileM) / e.rows_per_batch) * (size_t)p.N + (size_t)col;
+                        const uint16_t gr = reinterpret_cast<const uint16_t*>(e.gate)[gi];
+                        v.x = (e.c_dtype == LYRAQ_BF16) ? __uint_as_float((uint32_t)gr << 16) : __half2float(__ushort_as_half(gr));
+                    }
                     if (e.bias != nullptr) {
                         if (e.c_dtype == LYRAQ_F32) {
                             v.y = reinterpret_cast<const float*>(e.bias)[col];
@@ -575,6 +598,51 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 b16[cc]     = raw;
             }
             __syncwarp();
+            // 16-bit residual: this thread's row segment of the tile is asked into L2 now, while the main loop of the tile
+            // still runs, and chunk c + 1's 64 bytes are fetched into registers while chunk c is computed, so that the
+            // epilogue does not stand on a DRAM round trip in front of every chunk
+            const int  row_r    = m_blk * kTileM + (int)rank * kBlockM + quad * 32 + lane;
+            const bool res16    = RES && e.residual != nullptr && e.c_dtype != LYRAQ_F32 && e.c_dtype != LYRAQ_S32;
+            const bool vec_ok_r = (e.ldc & 7) == 0;
+            Vec16      resb[RES ? 2 : 1][RES ? 4 : 1];
+            auto load_res16 = [&](int c, Vec16* dst) {
+                const int col0r  = n_blk * BLOCK_N + half * kHalfN + c * 32;
+                const int validr = p.N - col0r;
+                if (!res16 || row_r >= p.M || validr <= 0) {
+                    return;
+                }
+                const uint16_t* rrow = reinterpret_cast<const uint16_t*>(e.residual) + (size_t)row_r * e.ldc + col0r;
+                if (vec_ok_r && validr >= 32) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        dst[q] = ld_nc_16_here(rrow + 8 * q);
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int      i0 = 8 * q + 2 * j;
+                            const uint32_t lo = (i0 < validr) ? rrow[i0] : 0u;
+                            const uint32_t hi = (i0 + 1 < validr) ? rrow[i0 + 1] : 0u;
+                            dst[q].w[j]       = lo | (hi << 16);
+                        }
+                    }
+                }
+            };
+            if (res16 && row_r < p.M) {
+                const int      col_h = n_blk * BLOCK_N + half * kHalfN;
+                const uint8_t* seg   = reinterpret_cast<const uint8_t*>(e.residual) + ((size_t)row_r * e.ldc + col_h) * 2;
+#pragma unroll
+                for (int b = 0; b < kHalfN * 2; b += 128) {
+                    if (col_h + b / 2 < p.N) {
+                        prefetch_l2(seg + b);
+                    }
+                }
+            }
+            if (RES) {
+                load_res16(0, resb[0]);
+            }
             // the verdict is made warp-uniform: the tensor-memory loads below need the whole warp
             PROF_T0(t_w2);
             if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag))) {
@@ -632,7 +700,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     continue;
                 }
-                const bool has_res  = e.residual != nullptr;
+                const bool has_res  = RES && e.residual != nullptr;
                 const bool in_range = row < p.M && valid > 0;
                 if (e.c_dtype == LYRAQ_F32) {
                     float v[32];
@@ -647,34 +715,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     continue;
                 }
                 // 16-bit outputs: packed arithmetic, 16 words of two values each
-                uint32_t        o[16];
-                Vec16           res[4];
-                const bool      res_vec = has_res && in_range && vec_ok && valid >= 32;
-                const uint16_t* rrow    = reinterpret_cast<const uint16_t*>(e.residual) + (size_t)row * e.ldc + col0;
-                if (has_res && in_range) {
-                    if (res_vec) {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            res[q] = ld_nc_16(rrow + 8 * q);
-                        }
-                    } else {
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int      i0 = 8 * q + 2 * j;
-                                const uint32_t lo = (i0 < valid) ? rrow[i0] : 0u;
-                                const uint32_t hi = (i0 + 1 < valid) ? rrow[i0 + 1] : 0u;
-                                res[q].w[j]       = lo | (hi << 16);
-                            }
-                        }
-                    }
+                uint32_t     o[16];
+                const Vec16* res = resb[RES ? (c & 1) : 0];
+                if (RES && c + 1 < kChunks) {
+                    load_res16(c + 1, resb[RES ? ((c + 1) & 1) : 0]);
                 }
                 const uint32_t* bias2 = reinterpret_cast<const uint32_t*>(b16 + c * 32);
                 if (e.c_dtype == LYRAQ_BF16) {
-                    epilogue_math16<KIND, __nv_bfloat16>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
+                    epilogue_math16<KIND, __nv_bfloat16, RES>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
                 } else {
-                    epilogue_math16<KIND, __half>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
+                    epilogue_math16<KIND, __half, RES>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
                 }
                 if (e.out_q_scale != nullptr) {
                     // fused activation quantize for the next FP8 linear: the T-rounded result times 1/s, e4m3 RNE satfinite
@@ -931,7 +981,7 @@ static TileChoice pick_tile(int m, int n, int k, int sms)
     return best;
 }
 
-template<int KIND, int BLOCK_N, int CTAS>
+template<int KIND, int BLOCK_N, int CTAS, bool RES>
 static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cudaStream_t stream)
 {
     using S = GemmSmem<BLOCK_N, CTAS>;
@@ -969,7 +1019,7 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
     const long tiles = (long)p.m_tiles * p.n_tiles;
     const long units = sms / CTAS;
     const int  grid  = (int)(tiles < units ? tiles : units) * CTAS;
-    auto       kern  = gemm_tcgen05_kernel<KIND, BLOCK_N, CTAS>;
+    auto       kern  = gemm_tcgen05_kernel<KIND, BLOCK_N, CTAS, RES>;
     const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (attr_err != cudaSuccess) {
         return cuda_status(attr_err, "cudaFuncSetAttribute(gemm_tcgen05_kernel, dynamic shared memory)");
@@ -1020,13 +1070,14 @@ template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams 
     if (g_forced_tile != 0) {
         t = TileChoice{g_forced_tile / 10, g_forced_tile % 10};
     }
+    const bool res = p.epi.residual != nullptr || p.epi.gate != nullptr;
     if (t.ctas == 2) {
-        return launch_gemm<KIND, 256, 2>(A, B, p, sms, stream);
+        return res ? launch_gemm<KIND, 256, 2, true>(A, B, p, sms, stream) : launch_gemm<KIND, 256, 2, false>(A, B, p, sms, stream);
     }
     if (t.block_n == 128) {
-        return launch_gemm<KIND, 128, 1>(A, B, p, sms, stream);
+        return res ? launch_gemm<KIND, 128, 1, true>(A, B, p, sms, stream) : launch_gemm<KIND, 128, 1, false>(A, B, p, sms, stream);
     }
-    return launch_gemm<KIND, 256, 1>(A, B, p, sms, stream);
+    return res ? launch_gemm<KIND, 256, 1, true>(A, B, p, sms, stream) : launch_gemm<KIND, 256, 1, false>(A, B, p, sms, stream);
 }
 
 }  // namespace lyraq
@@ -1135,6 +1186,40 @@ int lyraq_gemm_fp8(const uint8_t* X, const float* s_x, const uint8_t* W, const f
     p.epi.bias     = bias;
     p.epi.residual = residual;
     p.epi.gelu     = (epilogue & LYRAQ_EPI_GELU_TANH) ? 1 : 0;
+    return run_gemm<KIND_F8>(X, W, p, (cudaStream_t)stream);
+}
+
+int lyraq_gemm_fp8_gate(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, void* Y, int c_dtype,
+                        const void* bias, const void* gate, const void* residual, int rows_per_batch, int m, int n, int k,
+                        void* workspace, size_t workspace_bytes, void* stream)
+{
+    (void)workspace;
+    (void)workspace_bytes;
+    if ((c_dtype != LYRAQ_F16 && c_dtype != LYRAQ_BF16) || s_x == nullptr || s_w == nullptr || gate == nullptr ||
+        rows_per_batch <= 0) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (!aligned16(gate)) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    // a tile (up to 256 rows) must not straddle two batch entries, whose gates differ
+    if (m > rows_per_batch && (rows_per_batch % 256) != 0) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    GemmParams p{};
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.epi.C              = Y;
+    p.epi.c_dtype        = c_dtype;
+    p.epi.s_a            = s_x;
+    p.epi.s_b            = s_w;
+    p.epi.alpha          = 1.0f;
+    p.epi.beta           = (residual == nullptr) ? 0.0f : 1.0f;
+    p.epi.bias           = bias;
+    p.epi.residual       = residual;
+    p.epi.gate           = gate;
+    p.epi.rows_per_batch = rows_per_batch;
     return run_gemm<KIND_F8>(X, W, p, (cudaStream_t)stream);
 }
 

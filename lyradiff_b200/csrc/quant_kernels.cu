@@ -30,6 +30,8 @@ struct RowParams {
     int8_t*  q8;               // [rows, dim] or null
     float*   q8_scale;         // in (static/per-token) or out (dynamic)
     uint8_t* qf8;              // [rows, dim] or null
+    uint8_t* qf8b;             // second e4m3 output with its own scale (same y, another consumer), or null
+    const float* f8_scale_b;   // [1]
     int      scale_mode;
     int      f8_invert;
     size_t   rows;
@@ -265,6 +267,10 @@ row_quant_kernel(const RowParams p)
         const float s = __ldg(p.f8_scale);
         f8r           = p.f8_invert ? 1.0f / s : s;
     }
+    float f8rb = 0.0f;
+    if (p.qf8b != nullptr) {
+        f8rb = 1.0f / __ldg(p.f8_scale_b);
+    }
     const bool dynamic = (p.scale_mode == LYRAQ_SCALE_PER_TOKEN_DYNAMIC);
     if (p.q8 != nullptr) {
         if (dynamic) {
@@ -307,6 +313,11 @@ row_quant_kernel(const RowParams p)
                 const uint32_t w0 = f32x2_to_e4m3x2(f[i][0] * f8r, f[i][1] * f8r) | (f32x2_to_e4m3x2(f[i][2] * f8r, f[i][3] * f8r) << 16);
                 const uint32_t w1 = f32x2_to_e4m3x2(f[i][4] * f8r, f[i][5] * f8r) | (f32x2_to_e4m3x2(f[i][6] * f8r, f[i][7] * f8r) << 16);
                 st_8(p.qf8 + off, w0, w1);
+            }
+            if (p.qf8b != nullptr) {
+                const uint32_t w0 = f32x2_to_e4m3x2(f[i][0] * f8rb, f[i][1] * f8rb) | (f32x2_to_e4m3x2(f[i][2] * f8rb, f[i][3] * f8rb) << 16);
+                const uint32_t w1 = f32x2_to_e4m3x2(f[i][4] * f8rb, f[i][5] * f8rb) | (f32x2_to_e4m3x2(f[i][6] * f8rb, f[i][7] * f8rb) << 16);
+                st_8(p.qf8b + off, w0, w1);
             }
             if (p.q8 != nullptr) {
                 if (p.pre != nullptr) {
@@ -773,6 +784,41 @@ int lyraq_adaln_quant(void* y, int8_t* q8, float* q8_scale, uint8_t* qf8, const 
     p.qf8            = qf8;
     p.f8_scale       = f8_scale;
     p.f8_invert      = 1;
+    p.rows           = B * S;
+    p.dim            = (int)D;
+    p.in_cols        = (int)D;
+    p.rows_per_batch = (int)S;
+    p.eps            = (float)eps;
+    return dispatch_row<ROW_ADALN>(dtype, p, (cudaStream_t)stream);
+}
+
+int lyraq_adaln_quant_fp8x2(void* y, uint8_t* qa, const float* scale_a, uint8_t* qb, const float* scale_b, const void* x,
+                            const void* scale, const void* shift, int dtype, size_t B, size_t S, size_t D, double eps, void* stream)
+{
+    if (B * S == 0) {
+        return LYRAQ_OK;
+    }
+    if (x == nullptr || scale == nullptr || shift == nullptr || qa == nullptr || qb == nullptr || scale_a == nullptr ||
+        scale_b == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (!aligned16(x) || !aligned16(scale) || !aligned16(shift) || (y != nullptr && !aligned16(y)) ||
+        (reinterpret_cast<uintptr_t>(qa) & 7u) != 0 || (reinterpret_cast<uintptr_t>(qb) & 7u) != 0) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (D > 16384 || S > 0x7fffffffu) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    RowParams p{};
+    p.x              = x;
+    p.ada_scale      = scale;
+    p.ada_shift      = shift;
+    p.y              = y;
+    p.qf8            = qa;
+    p.f8_scale       = scale_a;
+    p.f8_invert      = 1;
+    p.qf8b           = qb;
+    p.f8_scale_b     = scale_b;
     p.rows           = B * S;
     p.dim            = (int)D;
     p.in_cols        = (int)D;

@@ -9,14 +9,13 @@ method names and tensor conventions, running the FP8 data flow of FluxSingleTran
 (src/lyradiff/layers/flux_single_transformer_block/FluxSingleTransformerFP8Block.cc:162-310) on liblyraq.so:
 
     msa = linear(temb)                       -> shift, scale, gate            (temb arrives SiLU'd, AdaFP8LayerNorm.cc:100)
-    norm = LN(x) * (1 + scale) + shift       -> bf16 and e4m3 in one kernel   (lyraq_adaln_quant)
+    norm = LN(x) * (1 + scale) + shift       -> two e4m3 forms in one kernel  (lyraq_adaln_quant_fp8x2)
     qkv = FP8 GEMM(norm_q8, to_qkv) + bias   -> QK RMSNorm + RoPE in place    (lyraq_gemm_fp8, lyraq_rmsnorm_rope)
     attn = attention(q, k, v)                                                 (torch SDPA: library code, as the reference's
                                                                               flash-attention layer is; not this path)
     cat8[:, :D]  = e4m3(attn)                                                 (lyraq_quant_fp8_2d)
-    cat8[:, D:]  = e4m3(gelu(FP8 GEMM(e4m3(norm), proj_mlp) + bias))          (lyraq_quant_fp8, lyraq_gemm_fp8_quant_ld)
-    y = FP8 GEMM(cat8, proj_out) + bias                                       (lyraq_gemm_fp8)
-    out = gate * y + x                                                        (lyraq_gate_residual)
+    cat8[:, D:]  = e4m3(gelu(FP8 GEMM(e4m3(norm), proj_mlp) + bias))          (lyraq_gemm_fp8_quant_ld)
+    out = gate * (FP8 GEMM(cat8, proj_out) + bias) + x                        (lyraq_gemm_fp8_gate: one launch)
 
 The 16-bit concat buffer and its quantize pass (invokeFusedCatAndGelu + invokeCudaD2DScaleCpyConvert) do not exist here.
 quant_level 1 (FP8_W8A8) keeps the modulation linear in 16 bits (a torch matmul, as the reference calls cuBLAS for it),
@@ -141,11 +140,12 @@ class FluxSingleTransformerBlockOp:
             msa = torch.addmm(w["norm_b"], temb, w["norm_w"].t())
         shift, scale, gate = (c.contiguous() for c in msa.chunk(3, dim=1))
 
-        # ---- AdaLN modulation, 16-bit result and its e4m3 form for to_qkv in one pass
-        norm = self._buffer("norm", (B, S, D), dt, dev)
+        # ---- AdaLN modulation straight into the e4m3 inputs of to_qkv and proj_mlp (their input scales differ); the
+        # 16-bit result is never written
         norm_q = self._buffer("norm_q", (T, D), torch.uint8, dev)
-        ops.invoke_layer_norm_with_shift_and_scale(norm, hidden_states, scale, shift, eps=1e-6, qf8=norm_q,
-                                                   f8_scale=w["qkv"].input_scale)
+        mlp_in = self._buffer("mlp_in", (T, D), torch.uint8, dev)
+        ops.adaln_quant_fp8x2(None, norm_q, w["qkv"].input_scale, mlp_in, w["mlp"].input_scale, hidden_states, scale, shift,
+                              eps=1e-6)
 
         # ---- attention branch
         qkv = self._buffer("qkv", (T, 3 * D), dt, dev)
@@ -159,16 +159,16 @@ class FluxSingleTransformerBlockOp:
         # ---- proj_out input [T, (mlp_scale + 1) * D] in e4m3, filled in place by its two producers
         cat8 = self._buffer("cat8", (T, (self.mlp_scale + 1) * D), torch.uint8, dev)
         ops.quant_fp8_into_columns(cat8, 0, attn, w["out"].input_scale)
-        mlp_in = self._buffer("mlp_in", (T, D), torch.uint8, dev)
-        ops.invoke_cuda_d2d_scale_cpy_convert(mlp_in, norm.view(T, D), w["mlp"].input_scale)
         ops.gemm_fp8_quant_into_columns(w["mlp"].qweight, w["mlp"].w_scale, mlp_in, w["mlp"].input_scale, cat8, D,
                                         w["out"].input_scale, dt, bias=w["mlp"].bias, is_gelu=True)
 
-        # ---- proj_out, then gate and residual
-        y = self._buffer("y", (T, D), dt, dev)
-        ops.gemm_with_residual_and_bias_fp8(w["out"].qweight, w["out"].w_scale, cat8, w["out"].input_scale, y, bias=w["out"].bias)
+        # ---- proj_out with gate and residual in its epilogue (a separate kernel only where a tile would straddle batches)
         out = torch.empty_like(hidden_states)
-        ops.invoke_fused_gate_and_residual(out, y.view(B, S, D), gate, hidden_states)
+        if not ops.gemm_fp8_gate_residual(w["out"].qweight, w["out"].w_scale, cat8, w["out"].input_scale, out.view(T, D), gate,
+                                          hidden_states.view(T, D), S, bias=w["out"].bias):
+            y = self._buffer("y", (T, D), dt, dev)
+            ops.gemm_with_residual_and_bias_fp8(w["out"].qweight, w["out"].w_scale, cat8, w["out"].input_scale, y, bias=w["out"].bias)
+            ops.invoke_fused_gate_and_residual(out, y.view(B, S, D), gate, hidden_states)
         return out
 
     __call__ = forward
@@ -273,17 +273,21 @@ class FluxTransformerBlockOp:
         aq = torch.empty(T, D, dtype=torch.uint8, device=dev)
         ops.invoke_cuda_d2d_scale_cpy_convert(aq, attn, w["out"].input_scale)
         y = torch.empty(T, D, dtype=dt, device=dev)
-        ops.gemm_with_residual_and_bias_fp8(w["out"].qweight, w["out"].w_scale, aq, w["out"].input_scale, y, bias=w["out"].bias)
         h = torch.empty_like(x)
-        ops.invoke_fused_gate_and_residual(h, y.view(B, S, D), mod[2], x)
+        if not ops.gemm_fp8_gate_residual(w["out"].qweight, w["out"].w_scale, aq, w["out"].input_scale, h.view(T, D), mod[2],
+                                          x.view(T, D), S, bias=w["out"].bias):
+            ops.gemm_with_residual_and_bias_fp8(w["out"].qweight, w["out"].w_scale, aq, w["out"].input_scale, y, bias=w["out"].bias)
+            ops.invoke_fused_gate_and_residual(h, y.view(B, S, D), mod[2], x)
         nq = torch.empty(T, D, dtype=torch.uint8, device=dev)
         ops.invoke_layer_norm_with_shift_and_scale(None, h, mod[4], mod[3], eps=1e-6, qf8=nq, f8_scale=w["ff1"].input_scale)
         f1 = torch.empty(T, w["ff1"].n, dtype=torch.uint8, device=dev)
         ops.gemm_fp8_quant_out(w["ff1"].qweight, w["ff1"].w_scale, nq, w["ff1"].input_scale, f1, w["ff2"].input_scale, dt,
                                bias=w["ff1"].bias, is_gelu=True)
-        ops.gemm_with_residual_and_bias_fp8(w["ff2"].qweight, w["ff2"].w_scale, f1, w["ff2"].input_scale, y, bias=w["ff2"].bias)
         out = torch.empty_like(x)
-        ops.invoke_fused_gate_and_residual(out, y.view(B, S, D), mod[5], h)
+        if not ops.gemm_fp8_gate_residual(w["ff2"].qweight, w["ff2"].w_scale, f1, w["ff2"].input_scale, out.view(T, D), mod[5],
+                                          h.view(T, D), S, bias=w["ff2"].bias):
+            ops.gemm_with_residual_and_bias_fp8(w["ff2"].qweight, w["ff2"].w_scale, f1, w["ff2"].input_scale, y, bias=w["ff2"].bias)
+            ops.invoke_fused_gate_and_residual(out, y.view(B, S, D), mod[5], h)
         return out
 
     def forward(self, hidden_states, encoder_hidden_states, rope_emb, temb):

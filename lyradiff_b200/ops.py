@@ -121,6 +121,16 @@ def invoke_layer_norm_with_shift_and_scale(dst, src, scale, shift, eps=1e-6, q8=
     return dst
 
 
+def adaln_quant_fp8x2(dst, qa, scale_a, qb, scale_b, src, scale, shift, eps=1e-6):
+    """AdaLN modulation with two e4m3 outputs (two consumers with their own input scales) in one pass
+    (lyraq_adaln_quant_fp8x2); dst (16-bit) may be None."""
+    b, s, d = src.shape
+    st = _lib.lib().lyraq_adaln_quant_fp8x2(_p(dst), _p(qa), _p(scale_a), _p(qb), _p(scale_b), _p(src), _p(scale), _p(shift),
+                                            _dt(src), b, s, d, float(eps), _stream())
+    _lib.check(st, "lyraq_adaln_quant_fp8x2")
+    return qa, qb
+
+
 def invoke_layer_norm_int8o(dst, src, gamma, beta, pre_quant_scale, input_quant_scale, eps=1e-5, residual=None,
                             bias=None, sum_out=None):
     """invokeLayerNormInt8O<T> / invokeFusedResidualBiasLayerNormInt8O<T>
@@ -210,6 +220,21 @@ def invoke_fused_gate_and_residual(out, y, gate, residual):
     st = _lib.lib().lyraq_gate_residual(_p(out), _p(y), _p(gate), _p(residual), _dt(y), b, s, d, _stream())
     _lib.check(st, "lyraq_gate_residual")
     return out
+
+
+def gemm_fp8_gate_residual(W, w_scale, X, x_scale, Y, gate, residual, rows_per_batch, bias=None):
+    """FP8 GEMM + invokeFusedGateAndResidual in one launch (lyraq_gemm_fp8_gate): Y = (X W^T * s + bias) * gate[b] + residual,
+    rounded to Y's dtype after every step.  Returns False (nothing launched) when the shape cannot be fused."""
+    m, k = X.shape
+    n = W.shape[0]
+    if W.shape[1] != k or tuple(Y.shape) != (m, n):
+        raise ValueError("shape mismatch")
+    if m > rows_per_batch and rows_per_batch % 256 != 0:
+        return False
+    st = _lib.lib().lyraq_gemm_fp8_gate(_p(X), _p(x_scale), _p(W), _p(w_scale), _p(Y), _dt(Y), _p(bias), _p(gate), _p(residual),
+                                        rows_per_batch, m, n, k, None, 0, _stream())
+    _lib.check(st, "lyraq_gemm_fp8_gate")
+    return True
 
 
 def gemm_fp8_quant_into_columns(W, w_scale, X, x_scale, dst, col0, y_scale, dtype, bias=None, is_gelu=False):

@@ -83,3 +83,34 @@ def test_gemm_with_strided_e4m3_output(ops, m, n, k, ld, col0):
     got = dst.cpu()
     assert_bit_equal(got[:, col0:col0 + n], ref.cpu())
     assert bool((got[:, :col0] == 0x55).all()) and bool((got[:, col0 + n:] == 0x55).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("batch,seq,n,k", [(1, 200, 264, 384), (2, 256, 512, 256), (3, 512, 128, 128)])
+def test_gemm_with_gate_and_residual_equals_the_two_kernels(ops, dtype, batch, seq, n, k):
+    """lyraq_gemm_fp8_gate = lyraq_gemm_fp8 followed by lyraq_gate_residual, bit for bit (the same roundings in the same
+    order), also in place on the residual."""
+    m = batch * seq
+    w = workloads.fp8_linear(m=m, k=k, n=n, seed=m + n, dtype=dtype)
+    g = torch.Generator().manual_seed(n)
+    gate = torch.randn(batch, n, generator=g).to(dtype)
+    res = torch.randn(m, n, generator=g).to(dtype)
+    y = torch.empty(m, n, dtype=dtype, device="cuda")
+    ops.gemm_with_residual_and_bias_fp8(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), y, bias=cu(w["bias"]))
+    want = torch.empty(batch, seq, n, dtype=dtype, device="cuda")
+    ops.invoke_fused_gate_and_residual(want, y.view(batch, seq, n), cu(gate), cu(res).view(batch, seq, n))
+    got = torch.empty(m, n, dtype=dtype, device="cuda")
+    assert ops.gemm_fp8_gate_residual(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), got, cu(gate), cu(res), seq,
+                                      bias=cu(w["bias"]))
+    check_status()
+    assert_bit_equal(got, want.view(m, n).cpu())
+    inplace = cu(res).clone()
+    ops.gemm_fp8_gate_residual(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), inplace, cu(gate), inplace, seq, bias=cu(w["bias"]))
+    assert_bit_equal(inplace, want.view(m, n).cpu())
+
+
+def test_gate_fusion_refuses_tiles_that_straddle_batches(ops):
+    w = workloads.fp8_linear(m=200, k=128, n=128, seed=1)
+    y = torch.empty(200, 128, dtype=torch.bfloat16, device="cuda")
+    gate = torch.ones(2, 128, dtype=torch.bfloat16, device="cuda")
+    assert ops.gemm_fp8_gate_residual(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), y, gate, y, 100) is False

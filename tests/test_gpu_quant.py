@@ -199,6 +199,29 @@ def test_adaln_quant_against_oracle(ops, dtype, b, s, d):
     assert torch.equal(q8b, q8) and torch.equal(s8b, s8)
 
 
+def test_adaln_two_e4m3_outputs_equal_two_single_passes(ops):
+    w = workloads.adaln_input(b=2, s=70, d=3072, seed=9)
+    sa, sb = torch.tensor([0.013]), torch.tensor([0.027])
+    rows = 2 * 70
+    qa = torch.empty(rows, 3072, dtype=torch.uint8, device="cuda")
+    qb = torch.empty_like(qa)
+    y = torch.empty(2, 70, 3072, dtype=torch.bfloat16, device="cuda")
+    ops.adaln_quant_fp8x2(y, qa, cu(sa), qb, cu(sb), cu(w["x"]), cu(w["scale"]), cu(w["shift"]))
+    ra, rb = torch.empty_like(qa), torch.empty_like(qa)
+    y1 = torch.empty_like(y)
+    ops.invoke_layer_norm_with_shift_and_scale(y1, cu(w["x"]), cu(w["scale"]), cu(w["shift"]), qf8=ra, f8_scale=cu(sa))
+    ops.invoke_layer_norm_with_shift_and_scale(None, cu(w["x"]), cu(w["scale"]), cu(w["shift"]), qf8=rb, f8_scale=cu(sb))
+    check_status()
+    assert_bit_equal(qa, ra.cpu())
+    assert_bit_equal(qb, rb.cpu())
+    assert_bit_equal(y, y1.cpu())
+    # and without the 16-bit output
+    qa2, qb2 = torch.empty_like(qa), torch.empty_like(qa)
+    ops.adaln_quant_fp8x2(None, qa2, cu(sa), qb2, cu(sb), cu(w["x"]), cu(w["scale"]), cu(w["shift"]))
+    assert_bit_equal(qa2, ra.cpu())
+    assert_bit_equal(qb2, rb.cpu())
+
+
 def test_adaln_golden(ops, golden):
     z = golden("adaln")
     b, s, d = z["x"].shape
