@@ -409,11 +409,11 @@ class FluxBlock:
         self.workload = ("one FLUX.1-dev single-stream block (the unit configs[4] repeats 38 times), FP8_W8A8, batch 1, %d tokens, "
                          "hidden 3072, 24 x 128 heads, random weights: %.3f TFLOP in FP8 linears + %.3f TFLOP in bf16 attention "
                          "(torch SDPA)" % (T, self.lin_flops / 1e12, self.attn_flops / 1e12))
-        self.launches_per_step = 9
+        self.launches_per_step = 6
         self.timed_names = ["block_forward"]
         self.timed_work = [self.work_per_step]
         self.roof = {"bound": "tensor", "unit": "TFLOP/s",
-                     "kernel": "whole block: 3 gemm_tcgen05_kernel<f8f6f4> launches + 6 element-wise kernels of this library, "
+                     "kernel": "whole block: 3 gemm_tcgen05_kernel<f8f6f4> launches + 3 element-wise kernels of this library, "
                                "plus the library attention and one small library matmul"}
         self.traffic = None
 
@@ -507,7 +507,7 @@ class FluxForward(FluxBlock):
                          "24 x 128 heads; one step = one pass through the stack = %.1f TFLOP (embedders and final layer left out); "
                          "ms_per_step is the reference's denoising-step time for the stack"
                          % (self.N_DOUBLE, self.N_SINGLE, self.tokens - self.TXT, self.TXT, self.work_per_step / 1e12))
-        self.launches_per_step = self.N_DOUBLE * 20 + self.N_SINGLE * 9
+        self.launches_per_step = self.N_DOUBLE * 16 + self.N_SINGLE * 6
         self.timed_names = ["stack_forward"]
         self.timed_work = [self.work_per_step]
         self.roof["kernel"] = "whole stack: 57 blocks, each 3 or 8 gemm_tcgen05_kernel<f8f6f4> launches + element-wise kernels of this " \
