@@ -279,8 +279,7 @@ __device__ __forceinline__ void epilogue_math16(const EpilogueParams& e, const u
             }
             t = add_f32x2(t, make_float2(c.y, c.w));
             if (e.gelu) {
-                t.x = gelu_tanh_f32(t.x);
-                t.y = gelu_tanh_f32(t.y);
+                t = gelu_tanh_f32x2(t);
             }
             o[i] = P2::from_f32(t.x, t.y);
         }
