@@ -1,0 +1,73 @@
+"""CPU checks of the oracle's block-level functions against independent formulations (no GPU, no library)."""
+
+import torch
+
+from oracle import blocks, norms
+
+
+def _rope(tokens, head_dim, g):
+    ang = torch.rand(tokens, head_dim // 2, generator=g) * 6.28
+    return torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(tokens, head_dim // 2, 2, 2)
+
+
+def test_rmsnorm_rope_is_a_rotation_of_the_normalised_head():
+    g = torch.Generator().manual_seed(0)
+    tokens, heads, hd = 6, 3, 128
+    qkv = torch.randn(tokens, 3 * heads * hd, generator=g).bfloat16()
+    scale = torch.ones(2 * hd).bfloat16()
+    rope = _rope(tokens, hd, g)
+    out = norms.rmsnorm_rope(qkv, scale, rope.bfloat16(), heads, hd, eps=1e-6).float().reshape(tokens, 3, heads, hd)
+    x = qkv.float().reshape(tokens, 3, heads, hd)
+    # v heads untouched
+    assert torch.equal(out[:, 2], x[:, 2])
+    # q, k: unit RMS after the norm, and a rotation keeps the length (bf16 rounding: 1 %)
+    rms = out[:, :2].pow(2).mean(dim=-1).sqrt()
+    assert float((rms - 1.0).abs().max()) < 0.02
+    # against complex multiplication in fp32
+    xn = x[:, :2] / x[:, :2].pow(2).mean(dim=-1, keepdim=True).sqrt()
+    z = torch.complex(xn[..., 0::2], xn[..., 1::2])
+    rot = torch.complex(rope[:, :, 0, 0], rope[:, :, 1, 0])[:, None, None, :]      # cos + i sin
+    w = z * rot
+    want = torch.stack([w.real, w.imag], dim=-1).reshape(tokens, 2, heads, hd)
+    assert float((out[:, :2] - want).abs().max()) < 0.05
+
+
+def test_gate_residual_rounds_after_each_step():
+    y = torch.tensor([[[1.0078125, 3.0]]]).bfloat16()
+    gate = torch.tensor([[1.0078125, 0.5]]).bfloat16()
+    x = torch.tensor([[[0.00390625, 1.0]]]).bfloat16()
+    out = norms.gate_residual(y, gate, x)
+    # 1.0078125^2 = 1.01568... rounds to 1.015625 in bf16; + 2^-8 = 1.01953125 -> 1.0234375 or 1.015625 (tie to even)
+    prod = torch.tensor(1.0078125 * 1.0078125).bfloat16().float()
+    assert float(out[0, 0, 0]) == float((prod + 0.00390625).bfloat16())
+    assert float(out[0, 0, 1]) == 2.5
+
+
+def test_oracle_blocks_run_and_identity_gate_returns_the_input():
+    g = torch.Generator().manual_seed(1)
+    D, heads, hd = 256, 2, 128
+    p = "b."
+    sd = {}
+    for name, n, k in (("norm.linear", 3 * D, D), ("attn.to_qkv", 3 * D, D), ("proj_mlp", 4 * D, D), ("proj_out", D, 5 * D)):
+        sd[p + name + ".weight"] = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+        sd[p + name + ".bias"] = torch.zeros(n).bfloat16()
+        sd[p + name + "_input_scale"] = torch.tensor([0.03])
+    sd[p + "attn.norm_q.weight"] = torch.ones(hd).bfloat16()
+    sd[p + "attn.norm_k.weight"] = torch.ones(hd).bfloat16()
+    hidden = torch.randn(1, 24, D, generator=g).bfloat16()
+    rope = _rope(24, hd, g).reshape(1, 24, hd // 2, 2, 2).bfloat16()
+    temb = torch.randn(1, D, generator=g).bfloat16()
+    out, mid = blocks.flux_single_block(hidden, rope, temb, sd, p, heads, hd, 4, 1)
+    assert out.shape == hidden.shape and not torch.equal(out, hidden)
+    assert set(mid) == {"msa", "norm", "qkv", "attn", "mlp", "y"}
+    # a zero modulation linear gives gate = 0: the block returns its input
+    sd[p + "norm.linear.weight"].zero_()
+    out0, _ = blocks.flux_single_block(hidden, rope, temb, sd, p, heads, hd, 4, 1)
+    assert torch.equal(out0, hidden)
+
+
+def test_attention_matches_torch_sdpa():
+    g = torch.Generator().manual_seed(2)
+    q, k, v = (torch.randn(1, 2, 17, 64, generator=g) for _ in range(3))
+    want = torch.nn.functional.scaled_dot_product_attention(q, k, v)
+    assert float((blocks.attention(q, k, v).float() - want).abs().max()) < 1e-5
