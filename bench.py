@@ -408,7 +408,7 @@ class FluxBlock:
         self.scale = 1e12
         self.workload = ("one FLUX.1-dev single-stream block (the unit configs[4] repeats 38 times), FP8_W8A8, batch 1, %d tokens, "
                          "hidden 3072, 24 x 128 heads, random weights: %.3f TFLOP in FP8 linears + %.3f TFLOP in bf16 attention "
-                         "(torch SDPA)" % (T, self.lin_flops / 1e12, self.attn_flops / 1e12))
+                         "(torch SDPA); the resident-input step is replayed as a CUDA graph" % (T, self.lin_flops / 1e12, self.attn_flops / 1e12))
         self.launches_per_step = 6
         self.timed_names = ["block_forward"]
         self.timed_work = [self.work_per_step]
@@ -453,15 +453,37 @@ class FluxBlock:
         self.e2e_x = [self.x, torch.empty_like(self.x)]
         self.e2e_y = [self.y, torch.empty_like(self.y)]
 
+    use_graph = True  # bench.py --no-graph turns the CUDA-graph replay off
+
+    def _forward(self, x):
+        return self.op.forward(x, self.rope, self.temb)
+
+    def _capture(self):
+        """One step on the resident input as a CUDA graph: the step is hundreds of short launches issued from Python,
+        and replaying them as a graph takes the launch gaps out (the library's entry points allocate nothing and
+        only enqueue, so they can be captured as they are)."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._forward(self.x)
+        torch.cuda.current_stream().wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.graph_out = self._forward(self.x)
+
     def step(self, events=None, io=None):
-        x = self.x if io is None else io[0]
         if events is not None:
             events[0][0].record()
-        out = self.op.forward(x, self.rope, self.temb)
+        if io is None and self.use_graph:
+            if getattr(self, "graph", None) is None:
+                self._capture()
+            self.graph.replay()
+        else:
+            out = self._forward(self.x if io is None else io[0])
+            if io is not None:
+                io[1].copy_(out)
         if events is not None:
             events[0][1].record()
-        if io is not None:
-            io[1].copy_(out)
 
     def peak(self, peaks):
         p8, p16 = 2.0 * peaks["bf16_sustained"], peaks["bf16_sustained"]
@@ -565,20 +587,14 @@ class FluxForward(FluxBlock):
         self.e2e_x = [self.x, torch.empty_like(self.x)]
         self.e2e_y = [self.y, torch.empty_like(self.y)]
 
-    def step(self, events=None, io=None):
-        img = self.x if io is None else io[0]
-        if events is not None:
-            events[0][0].record()
+    def _forward(self, img):
         txt = self.txt
         for op in self.double:
             img, txt = op.forward(img, txt, self.rope, self.temb)
         h = torch.cat([txt, img], dim=1)
         for op in self.single:
             h = op.forward(h, self.rope, self.temb)
-        if events is not None:
-            events[0][1].record()
-        if io is not None:
-            io[1].copy_(h)
+        return h
 
 
 class W4A4:
@@ -900,6 +916,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the number of token rows (0 = the configuration's own)")
     ap.add_argument("--tile", type=int, default=0, choices=[0, 2561, 1281, 2562],
                     help="force the dense-GEMM tile configuration (0 = automatic; see lyraq_debug_force_gemm_tile)")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="flux_block / flux_forward: issue every launch from Python instead of replaying the step as a CUDA graph")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch the kernels as ordinary stream-ordered kernels (see lyraq_debug_set_dependent_launch)")
     args = ap.parse_args()
@@ -908,6 +926,8 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     case = CASES[args.case](args.tokens)
+    if args.no_graph:
+        case.use_graph = False
     if args.impl == "reference":
         run_reference(case, args, rank, world)
     else:

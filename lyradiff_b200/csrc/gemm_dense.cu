@@ -90,7 +90,8 @@ struct GemmParams {
     unsigned int*  status;
     EpilogueParams epi;
 #ifdef LYRAQ_PROFILE_WAITS
-    int            skip;  // instrumentation only: bit 0 = the producer signals without loading, bit 1 = the epilogue frees
+    int            skip;  // instrumentation only: bit 0 = the producer signals without loading, bit 3 / 4 / 5 = the 16-bit
+                          // epilogue without TMA stores / arithmetic / shared-memory writes, bit 1 = the epilogue frees
                           // the accumulator without reading it
 #endif
 };
@@ -720,6 +721,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     load_res16(c + 1, resb[RES ? ((c + 1) & 1) : 0]);
                 }
                 const uint32_t* bias2 = reinterpret_cast<const uint32_t*>(b16 + c * 32);
+#ifdef LYRAQ_PROFILE_WAITS
+                if (p.skip & 16) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        o[i] = a[2 * i] ^ a[2 * i + 1];
+                    }
+                } else
+#endif
                 if (e.c_dtype == LYRAQ_BF16) {
                     epilogue_math16<KIND, __nv_bfloat16, RES>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
                 } else {
@@ -794,14 +803,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     __syncwarp();
                     uint8_t*  brow = box + lane * 64;
                     const int sw   = (lane >> 1) & 3;
+#ifdef LYRAQ_PROFILE_WAITS
+                    if (!(p.skip & 32))
+#endif
+                    {
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        Vec16 w;
-                        w.w[0] = o[4 * q]; w.w[1] = o[4 * q + 1]; w.w[2] = o[4 * q + 2]; w.w[3] = o[4 * q + 3];
-                        *reinterpret_cast<Vec16*>(brow + ((q ^ sw) << 4)) = w;
+                        for (int q = 0; q < 4; ++q) {
+                            Vec16 w;
+                            w.w[0] = o[4 * q]; w.w[1] = o[4 * q + 1]; w.w[2] = o[4 * q + 2]; w.w[3] = o[4 * q + 3];
+                            *reinterpret_cast<Vec16*>(brow + ((q ^ sw) << 4)) = w;
+                        }
+                        fence_proxy_async_smem();
                     }
-                    fence_proxy_async_smem();
                     __syncwarp();
+#ifdef LYRAQ_PROFILE_WAITS
+                    if (!(p.skip & 8))
+#endif
                     if (lane == 0 && row0 < p.M && valid > 0) {
                         tma_store_2d(&tmap_c, box_addr, col0, row0);
                         tma_store_commit();
