@@ -271,45 +271,56 @@ template<> struct Pair<__nv_bfloat16> {
 // also gives NaN -> 0.  That happens for about one vector in a thousand.
 // Variant for scales computed from the row itself (s = amax / 127): the quotient cannot exceed 127 * (1 + 2^-23)
 // in magnitude, so no clamp is needed, d always lies in [-0.5, 0.5], and the near-tie test reduces to one maximum.
-__device__ __forceinline__ void quant8_s8_inrange(const float* v, float s, float r, uint32_t& w0, uint32_t& w1)
+__device__ __forceinline__ void quant8_s8_inrange(const float2* v, float s, float r, uint32_t& w0, uint32_t& w1)
 {
-    const float magic = 12582912.0f;
-    uint32_t    b[8];
-    float       d[8];
+    const float2 mg = make_float2(12582912.0f, 12582912.0f);
+    const float2 r2 = make_float2(r, r);
+    const float2 m1 = make_float2(-1.0f, -1.0f);
+    uint32_t     b[8];
+    float        dmax = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float t = fmaf(v[j], r, magic);
-        d[j]          = fabsf(fmaf(v[j], r, magic - t));
-        b[j]          = __float_as_uint(t);
+    for (int j = 0; j < 4; ++j) {
+        const float2 t = fma_f32x2(v[j], r2, mg);
+        const float2 d = fma_f32x2(v[j], r2, fma_f32x2(t, m1, mg));  // v * r - (t - magic), the second term exact
+        dmax           = fmaxf(dmax, fmaxf(fabsf(d.x), fabsf(d.y)));
+        b[2 * j]       = __float_as_uint(t.x);
+        b[2 * j + 1]   = __float_as_uint(t.y);
     }
-    const float dmax = fmaxf(fmaxf(fmaxf(d[0], d[1]), fmaxf(d[2], d[3])), fmaxf(fmaxf(d[4], d[5]), fmaxf(d[6], d[7])));
     if (dmax > 0.5f - 6.1e-5f) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            b[j] = (uint32_t)f32_to_s8(v[j] / s);
+        for (int j = 0; j < 4; ++j) {
+            b[2 * j]     = (uint32_t)f32_to_s8(v[j].x / s);
+            b[2 * j + 1] = (uint32_t)f32_to_s8(v[j].y / s);
         }
     }
     w0 = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
     w1 = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
 }
 
-__device__ __forceinline__ void quant8_s8(const float* v, float s, float r, uint32_t& w0, uint32_t& w1)
+__device__ __forceinline__ void quant8_s8(const float2* v, float s, float r, uint32_t& w0, uint32_t& w1)
 {
-    const float magic = 12582912.0f;
-    uint32_t    b[8];
-    bool        redo = false;
+    const float  magic = 12582912.0f;
+    const float2 mg    = make_float2(magic, magic);
+    const float2 r2    = make_float2(r, r);
+    const float2 m1    = make_float2(-1.0f, -1.0f);
+    uint32_t     b[8];
+    bool         redo = false;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        const float t  = fmaf(v[j], r, magic);
-        const float tc = fminf(fmaxf(t, magic - 128.0f), magic + 127.0f);
-        const float d  = fmaf(v[j], r, magic - tc);
-        redo |= !(fabsf(fabsf(d) - 0.5f) >= 6.1e-5f);
-        b[j] = __float_as_uint(tc);
+    for (int j = 0; j < 4; ++j) {
+        const float2 t  = fma_f32x2(v[j], r2, mg);
+        const float2 tc = make_float2(fminf(fmaxf(t.x, magic - 128.0f), magic + 127.0f),
+                                      fminf(fmaxf(t.y, magic - 128.0f), magic + 127.0f));
+        const float2 d  = fma_f32x2(v[j], r2, fma_f32x2(tc, m1, mg));
+        redo |= !(fabsf(fabsf(d.x) - 0.5f) >= 6.1e-5f);
+        redo |= !(fabsf(fabsf(d.y) - 0.5f) >= 6.1e-5f);
+        b[2 * j]     = __float_as_uint(tc.x);
+        b[2 * j + 1] = __float_as_uint(tc.y);
     }
     if (redo) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            b[j] = (uint32_t)f32_to_s8(v[j] / s);
+        for (int j = 0; j < 4; ++j) {
+            b[2 * j]     = (uint32_t)f32_to_s8(v[j].x / s);
+            b[2 * j + 1] = (uint32_t)f32_to_s8(v[j].y / s);
         }
     }
     w0 = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);

@@ -122,7 +122,10 @@ row_quant_kernel(const RowParams p)
     }
     for (; row < p.rows; row += stride) {
     const bool live = true;
-    float      f[VPT][8];
+    // the row in fp32 as packed pairs: f[i][q] = elements (2q, 2q + 1) of this thread's i-th vector.  All fp32 steps
+    // below run as .f32x2 instructions (IEEE rounding per lane, so the results equal the scalar ones bit for bit) and
+    // keep the summation order of the scalar formulation.
+    float2     f[VPT][4];
 
     // ---- take the prefetched row (and, per mode, pre-combine in T arithmetic); start fetching the next one
     Vec16 cur[VPT];
@@ -189,14 +192,12 @@ row_quant_kernel(const RowParams p)
             }
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const float2 t = P2::to_f32(h.w[j]);
-                f[i][2 * j]     = t.x;
-                f[i][2 * j + 1] = t.y;
+                f[i][j] = P2::to_f32(h.w[j]);
             }
         } else {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                f[i][j] = 0.0f;
+            for (int j = 0; j < 4; ++j) {
+                f[i][j] = make_float2(0.0f, 0.0f);
             }
         }
     }
@@ -204,29 +205,28 @@ row_quant_kernel(const RowParams p)
     // ---- row statistics (fp32), then normalise and modulate (T arithmetic)
     if (MODE == ROW_ADALN || MODE == ROW_LN) {
         // four independent partial sums per pass: a single running sum would be one long dependency chain
-        float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // partial sums over elements (0,1)+(4,5) and (2,3)+(6,7) of every vector, as four scalar chains would keep them
+        float2 sa = make_float2(0.0f, 0.0f), sb = make_float2(0.0f, 0.0f);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                s4[j] += f[i][j] + f[i][j + 4];
-            }
+            sa = add_f32x2(sa, add_f32x2(f[i][0], f[i][2]));
+            sb = add_f32x2(sb, add_f32x2(f[i][1], f[i][3]));
         }
-        float s          = team_reduce<false>((s4[0] + s4[1]) + (s4[2] + s4[3]), tpr, red);
+        float s          = team_reduce<false>((sa.x + sa.y) + (sb.x + sb.y), tpr, red);
         const float mean = s / (float)p.dim;
-        float       q4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        const float2 nm  = make_float2(-mean, -mean);
+        float2       qa  = make_float2(0.0f, 0.0f), qb = make_float2(0.0f, 0.0f);
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int vi = tlane + i * tpr;
             if (vi < nvec) {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const float d0 = f[i][j] - mean, d1 = f[i][j + 4] - mean;
-                    q4[j]          = fmaf(d0, d0, fmaf(d1, d1, q4[j]));
-                }
+                const float2 d0 = add_f32x2(f[i][0], nm), d2 = add_f32x2(f[i][2], nm);
+                const float2 d1 = add_f32x2(f[i][1], nm), d3 = add_f32x2(f[i][3], nm);
+                qa              = fma_f32x2(d0, d0, fma_f32x2(d2, d2, qa));
+                qb              = fma_f32x2(d1, d1, fma_f32x2(d3, d3, qb));
             }
         }
-        float m2         = team_reduce<false>((q4[0] + q4[1]) + (q4[2] + q4[3]), tpr, red);
+        float m2         = team_reduce<false>((qa.x + qa.y) + (qb.x + qb.y), tpr, red);
         const float var  = fmaxf(m2 / (float)p.dim, 0.0f);
         const float rstd = 1.0f / sqrtf(var + p.eps);  // IEEE sqrt and divide: within one ulp of the exact value
 
@@ -246,12 +246,11 @@ row_quant_kernel(const RowParams p)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     // x_hat rounded to T; m = T(scale + 1) | gamma; y = T(T(m * x_hat) + shift)
-                    const uint32_t xh = P2::from_f32((f[i][2 * j] - mean) * rstd, (f[i][2 * j + 1] - mean) * rstd);
+                    const float2   xn = mul_f32x2(add_f32x2(f[i][j], nm), make_float2(rstd, rstd));
+                    const uint32_t xh = P2::from_f32(xn.x, xn.y);
                     const uint32_t m  = (MODE == ROW_ADALN) ? P2::add(a.w[j], P2::one()) : a.w[j];
                     y.w[j]            = P2::add(P2::mul(m, xh), b.w[j]);
-                    const float2 t    = P2::to_f32(y.w[j]);
-                    f[i][2 * j]       = t.x;
-                    f[i][2 * j + 1]   = t.y;
+                    f[i][j]           = P2::to_f32(y.w[j]);
                 }
                 if (p.y != nullptr) {
                     st_16(reinterpret_cast<T*>(p.y) + row * (size_t)p.dim + c, y);
@@ -278,17 +277,22 @@ row_quant_kernel(const RowParams p)
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int vi = tlane + i * tpr;
+                float2 g[4];
                 if (p.pre != nullptr && live && vi < nvec) {
                     const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
                     const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f[i][0] * p0.x), fabsf(f[i][1] * p0.y)),
-                                             fmaxf(fabsf(f[i][2] * p0.z), fabsf(f[i][3] * p0.w))));
-                    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(f[i][4] * p1.x), fabsf(f[i][5] * p1.y)),
-                                             fmaxf(fabsf(f[i][6] * p1.z), fabsf(f[i][7] * p1.w))));
+                    g[0] = mul_f32x2(f[i][0], make_float2(p0.x, p0.y));
+                    g[1] = mul_f32x2(f[i][1], make_float2(p0.z, p0.w));
+                    g[2] = mul_f32x2(f[i][2], make_float2(p1.x, p1.y));
+                    g[3] = mul_f32x2(f[i][3], make_float2(p1.z, p1.w));
                 } else {
-                    amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(f[i][0]), fabsf(f[i][1])), fmaxf(fabsf(f[i][2]), fabsf(f[i][3]))),
-                                             fmaxf(fmaxf(fabsf(f[i][4]), fabsf(f[i][5])), fmaxf(fabsf(f[i][6]), fabsf(f[i][7])))));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        g[j] = f[i][j];
+                    }
                 }
+                amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(g[0].x), fabsf(g[0].y)), fmaxf(fabsf(g[1].x), fabsf(g[1].y))),
+                                         fmaxf(fmaxf(fabsf(g[2].x), fabsf(g[2].y)), fmaxf(fabsf(g[3].x), fabsf(g[3].y)))));
             }
             amax = team_reduce<true>(amax, tpr, red);
             s8   = (amax == 0.0f) ? 1.0f : amax / 127.0f;
@@ -310,21 +314,29 @@ row_quant_kernel(const RowParams p)
         if (live && vi < nvec) {
             const size_t off = row * (size_t)p.dim + (vi << 3);
             if (p.qf8 != nullptr) {
-                const uint32_t w0 = f32x2_to_e4m3x2(f[i][0] * f8r, f[i][1] * f8r) | (f32x2_to_e4m3x2(f[i][2] * f8r, f[i][3] * f8r) << 16);
-                const uint32_t w1 = f32x2_to_e4m3x2(f[i][4] * f8r, f[i][5] * f8r) | (f32x2_to_e4m3x2(f[i][6] * f8r, f[i][7] * f8r) << 16);
+                const float2 r2 = make_float2(f8r, f8r);
+                const float2 e0 = mul_f32x2(f[i][0], r2), e1 = mul_f32x2(f[i][1], r2);
+                const float2 e2 = mul_f32x2(f[i][2], r2), e3 = mul_f32x2(f[i][3], r2);
+                const uint32_t w0 = f32x2_to_e4m3x2(e0.x, e0.y) | (f32x2_to_e4m3x2(e1.x, e1.y) << 16);
+                const uint32_t w1 = f32x2_to_e4m3x2(e2.x, e2.y) | (f32x2_to_e4m3x2(e3.x, e3.y) << 16);
                 st_8(p.qf8 + off, w0, w1);
             }
             if (p.qf8b != nullptr) {
-                const uint32_t w0 = f32x2_to_e4m3x2(f[i][0] * f8rb, f[i][1] * f8rb) | (f32x2_to_e4m3x2(f[i][2] * f8rb, f[i][3] * f8rb) << 16);
-                const uint32_t w1 = f32x2_to_e4m3x2(f[i][4] * f8rb, f[i][5] * f8rb) | (f32x2_to_e4m3x2(f[i][6] * f8rb, f[i][7] * f8rb) << 16);
+                const float2 r2 = make_float2(f8rb, f8rb);
+                const float2 e0 = mul_f32x2(f[i][0], r2), e1 = mul_f32x2(f[i][1], r2);
+                const float2 e2 = mul_f32x2(f[i][2], r2), e3 = mul_f32x2(f[i][3], r2);
+                const uint32_t w0 = f32x2_to_e4m3x2(e0.x, e0.y) | (f32x2_to_e4m3x2(e1.x, e1.y) << 16);
+                const uint32_t w1 = f32x2_to_e4m3x2(e2.x, e2.y) | (f32x2_to_e4m3x2(e3.x, e3.y) << 16);
                 st_8(p.qf8b + off, w0, w1);
             }
             if (p.q8 != nullptr) {
                 if (p.pre != nullptr) {
                     const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
                     const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
-                    f[i][0] *= p0.x; f[i][1] *= p0.y; f[i][2] *= p0.z; f[i][3] *= p0.w;
-                    f[i][4] *= p1.x; f[i][5] *= p1.y; f[i][6] *= p1.z; f[i][7] *= p1.w;
+                    f[i][0] = mul_f32x2(f[i][0], make_float2(p0.x, p0.y));
+                    f[i][1] = mul_f32x2(f[i][1], make_float2(p0.z, p0.w));
+                    f[i][2] = mul_f32x2(f[i][2], make_float2(p1.x, p1.y));
+                    f[i][3] = mul_f32x2(f[i][3], make_float2(p1.z, p1.w));
                 }
                 uint32_t w0, w1;
                 if (dynamic) {
