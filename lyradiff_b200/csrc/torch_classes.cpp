@@ -1,0 +1,364 @@
+// torch custom classes with the reference's names and signatures (namespace `lyradiff`, src/lyradiff/th_op/pybind.cc:9-96):
+//   torch.classes.lyradiff.LyraDiffCommonContext()
+//   torch.classes.lyradiff.FluxSingleTransformerBlockOp(inference_dtype, embedding_dim, embedding_head_num,
+//                                                       embedding_head_dim, mlp_scale, quant_level)
+//   torch.classes.lyradiff.FluxTransformerBlockOp(... same ...)
+// with initialize / forward / reload_model_from_state_dict / reload_model_from_bin / load_lora_by_name / clear_lora.
+// Host code only: every device operation is a call into the C ABI of liblyraq.so (include/lyraq.h) on torch's current
+// stream, plus two ATen library calls per block (scaled_dot_product_attention, and addmm for the 16-bit modulation
+// linear of quant_level 1).  torch supplies device memory, the stream and the class registry; nothing here computes.
+// The data flow is the one documented in lyradiff_b200/flux_blocks.py, which is the Python twin of this file.
+#include <ATen/cuda/CUDAContext.h>
+#include <torch/custom_class.h>
+#include <torch/script.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/lyraq.h"
+
+namespace {
+
+using at::Tensor;
+
+void check(int status, const char* what)
+{
+    TORCH_CHECK(status == LYRAQ_OK, what, " failed: ", lyraq_status_string(status),
+                status == LYRAQ_ERR_CUDA ? lyraq_last_cuda_error() : "");
+}
+
+void* stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int dt_code(at::ScalarType t)
+{
+    TORCH_CHECK(t == at::kBFloat16 || t == at::kHalf, "only bf16 and fp16 are supported");
+    return t == at::kBFloat16 ? LYRAQ_BF16 : LYRAQ_F16;
+}
+
+at::ScalarType parse_dtype(const std::string& s)
+{
+    TORCH_CHECK(s == "bf16" || s == "fp16", "inference_dtype must be 'bf16' or 'fp16'");
+    return s == "bf16" ? at::kBFloat16 : at::kHalf;
+}
+
+const void* ptr(const Tensor& t) { return t.defined() ? t.data_ptr() : nullptr; }
+
+// One FP8 linear as MACROLoadFP8WeightFromCache leaves it (src/lyradiff/utils/common_macro_def.h:76-92).
+struct Fp8Weight {
+    Tensor  qweight, w_scale, bias, input_scale;
+    int64_t n = 0, k = 0;
+
+    void load(const Tensor& weight, const Tensor& b, const Tensor& in_scale, const at::Device& dev, at::ScalarType dt)
+    {
+        Tensor w = weight.to(dev, dt).contiguous();
+        n        = w.size(0);
+        k        = w.size(1);
+        qweight  = at::empty({n, k}, w.options().dtype(at::kByte));
+        w_scale  = at::empty({1}, w.options().dtype(at::kFloat));
+        check(lyraq_weight_quant_fp8(qweight.data_ptr<uint8_t>(), w_scale.data_ptr<float>(), w.data_ptr(), dt_code(dt),
+                                     (size_t)w.numel(), stream()),
+              "lyraq_weight_quant_fp8");
+        bias        = b.to(dev, dt).contiguous();
+        input_scale = in_scale.to(dev, at::kFloat).reshape({1}).contiguous();
+    }
+};
+
+Tensor fp8_gemm(const Fp8Weight& w, const Tensor& xq, int64_t m, at::ScalarType dt)
+{
+    Tensor y = at::empty({m, w.n}, xq.options().dtype(dt));
+    check(lyraq_gemm_fp8(xq.data_ptr<uint8_t>(), w.input_scale.data_ptr<float>(), w.qweight.data_ptr<uint8_t>(),
+                         w.w_scale.data_ptr<float>(), y.data_ptr(), dt_code(dt), ptr(w.bias), nullptr, 1.0f, 0.0f, LYRAQ_EPI_NONE,
+                         (int)m, (int)w.n, (int)w.k, nullptr, 0, stream()),
+          "lyraq_gemm_fp8");
+    return y;
+}
+
+// out = gate * (x_q W^T * s + bias) + residual, in the GEMM's epilogue where a tile cannot straddle two batch entries.
+Tensor fp8_gemm_gate_residual(const Fp8Weight& w, const Tensor& xq, const Tensor& gate, const Tensor& residual, int64_t batch,
+                              int64_t seq, at::ScalarType dt)
+{
+    const int64_t m   = batch * seq;
+    Tensor        out = at::empty_like(residual);
+    if (batch == 1 || seq % 256 == 0) {
+        check(lyraq_gemm_fp8_gate(xq.data_ptr<uint8_t>(), w.input_scale.data_ptr<float>(), w.qweight.data_ptr<uint8_t>(),
+                                  w.w_scale.data_ptr<float>(), out.data_ptr(), dt_code(dt), ptr(w.bias), gate.data_ptr(),
+                                  residual.data_ptr(), (int)seq, (int)m, (int)w.n, (int)w.k, nullptr, 0, stream()),
+              "lyraq_gemm_fp8_gate");
+        return out;
+    }
+    Tensor y = fp8_gemm(w, xq, m, dt);
+    check(lyraq_gate_residual(out.data_ptr(), y.data_ptr(), gate.data_ptr(), residual.data_ptr(), dt_code(dt), (size_t)batch,
+                              (size_t)seq, (size_t)w.n, stream()),
+          "lyraq_gate_residual");
+    return out;
+}
+
+struct Modulation {
+    bool      fp8 = false;
+    Fp8Weight q;
+    Tensor    w, b;
+
+    void load(const c10::Dict<std::string, Tensor>& sd, const std::string& name, bool full, const at::Device& dev, at::ScalarType dt)
+    {
+        fp8 = full;
+        if (full) {
+            q.load(sd.at(name + ".weight"), sd.at(name + ".bias"), sd.at(name + "_input_scale"), dev, dt);
+        } else {
+            w = sd.at(name + ".weight").to(dev, dt).contiguous();
+            b = sd.at(name + ".bias").to(dev, dt).contiguous();
+        }
+    }
+
+    // linear(temb) -> `chunks` contiguous [B, D] tensors (AdaFP8LayerNorm<T>::forward, AdaFP8LayerNorm.cc:96-160)
+    std::vector<Tensor> run(const Tensor& temb, int64_t chunks, at::ScalarType dt) const
+    {
+        Tensor msa;
+        if (fp8) {
+            Tensor tq = at::empty(temb.sizes(), temb.options().dtype(at::kByte));
+            check(lyraq_quant_fp8(tq.data_ptr<uint8_t>(), temb.data_ptr(), dt_code(dt), q.input_scale.data_ptr<float>(), 1,
+                                  (size_t)temb.numel(), stream()),
+                  "lyraq_quant_fp8");
+            msa = fp8_gemm(q, tq, temb.size(0), dt);
+        } else {
+            msa = at::addmm(b, temb, w.t());
+        }
+        std::vector<Tensor> out;
+        for (auto& c : msa.chunk(chunks, 1)) {
+            out.push_back(c.contiguous());
+        }
+        return out;
+    }
+};
+
+void check_inputs(std::initializer_list<Tensor> ts, at::ScalarType dt)
+{
+    for (const Tensor& t : ts) {
+        TORCH_CHECK(t.is_cuda() && t.is_contiguous() && t.scalar_type() == dt,
+                    "inputs must be contiguous CUDA tensors of the inference dtype");
+    }
+}
+
+Tensor attention(const Tensor& qkv, int64_t B, int64_t S, int64_t H, int64_t Dh)
+{
+    Tensor v5 = qkv.view({B, S, 3, H, Dh});
+    Tensor q = v5.select(2, 0).transpose(1, 2), k = v5.select(2, 1).transpose(1, 2), v = v5.select(2, 2).transpose(1, 2);
+    return at::scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape({B, S, H * Dh});
+}
+
+}  // namespace
+
+struct LyraDiffCommonContext: torch::CustomClassHolder {
+    LyraDiffCommonContext() = default;
+};
+
+struct BlockBase: torch::CustomClassHolder {
+    at::ScalarType dtype;
+    int64_t        dim, heads, head_dim, mlp_scale, quant_level;
+    bool           loaded = false;
+
+    BlockBase(const std::string& inference_dtype, int64_t embedding_dim, int64_t embedding_head_num, int64_t embedding_head_dim,
+              int64_t mlp_scale_, int64_t quant_level_):
+        dtype(parse_dtype(inference_dtype)), dim(embedding_dim), heads(embedding_head_num), head_dim(embedding_head_dim),
+        mlp_scale(mlp_scale_), quant_level(quant_level_)
+    {
+        TORCH_CHECK(quant_level == 1 || quant_level == 2, "only quant_level 1 (FP8_W8A8) and 2 (FP8_W8A8_FULL) are built");
+        TORCH_CHECK(heads * head_dim == dim, "embedding_dim must equal embedding_head_num * embedding_head_dim");
+    }
+    void initialize(const c10::intrusive_ptr<LyraDiffCommonContext>&) {}
+    void reload_model_from_bin(const std::string&, const std::string&)
+    {
+        TORCH_CHECK(false, "the .bin directory loader is not built; use reload_model_from_state_dict");
+    }
+    void load_lora_by_name(const std::vector<std::string>&, const Tensor&, double) { TORCH_CHECK(false, "LoRA hot-swap is not built"); }
+    void clear_lora() { TORCH_CHECK(false, "LoRA hot-swap is not built"); }
+};
+
+// FluxSingleTransformerBlockOp (th_op/flux_single_transformer_block/FluxSingleTransformerBlockOp.h:287-315)
+struct FluxSingleTransformerBlockOp: BlockBase {
+    using BlockBase::BlockBase;
+    Fp8Weight  qkv, mlp, out;
+    Modulation norm;
+    Tensor     qk_scale;
+
+    void reload_model_from_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device)
+    {
+        const at::Device dev(device);
+        auto g = [&](const std::string& n) { return sd.at(prefix + n); };
+        qkv.load(g("attn.to_qkv.weight"), g("attn.to_qkv.bias"), g("attn.to_qkv_input_scale"), dev, dtype);
+        mlp.load(g("proj_mlp.weight"), g("proj_mlp.bias"), g("proj_mlp_input_scale"), dev, dtype);
+        out.load(g("proj_out.weight"), g("proj_out.bias"), g("proj_out_input_scale"), dev, dtype);
+        c10::Dict<std::string, Tensor> sub;
+        for (const char* n : {"norm.linear.weight", "norm.linear.bias"}) {
+            sub.insert(n, g(n));
+        }
+        if (quant_level == 2) {
+            sub.insert("norm.linear_input_scale", g("norm.linear_input_scale"));
+        }
+        norm.load(sub, "norm.linear", quant_level == 2, dev, dtype);
+        qk_scale = at::cat({g("attn.norm_q.weight").reshape({-1}), g("attn.norm_k.weight").reshape({-1})}).to(dev, dtype).contiguous();
+        TORCH_CHECK(qkv.n == 3 * dim && mlp.n == mlp_scale * dim && out.k == (mlp_scale + 1) * dim,
+                    "weight shapes do not match the block's dimensions");
+        loaded = true;
+    }
+
+    Tensor forward(const Tensor& hidden, const Tensor& rope, const Tensor& temb)
+    {
+        TORCH_CHECK(loaded, "weights not loaded");
+        check_inputs({hidden, rope, temb}, dtype);
+        const int64_t B = hidden.size(0), S = hidden.size(1), D = hidden.size(2), T = B * S;
+        TORCH_CHECK(D == dim && temb.size(0) == B && temb.size(1) == D && rope.numel() == T * head_dim * 2, "shape mismatch");
+        const int  dtc  = dt_code(dtype);
+        auto       mod  = norm.run(temb, 3, dtype);  // shift, scale, gate
+        const auto opt8 = hidden.options().dtype(at::kByte);
+        Tensor     nq = at::empty({T, D}, opt8), mq = at::empty({T, D}, opt8);
+        check(lyraq_adaln_quant_fp8x2(nullptr, nq.data_ptr<uint8_t>(), qkv.input_scale.data_ptr<float>(), mq.data_ptr<uint8_t>(),
+                                      mlp.input_scale.data_ptr<float>(), hidden.data_ptr(), mod[1].data_ptr(), mod[0].data_ptr(),
+                                      dtc, (size_t)B, (size_t)S, (size_t)D, 1e-6, stream()),
+              "lyraq_adaln_quant_fp8x2");
+        Tensor q3 = fp8_gemm(qkv, nq, T, dtype);
+        check(lyraq_rmsnorm_rope(q3.data_ptr(), q3.data_ptr(), qk_scale.data_ptr(), rope.data_ptr(), dtc, 1e-6, (size_t)B, (size_t)S,
+                                 (int)heads, (int)head_dim, stream()),
+              "lyraq_rmsnorm_rope");
+        Tensor attn = attention(q3, B, S, heads, head_dim).reshape({T, D}).contiguous();
+        const int64_t ld = (mlp_scale + 1) * D;
+        Tensor cat8 = at::empty({T, ld}, opt8);
+        check(lyraq_quant_fp8_2d(cat8.data_ptr<uint8_t>(), (size_t)ld, attn.data_ptr(), dtc, out.input_scale.data_ptr<float>(),
+                                 (size_t)T, (size_t)D, stream()),
+              "lyraq_quant_fp8_2d");
+        check(lyraq_gemm_fp8_quant_ld(mq.data_ptr<uint8_t>(), mlp.input_scale.data_ptr<float>(), mlp.qweight.data_ptr<uint8_t>(),
+                                      mlp.w_scale.data_ptr<float>(), cat8.data_ptr<uint8_t>() + D, (size_t)ld,
+                                      out.input_scale.data_ptr<float>(), dtc, ptr(mlp.bias), nullptr, 1.0f, 0.0f,
+                                      LYRAQ_EPI_GELU_TANH, (int)T, (int)mlp.n, (int)mlp.k, nullptr, 0, stream()),
+              "lyraq_gemm_fp8_quant_ld");
+        return fp8_gemm_gate_residual(out, cat8, mod[2], hidden, B, S, dtype);
+    }
+};
+
+// FluxTransformerBlockOp (th_op/flux_transformer_block/FluxTransformerBlockOp.h:187-237)
+struct FluxTransformerBlockOp: BlockBase {
+    using BlockBase::BlockBase;
+    struct Stream {
+        Fp8Weight  qkv, out, ff1, ff2;
+        Modulation norm;
+        Tensor     qk_scale;
+    } img, txt;
+
+    void load_stream(Stream& s, const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const at::Device& dev,
+                     const std::string& norm, const std::string& qkv, const std::string& out, const std::string& nq,
+                     const std::string& nk, const std::string& ff)
+    {
+        auto g = [&](const std::string& n) { return sd.at(prefix + n); };
+        auto lin = [&](Fp8Weight& w, const std::string& n) { w.load(g(n + ".weight"), g(n + ".bias"), g(n + "_input_scale"), dev, dtype); };
+        lin(s.qkv, qkv);
+        lin(s.out, out);
+        lin(s.ff1, ff + ".net.0.proj");
+        lin(s.ff2, ff + ".net.2");
+        c10::Dict<std::string, Tensor> sub;
+        sub.insert("m.weight", g(norm + ".linear.weight"));
+        sub.insert("m.bias", g(norm + ".linear.bias"));
+        if (quant_level == 2) {
+            sub.insert("m_input_scale", g(norm + ".linear_input_scale"));
+        }
+        s.norm.load(sub, "m", quant_level == 2, dev, dtype);
+        s.qk_scale = at::cat({g(nq).reshape({-1}), g(nk).reshape({-1})}).to(dev, dtype).contiguous();
+    }
+
+    void reload_model_from_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device)
+    {
+        const at::Device dev(device);
+        load_stream(img, prefix, sd, dev, "norm1", "attn.to_qkv", "attn.to_out.0", "attn.norm_q.weight", "attn.norm_k.weight", "ff");
+        load_stream(txt, prefix, sd, dev, "norm1_context", "attn.to_added_qkv", "attn.to_add_out", "attn.norm_added_q.weight",
+                    "attn.norm_added_k.weight", "ff_context");
+        loaded = true;
+    }
+
+    Tensor pre_attention(const Stream& s, const Tensor& x, const std::vector<Tensor>& mod)
+    {
+        const int64_t B = x.size(0), S = x.size(1), D = x.size(2);
+        Tensor nq = at::empty({B * S, D}, x.options().dtype(at::kByte));
+        check(lyraq_adaln_quant(nullptr, nullptr, nullptr, nq.data_ptr<uint8_t>(), s.qkv.input_scale.data_ptr<float>(), x.data_ptr(),
+                                mod[1].data_ptr(), mod[0].data_ptr(), dt_code(dtype), nullptr, (size_t)B, (size_t)S, (size_t)D, 1e-6,
+                                stream()),
+              "lyraq_adaln_quant");
+        return fp8_gemm(s.qkv, nq, B * S, dtype);
+    }
+
+    Tensor post_attention(const Stream& s, const Tensor& x, const Tensor& attn, const std::vector<Tensor>& mod)
+    {
+        const int64_t B = x.size(0), S = x.size(1), D = x.size(2), T = B * S;
+        const int     dtc  = dt_code(dtype);
+        const auto    opt8 = x.options().dtype(at::kByte);
+        Tensor aq = at::empty({T, D}, opt8);
+        check(lyraq_quant_fp8(aq.data_ptr<uint8_t>(), attn.data_ptr(), dtc, s.out.input_scale.data_ptr<float>(), 1, (size_t)(T * D),
+                              stream()),
+              "lyraq_quant_fp8");
+        Tensor h  = fp8_gemm_gate_residual(s.out, aq, mod[2], x, B, S, dtype);
+        Tensor nq = at::empty({T, D}, opt8);
+        check(lyraq_adaln_quant(nullptr, nullptr, nullptr, nq.data_ptr<uint8_t>(), s.ff1.input_scale.data_ptr<float>(), h.data_ptr(),
+                                mod[4].data_ptr(), mod[3].data_ptr(), dtc, nullptr, (size_t)B, (size_t)S, (size_t)D, 1e-6, stream()),
+              "lyraq_adaln_quant");
+        Tensor f1 = at::empty({T, s.ff1.n}, opt8);
+        check(lyraq_gemm_fp8_quant(nq.data_ptr<uint8_t>(), s.ff1.input_scale.data_ptr<float>(), s.ff1.qweight.data_ptr<uint8_t>(),
+                                   s.ff1.w_scale.data_ptr<float>(), f1.data_ptr<uint8_t>(), s.ff2.input_scale.data_ptr<float>(), dtc,
+                                   ptr(s.ff1.bias), nullptr, 1.0f, 0.0f, LYRAQ_EPI_GELU_TANH, (int)T, (int)s.ff1.n, (int)s.ff1.k,
+                                   nullptr, 0, stream()),
+              "lyraq_gemm_fp8_quant");
+        return fp8_gemm_gate_residual(s.ff2, f1, mod[5], h, B, S, dtype);
+    }
+
+    std::vector<Tensor> forward(const Tensor& hidden, const Tensor& encoder, const Tensor& rope, const Tensor& temb)
+    {
+        TORCH_CHECK(loaded, "weights not loaded");
+        check_inputs({hidden, encoder, rope, temb}, dtype);
+        const int64_t B = hidden.size(0), S = hidden.size(1), D = hidden.size(2), E = encoder.size(1), tot = S + E;
+        TORCH_CHECK(D == dim && encoder.size(0) == B && encoder.size(2) == D && temb.size(0) == B && temb.size(1) == D &&
+                        rope.numel() == B * tot * head_dim * 2,
+                    "shape mismatch");
+        auto   mod_i = img.norm.run(temb, 6, dtype), mod_t = txt.norm.run(temb, 6, dtype);
+        Tensor qi = pre_attention(img, hidden, mod_i).view({B, S, 3 * D});
+        Tensor qt = pre_attention(txt, encoder, mod_t).view({B, E, 3 * D});
+        // joint sequence [B, E + S, 3, H, Dh], text first (invokeFusedRmsNormCatAndRope, flux_apply_rope.cu:78-156)
+        Tensor joint = at::empty({B, tot, 3 * D}, hidden.options());
+        Tensor r     = rope.view({B, tot, head_dim * 2});
+        const int dtc = dt_code(dtype);
+        for (int64_t b = 0; b < B; ++b) {
+            check(lyraq_rmsnorm_rope(joint[b].slice(0, 0, E).data_ptr(), qt[b].data_ptr(), txt.qk_scale.data_ptr(),
+                                     r[b].slice(0, 0, E).data_ptr(), dtc, 1e-6, 1, (size_t)E, (int)heads, (int)head_dim, stream()),
+                  "lyraq_rmsnorm_rope");
+            check(lyraq_rmsnorm_rope(joint[b].slice(0, E, tot).data_ptr(), qi[b].data_ptr(), img.qk_scale.data_ptr(),
+                                     r[b].slice(0, E, tot).data_ptr(), dtc, 1e-6, 1, (size_t)S, (int)heads, (int)head_dim, stream()),
+                  "lyraq_rmsnorm_rope");
+        }
+        Tensor attn   = attention(joint, B, tot, heads, head_dim);
+        Tensor attn_t = attn.slice(1, 0, E).reshape({B * E, D}).contiguous();
+        Tensor attn_i = attn.slice(1, E, tot).reshape({B * S, D}).contiguous();
+        Tensor out_i  = post_attention(img, hidden, attn_i, mod_i);
+        Tensor out_t  = post_attention(txt, encoder, attn_t, mod_t);
+        return {out_i, out_t};
+    }
+};
+
+// The shared methods live in BlockBase; they are bound through lambdas on the concrete class, since the class registry
+// takes `self` from the member pointer's class and BlockBase itself is not registered.
+template<class Op>
+void register_block(torch::Library& m, const char* name)
+{
+    using Self = c10::intrusive_ptr<Op>;
+    m.class_<Op>(name)
+        .def(torch::init<std::string, int64_t, int64_t, int64_t, int64_t, int64_t>())
+        .def("initialize", [](const Self& self, const c10::intrusive_ptr<LyraDiffCommonContext>& ctx) { self->initialize(ctx); })
+        .def("forward", &Op::forward)
+        .def("reload_model_from_state_dict", &Op::reload_model_from_state_dict)
+        .def("reload_model_from_bin",
+             [](const Self& self, const std::string& path, const std::string& dtype) { self->reload_model_from_bin(path, dtype); })
+        .def("load_lora_by_name", [](const Self& self, const std::vector<std::string>& names, const Tensor& w,
+                                     double scale) { self->load_lora_by_name(names, w, scale); })
+        .def("clear_lora", [](const Self& self) { self->clear_lora(); });
+}
+
+TORCH_LIBRARY(lyradiff, m)
+{
+    m.class_<LyraDiffCommonContext>("LyraDiffCommonContext").def(torch::init<>());
+    register_block<FluxSingleTransformerBlockOp>(m, "FluxSingleTransformerBlockOp");
+    register_block<FluxTransformerBlockOp>(m, "FluxTransformerBlockOp");
+}

@@ -1,0 +1,50 @@
+"""The C++ torch custom classes load without a GPU, carry the reference's class and method names
+(src/lyradiff/th_op/pybind.cc:9-96) and refuse what is not built the way the Python mirrors do."""
+
+import pytest
+import torch
+
+METHODS = ["initialize", "forward", "reload_model_from_state_dict", "reload_model_from_bin", "load_lora_by_name", "clear_lora"]
+
+
+@pytest.fixture(scope="module")
+def ns():
+    from lyradiff_b200 import build, torch_classes
+    build.build_classes()
+    return torch_classes.load()
+
+
+@pytest.mark.parametrize("name", ["FluxSingleTransformerBlockOp", "FluxTransformerBlockOp"])
+def test_names_and_signatures(ns, name):
+    cls = getattr(ns, name)
+    op = cls("bf16", 256, 2, 128, 4, 1)
+    op.initialize(ns.LyraDiffCommonContext())
+    for m in METHODS:
+        assert callable(getattr(op, m)), m
+    with pytest.raises(RuntimeError, match="quant_level"):
+        cls("bf16", 256, 2, 128, 4, 0)
+    with pytest.raises(RuntimeError, match="inference_dtype"):
+        cls("fp32", 256, 2, 128, 4, 1)
+    with pytest.raises(RuntimeError, match="embedding_dim"):
+        cls("fp16", 256, 3, 128, 4, 1)
+    with pytest.raises(RuntimeError, match="not built"):
+        op.reload_model_from_bin("/nowhere", "bf16")
+    with pytest.raises(RuntimeError, match="not built"):
+        op.load_lora_by_name(["a"], torch.zeros(1), 1.0)
+    with pytest.raises(RuntimeError, match="not built"):
+        op.clear_lora()
+
+
+def test_forward_needs_weights(ns):
+    op = ns.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 1)
+    with pytest.raises(RuntimeError, match="weights not loaded"):
+        op.forward(torch.zeros(1, 8, 256), torch.zeros(1, 8, 64, 2, 2), torch.zeros(1, 256))
+    op2 = ns.FluxTransformerBlockOp("bf16", 256, 2, 128, 4, 2)
+    with pytest.raises(RuntimeError, match="weights not loaded"):
+        op2.forward(torch.zeros(1, 8, 256), torch.zeros(1, 4, 256), torch.zeros(1, 12, 64, 2, 2), torch.zeros(1, 256))
+
+
+def test_missing_state_dict_key_raises(ns):
+    op = ns.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 1)
+    with pytest.raises((RuntimeError, IndexError, KeyError)):
+        op.reload_model_from_state_dict("p.", {"p.attn.to_qkv.weight": torch.zeros(768, 256)}, "cpu")
