@@ -52,7 +52,13 @@ typedef enum {
 /* Epilogue flags of the GEMMs (bit set). */
 enum {
     LYRAQ_EPI_NONE = 0,
-    LYRAQ_EPI_GELU_TANH = 1 /* tanh-GELU after bias (and after beta*residual, as cuBLASLt orders it) */
+    LYRAQ_EPI_GELU_TANH = 1, /* tanh-GELU after bias (and after beta*residual, as cuBLASLt orders it) */
+    LYRAQ_EPI_ROUND_EACH = 2 /* W4A4 entry points only: round to the output type after the accumulate, after the bias,
+                              * after the GELU and after the residual, i.e. the bits the reference gets from its GEMM
+                              * followed by separate 16-bit kernels (invokeFusedBiasAndGelu, invokeFusedBiasAndResidual,
+                              * src/lyradiff/kernels/flux_single_transformer_block/flux_single_transformer_kernels.cu:68-134;
+                              * the bias add of fuseBiasRmsNormAndRope, kernels/rope/flux_apply_rope.cu:203-205).
+                              * Without it the epilogue rounds once. */
 };
 
 LYRAQ_API const char* lyraq_version(void);
@@ -263,7 +269,8 @@ LYRAQ_API int lyraq_gemm_fp8_quant_ld(const uint8_t* X, const float* s_x, const 
  * as the reference's caller passes it).  bias, R of c_dtype or NULL.
  * Replaces invokeFusedW4A4GemmAndLoraUp (src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.h:19-30; kernels
  * w4a4_gemm.cu:227-767) and the bias/GELU/residual kernels that follow it
- * (kernels/flux_single_transformer_block/flux_single_transformer_kernels.cu:68-134). */
+ * (kernels/flux_single_transformer_block/flux_single_transformer_kernels.cu:68-134); with LYRAQ_EPI_ROUND_EACH in
+ * `epilogue`, T(.) is applied after every step as those kernels do: T(T(epi(T(T(sum + lora) + bias))) + R). */
 LYRAQ_API int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* sa, const void* sb, int sb_dtype,
                     void* D, int c_dtype, const void* lora_act, int lora_act_dtype, const void* lora_up,
                     const void* bias, const void* residual, int epilogue, int m, int n, int k,

@@ -95,6 +95,7 @@ struct Params {
     const void*   bias;
     const void*   residual;
     int           gelu;
+    int           round_each;    // round to D's type after every epilogue step (the reference's separate 16-bit kernels)
     const void*   lora_act;      // [M, 32], fp32 or already of D's 16-bit type, or null
     int           lora_act_is_f32;
     const void*   lora_up;       // [N, 32] of D's 16-bit type or null
@@ -115,6 +116,16 @@ __device__ __forceinline__ void final_store32(const Params& p, const float* acc,
     for (int i = 0; i < 32; ++i) {
         v[i] = acc[i];
     }
+    const bool each = p.round_each != 0 && sizeof(T) == 2;
+    auto round_all = [&]() {
+        if (each) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                v[i] = to_f32(from_f32<T>(v[i]));
+            }
+        }
+    };
+    round_all();
     if (p.bias != nullptr) {
         const T* b = reinterpret_cast<const T*>(p.bias) + col0;
 #pragma unroll
@@ -123,12 +134,14 @@ __device__ __forceinline__ void final_store32(const Params& p, const float* acc,
                 v[i] += to_f32(b[i]);
             }
         }
+        round_all();
     }
     if (p.gelu) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             v[i] = gelu_tanh_f32(v[i]);
         }
+        round_all();
     }
     T* drow = reinterpret_cast<T*>(p.D) + (size_t)row * p.N + col0;
     if (p.residual != nullptr) {
@@ -784,7 +797,7 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
         return LYRAQ_ERR_INVALID_ARG;
     }
     if (c_dtype < LYRAQ_F16 || c_dtype > LYRAQ_F32 || (sb_dtype != LYRAQ_F32 && sb_dtype != LYRAQ_F16) ||
-        (epilogue & ~LYRAQ_EPI_GELU_TANH) != 0 || m < 0 || n < 0 || k < 0) {
+        (epilogue & ~(LYRAQ_EPI_GELU_TANH | LYRAQ_EPI_ROUND_EACH)) != 0 || m < 0 || n < 0 || k < 0) {
         return LYRAQ_ERR_INVALID_ARG;
     }
     if ((lora_act == nullptr) != (lora_up == nullptr)) {
@@ -823,6 +836,7 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     p.bias      = bias;
     p.residual  = residual;
     p.gelu      = (epilogue & LYRAQ_EPI_GELU_TANH) ? 1 : 0;
+    p.round_each = (epilogue & LYRAQ_EPI_ROUND_EACH) ? 1 : 0;
     p.lora_act  = lora_act;
     p.lora_act_is_f32 = (lora_act_dtype == LYRAQ_F32) ? 1 : 0;
     p.lora_up   = lora_up;

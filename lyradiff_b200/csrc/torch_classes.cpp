@@ -4,6 +4,7 @@
 //                                                       embedding_head_dim, mlp_scale, quant_level)
 //   torch.classes.lyradiff.FluxTransformerBlockOp(... same ...)
 // with initialize / forward / reload_model_from_state_dict / reload_model_from_bin / load_lora_by_name / clear_lora.
+// quant_level 1, 2 (FP8) for both blocks; 7, 8 (INT4 W4A4) for the single-stream block.
 // Host code only: every device operation is a call into the C ABI of liblyraq.so (include/lyraq.h) on torch's current
 // stream, plus two ATen library calls per block (scaled_dot_product_attention, and addmm for the 16-bit modulation
 // linear of quant_level 1).  torch supplies device memory, the stream and the class registry; nothing here computes.
@@ -93,6 +94,50 @@ Tensor fp8_gemm_gate_residual(const Fp8Weight& w, const Tensor& xq, const Tensor
     return out;
 }
 
+// One W4A4 linear with its rank-32 LoRA branch, from the tensors W4A4GemmWeight<T>::loadWeights reads
+// (src/lyradiff/layers/w4a4_gemm_block/W4A4GemmWeight.cc:62-79; the reference's state-dict loader for this layer is
+// empty, so its .bin names serve as keys).
+struct W4Weight {
+    Tensor  packed, w_scale, smooth, lora_down, lora_up, bias, workspace;
+    int64_t n = 0, k = 0;
+    int     epilogue = LYRAQ_EPI_ROUND_EACH;
+
+    void load(const c10::Dict<std::string, Tensor>& sd, const std::string& name, int64_t n_, int64_t k_, bool has_bias, bool gelu,
+              const at::Device& dev, at::ScalarType dt)
+    {
+        n         = n_;
+        k         = k_;
+        packed    = sd.at(name + "packed_weight").to(dev).contiguous().view(at::kByte).reshape({n, k / 2});
+        w_scale   = sd.at(name + "weight_scale").to(dev).contiguous().reshape({n, k / 64});
+        if (w_scale.scalar_type() != at::kFloat && w_scale.scalar_type() != at::kHalf) {
+            w_scale = w_scale.to(at::kFloat);
+        }
+        smooth    = sd.at(name + "smooth").to(dev, at::kFloat).contiguous();
+        lora_down = sd.at(name + "lora_down").to(dev, dt).contiguous().reshape({32, k});
+        lora_up   = sd.at(name + "lora_up").to(dev, dt).contiguous().reshape({n, 32});
+        if (has_bias) {
+            bias = sd.at(name + "bias").to(dev, dt).contiguous();
+        }
+        epilogue = LYRAQ_EPI_ROUND_EACH | (gelu ? LYRAQ_EPI_GELU_TANH : 0);
+    }
+
+    // the whole of W4A4Gemm<T>::forward with the roundings of the 16-bit kernels that follow it in the reference
+    Tensor run(const Tensor& x, int64_t m, const Tensor& residual, at::ScalarType dt)
+    {
+        const size_t need = lyraq_workspace_bytes(LYRAQ_OP_LINEAR_W4A4_LORA, (int)m, (int)n, (int)k);
+        if (!workspace.defined() || (size_t)workspace.numel() < need) {
+            workspace = at::empty({(int64_t)need}, x.options().dtype(at::kByte));
+        }
+        Tensor y = at::empty({m, n}, x.options().dtype(dt));
+        check(lyraq_w4a4_lora_forward(y.data_ptr(), x.data_ptr(), dt_code(dt), smooth.data_ptr<float>(), packed.data_ptr<uint8_t>(),
+                                      w_scale.data_ptr(), w_scale.scalar_type() == at::kHalf ? LYRAQ_F16 : LYRAQ_F32,
+                                      lora_down.data_ptr(), lora_up.data_ptr(), ptr(bias), ptr(residual), epilogue, (int)m, (int)n,
+                                      (int)k, workspace.data_ptr(), (size_t)workspace.numel(), stream()),
+              "lyraq_w4a4_lora_forward");
+        return y;
+    }
+};
+
 struct Modulation {
     bool      fp8 = false;
     Fp8Weight q;
@@ -161,7 +206,8 @@ struct BlockBase: torch::CustomClassHolder {
         dtype(parse_dtype(inference_dtype)), dim(embedding_dim), heads(embedding_head_num), head_dim(embedding_head_dim),
         mlp_scale(mlp_scale_), quant_level(quant_level_)
     {
-        TORCH_CHECK(quant_level == 1 || quant_level == 2, "only quant_level 1 (FP8_W8A8) and 2 (FP8_W8A8_FULL) are built");
+        TORCH_CHECK(quant_level == 1 || quant_level == 2 || quant_level == 7 || quant_level == 8,
+                    "only quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built");
         TORCH_CHECK(heads * head_dim == dim, "embedding_dim must equal embedding_head_num * embedding_head_dim");
     }
     void initialize(const c10::intrusive_ptr<LyraDiffCommonContext>&) {}
@@ -177,27 +223,40 @@ struct BlockBase: torch::CustomClassHolder {
 struct FluxSingleTransformerBlockOp: BlockBase {
     using BlockBase::BlockBase;
     Fp8Weight  qkv, mlp, out;
+    W4Weight   qkv4, mlp4, out4_attn, out4_mlp;  // quant_level 7 / 8
     Modulation norm;
     Tensor     qk_scale;
+
+    bool   int4() const { return quant_level == 7 || quant_level == 8; }
+    Tensor forward_int4(const Tensor& hidden, const Tensor& rope, const std::vector<Tensor>& mod);
 
     void reload_model_from_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device)
     {
         const at::Device dev(device);
         auto g = [&](const std::string& n) { return sd.at(prefix + n); };
-        qkv.load(g("attn.to_qkv.weight"), g("attn.to_qkv.bias"), g("attn.to_qkv_input_scale"), dev, dtype);
-        mlp.load(g("proj_mlp.weight"), g("proj_mlp.bias"), g("proj_mlp_input_scale"), dev, dtype);
-        out.load(g("proj_out.weight"), g("proj_out.bias"), g("proj_out_input_scale"), dev, dtype);
+        const bool fp8_modulation = quant_level == 2 || quant_level == 8;
+        if (int4()) {
+            // keys of FluxSingleTransformerInt4BlockWeight.cc:79-83 and FluxSingleAttentionInt4ProcessorWeight.cc:73-78
+            qkv4.load(sd, prefix + "attn.to_qkv.", 3 * dim, dim, true, false, dev, dtype);
+            mlp4.load(sd, prefix + "proj_mlp.", mlp_scale * dim, dim, true, true, dev, dtype);
+            out4_attn.load(sd, prefix + "proj_out.linears.0.", dim, dim, true, false, dev, dtype);
+            out4_mlp.load(sd, prefix + "proj_out.linears.1.linear.", dim, mlp_scale * dim, false, false, dev, dtype);
+        } else {
+            qkv.load(g("attn.to_qkv.weight"), g("attn.to_qkv.bias"), g("attn.to_qkv_input_scale"), dev, dtype);
+            mlp.load(g("proj_mlp.weight"), g("proj_mlp.bias"), g("proj_mlp_input_scale"), dev, dtype);
+            out.load(g("proj_out.weight"), g("proj_out.bias"), g("proj_out_input_scale"), dev, dtype);
+            TORCH_CHECK(qkv.n == 3 * dim && mlp.n == mlp_scale * dim && out.k == (mlp_scale + 1) * dim,
+                        "weight shapes do not match the block's dimensions");
+        }
         c10::Dict<std::string, Tensor> sub;
         for (const char* n : {"norm.linear.weight", "norm.linear.bias"}) {
             sub.insert(n, g(n));
         }
-        if (quant_level == 2) {
+        if (fp8_modulation) {
             sub.insert("norm.linear_input_scale", g("norm.linear_input_scale"));
         }
-        norm.load(sub, "norm.linear", quant_level == 2, dev, dtype);
+        norm.load(sub, "norm.linear", fp8_modulation, dev, dtype);
         qk_scale = at::cat({g("attn.norm_q.weight").reshape({-1}), g("attn.norm_k.weight").reshape({-1})}).to(dev, dtype).contiguous();
-        TORCH_CHECK(qkv.n == 3 * dim && mlp.n == mlp_scale * dim && out.k == (mlp_scale + 1) * dim,
-                    "weight shapes do not match the block's dimensions");
         loaded = true;
     }
 
@@ -209,6 +268,9 @@ struct FluxSingleTransformerBlockOp: BlockBase {
         TORCH_CHECK(D == dim && temb.size(0) == B && temb.size(1) == D && rope.numel() == T * head_dim * 2, "shape mismatch");
         const int  dtc  = dt_code(dtype);
         auto       mod  = norm.run(temb, 3, dtype);  // shift, scale, gate
+        if (int4()) {
+            return forward_int4(hidden, rope, mod);
+        }
         const auto opt8 = hidden.options().dtype(at::kByte);
         Tensor     nq = at::empty({T, D}, opt8), mq = at::empty({T, D}, opt8);
         check(lyraq_adaln_quant_fp8x2(nullptr, nq.data_ptr<uint8_t>(), qkv.input_scale.data_ptr<float>(), mq.data_ptr<uint8_t>(),
@@ -234,9 +296,39 @@ struct FluxSingleTransformerBlockOp: BlockBase {
     }
 };
 
+// FluxSingleTransformerInt4Block<T>::forward (layers/flux_single_transformer_block/FluxSingleTransformerInt4Block.cc:198-322):
+// every linear a W4A4 linear with its LoRA branch; proj_out is two of them, summed through the second one's residual.
+Tensor FluxSingleTransformerBlockOp::forward_int4(const Tensor& hidden, const Tensor& rope, const std::vector<Tensor>& mod)
+{
+    const int64_t B = hidden.size(0), S = hidden.size(1), D = hidden.size(2), T = B * S;
+    const int     dtc = dt_code(dtype);
+    Tensor norm16 = at::empty({T, D}, hidden.options());
+    check(lyraq_adaln_quant(norm16.data_ptr(), nullptr, nullptr, nullptr, nullptr, hidden.data_ptr(), mod[1].data_ptr(),
+                            mod[0].data_ptr(), dtc, nullptr, (size_t)B, (size_t)S, (size_t)D, 1e-6, stream()),
+          "lyraq_adaln_quant");
+    Tensor q3 = qkv4.run(norm16, T, Tensor(), dtype);
+    check(lyraq_rmsnorm_rope(q3.data_ptr(), q3.data_ptr(), qk_scale.data_ptr(), rope.data_ptr(), dtc, 1e-6, (size_t)B, (size_t)S,
+                             (int)heads, (int)head_dim, stream()),
+          "lyraq_rmsnorm_rope");
+    Tensor attn = attention(q3, B, S, heads, head_dim).reshape({T, D}).contiguous();
+    Tensor act  = mlp4.run(norm16, T, Tensor(), dtype);
+    Tensor h1   = out4_attn.run(attn, T, Tensor(), dtype);
+    Tensor h    = out4_mlp.run(act, T, h1, dtype);
+    Tensor out  = at::empty_like(hidden);
+    check(lyraq_gate_residual(out.data_ptr(), h.data_ptr(), mod[2].data_ptr(), hidden.data_ptr(), dtc, (size_t)B, (size_t)S, (size_t)D,
+                              stream()),
+          "lyraq_gate_residual");
+    return out;
+}
+
 // FluxTransformerBlockOp (th_op/flux_transformer_block/FluxTransformerBlockOp.h:187-237)
 struct FluxTransformerBlockOp: BlockBase {
-    using BlockBase::BlockBase;
+    FluxTransformerBlockOp(const std::string& inference_dtype, int64_t embedding_dim, int64_t embedding_head_num,
+                           int64_t embedding_head_dim, int64_t mlp_scale_, int64_t quant_level_):
+        BlockBase(inference_dtype, embedding_dim, embedding_head_num, embedding_head_dim, mlp_scale_, quant_level_)
+    {
+        TORCH_CHECK(quant_level == 1 || quant_level == 2, "the double-stream block is built for quant_level 1 and 2 only");
+    }
     struct Stream {
         Fp8Weight  qkv, out, ff1, ff2;
         Modulation norm;

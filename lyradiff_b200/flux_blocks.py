@@ -19,16 +19,32 @@ method names and tensor conventions, running the FP8 data flow of FluxSingleTran
 
 The 16-bit concat buffer and its quantize pass (invokeFusedCatAndGelu + invokeCudaD2DScaleCpyConvert) do not exist here.
 quant_level 1 (FP8_W8A8) keeps the modulation linear in 16 bits (a torch matmul, as the reference calls cuBLAS for it),
-quant_level 2 (FP8_W8A8_FULL) runs it in FP8 too.  Other levels, LoRA hot-swap and the .bin directory loader are not
-built: they raise NotImplementedError.
+quant_level 2 (FP8_W8A8_FULL) runs it in FP8 too.
+
+quant_level 7 (INT4_W4A4) and 8 (INT4_W4A4_FULL, FP8 modulation linear) of the single-stream block run the W4A4 data flow of
+FluxSingleTransformerInt4Block<T>::forward (layers/flux_single_transformer_block/FluxSingleTransformerInt4Block.cc:198-322)
+and FluxSingleAttentionInt4Processor<T>::forward (layers/flux_single_attention_processor/FluxSingleAttentionInt4Processor.cc:
+138-192), each linear one lyraq_w4a4_lora_forward (int4 quantize + LoRA-down, then grouped GEMM + LoRA-up + epilogue):
+
+    norm = LN(x) * (1 + scale) + shift                     16-bit                          (lyraq_adaln_quant, y only)
+    qkv  = T(T(W4A4(norm, to_qkv)) + bias)                 -> QK RMSNorm + RoPE in place   (the bias add of
+                                                                                           fuseBiasRmsNormAndRope)
+    mlp  = T(gelu(T(T(W4A4(norm, proj_mlp)) + bias)))                                      (invokeFusedBiasAndGelu)
+    h    = T(T(W4A4(mlp, proj_out.linears.1.linear)) + T(T(W4A4(attn, proj_out.linears.0)) + bias))
+                                                                                           (invokeFusedBiasAndResidual)
+    out  = T(T(h * gate) + x)                                                              (lyraq_gate_residual)
+
+with the roundings of the reference's separate 16-bit kernels kept inside the GEMM epilogues (LYRAQ_EPI_ROUND_EACH).
+Other levels, the INT4 double-stream block, LoRA hot-swap and the .bin directory loader are not built: they raise
+NotImplementedError.
 """
 
 import torch
 
-from . import ops
+from . import layers, ops
 
 _DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16}
-FP8_W8A8, FP8_W8A8_FULL = 1, 2
+FP8_W8A8, FP8_W8A8_FULL, INT4_W4A4, INT4_W4A4_FULL = 1, 2, 7, 8
 
 
 class LyraDiffCommonContext:
@@ -53,13 +69,29 @@ class _Fp8Weight:
         self.input_scale = input_scale.to(device=device, dtype=torch.float32).reshape(1).contiguous()
 
 
+def _w4a4_from_state_dict(sd, name, n, k, device, dtype, has_bias, gelu=False):
+    """One W4A4 linear from the tensors W4A4GemmWeight<T>::loadWeights reads (src/lyradiff/layers/w4a4_gemm_block/
+    W4A4GemmWeight.cc:62-79; the reference's own state-dict loader for this layer is empty, so the .bin names serve as
+    keys): `<name>packed_weight` int8/uint8 [n, k/2], `<name>weight_scale` fp32 (or fp16) [n, k/64], `<name>smooth`
+    fp32 [k], `<name>lora_down` [32, k], `<name>lora_up` [n, 32], `<name>bias` [n] where the layer has one."""
+    pw = sd[name + "packed_weight"].to(device).contiguous().view(torch.uint8).reshape(n, k // 2)
+    ws = sd[name + "weight_scale"].to(device).contiguous().reshape(n, k // 64)
+    if ws.dtype not in (torch.float32, torch.float16):
+        ws = ws.float()
+    smooth = sd[name + "smooth"].to(device=device, dtype=torch.float32).contiguous()
+    down = sd[name + "lora_down"].to(device=device, dtype=dtype).contiguous().reshape(32, k)
+    up = sd[name + "lora_up"].to(device=device, dtype=dtype).contiguous().reshape(n, 32)
+    bias = sd[name + "bias"].to(device=device, dtype=dtype).contiguous() if has_bias else None
+    return layers.W4A4Gemm(pw, ws, smooth, bias, gelu=gelu, lora_down=down, lora_up=up, round_each=True)
+
+
 class FluxSingleTransformerBlockOp:
     def __init__(self, inference_dtype="bf16", embedding_dim=3072, embedding_head_num=24, embedding_head_dim=128, mlp_scale=4,
                  quant_level=0):
         if inference_dtype not in _DTYPES:
             raise RuntimeError("inference_dtype must be 'bf16' or 'fp16'")
-        if quant_level not in (FP8_W8A8, FP8_W8A8_FULL):
-            raise NotImplementedError("only quant_level 1 (FP8_W8A8) and 2 (FP8_W8A8_FULL) are built")
+        if quant_level not in (FP8_W8A8, FP8_W8A8_FULL, INT4_W4A4, INT4_W4A4_FULL):
+            raise NotImplementedError("only quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built")
         if embedding_head_num * embedding_head_dim != embedding_dim:
             raise RuntimeError("embedding_dim must equal embedding_head_num * embedding_head_dim")
         self.dtype = _DTYPES[inference_dtype]
@@ -93,6 +125,8 @@ class FluxSingleTransformerBlockOp:
         sd = state_dict
         g = lambda name: sd[prefix + name]
         w = {}
+        if self.quant_level in (INT4_W4A4, INT4_W4A4_FULL):
+            return self._reload_int4(prefix, sd, dev)
         w["qkv"] = _Fp8Weight(g("attn.to_qkv.weight"), g("attn.to_qkv.bias"), g("attn.to_qkv_input_scale"), dev, self.dtype)
         w["mlp"] = _Fp8Weight(g("proj_mlp.weight"), g("proj_mlp.bias"), g("proj_mlp_input_scale"), dev, self.dtype)
         w["out"] = _Fp8Weight(g("proj_out.weight"), g("proj_out.bias"), g("proj_out_input_scale"), dev, self.dtype)
@@ -106,6 +140,48 @@ class FluxSingleTransformerBlockOp:
         if w["qkv"].n != 3 * self.dim or w["mlp"].n != self.mlp_scale * self.dim or w["out"].k != (self.mlp_scale + 1) * self.dim:
             raise RuntimeError("weight shapes do not match the block's dimensions")
         self._w = w
+
+    def _reload_int4(self, prefix, sd, dev):
+        """Keys (FluxSingleTransformerInt4BlockWeight.cc:79-83, FluxSingleAttentionInt4ProcessorWeight.cc:73-78):
+        `<prefix>norm.linear.{weight,bias}` (+ `norm.linear_input_scale` at level 8), `<prefix>attn.norm_q.weight`,
+        `<prefix>attn.norm_k.weight` and the W4A4 linears `<prefix>attn.to_qkv.`, `<prefix>proj_mlp.`,
+        `<prefix>proj_out.linears.0.` (all with bias) and `<prefix>proj_out.linears.1.linear.` (no bias)."""
+        D, dt = self.dim, self.dtype
+        g = lambda name: sd[prefix + name]
+        w = {"int4": True}
+        w["qkv"] = _w4a4_from_state_dict(sd, prefix + "attn.to_qkv.", 3 * D, D, dev, dt, True)
+        w["mlp"] = _w4a4_from_state_dict(sd, prefix + "proj_mlp.", self.mlp_scale * D, D, dev, dt, True, gelu=True)
+        w["out1"] = _w4a4_from_state_dict(sd, prefix + "proj_out.linears.0.", D, D, dev, dt, True)
+        w["out2"] = _w4a4_from_state_dict(sd, prefix + "proj_out.linears.1.linear.", D, self.mlp_scale * D, dev, dt, False)
+        if self.quant_level == INT4_W4A4_FULL:
+            w["norm"] = _Fp8Weight(g("norm.linear.weight"), g("norm.linear.bias"), g("norm.linear_input_scale"), dev, dt)
+        else:
+            w["norm_w"] = g("norm.linear.weight").to(device=dev, dtype=dt).contiguous()
+            w["norm_b"] = g("norm.linear.bias").to(device=dev, dtype=dt).contiguous()
+        w["qk_scale"] = torch.cat([g("attn.norm_q.weight").reshape(-1), g("attn.norm_k.weight").reshape(-1)]).to(
+            device=dev, dtype=dt).contiguous()
+        self._w = w
+
+    def _forward_int4(self, hidden_states, rope_emb, shift, scale, gate):
+        B, S, D = hidden_states.shape
+        w, dev, dt, T = self._w, hidden_states.device, self.dtype, B * S
+        norm = self._buffer("norm16", (T, D), dt, dev)
+        ops.invoke_layer_norm_with_shift_and_scale(norm.view(B, S, D), hidden_states, scale, shift, eps=1e-6)
+        qkv = self._buffer("qkv", (T, 3 * D), dt, dev)
+        w["qkv"].forward(norm, out=qkv)
+        ops.invoke_fused_rmsnorm_and_rope(qkv, qkv, w["qk_scale"], rope_emb, 1e-6, B, S, self.heads, self.head_dim)
+        v5 = qkv.view(B, S, 3, self.heads, self.head_dim)
+        q, k, v = (v5[:, :, i].transpose(1, 2) for i in range(3))
+        attn = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(T, D)
+        mlp = self._buffer("mlp16", (T, self.mlp_scale * D), dt, dev)
+        w["mlp"].forward(norm, out=mlp)
+        h1 = self._buffer("h1", (T, D), dt, dev)
+        w["out1"].forward(attn, out=h1)
+        h = self._buffer("h", (T, D), dt, dev)
+        w["out2"].forward(mlp, residual=h1, out=h)
+        out = torch.empty_like(hidden_states)
+        ops.invoke_fused_gate_and_residual(out, h.view(B, S, D), gate, hidden_states)
+        return out
 
     def _buffer(self, name, shape, dtype, device):
         t = self._buf.get(name)
@@ -130,7 +206,7 @@ class FluxSingleTransformerBlockOp:
         T = B * S
 
         # ---- modulation: msa = linear(temb) -> shift | scale | gate
-        if self.quant_level == FP8_W8A8_FULL:
+        if self.quant_level in (FP8_W8A8_FULL, INT4_W4A4_FULL):
             nw = w["norm"]
             tq = self._buffer("temb_q", (B, D), torch.uint8, dev)
             ops.invoke_cuda_d2d_scale_cpy_convert(tq, temb, nw.input_scale)
@@ -139,6 +215,8 @@ class FluxSingleTransformerBlockOp:
         else:
             msa = torch.addmm(w["norm_b"], temb, w["norm_w"].t())
         shift, scale, gate = (c.contiguous() for c in msa.chunk(3, dim=1))
+        if w.get("int4"):
+            return self._forward_int4(hidden_states, rope_emb, shift, scale, gate)
 
         # ---- AdaLN modulation straight into the e4m3 inputs of to_qkv and proj_mlp (their input scales differ); the
         # 16-bit result is never written

@@ -87,12 +87,15 @@ class W4A4Gemm:
     """W4A4 group-64 linear: W4A4Gemm<T> / W4A4GemmWeight<T> (src/lyradiff/layers/w4a4_gemm_block/W4A4Gemm.cc:113-169,
     W4A4GemmWeight.h:8-45): packed int4 weight [n, k/2], group scales [n, k/64], smoothing vector, optional bias."""
 
-    def __init__(self, packed_weight, weight_scale, smooth=None, bias=None, gelu=False, lora_down=None, lora_up=None):
+    def __init__(self, packed_weight, weight_scale, smooth=None, bias=None, gelu=False, lora_down=None, lora_up=None,
+                 round_each=False):
         self.n, self.k = packed_weight.shape[0], packed_weight.shape[1] * 2
         self.qweight, self.w_scale, self.smooth, self.bias, self.gelu = packed_weight, weight_scale, smooth, bias, gelu
         if (lora_down is None) != (lora_up is None):
             raise ValueError("lora_down [32, k] and lora_up [n, 32] come together")
         self.lora_down, self.lora_up = lora_down, lora_up
+        # round_each: round after every epilogue step (the bits of the reference's GEMM + separate 16-bit kernels)
+        self._epi = (ops.EPI_GELU_TANH if gelu else ops.EPI_NONE) | (ops.EPI_ROUND_EACH if round_each else 0)
         self._ws = None
 
     @classmethod
@@ -112,14 +115,13 @@ class W4A4Gemm:
             st = _lib.lib().lyraq_w4a4_lora_forward(
                 ops._p(y), ops._p(x2), ops._dt(x2), ops._p(self.smooth), ops._p(self.qweight), ops._p(self.w_scale),
                 ops._dt(self.w_scale), ops._p(self.lora_down), ops._p(self.lora_up), ops._p(self.bias), ops._p(residual),
-                ops.EPI_GELU_TANH if self.gelu else ops.EPI_NONE, m, self.n, self.k, ops._p(self._ws), self._ws.numel(),
-                ops._stream())
+                self._epi, m, self.n, self.k, ops._p(self._ws), self._ws.numel(), ops._stream())
             _lib.check(st, "lyraq_w4a4_lora_forward")
             return y.reshape(*x.shape[:-1], self.n)
         self._ws = _workspace(OP_LINEAR_W4A4, m, self.n, self.k, x.device, self._ws)
         st = _lib.lib().lyraq_w4a4_forward(
             ops._p(y), ops._p(x2), ops._dt(x2), ops._p(self.smooth), ops._p(self.qweight), ops._p(self.w_scale),
-            ops._dt(self.w_scale), ops._p(self.bias), ops._p(residual), ops.EPI_GELU_TANH if self.gelu else ops.EPI_NONE, m,
+            ops._dt(self.w_scale), ops._p(self.bias), ops._p(residual), self._epi, m,
             self.n, self.k, ops._p(self._ws), self._ws.numel(), ops._stream())
         _lib.check(st, "lyraq_w4a4_forward")
         return y.reshape(*x.shape[:-1], self.n)

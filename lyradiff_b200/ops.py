@@ -12,7 +12,7 @@ from . import _lib
 
 F16, BF16, F32, S32 = 0, 1, 2, 3
 SCALE_PER_TENSOR, SCALE_PER_TOKEN, SCALE_PER_TOKEN_DYNAMIC = 0, 1, 2
-EPI_NONE, EPI_GELU_TANH = 0, 1
+EPI_NONE, EPI_GELU_TANH, EPI_ROUND_EACH = 0, 1, 2
 
 _DTYPES = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32, torch.int32: S32}
 
@@ -265,10 +265,12 @@ def gemm_fp8_quant_out(W, w_scale, X, x_scale, Yq, y_scale, dtype, bias=None, re
     return Yq
 
 
-def invoke_fused_w4a4_gemm_and_lora_up(D, A, B, lora_act, lora_up, sa, sb, bias=None, residual=None, is_gelu=False):
+def invoke_fused_w4a4_gemm_and_lora_up(D, A, B, lora_act, lora_up, sa, sb, bias=None, residual=None, is_gelu=False,
+                                       round_each=False):
     """invokeFusedW4A4GemmAndLoraUp (src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.h:19-30) with the bias / GELU / residual
     kernels that follow it fused in.  A uint8 [m,k/2], B uint8 [n,k/2], sa fp32 [m,k/64], sb fp32|fp16 [n,k/64];
-    lora_act [m,32] fp32 (as the quantizer wrote it) or already of D's dtype, lora_up [n,32] of D's dtype."""
+    lora_act [m,32] fp32 (as the quantizer wrote it) or already of D's dtype, lora_up [n,32] of D's dtype.
+    round_each: round to D's dtype after every epilogue step, as the reference's separate kernels do."""
     m, kh = A.shape
     n = B.shape[0]
     k = kh * 2
@@ -276,7 +278,8 @@ def invoke_fused_w4a4_gemm_and_lora_up(D, A, B, lora_act, lora_up, sa, sb, bias=
         raise ValueError("shape mismatch")
     st = _lib.lib().lyraq_gemm_w4a4(_p(A), _p(B), _p(sa), _p(sb), _dt(sb), _p(D), _dt(D), _p(lora_act),
                                     F32 if lora_act is None else _dt(lora_act), _p(lora_up),
-                                    _p(bias), _p(residual), EPI_GELU_TANH if is_gelu else EPI_NONE, m, n, k, None, 0,
-                                    _stream())
+                                    _p(bias), _p(residual),
+                                    (EPI_GELU_TANH if is_gelu else EPI_NONE) | (EPI_ROUND_EACH if round_each else 0), m, n, k,
+                                    None, 0, _stream())
     _lib.check(st, "lyraq_gemm_w4a4")
     return D

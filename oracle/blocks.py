@@ -1,4 +1,5 @@
-"""CPU restatement of the FP8 FLUX single-stream block, for the parity test of lyradiff_b200.flux_blocks.
+"""CPU restatement of the FLUX blocks (FP8 single- and double-stream, INT4 single-stream), for the parity tests of
+lyradiff_b200.flux_blocks.
 
 TEST INFRASTRUCTURE ONLY (see oracle/__init__.py).  PARITY UNPINNED: the reference has no test or golden vector for
 this block; the data flow follows FluxSingleTransformerFP8Block<T>::forward
@@ -115,3 +116,45 @@ def flux_double_block(hidden, encoder, rope, temb, sd, prefix, heads, head_dim, 
         f2 = lin(f1, ff + ".net.2").reshape(B, L, D)
         outs[key] = _n.gate_residual(f2, mod[5], h)
     return outs["img"], outs["txt"]
+
+
+def _w4a4_linear(x, sd, name, out_dtype, gelu=False, residual=None):
+    """One W4A4 linear as W4A4Gemm<T>::forward runs it (src/lyradiff/layers/w4a4_gemm_block/W4A4Gemm.cc:113-169): int4
+    quantize of x / smooth with the low-rank down projection beside it, grouped s4 GEMM + LoRA-up stored as T, then the
+    reference's separate 16-bit kernels for bias / GELU / residual, each of which rounds to T (round_each).
+    Weights under `name`: packed_weight uint8 [n, k/2], weight_scale [n, k/64], smooth fp32 [k], lora_down T [32, k],
+    lora_up T [n, 32], optional bias T [n] (the file names of W4A4GemmWeight<T>::loadWeights, W4A4GemmWeight.cc:62-79)."""
+    _, sa, qa = _q.int4_quant_g64(x, sd[name + "smooth"])
+    act = _q.lora_down(x, sd[name + "lora_down"].to(out_dtype))
+    qw = _q.unpack_int4(sd[name + "packed_weight"])
+    return _g.w4a4_gemm(qa, qw, sa, sd[name + "weight_scale"], out_dtype=out_dtype, bias=sd.get(name + "bias"), gelu=gelu,
+                        residual=residual, lora_act=act, lora_up=sd[name + "lora_up"].to(out_dtype), round_each=True)
+
+
+def flux_single_block_int4(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_scale=4, quant_level=7):
+    """INT4 single-stream block: FluxSingleTransformerInt4Block<T>::forward
+    (src/lyradiff/layers/flux_single_transformer_block/FluxSingleTransformerInt4Block.cc:198-322) with
+    FluxSingleAttentionInt4Processor<T>::forward
+    (src/lyradiff/layers/flux_single_attention_processor/FluxSingleAttentionInt4Processor.cc:138-192).
+    quant_level 7: 16-bit modulation linear; 8: FP8 modulation linear.  proj_out is two W4A4 linears, one over the
+    attention output (with the bias) and one over the MLP activation, summed by fusedBiasAndResidual."""
+    dt = hidden.dtype
+    B, S, D = hidden.shape
+    g = lambda name: sd[prefix + name]
+    if quant_level == 8:
+        msa = _fp8_linear(temb, g("norm.linear.weight").to(dt), g("norm.linear.bias").to(dt), g("norm.linear_input_scale"), dt)
+    else:
+        msa = (temb.double() @ g("norm.linear.weight").to(dt).double().t() + g("norm.linear.bias").to(dt).double()).to(dt)
+    shift, scale, gate = msa.chunk(3, dim=1)
+    n2 = _n.adaln_modulate(hidden, scale, shift, eps=1e-6).reshape(B * S, D)
+    qkv = _w4a4_linear(n2, sd, prefix + "attn.to_qkv.", dt)  # the bias add of fuseBiasRmsNormAndRope is the T-rounded step
+    qk_scale = torch.cat([g("attn.norm_q.weight").reshape(-1), g("attn.norm_k.weight").reshape(-1)]).to(dt)
+    qkv = _n.rmsnorm_rope(qkv, qk_scale, rope.reshape(B * S, head_dim // 2, 2, 2), heads, head_dim, eps=1e-6)
+    v5 = qkv.reshape(B, S, 3, heads, head_dim)
+    q, k, v = (v5[:, :, i].transpose(1, 2) for i in range(3))
+    attn = attention(q, k, v).transpose(1, 2).reshape(B * S, D).to(dt)
+    mlp = _w4a4_linear(n2, sd, prefix + "proj_mlp.", dt, gelu=True)
+    h1 = _w4a4_linear(attn, sd, prefix + "proj_out.linears.0.", dt)
+    h = _w4a4_linear(mlp, sd, prefix + "proj_out.linears.1.linear.", dt, residual=h1)
+    out = _n.gate_residual(h.reshape(B, S, D), gate, hidden)
+    return out, {"msa": msa, "qkv": qkv, "attn": attn, "mlp": mlp, "h": h}

@@ -109,7 +109,7 @@ def w4a4_group_partials(qa, qw, group=64):
 
 
 def w4a4_gemm(qa, qw, sa, sb, out_dtype=torch.bfloat16, group=64, bias=None, gelu=False,
-              residual=None, lora_act=None, lora_up=None, fma=True):
+              residual=None, lora_act=None, lora_up=None, fma=True, round_each=False):
     """Grouped s4 GEMM with fp32 rescale.
 
     Follows w4a4_gemm (src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.cu:473-507): for g in order,
@@ -123,7 +123,9 @@ def w4a4_gemm(qa, qw, sa, sb, out_dtype=torch.bfloat16, group=64, bias=None, gel
     T(acc) (``:717``); bias / GELU-tanh / residual follow the standalone kernels that come
     next in the reference (src/lyradiff/kernels/flux_single_transformer_block/
     flux_single_transformer_kernels.cu:68-134) but are applied here in fp32 before the one
-    rounding, which is the fused order this build uses.
+    rounding, which is the fused order this build uses; round_each=True instead rounds to T after
+    the store and after each of those kernels, which is what the reference's separate launches give
+    (T(acc) ``:717``; `add` of two T2 values in fusedBiasAndGelu / fusedBiasAndResidual rounds to T).
     qa [M,K], qw [N,K] unpacked int8 in [-8,7]; sa fp32 [M,K/g]; sb fp32|fp16 [N,K/g].
     """
     m, k = qa.shape
@@ -146,10 +148,12 @@ def w4a4_gemm(qa, qw, sa, sb, out_dtype=torch.bfloat16, group=64, bias=None, gel
         # output are summed here in fp64 and added to the fp32 accumulator in one step
         a16 = lora_act.to(out_dtype if out_dtype != F32 else torch.bfloat16).double()
         acc = (acc.double() + a16 @ lora_up.double().t()).to(F32)
+    rnd = (lambda t: t.to(out_dtype).to(F32)) if round_each else (lambda t: t)
+    acc = rnd(acc)
     if bias is not None:
-        acc = acc + bias.to(F32)[None, :]
+        acc = rnd(acc + bias.to(F32)[None, :])
     if gelu:
-        acc = gelu_tanh(acc)
+        acc = rnd(gelu_tanh(acc))
     if residual is not None:
         acc = acc + residual.to(F32)
     return acc.to(out_dtype)

@@ -127,7 +127,9 @@ def test_double_block_against_oracle(level, B, S, E):
 def test_block_refuses_what_is_not_built():
     from lyradiff_b200 import flux_blocks
     with pytest.raises(NotImplementedError):
-        flux_blocks.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 7)
+        flux_blocks.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 3)
+    with pytest.raises(NotImplementedError):
+        flux_blocks.FluxTransformerBlockOp("bf16", 256, 2, 128, 4, 7)   # the INT4 double-stream block is not built
     op = flux_blocks.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 1)
     with pytest.raises(NotImplementedError):
         op.reload_model_from_bin("/nowhere", "bf16")
@@ -135,3 +137,72 @@ def test_block_refuses_what_is_not_built():
         op.forward(torch.zeros(1, 8, 256, dtype=torch.bfloat16, device="cuda"),
                    torch.zeros(1, 8, 64, 2, 2, dtype=torch.bfloat16, device="cuda"),
                    torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda"))
+
+
+def _int4_state_dict(prefix, D, mlp_scale, head_dim, level, g, dt=torch.bfloat16):
+    from oracle import quant
+    sd = {}
+
+    def w4(name, n, k, std, bias):
+        w = (torch.randn(n, k, generator=g) * std).to(dt)
+        pw, sw, _ = quant.int4_weight_quant_g64(w)
+        sd[prefix + name + "packed_weight"] = pw.view(torch.int8)
+        sd[prefix + name + "weight_scale"] = sw.float()
+        sd[prefix + name + "smooth"] = 0.5 + torch.rand(k, generator=g)
+        sd[prefix + name + "lora_down"] = (torch.randn(32, k, generator=g) * 0.02).to(dt)
+        sd[prefix + name + "lora_up"] = (torch.randn(n, 32, generator=g) * 0.05).to(dt)
+        if bias:
+            sd[prefix + name + "bias"] = (torch.randn(n, generator=g) * 0.02).to(dt)
+
+    sd[prefix + "norm.linear.weight"] = (torch.randn(3 * D, D, generator=g) * 0.03).to(dt)
+    sd[prefix + "norm.linear.bias"] = (torch.randn(3 * D, generator=g) * 0.02).to(dt)
+    if level == 8:
+        sd[prefix + "norm.linear_input_scale"] = torch.tensor([0.01])
+    w4("attn.to_qkv.", 3 * D, D, 0.05, True)
+    w4("proj_mlp.", mlp_scale * D, D, 0.05, True)
+    w4("proj_out.linears.0.", D, D, 0.04, True)
+    w4("proj_out.linears.1.linear.", D, mlp_scale * D, 0.03, False)
+    sd[prefix + "attn.norm_q.weight"] = (1.0 + 0.1 * torch.randn(head_dim, generator=g)).to(dt)
+    sd[prefix + "attn.norm_k.weight"] = (1.0 + 0.1 * torch.randn(head_dim, generator=g)).to(dt)
+    return sd
+
+
+@pytest.mark.parametrize("level", [7, 8])
+@pytest.mark.parametrize("B,S", [(1, 160), (2, 96)])
+def test_single_block_int4_against_oracle(level, B, S):
+    """quant_level 7 / 8: every linear of the block is a W4A4 linear with its rank-32 LoRA branch.  Tolerances as for the FP8
+    block; the int4 codes that flip where the attention output differs in the last bit are the dominant term."""
+    from lyradiff_b200 import flux_blocks
+    D, heads, head_dim, mlp_scale = 256, 2, 128, 4
+    g = torch.Generator().manual_seed(1000 * level + S)
+    prefix = "single_transformer_blocks.9."
+    sd = _int4_state_dict(prefix, D, mlp_scale, head_dim, level, g)
+    hidden = torch.randn(B, S, D, generator=g).bfloat16()
+    temb = torch.nn.functional.silu(torch.randn(B, D, generator=g)).bfloat16()
+    ang = torch.rand(B, S, head_dim // 2, generator=g) * 6.28
+    rope = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+        B, S, head_dim // 2, 2, 2).bfloat16()
+
+    op = flux_blocks.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    op.initialize(flux_blocks.LyraDiffCommonContext())
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    out = op.forward(cu(hidden), cu(rope), cu(temb))
+    out2 = op.forward(cu(hidden), cu(rope), cu(temb))
+    check_status()
+    assert tuple(out.shape) == (B, S, D) and out.dtype == torch.bfloat16
+
+    want, mid = blocks.flux_single_block_int4(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_scale, level)
+    # the pieces in front of the attention see identical inputs on both sides: the W4A4 linear with the bias rounded in
+    # and the QK norm + RoPE agree to the LoRA-down summation order (a few fp32 ulps before the rounding to bf16)
+    qkv_gpu = op._buf["qkv"].cpu().float()
+    dq = (qkv_gpu - mid["qkv"].float()).abs()
+    assert float((dq > 0).float().mean()) < 0.05 and float(dq.max()) <= 2.0 ** -6 * float(mid["qkv"].float().abs().max())
+
+    delta, wdelta = out.cpu().float() - hidden.float(), want.float() - hidden.float()
+    err = (delta - wdelta).abs()
+    amp = float(wdelta.abs().mean())
+    assert amp > 0.05
+    assert float(err.mean()) <= 0.03 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
+    assert float(err.max()) <= 0.3 * float(wdelta.abs().max()), float(err.max())
+    # the LoRA-down sums use floating-point atomics (as the reference's do), so two runs may differ in the last bit
+    assert float((out.float() - out2.float()).abs().max()) <= 2.0 ** -6 * float(out.float().abs().max())

@@ -71,6 +71,29 @@ def test_epilogues(ops):
     assert rel_err(d, want) < 5e-3  # tanh.approx.f32 on the device
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_round_each_step_matches_separate_kernels(ops, dt):
+    """LYRAQ_EPI_ROUND_EACH: T after the accumulate, after the bias, (after GELU,) after the residual, i.e. the bits of the
+    reference's GEMM followed by its separate 16-bit bias / residual kernels."""
+    qa, qw = _rand_int4(200, 264, 256, seed=18)
+    g = torch.Generator().manual_seed(18)
+    sa = (torch.rand(200, 4, generator=g) * 0.5 + 0.1).float()
+    sb = (torch.rand(264, 4, generator=g) * 0.01 + 0.001).float()
+    bias = (torch.randn(264, generator=g) * 0.1).to(dt)
+    res = torch.randn(200, 264, generator=g).to(dt)
+    pa, pw = cu(quant.pack_int4(qa)), cu(quant.pack_int4(qw))
+    d = torch.empty(200, 264, dtype=dt, device="cuda")
+    ops.invoke_fused_w4a4_gemm_and_lora_up(d, pa, pw, None, None, cu(sa), cu(sb), bias=cu(bias), residual=cu(res), round_each=True)
+    want = gemm.w4a4_gemm(qa, qw, sa, sb, out_dtype=dt, bias=bias, residual=res, round_each=True)
+    assert_bit_equal(d, want, "round each: bias + residual")
+    once = gemm.w4a4_gemm(qa, qw, sa, sb, out_dtype=dt, bias=bias, residual=res)
+    assert not torch.equal(want, once)  # the two roundings do differ on this input
+    ops.invoke_fused_w4a4_gemm_and_lora_up(d, pa, pw, None, None, cu(sa), cu(sb), bias=cu(bias), is_gelu=True, round_each=True)
+    want = gemm.w4a4_gemm(qa, qw, sa, sb, out_dtype=dt, bias=bias, gelu=True, round_each=True)
+    assert rel_err(d, want) < 5e-3  # tanh.approx.f32 on the device
+    check_status()
+
+
 def test_golden_vectors(ops, golden):
     z = golden("w4a4")
     m, n = z["packed_a"].shape[0], z["packed_w"].shape[0]

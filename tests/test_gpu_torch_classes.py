@@ -88,3 +88,33 @@ def test_forward_rejects_wrong_inputs(ns):
         op.forward(x, r[:, :4].contiguous(), t)
     with pytest.raises(RuntimeError, match="inference dtype"):
         op.forward(x.cpu(), r, t)
+
+
+@pytest.mark.parametrize("level", [7, 8])
+@pytest.mark.parametrize("B,S", [(1, 160), (2, 96)])
+def test_single_block_int4_same_bits_as_mirror(ns, level, B, S):
+    from lyradiff_b200 import flux_blocks
+    from tests.test_gpu_flux_block import _int4_state_dict
+    D, heads, head_dim, mlp_scale = 256, 2, 128, 4
+    g = torch.Generator().manual_seed(13 * level + S)
+    prefix = "single_transformer_blocks.2."
+    sd = _int4_state_dict(prefix, D, mlp_scale, head_dim, level, g)
+    hidden = cu(torch.randn(B, S, D, generator=g).bfloat16())
+    temb = cu(torch.nn.functional.silu(torch.randn(B, D, generator=g)).bfloat16())
+    rope = cu(_rope(B, S, head_dim, g, torch.bfloat16))
+
+    mirror = flux_blocks.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    mirror.reload_model_from_state_dict(prefix, sd, "cuda")
+    want = mirror.forward(hidden, rope, temb)
+
+    op = ns.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    op.initialize(ns.LyraDiffCommonContext())
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    got = op.forward(hidden, rope, temb)
+    check_status()
+    assert torch.equal(got, want)
+
+
+def test_double_block_has_no_int4_level(ns):
+    with pytest.raises(RuntimeError, match="quant_level"):
+        ns.FluxTransformerBlockOp("bf16", 256, 2, 128, 4, 7)

@@ -71,3 +71,51 @@ def test_attention_matches_torch_sdpa():
     q, k, v = (torch.randn(1, 2, 17, 64, generator=g) for _ in range(3))
     want = torch.nn.functional.scaled_dot_product_attention(q, k, v)
     assert float((blocks.attention(q, k, v).float() - want).abs().max()) < 1e-5
+
+
+def test_w4a4_round_each_differs_from_one_rounding_by_at_most_a_few_ulps():
+    from oracle import gemm, quant
+    g = torch.Generator().manual_seed(4)
+    m, n, k = 24, 40, 128
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    _, sw, qw = quant.int4_weight_quant_g64(w)
+    _, sa, qa = quant.int4_quant_g64(x, None)
+    bias = (torch.randn(n, generator=g) * 0.1).bfloat16()
+    res = torch.randn(m, n, generator=g).bfloat16()
+    once = gemm.w4a4_gemm(qa, qw, sa, sw, bias=bias, residual=res).float()
+    each = gemm.w4a4_gemm(qa, qw, sa, sw, bias=bias, residual=res, round_each=True).float()
+    # restated directly: three 16-bit kernels in a row
+    acc = gemm.w4a4_gemm(qa, qw, sa, sw)                              # T(acc)
+    step = (acc.float() + bias.float()).bfloat16()                    # add of two T values, rounded to T
+    step = (step.float() + res.float()).bfloat16()
+    assert torch.equal(each, step.float())
+    # each of the two extra roundings moves the value by at most half a bf16 ulp of that step's magnitude
+    mag = acc.float().abs() + bias.float().abs() + res.float().abs()
+    assert bool(((each - once).abs() <= 2.0 ** -7 * mag).all())
+
+
+def test_int4_block_oracle_zero_gate_returns_the_input():
+    from oracle import quant
+    g = torch.Generator().manual_seed(5)
+    D, heads, hd, p = 128, 1, 128, "s."
+    sd = {p + "norm.linear.weight": torch.zeros(3 * D, D).bfloat16(), p + "norm.linear.bias": torch.zeros(3 * D).bfloat16(),
+          p + "attn.norm_q.weight": torch.ones(hd).bfloat16(), p + "attn.norm_k.weight": torch.ones(hd).bfloat16()}
+    for name, n, k, bias in (("attn.to_qkv.", 3 * D, D, True), ("proj_mlp.", 4 * D, D, True), ("proj_out.linears.0.", D, D, True),
+                             ("proj_out.linears.1.linear.", D, 4 * D, False)):
+        pw, sw, _ = quant.int4_weight_quant_g64((torch.randn(n, k, generator=g) * 0.05).bfloat16())
+        sd[p + name + "packed_weight"], sd[p + name + "weight_scale"] = pw, sw
+        sd[p + name + "smooth"] = torch.ones(k)
+        sd[p + name + "lora_down"] = (torch.randn(32, k, generator=g) * 0.02).bfloat16()
+        sd[p + name + "lora_up"] = (torch.randn(n, 32, generator=g) * 0.05).bfloat16()
+        if bias:
+            sd[p + name + "bias"] = (torch.randn(n, generator=g) * 0.02).bfloat16()
+    hidden = torch.randn(1, 12, D, generator=g).bfloat16()
+    rope = _rope(12, hd, g).reshape(1, 12, hd // 2, 2, 2).bfloat16()
+    temb = torch.randn(1, D, generator=g).bfloat16()
+    out, mid = blocks.flux_single_block_int4(hidden, rope, temb, sd, p, heads, hd, 4, 7)
+    assert torch.equal(out, hidden)                     # zero modulation linear -> gate 0 -> the residual alone
+    assert float(mid["h"].float().abs().mean()) > 0.01  # while the branch itself is not zero
+    sd[p + "norm.linear.bias"] = torch.cat([torch.zeros(2 * D), torch.ones(D)]).bfloat16()   # gate 1
+    out1, mid1 = blocks.flux_single_block_int4(hidden, rope, temb, sd, p, heads, hd, 4, 7)
+    assert torch.equal(out1, (mid1["h"].reshape(1, 12, D).float() + hidden.float()).bfloat16())
