@@ -4,7 +4,7 @@
 //                                                       embedding_head_dim, mlp_scale, quant_level)
 //   torch.classes.lyradiff.FluxTransformerBlockOp(... same ...)
 // with initialize / forward / reload_model_from_state_dict / reload_model_from_bin / load_lora_by_name / clear_lora.
-// quant_level 1, 2 (FP8) for both blocks; 7, 8 (INT4 W4A4) for the single-stream block.
+// quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4; the double-stream block keeps net.2 in FP8, as the reference does).
 // Host code only: every device operation is a call into the C ABI of liblyraq.so (include/lyraq.h) on torch's current
 // stream, plus two ATen library calls per block (scaled_dot_product_attention, and addmm for the 16-bit modulation
 // linear of quant_level 1).  torch supplies device memory, the stream and the class registry; nothing here computes.
@@ -323,14 +323,11 @@ Tensor FluxSingleTransformerBlockOp::forward_int4(const Tensor& hidden, const Te
 
 // FluxTransformerBlockOp (th_op/flux_transformer_block/FluxTransformerBlockOp.h:187-237)
 struct FluxTransformerBlockOp: BlockBase {
-    FluxTransformerBlockOp(const std::string& inference_dtype, int64_t embedding_dim, int64_t embedding_head_num,
-                           int64_t embedding_head_dim, int64_t mlp_scale_, int64_t quant_level_):
-        BlockBase(inference_dtype, embedding_dim, embedding_head_num, embedding_head_dim, mlp_scale_, quant_level_)
-    {
-        TORCH_CHECK(quant_level == 1 || quant_level == 2, "the double-stream block is built for quant_level 1 and 2 only");
-    }
+    using BlockBase::BlockBase;
+    bool int4() const { return quant_level == 7 || quant_level == 8; }
     struct Stream {
         Fp8Weight  qkv, out, ff1, ff2;
+        W4Weight   qkv4, out4, ff14;  // quant_level 7 / 8: to_qkv, to_out and net.0.proj are W4A4 linears; net.2 stays FP8
         Modulation norm;
         Tensor     qk_scale;
     } img, txt;
@@ -341,17 +338,25 @@ struct FluxTransformerBlockOp: BlockBase {
     {
         auto g = [&](const std::string& n) { return sd.at(prefix + n); };
         auto lin = [&](Fp8Weight& w, const std::string& n) { w.load(g(n + ".weight"), g(n + ".bias"), g(n + "_input_scale"), dev, dtype); };
-        lin(s.qkv, qkv);
-        lin(s.out, out);
-        lin(s.ff1, ff + ".net.0.proj");
+        const bool fp8_modulation = quant_level == 2 || quant_level == 8;
+        if (int4()) {
+            // keys of FluxAttentionInt4ProcessorWeight.cc:63-66 and FluxAttnPostInt4ProcessorWeight.cc:94-96
+            s.qkv4.load(sd, prefix + qkv + ".", 3 * dim, dim, true, false, dev, dtype);
+            s.out4.load(sd, prefix + out + ".", dim, dim, true, false, dev, dtype);
+            s.ff14.load(sd, prefix + ff + ".net.0.proj.", 4 * dim, dim, true, true, dev, dtype);
+        } else {
+            lin(s.qkv, qkv);
+            lin(s.out, out);
+            lin(s.ff1, ff + ".net.0.proj");
+        }
         lin(s.ff2, ff + ".net.2");
         c10::Dict<std::string, Tensor> sub;
         sub.insert("m.weight", g(norm + ".linear.weight"));
         sub.insert("m.bias", g(norm + ".linear.bias"));
-        if (quant_level == 2) {
+        if (fp8_modulation) {
             sub.insert("m_input_scale", g(norm + ".linear_input_scale"));
         }
-        s.norm.load(sub, "m", quant_level == 2, dev, dtype);
+        s.norm.load(sub, "m", fp8_modulation, dev, dtype);
         s.qk_scale = at::cat({g(nq).reshape({-1}), g(nk).reshape({-1})}).to(dev, dtype).contiguous();
     }
 
@@ -364,9 +369,21 @@ struct FluxTransformerBlockOp: BlockBase {
         loaded = true;
     }
 
-    Tensor pre_attention(const Stream& s, const Tensor& x, const std::vector<Tensor>& mod)
+    Tensor adaln16(const Tensor& x, const Tensor& scale, const Tensor& shift)
+    {
+        Tensor y = at::empty_like(x);
+        check(lyraq_adaln_quant(y.data_ptr(), nullptr, nullptr, nullptr, nullptr, x.data_ptr(), scale.data_ptr(), shift.data_ptr(),
+                                dt_code(dtype), nullptr, (size_t)x.size(0), (size_t)x.size(1), (size_t)x.size(2), 1e-6, stream()),
+              "lyraq_adaln_quant");
+        return y;
+    }
+
+    Tensor pre_attention(Stream& s, const Tensor& x, const std::vector<Tensor>& mod)
     {
         const int64_t B = x.size(0), S = x.size(1), D = x.size(2);
+        if (int4()) {
+            return s.qkv4.run(adaln16(x, mod[1], mod[0]).view({B * S, D}), B * S, Tensor(), dtype);
+        }
         Tensor nq = at::empty({B * S, D}, x.options().dtype(at::kByte));
         check(lyraq_adaln_quant(nullptr, nullptr, nullptr, nq.data_ptr<uint8_t>(), s.qkv.input_scale.data_ptr<float>(), x.data_ptr(),
                                 mod[1].data_ptr(), mod[0].data_ptr(), dt_code(dtype), nullptr, (size_t)B, (size_t)S, (size_t)D, 1e-6,
@@ -375,11 +392,27 @@ struct FluxTransformerBlockOp: BlockBase {
         return fp8_gemm(s.qkv, nq, B * S, dtype);
     }
 
-    Tensor post_attention(const Stream& s, const Tensor& x, const Tensor& attn, const std::vector<Tensor>& mod)
+    Tensor post_attention(Stream& s, const Tensor& x, const Tensor& attn, const std::vector<Tensor>& mod)
     {
         const int64_t B = x.size(0), S = x.size(1), D = x.size(2), T = B * S;
         const int     dtc  = dt_code(dtype);
         const auto    opt8 = x.options().dtype(at::kByte);
+        if (int4()) {
+            // FluxAttnPostInt4Processor<T>::forward: W4A4 to_out and net.0.proj with the reference's 16-bit bias / GELU
+            // kernels as rounding steps of their epilogues, then the e4m3 quantize and the FP8 net.2 with gate + residual
+            Tensor ao = s.out4.run(attn, T, Tensor(), dtype);
+            Tensor h  = at::empty_like(x);
+            check(lyraq_gate_residual(h.data_ptr(), ao.data_ptr(), mod[2].data_ptr(), x.data_ptr(), dtc, (size_t)B, (size_t)S,
+                                      (size_t)D, stream()),
+                  "lyraq_gate_residual");
+            Tensor n2  = adaln16(h, mod[4], mod[3]);
+            Tensor f1  = s.ff14.run(n2.view({T, D}), T, Tensor(), dtype);
+            Tensor f1q = at::empty({T, s.ff14.n}, opt8);
+            check(lyraq_quant_fp8(f1q.data_ptr<uint8_t>(), f1.data_ptr(), dtc, s.ff2.input_scale.data_ptr<float>(), 1,
+                                  (size_t)f1.numel(), stream()),
+                  "lyraq_quant_fp8");
+            return fp8_gemm_gate_residual(s.ff2, f1q, mod[5], h, B, S, dtype);
+        }
         Tensor aq = at::empty({T, D}, opt8);
         check(lyraq_quant_fp8(aq.data_ptr<uint8_t>(), attn.data_ptr(), dtc, s.out.input_scale.data_ptr<float>(), 1, (size_t)(T * D),
                               stream()),

@@ -35,8 +35,7 @@ and FluxSingleAttentionInt4Processor<T>::forward (layers/flux_single_attention_p
     out  = T(T(h * gate) + x)                                                              (lyraq_gate_residual)
 
 with the roundings of the reference's separate 16-bit kernels kept inside the GEMM epilogues (LYRAQ_EPI_ROUND_EACH).
-Other levels, the INT4 double-stream block, LoRA hot-swap and the .bin directory loader are not built: they raise
-NotImplementedError.
+Other levels, LoRA hot-swap and the .bin directory loader are not built: they raise NotImplementedError.
 """
 
 import torch
@@ -256,7 +255,7 @@ def _modulation(op, w, temb, chunks):
     """msa = linear(temb) -> `chunks` contiguous [B, D] tensors (AdaFP8LayerNorm<T>::forward,
     src/lyradiff/layers/ada_layer_norm/AdaFP8LayerNorm.cc:96-160)."""
     B, D = temb.shape
-    if op.quant_level == FP8_W8A8_FULL:
+    if "fp8" in w:
         nw = w["fp8"]
         tq = torch.empty(B, D, dtype=torch.uint8, device=temb.device)
         ops.invoke_cuda_d2d_scale_cpy_convert(tq, temb, nw.input_scale)
@@ -281,14 +280,19 @@ class FluxTransformerBlockOp:
         h    = x + gate * (FP8 GEMM(e4m3(attn), to_out) + bias)
         ff   = FP8 GEMM(e4m3(gelu(FP8 GEMM(e4m3(LN(h)(1+scale2)+shift2), net.0.proj) + bias)), net.2) + bias
         out  = h + gate2 * ff              (the quantize between the two FF linears is fused into the first GEMM's epilogue)
+
+    quant_level 7 / 8 (FluxTransformerInt4Block.cc:155-240, FluxAttentionInt4Processor.cc:157-305,
+    FluxAttnPostInt4Processor.cc forward): to_qkv, to_out and net.0.proj of each stream are W4A4 linears with LoRA (their
+    bias added by a 16-bit kernel in the reference, kept as a rounding step here), AdaLN outputs stay 16-bit, and net.2
+    stays an FP8 linear fed by an e4m3 quantize of the GELU output.
     """
 
     def __init__(self, inference_dtype="bf16", embedding_dim=3072, embedding_head_num=24, embedding_head_dim=128, mlp_scale=6,
                  quant_level=0):
         if inference_dtype not in _DTYPES:
             raise RuntimeError("inference_dtype must be 'bf16' or 'fp16'")
-        if quant_level not in (FP8_W8A8, FP8_W8A8_FULL):
-            raise NotImplementedError("only quant_level 1 (FP8_W8A8) and 2 (FP8_W8A8_FULL) are built")
+        if quant_level not in (FP8_W8A8, FP8_W8A8_FULL, INT4_W4A4, INT4_W4A4_FULL):
+            raise NotImplementedError("only quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built")
         if embedding_head_num * embedding_head_dim != embedding_dim:
             raise RuntimeError("embedding_dim must equal embedding_head_num * embedding_head_dim")
         self.dtype = _DTYPES[inference_dtype]
@@ -319,9 +323,21 @@ class FluxTransformerBlockOp:
         def lin(name):
             return _Fp8Weight(g(name + ".weight"), g(name + ".bias"), g(name + "_input_scale"), dev, self.dtype)
 
+        int4 = self.quant_level in (INT4_W4A4, INT4_W4A4_FULL)
+        D = self.dim
+
         def stream(norm, qkv, out, nq, nk, ff):
-            w = {"qkv": lin(qkv), "out": lin(out), "ff1": lin(ff + ".net.0.proj"), "ff2": lin(ff + ".net.2")}
-            if self.quant_level == FP8_W8A8_FULL:
+            if int4:
+                # W4A4 linears under the .bin names of W4A4GemmWeight (FluxAttentionInt4ProcessorWeight.cc:63-66,
+                # FluxAttnPostInt4ProcessorWeight.cc:94-96); net.2 as in the FP8 block
+                w = {"int4": True,
+                     "qkv": _w4a4_from_state_dict(state_dict, prefix + qkv + ".", 3 * D, D, dev, self.dtype, True),
+                     "out": _w4a4_from_state_dict(state_dict, prefix + out + ".", D, D, dev, self.dtype, True),
+                     "ff1": _w4a4_from_state_dict(state_dict, prefix + ff + ".net.0.proj.", 4 * D, D, dev, self.dtype, True, gelu=True),
+                     "ff2": lin(ff + ".net.2")}
+            else:
+                w = {"qkv": lin(qkv), "out": lin(out), "ff1": lin(ff + ".net.0.proj"), "ff2": lin(ff + ".net.2")}
+            if self.quant_level in (FP8_W8A8_FULL, INT4_W4A4_FULL):
                 w["norm"] = {"fp8": lin(norm + ".linear")}
             else:
                 w["norm"] = {"w": g(norm + ".linear.weight").to(device=dev, dtype=self.dtype).contiguous(),
@@ -338,6 +354,10 @@ class FluxTransformerBlockOp:
     def _pre_attention(self, w, x, temb):
         B, S, D = x.shape
         mod = _modulation(self, w["norm"], temb, 6)
+        if w.get("int4"):
+            norm = torch.empty(B, S, D, dtype=self.dtype, device=x.device)
+            ops.invoke_layer_norm_with_shift_and_scale(norm, x, mod[1], mod[0], eps=1e-6)
+            return mod, w["qkv"].forward(norm.view(B * S, D))
         norm_q = torch.empty(B * S, D, dtype=torch.uint8, device=x.device)
         ops.invoke_layer_norm_with_shift_and_scale(None, x, mod[1], mod[0], eps=1e-6, qf8=norm_q, f8_scale=w["qkv"].input_scale)
         qkv = torch.empty(B * S, 3 * D, dtype=self.dtype, device=x.device)
@@ -348,6 +368,8 @@ class FluxTransformerBlockOp:
         B, S, D = x.shape
         T = B * S
         dev, dt = x.device, self.dtype
+        if w.get("int4"):
+            return self._post_attention_int4(w, x, attn, mod)
         aq = torch.empty(T, D, dtype=torch.uint8, device=dev)
         ops.invoke_cuda_d2d_scale_cpy_convert(aq, attn, w["out"].input_scale)
         y = torch.empty(T, D, dtype=dt, device=dev)
@@ -365,6 +387,26 @@ class FluxTransformerBlockOp:
         if not ops.gemm_fp8_gate_residual(w["ff2"].qweight, w["ff2"].w_scale, f1, w["ff2"].input_scale, out.view(T, D), mod[5],
                                           h.view(T, D), S, bias=w["ff2"].bias):
             ops.gemm_with_residual_and_bias_fp8(w["ff2"].qweight, w["ff2"].w_scale, f1, w["ff2"].input_scale, y, bias=w["ff2"].bias)
+            ops.invoke_fused_gate_and_residual(out, y.view(B, S, D), mod[5], h)
+        return out
+
+    def _post_attention_int4(self, w, x, attn, mod):
+        B, S, D = x.shape
+        T = B * S
+        dev, dt = x.device, self.dtype
+        ao = w["out"].forward(attn)                                    # T(T(acc) + bias): to_out + invokeAddBias
+        h = torch.empty_like(x)
+        ops.invoke_fused_gate_and_residual(h, ao.view(B, S, D), mod[2], x)
+        n2 = torch.empty_like(x)
+        ops.invoke_layer_norm_with_shift_and_scale(n2, h, mod[4], mod[3], eps=1e-6)
+        f1 = w["ff1"].forward(n2.view(T, D))                           # T(gelu(T(T(acc) + bias))): invokeFusedBiasAndGelu
+        f1q = torch.empty(T, 4 * D, dtype=torch.uint8, device=dev)
+        ops.invoke_cuda_d2d_scale_cpy_convert(f1q, f1, w["ff2"].input_scale)
+        out = torch.empty_like(x)
+        if not ops.gemm_fp8_gate_residual(w["ff2"].qweight, w["ff2"].w_scale, f1q, w["ff2"].input_scale, out.view(T, D), mod[5],
+                                          h.view(T, D), S, bias=w["ff2"].bias):
+            y = torch.empty(T, D, dtype=dt, device=dev)
+            ops.gemm_with_residual_and_bias_fp8(w["ff2"].qweight, w["ff2"].w_scale, f1q, w["ff2"].input_scale, y, bias=w["ff2"].bias)
             ops.invoke_fused_gate_and_residual(out, y.view(B, S, D), mod[5], h)
         return out
 

@@ -158,3 +158,57 @@ def flux_single_block_int4(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_
     h = _w4a4_linear(mlp, sd, prefix + "proj_out.linears.1.linear.", dt, residual=h1)
     out = _n.gate_residual(h.reshape(B, S, D), gate, hidden)
     return out, {"msa": msa, "qkv": qkv, "attn": attn, "mlp": mlp, "h": h}
+
+
+def flux_double_block_int4(hidden, encoder, rope, temb, sd, prefix, heads, head_dim, quant_level=7):
+    """INT4 double-stream block: FluxTransformerInt4Block<T>::forward
+    (src/lyradiff/layers/flux_transformer_block/FluxTransformerInt4Block.cc:155-240) with
+    FluxAttentionInt4Processor<T>::forward (layers/flux_attention_processor/FluxAttentionInt4Processor.cc:157-305) and
+    FluxAttnPostInt4Processor<T>::forward (layers/flux_attn_post_processor/FluxAttnPostInt4Processor.cc).  Per stream:
+    16-bit AdaLN, W4A4 to_qkv (+ invokeAddBias), joint QK norm / RoPE / attention, W4A4 to_out (+ invokeAddBias), gate +
+    residual, 16-bit AdaLN, W4A4 net.0.proj (+ invokeFusedBiasAndGelu), e4m3 quantize, FP8 net.2, gate + residual."""
+    dt = hidden.dtype
+    B, S, D = hidden.shape
+    E = encoder.shape[1]
+    g = lambda name: sd[prefix + name]
+    cache = {}
+
+    def modulation(norm):
+        if quant_level == 8:
+            msa = _fp8_linear(temb, g(norm + ".linear.weight").to(dt), g(norm + ".linear.bias").to(dt),
+                              g(norm + ".linear_input_scale"), dt)
+        else:
+            msa = (temb.double() @ g(norm + ".linear.weight").to(dt).double().t() + g(norm + ".linear.bias").to(dt).double()).to(dt)
+        return msa.chunk(6, dim=1)
+
+    streams = {"img": (hidden, "norm1", "attn.to_qkv.", "attn.to_out.0.", "attn.norm_q.weight", "attn.norm_k.weight", "ff"),
+               "txt": (encoder, "norm1_context", "attn.to_added_qkv.", "attn.to_add_out.", "attn.norm_added_q.weight",
+                       "attn.norm_added_k.weight", "ff_context")}
+    mods, qkvs = {}, {}
+    rope_j = rope.reshape(B, E + S, head_dim // 2, 2, 2)
+    for key, (x, norm, qkv_name, _, nq, nk, _) in streams.items():
+        mod = modulation(norm)
+        n = _n.adaln_modulate(x, mod[1], mod[0], eps=1e-6).reshape(-1, D)
+        qkv = _w4a4_linear(n, sd, prefix + qkv_name, dt)
+        scale = torch.cat([g(nq).reshape(-1), g(nk).reshape(-1)]).to(dt)
+        L = x.shape[1]
+        r = (rope_j[:, :E] if key == "txt" else rope_j[:, E:]).reshape(B * L, head_dim // 2, 2, 2)
+        qkvs[key] = _n.rmsnorm_rope(qkv, scale, r, heads, head_dim, eps=1e-6).reshape(B, L, 3 * D)
+        mods[key] = mod
+    joint = torch.cat([qkvs["txt"], qkvs["img"]], dim=1).reshape(B, E + S, 3, heads, head_dim)
+    q, k, v = (joint[:, :, i].transpose(1, 2) for i in range(3))
+    attn = attention(q, k, v).transpose(1, 2).reshape(B, E + S, D).to(dt)
+    outs = {}
+    for key, (x, _, _, out_name, _, _, ff) in streams.items():
+        mod = mods[key]
+        a = (attn[:, :E] if key == "txt" else attn[:, E:]).reshape(-1, D)
+        L = x.shape[1]
+        ao = _w4a4_linear(a, sd, prefix + out_name, dt).reshape(B, L, D)
+        h = _n.gate_residual(ao, mod[2], x)
+        n2 = _n.adaln_modulate(h, mod[4], mod[3], eps=1e-6).reshape(-1, D)
+        f1 = _w4a4_linear(n2, sd, prefix + ff + ".net.0.proj.", dt, gelu=True)
+        name = ff + ".net.2"
+        f2 = _fp8_linear(f1, g(name + ".weight").to(dt), g(name + ".bias").to(dt), g(name + "_input_scale"), dt, cache=cache,
+                         key=name).reshape(B, L, D)
+        outs[key] = _n.gate_residual(f2, mod[5], h)
+    return outs["img"], outs["txt"]

@@ -129,7 +129,7 @@ def test_block_refuses_what_is_not_built():
     with pytest.raises(NotImplementedError):
         flux_blocks.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 3)
     with pytest.raises(NotImplementedError):
-        flux_blocks.FluxTransformerBlockOp("bf16", 256, 2, 128, 4, 7)   # the INT4 double-stream block is not built
+        flux_blocks.FluxTransformerBlockOp("bf16", 256, 2, 128, 4, 5)
     op = flux_blocks.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 1)
     with pytest.raises(NotImplementedError):
         op.reload_model_from_bin("/nowhere", "bf16")
@@ -206,3 +206,67 @@ def test_single_block_int4_against_oracle(level, B, S):
     assert float(err.max()) <= 0.3 * float(wdelta.abs().max()), float(err.max())
     # the LoRA-down sums use floating-point atomics (as the reference's do), so two runs may differ in the last bit
     assert float((out.float() - out2.float()).abs().max()) <= 2.0 ** -6 * float(out.float().abs().max())
+
+
+def _int4_double_state_dict(prefix, D, head_dim, level, g, dt=torch.bfloat16):
+    from oracle import quant
+    sd = {}
+
+    def w4(name, n, k, std):
+        w = (torch.randn(n, k, generator=g) * std).to(dt)
+        pw, sw, _ = quant.int4_weight_quant_g64(w)
+        sd[prefix + name + "packed_weight"] = pw.view(torch.int8)
+        sd[prefix + name + "weight_scale"] = sw.float()
+        sd[prefix + name + "smooth"] = 0.5 + torch.rand(k, generator=g)
+        sd[prefix + name + "lora_down"] = (torch.randn(32, k, generator=g) * 0.02).to(dt)
+        sd[prefix + name + "lora_up"] = (torch.randn(n, 32, generator=g) * 0.05).to(dt)
+        sd[prefix + name + "bias"] = (torch.randn(n, generator=g) * 0.02).to(dt)
+
+    for norm in ("norm1", "norm1_context"):
+        sd[prefix + norm + ".linear.weight"] = (torch.randn(6 * D, D, generator=g) * 0.03).to(dt)
+        sd[prefix + norm + ".linear.bias"] = (torch.randn(6 * D, generator=g) * 0.02).to(dt)
+        if level == 8:
+            sd[prefix + norm + ".linear_input_scale"] = torch.tensor([0.01])
+    for qkv in ("attn.to_qkv.", "attn.to_added_qkv."):
+        w4(qkv, 3 * D, D, 0.05)
+    for out in ("attn.to_out.0.", "attn.to_add_out."):
+        w4(out, D, D, 0.05)
+    for ff in ("ff", "ff_context"):
+        w4(ff + ".net.0.proj.", 4 * D, D, 0.05)
+        sd[prefix + ff + ".net.2.weight"] = (torch.randn(D, 4 * D, generator=g) * 0.03).to(dt)
+        sd[prefix + ff + ".net.2.bias"] = (torch.randn(D, generator=g) * 0.02).to(dt)
+        sd[prefix + ff + ".net.2_input_scale"] = torch.tensor([0.02])
+    for n in ("attn.norm_q.weight", "attn.norm_k.weight", "attn.norm_added_q.weight", "attn.norm_added_k.weight"):
+        sd[prefix + n] = (1.0 + 0.1 * torch.randn(head_dim, generator=g)).to(dt)
+    return sd
+
+
+@pytest.mark.parametrize("level", [7, 8])
+@pytest.mark.parametrize("B,S,E", [(1, 128, 48), (2, 64, 24)])
+def test_double_block_int4_against_oracle(level, B, S, E):
+    from lyradiff_b200 import flux_blocks
+    D, heads, head_dim = 256, 2, 128
+    g = torch.Generator().manual_seed(77 * level + S)
+    prefix = "transformer_blocks.4."
+    sd = _int4_double_state_dict(prefix, D, head_dim, level, g)
+    hidden = torch.randn(B, S, D, generator=g).bfloat16()
+    encoder = torch.randn(B, E, D, generator=g).bfloat16()
+    temb = torch.nn.functional.silu(torch.randn(B, D, generator=g)).bfloat16()
+    ang = torch.rand(B, E + S, head_dim // 2, generator=g) * 6.28
+    rope = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+        B, E + S, head_dim // 2, 2, 2).bfloat16()
+
+    op = flux_blocks.FluxTransformerBlockOp("bf16", D, heads, head_dim, 6, level)
+    op.initialize(flux_blocks.LyraDiffCommonContext())
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    out_i, out_t = op.forward(cu(hidden), cu(encoder), cu(rope), cu(temb))
+    check_status()
+    want_i, want_t = blocks.flux_double_block_int4(hidden, encoder, rope, temb, sd, prefix, heads, head_dim, level)
+    for got, want, x in ((out_i, want_i, hidden), (out_t, want_t, encoder)):
+        assert tuple(got.shape) == tuple(x.shape) and got.dtype == torch.bfloat16
+        delta, wdelta = got.cpu().float() - x.float(), want.float() - x.float()
+        err = (delta - wdelta).abs()
+        amp = float(wdelta.abs().mean())
+        assert amp > 0.02
+        assert float(err.mean()) <= 0.04 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
+        assert float(err.max()) <= 0.3 * float(wdelta.abs().max()), float(err.max())

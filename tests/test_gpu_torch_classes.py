@@ -115,6 +115,29 @@ def test_single_block_int4_same_bits_as_mirror(ns, level, B, S):
     assert torch.equal(got, want)
 
 
-def test_double_block_has_no_int4_level(ns):
+@pytest.mark.parametrize("level", [7, 8])
+def test_double_block_int4_same_bits_as_mirror(ns, level):
+    from lyradiff_b200 import flux_blocks
+    from tests.test_gpu_flux_block import _int4_double_state_dict
+    D, heads, head_dim, B, S, E = 256, 2, 128, 2, 64, 24
+    g = torch.Generator().manual_seed(19 * level)
+    prefix = "transformer_blocks.0."
+    sd = _int4_double_state_dict(prefix, D, head_dim, level, g)
+    hidden = cu(torch.randn(B, S, D, generator=g).bfloat16())
+    encoder = cu(torch.randn(B, E, D, generator=g).bfloat16())
+    temb = cu(torch.nn.functional.silu(torch.randn(B, D, generator=g)).bfloat16())
+    rope = cu(_rope(B, E + S, head_dim, g, torch.bfloat16))
+    mirror = flux_blocks.FluxTransformerBlockOp("bf16", D, heads, head_dim, 6, level)
+    mirror.reload_model_from_state_dict(prefix, sd, "cuda")
+    want_i, want_t = mirror.forward(hidden, encoder, rope, temb)
+    op = ns.FluxTransformerBlockOp("bf16", D, heads, head_dim, 6, level)
+    op.initialize(ns.LyraDiffCommonContext())
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    got_i, got_t = op.forward(hidden, encoder, rope, temb)
+    check_status()
+    assert torch.equal(got_i, want_i) and torch.equal(got_t, want_t)
+
+
+def test_levels_that_are_not_built_raise(ns):
     with pytest.raises(RuntimeError, match="quant_level"):
-        ns.FluxTransformerBlockOp("bf16", 256, 2, 128, 4, 7)
+        ns.FluxTransformerBlockOp("bf16", 256, 2, 128, 4, 5)
