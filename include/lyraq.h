@@ -299,6 +299,12 @@ LYRAQ_API int lyraq_quant_fp8_2d(uint8_t* dst, size_t dst_ld, const void* src, i
 LYRAQ_API int lyraq_gate_residual(void* out, const void* y, const void* gate, const void* x, int dtype, size_t batch,
                                   size_t seq_len, size_t dim, void* stream);
 
+/* LoRA hot-swap on a 16-bit weight: weight[i] = T(weight[i] + T(lora[i] * T(alpha))), i < n, in place; every step rounds to
+ * T as the reference's 16-bit operators do.  The FP8 layers follow it with lyraq_weight_quant_fp8 on the merged weight
+ * (FP8LoraWeight<T>::load_lora, src/lyradiff/interface/IFLoraWeight.h:104-116).  Replaces invokeLoadLora<T>
+ * (src/lyradiff/kernels/lora/load_lora.h; kernel load_lora.cu:6-14). */
+LYRAQ_API int lyraq_load_lora(void* weight, const void* lora, int dtype, float alpha, size_t n, void* stream);
+
 /* ------------------------------------------------------------------ quantized-Linear layer forwards
  * Activation quantize + GEMM of one linear on `stream`; the quantized activation lives in `workspace`
  * (lyraq_workspace_bytes(LYRAQ_OP_LINEAR_*, m, n, k) bytes, 16-byte aligned, owned by the caller, free for reuse

@@ -54,6 +54,7 @@ SIGNATURES = {
     "lyraq_rmsnorm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_double, c_size_t, c_size_t, c_int, c_int,
                                    c_void_p]),
     "lyraq_quant_fp8_2d": (c_int, [c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_size_t, c_size_t, c_void_p]),
+    "lyraq_load_lora": (c_int, [c_void_p, c_void_p, c_int, c_float, c_size_t, c_void_p]),
     "lyraq_gate_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_size_t, c_void_p]),
     "lyraq_gemm_w4a4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),

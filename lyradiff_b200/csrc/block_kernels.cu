@@ -118,6 +118,33 @@ __global__ void __launch_bounds__(256) gate_residual_kernel(T* out, const T* y, 
     }
 }
 
+// w[i] = T(w[i] + T(lora[i] * T(alpha))), each step in T's own arithmetic: loadLora<T>
+// (src/lyradiff/kernels/lora/load_lora.cu:6-14).  n8 vectors of 8 elements, then a scalar tail.
+template<typename T>
+__global__ void __launch_bounds__(256) load_lora_kernel(T* w, const T* lora, size_t n, float alpha)
+{
+    using P2 = Pair<T>;
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const uint32_t a2     = P2::from_f32(alpha, alpha);
+    const size_t   n8     = n >> 3;
+    const size_t   stride = (size_t)gridDim.x * blockDim.x;
+    const size_t   tid    = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (size_t vi = tid; vi < n8; vi += stride) {
+        Vec16       o = *reinterpret_cast<const Vec16*>(w + (vi << 3));  // plain load: this kernel writes w
+        const Vec16 l = ld_nc_16(lora + (vi << 3));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            o.w[j] = P2::add(o.w[j], P2::mul(l.w[j], a2));
+        }
+        st_16(w + (vi << 3), o);
+    }
+    for (size_t i = (n8 << 3) + tid; i < n; i += stride) {
+        const T t = from_f32<T>(to_f32(lora[i]) * to_f32(from_f32<T>(alpha)));  // exact product of two T values, one rounding
+        w[i]      = from_f32<T>(to_f32(w[i]) + to_f32(t));
+    }
+}
+
 static unsigned stream_grid(size_t nvec)
 {
     size_t       g   = (nvec + 255) / 256;
@@ -229,6 +256,28 @@ int lyraq_gate_residual(void* out, const void* y, const void* gate, const void* 
         return LYRAQ_ERR_UNSUPPORTED;
     }
     return cuda_status(e, "cudaLaunchKernelEx(gate_residual_kernel)");
+}
+
+int lyraq_load_lora(void* weight, const void* lora, int dtype, float alpha, size_t n, void* stream)
+{
+    if (n == 0) {
+        return LYRAQ_OK;
+    }
+    if (weight == nullptr || lora == nullptr || !aligned16(weight) || !aligned16(lora)) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    const unsigned grid = stream_grid((n + 7) / 8);
+    cudaError_t    e;
+    if (dtype == LYRAQ_BF16) {
+        using T = __nv_bfloat16;
+        e = launch_kernel(load_lora_kernel<T>, grid, 256u, (size_t)0, (cudaStream_t)stream, 1u, (T*)weight, (const T*)lora, n, alpha);
+    } else if (dtype == LYRAQ_F16) {
+        using T = __half;
+        e = launch_kernel(load_lora_kernel<T>, grid, 256u, (size_t)0, (cudaStream_t)stream, 1u, (T*)weight, (const T*)lora, n, alpha);
+    } else {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    return cuda_status(e, "cudaLaunchKernelEx(load_lora_kernel)");
 }
 
 }  // extern "C"

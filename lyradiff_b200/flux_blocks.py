@@ -35,9 +35,15 @@ and FluxSingleAttentionInt4Processor<T>::forward (layers/flux_single_attention_p
     out  = T(T(h * gate) + x)                                                              (lyraq_gate_residual)
 
 with the roundings of the reference's separate 16-bit kernels kept inside the GEMM epilogues (LYRAQ_EPI_ROUND_EACH).
-Other levels, LoRA hot-swap and the .bin directory loader are not built: they raise NotImplementedError.
+Other quant levels are not built: the constructors raise NotImplementedError.  LoRA hot-swap (load_lora_by_name,
+clear_lora) re-merges from a host copy of the 16-bit weight and re-quantizes, as the reference's FP8 layers do;
+reload_model_from_bin reads the reference's raw .bin files.
 """
 
+import os
+import warnings
+
+import numpy as np
 import torch
 
 from . import layers, ops
@@ -56,16 +62,112 @@ class LyraDiffCommonContext:
 
 
 class _Fp8Weight:
-    """One quantized linear as MACROLoadFP8WeightFromCache leaves it (src/lyradiff/utils/common_macro_def.h:76-92)."""
+    """One quantized linear as MACROLoadFP8WeightFromCache leaves it (src/lyradiff/utils/common_macro_def.h:76-92): e4m3
+    weight with its amax / 448 scale, bias, static input scale, and a host copy of the 16-bit weight that every LoRA merge
+    starts from (FP8LoraWeight<T>, src/lyradiff/interface/IFLoraWeight.h:81-133)."""
 
     def __init__(self, weight, bias, input_scale, device, dtype):
         w = weight.to(device=device, dtype=dtype).contiguous()
         self.n, self.k = w.shape
+        self.weight_h = w.to("cpu")
         self.qweight = torch.empty(self.n, self.k, dtype=torch.uint8, device=device)
         self.w_scale = torch.empty(1, dtype=torch.float32, device=device)
         ops.weight_quant_fp8(self.qweight, self.w_scale, w)
         self.bias = None if bias is None else bias.to(device=device, dtype=dtype).contiguous()
         self.input_scale = input_scale.to(device=device, dtype=torch.float32).reshape(1).contiguous()
+        self.loaded_lora = False
+
+    def load_lora(self, lora_weight, scale):
+        """weight_h + lora * scale (16-bit arithmetic), then a fresh amax scale and e4m3 cast; merges do not stack."""
+        w = self.weight_h.to(self.qweight.device)
+        ops.invoke_load_lora(w, lora_weight.to(device=w.device, dtype=w.dtype).reshape(w.shape).contiguous(), scale)
+        ops.weight_quant_fp8(self.qweight, self.w_scale, w)
+        self.loaded_lora = True
+
+    def clear_lora(self):
+        if self.loaded_lora:
+            ops.weight_quant_fp8(self.qweight, self.w_scale, self.weight_h.to(self.qweight.device))
+            self.loaded_lora = False
+
+
+class _Linear16:
+    """The 16-bit modulation linear of quant_level 1 / 7 with its host copy (LoraWeightV2<T>, IFLoraWeight.h:40-78)."""
+
+    def __init__(self, weight, bias, device, dtype):
+        self.w = weight.to(device=device, dtype=dtype).contiguous()
+        self.b = bias.to(device=device, dtype=dtype).contiguous()
+        self.weight_h = self.w.to("cpu")
+        self.loaded_lora = False
+
+    def load_lora(self, lora_weight, scale):
+        self.w.copy_(self.weight_h)
+        ops.invoke_load_lora(self.w, lora_weight.to(device=self.w.device, dtype=self.w.dtype).reshape(self.w.shape).contiguous(), scale)
+        self.loaded_lora = True
+
+    def clear_lora(self):
+        if self.loaded_lora:
+            self.w.copy_(self.weight_h)
+            self.loaded_lora = False
+
+
+def _load_lora_by_name(table, names, weight, scale):
+    """IFLoraWeight<T>::loadLoraByName (IFLoraWeight.h:150-173): walk the nested name table; a name that leads nowhere is
+    reported and skipped, as the reference does."""
+    node = table
+    for name in names:
+        if isinstance(node, dict) and name in node:
+            node = node[name]
+        else:
+            warnings.warn("lora name cannot find weights to load: %s" % " ".join(names))
+            return
+    if isinstance(node, dict):
+        warnings.warn("lora name cannot find weights to load: %s" % " ".join(names))
+        return
+    node.load_lora(weight, scale)
+
+
+def _clear_lora(table):
+    for node in table.values():
+        if isinstance(node, dict):
+            _clear_lora(node)
+        else:
+            node.clear_lora()
+
+
+_BIN_DTYPES = {"fp32": np.float32, "fp16": np.float16}
+
+
+def _read_bin(path, key, shape, kind, file_dtype):
+    """One raw array of loadWeightFromBin (src/lyradiff/utils/memory_utils.cu:295-364): file `<path><key>.bin`, elements of
+    the model file type for 16-bit tensors ("T"), fp32 for scales ("f32"), int8 for packed int4 weights ("i8").  A missing
+    or short file raises (the reference logs a warning and leaves the weight uninitialised)."""
+    fn = path + key + ".bin"
+    dt = {"T": file_dtype, "f32": np.float32, "i8": np.int8}[kind]
+    count = int(np.prod(shape))
+    if not os.path.exists(fn) or os.path.getsize(fn) < count * np.dtype(dt).itemsize:
+        raise RuntimeError("weight file missing or too small: %s" % fn)
+    return torch.from_numpy(np.fromfile(fn, dtype=dt, count=count).reshape(shape))
+
+
+def _state_dict_from_bin(path, model_dtype, manifest):
+    if model_dtype not in _BIN_DTYPES:
+        raise ValueError("wrong model_dtype")  # std::invalid_argument in the reference (FluxSingleTransformerBlockOp.h:241-243)
+    return {key: _read_bin(path, key, shape, kind, _BIN_DTYPES[model_dtype]) for key, shape, kind in manifest}
+
+
+def _fp8_linear_files(name, n, k):
+    return [(name + ".weight", (n, k), "T"), (name + ".bias", (n,), "T"), (name + "_input_scale", (1,), "f32")]
+
+
+def _w4a4_linear_files(name, n, k, has_bias=True):
+    files = [(name + "packed_weight", (n, k // 2), "i8"), (name + "weight_scale", (n, k // 64), "f32"),
+             (name + "lora_up", (n, 32), "T"), (name + "lora_down", (32, k), "T"), (name + "smooth", (k,), "f32")]
+    return files + ([(name + "bias", (n,), "T")] if has_bias else [])
+
+
+def _modulation_files(name, chunks, D, fp8):
+    files = [(name + ".weight", (chunks * D, D), "T"), (name + ".bias", (chunks * D,), "T")]
+    return files + ([(name + "_input_scale", (1,), "f32")] if fp8 else [])
 
 
 def _w4a4_from_state_dict(sd, name, n, k, device, dtype, has_bias, gelu=False):
@@ -105,13 +207,42 @@ class FluxSingleTransformerBlockOp:
         self._ctx = ctx
 
     def reload_model_from_bin(self, path, dtype):
-        raise NotImplementedError("the .bin directory loader is not built; use reload_model_from_state_dict")
+        """FluxSingleTransformer*BlockWeight<T>::loadWeights: one raw file `<path><key>.bin` per tensor, keys as in
+        reload_model_from_state_dict, 16-bit tensors stored as `dtype` ("fp32" or "fp16"), scales as fp32, packed int4
+        weights as int8 (FluxSingleTransformerFP8BlockWeight.cc:97-121, FluxSingleTransformerInt4BlockWeight.cc:70-84).
+        `path` is a prefix, e.g. ".../single_transformer_blocks.0."; the weights go to the current CUDA device."""
+        D, m = self.dim, self.mlp_scale
+        full = self.quant_level in (FP8_W8A8_FULL, INT4_W4A4_FULL)
+        files = _modulation_files("norm.linear", 3, D, full)
+        files += [("attn.norm_q.weight", (self.head_dim,), "T"), ("attn.norm_k.weight", (self.head_dim,), "T")]
+        if self.quant_level in (INT4_W4A4, INT4_W4A4_FULL):
+            files += _w4a4_linear_files("attn.to_qkv.", 3 * D, D) + _w4a4_linear_files("proj_mlp.", m * D, D)
+            files += _w4a4_linear_files("proj_out.linears.0.", D, D)
+            files += _w4a4_linear_files("proj_out.linears.1.linear.", D, m * D, has_bias=False)
+        else:
+            files += _fp8_linear_files("attn.to_qkv", 3 * D, D) + _fp8_linear_files("proj_mlp", m * D, D)
+            files += _fp8_linear_files("proj_out", D, (m + 1) * D)
+        self.reload_model_from_state_dict("", _state_dict_from_bin(path, dtype, files), "cuda")
+
+    def _lora_table(self):
+        """Names as the reference's lora_layer_map / lora_weight_map nest them (FluxSingleTransformerFP8BlockWeight.cc:33,80-89,
+        FluxSingleAttentionFP8ProcessorWeight.cc:51-54, AdaFP8LayerNormWeight.cc:47-51).  The W4A4 linears have no
+        hot-swap in the reference either (they carry their LoRA branch as weights)."""
+        if self._w is None:
+            raise RuntimeError("weights not loaded")
+        w = self._w
+        table = {"norm": {"linear": w["norm"] if "norm" in w else w["norm16"]}}
+        if not w.get("int4"):
+            table.update({"attn": {"to_qkv": w["qkv"]}, "proj_mlp": w["mlp"], "proj_out": w["out"]})
+        return table
 
     def load_lora_by_name(self, names, weight, scale):
-        raise NotImplementedError("LoRA hot-swap is not built")
+        """names: the path to one linear, e.g. ["attn", "to_qkv"] or ["proj_mlp"]; weight: the merged low-rank update
+        (up @ down) in the layer's [n, k] layout and the inference dtype; scale: its strength."""
+        _load_lora_by_name(self._lora_table(), list(names), weight, float(scale))
 
     def clear_lora(self):
-        raise NotImplementedError("LoRA hot-swap is not built")
+        _clear_lora(self._lora_table())
 
     def reload_model_from_state_dict(self, prefix, state_dict, device):
         """Keys as the reference reads them (FluxSingleTransformerFP8BlockWeight.cc:135-149,
@@ -132,8 +263,7 @@ class FluxSingleTransformerBlockOp:
         if self.quant_level == FP8_W8A8_FULL:
             w["norm"] = _Fp8Weight(g("norm.linear.weight"), g("norm.linear.bias"), g("norm.linear_input_scale"), dev, self.dtype)
         else:
-            w["norm_w"] = g("norm.linear.weight").to(device=dev, dtype=self.dtype).contiguous()
-            w["norm_b"] = g("norm.linear.bias").to(device=dev, dtype=self.dtype).contiguous()
+            w["norm16"] = _Linear16(g("norm.linear.weight"), g("norm.linear.bias"), dev, self.dtype)
         w["qk_scale"] = torch.cat([g("attn.norm_q.weight").reshape(-1), g("attn.norm_k.weight").reshape(-1)]).to(
             device=dev, dtype=self.dtype).contiguous()
         if w["qkv"].n != 3 * self.dim or w["mlp"].n != self.mlp_scale * self.dim or w["out"].k != (self.mlp_scale + 1) * self.dim:
@@ -155,8 +285,7 @@ class FluxSingleTransformerBlockOp:
         if self.quant_level == INT4_W4A4_FULL:
             w["norm"] = _Fp8Weight(g("norm.linear.weight"), g("norm.linear.bias"), g("norm.linear_input_scale"), dev, dt)
         else:
-            w["norm_w"] = g("norm.linear.weight").to(device=dev, dtype=dt).contiguous()
-            w["norm_b"] = g("norm.linear.bias").to(device=dev, dtype=dt).contiguous()
+            w["norm16"] = _Linear16(g("norm.linear.weight"), g("norm.linear.bias"), dev, dt)
         w["qk_scale"] = torch.cat([g("attn.norm_q.weight").reshape(-1), g("attn.norm_k.weight").reshape(-1)]).to(
             device=dev, dtype=dt).contiguous()
         self._w = w
@@ -212,7 +341,7 @@ class FluxSingleTransformerBlockOp:
             msa = self._buffer("msa", (B, 3 * D), dt, dev)
             ops.gemm_with_residual_and_bias_fp8(nw.qweight, nw.w_scale, tq, nw.input_scale, msa, bias=nw.bias)
         else:
-            msa = torch.addmm(w["norm_b"], temb, w["norm_w"].t())
+            msa = torch.addmm(w["norm16"].b, temb, w["norm16"].w.t())
         shift, scale, gate = (c.contiguous() for c in msa.chunk(3, dim=1))
         if w.get("int4"):
             return self._forward_int4(hidden_states, rope_emb, shift, scale, gate)
@@ -262,7 +391,7 @@ def _modulation(op, w, temb, chunks):
         msa = torch.empty(B, chunks * D, dtype=op.dtype, device=temb.device)
         ops.gemm_with_residual_and_bias_fp8(nw.qweight, nw.w_scale, tq, nw.input_scale, msa, bias=nw.bias)
     else:
-        msa = torch.addmm(w["b"], temb, w["w"].t())
+        msa = torch.addmm(w["lin16"].b, temb, w["lin16"].w.t())
     return [c.contiguous() for c in msa.chunk(chunks, dim=1)]
 
 
@@ -303,14 +432,46 @@ class FluxTransformerBlockOp:
     def initialize(self, ctx):
         self._ctx = ctx
 
+    _STREAMS = (("norm1", "attn.to_qkv", "attn.to_out.0", "attn.norm_q.weight", "attn.norm_k.weight", "ff"),
+                ("norm1_context", "attn.to_added_qkv", "attn.to_add_out", "attn.norm_added_q.weight", "attn.norm_added_k.weight",
+                 "ff_context"))
+
     def reload_model_from_bin(self, path, dtype):
-        raise NotImplementedError("the .bin directory loader is not built; use reload_model_from_state_dict")
+        """FluxTransformer*BlockWeight<T>::loadWeights (FluxTransformerFP8BlockWeight.cc:84-100,
+        FluxTransformerInt4BlockWeight.cc:78-91): `<path><key>.bin` per tensor, keys as in reload_model_from_state_dict."""
+        D = self.dim
+        int4 = self.quant_level in (INT4_W4A4, INT4_W4A4_FULL)
+        files = []
+        for norm, qkv, out, nq, nk, ff in self._STREAMS:
+            files += _modulation_files(norm + ".linear", 6, D, self.quant_level in (FP8_W8A8_FULL, INT4_W4A4_FULL))
+            files += [(nq, (self.head_dim,), "T"), (nk, (self.head_dim,), "T")]
+            if int4:
+                files += _w4a4_linear_files(qkv + ".", 3 * D, D) + _w4a4_linear_files(out + ".", D, D)
+                files += _w4a4_linear_files(ff + ".net.0.proj.", 4 * D, D)
+            else:
+                files += _fp8_linear_files(qkv, 3 * D, D) + _fp8_linear_files(out, D, D) + _fp8_linear_files(ff + ".net.0.proj", 4 * D, D)
+            files += _fp8_linear_files(ff + ".net.2", D, 4 * D)
+        self.reload_model_from_state_dict("", _state_dict_from_bin(path, dtype, files), "cuda")
+
+    def _lora_table(self):
+        """FluxTransformerFP8BlockWeight.cc:41-45, FluxAttentionFP8ProcessorWeight.cc:91-108,
+        FluxAttnPostFP8ProcessorWeight.cc:58-64, AdaFP8LayerNormWeight.cc:47-51."""
+        if self._w is None:
+            raise RuntimeError("weights not loaded")
+        wi, wt = self._w["img"], self._w["txt"]
+        mod = lambda w: {"linear": w["norm"].get("fp8") or w["norm"]["lin16"]}
+        table = {"norm1": mod(wi), "norm1_context": mod(wt), "ff": {"net.2": wi["ff2"]}, "ff_context": {"net.2": wt["ff2"]}}
+        if not wi.get("int4"):
+            table["attn"] = {"to_qkv": wi["qkv"], "to_out.0": wi["out"], "to_added_qkv": wt["qkv"], "to_add_out": wt["out"]}
+            table["ff"]["net.0.proj"] = wi["ff1"]
+            table["ff_context"]["net.0.proj"] = wt["ff1"]
+        return table
 
     def load_lora_by_name(self, names, weight, scale):
-        raise NotImplementedError("LoRA hot-swap is not built")
+        _load_lora_by_name(self._lora_table(), list(names), weight, float(scale))
 
     def clear_lora(self):
-        raise NotImplementedError("LoRA hot-swap is not built")
+        _clear_lora(self._lora_table())
 
     def reload_model_from_state_dict(self, prefix, state_dict, device):
         """Keys (FluxTransformerFP8BlockWeight.cc:104-108 and the loaders it calls): per stream
@@ -340,8 +501,7 @@ class FluxTransformerBlockOp:
             if self.quant_level in (FP8_W8A8_FULL, INT4_W4A4_FULL):
                 w["norm"] = {"fp8": lin(norm + ".linear")}
             else:
-                w["norm"] = {"w": g(norm + ".linear.weight").to(device=dev, dtype=self.dtype).contiguous(),
-                             "b": g(norm + ".linear.bias").to(device=dev, dtype=self.dtype).contiguous()}
+                w["norm"] = {"lin16": _Linear16(g(norm + ".linear.weight"), g(norm + ".linear.bias"), dev, self.dtype)}
             w["qk_scale"] = torch.cat([g(nq).reshape(-1), g(nk).reshape(-1)]).to(device=dev, dtype=self.dtype).contiguous()
             return w
 

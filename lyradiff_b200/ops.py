@@ -222,6 +222,16 @@ def invoke_fused_gate_and_residual(out, y, gate, residual):
     return out
 
 
+def invoke_load_lora(weight, lora, alpha):
+    """invokeLoadLora<T> (src/lyradiff/kernels/lora/load_lora.h): weight += lora * alpha in place, in the weight's own 16-bit
+    arithmetic (both steps rounded)."""
+    if weight.shape != lora.shape or weight.dtype != lora.dtype or not (weight.is_contiguous() and lora.is_contiguous()):
+        raise ValueError("weight and lora must be contiguous tensors of one shape and dtype")
+    st = _lib.lib().lyraq_load_lora(_p(weight), _p(lora), _dt(weight), float(alpha), weight.numel(), _stream())
+    _lib.check(st, "lyraq_load_lora")
+    return weight
+
+
 def gemm_fp8_gate_residual(W, w_scale, X, x_scale, Y, gate, residual, rows_per_batch, bias=None):
     """FP8 GEMM + invokeFusedGateAndResidual in one launch (lyraq_gemm_fp8_gate): Y = (X W^T * s + bias) * gate[b] + residual,
     rounded to Y's dtype after every step.  Returns False (nothing launched) when the shape cannot be fused."""

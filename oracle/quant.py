@@ -187,3 +187,12 @@ def lora_down(x, down):
     UNSMOOTHED 16-bit x, fp32 result.  The reference adds its 64-column partial sums with floating-point atomics in
     no fixed order; the oracle sums in fp64 and rounds once, which every order agrees with to a few fp32 ulps."""
     return (x.double() @ down.double().t()).to(F32)
+
+
+def load_lora(w, lora, alpha):
+    """LoRA merge into a 16-bit weight, loadLora<T> (src/lyradiff/kernels/lora/load_lora.cu:6-14):
+    dst += src * T(alpha) with T's own operators, i.e. the product and the sum each rounded to T."""
+    dt = w.dtype
+    a = torch.tensor(alpha, dtype=F32).to(dt)
+    t = (lora.to(F32) * a.to(F32)).to(dt)
+    return (w.to(F32) + t.to(F32)).to(dt)

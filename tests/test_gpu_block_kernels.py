@@ -114,3 +114,18 @@ def test_gate_fusion_refuses_tiles_that_straddle_batches(ops):
     y = torch.empty(200, 128, dtype=torch.bfloat16, device="cuda")
     gate = torch.ones(2, 128, dtype=torch.bfloat16, device="cuda")
     assert ops.gemm_fp8_gate_residual(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), y, gate, y, 100) is False
+
+
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("n", [8, 1000, 3072 * 64 + 5])
+@pytest.mark.parametrize("alpha", [1.0, 0.3])
+def test_load_lora_rounds_like_the_16_bit_operators(dt, n, alpha):
+    from lyradiff_b200 import ops
+    from oracle import quant
+    g = torch.Generator().manual_seed(n)
+    w = torch.randn(n, generator=g).to(dt)
+    lora = (torch.randn(n, generator=g) * 0.05).to(dt)
+    got = cu(w).clone()
+    ops.invoke_load_lora(got, cu(lora), alpha)
+    assert_bit_equal(got, quant.load_lora(w, lora, alpha), "load_lora")
+    check_status()

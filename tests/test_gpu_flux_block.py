@@ -131,8 +131,10 @@ def test_block_refuses_what_is_not_built():
     with pytest.raises(NotImplementedError):
         flux_blocks.FluxTransformerBlockOp("bf16", 256, 2, 128, 4, 5)
     op = flux_blocks.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 1)
-    with pytest.raises(NotImplementedError):
-        op.reload_model_from_bin("/nowhere", "bf16")
+    with pytest.raises(ValueError):
+        op.reload_model_from_bin("/nowhere/", "bf16")      # file types are fp32 and fp16, as in the reference
+    with pytest.raises(RuntimeError):
+        op.reload_model_from_bin("/nowhere/", "fp16")      # a missing file raises
     with pytest.raises(RuntimeError):
         op.forward(torch.zeros(1, 8, 256, dtype=torch.bfloat16, device="cuda"),
                    torch.zeros(1, 8, 64, 2, 2, dtype=torch.bfloat16, device="cuda"),
@@ -270,3 +272,134 @@ def test_double_block_int4_against_oracle(level, B, S, E):
         assert amp > 0.02
         assert float(err.mean()) <= 0.04 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
         assert float(err.max()) <= 0.3 * float(wdelta.abs().max()), float(err.max())
+
+
+def _block_inputs(B, S, D, head_dim, g, dt=torch.bfloat16):
+    hidden = torch.randn(B, S, D, generator=g).to(dt)
+    temb = torch.nn.functional.silu(torch.randn(B, D, generator=g)).to(dt)
+    ang = torch.rand(B, S, head_dim // 2, generator=g) * 6.28
+    rope = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+        B, S, head_dim // 2, 2, 2).to(dt)
+    return cu(hidden), cu(rope), cu(temb)
+
+
+@pytest.mark.parametrize("level", [1, 2])
+def test_lora_hot_swap_equals_a_block_loaded_with_the_merged_weight(level):
+    """load_lora_by_name merges weight_h + lora * scale in 16-bit arithmetic and re-quantizes; the block must then give the
+    bits of a block that was loaded with that merged weight, and clear_lora must give back the original bits."""
+    from lyradiff_b200 import flux_blocks
+    from oracle import quant
+    D, heads, head_dim, mlp_scale = 256, 2, 128, 4
+    g = torch.Generator().manual_seed(40 + level)
+    prefix = "b."
+    sd = _state_dict(prefix, D, mlp_scale, head_dim, level, g)
+    x = _block_inputs(1, 96, D, head_dim, g)
+    op = flux_blocks.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    base = op.forward(*x).clone()
+
+    targets = [(["proj_mlp"], "proj_mlp.weight", 0.75), (["attn", "to_qkv"], "attn.to_qkv.weight", 1.0),
+               (["norm", "linear"], "norm.linear.weight", 0.5)]
+    merged = dict(sd)
+    for names, key, scale in targets:
+        lora = (torch.randn(sd[prefix + key].shape, generator=g) * 0.01).bfloat16()
+        op.load_lora_by_name(names, cu(lora), scale)
+        merged[prefix + key] = quant.load_lora(sd[prefix + key], lora, scale)
+    swapped = op.forward(*x).clone()
+    assert not torch.equal(swapped, base)
+
+    ref = flux_blocks.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    ref.reload_model_from_state_dict(prefix, merged, "cuda")
+    assert torch.equal(swapped, ref.forward(*x))
+
+    with pytest.warns(UserWarning, match="cannot find"):
+        op.load_lora_by_name(["attn", "to_k"], cu(torch.zeros(4, 4).bfloat16()), 1.0)
+    op.clear_lora()
+    assert torch.equal(op.forward(*x), base)
+    check_status()
+
+
+def test_lora_hot_swap_double_block_routes_every_name():
+    from lyradiff_b200 import flux_blocks
+    D, heads, head_dim = 256, 2, 128
+    g = torch.Generator().manual_seed(50)
+    prefix = "t."
+    sd = _double_state_dict(prefix, D, head_dim, 2, g)
+    op = flux_blocks.FluxTransformerBlockOp("bf16", D, heads, head_dim, 6, 2)
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    hidden, rope_i, temb = _block_inputs(1, 64, D, head_dim, g)
+    encoder = cu(torch.randn(1, 32, D, generator=g).bfloat16())
+    ang = torch.rand(1, 96, head_dim // 2, generator=g) * 6.28
+    rope = cu(torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+        1, 96, head_dim // 2, 2, 2).bfloat16())
+    base_i, base_t = (t.clone() for t in op.forward(hidden, encoder, rope, temb))
+    names = [(["norm1", "linear"], (6 * D, D)), (["norm1_context", "linear"], (6 * D, D)), (["attn", "to_qkv"], (3 * D, D)),
+             (["attn", "to_out.0"], (D, D)), (["attn", "to_added_qkv"], (3 * D, D)), (["attn", "to_add_out"], (D, D)),
+             (["ff", "net.0.proj"], (4 * D, D)), (["ff", "net.2"], (D, 4 * D)), (["ff_context", "net.0.proj"], (4 * D, D)),
+             (["ff_context", "net.2"], (D, 4 * D))]
+    for path, shape in names:
+        op.load_lora_by_name(path, cu((torch.randn(shape, generator=g) * 0.02).bfloat16()), 1.0)
+        out_i, out_t = op.forward(hidden, encoder, rope, temb)
+        assert not (torch.equal(out_i, base_i) and torch.equal(out_t, base_t)), path
+        op.clear_lora()
+        out_i, out_t = op.forward(hidden, encoder, rope, temb)
+        assert torch.equal(out_i, base_i) and torch.equal(out_t, base_t), path
+    check_status()
+
+
+def _write_bins(path, sd, prefix, file_dtype):
+    import numpy as np
+    for key, t in sd.items():
+        name = key[len(prefix):]
+        if t.dtype in (torch.int8, torch.uint8):
+            arr = t.view(torch.int8).numpy()
+        elif name.endswith("_input_scale") or name.endswith("weight_scale") or name.endswith("smooth"):
+            arr = t.float().numpy()
+        else:
+            arr = t.float().numpy().astype(file_dtype)
+        arr.tofile(path + name + ".bin")
+
+
+@pytest.mark.parametrize("level,dtype,file_type", [(1, "bf16", "fp32"), (2, "fp16", "fp16"), (7, "bf16", "fp32"), (8, "fp16", "fp16")])
+def test_reload_from_bin_gives_the_bits_of_the_state_dict_path(tmp_path, level, dtype, file_type):
+    import numpy as np
+    from lyradiff_b200 import flux_blocks
+    td = {"bf16": torch.bfloat16, "fp16": torch.float16}[dtype]
+    D, heads, head_dim, mlp_scale = 256, 2, 128, 4
+    g = torch.Generator().manual_seed(60 + level)
+    prefix = "single_transformer_blocks.7."
+    if level in (7, 8):
+        sd = _int4_state_dict(prefix, D, mlp_scale, head_dim, level, g, dt=td)
+    else:
+        sd = {k: (v.to(td) if v.dtype == torch.bfloat16 else v) for k, v in _state_dict(prefix, D, mlp_scale, head_dim, level, g).items()}
+    base = str(tmp_path) + "/" + prefix
+    _write_bins(base, sd, prefix, {"fp32": np.float32, "fp16": np.float16}[file_type])
+    x = _block_inputs(1, 64, D, head_dim, g, td)
+    a = flux_blocks.FluxSingleTransformerBlockOp(dtype, D, heads, head_dim, mlp_scale, level)
+    a.reload_model_from_state_dict(prefix, sd, "cuda")
+    b = flux_blocks.FluxSingleTransformerBlockOp(dtype, D, heads, head_dim, mlp_scale, level)
+    b.reload_model_from_bin(base, file_type)
+    assert torch.equal(a.forward(*x), b.forward(*x))
+
+
+@pytest.mark.parametrize("level", [2, 7])
+def test_double_block_reload_from_bin(tmp_path, level):
+    import numpy as np
+    from lyradiff_b200 import flux_blocks
+    D, heads, head_dim = 256, 2, 128
+    g = torch.Generator().manual_seed(70 + level)
+    prefix = "transformer_blocks.2."
+    sd = _int4_double_state_dict(prefix, D, head_dim, level, g) if level == 7 else _double_state_dict(prefix, D, head_dim, level, g)
+    base = str(tmp_path) + "/" + prefix
+    _write_bins(base, sd, prefix, np.float32)
+    hidden, _, temb = _block_inputs(1, 64, D, head_dim, g)
+    encoder = cu(torch.randn(1, 32, D, generator=g).bfloat16())
+    ang = torch.rand(1, 96, head_dim // 2, generator=g) * 6.28
+    rope = cu(torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+        1, 96, head_dim // 2, 2, 2).bfloat16())
+    a = flux_blocks.FluxTransformerBlockOp("bf16", D, heads, head_dim, 6, level)
+    a.reload_model_from_state_dict(prefix, sd, "cuda")
+    b = flux_blocks.FluxTransformerBlockOp("bf16", D, heads, head_dim, 6, level)
+    b.reload_model_from_bin(base, "fp32")
+    for u, v in zip(a.forward(hidden, encoder, rope, temb), b.forward(hidden, encoder, rope, temb)):
+        assert torch.equal(u, v)
