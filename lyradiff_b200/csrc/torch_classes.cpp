@@ -13,6 +13,9 @@
 #include <torch/custom_class.h>
 #include <torch/script.h>
 
+#include <cstdio>
+#include <map>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -44,23 +47,66 @@ at::ScalarType parse_dtype(const std::string& s)
 
 const void* ptr(const Tensor& t) { return t.defined() ? t.data_ptr() : nullptr; }
 
-// One FP8 linear as MACROLoadFP8WeightFromCache leaves it (src/lyradiff/utils/common_macro_def.h:76-92).
-struct Fp8Weight {
-    Tensor  qweight, w_scale, bias, input_scale;
-    int64_t n = 0, k = 0;
+// A weight that takes part in LoRA hot-swap (LoraWeight<T> and its subclasses, src/lyradiff/interface/IFLoraWeight.h:15-133).
+struct LoraTarget {
+    virtual void load_lora(const Tensor& lora, double scale) = 0;
+    virtual void clear_lora()                                = 0;
+    virtual ~LoraTarget()                                    = default;
+};
 
-    void load(const Tensor& weight, const Tensor& b, const Tensor& in_scale, const at::Device& dev, at::ScalarType dt)
+// w = T(w + T(lora * T(scale))) on the device copy `w` of a 16-bit weight
+void merge_lora(Tensor& w, const Tensor& lora, double scale, at::ScalarType dt)
+{
+    TORCH_CHECK(lora.numel() == w.numel(), "lora weight has ", lora.numel(), " elements, the layer's weight ", w.numel());
+    Tensor l = lora.to(w.device(), dt).contiguous();
+    check(lyraq_load_lora(w.data_ptr(), l.data_ptr(), dt_code(dt), (float)scale, (size_t)w.numel(), stream()), "lyraq_load_lora");
+}
+
+// One FP8 linear as MACROLoadFP8WeightFromCache leaves it (src/lyradiff/utils/common_macro_def.h:76-92): e4m3 weight with
+// its amax / 448 scale, bias, static input scale and a host copy of the 16-bit weight that every LoRA merge starts from
+// (FP8LoraWeight<T>, IFLoraWeight.h:81-133).
+struct Fp8Weight: LoraTarget {
+    Tensor         qweight, w_scale, bias, input_scale, weight_h;
+    int64_t        n = 0, k = 0;
+    at::ScalarType dt = at::kBFloat16;
+    bool           loaded_lora = false;
+
+    void quantize(const Tensor& w)
     {
-        Tensor w = weight.to(dev, dt).contiguous();
-        n        = w.size(0);
-        k        = w.size(1);
-        qweight  = at::empty({n, k}, w.options().dtype(at::kByte));
-        w_scale  = at::empty({1}, w.options().dtype(at::kFloat));
         check(lyraq_weight_quant_fp8(qweight.data_ptr<uint8_t>(), w_scale.data_ptr<float>(), w.data_ptr(), dt_code(dt),
                                      (size_t)w.numel(), stream()),
               "lyraq_weight_quant_fp8");
+    }
+
+    void load(const Tensor& weight, const Tensor& b, const Tensor& in_scale, const at::Device& dev, at::ScalarType dt_)
+    {
+        dt       = dt_;
+        Tensor w = weight.to(dev, dt).contiguous();
+        n        = w.size(0);
+        k        = w.size(1);
+        weight_h = w.to(at::kCPU);
+        qweight  = at::empty({n, k}, w.options().dtype(at::kByte));
+        w_scale  = at::empty({1}, w.options().dtype(at::kFloat));
+        quantize(w);
         bias        = b.to(dev, dt).contiguous();
         input_scale = in_scale.to(dev, at::kFloat).reshape({1}).contiguous();
+        loaded_lora = false;
+    }
+
+    void load_lora(const Tensor& lora, double scale) override
+    {
+        Tensor w = weight_h.to(qweight.device());
+        merge_lora(w, lora, scale, dt);
+        quantize(w);
+        loaded_lora = true;
+    }
+
+    void clear_lora() override
+    {
+        if (loaded_lora) {
+            quantize(weight_h.to(qweight.device()));
+            loaded_lora = false;
+        }
     }
 };
 
@@ -138,10 +184,12 @@ struct W4Weight {
     }
 };
 
-struct Modulation {
-    bool      fp8 = false;
-    Fp8Weight q;
-    Tensor    w, b;
+struct Modulation: LoraTarget {
+    bool           fp8 = false;
+    Fp8Weight      q;
+    Tensor         w, b, weight_h;  // the 16-bit linear of quant_level 1 / 7 (LoraWeightV2<T>, IFLoraWeight.h:40-78)
+    at::ScalarType dt16        = at::kBFloat16;
+    bool           loaded_lora = false;
 
     void load(const c10::Dict<std::string, Tensor>& sd, const std::string& name, bool full, const at::Device& dev, at::ScalarType dt)
     {
@@ -149,8 +197,32 @@ struct Modulation {
         if (full) {
             q.load(sd.at(name + ".weight"), sd.at(name + ".bias"), sd.at(name + "_input_scale"), dev, dt);
         } else {
-            w = sd.at(name + ".weight").to(dev, dt).contiguous();
-            b = sd.at(name + ".bias").to(dev, dt).contiguous();
+            dt16        = dt;
+            w           = sd.at(name + ".weight").to(dev, dt).contiguous();
+            b           = sd.at(name + ".bias").to(dev, dt).contiguous();
+            weight_h    = w.to(at::kCPU);
+            loaded_lora = false;
+        }
+    }
+
+    void load_lora(const Tensor& lora, double scale) override
+    {
+        if (fp8) {
+            q.load_lora(lora, scale);
+            return;
+        }
+        w.copy_(weight_h);
+        merge_lora(w, lora, scale, dt16);
+        loaded_lora = true;
+    }
+
+    void clear_lora() override
+    {
+        if (fp8) {
+            q.clear_lora();
+        } else if (loaded_lora) {
+            w.copy_(weight_h);
+            loaded_lora = false;
         }
     }
 
@@ -174,6 +246,57 @@ struct Modulation {
         return out;
     }
 };
+
+// One raw array of loadWeightFromBin (src/lyradiff/utils/memory_utils.cu:295-364): file `<path><key>.bin`; kind 'T' = a 16-bit
+// tensor stored in the model file type (fp32 or fp16), 'f' = fp32 scales, 'i' = int8 (packed int4 weights).  A missing or
+// short file raises (the reference logs a warning and leaves the weight uninitialised).
+struct BinFile {
+    std::string          key;
+    std::vector<int64_t> shape;
+    char                 kind;
+};
+
+Tensor read_bin(const std::string& path, const BinFile& f, bool file_fp16)
+{
+    const at::ScalarType st = f.kind == 'i' ? at::kChar : (f.kind == 'f' || !file_fp16) ? at::kFloat : at::kHalf;
+    Tensor               t  = at::empty(f.shape, at::TensorOptions().dtype(st).device(at::kCPU));
+    const std::string    fn = path + f.key + ".bin";
+    const size_t         bytes = (size_t)t.numel() * t.element_size();
+    FILE*                fp    = std::fopen(fn.c_str(), "rb");
+    TORCH_CHECK(fp != nullptr, "weight file missing: ", fn);
+    const size_t got = std::fread(t.data_ptr(), 1, bytes, fp);
+    std::fclose(fp);
+    TORCH_CHECK(got == bytes, "weight file too small: ", fn);
+    return t;
+}
+
+void fp8_linear_files(std::vector<BinFile>& v, const std::string& name, int64_t n, int64_t k)
+{
+    v.push_back({name + ".weight", {n, k}, 'T'});
+    v.push_back({name + ".bias", {n}, 'T'});
+    v.push_back({name + "_input_scale", {1}, 'f'});
+}
+
+void w4a4_linear_files(std::vector<BinFile>& v, const std::string& name, int64_t n, int64_t k, bool has_bias)
+{
+    v.push_back({name + "packed_weight", {n, k / 2}, 'i'});
+    v.push_back({name + "weight_scale", {n, k / 64}, 'f'});
+    v.push_back({name + "lora_up", {n, 32}, 'T'});
+    v.push_back({name + "lora_down", {32, k}, 'T'});
+    v.push_back({name + "smooth", {k}, 'f'});
+    if (has_bias) {
+        v.push_back({name + "bias", {n}, 'T'});
+    }
+}
+
+void modulation_files(std::vector<BinFile>& v, const std::string& name, int64_t chunks, int64_t D, bool fp8)
+{
+    v.push_back({name + ".weight", {chunks * D, D}, 'T'});
+    v.push_back({name + ".bias", {chunks * D}, 'T'});
+    if (fp8) {
+        v.push_back({name + "_input_scale", {1}, 'f'});
+    }
+}
 
 void check_inputs(std::initializer_list<Tensor> ts, at::ScalarType dt)
 {
@@ -210,13 +333,62 @@ struct BlockBase: torch::CustomClassHolder {
                     "only quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built");
         TORCH_CHECK(heads * head_dim == dim, "embedding_dim must equal embedding_head_num * embedding_head_dim");
     }
+    // one lock per op object, held for the whole call, as the reference's ops do (FluxSingleTransformerBlockOp.h:67,231)
+    std::mutex lock;
+
     void initialize(const c10::intrusive_ptr<LyraDiffCommonContext>&) {}
-    void reload_model_from_bin(const std::string&, const std::string&)
+
+    virtual void                               load_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd,
+                                                               const std::string& device) = 0;
+    virtual std::vector<BinFile>               bin_files()                                = 0;
+    virtual std::map<std::string, LoraTarget*> lora_table()                               = 0;
+
+    void reload_model_from_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device)
     {
-        TORCH_CHECK(false, "the .bin directory loader is not built; use reload_model_from_state_dict");
+        std::lock_guard<std::mutex> g(lock);
+        load_state_dict(prefix, sd, device);
     }
-    void load_lora_by_name(const std::vector<std::string>&, const Tensor&, double) { TORCH_CHECK(false, "LoRA hot-swap is not built"); }
-    void clear_lora() { TORCH_CHECK(false, "LoRA hot-swap is not built"); }
+
+    // *BlockWeight<T>::loadWeights: one raw file `<model_path><key>.bin` per tensor, keys as in the state dict; model_dtype
+    // "fp32" or "fp16" is the file type of the 16-bit tensors (FluxSingleTransformerBlockOp.h:229-248).
+    void reload_model_from_bin(const std::string& model_path, const std::string& model_dtype)
+    {
+        TORCH_CHECK(model_dtype == "fp32" || model_dtype == "fp16", "wrong model_dtype");
+        c10::Dict<std::string, Tensor> sd;
+        for (const BinFile& f : bin_files()) {
+            sd.insert(f.key, read_bin(model_path, f, model_dtype == "fp16"));
+        }
+        std::lock_guard<std::mutex> g(lock);
+        load_state_dict("", sd, "cuda");
+    }
+
+    // IFLoraWeight<T>::loadLoraByName (IFLoraWeight.h:150-173): the names are the path to one linear; a path that leads
+    // nowhere is reported and skipped, as the reference does.
+    void load_lora_by_name(const std::vector<std::string>& names, const Tensor& weight, double scale)
+    {
+        TORCH_CHECK(loaded, "weights not loaded");
+        std::string key;
+        for (const std::string& n : names) {
+            key += (key.empty() ? "" : "/") + n;
+        }
+        std::lock_guard<std::mutex> g(lock);
+        auto                        table = lora_table();
+        auto                        it    = table.find(key);
+        if (it == table.end()) {
+            TORCH_WARN("lora name cannot find weights to load: ", key);
+            return;
+        }
+        it->second->load_lora(weight, scale);
+    }
+
+    void clear_lora()
+    {
+        TORCH_CHECK(loaded, "weights not loaded");
+        std::lock_guard<std::mutex> g(lock);
+        for (auto& kv : lora_table()) {
+            kv.second->clear_lora();
+        }
+    }
 };
 
 // FluxSingleTransformerBlockOp (th_op/flux_single_transformer_block/FluxSingleTransformerBlockOp.h:287-315)
@@ -230,7 +402,40 @@ struct FluxSingleTransformerBlockOp: BlockBase {
     bool   int4() const { return quant_level == 7 || quant_level == 8; }
     Tensor forward_int4(const Tensor& hidden, const Tensor& rope, const std::vector<Tensor>& mod);
 
-    void reload_model_from_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device)
+    std::vector<BinFile> bin_files() override
+    {
+        std::vector<BinFile> v;
+        modulation_files(v, "norm.linear", 3, dim, quant_level == 2 || quant_level == 8);
+        v.push_back({"attn.norm_q.weight", {head_dim}, 'T'});
+        v.push_back({"attn.norm_k.weight", {head_dim}, 'T'});
+        if (int4()) {
+            w4a4_linear_files(v, "attn.to_qkv.", 3 * dim, dim, true);
+            w4a4_linear_files(v, "proj_mlp.", mlp_scale * dim, dim, true);
+            w4a4_linear_files(v, "proj_out.linears.0.", dim, dim, true);
+            w4a4_linear_files(v, "proj_out.linears.1.linear.", dim, mlp_scale * dim, false);
+        } else {
+            fp8_linear_files(v, "attn.to_qkv", 3 * dim, dim);
+            fp8_linear_files(v, "proj_mlp", mlp_scale * dim, dim);
+            fp8_linear_files(v, "proj_out", dim, (mlp_scale + 1) * dim);
+        }
+        return v;
+    }
+
+    // names as the reference's lora_layer_map / lora_weight_map nest them (FluxSingleTransformerFP8BlockWeight.cc:33,80-89,
+    // FluxSingleAttentionFP8ProcessorWeight.cc:51-54, AdaFP8LayerNormWeight.cc:47-51); the W4A4 linears have no hot-swap
+    // in the reference either
+    std::map<std::string, LoraTarget*> lora_table() override
+    {
+        std::map<std::string, LoraTarget*> t{{"norm/linear", &norm}};
+        if (!int4()) {
+            t["attn/to_qkv"] = &qkv;
+            t["proj_mlp"]    = &mlp;
+            t["proj_out"]    = &out;
+        }
+        return t;
+    }
+
+    void load_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device) override
     {
         const at::Device dev(device);
         auto g = [&](const std::string& n) { return sd.at(prefix + n); };
@@ -263,6 +468,7 @@ struct FluxSingleTransformerBlockOp: BlockBase {
     Tensor forward(const Tensor& hidden, const Tensor& rope, const Tensor& temb)
     {
         TORCH_CHECK(loaded, "weights not loaded");
+        std::lock_guard<std::mutex> guard(lock);
         check_inputs({hidden, rope, temb}, dtype);
         const int64_t B = hidden.size(0), S = hidden.size(1), D = hidden.size(2), T = B * S;
         TORCH_CHECK(D == dim && temb.size(0) == B && temb.size(1) == D && rope.numel() == T * head_dim * 2, "shape mismatch");
@@ -360,7 +566,48 @@ struct FluxTransformerBlockOp: BlockBase {
         s.qk_scale = at::cat({g(nq).reshape({-1}), g(nk).reshape({-1})}).to(dev, dtype).contiguous();
     }
 
-    void reload_model_from_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device)
+    std::vector<BinFile> bin_files() override
+    {
+        std::vector<BinFile> v;
+        const char*          names[2][6] = {{"norm1", "attn.to_qkv", "attn.to_out.0", "attn.norm_q.weight", "attn.norm_k.weight", "ff"},
+                                            {"norm1_context", "attn.to_added_qkv", "attn.to_add_out", "attn.norm_added_q.weight",
+                                             "attn.norm_added_k.weight", "ff_context"}};
+        for (auto& s : names) {
+            const std::string norm = s[0], qkv = s[1], out = s[2], ff = s[5];
+            modulation_files(v, norm + ".linear", 6, dim, quant_level == 2 || quant_level == 8);
+            v.push_back({s[3], {head_dim}, 'T'});
+            v.push_back({s[4], {head_dim}, 'T'});
+            if (int4()) {
+                w4a4_linear_files(v, qkv + ".", 3 * dim, dim, true);
+                w4a4_linear_files(v, out + ".", dim, dim, true);
+                w4a4_linear_files(v, ff + ".net.0.proj.", 4 * dim, dim, true);
+            } else {
+                fp8_linear_files(v, qkv, 3 * dim, dim);
+                fp8_linear_files(v, out, dim, dim);
+                fp8_linear_files(v, ff + ".net.0.proj", 4 * dim, dim);
+            }
+            fp8_linear_files(v, ff + ".net.2", dim, 4 * dim);
+        }
+        return v;
+    }
+
+    // FluxTransformerFP8BlockWeight.cc:41-45, FluxAttentionFP8ProcessorWeight.cc:91-108, FluxAttnPostFP8ProcessorWeight.cc:58-64
+    std::map<std::string, LoraTarget*> lora_table() override
+    {
+        std::map<std::string, LoraTarget*> t{{"norm1/linear", &img.norm}, {"norm1_context/linear", &txt.norm},
+                                             {"ff/net.2", &img.ff2}, {"ff_context/net.2", &txt.ff2}};
+        if (!int4()) {
+            t["attn/to_qkv"]           = &img.qkv;
+            t["attn/to_out.0"]         = &img.out;
+            t["attn/to_added_qkv"]     = &txt.qkv;
+            t["attn/to_add_out"]       = &txt.out;
+            t["ff/net.0.proj"]         = &img.ff1;
+            t["ff_context/net.0.proj"] = &txt.ff1;
+        }
+        return t;
+    }
+
+    void load_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device) override
     {
         const at::Device dev(device);
         load_stream(img, prefix, sd, dev, "norm1", "attn.to_qkv", "attn.to_out.0", "attn.norm_q.weight", "attn.norm_k.weight", "ff");
@@ -434,6 +681,7 @@ struct FluxTransformerBlockOp: BlockBase {
     std::vector<Tensor> forward(const Tensor& hidden, const Tensor& encoder, const Tensor& rope, const Tensor& temb)
     {
         TORCH_CHECK(loaded, "weights not loaded");
+        std::lock_guard<std::mutex> guard(lock);
         check_inputs({hidden, encoder, rope, temb}, dtype);
         const int64_t B = hidden.size(0), S = hidden.size(1), D = hidden.size(2), E = encoder.size(1), tot = S + E;
         TORCH_CHECK(D == dim && encoder.size(0) == B && encoder.size(2) == D && temb.size(0) == B && temb.size(1) == D &&
@@ -473,7 +721,8 @@ void register_block(torch::Library& m, const char* name)
         .def(torch::init<std::string, int64_t, int64_t, int64_t, int64_t, int64_t>())
         .def("initialize", [](const Self& self, const c10::intrusive_ptr<LyraDiffCommonContext>& ctx) { self->initialize(ctx); })
         .def("forward", &Op::forward)
-        .def("reload_model_from_state_dict", &Op::reload_model_from_state_dict)
+        .def("reload_model_from_state_dict", [](const Self& self, const std::string& prefix, const c10::Dict<std::string, Tensor>& sd,
+                                                const std::string& device) { self->reload_model_from_state_dict(prefix, sd, device); })
         .def("reload_model_from_bin",
              [](const Self& self, const std::string& path, const std::string& dtype) { self->reload_model_from_bin(path, dtype); })
         .def("load_lora_by_name", [](const Self& self, const std::vector<std::string>& names, const Tensor& w,

@@ -141,3 +141,79 @@ def test_double_block_int4_same_bits_as_mirror(ns, level):
 def test_levels_that_are_not_built_raise(ns):
     with pytest.raises(RuntimeError, match="quant_level"):
         ns.FluxTransformerBlockOp("bf16", 256, 2, 128, 4, 5)
+
+
+@pytest.mark.parametrize("level", [1, 2])
+def test_lora_hot_swap_same_bits_as_mirror(ns, level):
+    from lyradiff_b200 import flux_blocks
+    D, heads, head_dim, mlp_scale = 256, 2, 128, 4
+    g = torch.Generator().manual_seed(90 + level)
+    prefix = "s."
+    sd = _state_dict(prefix, D, mlp_scale, head_dim, level, g)
+    hidden = cu(torch.randn(1, 96, D, generator=g).bfloat16())
+    temb = cu(torch.nn.functional.silu(torch.randn(1, D, generator=g)).bfloat16())
+    rope = cu(_rope(1, 96, head_dim, g, torch.bfloat16))
+    mirror = flux_blocks.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    mirror.reload_model_from_state_dict(prefix, sd, "cuda")
+    op = ns.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    base = op.forward(hidden, rope, temb).clone()
+    for names, shape in ((["proj_out"], (D, 5 * D)), (["attn", "to_qkv"], (3 * D, D)), (["norm", "linear"], (3 * D, D))):
+        lora = cu((torch.randn(shape, generator=g) * 0.01).bfloat16())
+        mirror.load_lora_by_name(names, lora, 0.8)
+        op.load_lora_by_name(names, lora, 0.8)
+    got = op.forward(hidden, rope, temb)
+    assert torch.equal(got, mirror.forward(hidden, rope, temb)) and not torch.equal(got, base)
+    op.load_lora_by_name(["attn", "to_k"], cu(torch.zeros(4, 4).bfloat16()), 1.0)   # unknown path: reported and skipped
+    op.clear_lora()
+    assert torch.equal(op.forward(hidden, rope, temb), base)
+    check_status()
+
+
+@pytest.mark.parametrize("level,file_type", [(2, "fp32"), (7, "fp32")])
+def test_reload_from_bin_same_bits_as_state_dict(ns, tmp_path, level, file_type):
+    import numpy as np
+    from tests.test_gpu_flux_block import _int4_state_dict, _write_bins
+    D, heads, head_dim, mlp_scale = 256, 2, 128, 4
+    g = torch.Generator().manual_seed(95 + level)
+    prefix = "single_transformer_blocks.1."
+    sd = _int4_state_dict(prefix, D, mlp_scale, head_dim, level, g) if level == 7 else _state_dict(prefix, D, mlp_scale, head_dim, level, g)
+    base = str(tmp_path) + "/" + prefix
+    _write_bins(base, sd, prefix, np.float32)
+    hidden = cu(torch.randn(1, 64, D, generator=g).bfloat16())
+    temb = cu(torch.nn.functional.silu(torch.randn(1, D, generator=g)).bfloat16())
+    rope = cu(_rope(1, 64, head_dim, g, torch.bfloat16))
+    a = ns.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    a.reload_model_from_state_dict(prefix, sd, "cuda")
+    b = ns.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, mlp_scale, level)
+    b.reload_model_from_bin(base, file_type)
+    assert torch.equal(a.forward(hidden, rope, temb), b.forward(hidden, rope, temb))
+
+
+def test_double_block_reload_from_bin_and_lora(ns, tmp_path):
+    import numpy as np
+    from tests.test_gpu_flux_block import _write_bins
+    D, heads, head_dim = 256, 2, 128
+    g = torch.Generator().manual_seed(99)
+    prefix = "transformer_blocks.6."
+    sd = _double_state_dict(prefix, D, head_dim, 1, g)
+    base = str(tmp_path) + "/" + prefix
+    _write_bins(base, sd, prefix, np.float16)
+    sd16 = {k: (v.half() if v.dtype == torch.bfloat16 else v) for k, v in sd.items()}
+    hidden = cu(torch.randn(1, 64, D, generator=g).half())
+    encoder = cu(torch.randn(1, 32, D, generator=g).half())
+    temb = cu(torch.nn.functional.silu(torch.randn(1, D, generator=g)).half())
+    rope = cu(_rope(1, 96, head_dim, g, torch.float16))
+    a = ns.FluxTransformerBlockOp("fp16", D, heads, head_dim, 6, 1)
+    a.reload_model_from_state_dict(prefix, sd16, "cuda")
+    b = ns.FluxTransformerBlockOp("fp16", D, heads, head_dim, 6, 1)
+    b.reload_model_from_bin(base, "fp16")
+    want = a.forward(hidden, encoder, rope, temb)
+    for u, v in zip(want, b.forward(hidden, encoder, rope, temb)):
+        assert torch.equal(u, v)
+    b.load_lora_by_name(["ff_context", "net.2"], cu((torch.randn(D, 4 * D, generator=g) * 0.02).half()), 1.0)
+    out_i, out_t = b.forward(hidden, encoder, rope, temb)
+    assert torch.equal(out_i, want[0]) and not torch.equal(out_t, want[1])   # only the text stream's FF changed
+    b.clear_lora()
+    for u, v in zip(want, b.forward(hidden, encoder, rope, temb)):
+        assert torch.equal(u, v)

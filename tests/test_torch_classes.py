@@ -27,11 +27,13 @@ def test_names_and_signatures(ns, name):
         cls("fp32", 256, 2, 128, 4, 1)
     with pytest.raises(RuntimeError, match="embedding_dim"):
         cls("fp16", 256, 3, 128, 4, 1)
-    with pytest.raises(RuntimeError, match="not built"):
-        op.reload_model_from_bin("/nowhere", "bf16")
-    with pytest.raises(RuntimeError, match="not built"):
+    with pytest.raises(RuntimeError, match="wrong model_dtype"):
+        op.reload_model_from_bin("/nowhere/", "bf16")          # file types are fp32 and fp16, as in the reference
+    with pytest.raises(RuntimeError, match="weight file missing"):
+        op.reload_model_from_bin("/nowhere/", "fp16")
+    with pytest.raises(RuntimeError, match="weights not loaded"):
         op.load_lora_by_name(["a"], torch.zeros(1), 1.0)
-    with pytest.raises(RuntimeError, match="not built"):
+    with pytest.raises(RuntimeError, match="weights not loaded"):
         op.clear_lora()
 
 
