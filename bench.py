@@ -443,7 +443,7 @@ class FluxBlock:
         from lyradiff_b200 import flux_blocks
         g = _gen()
         prefix, sd = self._state_dict(g)
-        self.op = flux_blocks.FluxSingleTransformerBlockOp("bf16", self.D, self.H, self.DH, self.MLP, 1)
+        self.op = flux_blocks.FluxSingleTransformerBlockOp("bf16", self.D, self.H, self.DH, self.MLP, getattr(self, "quant_level", 1))
         self.op.initialize(flux_blocks.LyraDiffCommonContext())
         self.op.reload_model_from_state_dict(prefix, sd, dev)
         x, temb, rope = self._inputs(g, self.tokens)
@@ -509,6 +509,48 @@ class FluxBlock:
         return blocks.flux_single_block(x, rope, temb, self.cpu_sd, self.cpu_prefix, self.H, self.DH, self.MLP, 1, cache=self.cpu_cache)[0]
 
     cpu_note = "oracle block with weights quantized once: fp64 contractions of the e4m3 operands and exact attention over the sample's own rows"
+
+
+class FluxBlockInt4(FluxBlock):
+    """The same single-stream block at quant_level 7 (INT4_W4A4): every linear a W4A4 group-64 linear with its rank-32
+    LoRA branch (int4 quantize + LoRA-down, grouped GEMM + LoRA-up + epilogue), proj_out as the reference's two linears."""
+    name = "flux_block_int4"
+    metric = "flux_single_block_int4_throughput"
+    dtype = "int4 W4A4 linears (s32 per group of 64 in TMEM, f32 across groups) + bf16 library attention"
+
+    def __init__(self, tokens):
+        super().__init__(tokens)
+        self.workload = self.workload.replace("FP8_W8A8", "INT4_W4A4 (rank-32 LoRA branches)").replace("in FP8 linears", "in W4A4 linears")
+        self.launches_per_step = 15
+        self.roof["kernel"] = ("whole block: 4 x (int4 quantize, LoRA-down, gemm_w4a4_kernel) + AdaLN, QK-norm/RoPE and gate kernels of "
+                               "this library, plus the library attention and one small library matmul")
+
+    def _state_dict(self, g):
+        from oracle import quant
+        D, M = self.D, self.MLP
+        p = "single_transformer_blocks.0."
+        sd = {p + "norm.linear.weight": (torch.randn(3 * D, D, generator=g) * 0.02).bfloat16(),
+              p + "norm.linear.bias": (torch.randn(3 * D, generator=g) * 0.02).bfloat16(),
+              p + "attn.norm_q.weight": torch.ones(self.DH).bfloat16(), p + "attn.norm_k.weight": torch.ones(self.DH).bfloat16()}
+        for name, n, k, bias in (("attn.to_qkv.", 3 * D, D, True), ("proj_mlp.", M * D, D, True), ("proj_out.linears.0.", D, D, True),
+                                 ("proj_out.linears.1.linear.", D, M * D, False)):
+            pw, sw, _ = quant.int4_weight_quant_g64((torch.randn(n, k, generator=g) * 0.02).bfloat16())
+            sd[p + name + "packed_weight"], sd[p + name + "weight_scale"] = pw, sw
+            sd[p + name + "smooth"] = 0.5 + torch.rand(k, generator=g)
+            sd[p + name + "lora_down"] = (torch.randn(32, k, generator=g) * 0.02).bfloat16()
+            sd[p + name + "lora_up"] = (torch.randn(n, 32, generator=g) * 0.02).bfloat16()
+            if bias:
+                sd[p + name + "bias"] = (torch.randn(n, generator=g) * 0.02).bfloat16()
+        return p, sd
+
+    quant_level = 7
+
+    def step_cpu(self):
+        from oracle import blocks
+        x, temb, rope = self.cpu_in
+        return blocks.flux_single_block_int4(x, rope, temb, self.cpu_sd, self.cpu_prefix, self.H, self.DH, self.MLP, 7)[0]
+
+    cpu_note = "oracle INT4 block: exact int32 group sums with fp32 rescale in group order, fp64 LoRA sums, exact attention over the sample's own rows"
 
 
 class FluxForward(FluxBlock):
@@ -741,7 +783,7 @@ class AdalnQuant:
     cpu_note = "LayerNorm + modulation + int8 and e4m3 quantize"
 
 
-CASES = {c.name: c for c in (FluxFp8, FluxBlock, FluxForward, Int8Sdxl, SdxlFF, W4A4, AdalnQuant)}
+CASES = {c.name: c for c in (FluxFp8, FluxBlock, FluxBlockInt4, FluxForward, Int8Sdxl, SdxlFF, W4A4, AdalnQuant)}
 
 
 # =================================================================================================== CPU arm
