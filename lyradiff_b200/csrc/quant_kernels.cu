@@ -5,10 +5,12 @@
 // shuffles (plus one shared-memory hop when the team spans several warps), and writes the
 // quantized row once with 8- or 16-byte stores.  Nothing is staged through global memory.
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace lyraq {
 
 int device_sm_count();  // gemm_dense.cu
+unsigned int* status_word_ptr();  // api.cu
 int launch_lora_down(float* act, const void* x, const void* down, int dtype, size_t m, size_t k, cudaStream_t stream);  // lora_down.cu
 
 enum RowMode { ROW_PLAIN = 0, ROW_ADALN = 1, ROW_LN = 2, ROW_GEGLU = 3 };
@@ -455,6 +457,60 @@ __global__ void __launch_bounds__(256) fp8_cast_kernel(uint8_t* dst, const T* sr
     }
 }
 
+// The same conversion with the source staged through shared memory: one bulk asynchronous copy per block brings its
+// 32 KB chunk in (no registers held while it is in flight), so six resident blocks keep 192 KB per SM outstanding and a
+// tensor of up to 148 * 6 chunks (29 MB of 16-bit input) is read in a single wave with a single round trip to DRAM.
+constexpr int kBulkElems = 16384;
+constexpr int kBulkSmem  = kBulkElems * 2 + 16;
+template<typename T>
+__global__ void __launch_bounds__(256) fp8_cast_bulk_kernel(uint8_t* dst, const T* src, const float* scale, int invert, size_t n,
+                                                            unsigned int* status)
+{
+    extern __shared__ __align__(128) uint8_t cast_smem[];
+    const uint32_t data       = sm100::smem_u32(cast_smem);
+    const uint32_t bar        = data + kBulkElems * 2;
+    volatile int*  abort_flag = reinterpret_cast<volatile int*>(cast_smem + kBulkElems * 2 + 8);
+    const size_t   e0         = (size_t)blockIdx.x * kBulkElems;
+    const size_t   n8         = n & ~(size_t)7;
+    const uint32_t elems      = (uint32_t)((n8 - e0 < (size_t)kBulkElems) ? (n8 - e0) : (size_t)kBulkElems);
+    grid_launch_dependents();
+    if (threadIdx.x == 0) {
+        sm100::mbar_init(bar, 1);
+        *abort_flag = 0;
+        sm100::fence_barrier_init();
+    }
+    __syncthreads();
+    grid_dependency_wait();
+    if (threadIdx.x == 0 && elems != 0) {
+        sm100::mbar_arrive_expect_tx(bar, elems * 2u);
+        sm100::bulk_load(data, src + e0, elems * 2u, bar);
+    }
+    const float s = __ldg(scale);
+    const float r = invert ? 1.0f / s : s;
+    if (elems != 0) {
+        if (!sm100::mbar_wait(bar, 0u, abort_flag)) {
+            if (threadIdx.x == 0) {
+                report_timeout(status, 0x3100u);
+            }
+            return;
+        }
+        const uint32_t nv = elems >> 3;
+#pragma unroll 4
+        for (uint32_t v = threadIdx.x; v < nv; v += 256) {
+            float v8[8];
+            unpack8<T>(*reinterpret_cast<const Vec16*>(cast_smem + (size_t)v * 16), v8);
+            const uint32_t w0 = f32x2_to_e4m3x2(v8[0] * r, v8[1] * r) | (f32x2_to_e4m3x2(v8[2] * r, v8[3] * r) << 16);
+            const uint32_t w1 = f32x2_to_e4m3x2(v8[4] * r, v8[5] * r) | (f32x2_to_e4m3x2(v8[6] * r, v8[7] * r) << 16);
+            st_8(dst + e0 + ((size_t)v << 3), w0, w1);
+        }
+    }
+    // tail (n not a multiple of 8): the last block
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x < (n & 7)) {
+        const size_t i = n8 + threadIdx.x;
+        dst[i]         = (uint8_t)(f32x2_to_e4m3x2(to_f32(src[i]) * r, 0.0f) & 0xff);
+    }
+}
+
 // max|w|/448 folded into scale[0] with an integer atomicMax on the (non-negative) float bits.
 template<typename T> __global__ void __launch_bounds__(256) fp8_amax_kernel(float* scale, const T* src, size_t n)
 {
@@ -639,13 +695,31 @@ int lyraq_quant_fp8(uint8_t* dst, const void* src, int src_dtype, const float* s
     if (!aligned16(src) || (reinterpret_cast<uintptr_t>(dst) & 7u) != 0) {
         return LYRAQ_ERR_INVALID_ARG;
     }
+    if (src_dtype != LYRAQ_F16 && src_dtype != LYRAQ_BF16) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    // One 32 KB chunk per block through the bulk-staged kernel; fewer than 8 elements fall through to the grid-stride
+    // kernel's scalar tail.
+    const size_t chunks = ((n & ~(size_t)7) + kBulkElems - 1) / kBulkElems;
+    if (chunks >= 1 && chunks <= 0x7fffffffu) {
+        unsigned int* status = status_word_ptr();
+        if (status == nullptr) {
+            return LYRAQ_ERR_CUDA;
+        }
+        if (src_dtype == LYRAQ_F16) {
+            launch_kernel(fp8_cast_bulk_kernel<__half>, (unsigned)chunks, 256u, (size_t)kBulkSmem, (cudaStream_t)stream, 1u, dst,
+                          (const __half*)src, scale, invert_scale, n, status);
+        } else {
+            launch_kernel(fp8_cast_bulk_kernel<__nv_bfloat16>, (unsigned)chunks, 256u, (size_t)kBulkSmem, (cudaStream_t)stream, 1u, dst,
+                          (const __nv_bfloat16*)src, scale, invert_scale, n, status);
+        }
+        return launch_status();
+    }
     const unsigned grid = flat_grid(n >> 3);
     if (src_dtype == LYRAQ_F16) {
         launch_kernel(fp8_cast_kernel<__half>, (unsigned)(grid), 256u, (size_t)0, (cudaStream_t)stream, 1u, dst, (const __half*)src, scale, invert_scale, n);
-    } else if (src_dtype == LYRAQ_BF16) {
-        launch_kernel(fp8_cast_kernel<__nv_bfloat16>, (unsigned)(grid), 256u, (size_t)0, (cudaStream_t)stream, 1u, dst, (const __nv_bfloat16*)src, scale, invert_scale, n);
     } else {
-        return LYRAQ_ERR_UNSUPPORTED;
+        launch_kernel(fp8_cast_kernel<__nv_bfloat16>, (unsigned)(grid), 256u, (size_t)0, (cudaStream_t)stream, 1u, dst, (const __nv_bfloat16*)src, scale, invert_scale, n);
     }
     return launch_status();
 }
