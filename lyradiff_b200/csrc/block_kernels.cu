@@ -24,29 +24,38 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(T* out, const T* qkv,
     const size_t  total      = tokens * vec_per_tok;
     const size_t  stride     = (size_t)gridDim.x * blockDim.x;
     const bool    in_place   = (out == qkv);
-    // total is a multiple of LANES and so is the block size: the lanes of a head stay together in every iteration
-    for (size_t vi = (size_t)blockIdx.x * blockDim.x + threadIdx.x; vi < total; vi += stride) {
-        const size_t tok  = vi / vec_per_tok;
-        const int    rem  = (int)(vi - tok * vec_per_tok);
-        const int    head = rem / LANES;          // 0 .. 3 * heads - 1: q heads, k heads, v heads
-        const int    part = rem - head * LANES;   // which 8 elements of the head
-        const bool   is_v = head >= 2 * heads;
-        if (is_v && in_place) {
-            continue;  // whole groups of LANES lanes take this branch together
+    // total is a multiple of LANES and so is the block size: the lanes of a head stay together in every iteration.  A warp
+    // may hold a V head next to a Q/K head, and the tail of the last iteration may leave lanes without work, so every
+    // lane of the warp takes part in the shuffles (lanes without a Q/K head reduce zeros) and only the loads, the
+    // arithmetic and the store are predicated.
+    const size_t first = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t iters = (total + stride - 1) / stride;
+    for (size_t it = 0; it < iters; ++it) {
+        const size_t vi     = first + it * stride;
+        const bool   active = vi < total;
+        const size_t tok    = active ? vi / vec_per_tok : 0;
+        const int    rem    = active ? (int)(vi - tok * vec_per_tok) : 0;
+        const int    head   = rem / LANES;          // 0 .. 3 * heads - 1: q heads, k heads, v heads
+        const int    part   = rem - head * LANES;   // which 8 elements of the head
+        const bool   is_v   = head >= 2 * heads;
+        const bool   load   = active && !(is_v && in_place);
+        const bool   rotate = active && !is_v;
+        Vec16        x      = {};
+        if (load) {
+            x = ld_nc_16(qkv + (vi << 3));
         }
-        Vec16 x = ld_nc_16(qkv + (vi << 3));
-        if (!is_v) {
-            float f[8];
-            unpack8<T>(x, f);
-            float ss = 0.0f;
+        float f[8];
+        unpack8<T>(x, f);
+        float ss = 0.0f;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                ss = fmaf(f[j], f[j], ss);
-            }
+        for (int j = 0; j < 8; ++j) {
+            ss = fmaf(f[j], f[j], ss);
+        }
 #pragma unroll
-            for (int m = LANES / 2; m > 0; m >>= 1) {
-                ss += __shfl_xor_sync(0xffffffffu, ss, m);
-            }
+        for (int m = LANES / 2; m > 0; m >>= 1) {
+            ss += __shfl_xor_sync(0xffffffffu, ss, m);
+        }
+        if (rotate) {
             const float inv = rsqrtf(ss / (float)kHeadDim + eps);
             const Vec16 sc  = ld_nc_16_keep(scale + (head >= heads ? kHeadDim : 0) + part * 8);
             // rope: [tokens, head_dim / 2, 2, 2]; this thread's 4 pairs are 16 consecutive values
@@ -65,7 +74,9 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(T* out, const T* qkv,
                 x.w[j]          = P2::from_f32(pa.x + pa.y, pb.x + pb.y);  // fp32 sum of two T values, rounded once = T add
             }
         }
-        st_16(out + (vi << 3), x);
+        if (load) {
+            st_16(out + (vi << 3), x);
+        }
     }
 }
 
@@ -76,7 +87,7 @@ __global__ void __launch_bounds__(256) fp8_cast_2d_kernel(uint8_t* dst, size_t d
 {
     grid_launch_dependents();
     grid_dependency_wait();
-    const float  r       = 1.0f / __ldg(scale);
+    const float  r       = 1.0f / ld_f32(scale);
     const int    vec_row = cols >> 3;
     const size_t total   = rows * (size_t)vec_row;
     const size_t stride  = (size_t)gridDim.x * blockDim.x;

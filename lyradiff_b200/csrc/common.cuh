@@ -159,6 +159,30 @@ __device__ __forceinline__ Vec16 ld_nc_16_keep(const void* p)
     return v;
 }
 
+// Loads that stay where they are written.  Every kernel here may start before its predecessor in the stream has finished
+// (programmatic dependent launch) and reads global memory only after griddepcontrol.wait.  __ldg() is an invariant load
+// to the compiler, which may move it above that wait (an e4m3 cast then read its scale before the amax kernel in front
+// of it had written it); a volatile asm load is never moved across another volatile asm statement.  Use these for
+// anything a previous kernel may have produced: scales, per-token scale vectors, smoothing vectors, low-rank activations.
+__device__ __forceinline__ float ld_f32(const float* p)
+{
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ float4 ld_f32x4(const float4* p)
+{
+    float4 v;
+    asm volatile("ld.global.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ld_u32x4(const uint4* p)
+{
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ void st_16(void* p, const Vec16& v)
 {
     asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3])

@@ -557,7 +557,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t box_addr  = smem_base + S::kEpiOffset + (warp - kEpiWarp0) * kStoreBox;
         float fp8_scale = 0.0f;
         if (KIND == KIND_F8) {
-            fp8_scale = e.alpha * __ldg(e.s_a) * __ldg(e.s_b);
+            fp8_scale = e.alpha * ld_f32(e.s_a) * ld_f32(e.s_b);
         }
         const bool vec_ok = (e.c_dtype == LYRAQ_F32 || e.c_dtype == LYRAQ_S32) ? ((e.ldc & 3) == 0) : ((e.ldc & 7) == 0);
         int local = 0;
@@ -577,7 +577,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 uint16_t  raw = 0;
                 if (col < p.N) {
                     if (KIND == KIND_I8 && e.col_scale != nullptr) {
-                        v.x = __ldg(e.col_scale + col);
+                        v.x = ld_f32(e.col_scale + col);
                     }
                     if (RES && KIND == KIND_F8 && e.gate != nullptr) {
                         // all rows of a tile belong to one batch entry (checked on the host)
@@ -658,7 +658,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int row  = row0 + lane;
             float     row_scale = 1.0f;
             if (KIND == KIND_I8 && e.c_dtype != LYRAQ_S32) {
-                row_scale = e.row_scale_per_token ? ((row < p.M) ? __ldg(e.row_scale + row) : 0.0f) : __ldg(e.row_scale);
+                row_scale = e.row_scale_per_token ? ((row < p.M) ? ld_f32(e.row_scale + row) : 0.0f) : ld_f32(e.row_scale);
             }
             const uint32_t t_addr = tmem_base + lane_addr + (uint32_t)(buf * BLOCK_N + half * kHalfN);
 
@@ -737,7 +737,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 if (e.out_q_scale != nullptr) {
                     // fused activation quantize for the next FP8 linear: the T-rounded result times 1/s, e4m3 RNE satfinite
                     if (in_range) {
-                        const float r  = 1.0f / __ldg(e.out_q_scale);
+                        const float r  = 1.0f / ld_f32(e.out_q_scale);
                         uint32_t    w[8];
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {

@@ -414,14 +414,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const int    gcol = n_blk * kBN + r;
                     const float* pa   = p.sa + (size_t)grow * p.G + g0;
                     if (full && grow < p.M) {
-                        const float4 x0 = __ldg(reinterpret_cast<const float4*>(pa));
-                        const float4 x1 = __ldg(reinterpret_cast<const float4*>(pa) + 1);
+                        const float4 x0 = ld_f32x4(reinterpret_cast<const float4*>(pa));
+                        const float4 x1 = ld_f32x4(reinterpret_cast<const float4*>(pa) + 1);
                         va[rr][0] = x0.x; va[rr][1] = x0.y; va[rr][2] = x0.z; va[rr][3] = x0.w;
                         va[rr][4] = x1.x; va[rr][5] = x1.y; va[rr][6] = x1.z; va[rr][7] = x1.w;
                     } else {
 #pragma unroll
                         for (int g = 0; g < 8; ++g) {
-                            va[rr][g] = (grow < p.M && g0 + g < p.G) ? __ldg(pa + g) : 0.0f;
+                            va[rr][g] = (grow < p.M && g0 + g < p.G) ? ld_f32(pa + g) : 0.0f;
                         }
                     }
                     if (p.sb_is_f16) {
@@ -442,14 +442,14 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     } else {
                         const float* pb = reinterpret_cast<const float*>(p.sb) + (size_t)gcol * p.G + g0;
                         if (full && gcol < p.N) {
-                            const float4 x0 = __ldg(reinterpret_cast<const float4*>(pb));
-                            const float4 x1 = __ldg(reinterpret_cast<const float4*>(pb) + 1);
+                            const float4 x0 = ld_f32x4(reinterpret_cast<const float4*>(pb));
+                            const float4 x1 = ld_f32x4(reinterpret_cast<const float4*>(pb) + 1);
                             vb[rr][0] = x0.x; vb[rr][1] = x0.y; vb[rr][2] = x0.z; vb[rr][3] = x0.w;
                             vb[rr][4] = x1.x; vb[rr][5] = x1.y; vb[rr][6] = x1.z; vb[rr][7] = x1.w;
                         } else {
 #pragma unroll
                             for (int g = 0; g < 8; ++g) {
-                                vb[rr][g] = (gcol < p.N && g0 + g < p.G) ? __ldg(pb + g) : 0.0f;
+                                vb[rr][g] = (gcol < p.N && g0 + g < p.G) ? ld_f32(pb + g) : 0.0f;
                             }
                         }
                     }
@@ -566,9 +566,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 for (int cidx = 0; cidx < 4; ++cidx) {
                     uint4 av = make_uint4(0u, 0u, 0u, 0u), bv = make_uint4(0u, 0u, 0u, 0u);
                     if (arow < p.M && !p.lora_act_is_f32) {
-                        av = __ldg(a16 + cidx);
+                        av = ld_u32x4(a16 + cidx);
                     } else if (arow < p.M) {
-                        const float4 f0 = __ldg(asrc + 2 * cidx), f1 = __ldg(asrc + 2 * cidx + 1);
+                        const float4 f0 = ld_f32x4(asrc + 2 * cidx), f1 = ld_f32x4(asrc + 2 * cidx + 1);
                         if (p.c_dtype == LYRAQ_BF16) {
                             av.x = Pair<__nv_bfloat16>::from_f32(f0.x, f0.y); av.y = Pair<__nv_bfloat16>::from_f32(f0.z, f0.w);
                             av.z = Pair<__nv_bfloat16>::from_f32(f1.x, f1.y); av.w = Pair<__nv_bfloat16>::from_f32(f1.z, f1.w);
@@ -578,7 +578,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         }
                     }
                     if (brow < p.N) {
-                        bv = __ldg(bsrc + cidx);
+                        bv = ld_u32x4(bsrc + cidx);
                     }
                     *reinterpret_cast<uint4*>(dst + ((cidx ^ swz) << 4))                = av;
                     *reinterpret_cast<uint4*>(dst + kOperandTile + ((cidx ^ swz) << 4)) = bv;

@@ -265,12 +265,12 @@ row_quant_kernel(const RowParams p)
     float s8 = 1.0f;
     float f8r = 0.0f;
     if (p.qf8 != nullptr) {
-        const float s = __ldg(p.f8_scale);
+        const float s = ld_f32(p.f8_scale);
         f8r           = p.f8_invert ? 1.0f / s : s;
     }
     float f8rb = 0.0f;
     if (p.qf8b != nullptr) {
-        f8rb = 1.0f / __ldg(p.f8_scale_b);
+        f8rb = 1.0f / ld_f32(p.f8_scale_b);
     }
     const bool dynamic = (p.scale_mode == LYRAQ_SCALE_PER_TOKEN_DYNAMIC);
     if (p.q8 != nullptr) {
@@ -281,8 +281,8 @@ row_quant_kernel(const RowParams p)
                 const int vi = tlane + i * tpr;
                 float2 g[4];
                 if (p.pre != nullptr && live && vi < nvec) {
-                    const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
-                    const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
+                    const float4 p0 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
+                    const float4 p1 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
                     g[0] = mul_f32x2(f[i][0], make_float2(p0.x, p0.y));
                     g[1] = mul_f32x2(f[i][1], make_float2(p0.z, p0.w));
                     g[2] = mul_f32x2(f[i][2], make_float2(p1.x, p1.y));
@@ -302,9 +302,9 @@ row_quant_kernel(const RowParams p)
                 p.q8_scale[row] = s8;
             }
         } else if (p.scale_mode == LYRAQ_SCALE_PER_TOKEN) {
-            s8 = live ? __ldg(p.q8_scale + row) : 1.0f;
+            s8 = live ? ld_f32(p.q8_scale + row) : 1.0f;
         } else {
-            s8 = __ldg(p.q8_scale);
+            s8 = ld_f32(p.q8_scale);
         }
     }
     const float r8 = 1.0f / s8;
@@ -333,8 +333,8 @@ row_quant_kernel(const RowParams p)
             }
             if (p.q8 != nullptr) {
                 if (p.pre != nullptr) {
-                    const float4 p0 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
-                    const float4 p1 = __ldg(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
+                    const float4 p0 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + (vi << 3)));
+                    const float4 p1 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + (vi << 3) + 4));
                     f[i][0] = mul_f32x2(f[i][0], make_float2(p0.x, p0.y));
                     f[i][1] = mul_f32x2(f[i][1], make_float2(p0.z, p0.w));
                     f[i][2] = mul_f32x2(f[i][2], make_float2(p1.x, p1.y));
@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(256) fp8_cast_kernel(uint8_t* dst, const T* sr
 {
     grid_launch_dependents();
     grid_dependency_wait();
-    const float  s      = __ldg(scale);
+    const float  s      = ld_f32(scale);
     const float  r      = invert ? 1.0f / s : s;
     const size_t nvec   = n >> 3;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(256) fp8_cast_bulk_kernel(uint8_t* dst, const 
         sm100::mbar_arrive_expect_tx(bar, elems * 2u);
         sm100::bulk_load(data, src + e0, elems * 2u, bar);
     }
-    const float s = __ldg(scale);
+    const float s = ld_f32(scale);
     const float r = invert ? 1.0f / s : s;
     if (elems != 0) {
         if (!sm100::mbar_wait(bar, 0u, abort_flag)) {
@@ -558,8 +558,8 @@ int4_g64_kernel(uint32_t* q, ST* q_scale, const T* x, const float* smooth, size_
             unpack8<T>(ld_nc_16(x + (vi << 3)), v);
             if (smooth != nullptr) {
                 const int    c  = (int)(vi % vec_per_row) << 3;
-                const float4 s0 = __ldg(reinterpret_cast<const float4*>(smooth + c));
-                const float4 s1 = __ldg(reinterpret_cast<const float4*>(smooth + c + 4));
+                const float4 s0 = ld_f32x4(reinterpret_cast<const float4*>(smooth + c));
+                const float4 s1 = ld_f32x4(reinterpret_cast<const float4*>(smooth + c + 4));
                 v[0] /= s0.x; v[1] /= s0.y; v[2] /= s0.z; v[3] /= s0.w;
                 v[4] /= s1.x; v[5] /= s1.y; v[6] /= s1.z; v[7] /= s1.w;
             }
@@ -611,7 +611,7 @@ int8_weight_quant_kernel(float* w_scale, int8_t* qw, const T* w, const float* pr
     for (size_t c = threadIdx.x; c < d_in; c += blockDim.x) {
         float v = to_f32(wrow[c]);
         if (pre != nullptr) {
-            v = v / __ldg(pre + c);
+            v = v / ld_f32(pre + c);
         }
         amax = fmaxf(amax, fabsf(v));
     }
@@ -623,7 +623,7 @@ int8_weight_quant_kernel(float* w_scale, int8_t* qw, const T* w, const float* pr
     for (size_t c = threadIdx.x; c < d_in; c += blockDim.x) {
         float v = to_f32(wrow[c]);
         if (pre != nullptr) {
-            v = v / __ldg(pre + c);
+            v = v / ld_f32(pre + c);
         }
         qw[row * d_in + c] = (int8_t)f32_to_s8(v / s);
     }

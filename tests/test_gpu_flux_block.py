@@ -113,6 +113,21 @@ def test_double_block_against_oracle(level, B, S, E):
     op.reload_model_from_state_dict(prefix, sd, "cuda")
     out_i, out_t = op.forward(cu(hidden), cu(encoder), cu(rope), cu(temb))
     check_status()
+    # the loaded weights: e4m3 codes times the amax / 448 scale give the 16-bit weight back to within half an e4m3 step
+    for stream in ("img", "txt"):
+        for name, key in (("qkv", "attn.to_qkv" if stream == "img" else "attn.to_added_qkv"),
+                          ("out", "attn.to_out.0" if stream == "img" else "attn.to_add_out"),
+                          ("ff1", ("ff" if stream == "img" else "ff_context") + ".net.0.proj"),
+                          ("ff2", ("ff" if stream == "img" else "ff_context") + ".net.2")):
+            w = op._w[stream][name]
+            ref = sd[prefix + key + ".weight"].float()
+            assert abs(float(w.w_scale) / (float(ref.abs().max()) / 448.0) - 1.0) < 1e-6, (stream, name, float(w.w_scale))
+            deq = w.qweight.cpu().view(torch.float8_e4m3fn).float() * float(w.w_scale)
+            assert float((deq - ref).abs().max()) <= 0.07 * float(ref.abs().max()), (stream, name)
+            assert float(w.input_scale) == float(sd[prefix + key + "_input_scale"]), (stream, name)
+    # the same call gives the same bits
+    again_i, again_t = op.forward(cu(hidden), cu(encoder), cu(rope), cu(temb))
+    assert torch.equal(again_i, out_i) and torch.equal(again_t, out_t), "two forwards of one block differ"
     want_i, want_t = blocks.flux_double_block(hidden, encoder, rope, temb, sd, prefix, heads, head_dim, level)
     for got, want, x in ((out_i, want_i, hidden), (out_t, want_t, encoder)):
         assert tuple(got.shape) == tuple(x.shape) and got.dtype == torch.bfloat16

@@ -107,6 +107,27 @@ def test_fp8_weight_quant_in_one_call(ops, dtype):
     assert_bit_equal(q, quant.fp8_quant(w, want_s, invert_scale=True))
 
 
+def test_fp8_weight_quant_reads_its_scale_after_the_amax_kernel(ops):
+    """The cast of lyraq_weight_quant_fp8 may start while the amax kernel in front of it still runs (programmatic
+    dependent launch) and must read the scale only once that kernel has finished; an early read sees the zero the scale
+    was reset to (every code saturates) or a partial maximum.  The window is narrow and depends on launch timing, so this
+    loops over weights of several sizes copied from the host, as loading a model does."""
+    g = torch.Generator().manual_seed(16)
+    shapes = [(256, 256), (768, 256), (1536, 256), (256, 1024), (4096, 4096)]
+    for i in range(60):
+        n, k = shapes[i % len(shapes)]
+        wi = cu((torch.randn(n, k, generator=g) * 0.02 * (0.5 + i % 7)).bfloat16())
+        s = torch.full((1,), 1e30, dtype=torch.float32, device="cuda")
+        q = torch.empty(n, k, dtype=torch.uint8, device="cuda")
+        ops.weight_quant_fp8(q, s, wi)
+        amax = float(wi.float().abs().max())
+        assert abs(float(s) * 448.0 / amax - 1.0) < 1e-6
+        codes = q.view(torch.float8_e4m3fn).float()
+        assert float((codes.abs() >= 448.0).float().mean()) < 1e-2, "iteration %d: codes saturated" % i
+        assert float((codes * float(s) - wi.float()).abs().max()) <= 0.07 * amax
+    check_status()
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("m,k", [(1, 64), (24, 128), (130, 3072), (5, 12288)])
 def test_int4_g64_quant_bit_exact(ops, dtype, m, k):
