@@ -418,3 +418,43 @@ def test_double_block_reload_from_bin(tmp_path, level):
     b.reload_model_from_bin(base, "fp32")
     for u, v in zip(a.forward(hidden, encoder, rope, temb), b.forward(hidden, encoder, rope, temb)):
         assert torch.equal(u, v)
+
+
+def _poison_free_memory():
+    """Fill what the caching allocator will hand out next with NaN patterns, so that a kernel that reads a buffer before
+    anything wrote it shows up in the result."""
+    torch.cuda.synchronize()
+    junk = [torch.full((256 * 1024,), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(64)]
+    junk += [torch.full((n,), float("nan"), dtype=torch.bfloat16, device="cuda")
+             for n in (600000, 900000, 1500000, 3000000, 32 * 1024 * 1024) for _ in range(4)]
+    torch.cuda.synchronize()
+    del junk
+
+
+@pytest.mark.parametrize("level", [1, 8])
+def test_blocks_do_not_read_uninitialised_buffers(level):
+    from lyradiff_b200 import flux_blocks
+    D, heads, head_dim, B, S, E = 256, 2, 128, 2, 96, 40
+    g = torch.Generator().manual_seed(5 + level)
+    int4 = level == 8
+    sd_s = _int4_state_dict("s.", D, 4, head_dim, level, g) if int4 else _state_dict("s.", D, 4, head_dim, level, g)
+    sd_d = _int4_double_state_dict("d.", D, head_dim, level, g) if int4 else _double_state_dict("d.", D, head_dim, level, g)
+    hidden, rope_s, temb = _block_inputs(B, S, D, head_dim, g)
+    encoder = cu(torch.randn(B, E, D, generator=g).bfloat16())
+    ang = torch.rand(B, E + S, head_dim // 2, generator=g) * 6.28
+    rope_d = cu(torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+        B, E + S, head_dim // 2, 2, 2).bfloat16())
+    single = flux_blocks.FluxSingleTransformerBlockOp("bf16", D, heads, head_dim, 4, level)
+    single.reload_model_from_state_dict("s.", sd_s, "cuda")
+    double = flux_blocks.FluxTransformerBlockOp("bf16", D, heads, head_dim, 6, level)
+    double.reload_model_from_state_dict("d.", sd_d, "cuda")
+    want_s = single.forward(hidden, rope_s, temb).clone()
+    want_d = [t.clone() for t in double.forward(hidden, encoder, rope_d, temb)]
+    single._buf = {}
+    _poison_free_memory()
+    got_s = single.forward(hidden, rope_s, temb)
+    assert torch.equal(got_s, want_s)
+    _poison_free_memory()
+    got_d = double.forward(hidden, encoder, rope_d, temb)
+    assert torch.equal(got_d[0], want_d[0]) and torch.equal(got_d[1], want_d[1])
+    check_status()
