@@ -580,13 +580,25 @@ int4_g64_kernel(uint32_t* q, ST* q_scale, const T* x, const float* smooth, size_
         }
         const float s = amax / 7.0f;
         uint32_t    w = 0;
+        if (s > 0.0f && s <= 3.0e38f) {
+            // q = rne(fl(v / s)) without a division or a conversion per element: |v / s| <= 7 (1 + 2^-23), so the exact
+            // int8 form applies (reciprocal multiply, magic-number rounding, tie check with the IEEE divide as its
+            // fallback); the nibbles are the low halves of its eight bytes
+            const float2 vp[4] = {make_float2(v[0], v[1]), make_float2(v[2], v[3]), make_float2(v[4], v[5]), make_float2(v[6], v[7])};
+            uint32_t     w0, w1;
+            quant8_s8_inrange(vp, s, 1.0f / s, w0, w1);
+            w0 &= 0x0F0F0F0Fu;
+            w1 &= 0x0F0F0F0Fu;
+            w = __byte_perm(w0 | (w0 >> 4), w1 | (w1 >> 4), 0x6420);
+        } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            int qi;
-            // v/s with s == 0 is NaN (or inf); cvt.rni.s32.f32 maps NaN to 0 exactly as the reference's does.
-            asm("cvt.rni.s32.f32 %0, %1;" : "=r"(qi) : "f"(v[j] / s));
-            qi = max(-8, min(7, qi));
-            w |= (uint32_t)(qi & 0xf) << (4 * j);
+            for (int j = 0; j < 8; ++j) {
+                int qi;
+                // v/s with s == 0 is NaN (or inf); cvt.rni.s32.f32 maps NaN to 0 exactly as the reference's does.
+                asm("cvt.rni.s32.f32 %0, %1;" : "=r"(qi) : "f"(v[j] / s));
+                qi = max(-8, min(7, qi));
+                w |= (uint32_t)(qi & 0xf) << (4 * j);
+            }
         }
         if (live) {
             q[vi] = w;
