@@ -193,6 +193,13 @@ inline void invokeFusedGateAndResidual(T* out, const T* input, const T* gate, co
                         "invokeFusedGateAndResidual");
 }
 
+/* src/lyradiff/kernels/lora/load_lora.h:9-10 (kernel load_lora.cu:6-14): dst += src * T(alpha) in T arithmetic. */
+template<typename T>
+inline void invokeLoadLora(T* dst, const T* src, size_t size, float alpha, cudaStream_t stream = 0)
+{
+    lyraq_detail::check(lyraq_load_lora(dst, src, lyraq_detail::DType<T>::value, alpha, size, stream), "invokeLoadLora");
+}
+
 /* src/lyradiff/kernels/w4a4_gemm/w4a4_gemm.h:6-17.  A is bf16 [m,k]; B (lora_down) bf16 [32,k]; n is the LoRA rank. */
 inline void invokeFusedQuantizeAndLoraDownSimple(float* Cptr, uint32_t* quantized_input, float* quantized_scale,
                                                  const void* Aptr, const void* Bptr, const float* Smoothptr, int m, int n,

@@ -20,6 +20,7 @@ void flux_fp8_call_sites(__nv_fp8_e4m3* q8, __nv_bfloat16* b, const float* f, fl
 {
     invokeCudaD2DScaleCpyConvert<__nv_bfloat16, __nv_fp8_e4m3>(q8, b, f, true, 4608 * 3072, s);
     invokeGetFP8WeightScale<__nv_bfloat16>(fo, b, 9216 * 3072, s);
+    invokeLoadLora<__nv_bfloat16>(b, b, 9216 * 3072, 0.8f, s);                         // IFLoraWeight.h:108
     invokeLayerNormWithShiftAndScale<__nv_bfloat16>(b, b, b, b, 1, 4608, 3072, s);
     invokeLayerNormWithShiftAndScaleFp8O<__nv_bfloat16>(q8, f, nullptr, b, b, b, 1, 4608, 3072, s);
     invokeFusedRmsNormAndRope<__nv_bfloat16>(b, b, b, b, 1e-6f, 1, 4608, 24, 128, s);   // FluxSingleAttentionFP8Processor.cc:183
