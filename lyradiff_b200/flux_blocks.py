@@ -211,6 +211,9 @@ class FluxSingleTransformerBlockOp:
         reload_model_from_state_dict, 16-bit tensors stored as `dtype` ("fp32" or "fp16"), scales as fp32, packed int4
         weights as int8 (FluxSingleTransformerFP8BlockWeight.cc:97-121, FluxSingleTransformerInt4BlockWeight.cc:70-84).
         `path` is a prefix, e.g. ".../single_transformer_blocks.0."; the weights go to the current CUDA device."""
+        self.reload_model_from_state_dict("", _state_dict_from_bin(path, dtype, self._bin_files()), "cuda")
+
+    def _bin_files(self):
         D, m = self.dim, self.mlp_scale
         full = self.quant_level in (FP8_W8A8_FULL, INT4_W4A4_FULL)
         files = _modulation_files("norm.linear", 3, D, full)
@@ -222,7 +225,7 @@ class FluxSingleTransformerBlockOp:
         else:
             files += _fp8_linear_files("attn.to_qkv", 3 * D, D) + _fp8_linear_files("proj_mlp", m * D, D)
             files += _fp8_linear_files("proj_out", D, (m + 1) * D)
-        self.reload_model_from_state_dict("", _state_dict_from_bin(path, dtype, files), "cuda")
+        return files
 
     def _lora_table(self):
         """Names as the reference's lora_layer_map / lora_weight_map nest them (FluxSingleTransformerFP8BlockWeight.cc:33,80-89,
@@ -439,6 +442,9 @@ class FluxTransformerBlockOp:
     def reload_model_from_bin(self, path, dtype):
         """FluxTransformer*BlockWeight<T>::loadWeights (FluxTransformerFP8BlockWeight.cc:84-100,
         FluxTransformerInt4BlockWeight.cc:78-91): `<path><key>.bin` per tensor, keys as in reload_model_from_state_dict."""
+        self.reload_model_from_state_dict("", _state_dict_from_bin(path, dtype, self._bin_files()), "cuda")
+
+    def _bin_files(self):
         D = self.dim
         int4 = self.quant_level in (INT4_W4A4, INT4_W4A4_FULL)
         files = []
@@ -451,7 +457,7 @@ class FluxTransformerBlockOp:
             else:
                 files += _fp8_linear_files(qkv, 3 * D, D) + _fp8_linear_files(out, D, D) + _fp8_linear_files(ff + ".net.0.proj", 4 * D, D)
             files += _fp8_linear_files(ff + ".net.2", D, 4 * D)
-        self.reload_model_from_state_dict("", _state_dict_from_bin(path, dtype, files), "cuda")
+        return files
 
     def _lora_table(self):
         """FluxTransformerFP8BlockWeight.cc:41-45, FluxAttentionFP8ProcessorWeight.cc:91-108,

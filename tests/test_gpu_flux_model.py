@@ -1,0 +1,107 @@
+"""GPU test of the whole-model mirror (lyradiff_b200.flux_model.FluxTransformer2DModelOp) against the CPU oracle on a small
+configuration: two double-stream and two single-stream blocks between the embedders and the output projection."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import model as omodel
+from tests.test_gpu_flux_block import _double_state_dict, _int4_double_state_dict, _int4_state_dict, _state_dict, _write_bins
+from tests.util import check_status, cu
+
+pytestmark = pytest.mark.gpu
+
+D, HEADS, HD, IN_CH, JOINT, POOLED, NL, NS = 256, 2, 128, 16, 64, 32, 2, 2
+
+
+def _model_state_dict(level, g):
+    sd = {}
+    int4 = level in (7, 8)
+    for i in range(NL):
+        p = "transformer_blocks.%d." % i
+        sd.update(_int4_double_state_dict(p, D, HD, level, g) if int4 else _double_state_dict(p, D, HD, level, g))
+    for j in range(NS):
+        p = "single_transformer_blocks.%d." % j
+        sd.update(_int4_state_dict(p, D, 4, HD, level, g) if int4 else _state_dict(p, D, 4, HD, level, g))
+
+    def lin(name, n, k, std=0.05):
+        sd[name + ".weight"] = (torch.randn(n, k, generator=g) * std).bfloat16()
+        sd[name + ".bias"] = (torch.randn(n, generator=g) * 0.02).bfloat16()
+
+    lin("x_embedder", D, IN_CH, 0.2)
+    lin("context_embedder", D, JOINT, 0.1)
+    lin("proj_out", IN_CH, D, 0.05)
+    lin("norm_out.linear", 2 * D, D, 0.03)
+    for name, d_in in (("timestep_embedder", 256), ("guidance_embedder", 256), ("text_embedder", POOLED)):
+        lin("time_text_embed.%s.linear_1" % name, D, d_in, 0.05)
+        lin("time_text_embed.%s.linear_2" % name, D, D, 0.05)
+    return sd
+
+
+def _inputs(B, S, E, g):
+    hidden = torch.randn(B, S, IN_CH, generator=g).bfloat16()
+    encoder = torch.randn(B, E, JOINT, generator=g).bfloat16()
+    pooled = torch.randn(B, POOLED, generator=g).bfloat16()
+    ang = torch.rand(B, E + S, HD // 2, generator=g) * 6.28
+    rope = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).reshape(
+        B, E + S, HD // 2, 2, 2).bfloat16()
+    return hidden, encoder, rope, pooled
+
+
+def _op(level):
+    from lyradiff_b200 import flux_blocks, flux_model
+    op = flux_model.FluxTransformer2DModelOp("bf16", IN_CH, NL, NS, HD, HEADS, POOLED, JOINT, True, level)
+    op.initialize(flux_blocks.LyraDiffCommonContext())
+    return op
+
+
+@pytest.mark.parametrize("level", [1, 2, 8])
+def test_model_against_oracle(level):
+    g = torch.Generator().manual_seed(200 + level)
+    sd = _model_state_dict(level, g)
+    hidden, encoder, rope, pooled = _inputs(1, 64, 32, g)
+    op = _op(level)
+    op.reload_transformer_model_from_state_dict(sd, "cuda")
+    got = op.transformer_forward(cu(hidden), cu(encoder), cu(rope), cu(pooled), 500.0, 3.5)
+    check_status()
+    assert tuple(got.shape) == (1, 64, IN_CH) and got.dtype == torch.bfloat16
+    want = omodel.flux_model(hidden, encoder, rope, pooled, 500.0, 3.5, sd, NL, NS, HEADS, HD, level).float()
+    err = (got.cpu().float() - want).abs()
+    amp = float(want.abs().mean())
+    assert amp > 0.05
+    assert float(err.mean()) <= 0.04 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
+    assert float(err.max()) <= 0.3 * float(want.abs().max())
+
+
+def test_controlnet_residuals_bin_loading_and_lora(tmp_path):
+    g = torch.Generator().manual_seed(300)
+    sd = _model_state_dict(1, g)
+    hidden, encoder, rope, pooled = _inputs(1, 64, 32, g)
+    op = _op(1)
+    op.reload_transformer_model_from_state_dict(sd, "cuda")
+    args = (cu(hidden), cu(encoder), cu(rope), cu(pooled), 250.0, 2.0)
+    base = op.transformer_forward(*args).clone()
+
+    # ControlNet residual on the image stream after each double block
+    res = [(torch.randn(1, 64, D, generator=g) * 0.1).bfloat16()]
+    got = op.transformer_forward(*args, [cu(res[0])], None, False)
+    want = omodel.flux_model(hidden, encoder, rope, pooled, 250.0, 2.0, sd, NL, NS, HEADS, HD, 1, controlnet_block_samples=res).float()
+    err = (got.cpu().float() - want).abs()
+    assert float(err.mean()) <= 0.04 * float(want.abs().mean()) and not torch.equal(got, base)
+    with pytest.raises(RuntimeError):
+        op.transformer_forward(*args, None, [cu(res[0])], False)
+
+    # the raw .bin layout gives the same bits as the state dict
+    _write_bins(str(tmp_path) + "/", sd, "", np.float32)
+    op2 = _op(1)
+    op2.reload_transformer_model(str(tmp_path), "fp32")
+    assert torch.equal(op2.transformer_forward(*args), base)
+
+    # LoRA hot-swap through the model's name table, and back
+    op.load_lora_by_name(["single_transformer_blocks_1", "proj_mlp"], cu((torch.randn(4 * D, D, generator=g) * 0.02).bfloat16()), 1.0)
+    op.load_lora_by_name(["time_text_embed", "text_embedder", "linear_2"], cu((torch.randn(D, D, generator=g) * 0.02).bfloat16()), 1.0)
+    op.load_lora_by_name(["proj_out"], cu((torch.randn(IN_CH, D, generator=g) * 0.02).bfloat16()), 1.0)
+    assert not torch.equal(op.transformer_forward(*args), base)
+    op.clear_lora()
+    assert torch.equal(op.transformer_forward(*args), base)
+    check_status()

@@ -119,3 +119,15 @@ def test_int4_block_oracle_zero_gate_returns_the_input():
     sd[p + "norm.linear.bias"] = torch.cat([torch.zeros(2 * D), torch.ones(D)]).bfloat16()   # gate 1
     out1, mid1 = blocks.flux_single_block_int4(hidden, rope, temb, sd, p, heads, hd, 4, 7)
     assert torch.equal(out1, (mid1["h"].reshape(1, 12, D).float() + hidden.float()).bfloat16())
+
+
+def test_time_projection_is_the_sinusoidal_embedding_with_the_cosine_half_first():
+    import math
+    from oracle import model
+    e = model.time_projection(500.0, 256, torch.float32)
+    assert tuple(e.shape) == (1, 256)
+    # channel 0: frequency 1 -> cos(t), sin(t); the last channel: frequency max_period^-(127/128)
+    assert abs(float(e[0, 0]) - math.cos(500.0)) < 1e-4 and abs(float(e[0, 128]) - math.sin(500.0)) < 1e-4
+    w = math.exp(-math.log(10000.0) * 127 / 128)
+    assert abs(float(e[0, 127]) - math.cos(500.0 * w)) < 1e-4 and abs(float(e[0, 255]) - math.sin(500.0 * w)) < 1e-4
+    assert float((e[0, :128] ** 2 + e[0, 128:] ** 2 - 1.0).abs().max()) < 1e-5
