@@ -298,6 +298,15 @@ void modulation_files(std::vector<BinFile>& v, const std::string& name, int64_t 
     }
 }
 
+// The `device` argument of reload_model_from_state_dict says where the state dict's tensors live ("cpu" or "cuda...": the
+// reference picks the memcpy kind from it, FluxSingleTransformerBlockOp.h:261-264, and its Python wrappers pass "cpu"); the
+// weights always go to the current CUDA device.
+at::Device target_device(const std::string& device)
+{
+    TORCH_CHECK(device == "cpu" || device.rfind("cuda", 0) == 0, "device must be 'cpu' or 'cuda[:n]' (where the state dict's tensors are)");
+    return at::Device(at::kCUDA, at::cuda::current_device());
+}
+
 void check_inputs(std::initializer_list<Tensor> ts, at::ScalarType dt)
 {
     for (const Tensor& t : ts) {
@@ -437,7 +446,7 @@ struct FluxSingleTransformerBlockOp: BlockBase {
 
     void load_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device) override
     {
-        const at::Device dev(device);
+        const at::Device dev = target_device(device);
         auto g = [&](const std::string& n) { return sd.at(prefix + n); };
         const bool fp8_modulation = quant_level == 2 || quant_level == 8;
         if (int4()) {
@@ -609,7 +618,7 @@ struct FluxTransformerBlockOp: BlockBase {
 
     void load_state_dict(const std::string& prefix, const c10::Dict<std::string, Tensor>& sd, const std::string& device) override
     {
-        const at::Device dev(device);
+        const at::Device dev = target_device(device);
         load_stream(img, prefix, sd, dev, "norm1", "attn.to_qkv", "attn.to_out.0", "attn.norm_q.weight", "attn.norm_k.weight", "ff");
         load_stream(txt, prefix, sd, dev, "norm1_context", "attn.to_added_qkv", "attn.to_add_out", "attn.norm_added_q.weight",
                     "attn.norm_added_k.weight", "ff_context");

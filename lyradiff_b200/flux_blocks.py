@@ -110,6 +110,15 @@ class _Linear16:
             self.loaded_lora = False
 
 
+def _target_device(device):
+    """`device` of reload_model_from_state_dict says where the state-dict tensors LIVE ("cpu" or "cuda...": the reference
+    picks the memcpy kind from it, FluxSingleTransformerBlockOp.h:261-264, and its Python wrappers pass "cpu"); the weights
+    always go to the current CUDA device.  torch knows where each tensor is, so the argument is only validated."""
+    if not (isinstance(device, str) and (device == "cpu" or device.startswith("cuda"))):
+        raise RuntimeError("device must be 'cpu' or 'cuda[:n]' (where the state dict's tensors are)")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
 def _load_lora_by_name(table, names, weight, scale):
     """IFLoraWeight<T>::loadLoraByName (IFLoraWeight.h:150-173): walk the nested name table; a name that leads nowhere is
     reported and skipped, as the reference does."""
@@ -254,7 +263,7 @@ class FluxSingleTransformerBlockOp:
         `<prefix>proj_mlp.{weight,bias}`, `<prefix>proj_out.{weight,bias}` and the fp32 scalars
         `<prefix>attn.to_qkv_input_scale`, `<prefix>proj_mlp_input_scale`, `<prefix>proj_out_input_scale`
         (plus `<prefix>norm.linear_input_scale` at quant_level 2).  Host or device tensors; weights are quantized here."""
-        dev = torch.device(device)
+        dev = _target_device(device)
         sd = state_dict
         g = lambda name: sd[prefix + name]
         w = {}
@@ -484,7 +493,7 @@ class FluxTransformerBlockOp:
         `norm1[_context].linear`, `attn.to_qkv | attn.to_added_qkv`, `attn.to_out.0 | attn.to_add_out`,
         `attn.norm_q, norm_k | attn.norm_added_q, norm_added_k`, `ff[_context].net.0.proj`, `ff[_context].net.2`; every
         quantized linear X has X.weight, X.bias and the fp32 scalar X_input_scale."""
-        dev = torch.device(device)
+        dev = _target_device(device)
         g = lambda name: state_dict[prefix + name]
 
         def lin(name):

@@ -87,7 +87,7 @@ class FluxTransformer2DModelOp:
         `x_embedder`, `context_embedder`, `proj_out` (.weight / .bias), `time_text_embed.{timestep,guidance,text}_embedder.
         linear_{1,2}`, `norm_out.linear`, `transformer_blocks.<i>.*` and `single_transformer_blocks.<j>.*` as the block classes
         read them."""
-        dev, dt, sd = torch.device(device), self.dtype, weights
+        dev, dt, sd = flux_blocks._target_device(device), self.dtype, weights
         w = {name: _Linear16(sd[name + ".weight"], sd[name + ".bias"], dev, dt) for name in ("x_embedder", "context_embedder", "proj_out")}
         for name in ("timestep_embedder", "guidance_embedder", "text_embedder"):
             w[name] = _Mlp16(sd, "time_text_embed." + name + ".", dev, dt)

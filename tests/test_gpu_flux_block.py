@@ -458,3 +458,24 @@ def test_blocks_do_not_read_uninitialised_buffers(level):
     got_d = double.forward(hidden, encoder, rope_d, temb)
     assert torch.equal(got_d[0], want_d[0]) and torch.equal(got_d[1], want_d[1])
     check_status()
+
+
+def test_device_argument_names_where_the_state_dict_lives():
+    """The reference's wrappers pass "cpu" with host tensors (lyradiff_flux_transformer_model_v2.py:113,159); "cuda" means the
+    tensors are already on the device.  Either way the weights end up on the GPU and give the same bits."""
+    from lyradiff_b200 import flux_blocks, torch_classes
+    D, heads, head_dim = 256, 2, 128
+    g = torch.Generator().manual_seed(81)
+    prefix = "single_transformer_blocks.0."
+    sd = _state_dict(prefix, D, 4, head_dim, 2, g)
+    x = _block_inputs(1, 64, D, head_dim, g)
+    outs = []
+    for cls in (flux_blocks.FluxSingleTransformerBlockOp, torch_classes.load().FluxSingleTransformerBlockOp):
+        a = cls("bf16", D, heads, head_dim, 4, 2)
+        a.reload_model_from_state_dict(prefix, sd, "cpu")
+        b = cls("bf16", D, heads, head_dim, 4, 2)
+        b.reload_model_from_state_dict(prefix, {k: v.cuda() for k, v in sd.items()}, "cuda:0")
+        outs += [a.forward(*x), b.forward(*x)]
+        with pytest.raises(RuntimeError):
+            cls("bf16", D, heads, head_dim, 4, 2).reload_model_from_state_dict(prefix, sd, "tpu")
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
