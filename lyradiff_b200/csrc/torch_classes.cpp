@@ -3,6 +3,9 @@
 //   torch.classes.lyradiff.FluxSingleTransformerBlockOp(inference_dtype, embedding_dim, embedding_head_num,
 //                                                       embedding_head_dim, mlp_scale, quant_level)
 //   torch.classes.lyradiff.FluxTransformerBlockOp(... same ...)
+//   torch.classes.lyradiff.FluxTransformer2DModelOp(inference_dtype, input_channels, num_layers, num_single_layers,
+//                                                   attention_head_dim, num_attention_heads, pooled_projection_dim,
+//                                                   joint_attention_dim, guidance_embeds, quant_level)
 // with initialize / forward / reload_model_from_state_dict / reload_model_from_bin / load_lora_by_name / clear_lora.
 // quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4; the double-stream block keeps net.2 in FP8, as the reference does).
 // Host code only: every device operation is a call into the C ABI of liblyraq.so (include/lyraq.h) on torch's current
@@ -13,6 +16,7 @@
 #include <torch/custom_class.h>
 #include <torch/script.h>
 
+#include <cmath>
 #include <cstdio>
 #include <map>
 #include <mutex>
@@ -720,6 +724,269 @@ struct FluxTransformerBlockOp: BlockBase {
     }
 };
 
+// ---------------------------------------------------------------------------------------------------------------------
+// FluxTransformer2DModelOp (th_op/pybind.cc:13-44, th_op/flux_transformer_2d_model/FluxTransformer2DModelOp.cc:65-154):
+// FluxTransformer2DModel<T>::transformer_forward (models/flux_transformer_2d_model/FluxTransformer2DModel.cc:230-515).  The
+// quantized blocks are the classes above; what the reference runs in 16 bits through cuBLAS (the three small embedders,
+// x_embedder, context_embedder, norm_out.linear, proj_out) runs through ATen matmuls, library code on both sides.
+struct Linear16: LoraTarget {
+    Tensor         w, b, weight_h;
+    at::ScalarType dt = at::kBFloat16;
+    bool           loaded_lora = false;
+
+    void load(const c10::Dict<std::string, Tensor>& sd, const std::string& name, const at::Device& dev, at::ScalarType dt_)
+    {
+        dt          = dt_;
+        w           = sd.at(name + ".weight").to(dev, dt).contiguous();
+        b           = sd.at(name + ".bias").to(dev, dt).contiguous();
+        weight_h    = w.to(at::kCPU);
+        loaded_lora = false;
+    }
+    Tensor run(const Tensor& x) const { return at::addmm(b, x, w.t()); }
+    void   load_lora(const Tensor& lora, double scale) override
+    {
+        w.copy_(weight_h);
+        merge_lora(w, lora, scale, dt);
+        loaded_lora = true;
+    }
+    void clear_lora() override
+    {
+        if (loaded_lora) {
+            w.copy_(weight_h);
+            loaded_lora = false;
+        }
+    }
+};
+
+// TimestepEmbeddingBlock<T>::forward (layers/timestep_embedding_block/TimestepEmbeddingBlock.cc): linear_1 -> T(h + bias)
+// -> SiLU -> linear_2 + bias
+struct Mlp16 {
+    Linear16 l1, l2;
+    void load(const c10::Dict<std::string, Tensor>& sd, const std::string& prefix, const at::Device& dev, at::ScalarType dt)
+    {
+        l1.load(sd, prefix + "linear_1", dev, dt);
+        l2.load(sd, prefix + "linear_2", dev, dt);
+    }
+    Tensor run(const Tensor& x) const { return l2.run(at::silu(at::matmul(x, l1.w.t()) + l1.b)); }
+};
+
+struct FluxTransformer2DModelOp: torch::CustomClassHolder {
+    at::ScalarType dtype;
+    int64_t        in_ch, n_double, n_single, head_dim, heads, dim, pooled_dim, joint_dim, quant_level;
+    bool           loaded = false;
+    std::mutex     lock;
+    std::vector<c10::intrusive_ptr<FluxTransformerBlockOp>>       dbl;
+    std::vector<c10::intrusive_ptr<FluxSingleTransformerBlockOp>> sgl;
+    Linear16 x_embedder, context_embedder, proj_out, norm_out;
+    Mlp16    timestep_embedder, guidance_embedder, text_embedder;
+
+    FluxTransformer2DModelOp(const std::string& inference_dtype, int64_t input_channels, int64_t num_layers,
+                             int64_t num_single_layers, int64_t attention_head_dim, int64_t num_attention_heads,
+                             int64_t pooled_projection_dim, int64_t joint_attention_dim, bool guidance_embeds, int64_t quant_level_):
+        dtype(parse_dtype(inference_dtype)), in_ch(input_channels), n_double(num_layers), n_single(num_single_layers),
+        head_dim(attention_head_dim), heads(num_attention_heads), dim(attention_head_dim * num_attention_heads),
+        pooled_dim(pooled_projection_dim), joint_dim(joint_attention_dim), quant_level(quant_level_)
+    {
+        TORCH_CHECK(guidance_embeds, "the model is built with the guidance embedder, as the reference's C++ model is");
+        for (int64_t i = 0; i < n_double; ++i) {
+            dbl.push_back(c10::make_intrusive<FluxTransformerBlockOp>(inference_dtype, dim, heads, head_dim, 6, quant_level));
+        }
+        for (int64_t i = 0; i < n_single; ++i) {
+            sgl.push_back(c10::make_intrusive<FluxSingleTransformerBlockOp>(inference_dtype, dim, heads, head_dim, 4, quant_level));
+        }
+    }
+
+    void initialize(const c10::intrusive_ptr<LyraDiffCommonContext>&) {}
+
+    void load(const c10::Dict<std::string, Tensor>& sd, const std::string& device)
+    {
+        const at::Device dev = target_device(device);
+        x_embedder.load(sd, "x_embedder", dev, dtype);
+        context_embedder.load(sd, "context_embedder", dev, dtype);
+        proj_out.load(sd, "proj_out", dev, dtype);
+        norm_out.load(sd, "norm_out.linear", dev, dtype);
+        timestep_embedder.load(sd, "time_text_embed.timestep_embedder.", dev, dtype);
+        guidance_embedder.load(sd, "time_text_embed.guidance_embedder.", dev, dtype);
+        text_embedder.load(sd, "time_text_embed.text_embedder.", dev, dtype);
+        for (int64_t i = 0; i < n_double; ++i) {
+            dbl[i]->reload_model_from_state_dict("transformer_blocks." + std::to_string(i) + ".", sd, device);
+        }
+        for (int64_t i = 0; i < n_single; ++i) {
+            sgl[i]->reload_model_from_state_dict("single_transformer_blocks." + std::to_string(i) + ".", sd, device);
+        }
+        loaded = true;
+    }
+
+    // keys of FluxTransformer2DModelWeight<T>::loadWeightsFromCache (FluxTransformer2DModelWeight.cc:297-337)
+    void reload_transformer_model_from_state_dict(const c10::Dict<std::string, Tensor>& weights, const std::string& device)
+    {
+        std::lock_guard<std::mutex> g(lock);
+        load(weights, device);
+    }
+
+    // FluxTransformer2DModelWeight<T>::loadWeights (FluxTransformer2DModelWeight.cc:239-275): raw `<model_path><key>.bin` files
+    void reload_transformer_model(const std::string& model_path, const std::string& model_dtype)
+    {
+        TORCH_CHECK(model_dtype == "fp32" || model_dtype == "fp16", "wrong model_dtype");
+        std::string path = model_path;
+        if (!path.empty() && path.back() != '/') {
+            path += "/";
+        }
+        std::vector<BinFile> files;
+        auto lin = [&](const std::string& name, int64_t n, int64_t k) {
+            files.push_back({name + ".weight", {n, k}, 'T'});
+            files.push_back({name + ".bias", {n}, 'T'});
+        };
+        lin("x_embedder", dim, in_ch);
+        lin("context_embedder", dim, joint_dim);
+        lin("proj_out", in_ch, dim);
+        lin("norm_out.linear", 2 * dim, dim);
+        for (const char* e : {"timestep_embedder", "guidance_embedder", "text_embedder"}) {
+            const std::string p = std::string("time_text_embed.") + e + ".";
+            lin(p + "linear_1", dim, std::string(e) == "text_embedder" ? pooled_dim : 256);
+            lin(p + "linear_2", dim, dim);
+        }
+        for (int64_t i = 0; i < n_double; ++i) {
+            for (BinFile f : dbl[i]->bin_files()) {
+                f.key = "transformer_blocks." + std::to_string(i) + "." + f.key;
+                files.push_back(f);
+            }
+        }
+        for (int64_t i = 0; i < n_single; ++i) {
+            for (BinFile f : sgl[i]->bin_files()) {
+                f.key = "single_transformer_blocks." + std::to_string(i) + "." + f.key;
+                files.push_back(f);
+            }
+        }
+        c10::Dict<std::string, Tensor> sd;
+        for (const BinFile& f : files) {
+            sd.insert(f.key, read_bin(path, f, model_dtype == "fp16"));
+        }
+        std::lock_guard<std::mutex> g(lock);
+        load(sd, "cpu");
+    }
+
+    // FluxTransformer2DModelWeight.cc:34-97,160-175: blocks under transformer_blocks_<i> / single_transformer_blocks_<j>, the
+    // embedders under time_text_embed, then norm_out, x_embedder, context_embedder, proj_out
+    std::map<std::string, LoraTarget*> lora_table()
+    {
+        std::map<std::string, LoraTarget*> t{{"x_embedder", &x_embedder}, {"context_embedder", &context_embedder},
+                                             {"proj_out", &proj_out}, {"norm_out/linear", &norm_out}};
+        auto mlp = [&](const std::string& name, Mlp16& m) {
+            t["time_text_embed/" + name + "/linear_1"] = &m.l1;
+            t["time_text_embed/" + name + "/linear_2"] = &m.l2;
+        };
+        mlp("timestep_embedder", timestep_embedder);
+        mlp("guidance_embedder", guidance_embedder);
+        mlp("text_embedder", text_embedder);
+        for (int64_t i = 0; i < n_double; ++i) {
+            for (auto& kv : dbl[i]->lora_table()) {
+                t["transformer_blocks_" + std::to_string(i) + "/" + kv.first] = kv.second;
+            }
+        }
+        for (int64_t i = 0; i < n_single; ++i) {
+            for (auto& kv : sgl[i]->lora_table()) {
+                t["single_transformer_blocks_" + std::to_string(i) + "/" + kv.first] = kv.second;
+            }
+        }
+        return t;
+    }
+
+    void load_lora_by_name(const std::vector<std::string>& names, const Tensor& weight, double scale)
+    {
+        TORCH_CHECK(loaded, "weights not loaded");
+        std::string key;
+        for (const std::string& n : names) {
+            key += (key.empty() ? "" : "/") + n;
+        }
+        std::lock_guard<std::mutex> g(lock);
+        auto                        table = lora_table();
+        auto                        it    = table.find(key);
+        if (it == table.end()) {
+            TORCH_WARN("lora name cannot find weights to load: ", key);
+            return;
+        }
+        it->second->load_lora(weight, scale);
+    }
+
+    void clear_lora()
+    {
+        TORCH_CHECK(loaded, "weights not loaded");
+        std::lock_guard<std::mutex> g(lock);
+        for (auto& kv : lora_table()) {
+            kv.second->clear_lora();
+        }
+    }
+
+    // TimeProjection<T>(256, flip_sin_to_cos = true, downscale_freq_shift = 0) (layers/time_proj/TimeProjection.cc:39-51, kernel
+    // kernels/time_proj/time_proj_kernels.cu:70-97): fp32 exponents from the host, fp32 sin / cos, cast to T, cosine half first
+    Tensor time_projection(double value, const at::Device& dev) const
+    {
+        constexpr int      half   = 128;
+        const float        factor = -std::log(10000.0f) / (float)half;
+        std::vector<float> arg(half);
+        for (int i = 0; i < half; ++i) {
+            arg[i] = std::exp(factor * (float)i) * (float)value;
+        }
+        Tensor a = at::from_blob(arg.data(), {half}, at::TensorOptions().dtype(at::kFloat)).to(dev);
+        return at::cat({at::cos(a), at::sin(a)}).to(dtype).reshape({1, 2 * half});
+    }
+
+    Tensor transformer_forward(const Tensor& hidden_states, const Tensor& encoder_hidden_states, const Tensor& rope_emb,
+                               const Tensor& pooled_projection, double timestep, double guidance,
+                               const c10::optional<std::vector<Tensor>>& controlnet_block_samples,
+                               const c10::optional<std::vector<Tensor>>& controlnet_single_block_samples,
+                               const c10::optional<bool>&                controlnet_blocks_repeat)
+    {
+        TORCH_CHECK(loaded, "weights not loaded");
+        check_inputs({hidden_states, encoder_hidden_states, rope_emb, pooled_projection}, dtype);
+        TORCH_CHECK(!controlnet_single_block_samples.has_value() || controlnet_single_block_samples->empty(),
+                    "controlnet_single_block_samples currently needs to be 0");  // FluxTransformer2DModel.cc:252
+        std::lock_guard<std::mutex> guard(lock);
+        const int64_t B = hidden_states.size(0), S = hidden_states.size(1), E = encoder_hidden_states.size(1);
+        const auto    dev = hidden_states.device();
+
+        // conditioning vector, SiLU'd as the blocks expect it (add3Tensor2dAndSilu: src1 + src2 + src3 in T, then SiLU)
+        Tensor t_emb = timestep_embedder.run(time_projection(timestep, dev));
+        Tensor g_emb = guidance_embedder.run(time_projection(guidance, dev));
+        Tensor p_emb = text_embedder.run(pooled_projection);
+        Tensor temb  = at::silu((p_emb + g_emb) + t_emb).contiguous();
+
+        Tensor h = x_embedder.run(hidden_states.view({B * S, in_ch})).view({B, S, dim});
+        Tensor c = context_embedder.run(encoder_hidden_states.view({B * E, joint_dim})).view({B, E, dim});
+
+        const std::vector<Tensor> samples = controlnet_block_samples.value_or(std::vector<Tensor>{});
+        const bool    repeat   = controlnet_blocks_repeat.value_or(false);
+        const int64_t interval = samples.empty() ? 0 : (n_double - 1) / (int64_t)samples.size() + 1;
+        for (int64_t i = 0; i < n_double; ++i) {
+            auto out = dbl[i]->forward(h, c, rope_emb, temb);
+            h        = out[0];
+            c        = out[1];
+            if (!samples.empty()) {
+                Tensor res = (repeat ? samples[i % (int64_t)samples.size()] : samples[i / interval]).contiguous();
+                TORCH_CHECK(res.numel() == h.numel() && res.scalar_type() == dtype && res.is_cuda(), "controlnet sample mismatch");
+                check(lyraq_load_lora(h.data_ptr(), res.data_ptr(), dt_code(dtype), 1.0f, (size_t)h.numel(), stream()),
+                      "lyraq_load_lora");  // the reference adds it with invokeLoadLora too (FluxTransformer2DModel.cc:389)
+            }
+        }
+        Tensor x = at::cat({c, h}, 1);
+        for (int64_t i = 0; i < n_single; ++i) {
+            x = sgl[i]->forward(x, rope_emb, temb);
+        }
+        h = x.slice(1, E, E + S).contiguous();
+
+        // norm_out: AdaLayerNorm<T>(dim, 2, switch_scale = true): scale first, then shift
+        Tensor msa    = norm_out.run(temb);
+        auto   parts  = msa.chunk(2, 1);
+        Tensor scale  = parts[0].contiguous(), shift = parts[1].contiguous();
+        Tensor normed = at::empty_like(h);
+        check(lyraq_adaln_quant(normed.data_ptr(), nullptr, nullptr, nullptr, nullptr, h.data_ptr(), scale.data_ptr(), shift.data_ptr(),
+                                dt_code(dtype), nullptr, (size_t)B, (size_t)S, (size_t)dim, 1e-6, stream()),
+              "lyraq_adaln_quant");
+        return proj_out.run(normed.view({B * S, dim})).view({B, S, in_ch});
+    }
+};
+
 // The shared methods live in BlockBase; they are bound through lambdas on the concrete class, since the class registry
 // takes `self` from the member pointer's class and BlockBase itself is not registered.
 template<class Op>
@@ -744,4 +1011,20 @@ TORCH_LIBRARY(lyradiff, m)
     m.class_<LyraDiffCommonContext>("LyraDiffCommonContext").def(torch::init<>());
     register_block<FluxSingleTransformerBlockOp>(m, "FluxSingleTransformerBlockOp");
     register_block<FluxTransformerBlockOp>(m, "FluxTransformerBlockOp");
+    m.class_<FluxTransformer2DModelOp>("FluxTransformer2DModelOp")
+        .def(torch::init<std::string, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, bool, int64_t>(), "init",
+             {torch::arg("inference_dtype") = "bf16", torch::arg("input_channels") = 64, torch::arg("num_layers") = 19,
+              torch::arg("num_single_layers") = 38, torch::arg("attention_head_dim") = 128, torch::arg("num_attention_heads") = 24,
+              torch::arg("pooled_projection_dim") = 768, torch::arg("joint_attention_dim") = 4096,
+              torch::arg("guidance_embeds") = true, torch::arg("quant_level") = 0})
+        .def("initialize", &FluxTransformer2DModelOp::initialize)
+        .def("transformer_forward", &FluxTransformer2DModelOp::transformer_forward, "transformer_forward",
+             {torch::arg("hidden_states"), torch::arg("encoder_hidden_states"), torch::arg("rope_emb"),
+              torch::arg("pooled_projection"), torch::arg("timestep"), torch::arg("guidance"),
+              torch::arg("controlnet_block_samples") = c10::nullopt, torch::arg("controlnet_single_block_samples") = c10::nullopt,
+              torch::arg("controlnet_blocks_repeat") = false})
+        .def("reload_transformer_model", &FluxTransformer2DModelOp::reload_transformer_model)
+        .def("load_lora_by_name", &FluxTransformer2DModelOp::load_lora_by_name)
+        .def("clear_lora", &FluxTransformer2DModelOp::clear_lora)
+        .def("reload_transformer_model_from_state_dict", &FluxTransformer2DModelOp::reload_transformer_model_from_state_dict);
 }

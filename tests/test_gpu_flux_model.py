@@ -105,3 +105,37 @@ def test_controlnet_residuals_bin_loading_and_lora(tmp_path):
     op.clear_lora()
     assert torch.equal(op.transformer_forward(*args), base)
     check_status()
+
+
+@pytest.mark.parametrize("level", [2, 7])
+def test_cpp_class_same_bits_as_mirror(tmp_path, level):
+    from lyradiff_b200 import torch_classes
+    ns = torch_classes.load()
+    g = torch.Generator().manual_seed(400 + level)
+    sd = _model_state_dict(level, g)
+    hidden, encoder, rope, pooled = _inputs(1, 64, 32, g)
+    args = (cu(hidden), cu(encoder), cu(rope), cu(pooled), 750.0, 4.0)
+    mirror = _op(level)
+    mirror.reload_transformer_model_from_state_dict(sd, "cpu")
+    want = mirror.transformer_forward(*args)
+    op = ns.FluxTransformer2DModelOp("bf16", IN_CH, NL, NS, HD, HEADS, POOLED, JOINT, True, level)
+    op.initialize(ns.LyraDiffCommonContext())
+    op.reload_transformer_model_from_state_dict(sd, "cpu")
+    got = op.transformer_forward(*args)
+    check_status()
+    assert torch.equal(got, want)
+    res = cu((torch.randn(1, 64, D, generator=g) * 0.1).bfloat16())
+    assert torch.equal(op.transformer_forward(*args, [res], None, True), mirror.transformer_forward(*args, [res], None, True))
+    if level == 2:
+        _write_bins(str(tmp_path) + "/", sd, "", np.float32)
+        op2 = ns.FluxTransformer2DModelOp("bf16", IN_CH, NL, NS, HD, HEADS, POOLED, JOINT, True, level)
+        op2.reload_transformer_model(str(tmp_path), "fp32")
+        assert torch.equal(op2.transformer_forward(*args), want)
+        lora = cu((torch.randn(D, D, generator=g) * 0.02).bfloat16())
+        for m in (op, mirror):
+            m.load_lora_by_name(["transformer_blocks_1", "attn", "to_out.0"], lora, 0.7)
+            m.load_lora_by_name(["time_text_embed", "guidance_embedder", "linear_2"], lora, 0.7)
+        swapped = op.transformer_forward(*args)
+        assert torch.equal(swapped, mirror.transformer_forward(*args)) and not torch.equal(swapped, want)
+        op.clear_lora()
+        assert torch.equal(op.transformer_forward(*args), want)

@@ -50,3 +50,22 @@ def test_missing_state_dict_key_raises(ns):
     op = ns.FluxSingleTransformerBlockOp("bf16", 256, 2, 128, 4, 1)
     with pytest.raises((RuntimeError, IndexError, KeyError)):
         op.reload_model_from_state_dict("p.", {"p.attn.to_qkv.weight": torch.zeros(768, 256)}, "cpu")
+
+
+def test_whole_model_class_is_registered_with_the_reference_defaults(ns):
+    op = ns.FluxTransformer2DModelOp("bf16", 16, 1, 1, 128, 2, 32, 64, True, 1)
+    op.initialize(ns.LyraDiffCommonContext())
+    for m in ("transformer_forward", "reload_transformer_model", "reload_transformer_model_from_state_dict", "load_lora_by_name",
+              "clear_lora"):
+        assert callable(getattr(op, m)), m
+    with pytest.raises(RuntimeError, match="weights not loaded"):
+        op.clear_lora()
+    with pytest.raises(RuntimeError, match="wrong model_dtype"):
+        op.reload_transformer_model("/nowhere", "bf16")
+    with pytest.raises(RuntimeError, match="weight file missing"):
+        op.reload_transformer_model("/nowhere", "fp32")
+    with pytest.raises(RuntimeError, match="guidance"):
+        ns.FluxTransformer2DModelOp("bf16", 16, 1, 1, 128, 2, 32, 64, False, 1)
+    # keyword construction with the defaults of th_op/pybind.cc:13-27 (quant_level 0 is not built here)
+    with pytest.raises(RuntimeError, match="quant_level"):
+        ns.FluxTransformer2DModelOp(num_layers=1, num_single_layers=1)
