@@ -554,89 +554,96 @@ class FluxBlockInt4(FluxBlock):
 
 
 class FluxForward(FluxBlock):
-    """configs[4] without the embedders: the FLUX.1-dev block stack, 19 double-stream + 38 single-stream blocks, every
-    block with its own random FP8 weights, one image (4096 image + 512 text tokens) per GPU."""
+    """configs[4]: the whole FLUX.1-dev transformer through lyradiff_b200.flux_model.FluxTransformer2DModelOp -- embedders,
+    19 double-stream + 38 single-stream blocks (each with its own random FP8 weights), norm_out and proj_out -- one image
+    (4096 image + 512 text tokens) per GPU."""
     name = "flux_forward"
-    metric = "flux_block_stack_throughput"
-    N_DOUBLE, N_SINGLE, TXT = 19, 38, 512
+    metric = "flux_transformer_forward_throughput"
+    N_DOUBLE, N_SINGLE, TXT, IN_CH, JOINT, POOLED = 19, 38, 512, 64, 4096, 768
 
     def __init__(self, tokens):
         FluxBlock.__init__(self, tokens)
         self.blocks = self.N_DOUBLE + self.N_SINGLE
+        S, D = self.tokens - self.TXT, self.D
+        outer = 2.0 * D * (S * self.IN_CH * 2 + self.TXT * self.JOINT)   # x_embedder, proj_out, context_embedder (16-bit, library)
         self.lin_flops *= self.blocks
         self.attn_flops *= self.blocks
-        self.work_per_step = self.lin_flops + self.attn_flops
-        self.workload = ("configs[4] block stack: FLUX.1-dev architecture, %d double-stream + %d single-stream blocks, FP8_W8A8, "
-                         "random weights (each block its own), 1 image per GPU = %d image + %d text tokens, hidden 3072, "
-                         "24 x 128 heads; one step = one pass through the stack = %.1f TFLOP (embedders and final layer left out); "
-                         "ms_per_step is the reference's denoising-step time for the stack"
-                         % (self.N_DOUBLE, self.N_SINGLE, self.tokens - self.TXT, self.TXT, self.work_per_step / 1e12))
-        self.launches_per_step = self.N_DOUBLE * 16 + self.N_SINGLE * 6
-        self.timed_names = ["stack_forward"]
+        self.work_per_step = self.lin_flops + self.attn_flops + outer
+        self.workload = ("configs[4]: FLUX.1-dev transformer forward, embedders + %d double-stream + %d single-stream blocks + "
+                         "norm_out / proj_out, FP8_W8A8, random weights (each block its own), 1 image per GPU = %d image + %d text "
+                         "tokens, hidden 3072, 24 x 128 heads; one step = one forward = one denoising step = %.1f TFLOP"
+                         % (self.N_DOUBLE, self.N_SINGLE, S, self.TXT, self.work_per_step / 1e12))
+        self.launches_per_step = self.N_DOUBLE * 16 + self.N_SINGLE * 6 + 1
+        self.timed_names = ["transformer_forward"]
         self.timed_work = [self.work_per_step]
-        self.roof["kernel"] = "whole stack: 57 blocks, each 3 or 8 gemm_tcgen05_kernel<f8f6f4> launches + element-wise kernels of this " \
-                              "library, plus library attention and the small modulation matmuls"
+        self.roof["kernel"] = "whole model: 57 blocks, each 3 or 8 gemm_tcgen05_kernel<f8f6f4> launches + element-wise kernels of this " \
+                              "library, plus library attention, the small modulation matmuls and the 16-bit embedders / output layer"
 
     def setup_gpu(self, dev):
-        from lyradiff_b200 import flux_blocks
+        from lyradiff_b200 import flux_blocks, flux_model
         D, M, DH = self.D, self.MLP, self.DH
         g = torch.Generator(device=dev).manual_seed(0)
+        sd = {}
 
-        def lin(sd, name, n, k, scale=0.03):
+        def lin(name, n, k, scale=0.03, quantized=True):
             sd[name + ".weight"] = (torch.randn(n, k, generator=g, device=dev, dtype=torch.float32) * 0.02).bfloat16()
             sd[name + ".bias"] = (torch.randn(n, generator=g, device=dev, dtype=torch.float32) * 0.02).bfloat16()
-            sd[name + "_input_scale"] = torch.tensor([scale])
+            if quantized:
+                sd[name + "_input_scale"] = torch.tensor([scale])
 
-        ctx = flux_blocks.LyraDiffCommonContext()
-        self.double, self.single = [], []
         for i in range(self.N_DOUBLE):
-            sd = {}
+            p = "transformer_blocks.%d." % i
             for norm in ("norm1", "norm1_context"):
-                lin(sd, norm + ".linear", 6 * D, D)
+                lin(p + norm + ".linear", 6 * D, D, quantized=False)
             for a, b in (("attn.to_qkv", "attn.to_out.0"), ("attn.to_added_qkv", "attn.to_add_out")):
-                lin(sd, a, 3 * D, D)
-                lin(sd, b, D, D)
+                lin(p + a, 3 * D, D)
+                lin(p + b, D, D)
             for ff in ("ff", "ff_context"):
-                lin(sd, ff + ".net.0.proj", 4 * D, D)
-                lin(sd, ff + ".net.2", D, 4 * D)
+                lin(p + ff + ".net.0.proj", 4 * D, D)
+                lin(p + ff + ".net.2", D, 4 * D)
             for n in ("attn.norm_q.weight", "attn.norm_k.weight", "attn.norm_added_q.weight", "attn.norm_added_k.weight"):
-                sd[n] = torch.ones(DH, device=dev).bfloat16()
-            op = flux_blocks.FluxTransformerBlockOp("bf16", D, self.H, DH, 4, 1)
-            op.initialize(ctx)
-            op.reload_model_from_state_dict("", sd, dev)
-            self.double.append(op)
-            del sd
+                sd[p + n] = torch.ones(DH, device=dev).bfloat16()
         for i in range(self.N_SINGLE):
-            sd = {}
-            lin(sd, "norm.linear", 3 * D, D)
-            lin(sd, "attn.to_qkv", 3 * D, D)
-            lin(sd, "proj_mlp", M * D, D)
-            lin(sd, "proj_out", D, (M + 1) * D)
-            sd["attn.norm_q.weight"] = torch.ones(DH, device=dev).bfloat16()
-            sd["attn.norm_k.weight"] = torch.ones(DH, device=dev).bfloat16()
-            op = flux_blocks.FluxSingleTransformerBlockOp("bf16", D, self.H, DH, M, 1)
-            op.initialize(ctx)
-            op.reload_model_from_state_dict("", sd, dev)
-            self.single.append(op)
-            del sd
+            p = "single_transformer_blocks.%d." % i
+            lin(p + "norm.linear", 3 * D, D, quantized=False)
+            lin(p + "attn.to_qkv", 3 * D, D)
+            lin(p + "proj_mlp", M * D, D)
+            lin(p + "proj_out", D, (M + 1) * D)
+            sd[p + "attn.norm_q.weight"] = torch.ones(DH, device=dev).bfloat16()
+            sd[p + "attn.norm_k.weight"] = torch.ones(DH, device=dev).bfloat16()
+        lin("x_embedder", D, self.IN_CH, quantized=False)
+        lin("context_embedder", D, self.JOINT, quantized=False)
+        lin("proj_out", self.IN_CH, D, quantized=False)
+        lin("norm_out.linear", 2 * D, D, quantized=False)
+        for name, d_in in (("timestep_embedder", 256), ("guidance_embedder", 256), ("text_embedder", self.POOLED)):
+            lin("time_text_embed.%s.linear_1" % name, D, d_in, quantized=False)
+            lin("time_text_embed.%s.linear_2" % name, D, D, quantized=False)
+        self.op = flux_model.FluxTransformer2DModelOp("bf16", self.IN_CH, self.N_DOUBLE, self.N_SINGLE, DH, self.H, self.POOLED,
+                                                      self.JOINT, True, 1)
+        self.op.initialize(flux_blocks.LyraDiffCommonContext())
+        self.op.reload_transformer_model_from_state_dict(sd, "cuda")
+        del sd
         cg = _gen()
-        x, temb, rope = self._inputs(cg, self.tokens)
-        img = x[:, self.TXT:].contiguous()
-        self.txt = (torch.randn(1, self.TXT, D, generator=cg)).bfloat16().to(dev)
-        self.x, self.temb, self.rope = img.to(dev), temb.to(dev), rope.to(dev)
-        self.y = torch.empty(1, self.tokens, D, dtype=torch.bfloat16, device=dev)
+        S = self.tokens - self.TXT
+        _, _, rope = self._inputs(cg, self.tokens)
+        img = torch.randn(1, S, self.IN_CH, generator=cg).bfloat16()
+        self.txt = torch.randn(1, self.TXT, self.JOINT, generator=cg).bfloat16().to(dev)
+        self.pooled = torch.randn(1, self.POOLED, generator=cg).bfloat16().to(dev)
+        self.x, self.rope = img.to(dev), rope.to(dev)
+        self.y = torch.empty(1, S, self.IN_CH, dtype=torch.bfloat16, device=dev)
         self.h_in = img.pin_memory()
         self.e2e_x = [self.x, torch.empty_like(self.x)]
         self.e2e_y = [self.y, torch.empty_like(self.y)]
 
     def _forward(self, img):
-        txt = self.txt
-        for op in self.double:
-            img, txt = op.forward(img, txt, self.rope, self.temb)
-        h = torch.cat([txt, img], dim=1)
-        for op in self.single:
-            h = op.forward(h, self.rope, self.temb)
-        return h
+        return self.op.transformer_forward(img, self.txt, self.rope, self.pooled, 500.0, 3500.0)
+
+    def setup_cpu(self, rows):
+        # the CPU baseline of this case is the single-stream block of the stack on a row sample (its work is counted per block)
+        FluxBlock.setup_cpu(self, rows)
+
+    def cpu_work(self, rows):
+        return FluxBlock.cpu_work(self, rows)
 
 
 class W4A4:

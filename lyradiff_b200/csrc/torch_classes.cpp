@@ -779,6 +779,7 @@ struct FluxTransformer2DModelOp: torch::CustomClassHolder {
     std::vector<c10::intrusive_ptr<FluxSingleTransformerBlockOp>> sgl;
     Linear16 x_embedder, context_embedder, proj_out, norm_out;
     Mlp16    timestep_embedder, guidance_embedder, text_embedder;
+    Tensor   exponents;  // the frequency table of TimeProjection<T>, fp32 [128], on the device
 
     FluxTransformer2DModelOp(const std::string& inference_dtype, int64_t input_channels, int64_t num_layers,
                              int64_t num_single_layers, int64_t attention_head_dim, int64_t num_attention_heads,
@@ -808,6 +809,14 @@ struct FluxTransformer2DModelOp: torch::CustomClassHolder {
         timestep_embedder.load(sd, "time_text_embed.timestep_embedder.", dev, dtype);
         guidance_embedder.load(sd, "time_text_embed.guidance_embedder.", dev, dtype);
         text_embedder.load(sd, "time_text_embed.text_embedder.", dev, dtype);
+        // TimeProjection<T>(256, flip_sin_to_cos = true, downscale_freq_shift = 0) (layers/time_proj/TimeProjection.cc:39-51):
+        // exponents exp(-ln(10000) * i / 128) in fp32 on the host, copied to the device once
+        std::vector<float> table(128);
+        const float        factor = -std::log(10000.0f) / 128.0f;
+        for (int i = 0; i < 128; ++i) {
+            table[i] = std::exp(factor * (float)i);
+        }
+        exponents = at::from_blob(table.data(), {128}, at::TensorOptions().dtype(at::kFloat)).to(dev);
         for (int64_t i = 0; i < n_double; ++i) {
             dbl[i]->reload_model_from_state_dict("transformer_blocks." + std::to_string(i) + ".", sd, device);
         }
@@ -918,18 +927,12 @@ struct FluxTransformer2DModelOp: torch::CustomClassHolder {
         }
     }
 
-    // TimeProjection<T>(256, flip_sin_to_cos = true, downscale_freq_shift = 0) (layers/time_proj/TimeProjection.cc:39-51, kernel
-    // kernels/time_proj/time_proj_kernels.cu:70-97): fp32 exponents from the host, fp32 sin / cos, cast to T, cosine half first
-    Tensor time_projection(double value, const at::Device& dev) const
+    // kernel kernels/time_proj/time_proj_kernels.cu:70-97: fp32 sin / cos of exponent * value, cast to T, cosine half first;
+    // device work only, so a forward can be captured into a CUDA graph
+    Tensor time_projection(double value) const
     {
-        constexpr int      half   = 128;
-        const float        factor = -std::log(10000.0f) / (float)half;
-        std::vector<float> arg(half);
-        for (int i = 0; i < half; ++i) {
-            arg[i] = std::exp(factor * (float)i) * (float)value;
-        }
-        Tensor a = at::from_blob(arg.data(), {half}, at::TensorOptions().dtype(at::kFloat)).to(dev);
-        return at::cat({at::cos(a), at::sin(a)}).to(dtype).reshape({1, 2 * half});
+        Tensor a = exponents * (float)value;
+        return at::cat({at::cos(a), at::sin(a)}).to(dtype).reshape({1, 256});
     }
 
     Tensor transformer_forward(const Tensor& hidden_states, const Tensor& encoder_hidden_states, const Tensor& rope_emb,
@@ -944,11 +947,10 @@ struct FluxTransformer2DModelOp: torch::CustomClassHolder {
                     "controlnet_single_block_samples currently needs to be 0");  // FluxTransformer2DModel.cc:252
         std::lock_guard<std::mutex> guard(lock);
         const int64_t B = hidden_states.size(0), S = hidden_states.size(1), E = encoder_hidden_states.size(1);
-        const auto    dev = hidden_states.device();
 
         // conditioning vector, SiLU'd as the blocks expect it (add3Tensor2dAndSilu: src1 + src2 + src3 in T, then SiLU)
-        Tensor t_emb = timestep_embedder.run(time_projection(timestep, dev));
-        Tensor g_emb = guidance_embedder.run(time_projection(guidance, dev));
+        Tensor t_emb = timestep_embedder.run(time_projection(timestep));
+        Tensor g_emb = guidance_embedder.run(time_projection(guidance));
         Tensor p_emb = text_embedder.run(pooled_projection);
         Tensor temb  = at::silu((p_emb + g_emb) + t_emb).contiguous();
 

@@ -114,7 +114,8 @@ def _target_device(device):
     """`device` of reload_model_from_state_dict says where the state-dict tensors LIVE ("cpu" or "cuda...": the reference
     picks the memcpy kind from it, FluxSingleTransformerBlockOp.h:261-264, and its Python wrappers pass "cpu"); the weights
     always go to the current CUDA device.  torch knows where each tensor is, so the argument is only validated."""
-    if not (isinstance(device, str) and (device == "cpu" or device.startswith("cuda"))):
+    device = str(device)  # a torch.device is accepted too
+    if not (device == "cpu" or device.startswith("cuda")):
         raise RuntimeError("device must be 'cpu' or 'cuda[:n]' (where the state dict's tensors are)")
     return torch.device("cuda", torch.cuda.current_device())
 

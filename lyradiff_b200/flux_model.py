@@ -26,15 +26,20 @@ from .flux_blocks import (_DTYPES, FP8_W8A8, FP8_W8A8_FULL, INT4_W4A4, INT4_W4A4
                           _state_dict_from_bin)
 
 
-def time_projection(value, channels, dtype, device, max_period=10000.0):
-    """TimeProjection<T>(channels, flip_sin_to_cos=true, downscale_freq_shift=0) (src/lyradiff/layers/time_proj/
-    TimeProjection.cc:39-51, kernel kernels/time_proj/time_proj_kernels.cu:70-97): exponents exp(-ln(max_period) * i / half)
-    in fp32 on the host, sin / cos in fp32, cast to T; the cosine half comes first."""
+def time_exponents(channels, device, max_period=10000.0):
+    """The frequency table of TimeProjection<T> (src/lyradiff/layers/time_proj/TimeProjection.cc:39-51): exp(-ln(max_period) * i /
+    half) for i < half, computed in fp32 on the host once and kept on the device, as the reference does."""
     half = channels // 2
     factor = torch.tensor(-math.log(max_period), dtype=torch.float32) / half
-    exponents = torch.exp(factor * torch.arange(half, dtype=torch.float32))
-    arg = (exponents * torch.tensor(float(value), dtype=torch.float32)).to(device)
-    return torch.cat([torch.cos(arg), torch.sin(arg)]).to(dtype).reshape(1, channels)
+    return torch.exp(factor * torch.arange(half, dtype=torch.float32)).to(device)
+
+
+def time_projection(value, exponents, dtype):
+    """TimeProjection<T>(channels, flip_sin_to_cos=true, downscale_freq_shift=0) (kernel kernels/time_proj/
+    time_proj_kernels.cu:70-97): sin / cos of exponent * value in fp32, cast to T, the cosine half first.  Device work only
+    (no host-to-device copy), so a forward can be captured into a CUDA graph."""
+    arg = exponents * float(value)
+    return torch.cat([torch.cos(arg), torch.sin(arg)]).to(dtype).reshape(1, 2 * exponents.numel())
 
 
 class _Mlp16:
@@ -92,6 +97,7 @@ class FluxTransformer2DModelOp:
         for name in ("timestep_embedder", "guidance_embedder", "text_embedder"):
             w[name] = _Mlp16(sd, "time_text_embed." + name + ".", dev, dt)
         w["norm_out"] = _Linear16(sd["norm_out.linear.weight"], sd["norm_out.linear.bias"], dev, dt)
+        w["exponents"] = time_exponents(256, dev)
         for i, b in enumerate(self.double_blocks):
             b.reload_model_from_state_dict("transformer_blocks.%d." % i, sd, device)
         for j, b in enumerate(self.single_blocks):
@@ -159,8 +165,8 @@ class FluxTransformer2DModelOp:
             raise RuntimeError("shape mismatch")
 
         # conditioning vector, SiLU'd as the blocks expect it (CombinedTimestepGuidanceTextProjEmbeddings, need_silu = true)
-        t_emb = w["timestep_embedder"](time_projection(timestep, 256, dt, dev))
-        g_emb = w["guidance_embedder"](time_projection(guidance, 256, dt, dev))
+        t_emb = w["timestep_embedder"](time_projection(timestep, w["exponents"], dt))
+        g_emb = w["guidance_embedder"](time_projection(guidance, w["exponents"], dt))
         p_emb = w["text_embedder"](pooled_projection)
         temb = torch.nn.functional.silu(((p_emb + g_emb) + t_emb)).contiguous()   # add3Tensor2dAndSilu: src1 + src2 + src3 in T
 
