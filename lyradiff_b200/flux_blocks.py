@@ -331,10 +331,26 @@ class FluxSingleTransformerBlockOp:
             self._buf[name] = t
         return t
 
-    def forward(self, hidden_states, rope_emb, temb):
+    def modulation(self, temb):
+        """msa = norm.linear(temb) -> [shift, scale, gate], each [B, D] contiguous.  It depends on temb alone, so a caller that
+        runs many blocks with one temb (flux_model) may compute it ahead of the block, on another stream."""
+        w, dev, dt = self._w, temb.device, self.dtype
+        B, D = temb.shape
+        if self.quant_level in (FP8_W8A8_FULL, INT4_W4A4_FULL):
+            nw = w["norm"]
+            tq = torch.empty(B, D, dtype=torch.uint8, device=dev)
+            ops.invoke_cuda_d2d_scale_cpy_convert(tq, temb, nw.input_scale)
+            msa = torch.empty(B, 3 * D, dtype=dt, device=dev)
+            ops.gemm_with_residual_and_bias_fp8(nw.qweight, nw.w_scale, tq, nw.input_scale, msa, bias=nw.bias)
+        else:
+            msa = torch.addmm(w["norm16"].b, temb, w["norm16"].w.t())
+        return [c.contiguous() for c in msa.chunk(3, dim=1)]
+
+    def forward(self, hidden_states, rope_emb, temb, mod=None):
         """hidden_states [B, S, D], rope_emb [B, S, head_dim/2, 2, 2] (any shape with that many elements), temb [B, D]
         already SiLU'd; all CUDA, contiguous and of the inference dtype (FluxSingleTransformerBlockOp.cc:40-62).
-        Returns a new [B, S, D] tensor owned by torch."""
+        Returns a new [B, S, D] tensor owned by torch.  `mod` (not in the reference's signature) is an optional
+        (tensors, event) pair from modulation() computed ahead on another stream."""
         if self._w is None:
             raise RuntimeError("weights not loaded")
         for t in (hidden_states, rope_emb, temb):
@@ -347,15 +363,7 @@ class FluxSingleTransformerBlockOp:
         T = B * S
 
         # ---- modulation: msa = linear(temb) -> shift | scale | gate
-        if self.quant_level in (FP8_W8A8_FULL, INT4_W4A4_FULL):
-            nw = w["norm"]
-            tq = self._buffer("temb_q", (B, D), torch.uint8, dev)
-            ops.invoke_cuda_d2d_scale_cpy_convert(tq, temb, nw.input_scale)
-            msa = self._buffer("msa", (B, 3 * D), dt, dev)
-            ops.gemm_with_residual_and_bias_fp8(nw.qweight, nw.w_scale, tq, nw.input_scale, msa, bias=nw.bias)
-        else:
-            msa = torch.addmm(w["norm16"].b, temb, w["norm16"].w.t())
-        shift, scale, gate = (c.contiguous() for c in msa.chunk(3, dim=1))
+        shift, scale, gate = _take_modulation(mod) if mod is not None else self.modulation(temb)
         if w.get("int4"):
             return self._forward_int4(hidden_states, rope_emb, shift, scale, gate)
 
@@ -391,6 +399,17 @@ class FluxSingleTransformerBlockOp:
         return out
 
     __call__ = forward
+
+
+def _take_modulation(mod):
+    """A modulation computed on another stream: wait for its event on the current stream and tell the allocator that the
+    tensors are used here too."""
+    tensors, event = mod
+    cur = torch.cuda.current_stream()
+    cur.wait_event(event)
+    for t in tensors:
+        t.record_stream(cur)
+    return tensors
 
 
 def _modulation(op, w, temb, chunks):
@@ -527,9 +546,13 @@ class FluxTransformerBlockOp:
                           "attn.norm_added_k.weight", "ff_context"),
         }
 
-    def _pre_attention(self, w, x, temb):
+    def modulation(self, temb):
+        """(image-stream, text-stream) modulations, six [B, D] tensors each; see FluxSingleTransformerBlockOp.modulation."""
+        return [_modulation(self, self._w[s]["norm"], temb, 6) for s in ("img", "txt")]
+
+    def _pre_attention(self, w, x, temb, mod=None):
         B, S, D = x.shape
-        mod = _modulation(self, w["norm"], temb, 6)
+        mod = _modulation(self, w["norm"], temb, 6) if mod is None else mod
         if w.get("int4"):
             norm = torch.empty(B, S, D, dtype=self.dtype, device=x.device)
             ops.invoke_layer_norm_with_shift_and_scale(norm, x, mod[1], mod[0], eps=1e-6)
@@ -586,7 +609,7 @@ class FluxTransformerBlockOp:
             ops.invoke_fused_gate_and_residual(out, y.view(B, S, D), mod[5], h)
         return out
 
-    def forward(self, hidden_states, encoder_hidden_states, rope_emb, temb):
+    def forward(self, hidden_states, encoder_hidden_states, rope_emb, temb, mod=None):
         """hidden_states [B, S_img, D], encoder_hidden_states [B, S_txt, D], rope_emb over the S_txt + S_img joint
         sequence (text first) with B * (S_txt + S_img) * head_dim * 2 elements, temb [B, D] SiLU'd.
         Returns [hidden_out, encoder_out]."""
@@ -601,8 +624,12 @@ class FluxTransformerBlockOp:
                 tuple(temb.shape) != (B, D) or rope_emb.numel() != B * (S + E) * self.head_dim * 2:
             raise RuntimeError("shape mismatch")
         wi, wt = self._w["img"], self._w["txt"]
-        mod_i, qkv_i = self._pre_attention(wi, hidden_states, temb)
-        mod_t, qkv_t = self._pre_attention(wt, encoder_hidden_states, temb)
+        pre_i = pre_t = None
+        if mod is not None:   # ((image tensors, text tensors), event) computed ahead on another stream
+            (pre_i, pre_t), event = mod
+            _take_modulation((list(pre_i) + list(pre_t), event))
+        mod_i, qkv_i = self._pre_attention(wi, hidden_states, temb, pre_i)
+        mod_t, qkv_t = self._pre_attention(wt, encoder_hidden_states, temb, pre_t)
         # joint sequence [B, E + S, 3, H, Dh], text first (invokeFusedRmsNormCatAndRope, flux_apply_rope.cu:78-156)
         tot = E + S
         joint = torch.empty(B, tot, 3 * D, dtype=self.dtype, device=hidden_states.device)
