@@ -13,6 +13,9 @@
 // linear of quant_level 1).  torch supplies device memory, the stream and the class registry; nothing here computes.
 // The data flow is the one documented in lyradiff_b200/flux_blocks.py, which is the Python twin of this file.
 #include <ATen/cuda/CUDAContext.h>
+#include <ATen/cuda/CUDAEvent.h>
+#include <c10/cuda/CUDACachingAllocator.h>
+#include <c10/cuda/CUDAGuard.h>
 #include <torch/custom_class.h>
 #include <torch/script.h>
 
@@ -332,6 +335,24 @@ struct LyraDiffCommonContext: torch::CustomClassHolder {
     LyraDiffCommonContext() = default;
 };
 
+// A block's modulation computed ahead of the block on another stream (the whole-model forward does that: it depends on temb
+// alone): the tensors and the event recorded behind them.  take() makes the current stream wait for the event and tells the
+// caching allocator that the tensors are used on this stream too.
+struct AheadModulation {
+    std::vector<std::vector<Tensor>>       parts;  // single block: one list of 3; double block: image list of 6, text list of 6
+    std::shared_ptr<at::cuda::CUDAEvent>   event;
+    void take() const
+    {
+        auto cur = at::cuda::getCurrentCUDAStream();
+        event->block(cur);
+        for (const auto& list : parts) {
+            for (const Tensor& t : list) {
+                c10::cuda::CUDACachingAllocator::recordStream(t.storage().data_ptr(), cur);
+            }
+        }
+    }
+};
+
 struct BlockBase: torch::CustomClassHolder {
     at::ScalarType dtype;
     int64_t        dim, heads, head_dim, mlp_scale, quant_level;
@@ -478,7 +499,11 @@ struct FluxSingleTransformerBlockOp: BlockBase {
         loaded = true;
     }
 
-    Tensor forward(const Tensor& hidden, const Tensor& rope, const Tensor& temb)
+    std::vector<Tensor> modulation(const Tensor& temb) { return norm.run(temb, 3, dtype); }
+
+    Tensor forward(const Tensor& hidden, const Tensor& rope, const Tensor& temb) { return forward_with(hidden, rope, temb, nullptr); }
+
+    Tensor forward_with(const Tensor& hidden, const Tensor& rope, const Tensor& temb, const AheadModulation* ahead)
     {
         TORCH_CHECK(loaded, "weights not loaded");
         std::lock_guard<std::mutex> guard(lock);
@@ -486,7 +511,10 @@ struct FluxSingleTransformerBlockOp: BlockBase {
         const int64_t B = hidden.size(0), S = hidden.size(1), D = hidden.size(2), T = B * S;
         TORCH_CHECK(D == dim && temb.size(0) == B && temb.size(1) == D && rope.numel() == T * head_dim * 2, "shape mismatch");
         const int  dtc  = dt_code(dtype);
-        auto       mod  = norm.run(temb, 3, dtype);  // shift, scale, gate
+        if (ahead != nullptr) {
+            ahead->take();
+        }
+        auto       mod  = ahead != nullptr ? ahead->parts[0] : norm.run(temb, 3, dtype);  // shift, scale, gate
         if (int4()) {
             return forward_int4(hidden, rope, mod);
         }
@@ -691,7 +719,15 @@ struct FluxTransformerBlockOp: BlockBase {
         return fp8_gemm_gate_residual(s.ff2, f1, mod[5], h, B, S, dtype);
     }
 
+    std::vector<std::vector<Tensor>> modulation(const Tensor& temb) { return {img.norm.run(temb, 6, dtype), txt.norm.run(temb, 6, dtype)}; }
+
     std::vector<Tensor> forward(const Tensor& hidden, const Tensor& encoder, const Tensor& rope, const Tensor& temb)
+    {
+        return forward_with(hidden, encoder, rope, temb, nullptr);
+    }
+
+    std::vector<Tensor> forward_with(const Tensor& hidden, const Tensor& encoder, const Tensor& rope, const Tensor& temb,
+                                     const AheadModulation* ahead)
     {
         TORCH_CHECK(loaded, "weights not loaded");
         std::lock_guard<std::mutex> guard(lock);
@@ -700,7 +736,11 @@ struct FluxTransformerBlockOp: BlockBase {
         TORCH_CHECK(D == dim && encoder.size(0) == B && encoder.size(2) == D && temb.size(0) == B && temb.size(1) == D &&
                         rope.numel() == B * tot * head_dim * 2,
                     "shape mismatch");
-        auto   mod_i = img.norm.run(temb, 6, dtype), mod_t = txt.norm.run(temb, 6, dtype);
+        if (ahead != nullptr) {
+            ahead->take();
+        }
+        auto   mod_i = ahead != nullptr ? ahead->parts[0] : img.norm.run(temb, 6, dtype);
+        auto   mod_t = ahead != nullptr ? ahead->parts[1] : txt.norm.run(temb, 6, dtype);
         Tensor qi = pre_attention(img, hidden, mod_i).view({B, S, 3 * D});
         Tensor qt = pre_attention(txt, encoder, mod_t).view({B, E, 3 * D});
         // joint sequence [B, E + S, 3, H, Dh], text first (invokeFusedRmsNormCatAndRope, flux_apply_rope.cu:78-156)
@@ -957,11 +997,35 @@ struct FluxTransformer2DModelOp: torch::CustomClassHolder {
         Tensor h = x_embedder.run(hidden_states.view({B * S, in_ch})).view({B, S, dim});
         Tensor c = context_embedder.run(encoder_hidden_states.view({B * E, joint_dim})).view({B, E, dim});
 
+        // Every block's modulation linear depends on temb alone (an M = B product that streams 56-113 MB of weights): all of
+        // them are issued on a second stream now and each block waits only for its own event, so that memory-bound work
+        // overlaps the tensor-bound GEMMs of the blocks in front of it.
+        std::vector<AheadModulation> ahead((size_t)(n_double + n_single));
+        const auto                   main_stream = at::cuda::getCurrentCUDAStream();
+        const auto                   side_stream = at::cuda::getStreamFromPool(false, main_stream.device_index());
+        {
+            at::cuda::CUDAEvent ready;
+            ready.record(main_stream);
+            ready.block(side_stream);
+            c10::cuda::CUDACachingAllocator::recordStream(temb.storage().data_ptr(), side_stream);
+            c10::cuda::CUDAStreamGuard on_side(side_stream);
+            for (int64_t i = 0; i < n_double + n_single; ++i) {
+                AheadModulation& a = ahead[(size_t)i];
+                if (i < n_double) {
+                    a.parts = dbl[i]->modulation(temb);
+                } else {
+                    a.parts = {sgl[i - n_double]->modulation(temb)};
+                }
+                a.event = std::make_shared<at::cuda::CUDAEvent>();
+                a.event->record(side_stream);
+            }
+        }
+
         const std::vector<Tensor> samples = controlnet_block_samples.value_or(std::vector<Tensor>{});
         const bool    repeat   = controlnet_blocks_repeat.value_or(false);
         const int64_t interval = samples.empty() ? 0 : (n_double - 1) / (int64_t)samples.size() + 1;
         for (int64_t i = 0; i < n_double; ++i) {
-            auto out = dbl[i]->forward(h, c, rope_emb, temb);
+            auto out = dbl[i]->forward_with(h, c, rope_emb, temb, &ahead[(size_t)i]);
             h        = out[0];
             c        = out[1];
             if (!samples.empty()) {
@@ -973,7 +1037,12 @@ struct FluxTransformer2DModelOp: torch::CustomClassHolder {
         }
         Tensor x = at::cat({c, h}, 1);
         for (int64_t i = 0; i < n_single; ++i) {
-            x = sgl[i]->forward(x, rope_emb, temb);
+            x = sgl[i]->forward_with(x, rope_emb, temb, &ahead[(size_t)(n_double + i)]);
+        }
+        {
+            at::cuda::CUDAEvent joined;  // the second stream joins again (needed when the forward is being captured into a graph)
+            joined.record(side_stream);
+            joined.block(main_stream);
         }
         h = x.slice(1, E, E + S).contiguous();
 
