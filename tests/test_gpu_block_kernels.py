@@ -43,6 +43,33 @@ def test_rmsnorm_rope_against_oracle(ops, dtype, batch, seq, heads, head_dim):
     assert_bit_equal(inplace, got, "in place")
 
 
+def test_rmsnorm_rope_with_the_reference_table_fixture(ops):
+    """The rotary table of tests/golden/ref_rope_table.npz came out of the reference's own rope / EmbedND; fed to
+    lyraq_rmsnorm_rope in that [S, 64, 2, 2] layout (cast to the model type as the reference's wrapper does) the kernel
+    must agree with the oracle under the tolerance of the test above, and the library's own table builder must give
+    the kernel the same bits."""
+    import os
+    import numpy as np
+    from lyradiff_b200 import rope as rope_host
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_rope_table.npz"))
+    table = torch.from_numpy(z["table"])[0, 0].bfloat16()
+    S, heads, head_dim = table.shape[0], 4, 128
+    g = torch.Generator().manual_seed(12)
+    qkv = torch.randn(S, 3 * heads * head_dim, generator=g).bfloat16()
+    scale = (1.0 + 0.2 * torch.randn(2 * head_dim, generator=g)).bfloat16()
+    want = norms.rmsnorm_rope(qkv, scale, table, heads, head_dim, eps=1e-6)
+    out = torch.empty_like(qkv, device="cuda")
+    ops.invoke_fused_rmsnorm_and_rope(out, cu(qkv), cu(scale), cu(table), 1e-6, 1, S, heads, head_dim)
+    check_status()
+    diff = (out.cpu().float() - want.float()).abs()
+    assert float(diff.max()) <= 2 * torch.finfo(torch.bfloat16).eps * 8.0
+    assert float((diff > 0).float().mean()) <= 5e-3
+    own = rope_host.flux_rope_table(torch.from_numpy(z["ids"]))[0, 0].bfloat16()
+    out2 = torch.empty_like(qkv, device="cuda")
+    ops.invoke_fused_rmsnorm_and_rope(out2, cu(qkv), cu(scale), cu(own), 1e-6, 1, S, heads, head_dim)
+    assert_bit_equal(out2, out.cpu(), "library-built table")
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_gate_residual_bit_exact(ops, dtype):
     g = torch.Generator().manual_seed(3)

@@ -170,6 +170,34 @@ def test_int8_weight_quant_bit_exact(ops, dtype):
         assert_bit_equal(qw, q_ref)
 
 
+def test_int8_weight_quant_against_reference_run_fixture(ops):
+    """The device twin (lyraq_weight_quant_int8 = GetINT8WeightScale, quant_kernels.cu:173-223) beside the outputs of
+    the reference's offline exporter function tensor_quant (tests/golden/ref_int8_weight_quant.npz, written by running
+    that function).  The two rules differ by design: the device divides by s = amax/127 and saturates at -128, the
+    exporter multiplies by 127/amax, clamps at -127 and returns scale 1 for amax <= 2**-24 where the device returns
+    amax/127.  Stated bound on ordinary channels: at most one integer step on at most 0.1 % of the weights, scales
+    reciprocal to 3e-7; zero channels give q = 0 in both."""
+    import os
+    import numpy as np
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_int8_weight_quant.npz"))
+    for case in ("small_fp16", "k640_fp16"):           # weights the fixture holds as fp16 values: the device sees the same numbers
+        w = torch.from_numpy(z[case + "_w"]).half()
+        ref_q = torch.from_numpy(z[case + "_q"]).to(torch.int8)
+        ref_scale = torch.from_numpy(z[case + "_scale"]).reshape(-1)
+        n, k = w.shape
+        qw = torch.empty(n, k, dtype=torch.int8, device="cuda")
+        sw = torch.empty(n, dtype=torch.float32, device="cuda")
+        ops.invoke_get_int8_weight_scale(sw, qw, cu(w), None)
+        q, s = qw.cpu(), sw.cpu()
+        amax = w.float().abs().amax(dim=1)
+        ok = amax > 2.0 ** -14          # ordinary channels; the tiny ones are covered by the scale-1 rule stated above
+        d = (q[ok].int() - ref_q[ok].int()).abs()
+        assert int(d.max()) <= 1 and float((d != 0).float().mean()) <= 1e-3, case
+        assert float((s[ok].double() * ref_scale[ok].double() - 1.0).abs().max()) < 3e-7
+        if case == "small_fp16":
+            assert int(q[3].abs().sum()) == 0
+
+
 # Row statistics are summed in a different order on the device (fp32 shuffles) than in the oracle
 # (fp64), so a value sitting on a rounding boundary may land one step away.  Stated tolerance:
 # at most 1 LSB (int8) / 1 code (e4m3) / 1 ulp (16-bit y) on at most 0.1 % of the outputs.
