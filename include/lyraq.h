@@ -39,7 +39,8 @@ typedef enum {
     LYRAQ_F16 = 0,
     LYRAQ_BF16 = 1,
     LYRAQ_F32 = 2,
-    LYRAQ_S32 = 3
+    LYRAQ_S32 = 3,
+    LYRAQ_E4M3 = 4 /* FP8 e4m3 codes, one byte each (only where an entry point says so) */
 } lyraq_dtype_t;
 
 /* How the activation scale of an INT8 quantize / GEMM is given. */
@@ -286,6 +287,22 @@ LYRAQ_API int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* s
  * (src/lyradiff/kernels/rope/flux_apply_rope.h:20-30; kernel flux_apply_rope.cu:8-76). */
 LYRAQ_API int lyraq_rmsnorm_rope(void* out, const void* qkv, const void* scale, const void* rope, int dtype, double eps,
                                  size_t batch, size_t seq_len, int heads, int head_dim, void* stream);
+
+/* Attention of the FLUX blocks over the packed projection qkv [batch, seq, 3, heads, head_dim] (q heads, k heads, v heads,
+ * as lyraq_rmsnorm_rope leaves them): out[b, s, h, :] = softmax(q k^T * softmax_scale) v, no mask, head_dim 128, fp32
+ * scores and accumulation on tcgen05, probabilities rounded to the 16-bit type for the second product.  The result is
+ * rounded to `dtype` and written to out [batch, seq, heads * head_dim] with row pitch out_ld elements -- or, with
+ * out_dtype LYRAQ_E4M3, quantized from that rounded value with 1 / out_scale[0] as lyraq_quant_fp8 does, straight into
+ * the input of the FP8 linear that follows (a column window of a wider matrix when out_ld > heads * head_dim).  With
+ * out2 != NULL the rows [split, seq) of every batch go to out2 (row s - split, pitch out2_ld, scale out2_scale) and only
+ * rows [0, split) to out: the text and image parts of a joint sequence feed different linears.
+ * Replaces FlashAttention2Layer<T>::forward (src/lyradiff/layers/flash_attn2/flash_attn2.cu:59-118, called at
+ * layers/flux_single_attention_processor/FluxSingleAttentionFP8Processor.cc:213 and
+ * layers/flux_attention_processor/FluxAttentionFP8Processor.cc:274) and the e4m3 cast of its output
+ * (FluxSingleTransformerFP8Block.cc:254, FluxAttnPostFP8Processor.cc:135,168). */
+LYRAQ_API int lyraq_attention(void* out, int out_dtype, size_t out_ld, const float* out_scale, void* out2, size_t out2_ld,
+                              const float* out2_scale, size_t split, const void* qkv, int dtype, size_t batch, size_t seq_len,
+                              int heads, int head_dim, float softmax_scale, void* stream);
 
 /* e4m3 quantize of src [rows, cols] (static per-tensor scale, 1/scale[0] applied) into a column window of an e4m3
  * matrix with row pitch dst_ld bytes: the attention output's share of the proj_out input.  Same arithmetic as

@@ -53,6 +53,8 @@ SIGNATURES = {
                                         c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_rmsnorm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_double, c_size_t, c_size_t, c_int, c_int,
                                    c_void_p]),
+    "lyraq_attention": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_int,
+                                c_size_t, c_size_t, c_int, c_int, c_float, c_void_p]),
     "lyraq_quant_fp8_2d": (c_int, [c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_size_t, c_size_t, c_void_p]),
     "lyraq_load_lora": (c_int, [c_void_p, c_void_p, c_int, c_float, c_size_t, c_void_p]),
     "lyraq_gate_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_size_t, c_void_p]),

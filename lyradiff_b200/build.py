@@ -14,7 +14,7 @@ LIB = os.path.join(HERE, "liblyraq.so")
 CLASSES_LIB = os.path.join(HERE, "liblyradiff_classes.so")
 CLASSES_SRC = os.path.join(CSRC, "torch_classes.cpp")
 
-SOURCES = ["api.cu", "quant_kernels.cu", "gemm_dense.cu", "gemm_w4a4.cu", "lora_down.cu", "block_kernels.cu", "linear_layers.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "quant_kernels.cu", "gemm_dense.cu", "gemm_w4a4.cu", "lora_down.cu", "block_kernels.cu", "attention.cu", "linear_layers.cu", "noalloc.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

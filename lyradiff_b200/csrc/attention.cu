@@ -1,0 +1,526 @@
+// Attention forward for the FLUX blocks: out[b, s, h, :] = softmax(q k^T * scale) v over the packed projection
+// qkv [batch, seq, 3, heads, 128] (16-bit), no mask, no dropout.  Replaces the reference's FlashAttention-2 layer
+// (src/lyradiff/layers/flash_attn2/flash_attn2.cu:59-118, kernels flash_fwd_kernel.h) on the path between the QKV
+// linear and the output linear, and writes its result either in the 16-bit type or already quantized to e4m3 for the
+// FP8 linear that follows (the reference runs cudaD2DScaleCpyConvert over the attention output as a separate pass,
+// FluxSingleTransformerFP8Block.cc:254, FluxAttnPostFP8Processor.cc:135,168).
+//
+// One CTA owns 256 query rows of one head (two tiles of 128) and walks the keys in tiles of 128:
+//   warp 8    lane 0: TMA producer.  Q once (2 x 32 KB), then K_0, V_0, K_1, V_1, ... through a ring of five 32 KB slots.
+//             Every tile is two SWIZZLE_128B boxes of 128 rows x 64 columns, so q and k tiles are K-major operands and
+//             the v tile is an MN-major operand as it lies in memory -- nothing is transposed.
+//   warp 9    lane 0: MMA issuer; the warp owns the 512 columns of tensor memory:
+//             S_0 | S_1 | O_0 | O_1, 128 fp32 columns each.  S_t = Q_t K_j^T (8 x tcgen05.mma kind::f16, K = 16),
+//             O_t += P_t V_j with P_t read from tensor memory, where the softmax warps wrote it over S_t.
+//   warps 0-3 softmax of query tile 0, warps 4-7 of tile 1: a thread owns one query row (its tensor-memory lane), so
+//             row maxima and sums need no shuffles.  exp2 with the scale folded in; the running maximum is only
+//             raised when it grew by more than 2^8 (the accumulator and the row sum then share the stale reference,
+//             which cancels in O / l), so O is rescaled in tensor memory rarely, by these same warps, between two of
+//             their tile's MMAs.  After the last key tile the warps normalise and store their rows.
+// The two query tiles alternate on the tensor pipe: while the softmax warps of one tile work, the MMAs of the other run.
+// Every wait is bounded; on a timeout the role records it in the status word, raises the block's abort flag and all
+// roles leave; tensor memory is freed at the common exit.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace lyraq {
+
+using namespace sm100;
+
+typedef CUresult (*EncodeTiledFnAttn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+namespace attn {
+
+constexpr int kHeadDim   = 128;
+constexpr int kTile      = 128;                       // rows of a q tile and of a k / v tile
+constexpr int kQTiles    = 2;
+constexpr int kTileBytes = kTile * kHeadDim * 2;      // 32 KB: two boxes of 128 rows x 128 bytes
+constexpr int kBoxBytes  = kTileBytes / 2;
+constexpr int kSlots     = 5;
+constexpr int kQOffset   = 0;
+constexpr int kRingOffset = kQTiles * kTileBytes;
+constexpr int kBarOffset = kRingOffset + kSlots * kTileBytes;
+constexpr int kSmemTotal = kBarOffset + 256 + 1024;
+constexpr int kThreads   = 320;
+constexpr int kTmemCols  = 512;
+constexpr float kRescaleThreshold = 8.0f;             // in log2 units
+
+struct Params {
+    void*         out[2];        // rows [0, split) of every batch go to out[0], the rest to out[1] (row index - split)
+    long long     out_ld[2];     // row pitch in elements of the output type
+    long long     out_batch[2];  // batch pitch in elements
+    const float*  out_scale[2];  // e4m3 output: per-tensor scale of each part (1 / scale applied); unused otherwise
+    int           out_e4m3;
+    int           split;
+    int           batch, seq, heads;
+    int           q_blocks;      // ceil(seq / 256)
+    float         scale_log2;    // softmax scale * log2(e)
+    unsigned int* status;
+};
+
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_dst), "l"(m), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+template<typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t*       gen_base  = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars      = smem_base + kBarOffset;
+    // barriers: q_full | slot_full[5] | slot_empty[5] | s_full[2] | p_ready[2] | pv_done[2]
+    const uint32_t q_full = bars;
+    auto slot_full  = [&](int s) { return bars + 8u * (1 + s); };
+    auto slot_empty = [&](int s) { return bars + 8u * (1 + kSlots + s); };
+    auto s_full     = [&](int t) { return bars + 8u * (1 + 2 * kSlots + t); };
+    auto p_ready    = [&](int t) { return bars + 8u * (3 + 2 * kSlots + t); };
+    auto pv_done    = [&](int t) { return bars + 8u * (5 + 2 * kSlots + t); };
+    uint32_t*     tmem_slot  = reinterpret_cast<uint32_t*>(gen_base + kBarOffset + 8 * (7 + 2 * kSlots));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    grid_launch_dependents();
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < kSlots; ++s) {
+            mbar_init(slot_full(s), 1);
+            mbar_init(slot_empty(s), 1);
+        }
+        for (int t = 0; t < kQTiles; ++t) {
+            mbar_init(s_full(t), 1);
+            mbar_init(p_ready(t), 128);
+            mbar_init(pv_done(t), 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&tmap_qkv);
+    }
+    if (warp == 9) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    grid_dependency_wait();
+
+    // work item: consecutive blocks share a head, so the CTAs in flight together read the same k / v through L2
+    const int qb = blockIdx.x % p.q_blocks;
+    const int h  = (blockIdx.x / p.q_blocks) % p.heads;
+    const int b  = blockIdx.x / (p.q_blocks * p.heads);
+    const int q0 = qb * (kQTiles * kTile);
+    const int n_kv = (p.seq + kTile - 1) / kTile;
+    const int col_q = h * kHeadDim, col_k = (p.heads + h) * kHeadDim, col_v = (2 * p.heads + h) * kHeadDim;
+
+    if (warp == 8) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, (uint32_t)(kQTiles * kTileBytes));
+            for (int t = 0; t < kQTiles; ++t) {
+                for (int half = 0; half < 2; ++half) {
+                    tma_load_3d(smem_base + kQOffset + t * kTileBytes + half * kBoxBytes, &tmap_qkv, q_full, col_q + 64 * half,
+                                q0 + t * kTile, b);
+                }
+            }
+            int      slot = 0, issued = 0;
+            uint32_t phase = 0;
+            for (int i = 0; i < 2 * n_kv; ++i) {
+                if (!mbar_wait(slot_empty(slot), phase ^ 1u, abort_flag)) {
+                    report_timeout(p.status, 0x3100u | (unsigned)slot);
+                    *abort_flag = 1;
+                    break;
+                }
+                const uint32_t dst = smem_base + kRingOffset + slot * kTileBytes;
+                const int      col = (i & 1) ? col_v : col_k;
+                mbar_arrive_expect_tx(slot_full(slot), (uint32_t)kTileBytes);
+                tma_load_3d(dst, &tmap_qkv, slot_full(slot), col, (i >> 1) * kTile, b);
+                tma_load_3d(dst + kBoxBytes, &tmap_qkv, slot_full(slot), col + 64, (i >> 1) * kTile, b);
+                ++issued;
+                if (++slot == kSlots) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+            // no copy may be in flight when the block leaves: wait (bounded) for the slots filled last, and for q
+            int      s  = slot;
+            uint32_t ph = phase;
+            for (int i = 0; i < kSlots && i < issued; ++i) {
+                if (s == 0) {
+                    s = kSlots;
+                    ph ^= 1u;
+                }
+                --s;
+                const uint64_t t0 = global_timer_ns();
+                while (!mbar_try_wait(slot_full(s), ph)) {
+                    if (global_timer_ns() - t0 > kWaitLimitNs) {
+                        report_timeout(p.status, 0x3400u | (unsigned)s);
+                        break;
+                    }
+                }
+            }
+            const uint64_t t0 = global_timer_ns();
+            while (!mbar_try_wait(q_full, 0u)) {
+                if (global_timer_ns() - t0 > kWaitLimitNs) {
+                    report_timeout(p.status, 0x3401u);
+                    break;
+                }
+            }
+        }
+    } else if (warp == 9) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t kAb = sizeof(T) == 2 && TypeTag<T>::value == LYRAQ_BF16 ? 1u : 0u;
+            const uint32_t idesc_qk = umma_idesc(1u, kAb, 128, 128);
+            const uint32_t idesc_pv = umma_idesc(1u, kAb, 128, 128) | kIdescBMajorMN;
+            bool ok = true;
+            auto wait_or_fail = [&](uint32_t bar, uint32_t parity, unsigned code) {
+                if (ok && !mbar_wait(bar, parity, abort_flag)) {
+                    report_timeout(p.status, code);
+                    *abort_flag = 1;
+                    ok = false;
+                }
+                return ok;
+            };
+            auto slot_of  = [](int item) { return item % kSlots; };
+            auto phase_of = [](int item) { return (uint32_t)((item / kSlots) & 1); };
+            // S_t = Q_t K_j^T
+            auto issue_qk = [&](int t, int j) {
+                const uint32_t kbase = smem_base + kRingOffset + slot_of(2 * j) * kTileBytes;
+                const uint32_t qbase = smem_base + kQOffset + t * kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    const uint32_t off = (uint32_t)((ks >> 2) * kBoxBytes + (ks & 3) * 32);
+                    mma_f16(tmem_base + (uint32_t)(t * 128), umma_desc_k_sw128(qbase + off), umma_desc_k_sw128(kbase + off), idesc_qk,
+                            ks > 0 ? 1u : 0u);
+                }
+                tc_commit(s_full(t));
+            };
+            // O_t (+)= P_t V_j, P_t in tensor memory over the first 64 columns of S_t
+            auto issue_pv = [&](int t, int j) {
+                const uint32_t vbase = smem_base + kRingOffset + slot_of(2 * j + 1) * kTileBytes;
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    mma_f16_ts(tmem_base + (uint32_t)(256 + t * 128), tmem_base + (uint32_t)(t * 128 + ks * 8),
+                               umma_desc_mn_sw128(vbase + (uint32_t)(ks * 2048), (uint32_t)kBoxBytes), idesc_pv,
+                               (j > 0 || ks > 0) ? 1u : 0u);
+                }
+                tc_commit(pv_done(t));
+            };
+            if (wait_or_fail(q_full, 0u, 0x3200u) && wait_or_fail(slot_full(slot_of(0)), phase_of(0), 0x3201u)) {
+                tc_fence_after_sync();
+                issue_qk(0, 0);
+                issue_qk(1, 0);
+                tc_commit(slot_empty(slot_of(0)));
+            }
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const bool more = j + 1 < n_kv;
+                for (int t = 0; t < kQTiles && ok; ++t) {
+                    if (!wait_or_fail(p_ready(t), (uint32_t)(j & 1), 0x3210u | (unsigned)t)) {
+                        break;
+                    }
+                    if (t == 0 && !wait_or_fail(slot_full(slot_of(2 * j + 1)), phase_of(2 * j + 1), 0x3220u)) {
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    issue_pv(t, j);
+                    if (t == 1) {
+                        tc_commit(slot_empty(slot_of(2 * j + 1)));
+                    }
+                    if (more) {
+                        if (t == 0 && !wait_or_fail(slot_full(slot_of(2 * j + 2)), phase_of(2 * j + 2), 0x3230u)) {
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        issue_qk(t, j + 1);
+                        if (t == 1) {
+                            tc_commit(slot_empty(slot_of(2 * j + 2)));
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax + epilogue, one thread per query row
+        const int      t        = warp >> 2;                                   // query tile
+        const int      quadrant = warp & 3;                                    // tensor-memory lane quadrant of this warp
+        const uint32_t lane_off = (uint32_t)(quadrant * 32) << 16;
+        const uint32_t s_addr   = tmem_base + lane_off + (uint32_t)(t * 128);
+        const uint32_t o_addr   = tmem_base + lane_off + (uint32_t)(256 + t * 128);
+        const float    c        = p.scale_log2;
+        float          m        = -INFINITY;                                   // reference maximum of this row (raw scores)
+        float          l        = 0.0f;                                        // sum of exp2((s - m) c)
+        bool           ok       = true;
+
+        for (int j = 0; j < n_kv && ok; ++j) {
+            if (!__all_sync(0xffffffffu, mbar_wait(s_full(t), (uint32_t)(j & 1), abort_flag))) {
+                report_timeout(p.status, 0x3300u | (unsigned)t);
+                *abort_flag = 1;
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            uint32_t s[128];
+            tmem_ld_32x32(s_addr, s);
+            tmem_ld_32x32(s_addr + 32, s + 32);
+            tmem_ld_32x32(s_addr + 64, s + 64);
+            tmem_ld_32x32(s_addr + 96, s + 96);
+            tmem_ld_wait();
+            const int valid = p.seq - j * kTile;                               // keys of this tile inside the sequence
+            if (valid < kTile) {
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    if (i >= valid) {
+                        s[i] = 0xff800000u;                                    // -inf: zero-filled keys take no weight
+                    }
+                }
+            }
+            float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]), mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+#pragma unroll
+            for (int i = 4; i < 128; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(s[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            if (j == 0) {
+                m = mx;
+            } else {
+                const bool raise = (mx - m) * c > kRescaleThreshold;
+                if (__any_sync(0xffffffffu, raise)) {
+                    // the accumulator may only be touched between this tile's MMAs: the previous P V has to be complete
+                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((j - 1) & 1), abort_flag))) {
+                        report_timeout(p.status, 0x3310u | (unsigned)t);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const float f = raise ? ex2_approx((m - mx) * c) : 1.0f;
+                    if (raise) {
+                        m = mx;
+                        l *= f;
+                    }
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        uint32_t o[32];
+                        tmem_ld_32x32(o_addr + cc * 32, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        }
+                        tmem_st_32x32(o_addr + cc * 32, o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            const float nmc = -m * c;
+            float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
+#pragma unroll
+            for (int cc = 0; cc < 8; ++cc) {
+                uint32_t w[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc * 16 + 2 * i]), c, nmc));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(s[cc * 16 + 2 * i + 1]), c, nmc));
+                    if (i & 1) {
+                        sum2 += p0;
+                        sum3 += p1;
+                    } else {
+                        sum0 += p0;
+                        sum1 += p1;
+                    }
+                    w[i] = Pair<T>::from_f32(p0, p1);
+                }
+                // P over the start of S: columns [8 cc, 8 cc + 8) hold keys [16 cc, 16 cc + 16), all already in registers
+                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                             ::"r"(s_addr + (uint32_t)(cc * 8)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
+                               "r"(w[6]), "r"(w[7])
+                             : "memory");
+            }
+            l += (sum0 + sum1) + (sum2 + sum3);
+            tmem_st_wait();
+            tc_fence_before_sync();
+            mbar_arrive(p_ready(t));
+        }
+
+        // ---- epilogue: O / l, rounded to T, stored as T or as e4m3 of that value
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((n_kv - 1) & 1), abort_flag))) {
+            report_timeout(p.status, 0x3320u | (unsigned)t);
+            *abort_flag = 1;
+            ok = false;
+        }
+        if (ok) {
+            tc_fence_after_sync();
+            const int row = q0 + t * kTile + quadrant * 32 + lane;            // row inside the sequence
+            const int part = row >= p.split ? 1 : 0;
+            const long long r_out = part ? row - p.split : row;
+            const float inv_l = 1.0f / l;
+            // rows past the end of the sequence belong to no part (out_scale[1] may be NULL): they load nothing and store nothing
+            const float qs = (p.out_e4m3 && row < p.seq) ? 1.0f / ld_f32(p.out_scale[part]) : 1.0f;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                uint32_t o[32];
+                tmem_ld_32x32(o_addr + cc * 32, o);
+                tmem_ld_wait();
+                if (row < p.seq) {
+                    uint32_t w[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        w[i] = Pair<T>::from_f32(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l);
+                    }
+                    const long long col = (long long)h * kHeadDim + cc * 32;
+                    if (p.out_e4m3) {
+                        uint8_t* dst = static_cast<uint8_t*>(p.out[part]) + (long long)b * p.out_batch[part] + r_out * p.out_ld[part] + col;
+                        uint32_t q8[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float2 a = Pair<T>::to_f32(w[2 * i]), bb = Pair<T>::to_f32(w[2 * i + 1]);
+                            q8[i] = f32x2_to_e4m3x2(a.x * qs, a.y * qs) | (f32x2_to_e4m3x2(bb.x * qs, bb.y * qs) << 16);
+                        }
+                        *reinterpret_cast<uint4*>(dst)      = make_uint4(q8[0], q8[1], q8[2], q8[3]);
+                        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(q8[4], q8[5], q8[6], q8[7]);
+                    } else {
+                        T* dst = static_cast<T*>(p.out[part]) + (long long)b * p.out_batch[part] + r_out * p.out_ld[part] + col;
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 9) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+}  // namespace attn
+
+// out = softmax(q k^T * softmax_scale) v for qkv [batch, seq, 3, heads, 128]; see lyraq_attention in the header.
+int launch_attention(void* out, int out_dtype, size_t out_ld, const float* out_scale, void* out2, size_t out2_ld,
+                     const float* out2_scale, size_t split, const void* qkv, int dtype, size_t batch, size_t seq, int heads,
+                     int head_dim, float softmax_scale, cudaStream_t stream)
+{
+    if (out == nullptr || qkv == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if ((dtype != LYRAQ_BF16 && dtype != LYRAQ_F16) || head_dim != attn::kHeadDim || heads <= 0 ||
+        (out_dtype != dtype && out_dtype != LYRAQ_E4M3)) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    if (batch == 0 || seq == 0) {
+        return LYRAQ_OK;
+    }
+    if (out2 == nullptr) {
+        split = seq;
+    }
+    const bool   e4m3 = out_dtype == LYRAQ_E4M3;
+    const size_t esz  = e4m3 ? 1 : 2;
+    if (split > seq || seq > 0x3fffffffu || batch > 0xffffu || (e4m3 && (out_scale == nullptr || (out2 != nullptr && out2_scale == nullptr)))) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    const size_t width = (size_t)heads * attn::kHeadDim;
+    if (out_ld < width || (out2 != nullptr && out2_ld < width) || !aligned16(out) || !aligned16(out2) || !aligned16(qkv) ||
+        (out_ld * esz) % 16 != 0 || (out2_ld * esz) % 16 != 0) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    static EncodeTiledFnAttn encode = nullptr;
+    if (encode == nullptr) {
+        void*                           fp = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fp, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+            return LYRAQ_ERR_CUDA;
+        }
+        encode = reinterpret_cast<EncodeTiledFnAttn>(fp);
+    }
+    CUtensorMap      tm;
+    const cuuint64_t dims[3]    = {(cuuint64_t)(3 * width), (cuuint64_t)seq, (cuuint64_t)batch};
+    const cuuint64_t strides[2] = {(cuuint64_t)(3 * width * 2), (cuuint64_t)(3 * width * 2) * seq};
+    const cuuint32_t box[3]     = {64, (cuuint32_t)attn::kTile, 1};
+    const cuuint32_t estr[3]    = {1, 1, 1};
+    if (encode(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(qkv), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+        record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled refused the qkv tensor map");
+        return LYRAQ_ERR_CUDA;
+    }
+    attn::Params p{};
+    p.out[0]       = out;
+    p.out[1]       = out2;
+    p.out_ld[0]    = (long long)out_ld;
+    p.out_ld[1]    = (long long)out2_ld;
+    p.out_batch[0] = (long long)(split * out_ld);
+    p.out_batch[1] = (long long)((seq - split) * out2_ld);
+    p.out_scale[0] = out_scale;
+    p.out_scale[1] = out2_scale;
+    p.out_e4m3     = e4m3 ? 1 : 0;
+    p.split        = (int)split;
+    p.batch        = (int)batch;
+    p.seq          = (int)seq;
+    p.heads        = heads;
+    p.q_blocks     = (int)((seq + attn::kQTiles * attn::kTile - 1) / (attn::kQTiles * attn::kTile));
+    p.scale_log2   = softmax_scale * 1.4426950408889634f;
+    p.status       = status_word_ptr();
+    if (p.status == nullptr) {
+        return LYRAQ_ERR_CUDA;
+    }
+    const unsigned grid = (unsigned)(batch * (size_t)heads * (size_t)p.q_blocks);
+    if (dtype == LYRAQ_BF16) {
+        static bool attr_set = false;
+        if (!attr_set) {
+            const cudaError_t e = cudaFuncSetAttribute(attn::attention_fwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::kSmemTotal);
+            if (e != cudaSuccess) {
+                return cuda_status(e, "cudaFuncSetAttribute(attention_fwd_kernel<bf16>)");
+            }
+            attr_set = true;
+        }
+        return cuda_status(launch_kernel(attn::attention_fwd_kernel<__nv_bfloat16>, grid, (unsigned)attn::kThreads, (size_t)attn::kSmemTotal,
+                                         stream, 1u, tm, p),
+                           "cudaLaunchKernelEx(attention_fwd_kernel<bf16>)");
+    }
+    static bool attr_set_h = false;
+    if (!attr_set_h) {
+        const cudaError_t e = cudaFuncSetAttribute(attn::attention_fwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::kSmemTotal);
+        if (e != cudaSuccess) {
+            return cuda_status(e, "cudaFuncSetAttribute(attention_fwd_kernel<f16>)");
+        }
+        attr_set_h = true;
+    }
+    return cuda_status(launch_kernel(attn::attention_fwd_kernel<__half>, grid, (unsigned)attn::kThreads, (size_t)attn::kSmemTotal, stream,
+                                     1u, tm, p),
+                       "cudaLaunchKernelEx(attention_fwd_kernel<f16>)");
+}
+
+}  // namespace lyraq
+
+extern "C" int lyraq_attention(void* out, int out_dtype, size_t out_ld, const float* out_scale, void* out2, size_t out2_ld,
+                               const float* out2_scale, size_t split, const void* qkv, int dtype, size_t batch, size_t seq_len,
+                               int heads, int head_dim, float softmax_scale, void* stream)
+{
+    return lyraq::launch_attention(out, out_dtype, out_ld, out_scale, out2, out2_ld, out2_scale, split, qkv, dtype, batch, seq_len,
+                                   heads, head_dim, softmax_scale, (cudaStream_t)stream);
+}

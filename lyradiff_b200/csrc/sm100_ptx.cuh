@@ -181,6 +181,20 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_
         : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (M = 128 rows = lanes, K 16-bit elements packed two per 32-bit column)
+// is read from tensor memory, B through its shared-memory descriptor.  One instruction covers K = 16 (8 columns of A).
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp receives lane (base_lane + t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t* r)
 {
@@ -207,6 +221,30 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t* r)
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Stores: thread t of the warp writes lane (base_lane + t), 32 or 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* r)
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t* r)
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------- CTA pairs (cta_group::2)
 // Two CTAs of a cluster drive one 256-row MMA: each holds half of the A rows and half of the B rows in its own
@@ -304,6 +342,24 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr)
     d |= (uint64_t)2 << 61;                       // layout type: SWIZZLE_128B, bits [61,64)
     return d;
 }
+
+// Descriptor of an MN-major operand tile with the 128-byte swizzle: the tile is stored as rows of 128 bytes along the
+// operand's M/N dimension (64 16-bit elements), one row per K index -- what a SWIZZLE_128B TMA box of [K rows, 64
+// columns] writes.  Groups of 8 K rows are `1024` bytes apart (stride byte offset); the next block of 64 M/N elements
+// starts `mn_block_bytes` further (leading byte offset).  Stepping 16 K rows adds 2048 bytes (128 in address units).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t mn_block_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
+    d |= (uint64_t)((mn_block_bytes >> 4) & 0x3fff) << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// bit 16 of the instruction descriptor: the B operand is MN-major (bit 15: the A operand)
+constexpr uint32_t kIdescBMajorMN = 1u << 16;
 
 // Instruction descriptor of tcgen05.mma kind::i8 / kind::f8f6f4 / kind::f16, dense, both operands K-major.
 // c_format: 1 = f32, 2 = s32.  ab_format: kind::i8 -> 1 = signed 8-bit; kind::f8f6f4 -> 0 = e4m3;

@@ -10,7 +10,7 @@ import torch
 
 from . import _lib
 
-F16, BF16, F32, S32 = 0, 1, 2, 3
+F16, BF16, F32, S32, E4M3 = 0, 1, 2, 3, 4
 SCALE_PER_TENSOR, SCALE_PER_TOKEN, SCALE_PER_TOKEN_DYNAMIC = 0, 1, 2
 EPI_NONE, EPI_GELU_TANH, EPI_ROUND_EACH = 0, 1, 2
 
@@ -201,6 +201,32 @@ def invoke_fused_rmsnorm_and_rope(out, qkv, scale, rope_emb, eps, batch, seq_len
     st = _lib.lib().lyraq_rmsnorm_rope(_p(out), _p(qkv), _p(scale), _p(rope_emb), _dt(qkv), float(eps), batch, seq_len, heads,
                                        head_dim, _stream())
     _lib.check(st, "lyraq_rmsnorm_rope")
+    return out
+
+
+def flash_attention(qkv, batch, seq_len, heads, head_dim, out=None, out_scale=None, col0=0, out2=None, out2_scale=None,
+                    col0_2=0, split=None, softmax_scale=None):
+    """FlashAttention2Layer<T>::forward (src/lyradiff/layers/flash_attn2/flash_attn2.cu:59-118) on the packed projection
+    qkv [batch * seq_len, 3 * heads * head_dim].  out: [batch * rows, ld] of qkv's type, or uint8 (e4m3 codes, with
+    out_scale) -- columns col0 .. col0 + heads * head_dim are written; created as a 16-bit [batch * seq_len, heads *
+    head_dim] tensor when omitted.  With out2 / split the rows from `split` on go to out2 (see lyraq_attention)."""
+    width = heads * head_dim
+    if out is None:
+        out = torch.empty(batch * seq_len, width, dtype=qkv.dtype, device=qkv.device)
+    e4m3 = out.dtype == torch.uint8
+    if split is None:
+        split = seq_len
+    if softmax_scale is None:
+        softmax_scale = float(head_dim) ** -0.5
+    esz = 1 if e4m3 else 2
+    p1 = out.data_ptr() + col0 * esz
+    p2 = None if out2 is None else out2.data_ptr() + col0_2 * esz
+    if not out.is_contiguous() or (out2 is not None and not out2.is_contiguous()):
+        raise ValueError("expected contiguous outputs")
+    st = _lib.lib().lyraq_attention(p1, E4M3 if e4m3 else _dt(qkv), out.shape[-1], _p(out_scale), p2,
+                                    0 if out2 is None else out2.shape[-1], _p(out2_scale), split, _p(qkv), _dt(qkv), batch,
+                                    seq_len, heads, head_dim, float(softmax_scale), _stream())
+    _lib.check(st, "lyraq_attention")
     return out
 
 
