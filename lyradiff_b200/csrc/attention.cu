@@ -42,8 +42,13 @@ constexpr int kSlots     = 5;
 constexpr int kQOffset   = 0;
 constexpr int kRingOffset = kQTiles * kTileBytes;
 constexpr int kBarOffset = kRingOffset + kSlots * kTileBytes;
-constexpr int kSmemTotal = kBarOffset + 256 + 1024;
-constexpr int kThreads   = 320;
+constexpr int kXchgOffset = kBarOffset + 192;           // row maxima / sums passed between the two halves of a row
+constexpr int kSmemUsed  = kXchgOffset + 2 * kQTiles * kTile * 4;
+constexpr int kSmemTotal = 232448;                    // all a block may have; the tiles need 1024-byte alignment, which leaves
+static_assert(kSmemTotal - kSmemUsed >= 768, "");     // room for a base that is only 256-byte aligned
+constexpr int kThreads   = 576;                       // 16 softmax warps, the TMA producer (warp 16), the MMA issuer (warp 17)
+constexpr int kProducerWarp = 16;
+constexpr int kMmaWarp   = 17;
 constexpr int kTmemCols  = 512;
 constexpr float kRescaleThreshold = 8.0f;             // in log2 units
 
@@ -67,6 +72,19 @@ __device__ __forceinline__ float ex2_approx(float x)
     return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+
+// barrier among `count` threads (whole warps) of the block, ids 1..15
+__device__ __forceinline__ void named_bar_sync(int id, int count)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z)
 {
     asm volatile(
@@ -79,9 +97,15 @@ template<typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params p)
 {
-    extern __shared__ uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t*       gen_base  = smem_raw + (smem_base - smem_u32(smem_raw));
+    if (smem_base - smem_u32(smem_raw) + (uint32_t)kSmemUsed > (uint32_t)kSmemTotal) {
+        if (threadIdx.x == 0) {
+            report_timeout(p.status, 0x3001u);  // the aligned layout does not fit: nothing is touched
+        }
+        return;
+    }
     const uint32_t bars      = smem_base + kBarOffset;
     // barriers: q_full | slot_full[5] | slot_empty[5] | s_full[2] | p_ready[2] | pv_done[2]
     const uint32_t q_full = bars;
@@ -92,6 +116,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
     auto pv_done    = [&](int t) { return bars + 8u * (5 + 2 * kSlots + t); };
     uint32_t*     tmem_slot  = reinterpret_cast<uint32_t*>(gen_base + kBarOffset + 8 * (7 + 2 * kSlots));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float*        xchg       = reinterpret_cast<float*>(gen_base + kXchgOffset);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -105,14 +130,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
         }
         for (int t = 0; t < kQTiles; ++t) {
             mbar_init(s_full(t), 1);
-            mbar_init(p_ready(t), 128);
+            mbar_init(p_ready(t), 256);
             mbar_init(pv_done(t), 1);
         }
         *abort_flag = 0;
         fence_barrier_init();
         prefetch_tensormap(&tmap_qkv);
     }
-    if (warp == 9) {
+    if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(tmem_slot), kTmemCols);
         tmem_relinquish();
     }
@@ -130,7 +155,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
     const int n_kv = (p.seq + kTile - 1) / kTile;
     const int col_q = h * kHeadDim, col_k = (p.heads + h) * kHeadDim, col_v = (2 * p.heads + h) * kHeadDim;
 
-    if (warp == 8) {
+    if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             mbar_arrive_expect_tx(q_full, (uint32_t)(kQTiles * kTileBytes));
@@ -184,7 +209,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t kAb = sizeof(T) == 2 && TypeTag<T>::value == LYRAQ_BF16 ? 1u : 0u;
@@ -258,15 +283,23 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax + epilogue, one thread per query row
-        const int      t        = warp >> 2;                                   // query tile
+        // ------------------------------------------------------------------ softmax + epilogue
+        // Two threads per query row: warps 0-7 take keys / output columns 0..63 of their tile, warps 8-15 columns 64..127;
+        // the two halves of a row meet through shared memory for the row maximum (every tile) and the row sum (once).
+        const int      half     = warp >> 3;
+        const int      t        = (warp >> 2) & 1;                             // query tile
         const int      quadrant = warp & 3;                                    // tensor-memory lane quadrant of this warp
+        const int      row_t    = quadrant * 32 + lane;                        // row inside the tile
         const uint32_t lane_off = (uint32_t)(quadrant * 32) << 16;
-        const uint32_t s_addr   = tmem_base + lane_off + (uint32_t)(t * 128);
-        const uint32_t o_addr   = tmem_base + lane_off + (uint32_t)(256 + t * 128);
+        const uint32_t s_addr   = tmem_base + lane_off + (uint32_t)(t * 128 + half * 64);
+        const uint32_t p_addr   = tmem_base + lane_off + (uint32_t)(t * 128 + half * 32);
+        const uint32_t o_addr   = tmem_base + lane_off + (uint32_t)(256 + t * 128 + half * 64);
+        float*         my_slot  = xchg + (half * kQTiles + t) * kTile + row_t;
+        const float*   peer_slot = xchg + ((half ^ 1) * kQTiles + t) * kTile + row_t;
+        const int      pair_bar = 1 + t * 4 + quadrant;                        // named barrier of the two warps of these rows
         const float    c        = p.scale_log2;
         float          m        = -INFINITY;                                   // reference maximum of this row (raw scores)
-        float          l        = 0.0f;                                        // sum of exp2((s - m) c)
+        float          l        = 0.0f;                                        // this half's sum of exp2((s - m) c)
         bool           ok       = true;
 
         for (int j = 0; j < n_kv && ok; ++j) {
@@ -277,30 +310,36 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
                 break;
             }
             tc_fence_after_sync();
-            uint32_t s[128];
+            uint32_t s[64];
             tmem_ld_32x32(s_addr, s);
             tmem_ld_32x32(s_addr + 32, s + 32);
-            tmem_ld_32x32(s_addr + 64, s + 64);
-            tmem_ld_32x32(s_addr + 96, s + 96);
             tmem_ld_wait();
-            const int valid = p.seq - j * kTile;                               // keys of this tile inside the sequence
-            if (valid < kTile) {
+            const int valid = p.seq - j * kTile - half * 64;                   // keys of this half inside the sequence
+            if (valid < 64) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i) {
+                for (int i = 0; i < 64; ++i) {
                     if (i >= valid) {
                         s[i] = 0xff800000u;                                    // -inf: zero-filled keys take no weight
                     }
                 }
             }
-            float mx0 = __uint_as_float(s[0]), mx1 = __uint_as_float(s[1]), mx2 = __uint_as_float(s[2]), mx3 = __uint_as_float(s[3]);
+            float mx0 = max3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
+            float mx1 = max3(__uint_as_float(s[3]), __uint_as_float(s[4]), __uint_as_float(s[5]));
+            float mx2 = max3(__uint_as_float(s[6]), __uint_as_float(s[7]), __uint_as_float(s[8]));
+            float mx3 = max3(__uint_as_float(s[9]), __uint_as_float(s[10]), __uint_as_float(s[11]));
 #pragma unroll
-            for (int i = 4; i < 128; i += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(s[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(s[i + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(s[i + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(s[i + 3]));
+            for (int i = 12; i < 60; i += 8) {
+                mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
+                mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
+                mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
+                mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            mx0 = max3(mx0, __uint_as_float(s[60]), __uint_as_float(s[61]));
+            mx1 = max3(mx1, __uint_as_float(s[62]), __uint_as_float(s[63]));
+            float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            *my_slot = mx;
+            named_bar_sync(pair_bar, 64);
+            mx = fmaxf(mx, *peer_slot);                                        // a half with no valid key contributes -inf
             if (j == 0) {
                 m = mx;
             } else {
@@ -320,44 +359,46 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
                         l *= f;
                     }
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
-                        uint32_t o[32];
-                        tmem_ld_32x32(o_addr + cc * 32, o);
+                    for (int cc = 0; cc < 4; ++cc) {                             // rare path: small pieces keep the registers free
+                        uint32_t o[16];
+                        tmem_ld_32x16(o_addr + cc * 16, o);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
+                        for (int i = 0; i < 16; ++i) {
                             o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
                         }
-                        tmem_st_32x32(o_addr + cc * 32, o);
+                        tmem_st_32x16(o_addr + cc * 16, o);
                     }
                     tmem_st_wait();
                 }
             }
-            const float nmc = -m * c;
-            float sum0 = 0.0f, sum1 = 0.0f, sum2 = 0.0f, sum3 = 0.0f;
+            const float2 c2   = make_float2(c, c);
+            const float  nmc  = -m * c;
+            const float2 nmc2 = make_float2(nmc, nmc);
+            float2 sum_a = make_float2(0.0f, 0.0f), sum_b = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int cc = 0; cc < 8; ++cc) {
+            for (int cc = 0; cc < 4; ++cc) {
                 uint32_t w[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(s[cc * 16 + 2 * i]), c, nmc));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(s[cc * 16 + 2 * i + 1]), c, nmc));
+                    const float2 x = fma_f32x2(make_float2(__uint_as_float(s[cc * 16 + 2 * i]), __uint_as_float(s[cc * 16 + 2 * i + 1])), c2, nmc2);
+                    const float2 e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
                     if (i & 1) {
-                        sum2 += p0;
-                        sum3 += p1;
+                        sum_b = add_f32x2(sum_b, e);
                     } else {
-                        sum0 += p0;
-                        sum1 += p1;
+                        sum_a = add_f32x2(sum_a, e);
                     }
-                    w[i] = Pair<T>::from_f32(p0, p1);
+                    w[i] = Pair<T>::from_f32(e.x, e.y);
                 }
-                // P over the start of S: columns [8 cc, 8 cc + 8) hold keys [16 cc, 16 cc + 16), all already in registers
+                // P over the start of S: columns [8 k, 8 k + 8) hold keys [16 k, 16 k + 16); this half's S is in registers,
+                // and the other half's first columns are overwritten only after the pair barrier above, i.e. after its loads
                 asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                             ::"r"(s_addr + (uint32_t)(cc * 8)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
+                             ::"r"(p_addr + (uint32_t)(cc * 8)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
                                "r"(w[6]), "r"(w[7])
                              : "memory");
             }
-            l += (sum0 + sum1) + (sum2 + sum3);
+            const float2 sum = add_f32x2(sum_a, sum_b);
+            l += sum.x + sum.y;
             tmem_st_wait();
             tc_fence_before_sync();
             mbar_arrive(p_ready(t));
@@ -371,14 +412,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
         }
         if (ok) {
             tc_fence_after_sync();
-            const int row = q0 + t * kTile + quadrant * 32 + lane;            // row inside the sequence
+            *my_slot = l;
+            named_bar_sync(pair_bar, 64);
+            l += *peer_slot;
+            const int row = q0 + t * kTile + row_t;                            // row inside the sequence
             const int part = row >= p.split ? 1 : 0;
             const long long r_out = part ? row - p.split : row;
             const float inv_l = 1.0f / l;
             // rows past the end of the sequence belong to no part (out_scale[1] may be NULL): they load nothing and store nothing
             const float qs = (p.out_e4m3 && row < p.seq) ? 1.0f / ld_f32(p.out_scale[part]) : 1.0f;
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
+            for (int cc = 0; cc < 2; ++cc) {
                 uint32_t o[32];
                 tmem_ld_32x32(o_addr + cc * 32, o);
                 tmem_ld_wait();
@@ -388,7 +432,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
                     for (int i = 0; i < 16; ++i) {
                         w[i] = Pair<T>::from_f32(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l);
                     }
-                    const long long col = (long long)h * kHeadDim + cc * 32;
+                    const long long col = (long long)h * kHeadDim + half * 64 + cc * 32;
                     if (p.out_e4m3) {
                         uint8_t* dst = static_cast<uint8_t*>(p.out[part]) + (long long)b * p.out_batch[part] + r_out * p.out_ld[part] + col;
                         uint32_t q8[8];
@@ -413,7 +457,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
 
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 9) {
+    if (warp == kMmaWarp) {
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
