@@ -9,7 +9,7 @@
 // with initialize / forward / reload_model_from_state_dict / reload_model_from_bin / load_lora_by_name / clear_lora.
 // quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4; the double-stream block keeps net.2 in FP8, as the reference does).
 // Host code only: every device operation is a call into the C ABI of liblyraq.so (include/lyraq.h) on torch's current
-// stream, plus two ATen library calls per block (scaled_dot_product_attention, and addmm for the 16-bit modulation
+// stream (attention included: lyraq_attention), plus one ATen library call per block (addmm for the 16-bit modulation
 // linear of quant_level 1).  torch supplies device memory, the stream and the class registry; nothing here computes.
 // The data flow is the one documented in lyradiff_b200/flux_blocks.py, which is the Python twin of this file.
 #include <ATen/cuda/CUDAContext.h>
@@ -322,11 +322,18 @@ void check_inputs(std::initializer_list<Tensor> ts, at::ScalarType dt)
     }
 }
 
-Tensor attention(const Tensor& qkv, int64_t B, int64_t S, int64_t H, int64_t Dh)
+// FlashAttention2Layer<T>::forward of the reference (layers/flash_attn2/flash_attn2.cu:59-118) on the packed, normalised
+// and rotated projection qkv [B, S, 3, H, Dh]: lyraq_attention.  `out` is [B * rows, ld] in the inference type or, when
+// `scale` is given, e4m3 codes for the FP8 linear that follows (the reference's separate cast pass); with `out2` the rows
+// from `split` on of every batch go there (text and image parts of a joint sequence).
+void attention(const Tensor& qkv, int64_t B, int64_t S, int64_t H, int64_t Dh, at::ScalarType dtype, uint8_t* out, int64_t ld,
+               const Tensor* scale, uint8_t* out2 = nullptr, int64_t ld2 = 0, const Tensor* scale2 = nullptr, int64_t split = 0)
 {
-    Tensor v5 = qkv.view({B, S, 3, H, Dh});
-    Tensor q = v5.select(2, 0).transpose(1, 2), k = v5.select(2, 1).transpose(1, 2), v = v5.select(2, 2).transpose(1, 2);
-    return at::scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape({B, S, H * Dh});
+    const int dtc = dt_code(dtype);
+    check(lyraq_attention(out, scale != nullptr ? LYRAQ_E4M3 : dtc, (size_t)ld, scale != nullptr ? scale->data_ptr<float>() : nullptr,
+                          out2, (size_t)ld2, scale2 != nullptr ? scale2->data_ptr<float>() : nullptr, (size_t)split, qkv.data_ptr(),
+                          dtc, (size_t)B, (size_t)S, (int)H, (int)Dh, 1.0f / std::sqrt((float)Dh), stream()),
+          "lyraq_attention");
 }
 
 }  // namespace
@@ -528,12 +535,10 @@ struct FluxSingleTransformerBlockOp: BlockBase {
         check(lyraq_rmsnorm_rope(q3.data_ptr(), q3.data_ptr(), qk_scale.data_ptr(), rope.data_ptr(), dtc, 1e-6, (size_t)B, (size_t)S,
                                  (int)heads, (int)head_dim, stream()),
               "lyraq_rmsnorm_rope");
-        Tensor attn = attention(q3, B, S, heads, head_dim).reshape({T, D}).contiguous();
+        // the attention output leaves the kernel as e4m3 in the first column window of proj_out's [T, (mlp_scale + 1) D] input
         const int64_t ld = (mlp_scale + 1) * D;
         Tensor cat8 = at::empty({T, ld}, opt8);
-        check(lyraq_quant_fp8_2d(cat8.data_ptr<uint8_t>(), (size_t)ld, attn.data_ptr(), dtc, out.input_scale.data_ptr<float>(),
-                                 (size_t)T, (size_t)D, stream()),
-              "lyraq_quant_fp8_2d");
+        attention(q3, B, S, heads, head_dim, dtype, cat8.data_ptr<uint8_t>(), ld, &out.input_scale);
         check(lyraq_gemm_fp8_quant_ld(mq.data_ptr<uint8_t>(), mlp.input_scale.data_ptr<float>(), mlp.qweight.data_ptr<uint8_t>(),
                                       mlp.w_scale.data_ptr<float>(), cat8.data_ptr<uint8_t>() + D, (size_t)ld,
                                       out.input_scale.data_ptr<float>(), dtc, ptr(mlp.bias), nullptr, 1.0f, 0.0f,
@@ -557,7 +562,8 @@ Tensor FluxSingleTransformerBlockOp::forward_int4(const Tensor& hidden, const Te
     check(lyraq_rmsnorm_rope(q3.data_ptr(), q3.data_ptr(), qk_scale.data_ptr(), rope.data_ptr(), dtc, 1e-6, (size_t)B, (size_t)S,
                              (int)heads, (int)head_dim, stream()),
           "lyraq_rmsnorm_rope");
-    Tensor attn = attention(q3, B, S, heads, head_dim).reshape({T, D}).contiguous();
+    Tensor attn = at::empty({T, D}, hidden.options());
+    attention(q3, B, S, heads, head_dim, dtype, static_cast<uint8_t*>(attn.data_ptr()), D, nullptr);
     Tensor act  = mlp4.run(norm16, T, Tensor(), dtype);
     Tensor h1   = out4_attn.run(attn, T, Tensor(), dtype);
     Tensor h    = out4_mlp.run(act, T, h1, dtype);
@@ -701,11 +707,7 @@ struct FluxTransformerBlockOp: BlockBase {
                   "lyraq_quant_fp8");
             return fp8_gemm_gate_residual(s.ff2, f1q, mod[5], h, B, S, dtype);
         }
-        Tensor aq = at::empty({T, D}, opt8);
-        check(lyraq_quant_fp8(aq.data_ptr<uint8_t>(), attn.data_ptr(), dtc, s.out.input_scale.data_ptr<float>(), 1, (size_t)(T * D),
-                              stream()),
-              "lyraq_quant_fp8");
-        Tensor h  = fp8_gemm_gate_residual(s.out, aq, mod[2], x, B, S, dtype);
+        Tensor h  = fp8_gemm_gate_residual(s.out, attn, mod[2], x, B, S, dtype);  // attn: e4m3 codes from the attention kernel
         Tensor nq = at::empty({T, D}, opt8);
         check(lyraq_adaln_quant(nullptr, nullptr, nullptr, nq.data_ptr<uint8_t>(), s.ff1.input_scale.data_ptr<float>(), h.data_ptr(),
                                 mod[4].data_ptr(), mod[3].data_ptr(), dtc, nullptr, (size_t)B, (size_t)S, (size_t)D, 1e-6, stream()),
@@ -755,9 +757,13 @@ struct FluxTransformerBlockOp: BlockBase {
                                      r[b].slice(0, E, tot).data_ptr(), dtc, 1e-6, 1, (size_t)S, (int)heads, (int)head_dim, stream()),
                   "lyraq_rmsnorm_rope");
         }
-        Tensor attn   = attention(joint, B, tot, heads, head_dim);
-        Tensor attn_t = attn.slice(1, 0, E).reshape({B * E, D}).contiguous();
-        Tensor attn_i = attn.slice(1, E, tot).reshape({B * S, D}).contiguous();
+        // one attention over the joint sequence; its text rows and image rows leave as the inputs of the two to_out linears
+        // (e4m3 with each linear's input scale; the 16-bit type for the W4A4 linears, which quantize their own input)
+        const auto opt_a = int4() ? hidden.options() : hidden.options().dtype(at::kByte);
+        Tensor attn_t = at::empty({B * E, D}, opt_a), attn_i = at::empty({B * S, D}, opt_a);
+        attention(joint, B, tot, heads, head_dim, dtype, static_cast<uint8_t*>(attn_t.data_ptr()), D,
+                  int4() ? nullptr : &txt.out.input_scale, static_cast<uint8_t*>(attn_i.data_ptr()), D,
+                  int4() ? nullptr : &img.out.input_scale, E);
         Tensor out_i  = post_attention(img, hidden, attn_i, mod_i);
         Tensor out_t  = post_attention(txt, encoder, attn_t, mod_t);
         return {out_i, out_t};

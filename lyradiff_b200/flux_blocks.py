@@ -11,9 +11,8 @@ method names and tensor conventions, running the FP8 data flow of FluxSingleTran
     msa = linear(temb)                       -> shift, scale, gate            (temb arrives SiLU'd, AdaFP8LayerNorm.cc:100)
     norm = LN(x) * (1 + scale) + shift       -> two e4m3 forms in one kernel  (lyraq_adaln_quant_fp8x2)
     qkv = FP8 GEMM(norm_q8, to_qkv) + bias   -> QK RMSNorm + RoPE in place    (lyraq_gemm_fp8, lyraq_rmsnorm_rope)
-    attn = attention(q, k, v)                                                 (torch SDPA: library code, as the reference's
-                                                                              flash-attention layer is; not this path)
-    cat8[:, :D]  = e4m3(attn)                                                 (lyraq_quant_fp8_2d)
+    cat8[:, :D]  = e4m3(attention(q, k, v))                                   (lyraq_attention: tcgen05 attention forward
+                                                                              with the e4m3 quantize in its epilogue)
     cat8[:, D:]  = e4m3(gelu(FP8 GEMM(e4m3(norm), proj_mlp) + bias))          (lyraq_gemm_fp8_quant_ld)
     out = gate * (FP8 GEMM(cat8, proj_out) + bias) + x                        (lyraq_gemm_fp8_gate: one launch)
 
@@ -311,9 +310,8 @@ class FluxSingleTransformerBlockOp:
         qkv = self._buffer("qkv", (T, 3 * D), dt, dev)
         w["qkv"].forward(norm, out=qkv)
         ops.invoke_fused_rmsnorm_and_rope(qkv, qkv, w["qk_scale"], rope_emb, 1e-6, B, S, self.heads, self.head_dim)
-        v5 = qkv.view(B, S, 3, self.heads, self.head_dim)
-        q, k, v = (v5[:, :, i].transpose(1, 2) for i in range(3))
-        attn = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(T, D)
+        attn = self._buffer("attn16", (T, D), dt, dev)
+        ops.flash_attention(qkv, B, S, self.heads, self.head_dim, out=attn)
         mlp = self._buffer("mlp16", (T, self.mlp_scale * D), dt, dev)
         w["mlp"].forward(norm, out=mlp)
         h1 = self._buffer("h1", (T, D), dt, dev)
@@ -378,14 +376,11 @@ class FluxSingleTransformerBlockOp:
         qkv = self._buffer("qkv", (T, 3 * D), dt, dev)
         ops.gemm_with_residual_and_bias_fp8(w["qkv"].qweight, w["qkv"].w_scale, norm_q, w["qkv"].input_scale, qkv, bias=w["qkv"].bias)
         ops.invoke_fused_rmsnorm_and_rope(qkv, qkv, w["qk_scale"], rope_emb, 1e-6, B, S, self.heads, self.head_dim)
-        v5 = qkv.view(B, S, 3, self.heads, self.head_dim)
-        q, k, v = (v5[:, :, i].transpose(1, 2) for i in range(3))          # [B, H, S, Dh] views of the packed buffer
-        attn = torch.nn.functional.scaled_dot_product_attention(q, k, v)    # library attention (outside this path)
-        attn = attn.transpose(1, 2).reshape(T, D)
 
-        # ---- proj_out input [T, (mlp_scale + 1) * D] in e4m3, filled in place by its two producers
+        # ---- proj_out input [T, (mlp_scale + 1) * D] in e4m3, filled in place by its two producers: the attention kernel
+        # writes its output as e4m3 into the first D columns, the proj_mlp GEMM its GELU output into the rest
         cat8 = self._buffer("cat8", (T, (self.mlp_scale + 1) * D), torch.uint8, dev)
-        ops.quant_fp8_into_columns(cat8, 0, attn, w["out"].input_scale)
+        ops.flash_attention(qkv, B, S, self.heads, self.head_dim, out=cat8, out_scale=w["out"].input_scale)
         ops.gemm_fp8_quant_into_columns(w["mlp"].qweight, w["mlp"].w_scale, mlp_in, w["mlp"].input_scale, cat8, D,
                                         w["out"].input_scale, dt, bias=w["mlp"].bias, is_gelu=True)
 
@@ -437,7 +432,7 @@ class FluxTransformerBlockOp:
 
         shift, scale, gate, shift2, scale2, gate2 = linear(temb)
         qkv  = FP8 GEMM(e4m3(LN(x)(1+scale)+shift), to_qkv) + bias        (AdaLN + quantize in one kernel)
-        both streams: QK RMSNorm + RoPE into one [B, S_txt + S_img] buffer (text first), joint attention (torch SDPA)
+        both streams: QK RMSNorm + RoPE into one [B, S_txt + S_img] buffer (text first), joint attention (lyraq_attention, e4m3 out per stream)
         h    = x + gate * (FP8 GEMM(e4m3(attn), to_out) + bias)
         ff   = FP8 GEMM(e4m3(gelu(FP8 GEMM(e4m3(LN(h)(1+scale2)+shift2), net.0.proj) + bias)), net.2) + bias
         out  = h + gate2 * ff              (the quantize between the two FF linears is fused into the first GEMM's epilogue)
@@ -569,8 +564,7 @@ class FluxTransformerBlockOp:
         dev, dt = x.device, self.dtype
         if w.get("int4"):
             return self._post_attention_int4(w, x, attn, mod)
-        aq = torch.empty(T, D, dtype=torch.uint8, device=dev)
-        ops.invoke_cuda_d2d_scale_cpy_convert(aq, attn, w["out"].input_scale)
+        aq = attn                                  # e4m3 codes, quantized with to_out's input scale by the attention kernel
         y = torch.empty(T, D, dtype=dt, device=dev)
         h = torch.empty_like(x)
         if not ops.gemm_fp8_gate_residual(w["out"].qweight, w["out"].w_scale, aq, w["out"].input_scale, h.view(T, D), mod[2],
@@ -638,13 +632,17 @@ class FluxTransformerBlockOp:
         for b in range(B):
             ops.invoke_fused_rmsnorm_and_rope(joint[b, :E], qt[b], wt["qk_scale"], rope[b, :E], 1e-6, 1, E, self.heads, self.head_dim)
             ops.invoke_fused_rmsnorm_and_rope(joint[b, E:], qi[b], wi["qk_scale"], rope[b, E:], 1e-6, 1, S, self.heads, self.head_dim)
-        v5 = joint.view(B, tot, 3, self.heads, self.head_dim)
-        q, k, v = (v5[:, :, i].transpose(1, 2) for i in range(3))
-        attn = torch.nn.functional.scaled_dot_product_attention(q, k, v).transpose(1, 2).reshape(B, tot, D)
-        attn_t = attn[:, :E].reshape(B * E, D)
-        attn_i = attn[:, E:].reshape(B * S, D)
-        out_i = self._post_attention(wi, hidden_states, attn_i.contiguous(), mod_i)
-        out_t = self._post_attention(wt, encoder_hidden_states, attn_t.contiguous(), mod_t)
+        # one attention over the joint sequence; text rows and image rows leave as the inputs of the two to_out linears:
+        # e4m3 with each linear's input scale (FP8), or 16-bit for the W4A4 linears, which quantize their own input
+        int4 = bool(wi.get("int4"))
+        adt = self.dtype if int4 else torch.uint8
+        attn_t = torch.empty(B * E, D, dtype=adt, device=hidden_states.device)
+        attn_i = torch.empty(B * S, D, dtype=adt, device=hidden_states.device)
+        ops.flash_attention(joint.view(B * tot, 3 * D), B, tot, self.heads, self.head_dim, out=attn_t,
+                            out_scale=None if int4 else wt["out"].input_scale, out2=attn_i,
+                            out2_scale=None if int4 else wi["out"].input_scale, split=E)
+        out_i = self._post_attention(wi, hidden_states, attn_i, mod_i)
+        out_t = self._post_attention(wt, encoder_hidden_states, attn_t, mod_t)
         return [out_i, out_t]
 
     __call__ = forward
