@@ -93,6 +93,17 @@ class ClockSampler(threading.Thread):
                 "samples": len(s)}
 
 
+def tensor_peak(peaks, mode, factor, what):
+    """Measured tensor peak for the denominator of a roofline fraction.  mode "burst": the timed region is a short burst at
+    flat clocks (a kernel timed alone) -> bf16_tflops; "sustained": a seconds-long region under the power cap ->
+    bf16_tflops_sustained.  factor 2 for FP8 / INT8 (no FP8 peak is measured on this pool; dense FP8 / INT8 runs at twice
+    the bf16 rate), 1 for 16-bit."""
+    key = "bf16_burst" if mode == "burst" else "bf16_sustained"
+    name = "bf16_tflops" if mode == "burst" else "bf16_tflops_sustained"
+    return factor * peaks[key], "%s%s of MEASURED_PEAKS.json (%s, %s denominator)%s" % (
+        "2 x " if factor == 2 else "", name, peaks["source"], mode, what)
+
+
 def _gen(seed=0):
     return torch.Generator().manual_seed(seed)
 
@@ -175,9 +186,9 @@ class FluxFp8:
             if events is not None:
                 events[i][1].record()
 
-    def peak(self, peaks):
-        return 2.0 * peaks["bf16_sustained"], ("2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s): dense FP8 runs at "
-                                               "twice the bf16 rate; nominal dense FP8 is 4500" % peaks["source"]), 4500.0
+    def peak(self, peaks, mode):
+        v, src = tensor_peak(peaks, mode, 2, ": dense FP8 at twice the bf16 rate; nominal dense FP8 is 4500")
+        return v, src, 4500.0
 
     # ---- CPU restatement on a row sample
     def setup_cpu(self, rows):
@@ -237,22 +248,34 @@ class Int8Sdxl:
         self.roof = {"bound": "hbm", "unit": "GB/s", "kernel": "gemm_tcgen05_kernel<i8> (1 launch per step)"}
         self.traffic = 39.7e6 if T == 8192 else None  # profiles/gemm_tcgen05_int8_sdxl.md (most of the output is still in L2)
 
+    @staticmethod
+    def _inputs(rows, k, n):
+        """Seeded inputs of configs[0]: X ~ N(0,1) with 5 % of the channels scaled x20, W ~ N(0,0.02), bias ~ N(0,0.02), and the
+        SmoothQuant vector s_j = max|X_j|^0.5 / max|W_j|^0.5 (activations are multiplied by pre = 1/s)."""
+        g = _gen()
+        x = torch.randn(rows, k, generator=g)
+        x[:, torch.randperm(k, generator=g)[:max(1, (k * 5) // 100)]] *= 20.0
+        w = (torch.randn(n, k, generator=g) * 0.02).half()
+        bias = (torch.randn(n, generator=g) * 0.02).half()
+        x = x.half()
+        smooth = x.float().abs().amax(dim=0).sqrt() / w.float().abs().amax(dim=0).sqrt()
+        return x, w, bias, (1.0 / smooth).float()
+
     def setup_gpu(self, dev):
         from lyradiff_b200 import ops
-        from oracle import workloads
         self.ops = ops
-        wl = workloads.int8_smoothquant_linear(m=self.tokens, k=self.K, n=self.N, seed=0)
-        self.x = wl["x"].to(dev)
-        self.pre = wl["pre"].to(dev)
-        self.qw = wl["qw"].to(dev)
-        self.s_w = wl["s_w"].to(dev)
-        self.bias = wl["bias"].to(dev)
+        x, w, bias, pre = self._inputs(self.tokens, self.K, self.N)
+        self.x, self.pre, self.bias = x.to(dev), pre.to(dev), bias.to(dev)
+        # the folded weight W / pre is quantized per output channel by the library's own load-time kernel
+        self.qw = torch.empty(self.N, self.K, dtype=torch.int8, device=dev)
+        self.s_w = torch.empty(self.N, dtype=torch.float32, device=dev)
+        ops.invoke_get_int8_weight_scale(self.s_w, self.qw, w.to(dev), self.pre)
         self.qa = torch.empty(self.tokens, self.K, dtype=torch.int8, device=dev)
         self.sa = torch.empty(self.tokens, dtype=torch.float32, device=dev)
         self.y = torch.empty(self.tokens, self.N, dtype=torch.float16, device=dev)
         # a second output buffer alternates with the first so that consecutive steps do not rewrite lines still in L2
         self.y2 = torch.empty_like(self.y)
-        self.h_in = wl["x"].pin_memory()
+        self.h_in = x.pin_memory()
         self.e2e_x = [self.x, torch.empty_like(self.x)]
         self.e2e_y = [self.y, self.y2]
         self.flip = False
@@ -269,13 +292,14 @@ class Int8Sdxl:
         if events is not None:
             events[0][1].record()
 
-    def peak(self, peaks):
+    def peak(self, peaks, mode):
         return peaks["hbm_gbs"], "hbm_gbs of MEASURED_PEAKS.json (%s); the fp16 output store bounds this shape" % peaks["source"], 7700.0
 
     def setup_cpu(self, rows):
-        from oracle import workloads
-        self.cpu = workloads.int8_smoothquant_linear(m=rows, k=self.K, n=self.N, seed=0)
-        self.cpu["qw_t"] = self.cpu["qw"].t().contiguous()
+        from oracle import quant as oq
+        x, w, bias, pre = self._inputs(rows, self.K, self.N)
+        qw, s_w = oq.int8_weight_quant_device(w, pre)
+        self.cpu = {"x": x, "pre": pre, "bias": bias, "s_w": s_w, "qw_t": qw.t().contiguous()}
         self.cpu_rows = rows
 
     def step_cpu(self):
@@ -355,9 +379,9 @@ class SdxlFF:
         if events is not None:
             events[1][1].record()
 
-    def peak(self, peaks):
-        return 2.0 * peaks["bf16_sustained"], ("2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s) as the dense INT8 tensor "
-                                               "rate; at K = 640 the fp16 store of the first GEMM bounds the block" % peaks["source"]), 4500.0
+    def peak(self, peaks, mode):
+        v, src = tensor_peak(peaks, mode, 2, " as the dense INT8 rate; at K = 640 the fp16 store of the first GEMM bounds the block")
+        return v, src, 4500.0
 
     def setup_cpu(self, rows):
         g = _gen()
@@ -390,13 +414,13 @@ class SdxlFF:
 
 
 class FluxBlock:
-    """One FLUX.1-dev single-stream block through lyradiff_b200.flux_blocks.FluxSingleTransformerBlockOp (the per-block
-    unit of configs[4]): modulation, AdaLN + quantize, QKV, QK-norm + RoPE, attention (torch SDPA, library), MLP, proj_out,
-    gate + residual at 4608 tokens."""
+    """One FLUX.1-dev single-stream block through torch.classes.lyradiff.FluxSingleTransformerBlockOp (the C++ class; the
+    per-block unit of configs[4]): modulation, AdaLN + quantize, QKV, QK-norm + RoPE, attention, MLP, proj_out, gate +
+    residual at 4608 tokens.  --python-mirror runs lyradiff_b200.flux_blocks instead (same launches, same bits)."""
     name = "flux_block"
     metric = "flux_single_block_throughput"
     unit = "TFLOP/s"
-    dtype = "e4m3 linears (f32 accumulate in TMEM) + bf16 library attention"
+    dtype = "e4m3 linears (f32 accumulate in TMEM) + bf16 attention (f32 scores and accumulation in TMEM)"
     D, H, DH, MLP = 3072, 24, 128, 4
 
     def __init__(self, tokens):
@@ -408,16 +432,16 @@ class FluxBlock:
         self.scale = 1e12
         self.workload = ("one FLUX.1-dev single-stream block (the unit configs[4] repeats 38 times), FP8_W8A8, batch 1, %d tokens, "
                          "hidden 3072, 24 x 128 heads, random weights: %.3f TFLOP in FP8 linears + %.3f TFLOP in bf16 attention "
-                         "(torch SDPA); the resident-input step is replayed as a CUDA graph" % (T, self.lin_flops / 1e12, self.attn_flops / 1e12))
-        self.launches_per_step = 6
+                         "(this library's tcgen05 kernel); the resident-input step is replayed as a CUDA graph" % (T, self.lin_flops / 1e12, self.attn_flops / 1e12))
+        self.launches_per_step = 6   # AdaLN+quantize, QKV GEMM, QK-norm+RoPE, attention (e4m3 out), MLP GEMM, proj_out GEMM
         self.timed_names = ["block_forward"]
         self.timed_work = [self.work_per_step]
         self.roof = {"bound": "tensor", "unit": "TFLOP/s",
-                     "kernel": "whole block: 3 gemm_tcgen05_kernel<f8f6f4> launches + 3 element-wise kernels of this library, "
-                               "plus the library attention and one small library matmul"}
+                     "kernel": "whole block: 3 gemm_tcgen05_kernel<f8f6f4> launches, attention_fwd_kernel and 2 element-wise kernels "
+                               "of this library, plus one small library matmul (the 16-bit modulation linear)"}
         self.traffic = None
 
-    def _state_dict(self, g):
+    def _state_dict(self, g, on_gpu=False):
         D, M = self.D, self.MLP
         p = "single_transformer_blocks.0."
         sd = {}
@@ -439,13 +463,24 @@ class FluxBlock:
             1, rows, self.DH // 2, 2, 2).bfloat16()
         return x, temb, rope
 
+    use_mirror = False  # bench.py --python-mirror
+
+    def _namespace(self):
+        """The classes the step runs through: the C++ torch custom classes, or their Python mirrors."""
+        if self.use_mirror:
+            from lyradiff_b200 import flux_blocks, flux_model
+            return flux_blocks, flux_model
+        from lyradiff_b200 import torch_classes
+        ns = torch_classes.load()
+        return ns, ns
+
     def setup_gpu(self, dev):
-        from lyradiff_b200 import flux_blocks
+        blocks_ns, _ = self._namespace()
         g = _gen()
-        prefix, sd = self._state_dict(g)
-        self.op = flux_blocks.FluxSingleTransformerBlockOp("bf16", self.D, self.H, self.DH, self.MLP, getattr(self, "quant_level", 1))
-        self.op.initialize(flux_blocks.LyraDiffCommonContext())
-        self.op.reload_model_from_state_dict(prefix, sd, dev)
+        prefix, sd = self._state_dict(g, on_gpu=True)
+        self.op = blocks_ns.FluxSingleTransformerBlockOp("bf16", self.D, self.H, self.DH, self.MLP, getattr(self, "quant_level", 1))
+        self.op.initialize(blocks_ns.LyraDiffCommonContext())
+        self.op.reload_model_from_state_dict(prefix, sd, "cpu")
         x, temb, rope = self._inputs(g, self.tokens)
         self.x, self.temb, self.rope = x.to(dev), temb.to(dev), rope.to(dev)
         self.y = torch.empty_like(self.x)
@@ -485,12 +520,13 @@ class FluxBlock:
         if events is not None:
             events[0][1].record()
 
-    def peak(self, peaks):
-        p8, p16 = 2.0 * peaks["bf16_sustained"], peaks["bf16_sustained"]
-        blend = self.work_per_step / (self.lin_flops / p8 + self.attn_flops / p16)
+    def peak(self, peaks, mode):
+        p16, _ = tensor_peak(peaks, mode, 1, "")
+        blend = self.work_per_step / (self.lin_flops / (2.0 * p16) + self.attn_flops / p16)
         nominal = self.work_per_step / (self.lin_flops / 4500.0 + self.attn_flops / 2250.0)
-        return blend, ("FLOP-weighted blend of 2 x bf16_tflops_sustained (FP8 linears) and bf16_tflops_sustained (attention) of "
-                       "MEASURED_PEAKS.json (%s)" % peaks["source"]), nominal
+        name = "bf16_tflops" if mode == "burst" else "bf16_tflops_sustained"
+        return blend, ("FLOP-weighted blend of 2 x %s (FP8 linears) and %s (attention) of MEASURED_PEAKS.json (%s, %s denominator)"
+                       % (name, name, peaks["source"], mode)), nominal
 
     def setup_cpu(self, rows):
         g = _gen()
@@ -521,12 +557,11 @@ class FluxBlockInt4(FluxBlock):
     def __init__(self, tokens):
         super().__init__(tokens)
         self.workload = self.workload.replace("FP8_W8A8", "INT4_W4A4 (rank-32 LoRA branches)").replace("in FP8 linears", "in W4A4 linears")
-        self.launches_per_step = 15
-        self.roof["kernel"] = ("whole block: 4 x (int4 quantize, LoRA-down, gemm_w4a4_kernel) + AdaLN, QK-norm/RoPE and gate kernels of "
-                               "this library, plus the library attention and one small library matmul")
+        self.launches_per_step = 16
+        self.roof["kernel"] = ("whole block: 4 x (int4 quantize, LoRA-down, gemm_w4a4_kernel) + AdaLN, QK-norm/RoPE, attention and gate "
+                               "kernels of this library, plus one small library matmul")
 
-    def _state_dict(self, g):
-        from oracle import quant
+    def _state_dict(self, g, on_gpu=False):
         D, M = self.D, self.MLP
         p = "single_transformer_blocks.0."
         sd = {p + "norm.linear.weight": (torch.randn(3 * D, D, generator=g) * 0.02).bfloat16(),
@@ -534,7 +569,16 @@ class FluxBlockInt4(FluxBlock):
               p + "attn.norm_q.weight": torch.ones(self.DH).bfloat16(), p + "attn.norm_k.weight": torch.ones(self.DH).bfloat16()}
         for name, n, k, bias in (("attn.to_qkv.", 3 * D, D, True), ("proj_mlp.", M * D, D, True), ("proj_out.linears.0.", D, D, True),
                                  ("proj_out.linears.1.linear.", D, M * D, False)):
-            pw, sw, _ = quant.int4_weight_quant_g64((torch.randn(n, k, generator=g) * 0.02).bfloat16())
+            w = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+            if on_gpu:   # the product packs its own weights (lyraq_weight_quant_int4_g64)
+                from lyradiff_b200 import ops
+                pw = torch.empty(n, k // 2, dtype=torch.uint8, device="cuda")
+                sw = torch.empty(n, k // 64, dtype=torch.float32, device="cuda")
+                ops.weight_quant_int4_g64(pw, sw, w.cuda())
+                pw, sw = pw.cpu(), sw.cpu()
+            else:        # CPU baseline: the oracle's restatement of the same rule
+                from oracle import quant
+                pw, sw, _ = quant.int4_weight_quant_g64(w)
             sd[p + name + "packed_weight"], sd[p + name + "weight_scale"] = pw, sw
             sd[p + name + "smooth"] = 0.5 + torch.rand(k, generator=g)
             sd[p + name + "lora_down"] = (torch.randn(32, k, generator=g) * 0.02).bfloat16()
@@ -554,7 +598,7 @@ class FluxBlockInt4(FluxBlock):
 
 
 class FluxForward(FluxBlock):
-    """configs[4]: the whole FLUX.1-dev transformer through lyradiff_b200.flux_model.FluxTransformer2DModelOp -- embedders,
+    """configs[4]: the whole FLUX.1-dev transformer through torch.classes.lyradiff.FluxTransformer2DModelOp -- embedders,
     19 double-stream + 38 single-stream blocks (each with its own random FP8 weights), norm_out and proj_out -- one image
     (4096 image + 512 text tokens) per GPU."""
     name = "flux_forward"
@@ -573,14 +617,14 @@ class FluxForward(FluxBlock):
                          "norm_out / proj_out, FP8_W8A8, random weights (each block its own), 1 image per GPU = %d image + %d text "
                          "tokens, hidden 3072, 24 x 128 heads; one step = one forward = one denoising step = %.1f TFLOP"
                          % (self.N_DOUBLE, self.N_SINGLE, S, self.TXT, self.work_per_step / 1e12))
-        self.launches_per_step = self.N_DOUBLE * 16 + self.N_SINGLE * 6 + 1
+        self.launches_per_step = self.N_DOUBLE * 15 + self.N_SINGLE * 6 + 1
         self.timed_names = ["transformer_forward"]
         self.timed_work = [self.work_per_step]
-        self.roof["kernel"] = "whole model: 57 blocks, each 3 or 8 gemm_tcgen05_kernel<f8f6f4> launches + element-wise kernels of this " \
-                              "library, plus library attention, the small modulation matmuls and the 16-bit embedders / output layer"
+        self.roof["kernel"] = "whole model: 57 blocks, each 3 or 8 gemm_tcgen05_kernel<f8f6f4> launches + attention_fwd_kernel + " \
+                              "element-wise kernels of this library, plus the small 16-bit modulation matmuls, embedders and output layer"
 
     def setup_gpu(self, dev):
-        from lyradiff_b200 import flux_blocks, flux_model
+        blocks_ns, model_ns = self._namespace()
         D, M, DH = self.D, self.MLP, self.DH
         g = torch.Generator(device=dev).manual_seed(0)
         sd = {}
@@ -618,14 +662,19 @@ class FluxForward(FluxBlock):
         for name, d_in in (("timestep_embedder", 256), ("guidance_embedder", 256), ("text_embedder", self.POOLED)):
             lin("time_text_embed.%s.linear_1" % name, D, d_in, quantized=False)
             lin("time_text_embed.%s.linear_2" % name, D, D, quantized=False)
-        self.op = flux_model.FluxTransformer2DModelOp("bf16", self.IN_CH, self.N_DOUBLE, self.N_SINGLE, DH, self.H, self.POOLED,
-                                                      self.JOINT, True, 1)
-        self.op.initialize(flux_blocks.LyraDiffCommonContext())
+        self.op = model_ns.FluxTransformer2DModelOp("bf16", self.IN_CH, self.N_DOUBLE, self.N_SINGLE, DH, self.H, self.POOLED,
+                                                    self.JOINT, True, 1)
+        self.op.initialize(blocks_ns.LyraDiffCommonContext())
         self.op.reload_transformer_model_from_state_dict(sd, "cuda")
         del sd
         cg = _gen()
         S = self.tokens - self.TXT
-        _, _, rope = self._inputs(cg, self.tokens)
+        from lyradiff_b200 import rope as rope_host
+        side = int(round(S ** 0.5))
+        if side * side == S:   # the table FLUX builds from its position ids: text rows (0,0,0), image rows (0, y, x)
+            rope = rope_host.flux_rope_table(rope_host.flux_position_ids(self.TXT, side, side))[:, 0].bfloat16()
+        else:
+            _, _, rope = self._inputs(cg, self.tokens)
         img = torch.randn(1, S, self.IN_CH, generator=cg).bfloat16()
         self.txt = torch.randn(1, self.TXT, self.JOINT, generator=cg).bfloat16().to(dev)
         self.pooled = torch.randn(1, self.POOLED, generator=cg).bfloat16().to(dev)
@@ -637,6 +686,21 @@ class FluxForward(FluxBlock):
 
     def _forward(self, img):
         return self.op.transformer_forward(img, self.txt, self.rope, self.pooled, 500.0, 3500.0)
+
+    def verify(self):
+        """Before anything is timed: the full 19 + 38-block forward gives a finite result of sane amplitude, and the same
+        bits twice (every sum inside has a fixed order).  The per-block parity against the oracle is what tests/ checks."""
+        a = self._forward(self.x).float()
+        b = self._forward(self.x).float()
+        torch.cuda.synchronize()
+        if not bool(torch.isfinite(a).all()):
+            raise SystemExit("bench.py: the forward's output is not finite")
+        if not torch.equal(a, b):
+            raise SystemExit("bench.py: two forwards of the same input differ")
+        amp = float(a.abs().mean())
+        if not (1e-4 < amp < 1e4):
+            raise SystemExit("bench.py: output amplitude %g out of range" % amp)
+        return "output finite, mean |y| = %.4g, identical bits on a second forward" % amp
 
     def setup_cpu(self, rows):
         # the CPU baseline of this case is the single-stream block of the stack on a row sample (its work is counted per block)
@@ -697,10 +761,10 @@ class W4A4:
         if events is not None:
             events[0][1].record()
 
-    def peak(self, peaks):
-        return 2.0 * peaks["bf16_sustained"], ("2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s) as the dense INT8 tensor "
-                                               "rate; this kernel is bound by the per-group fp32 rescale on the CUDA cores, "
-                                               "not by the tensor pipe" % peaks["source"]), 4500.0
+    def peak(self, peaks, mode):
+        v, src = tensor_peak(peaks, mode, 2, " as the dense INT8 rate; the kernel is bound by the per-group fp32 rescale on the CUDA "
+                             "cores, not by the tensor pipe")
+        return v, src, 4500.0
 
     def setup_cpu(self, rows):
         from oracle import quant as oq
@@ -773,7 +837,7 @@ class AdalnQuant:
         if events is not None:
             events[0][1].record()
 
-    def peak(self, peaks):
+    def peak(self, peaks, mode):
         return peaks["hbm_gbs"], "hbm_gbs of MEASURED_PEAKS.json (%s)" % peaks["source"], 7700.0
 
     def setup_cpu(self, rows):
@@ -790,10 +854,79 @@ class AdalnQuant:
     cpu_note = "LayerNorm + modulation + int8 and e4m3 quantize"
 
 
-CASES = {c.name: c for c in (FluxFp8, FluxBlock, FluxBlockInt4, FluxForward, Int8Sdxl, SdxlFF, W4A4, AdalnQuant)}
+class Attention:
+    """The attention of one FLUX block (the 20 % of configs[4]'s FLOPs outside the linears): 4608 tokens, 24 heads x 128,
+    bf16, packed QKV in, e4m3 out into the proj_out input window."""
+    name = "attention"
+    metric = "flux_attention_throughput"
+    unit = "TFLOP/s"
+    dtype = "bf16 (f32 scores and accumulation in TMEM, bf16 probabilities), e4m3 out"
+    H, DH = 24, 128
+
+    def __init__(self, tokens):
+        self.tokens = tokens or 4608
+        T = self.tokens
+        self.work_per_step = 4.0 * T * T * self.H * self.DH
+        self.scale = 1e12
+        self.workload = ("attention of one FLUX.1-dev block: softmax(q k^T / sqrt(128)) v over %d tokens, 24 heads x 128, packed bf16 "
+                         "QKV [%d, 9216] in, e4m3 [%d, 3072] out (per-tensor scale)" % (T, T, T))
+        self.launches_per_step = 1
+        self.timed_names = ["attention"]
+        self.timed_work = [self.work_per_step]
+        self.roof = {"bound": "tensor", "unit": "TFLOP/s", "kernel": "attention_fwd_kernel<bf16> (1 launch per step)"}
+        self.traffic = None
+
+    def setup_gpu(self, dev):
+        from lyradiff_b200 import ops
+        self.ops = ops
+        g = _gen()
+        T, W = self.tokens, self.H * self.DH
+        # three input sets (85 MB each) rotate so that no step finds its q / k / v in L2 from the step before
+        self.qkv = [torch.randn(T, 3 * W, generator=g).bfloat16().to(dev) for _ in range(3)]
+        self.out = [torch.empty(T, W, dtype=torch.uint8, device=dev) for _ in range(2)]
+        self.s = torch.tensor([0.02], dtype=torch.float32, device=dev)
+        self.h_in = self.qkv[0].cpu().pin_memory()
+        self.e2e_x = [self.qkv[0], self.qkv[1]]
+        self.e2e_y = self.out
+        self.i = 0
+
+    def step(self, events=None, io=None):
+        self.i = (self.i + 1) % 3
+        qkv = self.qkv[self.i] if io is None else io[0]
+        out = self.out[0] if io is None else io[1]
+        if events is not None:
+            events[0][0].record()
+        self.ops.flash_attention(qkv, 1, self.tokens, self.H, self.DH, out=out, out_scale=self.s)
+        if events is not None:
+            events[0][1].record()
+
+    def peak(self, peaks, mode):
+        v, src = tensor_peak(peaks, mode, 1, "")
+        return v, src, 2250.0
+
+    def setup_cpu(self, rows):
+        g = _gen()
+        self.cpu = torch.randn(rows, 3, self.H, self.DH, generator=g).bfloat16()
+        self.cpu_rows = rows
+
+    def cpu_work(self, rows):
+        return 4.0 * rows * rows * self.H * self.DH
+
+    def step_cpu(self):
+        from oracle import blocks
+        x = self.cpu.permute(1, 2, 0, 3).unsqueeze(1)     # [3, 1, H, rows, Dh]
+        return blocks.attention(x[0], x[1], x[2])
+
+    cpu_note = "exact fp64 softmax attention over the sample's own rows"
+
+
+CASES = {c.name: c for c in (FluxFp8, FluxBlock, FluxBlockInt4, FluxForward, Int8Sdxl, SdxlFF, W4A4, AdalnQuant, Attention)}
 
 
 # =================================================================================================== CPU arm
+CPU_ROWS = 256  # token rows of the bounded CPU sample, the same in the GPU arm's cpu_baseline and in --impl reference
+
+
 def time_cpu(case, rows, steps, warmup):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
@@ -808,22 +941,25 @@ def time_cpu(case, rows, steps, warmup):
     return {"value": work / dt / case.scale, "unit": case.unit, "cores": cores, "kind": "port",
             "sample": "%d of %d token rows per step (%s), torch on %d threads, %d timed steps" % (
                 rows, case.tokens, case.cpu_note, cores, steps),
-            "ms_per_step_sample": dt * 1e3}
+            "ms_per_step_sample": dt * 1e3, "sample_work": work}
 
 
 def run_reference(case, args, rank, world):
+    """The reference arm: the CPU restatement of the reference's arithmetic for this path (the reference's own CUDA sources
+    cannot be built or run on host cores), all host threads, K timed steps of a bounded row sample.  ms_per_step is the
+    time of one sample step as measured; the figure scaled to the full row count sits in its own key."""
     if rank != 0:
         return
-    # exactly K timed steps; the row sample shrinks as K grows so that the whole run stays within a few minutes
-    rows = min(case.tokens, max(64, min(512, (512 * 20) // max(1, args.steps))))
+    rows = min(case.tokens, CPU_ROWS)
     base = time_cpu(case, rows, max(1, args.steps), max(1, min(args.warmup, 3)))
     line = {
         "impl": "reference", "metric": case.metric, "value": base["value"], "unit": case.unit, "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step_sample"] * case.tokens / rows,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step_sample"],
+        "ms_per_step_scaled_to_all_rows": base["ms_per_step_sample"] * case.work_per_step / base["sample_work"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": case.dtype + " restated on CPU",
         "data": "synthetic",
-        "config": {"workload": case.workload, "note": "CPU restatement of the reference arithmetic (the reference's CUDA sources "
-                   "cannot be built or run on host cores) on a bounded row sample; ms_per_step is the sample time scaled to all rows"},
+        "config": {"workload": case.workload, "parallelism": "replicas x%d: one copy of the workload per GPU, no collective" % world,
+                   "l2": "not applicable (host cores)"},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": case.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -831,6 +967,101 @@ def run_reference(case, args, rank, world):
 
 
 # =================================================================================================== GPU arm
+def time_events(fn, steps):
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def measure_resident(case, steps, warmup, barrier, sampler=None):
+    """Device-timed part of one case: a pass with an event pair around the dominant kernels (the roofline's per-launch
+    durations) and, directly after it, `steps` steps with no event inside (the value).  Returns (ms per step, per-kernel ms)."""
+    for _ in range(warmup):
+        case.step()
+    nt = len(case.timed_names)
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nt)] for _ in range(steps)]
+    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    if sampler is not None:
+        sampler.start()
+    # An event between two kernels takes away the overlap of one kernel's set-up with its predecessor's tail that
+    # dependent launch gives, so the per-kernel durations come from a pass of their own.
+    for s in range(steps):
+        case.step(ev[s])
+    t_begin.record()
+    for s in range(steps):
+        case.step()
+    t_end.record()
+    barrier()
+    timed_ms = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(steps)) / steps for i in range(nt)]
+    return t_begin.elapsed_time(t_end) / steps, timed_ms
+
+
+def roofline_block(case, peaks, timed_ms, mode):
+    rscale = getattr(case, "roof_scale", case.scale)
+    achieved = sum(case.timed_work) / (sum(timed_ms) * 1e-3) / rscale
+    peak, peak_source, nominal = case.peak(peaks, mode)
+    roof = dict(case.roof)
+    roof.update({"achieved": achieved, "peak": peak, "frac": achieved / peak, "traffic": getattr(case, "traffic", None),
+                 "traffic_unit": "bytes of DRAM read + write per launch, from the ncu capture summarised under profiles/",
+                 "peak_source": peak_source, "frac_of_nominal": achieved / nominal, "nominal": nominal,
+                 "per_launch_ms": dict(zip(case.timed_names, timed_ms)),
+                 "per_launch_achieved": dict(zip(case.timed_names, [w / (t * 1e-3) / rscale for w, t in zip(case.timed_work, timed_ms)]))})
+    return roof
+
+
+def sub_record(name, dev, peaks, steps):
+    """One of the other configurations, timed alone with inputs resident (a burst at flat clocks): metric, ms, achieved,
+    fraction of the measured peak, traffic."""
+    case = CASES[name](0)
+    case.setup_gpu(dev)
+    ms_step, timed_ms = measure_resident(case, steps, 5, lambda: torch.cuda.synchronize())
+    roof = roofline_block(case, peaks, timed_ms, "burst")
+    rec = {"metric": case.metric, "value": case.work_per_step / (ms_step * 1e-3) / case.scale, "unit": case.unit,
+           "ms_per_step": ms_step, "steps": steps, "workload": case.workload, "gpu_launches_per_step": case.launches_per_step,
+           "roofline": {k: roof[k] for k in ("bound", "unit", "kernel", "achieved", "peak", "frac", "peak_source", "traffic",
+                                             "per_launch_ms", "per_launch_achieved")}}
+    del case
+    torch.cuda.empty_cache()
+    return rec
+
+
+def library_baseline(dev, steps):
+    """cuBLASLt FP8 (torch._scaled_mm) on the four FLUX linear shapes -- the reference's FP8 linear IS that library call
+    (src/lyradiff/utils/cublasMMWrapper.cc:1251) -- and the library attention (torch SDPA) on the block's shape, timed in
+    this run beside this library's kernels.  Measurement only: nothing in the product path calls them."""
+    out = {"note": "library kernels timed beside this library's (cuBLASLt FP8 through torch._scaled_mm; cuDNN / flash attention "
+                   "through torch SDPA); not on the product path", "steps": steps}
+    T = 4608
+    one = torch.ones((), dtype=torch.float32, device=dev)
+    try:
+        for name, k, n, _, _ in FluxFp8.LINEARS:
+            a = torch.randn(T, k, device=dev).to(torch.float8_e4m3fn)
+            b = torch.randn(n, k, device=dev).to(torch.float8_e4m3fn)
+            fn = lambda: torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            for _ in range(5):
+                fn()
+            ms = time_events(fn, steps)
+            out[name] = {"ms": ms, "tflops": 2.0 * T * k * n / (ms * 1e-3) / 1e12}
+    except Exception as e:  # an unavailable library call must not cost the bench line
+        out["fp8_error"] = repr(e)[:200]
+    try:
+        qkv = torch.randn(1, T, 3, 24, 128, device=dev).bfloat16()
+        q, k_, v = (qkv.select(2, i).transpose(1, 2) for i in range(3))
+        fn = lambda: torch.nn.functional.scaled_dot_product_attention(q, k_, v)
+        for _ in range(5):
+            fn()
+        ms = time_events(fn, steps)
+        out["attention"] = {"ms": ms, "tflops": 4.0 * T * T * 3072 / (ms * 1e-3) / 1e12}
+    except Exception as e:
+        out["attention_error"] = repr(e)[:200]
+    return out
+
+
 def run_ours(case, args, rank, world, local_rank):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the GPU arm has no CPU fallback")
@@ -856,31 +1087,15 @@ def run_ours(case, args, rank, world, local_rank):
     case.setup_gpu(dev)
     peaks = load_peaks()
     warmup = max(args.warmup, 3)
-    for _ in range(warmup):
-        case.step()
+    checked = case.verify() if hasattr(case, "verify") else None
     check_device()
 
     # ---- timed region 1: kernels only, inputs resident
-    nt = len(case.timed_names)
-    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(nt)]
-          for _ in range(args.steps)]
-    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local_rank)
-    barrier()
-    sampler.start()
-    # K steps with an event pair around the dominant kernels: the roofline's per-launch durations.  They run as a pass
-    # of their own because an event between two kernels takes away the overlap of one kernel's set-up with its
-    # predecessor's tail that dependent launch gives; the K steps behind `value` follow directly, with no event inside.
-    for s in range(args.steps):
-        case.step(ev[s])
-    t_begin.record()
-    for s in range(args.steps):
-        case.step()
-    t_end.record()
-    barrier()
+    ms_step, timed_ms = measure_resident(case, args.steps, warmup, barrier, sampler)
     clocks = sampler.result()
-    ms_total = t_begin.elapsed_time(t_end)
-    timed_ms = [sum(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(args.steps)) / args.steps for i in range(nt)]
+    ms_total = ms_step * args.steps
+    check_device()
 
     # ---- timed region 2: end to end from pinned host buffers.  Every step copies its activations host -> device,
     # runs, and copies its result device -> host; the three stages of neighbouring steps overlap on three streams
@@ -927,18 +1142,10 @@ def run_ours(case, args, rank, world, local_rank):
         ms_step = ms_total / args.steps
         value = world * case.work_per_step / (ms_step * 1e-3) / case.scale
         e2e_value = world * case.work_per_step / (ms_e2e / args.steps * 1e-3) / case.scale
-        rscale = getattr(case, "roof_scale", case.scale)
-        achieved = sum(case.timed_work) / (sum(timed_ms) * 1e-3) / rscale
-        peak, peak_source, nominal = case.peak(peaks)
-        cpu = time_cpu(case, min(case.tokens, 256), 3, 1)
-        roof = dict(case.roof)
-        roof.update({"achieved": achieved, "peak": peak, "frac": achieved / peak, "traffic": getattr(case, "traffic", None),
-                     "traffic_unit": "bytes of DRAM read + write per launch, from the ncu capture summarised under profiles/",
-                     "peak_source": peak_source,
-                     "frac_of_nominal": achieved / nominal, "nominal": nominal,
-                     "per_launch_ms": dict(zip(case.timed_names, timed_ms)),
-                     "per_launch_achieved": dict(zip(case.timed_names,
-                                                     [w / (t * 1e-3) / rscale for w, t in zip(case.timed_work, timed_ms)]))})
+        # a region of half a second or more runs under the power cap: sustained peak; shorter ones are bursts at flat clocks
+        mode = "sustained" if ms_total >= 500.0 else "burst"
+        roof = roofline_block(case, peaks, timed_ms, mode)
+        roof["timed_region_ms"] = ms_total
         line = {
             "metric": case.metric, "value": value, "unit": case.unit, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": case.dtype,
@@ -949,24 +1156,51 @@ def run_ours(case, args, rank, world, local_rank):
                     "d2h_bytes_per_step": h_out[0].numel() * h_out[0].element_size(), "ms_per_step": ms_e2e / args.steps,
                     "overlap": "H2D, compute and D2H of neighbouring steps overlap on three streams (double-buffered slots)"},
             "gpu_launches": args.steps * case.launches_per_step,
-            "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
+            "clocks": clocks,
         }
+        if checked is not None:
+            line["config"]["checked_before_timing"] = checked
+        if world == 1 and not args.no_subrecords and case.name == DEFAULT_CASE:
+            # the other configurations and the library kernels, each timed alone after the headline (rank 0, N = 1 only)
+            del case.op
+            torch.cuda.empty_cache()
+            subs = {}
+            for name in ("flux_fp8", "int8_sdxl", "w4a4", "adaln_quant", "attention"):
+                subs[name] = sub_record(name, dev, peaks, 20)
+                check_device()
+            line["configs"] = subs
+            line["library_baseline"] = library_baseline(dev, 20)
+            # the dominant kernel of the forward is the FP8 GEMM (58 % of its device time): its roofline is the one of the
+            # four FLUX linear shapes timed alone just above; the whole forward against the blended peak sits beside it
+            line["forward_roofline"] = roof
+            roof = dict(subs["flux_fp8"]["roofline"])
+            roof["note"] = ("per-launch figures of gemm_tcgen05_kernel<f8f6f4> on the forward's four linear shapes, timed alone in "
+                            "this run (configs.flux_fp8); the whole forward against the blended peak is in forward_roofline")
+        line["roofline"] = roof
+        line["cpu_baseline"] = time_cpu(case, min(case.tokens, CPU_ROWS), 3, 1)
         print(json.dumps(line), flush=True)
     replicas.shutdown()
+
+
+DEFAULT_CASE = "flux_forward"
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--case", default="flux_fp8", choices=sorted(CASES))
+    ap.add_argument("--case", default=DEFAULT_CASE, choices=sorted(CASES))
     ap.add_argument("--tokens", type=int, default=0, help="override the number of token rows (0 = the configuration's own)")
     ap.add_argument("--tile", type=int, default=0, choices=[0, 2561, 1281, 2562],
                     help="force the dense-GEMM tile configuration (0 = automatic; see lyraq_debug_force_gemm_tile)")
     ap.add_argument("--no-graph", action="store_true",
-                    help="flux_block / flux_forward: issue every launch from Python instead of replaying the step as a CUDA graph")
+                    help="flux_block / flux_forward: issue every launch from the host instead of replaying the step as a CUDA graph")
+    ap.add_argument("--python-mirror", action="store_true",
+                    help="flux_block / flux_forward: run the Python mirrors instead of the C++ torch classes (same launches)")
+    ap.add_argument("--no-subrecords", action="store_true",
+                    help="default case at N = 1: skip the sub-records of the other configurations and the library baseline")
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch the kernels as ordinary stream-ordered kernels (see lyraq_debug_set_dependent_launch)")
     args = ap.parse_args()
@@ -977,6 +1211,8 @@ def main():
     case = CASES[args.case](args.tokens)
     if args.no_graph:
         case.use_graph = False
+    if args.python_mirror:
+        case.use_mirror = True
     if args.impl == "reference":
         run_reference(case, args, rank, world)
     else:

@@ -18,9 +18,11 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdio>
 #include <stdexcept>
 #include <string>
 #include <type_traits>
+#include <vector>
 
 #include "lyraq.h"
 
@@ -224,6 +226,186 @@ inline void invokeFusedW4A4GemmAndLoraUp(void* Dptr, const void* Aptr, const voi
                                         LoraBptr, nullptr, nullptr, LYRAQ_EPI_NONE, m, n, k, nullptr, 0, stream),
                         "invokeFusedW4A4GemmAndLoraUp");
 }
+
+/* Element type of a raw .bin weight file (src/lyradiff/utils/cuda_utils.h:37-43) and the quantization levels the torch
+ * ops are constructed with (:45-55; only the levels this library runs are named). */
+enum FtCudaDataType { FP32 = 0, FP16 = 1, BF16 = 2, INT8 = 3, FP8 = 4 };
+enum class LyraQuantType { NONE = 0, FP8_W8A8 = 1, FP8_W8A8_FULL = 2, INT4_W4A4 = 7, INT4_W4A4_FULL = 8 };
+
+namespace lyraq_detail {
+inline void cuda_check(cudaError_t e, const char* what)
+{
+    if (e != cudaSuccess) {
+        throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
+    }
+}
+template<typename T> inline T from_float(float v);
+template<> inline float from_float<float>(float v) { return v; }
+template<> inline half from_float<half>(float v) { return __float2half(v); }
+template<> inline __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+
+/* Reads `count` elements of file type `file_type` from a raw .bin file into device memory as T (the reference's
+ * loadWeightFromBin<T>, src/lyradiff/utils/memory_utils.cu: same-type files are copied, other types converted). */
+template<typename T>
+inline void load_bin(T* dst, size_t count, const std::string& path, FtCudaDataType file_type)
+{
+    const size_t esz = file_type == FP32 ? 4 : (file_type == INT8 || file_type == FP8) ? 1 : 2;
+    std::vector<unsigned char> raw(count * esz);
+    FILE* f = std::fopen(path.c_str(), "rb");
+    if (f == nullptr) {
+        throw std::runtime_error("cannot open " + path);
+    }
+    const size_t got = std::fread(raw.data(), 1, raw.size(), f);
+    std::fclose(f);
+    if (got != raw.size()) {
+        throw std::runtime_error(path + ": file is shorter than the tensor it should hold");
+    }
+    std::vector<T> host(count);
+    for (size_t i = 0; i < count; ++i) {
+        float v;
+        if (file_type == FP32) {
+            v = reinterpret_cast<const float*>(raw.data())[i];
+        } else if (file_type == FP16) {
+            v = __half2float(reinterpret_cast<const half*>(raw.data())[i]);
+        } else if (file_type == BF16) {
+            v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(raw.data())[i]);
+        } else {
+            v = (float)reinterpret_cast<const signed char*>(raw.data())[i];
+        }
+        host[i] = from_float<T>(v);
+    }
+    cuda_check(cudaMemcpy(dst, host.data(), count * sizeof(T), cudaMemcpyHostToDevice), "cudaMemcpy(load_bin)");
+}
+template<> inline void load_bin<int8_t>(int8_t* dst, size_t count, const std::string& path, FtCudaDataType)
+{
+    std::vector<int8_t> raw(count);
+    FILE* f = std::fopen(path.c_str(), "rb");
+    if (f == nullptr) {
+        throw std::runtime_error("cannot open " + path);
+    }
+    const size_t got = std::fread(raw.data(), 1, raw.size(), f);
+    std::fclose(f);
+    if (got != raw.size()) {
+        throw std::runtime_error(path + ": file is shorter than the tensor it should hold");
+    }
+    cuda_check(cudaMemcpy(dst, raw.data(), count, cudaMemcpyHostToDevice), "cudaMemcpy(load_bin)");
+}
+}  // namespace lyraq_detail
+
+/* The weights of one W4A4 linear, with the reference's member names, sizes and file names
+ * (src/lyradiff/layers/w4a4_gemm_block/W4A4GemmWeight.h:8-45, W4A4GemmWeight.cc:48-82): packed int4 weight [d_out, d_in / 2]
+ * (even element in the low nibble), fp32 group scales [d_out, d_in / 64], the rank-32 low-rank factors, the smoothing
+ * vector and an optional bias.  The object owns its device buffers once mallocWeights() or loadWeights() has run. */
+template<typename T>
+class W4A4GemmWeight {
+public:
+    int8_t* packed_weight = nullptr;
+    float*  weight_scale  = nullptr;
+    T*      lora_up       = nullptr;
+    T*      lora_down     = nullptr;
+    T*      bias          = nullptr;
+    float*  smooth        = nullptr;
+
+    W4A4GemmWeight() = default;
+    W4A4GemmWeight(size_t d_out, size_t d_in, size_t lora_rank = 32, bool has_bias = false, size_t group_size = 64,
+                   LyraQuantType = LyraQuantType::NONE, void* /*allocator*/ = nullptr):
+        d_out_(d_out), d_in_(d_in), lora_rank_(lora_rank), group_size_(group_size), group_num_(d_in / group_size), has_bias_(has_bias)
+    {
+        if (lora_rank != 32 || group_size != 64 || d_in % 64 != 0) {
+            throw std::runtime_error("W4A4GemmWeight: rank 32 and groups of 64 only (as the reference's kernels)");
+        }
+    }
+    W4A4GemmWeight(const W4A4GemmWeight&)            = delete;
+    W4A4GemmWeight& operator=(const W4A4GemmWeight&) = delete;
+    virtual ~W4A4GemmWeight()
+    {
+        if (is_maintain_buffer) {
+            cudaFree(packed_weight);
+            cudaFree(weight_scale);
+            cudaFree(lora_up);
+            cudaFree(lora_down);
+            cudaFree(smooth);
+            cudaFree(bias);
+        }
+    }
+
+    virtual void mallocWeights()
+    {
+        if (!is_maintain_buffer) {
+            lyraq_detail::cuda_check(cudaMalloc(&packed_weight, d_out_ * d_in_ / 2), "cudaMalloc(packed_weight)");
+            lyraq_detail::cuda_check(cudaMalloc(&weight_scale, d_out_ * group_num_ * sizeof(float)), "cudaMalloc(weight_scale)");
+            lyraq_detail::cuda_check(cudaMalloc(&lora_up, d_out_ * lora_rank_ * sizeof(T)), "cudaMalloc(lora_up)");
+            lyraq_detail::cuda_check(cudaMalloc(&lora_down, d_in_ * lora_rank_ * sizeof(T)), "cudaMalloc(lora_down)");
+            lyraq_detail::cuda_check(cudaMalloc(&smooth, d_in_ * sizeof(float)), "cudaMalloc(smooth)");
+            if (has_bias_) {
+                lyraq_detail::cuda_check(cudaMalloc(&bias, d_out_ * sizeof(T)), "cudaMalloc(bias)");
+            }
+        }
+        is_maintain_buffer = true;
+    }
+
+    /* <prefix>packed_weight.bin, weight_scale.bin, lora_up.bin, lora_down.bin, smooth.bin, bias.bin */
+    virtual void loadWeights(const std::string prefix, FtCudaDataType model_file_type)
+    {
+        mallocWeights();
+        lyraq_detail::load_bin<int8_t>(packed_weight, d_out_ * d_in_ / 2, prefix + "packed_weight.bin", INT8);
+        lyraq_detail::load_bin<float>(weight_scale, d_out_ * group_num_, prefix + "weight_scale.bin", FP32);
+        lyraq_detail::load_bin<T>(lora_up, d_out_ * lora_rank_, prefix + "lora_up.bin", model_file_type);
+        lyraq_detail::load_bin<T>(lora_down, d_in_ * lora_rank_, prefix + "lora_down.bin", model_file_type);
+        lyraq_detail::load_bin<float>(smooth, d_in_, prefix + "smooth.bin", FP32);
+        if (has_bias_) {
+            lyraq_detail::load_bin<T>(bias, d_out_, prefix + "bias.bin", model_file_type);
+        }
+    }
+
+    size_t d_out() const { return d_out_; }
+    size_t d_in() const { return d_in_; }
+    size_t group_num() const { return group_num_; }
+    bool   has_bias() const { return has_bias_; }
+
+protected:
+    bool is_maintain_buffer = false;
+
+private:
+    size_t d_out_ = 0, d_in_ = 0, lora_rank_ = 32, group_size_ = 64, group_num_ = 0;
+    bool   has_bias_ = true;
+};
+
+/* W4A4Gemm<T>::forward (src/lyradiff/layers/w4a4_gemm_block/W4A4Gemm.cc:113-169) on raw pointers: int4 quantize + low-rank
+ * down projection, grouped GEMM + low-rank up projection -> output [m, d_out] of T, no bias (the reference's layers add it
+ * afterwards).  The layer keeps its scratch (quantized input, scales, low-rank activation) between calls and grows it
+ * when m grows, as the reference's allocateBuffer does. */
+template<typename T>
+class W4A4Gemm {
+public:
+    W4A4Gemm(size_t d_out, size_t d_in, cudaStream_t stream = 0): d_out_(d_out), d_in_(d_in), stream_(stream) {}
+    W4A4Gemm(const W4A4Gemm&)            = delete;
+    W4A4Gemm& operator=(const W4A4Gemm&) = delete;
+    ~W4A4Gemm() { cudaFree(workspace_); }
+
+    void forward(T* output, const T* input, size_t m, const W4A4GemmWeight<T>* weights)
+    {
+        const size_t need = lyraq_workspace_bytes(LYRAQ_OP_LINEAR_W4A4_LORA, (int)m, (int)d_out_, (int)d_in_);
+        if (need > workspace_bytes_) {
+            cudaFree(workspace_);
+            workspace_ = nullptr;
+            workspace_bytes_ = 0;
+            lyraq_detail::cuda_check(cudaMalloc(&workspace_, need), "cudaMalloc(W4A4Gemm workspace)");
+            workspace_bytes_ = need;
+        }
+        lyraq_detail::check(lyraq_w4a4_lora_forward(output, input, lyraq_detail::DType<T>::value, weights->smooth,
+                                                    reinterpret_cast<const uint8_t*>(weights->packed_weight), weights->weight_scale,
+                                                    LYRAQ_F32, weights->lora_down, weights->lora_up, nullptr, nullptr, LYRAQ_EPI_NONE,
+                                                    (int)m, (int)d_out_, (int)d_in_, workspace_, workspace_bytes_, stream_),
+                            "W4A4Gemm::forward");
+    }
+
+private:
+    size_t       d_out_, d_in_;
+    cudaStream_t stream_;
+    void*        workspace_       = nullptr;
+    size_t       workspace_bytes_ = 0;
+};
 
 /* The two quantized entry points of cublasMMWrapper (src/lyradiff/utils/cublasMMWrapper.h:300-317 and :354-385),
  * as a small class that the layers can hold where they hold `cublas_wrapper_`. */
