@@ -87,6 +87,13 @@ LYRAQ_API int lyraq_debug_set_dependent_launch(int on);
  * through CutlassGemmConfig (src/lyradiff/kernels/cutlass_extensions/include/cutlass_extensions/gemm_configs.h:101-130). */
 LYRAQ_API int lyraq_debug_force_gemm_tile(int code);
 
+/* Test hook for the bounded waits (process-wide, not thread-safe): with skip_loads != 0 the attention kernel's producer
+ * issues no copy, so every consumer's wait runs out after wait_limit_ms (0 = the default of 2 s) -- the non-faulting way
+ * to run the path a timed-out wait takes: the kernel records LYRAQ_ERR_DEVICE_TIMEOUT in the status word, raises its
+ * block-wide abort flag, all roles leave, tensor memory is freed and the kernel returns without having written anything.
+ * (0, 0) restores normal operation.  It has no counterpart in the reference, whose kernels have no bounded waits. */
+LYRAQ_API int lyraq_debug_attention_wait_test(int skip_loads, unsigned int wait_limit_ms);
+
 /* Test / sweep hook for the row kernels (quantize, LayerNorm, AdaLN, GEGLU): the most 16-byte vectors one thread
  * holds (4 or 6, default 6) before a row is given to a team twice as large.  Process-wide, not thread-safe.
  * No counterpart in the reference, whose kernels fix columns-per-thread per supported width
@@ -358,15 +365,19 @@ LYRAQ_API int lyraq_w4a4_lora_forward(void* D, const void* x, int dtype, const f
                                       void* workspace, size_t workspace_bytes, void* stream);
 
 /* lyraq_w4a4_forward without a workspace argument and without any allocation: the packed activation and its group
- * scales are kept in a fixed 16 MiB array inside the library's device image (lyraq_static_scratch_bytes()), present on
- * every GPU that loads the library until the process exits.  Meant for hosts that may not allocate device memory and
+ * scales are kept in a fixed 16 MiB array inside the library's device image (lyraq_static_scratch_bytes()), which a GPU
+ * holds from the moment the array is first used there until the process exits.  Meant for hosts that may not allocate device memory and
  * have no scratch pointer to pass (an asynchronous enqueue hook, a plug-in interface with inputs and outputs only, a
  * process whose memory pool belongs to another framework).  It has no counterpart in the reference, whose layers
  * always draw their buffers from the context's allocator.
  *   - m * k / 2 + 4 * m * (k / 64) (each rounded up to 256) must fit in the array; larger problems get
  *     LYRAQ_ERR_WORKSPACE and nothing is launched.
- *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress); make that first call
- *     outside any stream capture.  No call allocates or frees anything.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress).  CUDA loads device images
+ *     lazily by default, so that look-up is when the driver creates the array -- its one allocation, which may
+ *     synchronise the device and can fail with LYRAQ_ERR_CUDA if the memory pool is exhausted.  Make that first call
+ *     outside any stream capture and outside the latency-critical path, or call lyraq_static_scratch_bytes() once per
+ *     device at start-up, which does the same look-up (CUDA_MODULE_LOADING=EAGER moves it to context creation).
+ *     After that no call allocates or frees anything.
  *   - Every call reuses the same array, which keeps the previous call's contents; nothing in it needs clearing
  *     because the quantizer rewrites all of it that the GEMM reads.  Calls whose GPU work overlaps race on it:
  *     issue them on one stream.
@@ -375,7 +386,9 @@ LYRAQ_API int lyraq_w4a4_forward_static(void* D, const void* x, int dtype, const
                                         const void* w_scale, int w_scale_dtype, const void* bias, const void* residual,
                                         int epilogue, int m, int n, int k, void* stream);
 
-/* Size in bytes of the fixed scratch array behind lyraq_w4a4_forward_static (no counterpart in the reference). */
+/* Size in bytes of the fixed scratch array behind lyraq_w4a4_forward_static (no counterpart in the reference).  When a
+ * device is present the call also resolves the array's address on the current device: the start-up warm-up of that
+ * entry point.  A failure of the look-up is not reported here; the first forward reports it. */
 LYRAQ_API size_t lyraq_static_scratch_bytes(void);
 
 #ifdef __cplusplus

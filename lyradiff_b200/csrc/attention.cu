@@ -63,6 +63,8 @@ struct Params {
     int           q_blocks;      // ceil(seq / 256)
     float         scale_log2;    // softmax scale * log2(e)
     unsigned int* status;
+    unsigned long long wait_limit_ns;  // longest a single wait may last (2 s; a test hook shortens it)
+    int           skip_loads;          // test hook: the producer issues no copy, so every consumer's wait runs out
 };
 
 __device__ __forceinline__ float ex2_approx(float x)
@@ -157,7 +159,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
 
     if (warp == kProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
+        if (lane == 0 && p.skip_loads == 0) {
             mbar_arrive_expect_tx(q_full, (uint32_t)(kQTiles * kTileBytes));
             for (int t = 0; t < kQTiles; ++t) {
                 for (int half = 0; half < 2; ++half) {
@@ -168,7 +170,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
             int      slot = 0, issued = 0;
             uint32_t phase = 0;
             for (int i = 0; i < 2 * n_kv; ++i) {
-                if (!mbar_wait(slot_empty(slot), phase ^ 1u, abort_flag)) {
+                if (!mbar_wait(slot_empty(slot), phase ^ 1u, abort_flag, p.wait_limit_ns)) {
                     report_timeout(p.status, 0x3100u | (unsigned)slot);
                     *abort_flag = 1;
                     break;
@@ -195,7 +197,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
                 --s;
                 const uint64_t t0 = global_timer_ns();
                 while (!mbar_try_wait(slot_full(s), ph)) {
-                    if (global_timer_ns() - t0 > kWaitLimitNs) {
+                    if (global_timer_ns() - t0 > p.wait_limit_ns) {
                         report_timeout(p.status, 0x3400u | (unsigned)s);
                         break;
                     }
@@ -203,7 +205,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
             }
             const uint64_t t0 = global_timer_ns();
             while (!mbar_try_wait(q_full, 0u)) {
-                if (global_timer_ns() - t0 > kWaitLimitNs) {
+                if (global_timer_ns() - t0 > p.wait_limit_ns) {
                     report_timeout(p.status, 0x3401u);
                     break;
                 }
@@ -217,7 +219,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
             const uint32_t idesc_pv = umma_idesc(1u, kAb, 128, 128) | kIdescBMajorMN;
             bool ok = true;
             auto wait_or_fail = [&](uint32_t bar, uint32_t parity, unsigned code) {
-                if (ok && !mbar_wait(bar, parity, abort_flag)) {
+                if (ok && !mbar_wait(bar, parity, abort_flag, p.wait_limit_ns)) {
                     report_timeout(p.status, code);
                     *abort_flag = 1;
                     ok = false;
@@ -303,7 +305,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
         bool           ok       = true;
 
         for (int j = 0; j < n_kv && ok; ++j) {
-            if (!__all_sync(0xffffffffu, mbar_wait(s_full(t), (uint32_t)(j & 1), abort_flag))) {
+            if (!__all_sync(0xffffffffu, mbar_wait(s_full(t), (uint32_t)(j & 1), abort_flag, p.wait_limit_ns))) {
                 report_timeout(p.status, 0x3300u | (unsigned)t);
                 *abort_flag = 1;
                 ok = false;
@@ -346,7 +348,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
                 const bool raise = (mx - m) * c > kRescaleThreshold;
                 if (__any_sync(0xffffffffu, raise)) {
                     // the accumulator may only be touched between this tile's MMAs: the previous P V has to be complete
-                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((j - 1) & 1), abort_flag))) {
+                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit_ns))) {
                         report_timeout(p.status, 0x3310u | (unsigned)t);
                         *abort_flag = 1;
                         ok = false;
@@ -405,7 +407,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
         }
 
         // ---- epilogue: O / l, rounded to T, stored as T or as e4m3 of that value
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((n_kv - 1) & 1), abort_flag))) {
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((n_kv - 1) & 1), abort_flag, p.wait_limit_ns))) {
             report_timeout(p.status, 0x3320u | (unsigned)t);
             *abort_flag = 1;
             ok = false;
@@ -466,6 +468,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
 }  // namespace attn
 
 // out = softmax(q k^T * softmax_scale) v for qkv [batch, seq, 3, heads, 128]; see lyraq_attention in the header.
+// Test hook (lyraq_debug_attention_wait_test): a producer that never signals and a short wait limit, so that the path a
+// timed-out wait takes -- status word, abort flag, every role leaving, tensor memory freed -- can be run without a fault.
+static int                g_attn_skip_loads    = 0;
+static unsigned long long g_attn_wait_limit_ns = kWaitLimitNs;
+
 int launch_attention(void* out, int out_dtype, size_t out_ld, const float* out_scale, void* out2, size_t out2_ld,
                      const float* out2_scale, size_t split, const void* qkv, int dtype, size_t batch, size_t seq, int heads,
                      int head_dim, float softmax_scale, cudaStream_t stream)
@@ -529,6 +536,8 @@ int launch_attention(void* out, int out_dtype, size_t out_ld, const float* out_s
     p.q_blocks     = (int)((seq + attn::kQTiles * attn::kTile - 1) / (attn::kQTiles * attn::kTile));
     p.scale_log2   = softmax_scale * 1.4426950408889634f;
     p.status       = status_word_ptr();
+    p.wait_limit_ns = g_attn_wait_limit_ns;
+    p.skip_loads    = g_attn_skip_loads;
     if (p.status == nullptr) {
         return LYRAQ_ERR_CUDA;
     }
@@ -560,6 +569,13 @@ int launch_attention(void* out, int out_dtype, size_t out_ld, const float* out_s
 }
 
 }  // namespace lyraq
+
+extern "C" int lyraq_debug_attention_wait_test(int skip_loads, unsigned int wait_limit_ms)
+{
+    lyraq::g_attn_skip_loads    = skip_loads ? 1 : 0;
+    lyraq::g_attn_wait_limit_ns = wait_limit_ms == 0 ? lyraq::sm100::kWaitLimitNs : (unsigned long long)wait_limit_ms * 1000000ull;
+    return LYRAQ_OK;
+}
 
 extern "C" int lyraq_attention(void* out, int out_dtype, size_t out_ld, const float* out_scale, void* out2, size_t out2_ld,
                                const float* out2_scale, size_t split, const void* qkv, int dtype, size_t batch, size_t seq_len,

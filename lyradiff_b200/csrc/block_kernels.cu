@@ -42,7 +42,12 @@ __global__ void __launch_bounds__(256) rmsnorm_rope_kernel(T* out, const T* qkv,
         const bool   rotate = active && !is_v;
         Vec16        x      = {};
         if (load) {
-            x = ld_nc_16(qkv + (vi << 3));
+            // an ordered plain load, not the read-only (.nc) path: with out == qkv this kernel writes what it reads
+            const uint4 raw = ld_u32x4(reinterpret_cast<const uint4*>(qkv + (vi << 3)));
+            x.w[0] = raw.x;
+            x.w[1] = raw.y;
+            x.w[2] = raw.z;
+            x.w[3] = raw.w;
         }
         float f[8];
         unpack8<T>(x, f);

@@ -302,15 +302,19 @@ __device__ __forceinline__ void quant8_s8_inrange(const float2* v, float s, floa
     const float2 m1 = make_float2(-1.0f, -1.0f);
     uint32_t     b[8];
     float        dmax = 0.0f;
+    float2       bad  = make_float2(0.0f, 0.0f);  // becomes NaN if any d is NaN or infinite (fmaxf would drop a NaN)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const float2 t = fma_f32x2(v[j], r2, mg);
         const float2 d = fma_f32x2(v[j], r2, fma_f32x2(t, m1, mg));  // v * r - (t - magic), the second term exact
         dmax           = fmaxf(dmax, fmaxf(fabsf(d.x), fabsf(d.y)));
+        bad            = fma_f32x2(d, make_float2(0.0f, 0.0f), bad);
         b[2 * j]       = __float_as_uint(t.x);
         b[2 * j + 1]   = __float_as_uint(t.y);
     }
-    if (dmax > 0.5f - 6.1e-5f) {
+    // NaN input, or a scale so small that r = 1 / s is infinite (inf * 0 = NaN): the IEEE divide and cvt give the
+    // reference's bytes (NaN -> 0, saturation) where the integer trick would leave NaN bits in the byte
+    if (dmax > 0.5f - 6.1e-5f || !(bad.x + bad.y == 0.0f)) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             b[2 * j]     = (uint32_t)f32_to_s8(v[j].x / s);

@@ -7,8 +7,12 @@
 // every byte of the memory pool.  For them the scratch that lyraq_w4a4_forward takes as `workspace` (the int4-packed
 // activation and its per-group scales) lives in a fixed array inside the library's own device image instead.
 //
-// The array is 16 MiB and is resident on every GPU that loads the library, from load until the process exits.
-// All calls share it and it keeps whatever the last call left there.  Nothing in it has to start at zero: the
+// The array is 16 MiB per GPU and stays until the process exits.  CUDA loads a module's device image lazily by default,
+// so the driver sets the array up -- its one allocation, possibly with a device synchronisation -- when the address is
+// first asked for on a device: at the first call of this entry point there, or earlier and outside any enqueue hook or
+// stream capture if the host calls lyraq_static_scratch_bytes() once per device at start-up (CUDA_MODULE_LOADING=EAGER
+// moves it to context creation instead).  If that set-up fails, e.g. because the pool is exhausted, the call returns
+// LYRAQ_ERR_CUDA and launches nothing.  All calls share the array and it keeps whatever the last call left there.  Nothing in it has to start at zero: the
 // quantizer overwrites every byte the GEMM will read before the GEMM reads it.  Two calls whose GPU work overlaps
 // in time (different streams, or different host threads) race on the array; run them on one stream.
 #include "common.cuh"
@@ -52,7 +56,19 @@ using namespace lyraq;
 
 extern "C" {
 
-size_t lyraq_static_scratch_bytes(void) { return kStaticScratchBytes; }
+// Size of the array; as a side effect resolves its address on the current device (the warm-up described at the top).
+// Without a device, or if the set-up fails, the size is still returned and the failure shows up at the first forward.
+size_t lyraq_static_scratch_bytes(void)
+{
+    unsigned char* unused = nullptr;
+    int            count  = 0;
+    if (cudaGetDeviceCount(&count) == cudaSuccess && count > 0) {
+        (void)static_scratch_ptr(&unused);
+    } else {
+        (void)cudaGetLastError();
+    }
+    return kStaticScratchBytes;
+}
 
 int lyraq_w4a4_forward_static(void* D, const void* x, int dtype, const float* smooth, const uint8_t* W, const void* w_scale,
                               int w_scale_dtype, const void* bias, const void* residual, int epilogue, int m, int n, int k,

@@ -817,18 +817,24 @@ static int int4_g64_dispatch(uint8_t* q, void* q_scale, int scale_dtype, const v
     }
     const unsigned grid = flat_grid(rows * (k >> 3));
     uint32_t*      qo   = reinterpret_cast<uint32_t*>(q);
+    const char* where = "cudaLaunchKernelEx(int4_g64_kernel)";
     if (x_dtype == LYRAQ_BF16 && scale_dtype == LYRAQ_F32) {
-        launch_kernel(int4_g64_kernel<__nv_bfloat16, float>, (unsigned)(grid), 256u, (size_t)0, stream, 1u, qo, (float*)q_scale, (const __nv_bfloat16*)x, smooth, rows, (int)k);
-    } else if (x_dtype == LYRAQ_F16 && scale_dtype == LYRAQ_F32) {
-        launch_kernel(int4_g64_kernel<__half, float>, (unsigned)(grid), 256u, (size_t)0, stream, 1u, qo, (float*)q_scale, (const __half*)x, smooth, rows, (int)k);
-    } else if (x_dtype == LYRAQ_BF16 && scale_dtype == LYRAQ_F16) {
-        launch_kernel(int4_g64_kernel<__nv_bfloat16, __half>, (unsigned)(grid), 256u, (size_t)0, stream, 1u, qo, (__half*)q_scale, (const __nv_bfloat16*)x, smooth, rows, (int)k);
-    } else if (x_dtype == LYRAQ_F16 && scale_dtype == LYRAQ_F16) {
-        launch_kernel(int4_g64_kernel<__half, __half>, (unsigned)(grid), 256u, (size_t)0, stream, 1u, qo, (__half*)q_scale, (const __half*)x, smooth, rows, (int)k);
-    } else {
-        return LYRAQ_ERR_UNSUPPORTED;
+        return cuda_status(launch_kernel(int4_g64_kernel<__nv_bfloat16, float>, grid, 256u, (size_t)0, stream, 1u, qo, (float*)q_scale,
+                                         (const __nv_bfloat16*)x, smooth, rows, (int)k), where);
     }
-    return launch_status();
+    if (x_dtype == LYRAQ_F16 && scale_dtype == LYRAQ_F32) {
+        return cuda_status(launch_kernel(int4_g64_kernel<__half, float>, grid, 256u, (size_t)0, stream, 1u, qo, (float*)q_scale,
+                                         (const __half*)x, smooth, rows, (int)k), where);
+    }
+    if (x_dtype == LYRAQ_BF16 && scale_dtype == LYRAQ_F16) {
+        return cuda_status(launch_kernel(int4_g64_kernel<__nv_bfloat16, __half>, grid, 256u, (size_t)0, stream, 1u, qo, (__half*)q_scale,
+                                         (const __nv_bfloat16*)x, smooth, rows, (int)k), where);
+    }
+    if (x_dtype == LYRAQ_F16 && scale_dtype == LYRAQ_F16) {
+        return cuda_status(launch_kernel(int4_g64_kernel<__half, __half>, grid, 256u, (size_t)0, stream, 1u, qo, (__half*)q_scale,
+                                         (const __half*)x, smooth, rows, (int)k), where);
+    }
+    return LYRAQ_ERR_UNSUPPORTED;
 }
 
 int lyraq_quant_int4_g64(uint8_t* q, float* q_scale, float* lora_act, const void* x, int x_dtype, const float* smooth,

@@ -63,7 +63,7 @@ constexpr unsigned kPollSleepNs = 32;
 
 // Bounded wait on an mbarrier phase.  Returns false if the limit ran out or another role of the
 // block already gave up (abort flag in shared memory).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint64_t limit_ns = kWaitLimitNs)
 {
     // The common case ends within the first polls.  Reading %globaltimer is slow, so the clock is first looked at
     // only after a batch of failed polls (the limit then counts from that moment) and once per batch afterwards.
@@ -86,7 +86,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (*abort_flag != 0) {
             return false;
         }
-        if (global_timer_ns() - t0 > kWaitLimitNs) {
+        if (global_timer_ns() - t0 > limit_ns) {
             return false;
         }
     }

@@ -370,8 +370,9 @@ struct BlockBase: torch::CustomClassHolder {
         dtype(parse_dtype(inference_dtype)), dim(embedding_dim), heads(embedding_head_num), head_dim(embedding_head_dim),
         mlp_scale(mlp_scale_), quant_level(quant_level_)
     {
-        TORCH_CHECK(quant_level == 1 || quant_level == 2 || quant_level == 7 || quant_level == 8,
-                    "only quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built");
+        TORCH_CHECK(quant_level == 1 || quant_level == 2 || quant_level == 7 || quant_level == 8, "quant_level ", quant_level,
+                    ": only 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built here; the 16-bit level 0 (the reference's default) and FP8 "
+                    "weight-only level 3 stay with the reference's own library");
         TORCH_CHECK(heads * head_dim == dim, "embedding_dim must equal embedding_head_num * embedding_head_dim");
     }
     // one lock per op object, held for the whole call, as the reference's ops do (FluxSingleTransformerBlockOp.h:67,231)
@@ -1067,11 +1068,14 @@ struct FluxTransformer2DModelOp: torch::CustomClassHolder {
 // The shared methods live in BlockBase; they are bound through lambdas on the concrete class, since the class registry
 // takes `self` from the member pointer's class and BlockBase itself is not registered.
 template<class Op>
-void register_block(torch::Library& m, const char* name)
+void register_block(torch::Library& m, const char* name, int64_t default_mlp_scale)
 {
     using Self = c10::intrusive_ptr<Op>;
+    // argument names and defaults of th_op/pybind.cc:66-96 (mlp_scale 6 for the double-stream block, 4 for the single one)
     m.class_<Op>(name)
-        .def(torch::init<std::string, int64_t, int64_t, int64_t, int64_t, int64_t>())
+        .def(torch::init<std::string, int64_t, int64_t, int64_t, int64_t, int64_t>(), "init",
+             {torch::arg("inference_dtype") = "bf16", torch::arg("embedding_dim") = 3072, torch::arg("embedding_head_num") = 24,
+              torch::arg("embedding_head_dim") = 128, torch::arg("mlp_scale") = default_mlp_scale, torch::arg("quant_level") = 0})
         .def("initialize", [](const Self& self, const c10::intrusive_ptr<LyraDiffCommonContext>& ctx) { self->initialize(ctx); })
         .def("forward", &Op::forward)
         .def("reload_model_from_state_dict", [](const Self& self, const std::string& prefix, const c10::Dict<std::string, Tensor>& sd,
@@ -1086,8 +1090,8 @@ void register_block(torch::Library& m, const char* name)
 TORCH_LIBRARY(lyradiff, m)
 {
     m.class_<LyraDiffCommonContext>("LyraDiffCommonContext").def(torch::init<>());
-    register_block<FluxSingleTransformerBlockOp>(m, "FluxSingleTransformerBlockOp");
-    register_block<FluxTransformerBlockOp>(m, "FluxTransformerBlockOp");
+    register_block<FluxSingleTransformerBlockOp>(m, "FluxSingleTransformerBlockOp", 4);
+    register_block<FluxTransformerBlockOp>(m, "FluxTransformerBlockOp", 6);
     m.class_<FluxTransformer2DModelOp>("FluxTransformer2DModelOp")
         .def(torch::init<std::string, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, bool, int64_t>(), "init",
              {torch::arg("inference_dtype") = "bf16", torch::arg("input_channels") = 64, torch::arg("num_layers") = 19,

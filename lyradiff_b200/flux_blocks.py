@@ -201,7 +201,8 @@ class FluxSingleTransformerBlockOp:
         if inference_dtype not in _DTYPES:
             raise RuntimeError("inference_dtype must be 'bf16' or 'fp16'")
         if quant_level not in (FP8_W8A8, FP8_W8A8_FULL, INT4_W4A4, INT4_W4A4_FULL):
-            raise NotImplementedError("only quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built")
+            raise NotImplementedError("quant_level %r: only 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built here; the 16-bit level 0 (the "
+                                      "reference's default) and FP8 weight-only level 3 stay with the reference's own library" % (quant_level,))
         if embedding_head_num * embedding_head_dim != embedding_dim:
             raise RuntimeError("embedding_dim must equal embedding_head_num * embedding_head_dim")
         self.dtype = _DTYPES[inference_dtype]
@@ -448,7 +449,8 @@ class FluxTransformerBlockOp:
         if inference_dtype not in _DTYPES:
             raise RuntimeError("inference_dtype must be 'bf16' or 'fp16'")
         if quant_level not in (FP8_W8A8, FP8_W8A8_FULL, INT4_W4A4, INT4_W4A4_FULL):
-            raise NotImplementedError("only quant_level 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built")
+            raise NotImplementedError("quant_level %r: only 1, 2 (FP8) and 7, 8 (INT4 W4A4) are built here; the 16-bit level 0 (the "
+                                      "reference's default) and FP8 weight-only level 3 stay with the reference's own library" % (quant_level,))
         if embedding_head_num * embedding_head_dim != embedding_dim:
             raise RuntimeError("embedding_dim must equal embedding_head_num * embedding_head_dim")
         self.dtype = _DTYPES[inference_dtype]

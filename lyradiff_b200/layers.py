@@ -70,6 +70,37 @@ class SmoothQuantLinear:
         ops.invoke_get_int8_weight_scale(sw, qw, weight.contiguous(), pre_quant_scale)
         return cls(qw, sw, pre_quant_scale, bias, input_scale)
 
+    @staticmethod
+    def bin_files(name, d_out, d_in, has_bias=True):
+        """The raw files of one INT8 linear `name` (e.g. "ff.net.0.proj") under a block prefix, as the reference's loader
+        reads them (MACROLoadLinearInt8WeightFromBin, src/lyradiff/utils/common_macro_def.h:51-59, used at
+        layers/basic_transformer/BasicTransformerInt8BlockWeight.cc:249-288; written by the exporter,
+        lyradiff/convert_model_scripts/convert_sd_quant_model.py:182-219): (suffix, element kind, shape)."""
+        files = [(name + ".weight_int8.bin", "int8", (d_out, d_in)), (name + ".weight_quant_scale.bin", "fp32", (d_out,)),
+                 (name + ".input_quant_scale.bin", "fp32", (1,)), (name + ".pre_quant_scale.bin", "fp32", (d_in,))]
+        if has_bias:
+            files.append((name + ".bias.bin", "model", (d_out,)))
+        return files
+
+    @classmethod
+    def from_bin(cls, prefix, name, d_out, d_in, dtype=torch.float16, model_file_type="fp16", has_bias=True, device="cuda"):
+        """Reads <prefix><name>.weight_int8.bin / .weight_quant_scale.bin / .input_quant_scale.bin / .pre_quant_scale.bin
+        (+ .bias.bin in the model's file type, "fp32" or "fp16") and returns the linear with its static input scale.  A
+        missing or short file raises; nothing is defaulted."""
+        import numpy as np
+        kinds = {"int8": np.int8, "fp32": np.float32, "model": {"fp32": np.float32, "fp16": np.float16}[model_file_type]}
+        got = {}
+        for fname, kind, shape in cls.bin_files(name, d_out, d_in, has_bias):
+            path = prefix + fname
+            count = int(np.prod(shape))
+            arr = np.fromfile(path, dtype=kinds[kind])
+            if arr.size != count:
+                raise RuntimeError("%s holds %d elements, expected %d" % (path, arr.size, count))
+            got[fname[len(name) + 1:-4]] = torch.from_numpy(arr.reshape(shape).copy())
+        bias = got["bias"].to(dtype).to(device) if has_bias else None
+        return cls(got["weight_int8"].to(device), got["weight_quant_scale"].to(device), got["pre_quant_scale"].to(device), bias,
+                   got["input_quant_scale"].to(device))
+
     def forward(self, x, out=None):
         m = x.numel() // self.k
         x2 = x.reshape(m, self.k)

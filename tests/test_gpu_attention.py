@@ -141,3 +141,33 @@ def test_attention_argument_checks():
     assert lib.lyraq_attention(p, 4, 256, None, None, 0, None, 0, p, 1, 1, 8, 2, 128, 0.1, None) == 1      # e4m3 without a scale
     assert lib.lyraq_attention(p, 1, 128, None, None, 0, None, 0, p, 1, 1, 8, 2, 128, 0.1, None) == 1      # pitch below the width
     assert lib.lyraq_attention(p, 1, 256, None, None, 0, None, 0, p, 1, 0, 8, 2, 128, 0.1, None) == 0      # empty
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_kernel_returns(ops):
+    """Nothing faults or hangs here: a test hook makes the producer issue no copy and shortens the wait limit to 50 ms, so
+    the consumers' waits run out.  The kernel must come back, leave LYRAQ_ERR_DEVICE_TIMEOUT (4) with the code of an
+    attention wait (0x3xxx) in the status word, write nothing -- and the next ordinary call must work and give the usual
+    bits (the abort path freed tensor memory and left no copy in flight)."""
+    from lyradiff_b200 import _lib
+    lib = _lib.lib()
+    g = torch.Generator().manual_seed(3)
+    qkv = cu(_qkv(1, 256, 2, 128, torch.bfloat16, g))
+    good = torch.empty(256, 256, dtype=torch.bfloat16, device="cuda")
+    ops.flash_attention(qkv, 1, 256, 2, 128, out=good)
+    check_status()
+    out = torch.full((256, 256), 7.0, dtype=torch.bfloat16, device="cuda")
+    assert lib.lyraq_debug_attention_wait_test(1, 50) == 0
+    try:
+        ops.flash_attention(qkv, 1, 256, 2, 128, out=out)          # the launch itself succeeds
+        torch.cuda.synchronize()
+        status, detail = ops.last_status()
+    finally:
+        assert lib.lyraq_debug_attention_wait_test(0, 0) == 0
+    assert status == 4, status
+    assert 0x3000 <= detail < 0x4000, hex(detail)
+    assert bool((out == 7.0).all()), "a timed-out kernel must not store results"
+    assert ops.last_status()[0] == 0                               # reading the status cleared it
+    again = torch.empty_like(good)
+    ops.flash_attention(qkv, 1, 256, 2, 128, out=again)
+    check_status()
+    assert_bit_equal(again, good.cpu(), "after a timed-out launch")

@@ -139,3 +139,98 @@ def test_cpp_class_same_bits_as_mirror(tmp_path, level):
         assert torch.equal(swapped, mirror.transformer_forward(*args)) and not torch.equal(swapped, want)
         op.clear_lora()
         assert torch.equal(op.transformer_forward(*args), want)
+
+
+class _CppBlock:
+    """A per-block C++ class in the place of a block of the Python model mirror: its own forward (modulation linear
+    inside), so the mirror's embedders and output layer chain the C++ blocks by hand."""
+
+    def __init__(self, op, double):
+        self.op, self.double = op, double
+
+    def modulation(self, temb):
+        return None
+
+    def forward(self, *args):
+        args = args[:-1]                      # the modulation computed ahead is not used: the block computes its own
+        return self.op.forward(*args)
+
+
+def test_full_width_model_equals_its_blocks_chained_by_hand_at_4608_tokens():
+    """FLUX.1-dev width (hidden 3072, 24 heads x 128) and sequence (4096 image + 512 text tokens), 3 double-stream + 3
+    single-stream blocks with their own random FP8 weights: the C++ whole-model class gives a finite output and exactly
+    the bits of the per-block C++ classes called one after another between the embedders and the output layer."""
+    from lyradiff_b200 import flux_blocks, flux_model, rope as rope_host, torch_classes
+    ns = torch_classes.load()
+    Dw, H, DH, CH, JT, PL, nl, nsingle, S, E = 3072, 24, 128, 64, 4096, 768, 3, 3, 4096, 512
+    g = torch.Generator(device="cuda").manual_seed(77)
+    sd = {}
+
+    def lin(name, n, k, quantized=True, std=0.02):
+        sd[name + ".weight"] = (torch.randn(n, k, generator=g, device="cuda") * std).bfloat16()
+        sd[name + ".bias"] = (torch.randn(n, generator=g, device="cuda") * 0.02).bfloat16()
+        if quantized:
+            sd[name + "_input_scale"] = torch.tensor([0.03])
+
+    for i in range(nl):
+        p = "transformer_blocks.%d." % i
+        for norm in ("norm1", "norm1_context"):
+            lin(p + norm + ".linear", 6 * Dw, Dw, quantized=False)
+        for a, b in (("attn.to_qkv", "attn.to_out.0"), ("attn.to_added_qkv", "attn.to_add_out")):
+            lin(p + a, 3 * Dw, Dw)
+            lin(p + b, Dw, Dw)
+        for ff in ("ff", "ff_context"):
+            lin(p + ff + ".net.0.proj", 4 * Dw, Dw)
+            lin(p + ff + ".net.2", Dw, 4 * Dw)
+        for n in ("attn.norm_q.weight", "attn.norm_k.weight", "attn.norm_added_q.weight", "attn.norm_added_k.weight"):
+            sd[p + n] = torch.ones(DH, device="cuda").bfloat16()
+    for j in range(nsingle):
+        p = "single_transformer_blocks.%d." % j
+        lin(p + "norm.linear", 3 * Dw, Dw, quantized=False)
+        lin(p + "attn.to_qkv", 3 * Dw, Dw)
+        lin(p + "proj_mlp", 4 * Dw, Dw)
+        lin(p + "proj_out", Dw, 5 * Dw)
+        sd[p + "attn.norm_q.weight"] = torch.ones(DH, device="cuda").bfloat16()
+        sd[p + "attn.norm_k.weight"] = torch.ones(DH, device="cuda").bfloat16()
+    lin("x_embedder", Dw, CH, quantized=False)
+    lin("context_embedder", Dw, JT, quantized=False)
+    lin("proj_out", CH, Dw, quantized=False)
+    lin("norm_out.linear", 2 * Dw, Dw, quantized=False)
+    for name, d_in in (("timestep_embedder", 256), ("guidance_embedder", 256), ("text_embedder", PL)):
+        lin("time_text_embed.%s.linear_1" % name, Dw, d_in, quantized=False)
+        lin("time_text_embed.%s.linear_2" % name, Dw, Dw, quantized=False)
+
+    cg = torch.Generator().manual_seed(78)
+    img = cu(torch.randn(1, S, CH, generator=cg).bfloat16())
+    txt = cu(torch.randn(1, E, JT, generator=cg).bfloat16())
+    pooled = cu(torch.randn(1, PL, generator=cg).bfloat16())
+    rope = cu(rope_host.flux_rope_table(rope_host.flux_position_ids(E, 64, 64))[:, 0].bfloat16())
+    args = (img, txt, rope, pooled, 500.0, 3500.0)
+
+    model = ns.FluxTransformer2DModelOp("bf16", CH, nl, nsingle, DH, H, PL, JT, True, 1)
+    model.initialize(ns.LyraDiffCommonContext())
+    model.reload_transformer_model_from_state_dict(sd, "cuda")
+    got = model.transformer_forward(*args)
+    check_status()
+    assert tuple(got.shape) == (1, S, CH) and bool(torch.isfinite(got.float()).all())
+    assert 1e-3 < float(got.float().abs().mean()) < 1e3
+
+    # by hand: the mirror's embedders / output layer around the per-block C++ classes
+    chain = flux_model.FluxTransformer2DModelOp("bf16", CH, 0, 0, DH, H, PL, JT, True, 1)
+    chain.initialize(flux_blocks.LyraDiffCommonContext())
+    chain.reload_transformer_model_from_state_dict(sd, "cuda")
+    ctx = ns.LyraDiffCommonContext()
+    for i in range(nl):
+        op = ns.FluxTransformerBlockOp("bf16", Dw, H, DH, 6, 1)
+        op.initialize(ctx)
+        op.reload_model_from_state_dict("transformer_blocks.%d." % i, sd, "cuda")
+        chain.double_blocks.append(_CppBlock(op, True))
+    for j in range(nsingle):
+        op = ns.FluxSingleTransformerBlockOp("bf16", Dw, H, DH, 4, 1)
+        op.initialize(ctx)
+        op.reload_model_from_state_dict("single_transformer_blocks.%d." % j, sd, "cuda")
+        chain.single_blocks.append(_CppBlock(op, False))
+    chain.n_double, chain.n_single = nl, nsingle
+    want = chain.transformer_forward(*args)
+    check_status()
+    assert torch.equal(got, want), "max |diff| %g" % float((got.float() - want.float()).abs().max())

@@ -94,3 +94,28 @@ def test_workspace_is_checked(layers):
     st = L.lyraq_linear_fp8_forward(y.data_ptr(), x.data_ptr(), 1, s.data_ptr(), w.data_ptr(), s.data_ptr(), None, None, 0.0, 0,
                                     128, 256, 512, small.data_ptr(), small.numel(), None)
     assert st == 5  # LYRAQ_ERR_WORKSPACE
+
+
+def test_int8_linear_from_the_reference_bin_layout(layers, tmp_path):
+    """SDXL INT8 on-disk layout (<name>.weight_int8.bin, .weight_quant_scale.bin, .input_quant_scale.bin,
+    .pre_quant_scale.bin, .bias.bin): write the files the exporter writes, read them back, same bits as the layer built
+    from tensors; a short file is refused."""
+    import numpy as np
+    wl = workloads.int8_smoothquant_linear(m=130, k=640, n=200, seed=34)
+    s = torch.tensor([0.21], dtype=torch.float32)
+    prefix, name = str(tmp_path) + "/down_blocks.1.attentions.0.transformer_blocks.0.", "ff.net.0.proj"
+    wl["qw"].numpy().tofile(prefix + name + ".weight_int8.bin")
+    wl["s_w"].numpy().tofile(prefix + name + ".weight_quant_scale.bin")
+    s.numpy().tofile(prefix + name + ".input_quant_scale.bin")
+    wl["pre"].numpy().tofile(prefix + name + ".pre_quant_scale.bin")
+    wl["bias"].numpy().astype(np.float16).tofile(prefix + name + ".bias.bin")
+    lin = layers.SmoothQuantLinear.from_bin(prefix, name, 200, 640)
+    ref = layers.SmoothQuantLinear(cu(wl["qw"]), cu(wl["s_w"]), cu(wl["pre"]), bias=cu(wl["bias"]), input_scale=cu(s))
+    x = cu(wl["x"])
+    assert_bit_equal(lin.forward(x), ref.forward(x).cpu())
+    qs = quant.sq_input_quant(wl["x"], wl["pre"], s)
+    assert_bit_equal(lin.forward(x), gemm.int8_gemm(qs, wl["qw"], wl["s_w"], s, torch.float16, bias=wl["bias"]))
+    wl["s_w"].numpy()[:-1].tofile(prefix + name + ".weight_quant_scale.bin")
+    with pytest.raises(RuntimeError, match="expected 200"):
+        layers.SmoothQuantLinear.from_bin(prefix, name, 200, 640)
+    check_status()

@@ -83,3 +83,24 @@ def test_device_argument_is_validated_before_anything_is_loaded():
         warnings.simplefilter("error")
         with pytest.raises(RuntimeError, match="weights not loaded"):
             op.clear_lora()
+
+
+def test_sdxl_int8_bin_manifest_names_the_reference_files():
+    from lyradiff_b200 import layers
+    files = layers.SmoothQuantLinear.bin_files("attn1.to_qkv", 1920, 640, has_bias=False)
+    assert [f[0] for f in files] == ["attn1.to_qkv.weight_int8.bin", "attn1.to_qkv.weight_quant_scale.bin",
+                                     "attn1.to_qkv.input_quant_scale.bin", "attn1.to_qkv.pre_quant_scale.bin"]
+    assert [f[2] for f in files] == [(1920, 640), (1920,), (1,), (640,)]
+    assert layers.SmoothQuantLinear.bin_files("ff.net.2", 640, 2560)[-1] == ("ff.net.2.bias.bin", "model", (640,))
+
+
+def test_unbuilt_quant_levels_are_refused_by_name():
+    """The reference's constructors default to quant_level 0 (16-bit); this library builds the quantized levels only and
+    says so at construction, in the mirrors as in the C++ classes."""
+    for level in (0, 3, 5):
+        with pytest.raises(NotImplementedError, match="only 1, 2"):
+            flux_blocks.FluxSingleTransformerBlockOp("bf16", 3072, 24, 128, 4, level)
+        with pytest.raises(NotImplementedError, match="only 1, 2"):
+            flux_blocks.FluxTransformerBlockOp("bf16", 3072, 24, 128, 6, level)
+    with pytest.raises(NotImplementedError):
+        flux_blocks.FluxSingleTransformerBlockOp()            # the reference's default arguments

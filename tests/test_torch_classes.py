@@ -69,3 +69,18 @@ def test_whole_model_class_is_registered_with_the_reference_defaults(ns):
     # keyword construction with the defaults of th_op/pybind.cc:13-27 (quant_level 0 is not built here)
     with pytest.raises(RuntimeError, match="quant_level"):
         ns.FluxTransformer2DModelOp(num_layers=1, num_single_layers=1)
+
+
+def test_block_classes_take_the_reference_keywords_and_defaults(ns):
+    """th_op/pybind.cc:66-96: inference_dtype="bf16", embedding_dim=3072, embedding_head_num=24, embedding_head_dim=128,
+    mlp_scale=6 (double-stream) / 4 (single-stream), quant_level=0.  Level 0 is not built here, so the all-default
+    construction is refused by name; with a built level the keywords and the other defaults go through."""
+    for cls in (ns.FluxSingleTransformerBlockOp, ns.FluxTransformerBlockOp):
+        with pytest.raises(RuntimeError, match="quant_level 0"):
+            cls()
+        op = cls(quant_level=1)                                   # every other argument at its default
+        with pytest.raises(RuntimeError, match="weights not loaded"):
+            op.clear_lora()
+        op = cls(inference_dtype="fp16", embedding_dim=256, embedding_head_num=2, embedding_head_dim=128, quant_level=2)
+        with pytest.raises(RuntimeError, match="embedding_dim must equal"):
+            cls(embedding_dim=512, embedding_head_num=2, embedding_head_dim=128, quant_level=1)

@@ -26,7 +26,7 @@ def test_static_scratch_forward_matches_workspace_forward_twice_in_a_row():
     from lyradiff_b200 import _lib, layers, ops
 
     L = _lib.lib()
-    cap = L.lyraq_static_scratch_bytes()
+    cap = L.lyraq_static_scratch_bytes()       # also the start-up warm-up: resolves the array on this device
     assert cap == 16 << 20
     stream = torch.cuda.current_stream().cuda_stream
     # two different problems back to back: the second one finds the first one's bytes in the array
