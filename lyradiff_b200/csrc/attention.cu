@@ -5,19 +5,21 @@
 // FP8 linear that follows (the reference runs cudaD2DScaleCpyConvert over the attention output as a separate pass,
 // FluxSingleTransformerFP8Block.cc:254, FluxAttnPostFP8Processor.cc:135,168).
 //
-// One CTA owns 256 query rows of one head (two tiles of 128) and walks the keys in tiles of 128:
-//   warp 8    lane 0: TMA producer.  Q once (2 x 32 KB), then K_0, V_0, K_1, V_1, ... through a ring of five 32 KB slots.
-//             Every tile is two SWIZZLE_128B boxes of 128 rows x 64 columns, so q and k tiles are K-major operands and
-//             the v tile is an MN-major operand as it lies in memory -- nothing is transposed.
-//   warp 9    lane 0: MMA issuer; the warp owns the 512 columns of tensor memory:
-//             S_0 | S_1 | O_0 | O_1, 128 fp32 columns each.  S_t = Q_t K_j^T (8 x tcgen05.mma kind::f16, K = 16),
-//             O_t += P_t V_j with P_t read from tensor memory, where the softmax warps wrote it over S_t.
-//   warps 0-3 softmax of query tile 0, warps 4-7 of tile 1: a thread owns one query row (its tensor-memory lane), so
-//             row maxima and sums need no shuffles.  exp2 with the scale folded in; the running maximum is only
-//             raised when it grew by more than 2^8 (the accumulator and the row sum then share the stale reference,
-//             which cancels in O / l), so O is rescaled in tensor memory rarely, by these same warps, between two of
-//             their tile's MMAs.  After the last key tile the warps normalise and store their rows.
-// The two query tiles alternate on the tensor pipe: while the softmax warps of one tile work, the MMAs of the other run.
+// One CTA owns 256 query rows of one head (two tiles of 128) and walks the keys in steps of 64:
+//   warp 8      lane 0: TMA producer.  Q once (2 x 32 KB), then K_0, V_0, K_1, V_1, ... (tiles of 128 keys, two steps each)
+//               through a ring of five 32 KB slots.  Every tile is two SWIZZLE_128B boxes of 128 rows x 64 columns, so q
+//               and k tiles are K-major operands and the v tile is an MN-major operand as it lies in memory.
+//   warps 9, 10 lane 0: MMA issuer of query tile 0 / 1.  Tensor memory (512 columns, owned by warp 9) per query tile:
+//               S_a | S_b (64 fp32 columns each) | O (128 columns).  Step i: S[i & 1] = Q K_i^T (8 x tcgen05.mma kind::f16,
+//               M 128, N 64, K 16); O += P_i V_i (4 MMAs, K 16) with P_i read from tensor memory, where the softmax warps
+//               wrote it over the first half of S[i & 1].  The scores of step i + 1 are issued BEFORE the softmax of step i
+//               has finished (they go to the other S buffer), so the softmax warps never wait for the tensor pipe and the
+//               tensor pipe always has the next scores and the previous P V to work on.
+//   warps 0-3   softmax of query tile 0, warps 4-7 of tile 1: a thread owns one query row (its tensor-memory lane), so
+//               row maxima and sums need no shuffles.  exp2 with the scale folded in; the running maximum is only raised
+//               when it grew by more than 2^8 (the accumulator and the row sum then share the stale reference, which
+//               cancels in O / l), so O is rescaled in tensor memory rarely, by these same warps, between two of their
+//               tile's P V products.  After the last step the warps normalise and store their rows.
 // Every wait is bounded; on a timeout the role records it in the status word, raises the block's abort flag and all
 // roles leave; tensor memory is freed at the common exit.
 #include "common.cuh"
@@ -34,7 +36,8 @@ typedef CUresult (*EncodeTiledFnAttn)(CUtensorMap*, CUtensorMapDataType, cuuint3
 namespace attn {
 
 constexpr int kHeadDim   = 128;
-constexpr int kTile      = 128;                       // rows of a q tile and of a k / v tile
+constexpr int kTile      = 128;                       // rows of a q tile and of a k / v tile in shared memory
+constexpr int kStep      = 64;                        // keys per softmax step
 constexpr int kQTiles    = 2;
 constexpr int kTileBytes = kTile * kHeadDim * 2;      // 32 KB: two boxes of 128 rows x 128 bytes
 constexpr int kBoxBytes  = kTileBytes / 2;
@@ -42,14 +45,14 @@ constexpr int kSlots     = 5;
 constexpr int kQOffset   = 0;
 constexpr int kRingOffset = kQTiles * kTileBytes;
 constexpr int kBarOffset = kRingOffset + kSlots * kTileBytes;
-constexpr int kXchgOffset = kBarOffset + 192;           // row maxima / sums passed between the two halves of a row
-constexpr int kSmemUsed  = kXchgOffset + 2 * kQTiles * kTile * 4;
+constexpr int kSmemUsed  = kBarOffset + 192;
 constexpr int kSmemTotal = 232448;                    // all a block may have; the tiles need 1024-byte alignment, which leaves
 static_assert(kSmemTotal - kSmemUsed >= 768, "");     // room for a base that is only 256-byte aligned
-constexpr int kThreads   = 576;                       // 16 softmax warps, the TMA producer (warp 16), the MMA issuer (warp 17)
-constexpr int kProducerWarp = 16;
-constexpr int kMmaWarp   = 17;
+constexpr int kThreads   = 352;                       // 8 softmax warps, the TMA producer (warp 8), two MMA issuers (warps 9, 10)
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp   = 9;                         // + query tile
 constexpr int kTmemCols  = 512;
+constexpr int kTileCols  = 256;                       // tensor-memory columns per query tile: S_a 64 | S_b 64 | O 128
 constexpr float kRescaleThreshold = 8.0f;             // in log2 units
 
 struct Params {
@@ -81,12 +84,6 @@ __device__ __forceinline__ float max3(float a, float b, float c)
     return d;
 }
 
-// barrier among `count` threads (whole warps) of the block, ids 1..15
-__device__ __forceinline__ void named_bar_sync(int id, int count)
-{
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
 __device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z)
 {
     asm volatile(
@@ -108,17 +105,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
         }
         return;
     }
-    const uint32_t bars      = smem_base + kBarOffset;
-    // barriers: q_full | slot_full[5] | slot_empty[5] | s_full[2] | p_ready[2] | pv_done[2]
+    const uint32_t bars = smem_base + kBarOffset;
+    // barriers: q_full | slot_full[5] | slot_empty[5] | s_full[tile][buffer] | p_ready[tile][buffer] | pv_done[tile] | o_done[tile]
     const uint32_t q_full = bars;
     auto slot_full  = [&](int s) { return bars + 8u * (1 + s); };
     auto slot_empty = [&](int s) { return bars + 8u * (1 + kSlots + s); };
-    auto s_full     = [&](int t) { return bars + 8u * (1 + 2 * kSlots + t); };
-    auto p_ready    = [&](int t) { return bars + 8u * (3 + 2 * kSlots + t); };
-    auto pv_done    = [&](int t) { return bars + 8u * (5 + 2 * kSlots + t); };
-    uint32_t*     tmem_slot  = reinterpret_cast<uint32_t*>(gen_base + kBarOffset + 8 * (7 + 2 * kSlots));
+    auto s_full     = [&](int t, int b) { return bars + 8u * (1 + 2 * kSlots + 2 * t + b); };
+    auto p_ready    = [&](int t, int b) { return bars + 8u * (5 + 2 * kSlots + 2 * t + b); };
+    auto pv_done    = [&](int t) { return bars + 8u * (9 + 2 * kSlots + t); };
+    auto o_done     = [&](int t) { return bars + 8u * (11 + 2 * kSlots + t); };
+    uint32_t*     tmem_slot  = reinterpret_cast<uint32_t*>(gen_base + kBarOffset + 8 * (13 + 2 * kSlots));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float*        xchg       = reinterpret_cast<float*>(gen_base + kXchgOffset);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -128,12 +125,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
         mbar_init(q_full, 1);
         for (int s = 0; s < kSlots; ++s) {
             mbar_init(slot_full(s), 1);
-            mbar_init(slot_empty(s), 1);
+            mbar_init(slot_empty(s), kQTiles);           // both tiles' issuers release a slot
         }
         for (int t = 0; t < kQTiles; ++t) {
-            mbar_init(s_full(t), 1);
-            mbar_init(p_ready(t), 256);
+            for (int b = 0; b < 2; ++b) {
+                mbar_init(s_full(t, b), 1);
+                mbar_init(p_ready(t, b), 128);
+            }
             mbar_init(pv_done(t), 1);
+            mbar_init(o_done(t), 1);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -154,7 +154,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
     const int h  = (blockIdx.x / p.q_blocks) % p.heads;
     const int b  = blockIdx.x / (p.q_blocks * p.heads);
     const int q0 = qb * (kQTiles * kTile);
-    const int n_kv = (p.seq + kTile - 1) / kTile;
+    const int n_steps = (p.seq + kStep - 1) / kStep;    // softmax steps of 64 keys
+    const int n_kv    = (n_steps + 1) / 2;              // k / v tiles of 128 keys
     const int col_q = h * kHeadDim, col_k = (p.heads + h) * kHeadDim, col_v = (2 * p.heads + h) * kHeadDim;
 
     if (warp == kProducerWarp) {
@@ -211,11 +212,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
                 }
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ------------------------------------------------------------------ MMA issuer
+    } else if (warp >= kMmaWarp) {
+        // ------------------------------------------------------------------ MMA issuer of query tile t
         if (lane == 0) {
-            constexpr uint32_t kAb = sizeof(T) == 2 && TypeTag<T>::value == LYRAQ_BF16 ? 1u : 0u;
-            const uint32_t idesc_qk = umma_idesc(1u, kAb, 128, 128);
+            const int      t      = warp - kMmaWarp;
+            const uint32_t tcol   = tmem_base + (uint32_t)(t * kTileCols);
+            constexpr uint32_t kAb = TypeTag<T>::value == LYRAQ_BF16 ? 1u : 0u;
+            const uint32_t idesc_qk = umma_idesc(1u, kAb, 128, kStep);
             const uint32_t idesc_pv = umma_idesc(1u, kAb, 128, 128) | kIdescBMajorMN;
             bool ok = true;
             auto wait_or_fail = [&](uint32_t bar, uint32_t parity, unsigned code) {
@@ -228,84 +231,80 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
             };
             auto slot_of  = [](int item) { return item % kSlots; };
             auto phase_of = [](int item) { return (uint32_t)((item / kSlots) & 1); };
-            // S_t = Q_t K_j^T
-            auto issue_qk = [&](int t, int j) {
-                const uint32_t kbase = smem_base + kRingOffset + slot_of(2 * j) * kTileBytes;
+            // the last step that reads a k / v tile gives the tile's slot back (this issuer's share of it)
+            auto last_use = [&](int i) { return (i & 1) == 1 || i == n_steps - 1; };
+            // S[i & 1] = Q_t K_i^T, 64 keys: rows (i & 1) * 64 .. + 63 of k tile i / 2
+            auto issue_qk = [&](int i) {
+                const int      kslot = slot_of(2 * (i >> 1));
+                const uint32_t kbase = smem_base + kRingOffset + kslot * kTileBytes + (uint32_t)((i & 1) * kStep * 128);
                 const uint32_t qbase = smem_base + kQOffset + t * kTileBytes;
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks) {
                     const uint32_t off = (uint32_t)((ks >> 2) * kBoxBytes + (ks & 3) * 32);
-                    mma_f16(tmem_base + (uint32_t)(t * 128), umma_desc_k_sw128(qbase + off), umma_desc_k_sw128(kbase + off), idesc_qk,
+                    mma_f16(tcol + (uint32_t)((i & 1) * kStep), umma_desc_k_sw128(qbase + off), umma_desc_k_sw128(kbase + off), idesc_qk,
                             ks > 0 ? 1u : 0u);
                 }
-                tc_commit(s_full(t));
+                tc_commit(s_full(t, i & 1));
+                if (last_use(i)) {
+                    tc_commit(slot_empty(kslot));
+                }
             };
-            // O_t (+)= P_t V_j, P_t in tensor memory over the first 64 columns of S_t
-            auto issue_pv = [&](int t, int j) {
-                const uint32_t vbase = smem_base + kRingOffset + slot_of(2 * j + 1) * kTileBytes;
+            // O_t (+)= P_i V_i: P in tensor memory over the first 32 columns of S[i & 1], v rows (i & 1) * 64 .. + 63
+            auto issue_pv = [&](int i) {
+                const int      vslot = slot_of(2 * (i >> 1) + 1);
+                const uint32_t vbase = smem_base + kRingOffset + vslot * kTileBytes + (uint32_t)((i & 1) * kStep * 128);
 #pragma unroll
-                for (int ks = 0; ks < 8; ++ks) {
-                    mma_f16_ts(tmem_base + (uint32_t)(256 + t * 128), tmem_base + (uint32_t)(t * 128 + ks * 8),
-                               umma_desc_mn_sw128(vbase + (uint32_t)(ks * 2048), (uint32_t)kBoxBytes), idesc_pv,
-                               (j > 0 || ks > 0) ? 1u : 0u);
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    mma_f16_ts(tcol + 128u, tcol + (uint32_t)((i & 1) * kStep + k4 * 8),
+                               umma_desc_mn_sw128(vbase + (uint32_t)(k4 * 2048), (uint32_t)kBoxBytes), idesc_pv, (i > 0 || k4 > 0) ? 1u : 0u);
                 }
                 tc_commit(pv_done(t));
+                if (last_use(i)) {
+                    tc_commit(slot_empty(vslot));
+                }
+                if (i == n_steps - 1) {
+                    tc_commit(o_done(t));   // the accumulator is final
+                }
             };
             if (wait_or_fail(q_full, 0u, 0x3200u) && wait_or_fail(slot_full(slot_of(0)), phase_of(0), 0x3201u)) {
                 tc_fence_after_sync();
-                issue_qk(0, 0);
-                issue_qk(1, 0);
-                tc_commit(slot_empty(slot_of(0)));
+                issue_qk(0);
+                if (n_steps > 1) {
+                    issue_qk(1);
+                }
             }
-            for (int j = 0; j < n_kv && ok; ++j) {
-                const bool more = j + 1 < n_kv;
-                for (int t = 0; t < kQTiles && ok; ++t) {
-                    if (!wait_or_fail(p_ready(t), (uint32_t)(j & 1), 0x3210u | (unsigned)t)) {
-                        break;
-                    }
-                    if (t == 0 && !wait_or_fail(slot_full(slot_of(2 * j + 1)), phase_of(2 * j + 1), 0x3220u)) {
+            for (int i = 0; i < n_steps && ok; ++i) {
+                if (!wait_or_fail(p_ready(t, i & 1), (uint32_t)((i >> 1) & 1), 0x3210u | (unsigned)t)) {
+                    break;
+                }
+                if ((i & 1) == 0 && !wait_or_fail(slot_full(slot_of(i + 1)), phase_of(i + 1), 0x3220u | (unsigned)t)) {  // v tile i / 2
+                    break;
+                }
+                tc_fence_after_sync();
+                issue_pv(i);
+                if (i + 2 < n_steps) {
+                    if ((i & 1) == 0 && !wait_or_fail(slot_full(slot_of(i + 2)), phase_of(i + 2), 0x3230u | (unsigned)t)) {  // k tile i / 2 + 1
                         break;
                     }
                     tc_fence_after_sync();
-                    issue_pv(t, j);
-                    if (t == 1) {
-                        tc_commit(slot_empty(slot_of(2 * j + 1)));
-                    }
-                    if (more) {
-                        if (t == 0 && !wait_or_fail(slot_full(slot_of(2 * j + 2)), phase_of(2 * j + 2), 0x3230u)) {
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        issue_qk(t, j + 1);
-                        if (t == 1) {
-                            tc_commit(slot_empty(slot_of(2 * j + 2)));
-                        }
-                    }
+                    issue_qk(i + 2);
                 }
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax + epilogue
-        // Two threads per query row: warps 0-7 take keys / output columns 0..63 of their tile, warps 8-15 columns 64..127;
-        // the two halves of a row meet through shared memory for the row maximum (every tile) and the row sum (once).
-        const int      half     = warp >> 3;
-        const int      t        = (warp >> 2) & 1;                             // query tile
+        // ------------------------------------------------------------------ softmax + epilogue, one thread per query row
+        const int      t        = warp >> 2;                                   // query tile
         const int      quadrant = warp & 3;                                    // tensor-memory lane quadrant of this warp
-        const int      row_t    = quadrant * 32 + lane;                        // row inside the tile
-        const uint32_t lane_off = (uint32_t)(quadrant * 32) << 16;
-        const uint32_t s_addr   = tmem_base + lane_off + (uint32_t)(t * 128 + half * 64);
-        const uint32_t p_addr   = tmem_base + lane_off + (uint32_t)(t * 128 + half * 32);
-        const uint32_t o_addr   = tmem_base + lane_off + (uint32_t)(256 + t * 128 + half * 64);
-        float*         my_slot  = xchg + (half * kQTiles + t) * kTile + row_t;
-        const float*   peer_slot = xchg + ((half ^ 1) * kQTiles + t) * kTile + row_t;
-        const int      pair_bar = 1 + t * 4 + quadrant;                        // named barrier of the two warps of these rows
+        const uint32_t tcol     = tmem_base + ((uint32_t)(quadrant * 32) << 16) + (uint32_t)(t * kTileCols);
+        const uint32_t o_addr   = tcol + 128u;
         const float    c        = p.scale_log2;
         float          m        = -INFINITY;                                   // reference maximum of this row (raw scores)
-        float          l        = 0.0f;                                        // this half's sum of exp2((s - m) c)
+        float          l        = 0.0f;                                        // sum of exp2((s - m) c)
         bool           ok       = true;
 
-        for (int j = 0; j < n_kv && ok; ++j) {
-            if (!__all_sync(0xffffffffu, mbar_wait(s_full(t), (uint32_t)(j & 1), abort_flag, p.wait_limit_ns))) {
+        for (int i = 0; i < n_steps && ok; ++i) {
+            const uint32_t s_addr = tcol + (uint32_t)((i & 1) * kStep);
+            if (!__all_sync(0xffffffffu, mbar_wait(s_full(t, i & 1), (uint32_t)((i >> 1) & 1), abort_flag, p.wait_limit_ns))) {
                 report_timeout(p.status, 0x3300u | (unsigned)t);
                 *abort_flag = 1;
                 ok = false;
@@ -316,12 +315,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
             tmem_ld_32x32(s_addr, s);
             tmem_ld_32x32(s_addr + 32, s + 32);
             tmem_ld_wait();
-            const int valid = p.seq - j * kTile - half * 64;                   // keys of this half inside the sequence
-            if (valid < 64) {
+            const int valid = p.seq - i * kStep;                               // keys of this step inside the sequence
+            if (valid < kStep) {
 #pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    if (i >= valid) {
-                        s[i] = 0xff800000u;                                    // -inf: zero-filled keys take no weight
+                for (int k = 0; k < 64; ++k) {
+                    if (k >= valid) {
+                        s[k] = 0xff800000u;                                    // -inf: zero-filled keys take no weight
                     }
                 }
             }
@@ -330,25 +329,24 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
             float mx2 = max3(__uint_as_float(s[6]), __uint_as_float(s[7]), __uint_as_float(s[8]));
             float mx3 = max3(__uint_as_float(s[9]), __uint_as_float(s[10]), __uint_as_float(s[11]));
 #pragma unroll
-            for (int i = 12; i < 60; i += 8) {
-                mx0 = max3(mx0, __uint_as_float(s[i]), __uint_as_float(s[i + 1]));
-                mx1 = max3(mx1, __uint_as_float(s[i + 2]), __uint_as_float(s[i + 3]));
-                mx2 = max3(mx2, __uint_as_float(s[i + 4]), __uint_as_float(s[i + 5]));
-                mx3 = max3(mx3, __uint_as_float(s[i + 6]), __uint_as_float(s[i + 7]));
+            for (int k = 12; k < 60; k += 8) {
+                mx0 = max3(mx0, __uint_as_float(s[k]), __uint_as_float(s[k + 1]));
+                mx1 = max3(mx1, __uint_as_float(s[k + 2]), __uint_as_float(s[k + 3]));
+                mx2 = max3(mx2, __uint_as_float(s[k + 4]), __uint_as_float(s[k + 5]));
+                mx3 = max3(mx3, __uint_as_float(s[k + 6]), __uint_as_float(s[k + 7]));
             }
             mx0 = max3(mx0, __uint_as_float(s[60]), __uint_as_float(s[61]));
             mx1 = max3(mx1, __uint_as_float(s[62]), __uint_as_float(s[63]));
-            float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-            *my_slot = mx;
-            named_bar_sync(pair_bar, 64);
-            mx = fmaxf(mx, *peer_slot);                                        // a half with no valid key contributes -inf
-            if (j == 0) {
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            if (i == 0) {
                 m = mx;
             } else {
                 const bool raise = (mx - m) * c > kRescaleThreshold;
                 if (__any_sync(0xffffffffu, raise)) {
-                    // the accumulator may only be touched between this tile's MMAs: the previous P V has to be complete
-                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((j - 1) & 1), abort_flag, p.wait_limit_ns))) {
+                    // the accumulator may only be touched between this tile's P V products: the previous one has to be complete
+                    // (the next one is not issued before this step's P is ready).  S_i exists, so P V of step i - 2 is
+                    // complete: pv_done has finished i - 1 or i phases, which the parity of phase i - 1 tells apart
+                    if (!__all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((i - 1) & 1), abort_flag, p.wait_limit_ns))) {
                         report_timeout(p.status, 0x3310u | (unsigned)t);
                         *abort_flag = 1;
                         ok = false;
@@ -361,13 +359,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
                         l *= f;
                     }
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {                             // rare path: small pieces keep the registers free
+                    for (int cc = 0; cc < 8; ++cc) {                             // rare path: small pieces keep the registers free
                         uint32_t o[16];
                         tmem_ld_32x16(o_addr + cc * 16, o);
                         tmem_ld_wait();
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+                        for (int k = 0; k < 16; ++k) {
+                            o[k] = __float_as_uint(__uint_as_float(o[k]) * f);
                         }
                         tmem_st_32x16(o_addr + cc * 16, o);
                     }
@@ -382,20 +380,19 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
             for (int cc = 0; cc < 4; ++cc) {
                 uint32_t w[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float2 x = fma_f32x2(make_float2(__uint_as_float(s[cc * 16 + 2 * i]), __uint_as_float(s[cc * 16 + 2 * i + 1])), c2, nmc2);
+                for (int k = 0; k < 8; ++k) {
+                    const float2 x = fma_f32x2(make_float2(__uint_as_float(s[cc * 16 + 2 * k]), __uint_as_float(s[cc * 16 + 2 * k + 1])), c2, nmc2);
                     const float2 e = make_float2(ex2_approx(x.x), ex2_approx(x.y));
-                    if (i & 1) {
+                    if (k & 1) {
                         sum_b = add_f32x2(sum_b, e);
                     } else {
                         sum_a = add_f32x2(sum_a, e);
                     }
-                    w[i] = Pair<T>::from_f32(e.x, e.y);
+                    w[k] = Pair<T>::from_f32(e.x, e.y);
                 }
-                // P over the start of S: columns [8 k, 8 k + 8) hold keys [16 k, 16 k + 16); this half's S is in registers,
-                // and the other half's first columns are overwritten only after the pair barrier above, i.e. after its loads
+                // P over the start of this S buffer: columns [8 cc, 8 cc + 8) hold keys [16 cc, 16 cc + 16), all in registers by now
                 asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                             ::"r"(p_addr + (uint32_t)(cc * 8)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
+                             ::"r"(s_addr + (uint32_t)(cc * 8)), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]),
                                "r"(w[6]), "r"(w[7])
                              : "memory");
             }
@@ -403,53 +400,52 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
             l += sum.x + sum.y;
             tmem_st_wait();
             tc_fence_before_sync();
-            mbar_arrive(p_ready(t));
+            mbar_arrive(p_ready(t, i & 1));
         }
 
-        // ---- epilogue: O / l, rounded to T, stored as T or as e4m3 of that value
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done(t), (uint32_t)((n_kv - 1) & 1), abort_flag, p.wait_limit_ns))) {
+        // ---- epilogue: O / l, rounded to T, stored as T or as e4m3 of that value.  The softmax runs up to two P V products
+        // ahead of the tensor pipe here, which a parity wait on pv_done cannot tell apart (its phase may be one OR two
+        // behind): the last product signals a barrier of its own.
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(o_done(t), 0u, abort_flag, p.wait_limit_ns))) {
             report_timeout(p.status, 0x3320u | (unsigned)t);
             *abort_flag = 1;
             ok = false;
         }
         if (ok) {
             tc_fence_after_sync();
-            *my_slot = l;
-            named_bar_sync(pair_bar, 64);
-            l += *peer_slot;
-            const int row = q0 + t * kTile + row_t;                            // row inside the sequence
+            const int row = q0 + t * kTile + quadrant * 32 + lane;            // row inside the sequence
             const int part = row >= p.split ? 1 : 0;
             const long long r_out = part ? row - p.split : row;
             const float inv_l = 1.0f / l;
             // rows past the end of the sequence belong to no part (out_scale[1] may be NULL): they load nothing and store nothing
             const float qs = (p.out_e4m3 && row < p.seq) ? 1.0f / ld_f32(p.out_scale[part]) : 1.0f;
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {
+            for (int cc = 0; cc < 4; ++cc) {
                 uint32_t o[32];
                 tmem_ld_32x32(o_addr + cc * 32, o);
                 tmem_ld_wait();
                 if (row < p.seq) {
                     uint32_t w[16];
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        w[i] = Pair<T>::from_f32(__uint_as_float(o[2 * i]) * inv_l, __uint_as_float(o[2 * i + 1]) * inv_l);
+                    for (int k = 0; k < 16; ++k) {
+                        w[k] = Pair<T>::from_f32(__uint_as_float(o[2 * k]) * inv_l, __uint_as_float(o[2 * k + 1]) * inv_l);
                     }
-                    const long long col = (long long)h * kHeadDim + half * 64 + cc * 32;
+                    const long long col = (long long)h * kHeadDim + cc * 32;
                     if (p.out_e4m3) {
                         uint8_t* dst = static_cast<uint8_t*>(p.out[part]) + (long long)b * p.out_batch[part] + r_out * p.out_ld[part] + col;
                         uint32_t q8[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            const float2 a = Pair<T>::to_f32(w[2 * i]), bb = Pair<T>::to_f32(w[2 * i + 1]);
-                            q8[i] = f32x2_to_e4m3x2(a.x * qs, a.y * qs) | (f32x2_to_e4m3x2(bb.x * qs, bb.y * qs) << 16);
+                        for (int k = 0; k < 8; ++k) {
+                            const float2 a = Pair<T>::to_f32(w[2 * k]), bb = Pair<T>::to_f32(w[2 * k + 1]);
+                            q8[k] = f32x2_to_e4m3x2(a.x * qs, a.y * qs) | (f32x2_to_e4m3x2(bb.x * qs, bb.y * qs) << 16);
                         }
                         *reinterpret_cast<uint4*>(dst)      = make_uint4(q8[0], q8[1], q8[2], q8[3]);
                         *reinterpret_cast<uint4*>(dst + 16) = make_uint4(q8[4], q8[5], q8[6], q8[7]);
                     } else {
                         T* dst = static_cast<T*>(p.out[part]) + (long long)b * p.out_batch[part] + r_out * p.out_ld[part] + col;
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            reinterpret_cast<uint4*>(dst)[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+                        for (int k = 0; k < 4; ++k) {
+                            reinterpret_cast<uint4*>(dst)[k] = make_uint4(w[4 * k], w[4 * k + 1], w[4 * k + 2], w[4 * k + 3]);
                         }
                     }
                 }
@@ -467,7 +463,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const Params 
 
 }  // namespace attn
 
-// out = softmax(q k^T * softmax_scale) v for qkv [batch, seq, 3, heads, 128]; see lyraq_attention in the header.
 // Test hook (lyraq_debug_attention_wait_test): a producer that never signals and a short wait limit, so that the path a
 // timed-out wait takes -- status word, abort flag, every role leaving, tensor memory freed -- can be run without a fault.
 static int                g_attn_skip_loads    = 0;

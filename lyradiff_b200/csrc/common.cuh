@@ -355,6 +355,46 @@ __device__ __forceinline__ void quant8_s8(const float2* v, float s, float r, uin
     w1 = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
 }
 
+// INT4 group-of-64 quantize, the part 8 consecutive lanes do together: each lane holds 8 consecutive values v of the group
+// (already divided by the smoothing vector), the group maximum is formed with xor-shuffles over the 8 lanes, s = amax / 7,
+// q = sat_s4(rne(fl(v / s))).  Returns the lane's 8 nibbles (element j at bits 4 j) and s.  All 32 lanes of the warp call it.
+__device__ __forceinline__ uint32_t int4_g64_quantize8(const float (&v)[8], float& s_out)
+{
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        amax = fmaxf(amax, fabsf(v[j]));
+    }
+#pragma unroll
+    for (int m = 1; m < 8; m <<= 1) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    }
+    const float s = amax / 7.0f;
+    uint32_t    w = 0;
+    if (s > 0.0f && s <= 3.0e38f) {
+        // q = rne(fl(v / s)) without a division or a conversion per element: |v / s| <= 7 (1 + 2^-23), so the exact
+        // int8 form applies (reciprocal multiply, magic-number rounding, tie check with the IEEE divide as its
+        // fallback); the nibbles are the low halves of its eight bytes
+        const float2 vp[4] = {make_float2(v[0], v[1]), make_float2(v[2], v[3]), make_float2(v[4], v[5]), make_float2(v[6], v[7])};
+        uint32_t     w0, w1;
+        quant8_s8_inrange(vp, s, 1.0f / s, w0, w1);
+        w0 &= 0x0F0F0F0Fu;
+        w1 &= 0x0F0F0F0Fu;
+        w = __byte_perm(w0 | (w0 >> 4), w1 | (w1 >> 4), 0x6420);
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            int qi;
+            // v/s with s == 0 is NaN (or inf); cvt.rni.s32.f32 maps NaN to 0 exactly as the reference's does.
+            asm("cvt.rni.s32.f32 %0, %1;" : "=r"(qi) : "f"(v[j] / s));
+            qi = max(-8, min(7, qi));
+            w |= (uint32_t)(qi & 0xf) << (4 * j);
+        }
+    }
+    s_out = s;
+    return w;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Host-side checks.
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -12,6 +12,11 @@
 //   warp 0   lane 0: TMA producer (x tile 32 x 128 B, lora_down tile 128 x 128 B, ring of 8 stages);
 //            afterwards the whole warp reads accumulator lanes 0..31 and stores act
 //   warp 1   lane 0: MMA issuer; the warp owns the tensor-memory allocation
+//   warps 2-5 (fused form only): the int4 quantize of the same x tiles.  One stage holds, for each of the CTA's 32 rows,
+//            exactly one group of 64 values (a 128-byte row of the swizzled tile), so x is read from memory once for
+//            both results, as in the reference's fused kernel.  Warp w takes the stages with kb % 4 == w - 2: 8 lanes
+//            share a group (the arithmetic of int4_g64_kernel, bit for bit), 4 rows per pass, 8 passes; a stage goes
+//            back to the producer when both the MMAs that read it and its quantizer warp are done.
 // All waits are bounded; a timeout sets the status word and the block leaves.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -34,16 +39,23 @@ constexpr int kXTile     = kRows * kBlockKB;      // 4 KB
 constexpr int kStage     = kDownTile + kXTile;
 constexpr int kBarOffset = kStages * kStage;
 constexpr int kSmemTotal = kBarOffset + 256 + 1024;
-constexpr int kThreads   = 64;
+constexpr int kThreads   = 64;                    // down projection alone
+constexpr int kQuantWarps = 4;
+constexpr int kThreadsFused = kThreads + 32 * kQuantWarps;
 
 struct Params {
     float*        act;   // [m, 32]
     int           m, k;
     int           is_bf16;
     unsigned int* status;
+    // fused int4 quantize (all null / 0 for the down projection alone)
+    uint32_t*     q;        // [m, k / 8]: eight nibbles per word
+    float*        q_scale;  // [m, k / 64]
+    const float*  smooth;   // [k] or null
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+template<bool FUSED>
+__global__ void __launch_bounds__(FUSED ? kThreadsFused : kThreads, 1)
 lora_down_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_down, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -63,7 +75,7 @@ lora_down_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), 1);
+            mbar_init(empty_bar(s), FUSED ? 2 : 1);   // the MMAs' commit, and the stage's quantizer warp
         }
         mbar_init(done_bar, 1);
         *abort_flag = 0;
@@ -138,7 +150,57 @@ lora_down_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         } else if (lane == 0) {
             report_timeout(p.status, 0x2300u);
         }
-    } else if (lane == 0) {
+    } else if (FUSED && warp >= 2) {
+        // ------------------------------------------------------------------ int4 quantize of the staged x tiles
+        const int part = lane & 7;                  // which 8 values of the group of 64
+        const int sub  = lane >> 3;                 // which of the pass's 4 rows
+        bool      ok   = true;
+        for (int kb = warp - 2; kb < num_kb && ok; kb += kQuantWarps) {
+            const int      stage = kb % kStages;
+            const uint32_t phase = (uint32_t)((kb / kStages) & 1);
+            if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag))) {
+                if (lane == 0) {
+                    report_timeout(p.status, 0x2500u | (unsigned)stage);
+                    *abort_flag = 1;
+                }
+                ok = false;
+                break;
+            }
+            const uint8_t* xt = gen_base + stage * kStage + kDownTile;   // 32 rows x 128 B, 128-byte swizzle
+            float4 s0 = make_float4(1.0f, 1.0f, 1.0f, 1.0f), s1 = s0;
+            if (p.smooth != nullptr) {
+                s0 = ld_f32x4(reinterpret_cast<const float4*>(p.smooth + kb * 64 + part * 8));
+                s1 = ld_f32x4(reinterpret_cast<const float4*>(p.smooth + kb * 64 + part * 8 + 4));
+            }
+#pragma unroll 2
+            for (int pass = 0; pass < kRows / 4; ++pass) {
+                const int   r = pass * 4 + sub;
+                const Vec16 raw = *reinterpret_cast<const Vec16*>(xt + r * 128 + ((part ^ (r & 7)) << 4));
+                float       v[8];
+                if (p.is_bf16) {
+                    unpack8<__nv_bfloat16>(raw, v);
+                } else {
+                    unpack8<__half>(raw, v);
+                }
+                if (p.smooth != nullptr) {
+                    v[0] /= s0.x; v[1] /= s0.y; v[2] /= s0.z; v[3] /= s0.w;
+                    v[4] /= s1.x; v[5] /= s1.y; v[6] /= s1.z; v[7] /= s1.w;
+                }
+                float          sc;
+                const uint32_t w = int4_g64_quantize8(v, sc);
+                if (row0 + r < p.m) {
+                    p.q[(size_t)(row0 + r) * (size_t)(p.k >> 3) + (size_t)(kb * 8 + part)] = w;
+                    if (part == 0) {
+                        p.q_scale[(size_t)(row0 + r) * (size_t)(p.k >> 6) + (size_t)kb] = sc;
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(empty_bar(stage));      // this warp's share of the stage's release
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
         int      stage = 0;
         uint32_t phase = 0;
         bool     ok    = true;
@@ -178,8 +240,11 @@ lora_down_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
 
 }  // namespace lora
 
-// act[m, 32] (fp32) = x[m, k] * down[32, k]^T; x and down of the same 16-bit type; k a multiple of 8.
-int launch_lora_down(float* act, const void* x, const void* down, int dtype, size_t m, size_t k, cudaStream_t stream)
+// act[m, 32] (fp32) = x[m, k] * down[32, k]^T; x and down of the same 16-bit type; k a multiple of 8.  With q != null the
+// same launch also writes the int4 group-64 quantization of x / smooth (packed nibbles q [m, k / 2 bytes], fp32 scales
+// q_scale [m, k / 64]); k then has to be a multiple of 64.
+static int launch_lora_down_impl(float* act, const void* x, const void* down, int dtype, size_t m, size_t k, uint8_t* q, float* q_scale,
+                                 const float* smooth, cudaStream_t stream)
 {
     if (act == nullptr || x == nullptr || down == nullptr) {
         return LYRAQ_ERR_INVALID_ARG;
@@ -190,7 +255,11 @@ int launch_lora_down(float* act, const void* x, const void* down, int dtype, siz
     if (!aligned16(x) || !aligned16(down) || (reinterpret_cast<uintptr_t>(act) & 3u) != 0) {
         return LYRAQ_ERR_INVALID_ARG;
     }
-    if ((k & 7) != 0 || k == 0 || k > 0x3fffffffu || m > 0x7fffffffu) {
+    const bool fused = q != nullptr;
+    if (fused && (q_scale == nullptr || (reinterpret_cast<uintptr_t>(q) & 3u) != 0 || (smooth != nullptr && !aligned16(smooth)))) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if ((k & 7) != 0 || k == 0 || k > 0x3fffffffu || m > 0x7fffffffu || (fused && (k & 63) != 0)) {
         return LYRAQ_ERR_UNSUPPORTED;
     }
     lora::Params p{};
@@ -198,6 +267,9 @@ int launch_lora_down(float* act, const void* x, const void* down, int dtype, siz
     p.m       = (int)m;
     p.k       = (int)k;
     p.is_bf16 = (dtype == LYRAQ_BF16) ? 1 : 0;
+    p.q       = reinterpret_cast<uint32_t*>(q);
+    p.q_scale = q_scale;
+    p.smooth  = smooth;
     p.status  = status_word_ptr();
     if (p.status == nullptr) {
         return LYRAQ_ERR_CUDA;
@@ -211,15 +283,40 @@ int launch_lora_down(float* act, const void* x, const void* down, int dtype, siz
     if (st != LYRAQ_OK) {
         return st;
     }
+    const unsigned grid = (unsigned)((m + lora::kRows - 1) / lora::kRows);
+    if (fused) {
+        const cudaError_t attr_err =
+            cudaFuncSetAttribute(lora::lora_down_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lora::kSmemTotal);
+        if (attr_err != cudaSuccess) {
+            return cuda_status(attr_err, "cudaFuncSetAttribute(lora_down_kernel<fused>, dynamic shared memory)");
+        }
+        return cuda_status(launch_kernel(lora::lora_down_kernel<true>, grid, (unsigned)lora::kThreadsFused, (size_t)lora::kSmemTotal,
+                                         stream, 1u, tx, td, p),
+                           "cudaLaunchKernelEx(lora_down_kernel<fused>)");
+    }
     const cudaError_t attr_err =
-        cudaFuncSetAttribute(lora::lora_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lora::kSmemTotal);
+        cudaFuncSetAttribute(lora::lora_down_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lora::kSmemTotal);
     if (attr_err != cudaSuccess) {
         return cuda_status(attr_err, "cudaFuncSetAttribute(lora_down_kernel, dynamic shared memory)");
     }
-    const unsigned grid = (unsigned)((m + lora::kRows - 1) / lora::kRows);
-    return cuda_status(launch_kernel(lora::lora_down_kernel, grid, (unsigned)lora::kThreads, (size_t)lora::kSmemTotal, stream, 1u,
+    return cuda_status(launch_kernel(lora::lora_down_kernel<false>, grid, (unsigned)lora::kThreads, (size_t)lora::kSmemTotal, stream, 1u,
                                      tx, td, p),
                        "cudaLaunchKernelEx(lora_down_kernel)");
+}
+
+int launch_lora_down(float* act, const void* x, const void* down, int dtype, size_t m, size_t k, cudaStream_t stream)
+{
+    return launch_lora_down_impl(act, x, down, dtype, m, k, nullptr, nullptr, nullptr, stream);
+}
+
+// The reference's fused_quantized_and_lora_down_simple (w4a4_gemm.cu:769-954) as ONE launch over one read of x.
+int launch_quant_int4_lora_down(uint8_t* q, float* q_scale, float* act, const void* x, const void* down, const float* smooth, int dtype,
+                                size_t m, size_t k, cudaStream_t stream)
+{
+    if (q == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    return launch_lora_down_impl(act, x, down, dtype, m, k, q, q_scale, smooth, stream);
 }
 
 }  // namespace lyraq

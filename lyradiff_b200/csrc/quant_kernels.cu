@@ -11,7 +11,9 @@ namespace lyraq {
 
 int device_sm_count();  // gemm_dense.cu
 unsigned int* status_word_ptr();  // api.cu
-int launch_lora_down(float* act, const void* x, const void* down, int dtype, size_t m, size_t k, cudaStream_t stream);  // lora_down.cu
+int launch_lora_down(float* act, const void* x, const void* down, int dtype, size_t m, size_t k, cudaStream_t stream);
+int launch_quant_int4_lora_down(uint8_t* q, float* q_scale, float* act, const void* x, const void* down, const float* smooth, int dtype,
+                                size_t m, size_t k, cudaStream_t stream);  // lora_down.cu
 
 enum RowMode { ROW_PLAIN = 0, ROW_ADALN = 1, ROW_LN = 2, ROW_GEGLU = 3 };
 
@@ -569,37 +571,8 @@ int4_g64_kernel(uint32_t* q, ST* q_scale, const T* x, const float* smooth, size_
                 v[j] = 0.0f;
             }
         }
-        float amax = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            amax = fmaxf(amax, fabsf(v[j]));
-        }
-#pragma unroll
-        for (int m = 1; m < 8; m <<= 1) {
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
-        }
-        const float s = amax / 7.0f;
-        uint32_t    w = 0;
-        if (s > 0.0f && s <= 3.0e38f) {
-            // q = rne(fl(v / s)) without a division or a conversion per element: |v / s| <= 7 (1 + 2^-23), so the exact
-            // int8 form applies (reciprocal multiply, magic-number rounding, tie check with the IEEE divide as its
-            // fallback); the nibbles are the low halves of its eight bytes
-            const float2 vp[4] = {make_float2(v[0], v[1]), make_float2(v[2], v[3]), make_float2(v[4], v[5]), make_float2(v[6], v[7])};
-            uint32_t     w0, w1;
-            quant8_s8_inrange(vp, s, 1.0f / s, w0, w1);
-            w0 &= 0x0F0F0F0Fu;
-            w1 &= 0x0F0F0F0Fu;
-            w = __byte_perm(w0 | (w0 >> 4), w1 | (w1 >> 4), 0x6420);
-        } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                int qi;
-                // v/s with s == 0 is NaN (or inf); cvt.rni.s32.f32 maps NaN to 0 exactly as the reference's does.
-                asm("cvt.rni.s32.f32 %0, %1;" : "=r"(qi) : "f"(v[j] / s));
-                qi = max(-8, min(7, qi));
-                w |= (uint32_t)(qi & 0xf) << (4 * j);
-            }
-        }
+        float          s;
+        const uint32_t w = int4_g64_quantize8(v, s);
         if (live) {
             q[vi] = w;
             if ((threadIdx.x & 7) == 0) {
@@ -843,12 +816,15 @@ int lyraq_quant_int4_g64(uint8_t* q, float* q_scale, float* lora_act, const void
     if ((lora_act == nullptr) != (lora_down == nullptr)) {
         return LYRAQ_ERR_INVALID_ARG;
     }
-    const int st = int4_g64_dispatch(q, q_scale, LYRAQ_F32, x, x_dtype, smooth, m, k, (cudaStream_t)stream);
-    if (st != LYRAQ_OK || lora_act == nullptr || m == 0) {
-        return st;
+    if (lora_act == nullptr || m == 0) {
+        return int4_g64_dispatch(q, q_scale, LYRAQ_F32, x, x_dtype, smooth, m, k, (cudaStream_t)stream);
     }
-    // the low-rank down projection reads the unsmoothed x once more (from L2 at these sizes) with its own kernel
-    return launch_lora_down(lora_act, x, lora_down, x_dtype, m, k, (cudaStream_t)stream);
+    if (q == nullptr || q_scale == nullptr || x == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    // quantize and low-rank down projection in one launch over one read of x: the quantizer warps work on the tiles the
+    // down projection's TMA ring has staged (lora_down.cu)
+    return launch_quant_int4_lora_down(q, q_scale, lora_act, x, lora_down, smooth, x_dtype, m, k, (cudaStream_t)stream);
 }
 
 int lyraq_weight_quant_int4_g64(uint8_t* qw, void* w_scale, int scale_dtype, const void* w, int w_dtype, size_t n,

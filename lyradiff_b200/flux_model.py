@@ -27,11 +27,19 @@ from .flux_blocks import (_DTYPES, FP8_W8A8, FP8_W8A8_FULL, INT4_W4A4, INT4_W4A4
 
 
 def time_exponents(channels, device, max_period=10000.0):
-    """The frequency table of TimeProjection<T> (src/lyradiff/layers/time_proj/TimeProjection.cc:39-51): exp(-ln(max_period) * i /
-    half) for i < half, computed in fp32 on the host once and kept on the device, as the reference does."""
+    """The frequency table of TimeProjection<T> (src/lyradiff/layers/time_proj/TimeProjection.cc:39-51): expf(factor * i) with
+    factor = -logf(max_period) / half, single precision on the host, kept on the device.  The C library's logf / expf are
+    called directly (as the reference and the C++ class do): a vectorised exp may differ from them in the last bit, which at
+    guidance values in the thousands moves a rounding of the projection and, through temb, every block's modulation."""
+    import ctypes
+    import ctypes.util
+    libm = ctypes.CDLL(ctypes.util.find_library("m") or "libm.so.6")
+    for f in (libm.expf, libm.logf):
+        f.restype, f.argtypes = ctypes.c_float, [ctypes.c_float]
     half = channels // 2
-    factor = torch.tensor(-math.log(max_period), dtype=torch.float32) / half
-    return torch.exp(factor * torch.arange(half, dtype=torch.float32)).to(device)
+    factor = ctypes.c_float(-libm.logf(ctypes.c_float(max_period)) / half).value
+    table = [libm.expf(ctypes.c_float(ctypes.c_float(factor * i).value)) for i in range(half)]
+    return torch.tensor(table, dtype=torch.float32).to(device)
 
 
 def time_projection(value, exponents, dtype):

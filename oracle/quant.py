@@ -53,7 +53,7 @@ def dynamic_per_token_scale(x, pre_quant_scale):
     v = _f32(x)
     if pre_quant_scale is not None:
         v = v * _f32(pre_quant_scale)[None, :]
-    amax = v.abs().amax(dim=1)
+    amax = torch.nan_to_num(v.abs(), nan=0.0).amax(dim=1)   # a maximum taken with fmaxf drops NaN operands
     s = amax / torch.tensor(127.0, dtype=F32)
     return torch.where(amax == 0, torch.ones_like(s), s)
 
@@ -165,7 +165,7 @@ def int4_quant_g64(x, smooth, group=64):
         v = v / _f32(smooth)[None, :]
     m, k = v.shape
     vg = v.reshape(m, k // group, group)
-    s = vg.abs().amax(dim=2) / torch.tensor(7.0, dtype=F32)
+    s = torch.nan_to_num(vg.abs(), nan=0.0).amax(dim=2) / torch.tensor(7.0, dtype=F32)   # fmaxf drops NaN operands
     q = _rne_sat(vg / s[:, :, None], -8, 7).reshape(m, k).to(torch.int8)
     return pack_int4(q), s.contiguous(), q
 

@@ -353,3 +353,32 @@ def test_adaln_full_size_properties(ops):
     ref = norms.adaln_quant(a["x"][:, rows], a["scale"], a["shift"], fp8_scale=f8)
     _close(q8.cpu()[rows], ref["q8"], frac=2e-3)
     check_status()
+
+
+def test_nan_elements_and_subnormal_scales_take_the_exact_path(ops):
+    """Inputs on which the division-free int8 / int4 rounding cannot be trusted: a NaN element (the reference's
+    cvt.rni.sat gives 0 for it; a maximum taken with fmaxf ignores it) and a row / group whose scale is subnormal, so that
+    1 / s is infinite.  Neither faults; both must give the oracle's bytes, i.e. the IEEE divide path."""
+    g = torch.Generator().manual_seed(17)
+    x = torch.randn(6, 256, generator=g).bfloat16()
+    x[1, 5] = float("nan")
+    x[2] = (torch.randn(256, generator=g) * 2.0 ** -131).bfloat16()        # amax / 127 and amax / 7 are subnormal
+    x[3, 64:128] = (torch.randn(64, generator=g) * 2.0 ** -130).bfloat16()  # one subnormal-scale group in a normal row
+    x[4, 200] = float("nan")
+    x[4, 130:140] = 0.0
+    # int8, dynamic per-token scales
+    q = torch.empty(6, 256, dtype=torch.int8, device="cuda")
+    sc = torch.empty(6, dtype=torch.float32, device="cuda")
+    ops.invoke_sq_input_quant(q, cu(x), None, sc, dynamic=True)
+    q_ref, s_ref = quant.sq_input_quant_dynamic(x, None)
+    assert_bit_equal(sc, s_ref, "dynamic scales")
+    assert_bit_equal(q, q_ref, "int8 with NaN / subnormal rows")
+    assert int(q.cpu()[1, 5]) == 0 and int(q.cpu()[4, 200]) == 0
+    # int4, groups of 64
+    p4 = torch.empty(6, 128, dtype=torch.uint8, device="cuda")
+    s4 = torch.empty(6, 4, dtype=torch.float32, device="cuda")
+    ops.invoke_fused_quantize_and_lora_down_simple(None, p4, s4, cu(x), None, None)
+    p_ref, s4_ref, _ = quant.int4_quant_g64(x, None)
+    assert_bit_equal(s4, s4_ref, "int4 group scales")
+    assert_bit_equal(p4, p_ref, "int4 with NaN / subnormal groups")
+    check_status()

@@ -217,3 +217,34 @@ def test_double_block_reload_from_bin_and_lora(ns, tmp_path):
     b.clear_lora()
     for u, v in zip(want, b.forward(hidden, encoder, rope, temb)):
         assert torch.equal(u, v)
+
+
+def test_densely_launched_forwards_repeat_bit_for_bit(ns):
+    """The C++ class issues a block's launches back to back, so consecutive kernels overlap through dependent launch and
+    run beside one another on the SMs, which the Python mirror's launch gaps never produce.  Sixty forwards in a row,
+    with unrelated work in between to vary the timing, must give one and the same result (this is the test that caught
+    an attention epilogue reading its accumulator one product early)."""
+    from lyradiff_b200 import flux_blocks
+    D, heads, head_dim, B, S, E, level = 256, 2, 128, 2, 256, 256, 2
+    g = torch.Generator().manual_seed(91)
+    prefix = "transformer_blocks.0."
+    sd = _double_state_dict(prefix, D, head_dim, level, g)
+    hidden = cu(torch.randn(B, S, D, generator=g).bfloat16())
+    encoder = cu(torch.randn(B, E, D, generator=g).bfloat16())
+    temb = cu(torch.nn.functional.silu(torch.randn(B, D, generator=g)).bfloat16())
+    rope = cu(_rope(B, E + S, head_dim, g, torch.bfloat16))
+    mirror = flux_blocks.FluxTransformerBlockOp("bf16", D, heads, head_dim, 4, level)
+    mirror.reload_model_from_state_dict(prefix, sd, "cuda")
+    want_i, want_t = (t.clone() for t in mirror.forward(hidden, encoder, rope, temb))
+    op = ns.FluxTransformerBlockOp("bf16", D, heads, head_dim, 4, level)
+    op.initialize(ns.LyraDiffCommonContext())
+    op.reload_model_from_state_dict(prefix, sd, "cuda")
+    junk = torch.randn(2048, 2048, device="cuda")
+    bad = 0
+    for it in range(60):
+        if it % 3 == 0:
+            junk = torch.tanh(junk @ junk * 1e-3)
+        got_i, got_t = op.forward(hidden, encoder, rope, temb)
+        bad += int(not (torch.equal(got_i, want_i) and torch.equal(got_t, want_t)))
+    check_status()
+    assert bad == 0, "%d of 60 forwards differ" % bad
