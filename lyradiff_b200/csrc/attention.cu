@@ -538,7 +538,12 @@ int launch_attention(void* out, int out_dtype, size_t out_ld, const float* out_s
     }
     const unsigned grid = (unsigned)(batch * (size_t)heads * (size_t)p.q_blocks);
     if (dtype == LYRAQ_BF16) {
-        static bool attr_set = false;
+        static bool attr_set_dev[64] = {};
+        int         dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+            return LYRAQ_ERR_CUDA;
+        }
+        bool& attr_set = attr_set_dev[dev];
         if (!attr_set) {
             const cudaError_t e = cudaFuncSetAttribute(attn::attention_fwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::kSmemTotal);
             if (e != cudaSuccess) {
@@ -550,7 +555,12 @@ int launch_attention(void* out, int out_dtype, size_t out_ld, const float* out_s
                                          stream, 1u, tm, p),
                            "cudaLaunchKernelEx(attention_fwd_kernel<bf16>)");
     }
-    static bool attr_set_h = false;
+    static bool attr_set_h_dev[64] = {};
+    int         dev_h = 0;
+    if (cudaGetDevice(&dev_h) != cudaSuccess || dev_h < 0 || dev_h >= 64) {
+        return LYRAQ_ERR_CUDA;
+    }
+    bool& attr_set_h = attr_set_h_dev[dev_h];
     if (!attr_set_h) {
         const cudaError_t e = cudaFuncSetAttribute(attn::attention_fwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::kSmemTotal);
         if (e != cudaSuccess) {

@@ -44,21 +44,6 @@ constexpr int kBarBytes    = 256;
 
 enum GemmKind { KIND_I8 = 0, KIND_F8 = 1 };
 
-// Optional instrumentation (compile with -DLYRAQ_PROFILE_WAITS): per CTA, the cycles each role spends waiting on
-// its barriers and in total.  Slots: 0 producer wait-empty, 1 producer total, 2 MMA wait-full, 3 MMA wait-tmem,
-// 4 MMA total, 5 epilogue (warp 4) wait-full-accumulator, 6 epilogue total, 7 MMA total in nanoseconds.
-#ifdef LYRAQ_PROFILE_WAITS
-__device__ unsigned long long g_wait_prof[296 * 8];
-#define PROF_DECL(name) long long name = 0
-#define PROF_T0(t) const long long t = clock64()
-#define PROF_ADD(acc, t) acc += clock64() - (t)
-#define PROF_STORE(slot, v) g_wait_prof[blockIdx.x * 8 + (slot)] = (unsigned long long)(v)
-#else
-#define PROF_DECL(name)
-#define PROF_T0(t)
-#define PROF_ADD(acc, t)
-#define PROF_STORE(slot, v)
-#endif
 
 struct EpilogueParams {
     void*        C;
@@ -89,11 +74,6 @@ struct GemmParams {
     int            m_tiles, n_tiles;
     unsigned int*  status;
     EpilogueParams epi;
-#ifdef LYRAQ_PROFILE_WAITS
-    int            skip;  // instrumentation only: bit 0 = the producer signals without loading, bit 3 / 4 / 5 = the 16-bit
-                          // epilogue without TMA stores / arithmetic / shared-memory writes, bit 1 = the epilogue frees
-                          // the accumulator without reading it
-#endif
 };
 
 // BLOCK_N is the width of the output tile; CTAS = 1: one CTA computes 128 x BLOCK_N; CTAS = 2: a pair of CTAs
@@ -369,13 +349,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint32_t phase = 0;
         int      issued = 0;
         bool     ok = true;
-        PROF_DECL(w_empty);
-        PROF_T0(t_all);
-#ifdef LYRAQ_PROFILE_WAITS
-        if ((p.skip & 4) && !leader) {
-            ok = false;  // with bit 2 the peer gets no per-stage signal, so its producer must not wait for one
-        }
-#endif
         // Every other tile of a CTA walks K from the far end: the K slices a wave touched last are the ones the next wave
         // asks for first, so for a deep K they are still in L2 instead of being fetched from HBM once per wave.
         const int kb_far = ((num_kb - 1) / S::kSub) * S::kSub;
@@ -387,21 +360,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             const int b_row = n_blk * BLOCK_N + (int)rank * (BLOCK_N / CTAS);
             for (int step = 0; step < num_kb; step += S::kSub) {
                 const int kb = flip ? kb_far - step : step;
-                PROF_T0(t_w);
                 if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
                     report_timeout(p.status, 0x100u | (unsigned)stage);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
-                PROF_ADD(w_empty, t_w);
-#ifdef LYRAQ_PROFILE_WAITS
-                if (p.skip & 1) {
-                    if (leader) {
-                        mbar_arrive(full_bar(stage));
-                    }
-                } else
-#endif
                 if (CTAS == 2) {
                     // both CTAs' bytes are counted on the leader's barrier, which the leader arms for the pair
                     const uint32_t lbar = map_to_cta(full_bar(stage), 0u);
@@ -429,10 +393,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
         }
-#ifdef LYRAQ_PROFILE_WAITS
-        PROF_STORE(0, w_empty);
-        PROF_STORE(1, clock64() - t_all);
-#endif
         if (CTAS == 1 || leader) {
             // Drain: every load counted on this CTA's barriers must have landed before the block may exit.
             // (stage, phase) now name the next slot to fill; walk back over the last min(issued, kStages) slots.
@@ -461,33 +421,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         bool     ok = true;
         // cluster addresses of the peer's barriers (same offsets): its producer and epilogue wait on those
         const uint32_t peer = (CTAS == 2) ? 1u : 0u;
-        PROF_DECL(w_full);
-        PROF_DECL(w_tmem);
-        PROF_T0(t_all);
-#ifdef LYRAQ_PROFILE_WAITS
-        const uint64_t ns0 = global_timer_ns();
-#endif
         for (int tile = unit; ok && tile < num_tiles; tile += n_units, ++local) {
             const int      buf       = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
-            PROF_T0(t_w0);
             if (!mbar_wait(tmem_empty_bar(buf), acc_phase ^ 1u, abort_flag)) {
                 report_timeout(p.status, 0x200u | (unsigned)buf);
                 *abort_flag = 1;
                 break;
             }
-            PROF_ADD(w_tmem, t_w0);
             tc_fence_after_sync();
             const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BLOCK_N);
             for (int kb = 0; kb < num_kb; kb += S::kSub) {
-                PROF_T0(t_w1);
                 if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                     report_timeout(p.status, 0x300u | (unsigned)stage);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
-                PROF_ADD(w_full, t_w1);
                 tc_fence_after_sync();
 #pragma unroll
                 for (int sk = 0; sk < S::kSub * (kBlockK / kUmmaK); ++sk) {
@@ -515,9 +465,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 // the stage is free, in both CTAs, once these MMAs have read it
                 if (CTAS == 2) {
                     tc_commit_pair(empty_bar(stage));
-#ifdef LYRAQ_PROFILE_WAITS
-                    if (!(p.skip & 4))
-#endif
                     tc_commit_pair(map_to_cta(empty_bar(stage), peer));
                 } else {
                     tc_commit(empty_bar(stage));
@@ -537,12 +484,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 }
             }
         }
-#ifdef LYRAQ_PROFILE_WAITS
-        PROF_STORE(2, w_full);
-        PROF_STORE(3, w_tmem);
-        PROF_STORE(4, clock64() - t_all);
-        PROF_STORE(7, global_timer_ns() - ns0);  // wall time of the same span: cycles / ns = the SM clock under load
-#endif
     } else if (warp >= kEpiWarp0) {
         // ------------------------------------------------------------------ epilogue (warps 4..11)
         const int      quad      = warp & 3;                 // the TMEM lane quadrant this warp may read
@@ -561,8 +502,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         const bool vec_ok = (e.c_dtype == LYRAQ_F32 || e.c_dtype == LYRAQ_S32) ? ((e.ldc & 3) == 0) : ((e.ldc & 7) == 0);
         int local = 0;
-        PROF_DECL(w_acc);
-        PROF_T0(t_all);
         for (int tile = unit; tile < num_tiles; tile += n_units, ++local) {
             const int      buf       = local & 1;
             const uint32_t acc_phase = (uint32_t)(local >> 1) & 1u;
@@ -644,7 +583,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 load_res16(0, resb[0]);
             }
             // the verdict is made warp-uniform: the tensor-memory loads below need the whole warp
-            PROF_T0(t_w2);
             if (!__all_sync(0xffffffffu, mbar_wait(tmem_full_bar(buf), acc_phase, abort_flag))) {
                 if (lane == 0) {
                     report_timeout(p.status, 0x400u | (unsigned)buf);
@@ -652,7 +590,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 *abort_flag = 1;
                 break;
             }
-            PROF_ADD(w_acc, t_w2);
             tc_fence_after_sync();
             const int row0 = m_blk * kTileM + (int)rank * kBlockM + quad * 32;  // first row of this warp
             const int row  = row0 + lane;
@@ -666,11 +603,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tmem_ld_32x32(t_addr, acc[0]);
 #pragma unroll
             for (int c = 0; c < kChunks; ++c) {
-#ifdef LYRAQ_PROFILE_WAITS
-                if (p.skip & 2) {
-                    continue;
-                }
-#endif
                 tmem_ld_wait();
                 if (c + 1 < kChunks) {
                     tmem_ld_32x32(t_addr + (uint32_t)((c + 1) * 32), acc[(c + 1) & 1]);
@@ -721,14 +653,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     load_res16(c + 1, resb[RES ? ((c + 1) & 1) : 0]);
                 }
                 const uint32_t* bias2 = reinterpret_cast<const uint32_t*>(b16 + c * 32);
-#ifdef LYRAQ_PROFILE_WAITS
-                if (p.skip & 16) {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        o[i] = a[2 * i] ^ a[2 * i + 1];
-                    }
-                } else
-#endif
                 if (e.c_dtype == LYRAQ_BF16) {
                     epilogue_math16<KIND, __nv_bfloat16, RES>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
                 } else {
@@ -803,9 +727,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     __syncwarp();
                     uint8_t*  brow = box + lane * 64;
                     const int sw   = (lane >> 1) & 3;
-#ifdef LYRAQ_PROFILE_WAITS
-                    if (!(p.skip & 32))
-#endif
                     {
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
@@ -816,9 +737,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                         fence_proxy_async_smem();
                     }
                     __syncwarp();
-#ifdef LYRAQ_PROFILE_WAITS
-                    if (!(p.skip & 8))
-#endif
                     if (lane == 0 && row0 < p.M && valid > 0) {
                         tma_store_2d(&tmap_c, box_addr, col0, row0);
                         tma_store_commit();
@@ -859,12 +777,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (lane == 0) {
             tma_store_wait_read();  // shared memory must outlive the last store's read of it
         }
-#ifdef LYRAQ_PROFILE_WAITS
-        if (threadIdx.x == kEpiWarp0 * 32) {
-            PROF_STORE(5, w_acc);
-            PROF_STORE(6, clock64() - t_all);
-        }
-#endif
     }
 
     // ---------------------------------------------------------------------- common exit
@@ -905,11 +817,62 @@ static EncodeTiledFn encode_tiled_fn()
     return fn;
 }
 
+// Encoding a tensor map is a pure function of its arguments and costs a driver call of a microsecond or two; a forward
+// re-uses the same few (pointer, shape) combinations launch after launch (weights always, activations whenever the
+// caller's allocator hands the same block out again), so each host thread keeps the last maps it built.
+struct TmapKey {
+    const void* base;
+    uint64_t    d0, d1, stride;
+    uint32_t    b0, b1;
+    int         kind;  // data type and swizzle of the encode call
+    bool operator==(const TmapKey& o) const
+    {
+        return base == o.base && d0 == o.d0 && d1 == o.d1 && stride == o.stride && b0 == o.b0 && b1 == o.b1 && kind == o.kind;
+    }
+};
+struct TmapCache {
+    static constexpr int kEntries = 64;
+    TmapKey     key[kEntries];
+    CUtensorMap map[kEntries];
+    bool        used[kEntries] = {};
+    static unsigned slot(const TmapKey& k)
+    {
+        uint64_t h = reinterpret_cast<uintptr_t>(k.base) * 0x9E3779B97F4A7C15ull;
+        h ^= (k.d0 * 31 + k.d1) * 0xC2B2AE3D27D4EB4Full + k.stride + ((uint64_t)k.b0 << 40) + ((uint64_t)k.b1 << 20) + (uint64_t)k.kind;
+        return (unsigned)((h >> 32) % kEntries);
+    }
+    bool find(const TmapKey& k, CUtensorMap* out) const
+    {
+        const unsigned s = slot(k);
+        if (used[s] && key[s] == k) {
+            *out = map[s];
+            return true;
+        }
+        return false;
+    }
+    void put(const TmapKey& k, const CUtensorMap& m)
+    {
+        const unsigned s = slot(k);
+        key[s]  = k;
+        map[s]  = m;
+        used[s] = true;
+    }
+};
+static TmapCache& tmap_cache()
+{
+    static thread_local TmapCache cache;
+    return cache;
+}
+
 // Tensor map of a row-major [rows, k_bytes] byte matrix, tiles of box_rows x 128 bytes, 128-byte swizzle,
 // out-of-range elements read as zero.
 int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k_bytes, uint64_t row_stride_bytes,
                        uint32_t box_rows, uint32_t box_bytes, bool swizzle128)
 {
+    const TmapKey key{base, k_bytes, rows, row_stride_bytes, box_bytes, box_rows, swizzle128 ? 1 : 0};
+    if (tmap_cache().find(key, map)) {
+        return LYRAQ_OK;
+    }
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) {
         return LYRAQ_ERR_CUDA;
@@ -925,6 +888,7 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
         record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled refused the tensor map");
         return LYRAQ_ERR_CUDA;
     }
+    tmap_cache().put(key, *map);
     return LYRAQ_OK;
 }
 
@@ -932,6 +896,10 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
 // shared-memory image uses the swizzle that matches the box's row size (32 or 64 bytes).
 int make_tmap_store(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int elem_bytes)
 {
+    const TmapKey key{base, cols, rows, ld * (uint64_t)elem_bytes, 32, 32, 16 + elem_bytes};
+    if (tmap_cache().find(key, map)) {
+        return LYRAQ_OK;
+    }
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) {
         return LYRAQ_ERR_CUDA;
@@ -948,6 +916,7 @@ int make_tmap_store(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
         record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled refused the output tensor map");
         return LYRAQ_ERR_CUDA;
     }
+    tmap_cache().put(key, *map);
     return LYRAQ_OK;
 }
 
@@ -1036,9 +1005,18 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
     const long units = sms / CTAS;
     const int  grid  = (int)(tiles < units ? tiles : units) * CTAS;
     auto       kern  = gemm_tcgen05_kernel<KIND, BLOCK_N, CTAS, RES>;
-    const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
-    if (attr_err != cudaSuccess) {
-        return cuda_status(attr_err, "cudaFuncSetAttribute(gemm_tcgen05_kernel, dynamic shared memory)");
+    // the dynamic shared-memory limit of this instance is raised once per device, not per launch
+    static bool attr_set[64] = {};
+    int         dev         = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        return LYRAQ_ERR_CUDA;
+    }
+    if (!attr_set[dev]) {
+        const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+        if (attr_err != cudaSuccess) {
+            return cuda_status(attr_err, "cudaFuncSetAttribute(gemm_tcgen05_kernel, dynamic shared memory)");
+        }
+        attr_set[dev] = true;
     }
     return cuda_status(launch_kernel(kern, (unsigned)grid, (unsigned)kThreads, (size_t)S::kTotal, stream, (unsigned)CTAS, ta, tb, tc, p),
                        "cudaLaunchKernelEx(gemm_tcgen05_kernel)");
@@ -1046,9 +1024,6 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
 
 // forced tile configuration for tests and sweeps: 0 = automatic, else block_n * 10 + ctas (2561, 1281, 2562)
 static int g_forced_tile = 0;
-#ifdef LYRAQ_PROFILE_WAITS
-static int g_prof_skip = 0;
-#endif
 
 template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams p, cudaStream_t stream)
 {
@@ -1080,9 +1055,6 @@ template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams 
         p.epi.ldc = p.N;
     }
     TileChoice t = pick_tile(p.M, p.N, p.K, sms);
-#ifdef LYRAQ_PROFILE_WAITS
-    p.skip = g_prof_skip;
-#endif
     if (g_forced_tile != 0) {
         t = TileChoice{g_forced_tile / 10, g_forced_tile % 10};
     }
@@ -1102,17 +1074,6 @@ using namespace lyraq;
 
 extern "C" {
 
-#ifdef LYRAQ_PROFILE_WAITS
-__attribute__((visibility("default"))) int lyraq_debug_set_skip(int mask)
-{
-    lyraq::g_prof_skip = mask;
-    return LYRAQ_OK;
-}
-__attribute__((visibility("default"))) int lyraq_debug_read_wait_profile(unsigned long long* host, int n_words)
-{
-    return cuda_status(cudaMemcpyFromSymbol(host, g_wait_prof, sizeof(unsigned long long) * (size_t)n_words), "read wait profile");
-}
-#endif
 
 int lyraq_debug_force_gemm_tile(int code)
 {

@@ -44,24 +44,6 @@ int device_sm_count();
 
 namespace w4 {
 
-// Optional instrumentation (-DLYRAQ_PROFILE_WAITS -DLYRAQ_W4_TIMERS): cycles per CTA that a role spends in its waits and
-// in total.  Slots: 3 expand wait-packed, 4 expand wait-stage-free, 5 expand total, 11 expand copy loop, 6 drain
-// wait-partial, 7 drain wait-scales, 8 drain total.  (The clock reads themselves slow the kernel noticeably.)
-#ifdef LYRAQ_PROFILE_WAITS
-static int g_w4_skip = 0;
-__device__ unsigned long long g_w4_prof[148 * 16];
-#endif
-#if defined(LYRAQ_PROFILE_WAITS) && defined(LYRAQ_W4_TIMERS)
-#define W4_DECL(name) long long name = 0
-#define W4_T0(t) const long long t = clock64()
-#define W4_ADD(acc, t) acc += clock64() - (t)
-#define W4_STORE(slot, v) g_w4_prof[blockIdx.x * 16 + (slot)] = (unsigned long long)(v)
-#else
-#define W4_DECL(name)
-#define W4_T0(t)
-#define W4_ADD(acc, t)
-#define W4_STORE(slot, v)
-#endif
 
 constexpr int kBM          = 128;
 constexpr int kBN          = 128;
@@ -100,10 +82,6 @@ struct Params {
     int           lora_act_is_f32;
     const void*   lora_up;       // [N, 32] of D's 16-bit type or null
     unsigned int* status;
-#ifdef LYRAQ_PROFILE_WAITS
-    int           skip;          // instrumentation: bit 0 = no nibble expansion, bit 1 = no drain work, bit 2 = no MMAs,
-                                 // bit 3 = no TMA loads, bit 4 = no scale loads
-#endif
 };
 
 constexpr int kLoraRank = 32;
@@ -274,11 +252,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         break;
                     }
                     const uint32_t dst = packed0 + stage * kPackedStage;
-#ifdef LYRAQ_PROFILE_WAITS
-                    if (p.skip & 8) {
-                        mbar_arrive(full_p(stage));
-                    } else
-#endif
                     {
                         mbar_arrive_expect_tx(full_p(stage), (uint32_t)kPackedStage);
                         tma_load_2d(dst, &tmap_a, full_p(stage), kb * kPackedRowB, m_blk * kBM);
@@ -352,9 +325,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                 mma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (uint32_t)k);
                             }
                         } else
-#ifdef LYRAQ_PROFILE_WAITS
-                        if (!(p.skip & 4))
-#endif
                         {
 #pragma unroll
                             for (int k = 0; k < 2; ++k) {
@@ -395,18 +365,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const int  g0   = sl * kSlotGroups;
                 const bool full = p.scale_vec_ok && (g0 + kSlotGroups <= p.G);
                 float      va[4][8], vb[4][8];
-#ifdef LYRAQ_PROFILE_WAITS
-                if (p.skip & 16) {
-#pragma unroll
-                    for (int rr = 0; rr < 4; ++rr) {
-#pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            va[rr][g] = 1.0f;
-                            vb[rr][g] = 1.0f;
-                        }
-                    }
-                } else
-#endif
 #pragma unroll
                 for (int rr = 0; rr < 4; ++rr) {
                     const int    r    = lane + 32 * rr;
@@ -487,18 +445,10 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int       pstage = 0, ustage = 0;
         uint32_t  pphase = 0, uphase = 0;
         bool      ok = true;
-        W4_DECL(w_p);
-        W4_DECL(w_u);
-        W4_DECL(w_x);
-        W4_T0(t_all);
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
             for (int kb = 0; kb < num_kb; ++kb) {
-                W4_T0(t_w);
                 bool w = mbar_wait(full_p(pstage), pphase, abort_flag);
-                W4_ADD(w_p, t_w);
-                W4_T0(t_w2);
                 w      = w && mbar_wait(empty_u(ustage), uphase ^ 1u, abort_flag);
-                W4_ADD(w_u, t_w2);
                 if (!__all_sync(0xffffffffu, w)) {
                     if (lane == 0) {
                         report_timeout(p.status, 0x1400u | (unsigned)(pstage * 16 + ustage));
@@ -507,12 +457,8 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     ok = false;
                     break;
                 }
-                W4_T0(t_x);
                 const uint8_t* src = gen_base + (packed0 - smem_base) + pstage * kPackedStage + src_o;
                 uint8_t*       dst = gen_base + (ustage0 - smem_base) + ustage * kUStage;
-#ifdef LYRAQ_PROFILE_WAITS
-                if (!(p.skip & 1))
-#endif
 #pragma unroll
                 for (int it = 0; it < 8; ++it) {
                     // 32 rows further per step: 32 * 64 B in the packed tile, 4 * 1024 B in the operand tile;
@@ -526,7 +472,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     *reinterpret_cast<uint4*>(dst + it * 4096 + dst_ev) = ev;
                     *reinterpret_cast<uint4*>(dst + it * 4096 + dst_od) = od;
                 }
-                W4_ADD(w_x, t_x);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
@@ -594,14 +539,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
-#if defined(LYRAQ_PROFILE_WAITS) && defined(LYRAQ_W4_TIMERS)
-        if (tu == 0) {
-            W4_STORE(3, w_p);
-            W4_STORE(4, w_u);
-            W4_STORE(5, clock64() - t_all);
-            W4_STORE(11, w_x);
-        }
-#endif
     } else if (warp >= 4 && warp <= 11) {
         // ------------------------------------------------------------------ drain + epilogue (warps 4..11)
         const int      quad      = warp & 3;
@@ -613,9 +550,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t       sphase = 0;
         uint32_t       n0 = 0, n1 = 0;  // groups drained per MMA issuer (issuer i: group i of a K block, buffers i, i + 2)
         bool           ok = true;
-        W4_DECL(w_pf);
-        W4_DECL(w_sc);
-        W4_T0(t_all);
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
             const int m_blk = tile % p.m_tiles;
             const int n_blk = tile / p.m_tiles;
@@ -626,9 +560,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             for (int kb = 0; ok && kb < num_kb; ++kb) {
                 if ((kb & 3) == 0) {
-                    W4_T0(t_w);
                     const bool got_s = mbar_wait(sc_full(slot), sphase, abort_flag);
-                    W4_ADD(w_sc, t_w);
                     if (!__all_sync(0xffffffffu, got_s)) {
                         if (lane == 0) {
                             report_timeout(p.status, 0x1600u | (unsigned)slot);
@@ -646,11 +578,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const uint32_t nsel = g ? n1 : n0;
                     const int      pb   = g + 2 * (int)(nsel & 1u);
                     const int      gs   = (kb & 3) * 2 + g;  // group index inside the scale slot
-                    W4_T0(t_w2);
                     const bool got_p = mbar_wait(part_full(pb), (nsel >> 1) & 1u, abort_flag);
                     n0 += (g == 0) ? 1u : 0u;
                     n1 += (g == 1) ? 1u : 0u;
-                    W4_ADD(w_pf, t_w2);
                     if (!__all_sync(0xffffffffu, got_p)) {
                         if (lane == 0) {
                             report_timeout(p.status, 0x1700u | (unsigned)pb);
@@ -663,9 +593,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const float  sa_s = sas[gs * kBM + trow];
                     const float2 sa_v = make_float2(sa_s, sa_s);
                     const uint32_t t_addr = tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64);
-#ifdef LYRAQ_PROFILE_WAITS
-                    if (!(p.skip & 2))
-#endif
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t pc[16];
@@ -749,13 +676,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
-#if defined(LYRAQ_PROFILE_WAITS) && defined(LYRAQ_W4_TIMERS)
-        if (threadIdx.x == 128) {
-            W4_STORE(6, w_pf);
-            W4_STORE(7, w_sc);
-            W4_STORE(8, clock64() - t_all);
-        }
-#endif
     }
 
     tc_fence_before_sync();
@@ -771,17 +691,6 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
 using namespace lyraq;
 
-#ifdef LYRAQ_PROFILE_WAITS
-extern "C" __attribute__((visibility("default"))) int lyraq_debug_set_w4_skip(int mask)
-{
-    w4::g_w4_skip = mask;
-    return LYRAQ_OK;
-}
-extern "C" __attribute__((visibility("default"))) int lyraq_debug_read_w4_profile(unsigned long long* host, int n_words)
-{
-    return cuda_status(cudaMemcpyFromSymbol(host, w4::g_w4_prof, sizeof(unsigned long long) * (size_t)n_words), "read w4 profile");
-}
-#endif
 
 extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* sa, const void* sb, int sb_dtype, void* D,
                                int c_dtype, const void* lora_act, int lora_act_dtype, const void* lora_up, const void* bias,
@@ -840,9 +749,6 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     p.lora_act  = lora_act;
     p.lora_act_is_f32 = (lora_act_dtype == LYRAQ_F32) ? 1 : 0;
     p.lora_up   = lora_up;
-#ifdef LYRAQ_PROFILE_WAITS
-    p.skip      = w4::g_w4_skip;
-#endif
     p.status    = status_word_ptr();
     if (p.status == nullptr) {
         return LYRAQ_ERR_CUDA;
