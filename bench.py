@@ -485,7 +485,7 @@ class FluxBlock:
         self.x, self.temb, self.rope = x.to(dev), temb.to(dev), rope.to(dev)
         self.y = torch.empty_like(self.x)
         self.h_in = x.pin_memory()
-        self.e2e_x = [self.x, torch.empty_like(self.x)]
+        self.e2e_x = [torch.empty_like(self.x), torch.empty_like(self.x)]   # the two device slots a step's input arrives in
         self.e2e_y = [self.y, torch.empty_like(self.y)]
 
     use_graph = True  # bench.py --no-graph turns the CUDA-graph replay off
@@ -509,10 +509,17 @@ class FluxBlock:
     def step(self, events=None, io=None):
         if events is not None:
             events[0][0].record()
-        if io is None and self.use_graph:
+        if self.use_graph:
+            # The captured step reads self.x and leaves its result in self.graph_out.  End to end (io given) the step's
+            # input slot is copied into self.x and the result out of self.graph_out on the step's own stream, so the graph
+            # (hundreds of launches issued without host work in between) serves both timed regions.
             if getattr(self, "graph", None) is None:
                 self._capture()
+            if io is not None:
+                self.x.copy_(io[0], non_blocking=True)
             self.graph.replay()
+            if io is not None:
+                io[1].copy_(self.graph_out, non_blocking=True)
         else:
             out = self._forward(self.x if io is None else io[0])
             if io is not None:
@@ -681,7 +688,7 @@ class FluxForward(FluxBlock):
         self.x, self.rope = img.to(dev), rope.to(dev)
         self.y = torch.empty(1, S, self.IN_CH, dtype=torch.bfloat16, device=dev)
         self.h_in = img.pin_memory()
-        self.e2e_x = [self.x, torch.empty_like(self.x)]
+        self.e2e_x = [torch.empty_like(self.x), torch.empty_like(self.x)]   # the two device slots a step's input arrives in
         self.e2e_y = [self.y, torch.empty_like(self.y)]
 
     def _forward(self, img):

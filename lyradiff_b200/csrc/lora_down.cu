@@ -12,11 +12,12 @@
 //   warp 0   lane 0: TMA producer (x tile 32 x 128 B, lora_down tile 128 x 128 B, ring of 8 stages);
 //            afterwards the whole warp reads accumulator lanes 0..31 and stores act
 //   warp 1   lane 0: MMA issuer; the warp owns the tensor-memory allocation
-//   warps 2-5 (fused form only): the int4 quantize of the same x tiles.  One stage holds, for each of the CTA's 32 rows,
+//   warps 2-17 (fused form only): the int4 quantize of the same x tiles.  One stage holds, for each of the CTA's 32 rows,
 //            exactly one group of 64 values (a 128-byte row of the swizzled tile), so x is read from memory once for
-//            both results, as in the reference's fused kernel.  Warp w takes the stages with kb % 4 == w - 2: 8 lanes
-//            share a group (the arithmetic of int4_g64_kernel, bit for bit), 4 rows per pass, 8 passes; a stage goes
-//            back to the producer when both the MMAs that read it and its quantizer warp are done.
+//            both results, as in the reference's fused kernel.  Eight lanes share a group (the arithmetic of
+//            int4_g64_kernel, bit for bit), so a warp takes 4 rows and eight warps one stage; the two sets of eight warps
+//            alternate over the stages, which keeps enough independent divides in flight to hide their latency.  A stage
+//            goes back to the producer when the MMAs that read it and its eight quantizer warps are done.
 // All waits are bounded; a timeout sets the status word and the block leaves.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -40,7 +41,7 @@ constexpr int kStage     = kDownTile + kXTile;
 constexpr int kBarOffset = kStages * kStage;
 constexpr int kSmemTotal = kBarOffset + 256 + 1024;
 constexpr int kThreads   = 64;                    // down projection alone
-constexpr int kQuantWarps = 4;
+constexpr int kQuantWarps = 16;               // two sets of eight: a set covers the 32 rows of one stage
 constexpr int kThreadsFused = kThreads + 32 * kQuantWarps;
 
 struct Params {
@@ -75,7 +76,7 @@ lora_down_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
             mbar_init(full_bar(s), 1);
-            mbar_init(empty_bar(s), FUSED ? 2 : 1);   // the MMAs' commit, and the stage's quantizer warp
+            mbar_init(empty_bar(s), FUSED ? 9 : 1);   // the MMAs' commit, and the stage's eight quantizer warps
         }
         mbar_init(done_bar, 1);
         *abort_flag = 0;
@@ -155,7 +156,9 @@ lora_down_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
         const int part = lane & 7;                  // which 8 values of the group of 64
         const int sub  = lane >> 3;                 // which of the pass's 4 rows
         bool      ok   = true;
-        for (int kb = warp - 2; kb < num_kb && ok; kb += kQuantWarps) {
+        const int qw  = warp - 2;
+        const int r   = (qw & 7) * 4 + sub;      // this lane's row of the tile
+        for (int kb = qw >> 3; kb < num_kb && ok; kb += 2) {
             const int      stage = kb % kStages;
             const uint32_t phase = (uint32_t)((kb / kStages) & 1);
             if (!__all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, abort_flag))) {
@@ -166,38 +169,31 @@ lora_down_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_consta
                 ok = false;
                 break;
             }
-            const uint8_t* xt = gen_base + stage * kStage + kDownTile;   // 32 rows x 128 B, 128-byte swizzle
-            float4 s0 = make_float4(1.0f, 1.0f, 1.0f, 1.0f), s1 = s0;
-            if (p.smooth != nullptr) {
-                s0 = ld_f32x4(reinterpret_cast<const float4*>(p.smooth + kb * 64 + part * 8));
-                s1 = ld_f32x4(reinterpret_cast<const float4*>(p.smooth + kb * 64 + part * 8 + 4));
+            const uint8_t* xt  = gen_base + stage * kStage + kDownTile;   // 32 rows x 128 B, 128-byte swizzle
+            const Vec16    raw = *reinterpret_cast<const Vec16*>(xt + r * 128 + ((part ^ (r & 7)) << 4));
+            float          v[8];
+            if (p.is_bf16) {
+                unpack8<__nv_bfloat16>(raw, v);
+            } else {
+                unpack8<__half>(raw, v);
             }
-#pragma unroll 2
-            for (int pass = 0; pass < kRows / 4; ++pass) {
-                const int   r = pass * 4 + sub;
-                const Vec16 raw = *reinterpret_cast<const Vec16*>(xt + r * 128 + ((part ^ (r & 7)) << 4));
-                float       v[8];
-                if (p.is_bf16) {
-                    unpack8<__nv_bfloat16>(raw, v);
-                } else {
-                    unpack8<__half>(raw, v);
-                }
-                if (p.smooth != nullptr) {
-                    v[0] /= s0.x; v[1] /= s0.y; v[2] /= s0.z; v[3] /= s0.w;
-                    v[4] /= s1.x; v[5] /= s1.y; v[6] /= s1.z; v[7] /= s1.w;
-                }
-                float          sc;
-                const uint32_t w = int4_g64_quantize8(v, sc);
-                if (row0 + r < p.m) {
-                    p.q[(size_t)(row0 + r) * (size_t)(p.k >> 3) + (size_t)(kb * 8 + part)] = w;
-                    if (part == 0) {
-                        p.q_scale[(size_t)(row0 + r) * (size_t)(p.k >> 6) + (size_t)kb] = sc;
-                    }
-                }
+            if (p.smooth != nullptr) {
+                const float4 s0 = ld_f32x4(reinterpret_cast<const float4*>(p.smooth + kb * 64 + part * 8));
+                const float4 s1 = ld_f32x4(reinterpret_cast<const float4*>(p.smooth + kb * 64 + part * 8 + 4));
+                v[0] /= s0.x; v[1] /= s0.y; v[2] /= s0.z; v[3] /= s0.w;
+                v[4] /= s1.x; v[5] /= s1.y; v[6] /= s1.z; v[7] /= s1.w;
             }
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(empty_bar(stage));      // this warp's share of the stage's release
+                mbar_arrive(empty_bar(stage));      // the tile is in registers: this warp's share of the stage's release
+            }
+            float          sc;
+            const uint32_t w = int4_g64_quantize8(v, sc);
+            if (row0 + r < p.m) {
+                p.q[(size_t)(row0 + r) * (size_t)(p.k >> 3) + (size_t)(kb * 8 + part)] = w;
+                if (part == 0) {
+                    p.q_scale[(size_t)(row0 + r) * (size_t)(p.k >> 6) + (size_t)kb] = sc;
+                }
             }
         }
     } else if (warp == 1 && lane == 0) {

@@ -13,6 +13,15 @@ from tests.util import check_status, cu
 pytestmark = pytest.mark.gpu
 
 
+def _impl(name):
+    """The block classes under test: the C++ torch custom classes (the product) or their Python mirrors (same API)."""
+    if name == "cpp":
+        from lyradiff_b200 import torch_classes
+        return torch_classes.load()
+    from lyradiff_b200 import flux_blocks as fb
+    return fb
+
+
 def _state_dict(prefix, D, mlp_scale, head_dim, level, g):
     sd = {}
 
@@ -34,10 +43,11 @@ def _state_dict(prefix, D, mlp_scale, head_dim, level, g):
     return sd
 
 
+@pytest.mark.parametrize("impl", ["cpp", "mirror"])
 @pytest.mark.parametrize("level", [1, 2])
 @pytest.mark.parametrize("B,S", [(1, 160), (2, 96)])
-def test_single_block_against_oracle(level, B, S):
-    from lyradiff_b200 import flux_blocks
+def test_single_block_against_oracle(impl, level, B, S):
+    flux_blocks = _impl(impl)
     D, heads, head_dim, mlp_scale = 256, 2, 128, 4
     g = torch.Generator().manual_seed(100 * level + S)
     prefix = "single_transformer_blocks.0."
@@ -93,10 +103,11 @@ def _double_state_dict(prefix, D, head_dim, level, g):
     return sd
 
 
+@pytest.mark.parametrize("impl", ["cpp", "mirror"])
 @pytest.mark.parametrize("level", [1, 2])
 @pytest.mark.parametrize("B,S,E", [(1, 128, 48), (2, 64, 24)])
-def test_double_block_against_oracle(level, B, S, E):
-    from lyradiff_b200 import flux_blocks
+def test_double_block_against_oracle(impl, level, B, S, E):
+    flux_blocks = _impl(impl)
     D, heads, head_dim = 256, 2, 128
     g = torch.Generator().manual_seed(7 * level + S)
     prefix = "transformer_blocks.3."
@@ -114,7 +125,8 @@ def test_double_block_against_oracle(level, B, S, E):
     out_i, out_t = op.forward(cu(hidden), cu(encoder), cu(rope), cu(temb))
     check_status()
     # the loaded weights: e4m3 codes times the amax / 448 scale give the 16-bit weight back to within half an e4m3 step
-    for stream in ("img", "txt"):
+    # (the Python mirror exposes its weight objects; the C++ class is checked through its output below)
+    for stream in ("img", "txt") if impl == "mirror" else ():
         for name, key in (("qkv", "attn.to_qkv" if stream == "img" else "attn.to_added_qkv"),
                           ("out", "attn.to_out.0" if stream == "img" else "attn.to_add_out"),
                           ("ff1", ("ff" if stream == "img" else "ff_context") + ".net.0.proj"),
@@ -184,12 +196,13 @@ def _int4_state_dict(prefix, D, mlp_scale, head_dim, level, g, dt=torch.bfloat16
     return sd
 
 
+@pytest.mark.parametrize("impl", ["cpp", "mirror"])
 @pytest.mark.parametrize("level", [7, 8])
 @pytest.mark.parametrize("B,S", [(1, 160), (2, 96)])
-def test_single_block_int4_against_oracle(level, B, S):
+def test_single_block_int4_against_oracle(impl, level, B, S):
     """quant_level 7 / 8: every linear of the block is a W4A4 linear with its rank-32 LoRA branch.  Tolerances as for the FP8
     block; the int4 codes that flip where the attention output differs in the last bit are the dominant term."""
-    from lyradiff_b200 import flux_blocks
+    flux_blocks = _impl(impl)
     D, heads, head_dim, mlp_scale = 256, 2, 128, 4
     g = torch.Generator().manual_seed(1000 * level + S)
     prefix = "single_transformer_blocks.9."
@@ -211,9 +224,10 @@ def test_single_block_int4_against_oracle(level, B, S):
     want, mid = blocks.flux_single_block_int4(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_scale, level)
     # the pieces in front of the attention see identical inputs on both sides: the W4A4 linear with the bias rounded in
     # and the QK norm + RoPE agree to the LoRA-down summation order (a few fp32 ulps before the rounding to bf16)
-    qkv_gpu = op._buf["qkv"].cpu().float()
-    dq = (qkv_gpu - mid["qkv"].float()).abs()
-    assert float((dq > 0).float().mean()) < 0.05 and float(dq.max()) <= 2.0 ** -6 * float(mid["qkv"].float().abs().max())
+    if impl == "mirror":   # the mirror keeps its intermediate buffers; the C++ class is judged by its output
+        qkv_gpu = op._buf["qkv"].cpu().float()
+        dq = (qkv_gpu - mid["qkv"].float()).abs()
+        assert float((dq > 0).float().mean()) < 0.05 and float(dq.max()) <= 2.0 ** -6 * float(mid["qkv"].float().abs().max())
 
     delta, wdelta = out.cpu().float() - hidden.float(), want.float() - hidden.float()
     err = (delta - wdelta).abs()
@@ -258,10 +272,11 @@ def _int4_double_state_dict(prefix, D, head_dim, level, g, dt=torch.bfloat16):
     return sd
 
 
+@pytest.mark.parametrize("impl", ["cpp", "mirror"])
 @pytest.mark.parametrize("level", [7, 8])
 @pytest.mark.parametrize("B,S,E", [(1, 128, 48), (2, 64, 24)])
-def test_double_block_int4_against_oracle(level, B, S, E):
-    from lyradiff_b200 import flux_blocks
+def test_double_block_int4_against_oracle(impl, level, B, S, E):
+    flux_blocks = _impl(impl)
     D, heads, head_dim = 256, 2, 128
     g = torch.Generator().manual_seed(77 * level + S)
     prefix = "transformer_blocks.4."

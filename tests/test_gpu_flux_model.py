@@ -48,19 +48,27 @@ def _inputs(B, S, E, g):
     return hidden, encoder, rope, pooled
 
 
-def _op(level):
+def _op(level, impl="mirror"):
+    """The whole-model class under test: the C++ torch custom class (the product) or its Python mirror (same API)."""
+    if impl == "cpp":
+        from lyradiff_b200 import torch_classes
+        ns = torch_classes.load()
+        op = ns.FluxTransformer2DModelOp("bf16", IN_CH, NL, NS, HD, HEADS, POOLED, JOINT, True, level)
+        op.initialize(ns.LyraDiffCommonContext())
+        return op
     from lyradiff_b200 import flux_blocks, flux_model
     op = flux_model.FluxTransformer2DModelOp("bf16", IN_CH, NL, NS, HD, HEADS, POOLED, JOINT, True, level)
     op.initialize(flux_blocks.LyraDiffCommonContext())
     return op
 
 
+@pytest.mark.parametrize("impl", ["cpp", "mirror"])
 @pytest.mark.parametrize("level", [1, 2, 8])
-def test_model_against_oracle(level):
+def test_model_against_oracle(impl, level):
     g = torch.Generator().manual_seed(200 + level)
     sd = _model_state_dict(level, g)
     hidden, encoder, rope, pooled = _inputs(1, 64, 32, g)
-    op = _op(level)
+    op = _op(level, impl)
     op.reload_transformer_model_from_state_dict(sd, "cuda")
     got = op.transformer_forward(cu(hidden), cu(encoder), cu(rope), cu(pooled), 500.0, 3.5)
     check_status()
