@@ -881,7 +881,7 @@ class Attention:
         self.timed_names = ["attention"]
         self.timed_work = [self.work_per_step]
         self.roof = {"bound": "tensor", "unit": "TFLOP/s", "kernel": "attention_fwd_kernel<bf16> (1 launch per step)"}
-        self.traffic = None
+        self.traffic = 90.3e6 if self.tokens == 4608 else None   # profiles/attention_fwd_4608x24x128.md
 
     def setup_gpu(self, dev):
         from lyradiff_b200 import ops
