@@ -2,7 +2,9 @@
 
 Both sides quantize with the same static scales and the same e4m3 arithmetic, so what differs is rounding inside the
 block: bf16 library attention against an exact softmax, fp32 tensor-core sums against fp64, and the e4m3 codes that
-flip where those differences cross a rounding boundary.  The tolerance is stated against the output's own amplitude."""
+flip where those differences cross a rounding boundary.  The tolerance is stated against the output's own amplitude
+and set at about twice what these cases measure on a B200 (single FP8 block: mean 0.13 %, largest 1.2 %; double FP8
+block: 1.2 % / 2.9 %; single INT4 block: 0.3 % / 1.4 %; double INT4 block: 1.8 % / 6 %), so a kernel that drifts shows."""
 
 import pytest
 import torch
@@ -74,8 +76,8 @@ def test_single_block_against_oracle(impl, level, B, S):
     err = (delta - wdelta).abs()
     amp = float(wdelta.abs().mean())
     assert amp > 0.05                         # the block does something in this test
-    assert float(err.mean()) <= 0.02 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
-    assert float(err.max()) <= 0.25 * float(wdelta.abs().max()), float(err.max())
+    assert float(err.mean()) <= 0.004 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
+    assert float(err.max()) <= 0.03 * float(wdelta.abs().max()), float(err.max())
 
 
 def _double_state_dict(prefix, D, head_dim, level, g):
@@ -147,8 +149,8 @@ def test_double_block_against_oracle(impl, level, B, S, E):
         err = (delta - wdelta).abs()
         amp = float(wdelta.abs().mean())
         assert amp > 0.02
-        assert float(err.mean()) <= 0.03 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
-        assert float(err.max()) <= 0.3 * float(wdelta.abs().max()), float(err.max())
+        assert float(err.mean()) <= 0.025 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
+        assert float(err.max()) <= 0.06 * float(wdelta.abs().max()), float(err.max())
 
 
 def test_block_refuses_what_is_not_built():
@@ -233,8 +235,8 @@ def test_single_block_int4_against_oracle(impl, level, B, S):
     err = (delta - wdelta).abs()
     amp = float(wdelta.abs().mean())
     assert amp > 0.05
-    assert float(err.mean()) <= 0.03 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
-    assert float(err.max()) <= 0.3 * float(wdelta.abs().max()), float(err.max())
+    assert float(err.mean()) <= 0.008 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
+    assert float(err.max()) <= 0.04 * float(wdelta.abs().max()), float(err.max())
     # the LoRA-down sums use floating-point atomics (as the reference's do), so two runs may differ in the last bit
     assert float((out.float() - out2.float()).abs().max()) <= 2.0 ** -6 * float(out.float().abs().max())
 
@@ -300,8 +302,8 @@ def test_double_block_int4_against_oracle(impl, level, B, S, E):
         err = (delta - wdelta).abs()
         amp = float(wdelta.abs().mean())
         assert amp > 0.02
-        assert float(err.mean()) <= 0.04 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
-        assert float(err.max()) <= 0.3 * float(wdelta.abs().max()), float(err.max())
+        assert float(err.mean()) <= 0.035 * amp, "mean error %.4g of mean amplitude %.4g" % (float(err.mean()), amp)
+        assert float(err.max()) <= 0.12 * float(wdelta.abs().max()), float(err.max())
 
 
 def _block_inputs(B, S, D, head_dim, g, dt=torch.bfloat16):

@@ -42,6 +42,12 @@ def test_static_scratch_forward_matches_workspace_forward_twice_in_a_row():
         torch.cuda.synchronize()
         # same kernels, same arithmetic: the tolerance the W4A4 tests use is bit equality
         assert torch.equal(got.view(torch.int16), want.view(torch.int16)), "call %d differs" % call
+        # and directly against the CPU oracle, as the other W4A4 tests do (exact int32 group sums, fp32 rescale in group order)
+        from oracle import gemm as ogemm
+        from oracle import quant as oquant
+        _, sa, qa = oquant.int4_quant_g64(x.cpu(), smooth.cpu())
+        ref = ogemm.w4a4_gemm(qa, oquant.unpack_int4(lin.qweight.cpu()), sa, lin.w_scale.cpu(), bias=bias.cpu())
+        assert torch.equal(got.cpu().view(torch.int16), ref.view(torch.int16)), "call %d differs from the oracle" % call
     status, detail = ops.last_status()
     assert status == 0, detail
 
