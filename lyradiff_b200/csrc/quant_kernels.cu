@@ -403,10 +403,189 @@ template<typename T, int MODE> static int launch_row(RowParams p, cudaStream_t s
     return LYRAQ_ERR_UNSUPPORTED;
 }
 
+// ---------------------------------------------------------------------------------------------
+// AdaLN + e4m3 quantize of rows of 3072 elements, the form the FLUX blocks use, optionally with the int8 output and its
+// per-token dynamic scale (then y replaces x in the registers and a last pass quantizes it).  One warp owns a row:
+// the row stays in registers as the 12 sixteen-byte vectors each lane loaded (vector lane + 32 j), statistics are reduced
+// with shuffles only -- no shared memory, no block barrier, and three times the rows in flight of the general kernel.  The arithmetic is row_quant_kernel's, step for step,
+// including the order of the fp32 sums: there two warps share a row and a thread sums vectors t + 64 i, so lane l here
+// plays thread l (its even j) and thread l + 32 (its odd j), reduces the two halves separately and adds them as the general
+// kernel adds its two warps.  The results are the same bits.
+#ifndef ADALN_OUT_UNROLL
+#define ADALN_OUT_UNROLL 4
+#endif
+#ifndef ADALN_PER_SM
+#define ADALN_PER_SM 2
+#endif
+template<typename T, bool HAS_Y, bool HAS_B, bool HAS_Q8>
+__global__ void __launch_bounds__(256, ADALN_PER_SM) adaln3072_e4m3_kernel(const RowParams p)
+{
+    using P2 = Pair<T>;
+    constexpr int kVec = 12;             // 16-byte vectors per lane
+    constexpr int kDim = 3072;
+    constexpr int kOutGroup = ADALN_OUT_UNROLL;    // output vectors whose scale / shift loads may be in flight together (register budget)
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int    lane   = threadIdx.x & 31;
+    const size_t stride = (size_t)gridDim.x * 8;
+    size_t       row    = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+
+    const float f8r  = (!HAS_Q8 || p.qf8 != nullptr) ? 1.0f / ld_f32(p.f8_scale) : 0.0f;
+    const float f8rb = HAS_B ? 1.0f / ld_f32(p.f8_scale_b) : 0.0f;
+    const bool  has_f8 = !HAS_Q8 || p.qf8 != nullptr;
+    for (; row < p.rows; row += stride) {
+        // twelve independent loads per lane; the other warps of the SM (two blocks of eight) work while they are in flight
+        Vec16 cur[kVec];
+        {
+            const T* xr = reinterpret_cast<const T*>(p.x) + row * (size_t)kDim;
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) {
+                cur[j] = ld_nc_16(xr + ((lane + 32 * j) << 3));
+            }
+        }
+        // ---- mean: per played thread, partial sums over elements (0,1)+(4,5) and (2,3)+(6,7) of its vectors in order
+        float2 sa[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)}, sb[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+            const float2 f0 = P2::to_f32(cur[j].w[0]), f1 = P2::to_f32(cur[j].w[1]), f2 = P2::to_f32(cur[j].w[2]), f3 = P2::to_f32(cur[j].w[3]);
+            sa[j & 1] = add_f32x2(sa[j & 1], add_f32x2(f0, f2));
+            sb[j & 1] = add_f32x2(sb[j & 1], add_f32x2(f1, f3));
+        }
+        float s0 = (sa[0].x + sa[0].y) + (sb[0].x + sb[0].y), s1 = (sa[1].x + sa[1].y) + (sb[1].x + sb[1].y);
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            s0 += __shfl_xor_sync(0xffffffffu, s0, m);
+            s1 += __shfl_xor_sync(0xffffffffu, s1, m);
+        }
+        const float  mean = (s0 + s1) / (float)kDim;
+        const float2 nm   = make_float2(-mean, -mean);
+        // ---- variance, the same way
+        float2 qa[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)}, qb[2] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+            const float2 d0 = add_f32x2(P2::to_f32(cur[j].w[0]), nm), d2 = add_f32x2(P2::to_f32(cur[j].w[2]), nm);
+            const float2 d1 = add_f32x2(P2::to_f32(cur[j].w[1]), nm), d3 = add_f32x2(P2::to_f32(cur[j].w[3]), nm);
+            qa[j & 1] = fma_f32x2(d0, d0, fma_f32x2(d2, d2, qa[j & 1]));
+            qb[j & 1] = fma_f32x2(d1, d1, fma_f32x2(d3, d3, qb[j & 1]));
+        }
+        float v0 = (qa[0].x + qa[0].y) + (qb[0].x + qb[0].y), v1 = (qa[1].x + qa[1].y) + (qb[1].x + qb[1].y);
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) {
+            v0 += __shfl_xor_sync(0xffffffffu, v0, m);
+            v1 += __shfl_xor_sync(0xffffffffu, v1, m);
+        }
+        const float  var  = fmaxf((v0 + v1) / (float)kDim, 0.0f);
+        const float  rstd = 1.0f / sqrtf(var + p.eps);
+        const float2 rs2  = make_float2(rstd, rstd);
+        // ---- x_hat rounded to T; m = T(scale + 1); y = T(T(m * x_hat) + shift); e4m3 of float(y) / scale
+        const size_t brow  = row / (size_t)p.rows_per_batch;
+        const T*     mul_v = reinterpret_cast<const T*>(p.ada_scale) + brow * (size_t)kDim;
+        const T*     add_v = reinterpret_cast<const T*>(p.ada_shift) + brow * (size_t)kDim;
+        float        amax  = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kVec; ++j) {
+            if (j % kOutGroup == 0) {
+                asm volatile("" ::: "memory");   // keeps the scale / shift loads of later groups from being hoisted up here
+            }
+            const int   c = (lane + 32 * j) << 3;
+            const Vec16 a = ld_nc_16_keep(mul_v + c);
+            const Vec16 b = ld_nc_16_keep(add_v + c);
+            Vec16  y;
+            float2 e[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2   xn = mul_f32x2(add_f32x2(P2::to_f32(cur[j].w[k]), nm), rs2);
+                const uint32_t xh = P2::from_f32(xn.x, xn.y);
+                const uint32_t m  = P2::add(a.w[k], P2::one());
+                y.w[k]            = P2::add(P2::mul(m, xh), b.w[k]);
+                e[k]              = P2::to_f32(y.w[k]);
+            }
+            const size_t off = row * (size_t)kDim + c;
+            if (HAS_Y) {
+                st_16(reinterpret_cast<T*>(p.y) + off, y);
+            }
+            if (has_f8) {
+                const float2 r2 = make_float2(f8r, f8r);
+                const float2 e0 = mul_f32x2(e[0], r2), e1 = mul_f32x2(e[1], r2), e2 = mul_f32x2(e[2], r2), e3 = mul_f32x2(e[3], r2);
+                st_8(p.qf8 + off, f32x2_to_e4m3x2(e0.x, e0.y) | (f32x2_to_e4m3x2(e1.x, e1.y) << 16),
+                     f32x2_to_e4m3x2(e2.x, e2.y) | (f32x2_to_e4m3x2(e3.x, e3.y) << 16));
+            }
+            if (HAS_Q8) {
+                cur[j] = y;   // x is no longer needed: the row's y waits here for its scale
+                amax   = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(e[0].x), fabsf(e[0].y)), fmaxf(fabsf(e[1].x), fabsf(e[1].y))),
+                                           fmaxf(fmaxf(fabsf(e[2].x), fabsf(e[2].y)), fmaxf(fabsf(e[3].x), fabsf(e[3].y)))));
+            }
+            if (HAS_B) {
+                const float2 r2 = make_float2(f8rb, f8rb);
+                const float2 e0 = mul_f32x2(e[0], r2), e1 = mul_f32x2(e[1], r2), e2 = mul_f32x2(e[2], r2), e3 = mul_f32x2(e[3], r2);
+                st_8(p.qf8b + off, f32x2_to_e4m3x2(e0.x, e0.y) | (f32x2_to_e4m3x2(e1.x, e1.y) << 16),
+                     f32x2_to_e4m3x2(e2.x, e2.y) | (f32x2_to_e4m3x2(e3.x, e3.y) << 16));
+            }
+        }
+        if (HAS_Q8) {
+            // ---- int8 with the row's own scale: s = amax / 127 (1 for an all-zero row), q = sat_s8(rne(float(y) / s))
+#pragma unroll
+            for (int m = 16; m > 0; m >>= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+            }
+            const float s8 = (amax == 0.0f) ? 1.0f : amax / 127.0f;
+            const float r8 = 1.0f / s8;
+            if (lane == 0) {
+                p.q8_scale[row] = s8;
+            }
+#pragma unroll
+            for (int j = 0; j < kVec; ++j) {
+                const float2 f[4] = {P2::to_f32(cur[j].w[0]), P2::to_f32(cur[j].w[1]), P2::to_f32(cur[j].w[2]), P2::to_f32(cur[j].w[3])};
+                uint32_t     w0, w1;
+                quant8_s8_inrange(f, s8, r8, w0, w1);
+                st_8(p.q8 + row * (size_t)kDim + ((lane + 32 * j) << 3), w0, w1);
+            }
+        }
+    }
+}
+
+template<typename T, bool HAS_Y, bool HAS_B, bool HAS_Q8> static int launch_adaln3072(const RowParams& p, cudaStream_t stream)
+{
+    return launch_row_variant(adaln3072_e4m3_kernel<T, HAS_Y, HAS_B, HAS_Q8>, p, (p.rows + 7) / 8, stream);
+}
+
+// AdaLN over rows of 3072 with an e4m3 output (the FLUX form), or with the dynamically scaled int8 output and optionally e4m3
+// beside it, has a kernel of its own; it reproduces the general kernel's bits for the general kernel's default team shape,
+// so it steps aside when the debug hook has changed that shape.
+template<typename T> static bool adaln_fast_path(const RowParams& p, cudaStream_t stream, int& status)
+{
+    if (p.dim != 3072 || p.pre != nullptr || g_row_max_vpt != 6 || (p.qf8 != nullptr && p.f8_invert == 0)) {
+        return false;
+    }
+    if (p.q8 != nullptr) {
+        if (p.scale_mode != LYRAQ_SCALE_PER_TOKEN_DYNAMIC || p.qf8b != nullptr) {
+            return false;
+        }
+        status = p.y != nullptr ? launch_adaln3072<T, true, false, true>(p, stream) : launch_adaln3072<T, false, false, true>(p, stream);
+        return true;
+    }
+    if (p.qf8 == nullptr) {
+        return false;
+    }
+    if (p.y != nullptr) {
+        status = p.qf8b != nullptr ? launch_adaln3072<T, true, true, false>(p, stream) : launch_adaln3072<T, true, false, false>(p, stream);
+    } else {
+        status = p.qf8b != nullptr ? launch_adaln3072<T, false, true, false>(p, stream) : launch_adaln3072<T, false, false, false>(p, stream);
+    }
+    return true;
+}
+
 template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaStream_t stream)
 {
     if (p.dim <= 0 || (p.dim & 7) != 0 || p.dim > 16384) {
         return LYRAQ_ERR_UNSUPPORTED;
+    }
+    if (MODE == ROW_ADALN) {
+        int status = LYRAQ_OK;
+        if ((dtype == LYRAQ_F16 && adaln_fast_path<__half>(p, stream, status)) ||
+            (dtype == LYRAQ_BF16 && adaln_fast_path<__nv_bfloat16>(p, stream, status))) {
+            return status;
+        }
     }
     if (dtype == LYRAQ_F16) {
         return launch_row<__half, MODE>(p, stream);
