@@ -295,6 +295,17 @@ LYRAQ_API int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* s
 LYRAQ_API int lyraq_rmsnorm_rope(void* out, const void* qkv, const void* scale, const void* rope, int dtype, double eps,
                                  size_t batch, size_t seq_len, int heads, int head_dim, void* stream);
 
+/* The QKV projection of a FLUX block with lyraq_rmsnorm_rope fused into its epilogue: Y[m, 0 .. n) (row pitch ldy
+ * elements) = X W^T * (s_x s_w) + bias, rounded to T, and then, for the q and k heads (columns below 2 * heads * 128), the
+ * RMSNorm with qk_norm [2, 128] and the rotation rope [m, 64, 2, 2] of row m, each step rounded as lyraq_rmsnorm_rope rounds
+ * it; the bits equal those of lyraq_gemm_fp8 followed by lyraq_rmsnorm_rope in place.  n = 3 * heads * 128, 16-bit Y.
+ * Replaces the pair of calls in FluxSingleTransformerFP8Block.cc:224-250 and FluxAttentionFP8Processor.cc (the to_qkv GEMM,
+ * then invokeFusedRmsNormAndRope, src/lyradiff/kernels/rope/flux_apply_rope.h:20-30) with one launch and one pass
+ * over the projection. */
+LYRAQ_API int lyraq_gemm_fp8_qk_rope(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, void* Y, size_t ldy,
+                                     int c_dtype, const void* bias, const void* qk_norm, const void* rope, int heads, int head_dim,
+                                     double eps, int m, int n, int k, void* stream);
+
 /* Attention of the FLUX blocks over the packed projection qkv [batch, seq, 3, heads, head_dim] (q heads, k heads, v heads,
  * as lyraq_rmsnorm_rope leaves them): out[b, s, h, :] = softmax(q k^T * softmax_scale) v, no mask, head_dim 128, fp32
  * scores and accumulation on tcgen05, probabilities rounded to the 16-bit type for the second product.  The result is

@@ -52,6 +52,8 @@ SIGNATURES = {
                                      c_float, c_float, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "lyraq_gemm_fp8_quant_ld": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_int, c_void_p,
                                         c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "lyraq_gemm_fp8_qk_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p, c_void_p, c_void_p,
+                                       c_int, c_int, c_double, c_int, c_int, c_int, c_void_p]),
     "lyraq_rmsnorm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_double, c_size_t, c_size_t, c_int, c_int,
                                    c_void_p]),
     "lyraq_attention": (c_int, [c_void_p, c_int, c_size_t, c_void_p, c_void_p, c_size_t, c_void_p, c_size_t, c_void_p, c_int,

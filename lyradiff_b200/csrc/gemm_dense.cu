@@ -67,6 +67,12 @@ struct EpilogueParams {
     // optional gate (fp8, 16-bit outputs): y = T(T(T(acc * scale + bias) * gate[batch, n]) + R), gate of type T [batches, N]
     const void*  gate;
     int          rows_per_batch;
+    // optional QK RMSNorm + rotary embedding on a packed QKV projection (fp8, 16-bit outputs, 256-wide tiles, N = 3 * heads * 128):
+    // the heads of q and k (columns below 2 * qk_heads * 128) leave normalised and rotated, the v heads as they are
+    const void*  qk_norm;     // T [2][128]: RMSNorm weights of q, then of k
+    const void*  rope;        // T [M][64][2][2]: the rotation of every row (token)
+    int          qk_heads;
+    float        qk_eps;
 };
 
 struct GemmParams {
@@ -75,6 +81,67 @@ struct GemmParams {
     unsigned int*  status;
     EpilogueParams epi;
 };
+
+// QK RMSNorm + rotary embedding inside the epilogue of the QKV projection.  Arithmetic and order are those of
+// rmsnorm_rope_kernel (block_kernels.cu; reference fuseRmsNormAndRope, src/lyradiff/kernels/rope/flux_apply_rope.cu:8-76),
+// so the fused epilogue leaves the bits the GEMM followed by that kernel leaves: there sixteen lanes own eight elements of a
+// head each, sum their squares with an fma chain and combine the sixteen partial sums with xor shuffles over 8, 4, 2, 1;
+// here one thread owns the head's row and adds the same sixteen partial sums in the same tree.
+template<typename T>
+__device__ __forceinline__ void qk_sumsq_chunk(const uint32_t* o, float* part)
+{
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = Pair<T>::to_f32(o[4 * g + j]);
+            ss             = fmaf(f.x, f.x, ss);
+            ss             = fmaf(f.y, f.y, ss);
+        }
+        part[g] = ss;
+    }
+}
+
+__device__ __forceinline__ float qk_sumsq_tree(const float* part)
+{
+    float a[8], b[4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        a[i] = part[i] + part[i + 8];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        b[i] = a[i] + a[i + 4];
+    }
+    return (b[0] + b[2]) + (b[1] + b[3]);
+}
+
+// o: the 32 values of chunk c of this row's head, as 16 words of two T values; norm: the head's 128 weights; rope_row: the row's
+// 64 x 2 x 2 rotation values
+template<typename T>
+__device__ __forceinline__ void qk_norm_rope_chunk(uint32_t* o, int c, float inv, const T* norm, const T* rope_row)
+{
+    using P2 = Pair<T>;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        const int   part = c * 4 + g;                       // which 8 elements of the head
+        const Vec16 sc   = ld_nc_16_keep(norm + part * 8);
+        const Vec16 r0   = ld_nc_16_keep(rope_row + part * 16);
+        const Vec16 r1   = ld_nc_16_keep(rope_row + part * 16 + 8);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = P2::to_f32(o[4 * g + j]);
+            uint32_t     t = P2::from_f32(f.x * inv, f.y * inv);
+            t              = P2::mul(t, sc.w[j]);
+            const uint32_t ra = (j < 2) ? r0.w[2 * j] : r1.w[2 * (j - 2)];
+            const uint32_t rb = (j < 2) ? r0.w[2 * j + 1] : r1.w[2 * (j - 2) + 1];
+            const float2   pa = P2::to_f32(P2::mul(t, ra));
+            const float2   pb = P2::to_f32(P2::mul(t, rb));
+            o[4 * g + j]      = P2::from_f32(pa.x + pa.y, pb.x + pb.y);
+        }
+    }
+}
 
 // BLOCK_N is the width of the output tile; CTAS = 1: one CTA computes 128 x BLOCK_N; CTAS = 2: a pair of CTAs
 // computes 256 x BLOCK_N with cta_group::2 MMAs, each CTA staging 128 A rows and BLOCK_N / 2 B rows per K block.
@@ -579,6 +646,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                 }
             }
+            if (!RES && KIND == KIND_F8 && BLOCK_N == 256 && e.rope != nullptr && row_r < p.M) {
+                // the row's rotation values (512 bytes) are asked into L2 / L1 now, while the main loop of the tile still runs
+                const uint8_t* rr = reinterpret_cast<const uint8_t*>(e.rope) + (size_t)row_r * 512;
+#pragma unroll
+                for (int b = 0; b < 512; b += 128) {
+                    prefetch_l2(rr + b);
+                }
+            }
             if (RES) {
                 load_res16(0, resb[0]);
             }
@@ -599,6 +674,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             }
             const uint32_t t_addr = tmem_base + lane_addr + (uint32_t)(buf * BLOCK_N + half * kHalfN);
 
+            // QK RMSNorm + RoPE: this warp's 128 columns are one head.  A first pass over the accumulator gives the row's sum
+            // of squares of the values as they would be stored; the ordinary pass below then normalises and rotates them.
+            bool  qk_rope = false;
+            float qk_inv  = 0.0f;
+            int   qk_head = 0;
+            if (!RES && KIND == KIND_F8 && BLOCK_N == 256 && e.rope != nullptr) {
+                qk_head = (n_blk * BLOCK_N + half * kHalfN) >> 7;
+                if (qk_head < 2 * e.qk_heads) {
+                    qk_rope = true;
+                    float part[16];
+#pragma unroll
+                    for (int c = 0; c < kChunks; ++c) {
+                        uint32_t a1[32], o1[16];
+                        tmem_ld_32x32(t_addr + (uint32_t)(c * 32), a1);
+                        tmem_ld_wait();
+                        const uint32_t* bias1 = reinterpret_cast<const uint32_t*>(b16 + c * 32);
+                        if (e.c_dtype == LYRAQ_BF16) {
+                            epilogue_math16<KIND, __nv_bfloat16, RES>(e, a1, cp_tile + c * 32, bias1, row_scale, fp8_scale, false, resb[0], o1);
+                            qk_sumsq_chunk<__nv_bfloat16>(o1, part + (c & 3) * 4);
+                        } else {
+                            epilogue_math16<KIND, __half, RES>(e, a1, cp_tile + c * 32, bias1, row_scale, fp8_scale, false, resb[0], o1);
+                            qk_sumsq_chunk<__half>(o1, part + (c & 3) * 4);
+                        }
+                    }
+                    qk_inv = rsqrtf(qk_sumsq_tree(part) / 128.0f + e.qk_eps);
+                }
+            }
             uint32_t acc[2][32];
             tmem_ld_32x32(t_addr, acc[0]);
 #pragma unroll
@@ -657,6 +759,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     epilogue_math16<KIND, __nv_bfloat16, RES>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
                 } else {
                     epilogue_math16<KIND, __half, RES>(e, a, cp_tile + c * 32, bias2, row_scale, fp8_scale, has_res && in_range, res, o);
+                }
+                if (qk_rope && row < p.M) {
+                    const size_t noff = (qk_head >= e.qk_heads) ? 128 : 0;
+                    if (e.c_dtype == LYRAQ_BF16) {
+                        qk_norm_rope_chunk<__nv_bfloat16>(o, c & 3, qk_inv, reinterpret_cast<const __nv_bfloat16*>(e.qk_norm) + noff,
+                                                          reinterpret_cast<const __nv_bfloat16*>(e.rope) + (size_t)row * 256);
+                    } else {
+                        qk_norm_rope_chunk<__half>(o, c & 3, qk_inv, reinterpret_cast<const __half*>(e.qk_norm) + noff,
+                                                   reinterpret_cast<const __half*>(e.rope) + (size_t)row * 256);
+                    }
                 }
                 if (e.out_q_scale != nullptr) {
                     // fused activation quantize for the next FP8 linear: the T-rounded result times 1/s, e4m3 RNE satfinite
@@ -1058,6 +1170,9 @@ template<int KIND> static int run_gemm(const void* A, const void* B, GemmParams 
     if (g_forced_tile != 0) {
         t = TileChoice{g_forced_tile / 10, g_forced_tile % 10};
     }
+    if (p.epi.rope != nullptr && t.block_n != 256) {
+        t = TileChoice{256, 1};   // the fused QK norm needs a whole head (128 columns) per epilogue warp
+    }
     const bool res = p.epi.residual != nullptr || p.epi.gate != nullptr;
     if (t.ctas == 2) {
         return res ? launch_gemm<KIND, 256, 2, true>(A, B, p, sms, stream) : launch_gemm<KIND, 256, 2, false>(A, B, p, sms, stream);
@@ -1163,6 +1278,38 @@ int lyraq_gemm_fp8(const uint8_t* X, const float* s_x, const uint8_t* W, const f
     p.epi.bias     = bias;
     p.epi.residual = residual;
     p.epi.gelu     = (epilogue & LYRAQ_EPI_GELU_TANH) ? 1 : 0;
+    return run_gemm<KIND_F8>(X, W, p, (cudaStream_t)stream);
+}
+
+int lyraq_gemm_fp8_qk_rope(const uint8_t* X, const float* s_x, const uint8_t* W, const float* s_w, void* Y, size_t ldy, int c_dtype,
+                           const void* bias, const void* qk_norm, const void* rope, int heads, int head_dim, double eps, int m, int n, int k,
+                           void* stream)
+{
+    if ((c_dtype != LYRAQ_F16 && c_dtype != LYRAQ_BF16) || s_x == nullptr || s_w == nullptr || qk_norm == nullptr || rope == nullptr) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    if (head_dim != 128 || heads <= 0 || (long long)n != 3ll * heads * head_dim) {
+        return LYRAQ_ERR_UNSUPPORTED;
+    }
+    if (!aligned16(qk_norm) || !aligned16(rope) || ldy < (size_t)n || (ldy & 7) != 0 || ldy > 0x7fffffffu) {
+        return LYRAQ_ERR_INVALID_ARG;
+    }
+    GemmParams p{};
+    p.M = m;
+    p.N = n;
+    p.K = k;
+    p.epi.C        = Y;
+    p.epi.c_dtype  = c_dtype;
+    p.epi.ldc      = (int)ldy;
+    p.epi.s_a      = s_x;
+    p.epi.s_b      = s_w;
+    p.epi.alpha    = 1.0f;
+    p.epi.beta     = 0.0f;
+    p.epi.bias     = bias;
+    p.epi.qk_norm  = qk_norm;
+    p.epi.rope     = rope;
+    p.epi.qk_heads = heads;
+    p.epi.qk_eps   = (float)eps;
     return run_gemm<KIND_F8>(X, W, p, (cudaStream_t)stream);
 }
 

@@ -195,6 +195,21 @@ def gemm_with_residual_and_bias_fp8(W, w_scale, X, x_scale, Y, bias=None, residu
     return Y
 
 
+def gemm_fp8_qk_rope(W, w_scale, X, x_scale, Y, qk_scale, rope_emb, heads, head_dim, bias=None, eps=1e-6):
+    """The to_qkv FP8 GEMM with invokeFusedRmsNormAndRope (src/lyradiff/kernels/rope/flux_apply_rope.h:20-30) fused into its
+    epilogue: Y [m, 3*heads*head_dim] (rows may be a window of a taller, equally wide tensor) gets the projection with q and k
+    heads normalised and rotated; rope_emb holds the rotations of exactly these m rows.  Same bits as
+    gemm_with_residual_and_bias_fp8 followed by invoke_fused_rmsnorm_and_rope in place."""
+    m, k = X.shape
+    n = W.shape[0]
+    if W.shape[1] != k or tuple(Y.shape) != (m, n) or Y.stride(1) != 1 or rope_emb.numel() != m * head_dim * 2:
+        raise ValueError("shape mismatch")
+    st = _lib.lib().lyraq_gemm_fp8_qk_rope(_p(X), _p(x_scale), _p(W), _p(w_scale), _p(Y), Y.stride(0), _dt(Y), _p(bias), _p(qk_scale),
+                                           _p(rope_emb), heads, head_dim, float(eps), m, n, k, _stream())
+    _lib.check(st, "lyraq_gemm_fp8_qk_rope")
+    return Y
+
+
 def invoke_fused_rmsnorm_and_rope(out, qkv, scale, rope_emb, eps, batch, seq_len, heads, head_dim):
     """invokeFusedRmsNormAndRope<T> (src/lyradiff/kernels/rope/flux_apply_rope.h:20-30): qkv [batch, seq, 3*heads*head_dim]
     packed q|k|v, scale [2*head_dim], rope_emb [batch, seq, head_dim/2, 2, 2]; out may be qkv itself."""

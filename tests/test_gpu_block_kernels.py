@@ -136,6 +136,49 @@ def test_gemm_with_gate_and_residual_equals_the_two_kernels(ops, dtype, batch, s
     assert_bit_equal(inplace, want.view(m, n).cpu())
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,heads,k,tile", [(200, 2, 256, 0), (512, 3, 384, 0), (700, 4, 3072, 0), (300, 2, 256, 2561), (520, 4, 2048, 2562)])
+def test_qkv_gemm_with_fused_qk_norm_and_rope_equals_the_two_kernels(ops, dtype, m, heads, k, tile):
+    """lyraq_gemm_fp8_qk_rope = lyraq_gemm_fp8 followed by lyraq_rmsnorm_rope in place, bit for bit (the same roundings and the
+    same order of the fp32 sums), with one CTA per tile and with CTA pairs, into a plain output and into a row window of a
+    taller tensor (the joint sequence of a double-stream block); v heads and the rows around the window are untouched."""
+    from lyradiff_b200 import _lib
+    n = 3 * heads * 128
+    w = workloads.fp8_linear(m=m, k=k, n=n, seed=m + heads, dtype=dtype)
+    g = torch.Generator().manual_seed(m)
+    scale = (1.0 + 0.2 * torch.randn(2 * 128, generator=g)).to(dtype)
+    ang = torch.rand(m, 64, generator=g) * 6.28
+    rope = torch.stack([torch.cos(ang), -torch.sin(ang), torch.sin(ang), torch.cos(ang)], dim=-1).to(dtype)
+    want = torch.empty(m, n, dtype=dtype, device="cuda")
+    ops.gemm_with_residual_and_bias_fp8(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), want, bias=cu(w["bias"]))
+    plain = want.clone()
+    ops.invoke_fused_rmsnorm_and_rope(want, want, cu(scale), cu(rope), 1e-6, 1, m, heads, 128)
+    assert _lib.lib().lyraq_debug_force_gemm_tile(tile) == 0
+    try:
+        got = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+        ops.gemm_fp8_qk_rope(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), got, cu(scale), cu(rope), heads, 128, bias=cu(w["bias"]))
+        tall = torch.full((m + 37, n), 3.0, dtype=dtype, device="cuda")
+        ops.gemm_fp8_qk_rope(cu(w["qw"]), cu(w["s_w"]), cu(w["qx"]), cu(w["s_x"]), tall[16:16 + m], cu(scale), cu(rope), heads, 128,
+                             bias=cu(w["bias"]))
+    finally:
+        _lib.lib().lyraq_debug_force_gemm_tile(0)
+    check_status()
+    assert_bit_equal(got, want.cpu())
+    assert_bit_equal(got[:, 2 * heads * 128:], plain[:, 2 * heads * 128:].cpu(), "v heads")
+    assert not torch.equal(got[:, :2 * heads * 128], plain[:, :2 * heads * 128])
+    assert_bit_equal(tall[16:16 + m], want.cpu(), "row window")
+    assert bool((tall[:16] == 3.0).all()) and bool((tall[16 + m:] == 3.0).all())
+
+
+def test_fused_qk_rope_gemm_refuses_other_head_sizes(ops):
+    from lyradiff_b200 import _lib
+    p = 0x10000
+    L = _lib.lib()
+    assert L.lyraq_gemm_fp8_qk_rope(p, p, p, p, p, 192, 1, None, p, p, 1, 64, 1e-6, 128, 192, 128, None) == 2   # LYRAQ_ERR_UNSUPPORTED
+    assert L.lyraq_gemm_fp8_qk_rope(p, p, p, p, p, 768, 1, None, p, p, 1, 128, 1e-6, 128, 768, 128, None) == 2  # n != 3 * heads * 128
+    assert L.lyraq_gemm_fp8_qk_rope(p, p, p, p, p, 384, 2, None, p, p, 1, 128, 1e-6, 128, 384, 128, None) == 1  # fp32 output: invalid
+
+
 def test_gate_fusion_refuses_tiles_that_straddle_batches(ops):
     w = workloads.fp8_linear(m=200, k=128, n=128, seed=1)
     y = torch.empty(200, 128, dtype=torch.bfloat16, device="cuda")
