@@ -811,8 +811,8 @@ class AdalnQuant:
         self.launches_per_step = 1
         self.timed_names = ["adaln_quant"]
         self.timed_work = [self.work_per_step]
-        self.roof = {"bound": "hbm", "unit": "GB/s", "kernel": "row_quant_kernel<bf16, ROW_ADALN> (1 launch per step)"}
-        self.traffic = 28.5e6 if T == 4608 else None  # profiles/row_quant_adaln_4608x3072.md (outputs absorbed by L2)
+        self.roof = {"bound": "hbm", "unit": "GB/s", "kernel": "adaln3072_e4m3_kernel<bf16, int8 + e4m3 out> (1 launch per step)"}
+        self.traffic = 28.6e6 if T == 4608 else None  # profiles/adaln3072_4608x3072.md (outputs absorbed by L2)
 
     def setup_gpu(self, dev):
         from lyradiff_b200 import ops

@@ -127,17 +127,6 @@ Tensor fp8_gemm(const Fp8Weight& w, const Tensor& xq, int64_t m, at::ScalarType 
     return y;
 }
 
-// The to_qkv projection with the QK RMSNorm and the rotary embedding in the GEMM's epilogue: rows [0, m) of y (a tensor of
-// row pitch w.n, possibly a window of a taller one) get the projection as lyraq_gemm_fp8 + lyraq_rmsnorm_rope would leave it.
-void fp8_gemm_qk_rope(const Fp8Weight& w, const Tensor& xq, int64_t m, at::ScalarType dt, void* y, const Tensor& qk_scale, const void* rope,
-                      int64_t heads, int64_t head_dim)
-{
-    check(lyraq_gemm_fp8_qk_rope(xq.data_ptr<uint8_t>(), w.input_scale.data_ptr<float>(), w.qweight.data_ptr<uint8_t>(),
-                                 w.w_scale.data_ptr<float>(), y, (size_t)w.n, dt_code(dt), ptr(w.bias), qk_scale.data_ptr(), rope, (int)heads,
-                                 (int)head_dim, 1e-6, (int)m, (int)w.n, (int)w.k, stream()),
-          "lyraq_gemm_fp8_qk_rope");
-}
-
 // out = gate * (x_q W^T * s + bias) + residual, in the GEMM's epilogue where a tile cannot straddle two batch entries.
 Tensor fp8_gemm_gate_residual(const Fp8Weight& w, const Tensor& xq, const Tensor& gate, const Tensor& residual, int64_t batch,
                               int64_t seq, at::ScalarType dt)
@@ -543,9 +532,10 @@ struct FluxSingleTransformerBlockOp: BlockBase {
                                       mlp.input_scale.data_ptr<float>(), hidden.data_ptr(), mod[1].data_ptr(), mod[0].data_ptr(),
                                       dtc, (size_t)B, (size_t)S, (size_t)D, 1e-6, stream()),
               "lyraq_adaln_quant_fp8x2");
-        // to_qkv with QK RMSNorm + RoPE in its epilogue (the reference's GEMM followed by invokeFusedRmsNormAndRope, same bits)
-        Tensor q3 = at::empty({T, 3 * D}, hidden.options());
-        fp8_gemm_qk_rope(qkv, nq, T, dtype, q3.data_ptr(), qk_scale, rope.data_ptr(), heads, head_dim);
+        Tensor q3 = fp8_gemm(qkv, nq, T, dtype);
+        check(lyraq_rmsnorm_rope(q3.data_ptr(), q3.data_ptr(), qk_scale.data_ptr(), rope.data_ptr(), dtc, 1e-6, (size_t)B, (size_t)S,
+                                 (int)heads, (int)head_dim, stream()),
+              "lyraq_rmsnorm_rope");
         // the attention output leaves the kernel as e4m3 in the first column window of proj_out's [T, (mlp_scale + 1) D] input
         const int64_t ld = (mlp_scale + 1) * D;
         Tensor cat8 = at::empty({T, ld}, opt8);
@@ -689,19 +679,12 @@ struct FluxTransformerBlockOp: BlockBase {
         if (int4()) {
             return s.qkv4.run(adaln16(x, mod[1], mod[0]).view({B * S, D}), B * S, Tensor(), dtype);
         }
-        return fp8_gemm(s.qkv, adaln_e4m3(s, x, mod), B * S, dtype);
-    }
-
-    // AdaLN of a stream's input, quantized to e4m3 with the input scale of its to_qkv linear
-    Tensor adaln_e4m3(Stream& s, const Tensor& x, const std::vector<Tensor>& mod)
-    {
-        const int64_t B = x.size(0), S = x.size(1), D = x.size(2);
         Tensor nq = at::empty({B * S, D}, x.options().dtype(at::kByte));
         check(lyraq_adaln_quant(nullptr, nullptr, nullptr, nq.data_ptr<uint8_t>(), s.qkv.input_scale.data_ptr<float>(), x.data_ptr(),
                                 mod[1].data_ptr(), mod[0].data_ptr(), dt_code(dtype), nullptr, (size_t)B, (size_t)S, (size_t)D, 1e-6,
                                 stream()),
               "lyraq_adaln_quant");
-        return nq;
+        return fp8_gemm(s.qkv, nq, B * S, dtype);
     }
 
     Tensor post_attention(Stream& s, const Tensor& x, const Tensor& attn, const std::vector<Tensor>& mod)
@@ -761,24 +744,13 @@ struct FluxTransformerBlockOp: BlockBase {
         }
         auto   mod_i = ahead != nullptr ? ahead->parts[0] : img.norm.run(temb, 6, dtype);
         auto   mod_t = ahead != nullptr ? ahead->parts[1] : txt.norm.run(temb, 6, dtype);
+        Tensor qi = pre_attention(img, hidden, mod_i).view({B, S, 3 * D});
+        Tensor qt = pre_attention(txt, encoder, mod_t).view({B, E, 3 * D});
         // joint sequence [B, E + S, 3, H, Dh], text first (invokeFusedRmsNormCatAndRope, flux_apply_rope.cu:78-156)
         Tensor joint = at::empty({B, tot, 3 * D}, hidden.options());
         Tensor r     = rope.view({B, tot, head_dim * 2});
         const int dtc = dt_code(dtype);
-        // One batch entry and FP8 linears: each stream's to_qkv GEMM normalises, rotates and writes its rows of the joint
-        // sequence itself.  Otherwise the projections are computed apart and the rope kernel joins them.
-        const bool fused_qk = !int4() && B == 1;
-        Tensor qi, qt;
-        if (fused_qk) {
-            fp8_gemm_qk_rope(txt.qkv, adaln_e4m3(txt, encoder, mod_t), E, dtype, joint[0].slice(0, 0, E).data_ptr(), txt.qk_scale,
-                             r[0].slice(0, 0, E).data_ptr(), heads, head_dim);
-            fp8_gemm_qk_rope(img.qkv, adaln_e4m3(img, hidden, mod_i), S, dtype, joint[0].slice(0, E, tot).data_ptr(), img.qk_scale,
-                             r[0].slice(0, E, tot).data_ptr(), heads, head_dim);
-        } else {
-            qi = pre_attention(img, hidden, mod_i).view({B, S, 3 * D});
-            qt = pre_attention(txt, encoder, mod_t).view({B, E, 3 * D});
-        }
-        for (int64_t b = 0; b < B && !fused_qk; ++b) {
+        for (int64_t b = 0; b < B; ++b) {
             check(lyraq_rmsnorm_rope(joint[b].slice(0, 0, E).data_ptr(), qt[b].data_ptr(), txt.qk_scale.data_ptr(),
                                      r[b].slice(0, 0, E).data_ptr(), dtc, 1e-6, 1, (size_t)E, (int)heads, (int)head_dim, stream()),
                   "lyraq_rmsnorm_rope");
