@@ -1,6 +1,6 @@
 """Writes tests/golden/ref_*.npz: outputs of the REFERENCE's own Python functions on seeded inputs.
 
-    python tests/golden/make_reference_fixtures.py [path/to/lyraDiff checkout]
+    python tests/golden/make_reference_fixtures.py path/to/lyraDiff-checkout
 
 Three functions of the reference are plain torch and run on a CPU once they are lifted out of their modules (the
 modules themselves import diffusers / modelopt, which are not installed, so the function definitions are taken from the
@@ -53,7 +53,9 @@ def int8_weight_cases(g):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_reference_fixtures.py <checkout of the reference repository>")
+    ref = sys.argv[1]
     g = torch.Generator().manual_seed(20240607)
 
     # ---- tensor_quant: INT8 weights, per output channel (amax [N, 1] as the exporter passes it, :209-219)

@@ -226,7 +226,7 @@ def test_single_block_int4_against_oracle(impl, level, B, S):
     want, mid = blocks.flux_single_block_int4(hidden, rope, temb, sd, prefix, heads, head_dim, mlp_scale, level)
     # the pieces in front of the attention see identical inputs on both sides: the W4A4 linear with the bias rounded in
     # and the QK norm + RoPE agree to the LoRA-down summation order (a few fp32 ulps before the rounding to bf16)
-    if impl == "mirror":   # the mirror keeps its intermediate buffers; the C++ class is judged by its output
+    if impl == "mirror":   # the mirror keeps its intermediate buffers; the C++ class is checked through its output
         qkv_gpu = op._buf["qkv"].cpu().float()
         dq = (qkv_gpu - mid["qkv"].float()).abs()
         assert float((dq > 0).float().mean()) < 0.05 and float(dq.max()) <= 2.0 ** -6 * float(mid["qkv"].float().abs().max())
