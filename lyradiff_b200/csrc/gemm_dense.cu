@@ -576,32 +576,57 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             tile_coords(tile, p.m_tiles, p.n_tiles, m_blk, n_blk);
             // column parameters of this warp's half of the tile, staged while the main loop of the tile may still run
             __syncwarp();
+            {
+                // All of a lane's loads are issued before any of them is used: the loop below is not hidden behind the main
+                // loop when K is small, and one load after the other costs a round trip to L2 per column.
+                constexpr int kPer = kHalfN / 32;   // columns per lane: 4 or 2
+                float    cs[kPer];
+                uint16_t braw[kPer], graw[kPer];
+                float    b32[kPer];
 #pragma unroll
-            for (int cc = lane; cc < kHalfN; cc += 32) {
-                const int col = n_blk * BLOCK_N + half * kHalfN + cc;
-                float2    v   = make_float2(0.0f, 0.0f);
-                uint16_t  raw = 0;
-                if (col < p.N) {
-                    if (KIND == KIND_I8 && e.col_scale != nullptr) {
-                        v.x = ld_f32(e.col_scale + col);
-                    }
-                    if (RES && KIND == KIND_F8 && e.gate != nullptr) {
-                        // all rows of a tile belong to one batch entry (checked on the host)
-                        const size_t   gi = (size_t)((m_blk * kTileM) / e.rows_per_batch) * (size_t)p.N + (size_t)col;
-                        const uint16_t gr = reinterpret_cast<const uint16_t*>(e.gate)[gi];
-                        v.x = (e.c_dtype == LYRAQ_BF16) ? __uint_as_float((uint32_t)gr << 16) : __half2float(__ushort_as_half(gr));
-                    }
-                    if (e.bias != nullptr) {
-                        if (e.c_dtype == LYRAQ_F32) {
-                            v.y = reinterpret_cast<const float*>(e.bias)[col];
-                        } else {
-                            raw = reinterpret_cast<const uint16_t*>(e.bias)[col];
-                            v.y = (e.c_dtype == LYRAQ_BF16) ? __uint_as_float((uint32_t)raw << 16) : __half2float(__ushort_as_half(raw));
+                for (int i = 0; i < kPer; ++i) {
+                    const int col = n_blk * BLOCK_N + half * kHalfN + lane + 32 * i;
+                    cs[i]   = 0.0f;
+                    braw[i] = 0;
+                    graw[i] = 0;
+                    b32[i]  = 0.0f;
+                    if (col < p.N) {
+                        if (KIND == KIND_I8 && e.col_scale != nullptr) {
+                            cs[i] = ld_f32(e.col_scale + col);
+                        }
+                        if (RES && KIND == KIND_F8 && e.gate != nullptr) {
+                            // all rows of a tile belong to one batch entry (checked on the host)
+                            const size_t gi = (size_t)((m_blk * kTileM) / e.rows_per_batch) * (size_t)p.N + (size_t)col;
+                            graw[i] = reinterpret_cast<const uint16_t*>(e.gate)[gi];
+                        }
+                        if (e.bias != nullptr) {
+                            if (e.c_dtype == LYRAQ_F32) {
+                                b32[i] = reinterpret_cast<const float*>(e.bias)[col];
+                            } else {
+                                braw[i] = reinterpret_cast<const uint16_t*>(e.bias)[col];
+                            }
                         }
                     }
                 }
-                cp_tile[cc] = v;
-                b16[cc]     = raw;
+#pragma unroll
+                for (int i = 0; i < kPer; ++i) {
+                    const int cc  = lane + 32 * i;
+                    const int col = n_blk * BLOCK_N + half * kHalfN + cc;
+                    float2    v   = make_float2(0.0f, 0.0f);
+                    if (col < p.N) {
+                        v.x = cs[i];
+                        if (RES && KIND == KIND_F8 && e.gate != nullptr) {
+                            v.x = (e.c_dtype == LYRAQ_BF16) ? __uint_as_float((uint32_t)graw[i] << 16) : __half2float(__ushort_as_half(graw[i]));
+                        }
+                        if (e.bias != nullptr) {
+                            v.y = (e.c_dtype == LYRAQ_F32)    ? b32[i]
+                                  : (e.c_dtype == LYRAQ_BF16) ? __uint_as_float((uint32_t)braw[i] << 16)
+                                                              : __half2float(__ushort_as_half(braw[i]));
+                        }
+                    }
+                    cp_tile[cc] = v;
+                    b16[cc]     = (col < p.N && e.bias != nullptr && e.c_dtype != LYRAQ_F32) ? braw[i] : (uint16_t)0;
+                }
             }
             __syncwarp();
             // 16-bit residual: this thread's row segment of the tile is asked into L2 now, while the main loop of the tile
