@@ -206,7 +206,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         for (int s = 0; s < kUStages; ++s) {
             mbar_init(full_u(s), kExpandWarps);
-            mbar_init(empty_u(s), 2);   // one commit per MMA issuer
+            mbar_init(empty_u(s), 1);   // the issuer's commit
         }
         for (int b = 0; b < kPBufs; ++b) {
             mbar_init(part_full(b), 1);
@@ -281,20 +281,18 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
         }
-    } else if (warp == 1 || warp == 15) {
+    } else if (warp == 1) {
         if (lane == 0) {
-            // -------------------------------------------------------------- MMA issuers
-            // Every tcgen05 instruction and barrier operation costs its issuing thread tens of cycles, and one group is
-            // only 128 cycles of tensor work, so a single issuer would bound the kernel.  Two threads share the work:
-            // issuer i takes group i of every K block and owns the partial buffers i and i + 2; each commits the
-            // operand stage when its own MMAs are done (the stage's barrier counts both).
-            const int iss    = (warp == 1) ? 0 : 1;
+            // -------------------------------------------------------------- MMA issuer
+            // One hand-off per K block, not per group: both groups of a block go into the two partial buffers of a pair
+            // (pairs alternate between blocks) behind one commit, and the drain warps wait once for both.  A hand-off through
+            // an mbarrier costs each side a couple of hundred cycles, a group is 128 cycles of tensor work.
             int       ustage = 0;
             uint32_t  uphase = 0;
-            uint32_t  n      = 0;  // groups this issuer has issued
+            uint32_t  n      = 0;  // K-block steps issued
             bool      ok     = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-                const int steps = num_kb + (p.lora_act != nullptr ? 1 : 0);  // the low-rank step is issuer 0's
+                const int steps = num_kb + (p.lora_act != nullptr ? 1 : 0);  // the low-rank product is one more step
                 for (int kb = 0; ok && kb < steps; ++kb) {
                     if (!mbar_wait(full_u(ustage), uphase, abort_flag)) {
                         report_timeout(p.status, 0x1200u | (unsigned)ustage);
@@ -302,39 +300,38 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         ok = false;
                         break;
                     }
-                    const bool lora_step = (kb == num_kb);
-                    const int  groups    = lora_step ? 1 : min(2, p.G - 2 * kb);
-                    if (iss < groups) {
-                        const int pb = iss + 2 * (int)(n & 1u);
-                        if (!mbar_wait(part_empty(pb), ((n >> 1) & 1u) ^ 1u, abort_flag)) {
-                            report_timeout(p.status, 0x1300u | (unsigned)pb);
-                            *abort_flag = 1;
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        const uint32_t a_addr = ustage0 + ustage * kUStage;
-                        const uint64_t adesc  = umma_desc_k_sw128(a_addr);
-                        const uint64_t bdesc  = umma_desc_k_sw128(a_addr + kOperandTile);
-                        const uint32_t d_tmem = tmem_base + (uint32_t)(pb * kBN);
-                        if (lora_step) {
-                            // two K = 16 MMAs on 16-bit operands: the fp32 low-rank product
-                            const uint32_t idesc = umma_idesc(1u, p.c_dtype == LYRAQ_BF16 ? 1u : 0u, kBM, kBN);
+                    const int q = (int)(n & 1u);
+                    if (!mbar_wait(part_empty(q), ((n >> 1) & 1u) ^ 1u, abort_flag)) {
+                        report_timeout(p.status, 0x1300u | (unsigned)q);
+                        *abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const bool     lora_step = (kb == num_kb);
+                    const int      groups    = lora_step ? 1 : min(2, p.G - 2 * kb);
+                    const uint32_t a_addr    = ustage0 + ustage * kUStage;
+                    const uint64_t adesc     = umma_desc_k_sw128(a_addr);
+                    const uint64_t bdesc     = umma_desc_k_sw128(a_addr + kOperandTile);
+                    if (lora_step) {
+                        // two K = 16 MMAs on 16-bit operands: the fp32 low-rank product
+                        const uint32_t idesc = umma_idesc(1u, p.c_dtype == LYRAQ_BF16 ? 1u : 0u, kBM, kBN);
 #pragma unroll
-                            for (int k = 0; k < kLoraRank / 16; ++k) {
-                                mma_f16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (uint32_t)k);
-                            }
-                        } else
-                        {
+                        for (int k = 0; k < kLoraRank / 16; ++k) {
+                            mma_f16(tmem_base + (uint32_t)(2 * q * kBN), adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, (uint32_t)k);
+                        }
+                    } else {
+                        for (int g = 0; g < groups; ++g) {
+                            const uint32_t d_tmem = tmem_base + (uint32_t)((2 * q + g) * kBN);
 #pragma unroll
                             for (int k = 0; k < 2; ++k) {
-                                const uint64_t koff = (uint64_t)((iss * 2 + k) * 2);  // 32-byte K steps, in 16-byte units
+                                const uint64_t koff = (uint64_t)((g * 2 + k) * 2);  // 32-byte K steps, in 16-byte units
                                 mma_i8(d_tmem, adesc + koff, bdesc + koff, kIdesc, (uint32_t)k);
                             }
                         }
-                        tc_commit(part_full(pb));
-                        ++n;
                     }
+                    tc_commit(part_full(q));
+                    ++n;
                     tc_commit(empty_u(ustage));
                     if (++ustage == kUStages) {
                         ustage = 0;
@@ -548,7 +545,7 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const bool     vec_ok    = (p.c_dtype == LYRAQ_F32) ? ((p.N & 3) == 0) : ((p.N & 7) == 0);
         int            slot = 0;
         uint32_t       sphase = 0;
-        uint32_t       n0 = 0, n1 = 0;  // groups drained per MMA issuer (issuer i: group i of a K block, buffers i, i + 2)
+        uint32_t       n = 0;  // K-block steps drained (step s uses the partial buffers 2 (s & 1) and 2 (s & 1) + 1)
         bool           ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
             const int m_blk = tile % p.m_tiles;
@@ -573,23 +570,22 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 const float* sas    = reinterpret_cast<const float*>(gen_base + kScaleOffset + slot * kScaleSlot);
                 const float* sbs    = sas + kSlotGroups * kBM;
                 const int    groups = min(2, p.G - 2 * kb);
+                const int    q      = (int)(n & 1u);
+                const bool   got_p  = mbar_wait(part_full(q), (n >> 1) & 1u, abort_flag);
+                ++n;
+                if (!__all_sync(0xffffffffu, got_p)) {
+                    if (lane == 0) {
+                        report_timeout(p.status, 0x1700u | (unsigned)q);
+                    }
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
 #pragma unroll 1
                 for (int g = 0; g < groups; ++g) {
-                    const uint32_t nsel = g ? n1 : n0;
-                    const int      pb   = g + 2 * (int)(nsel & 1u);
-                    const int      gs   = (kb & 3) * 2 + g;  // group index inside the scale slot
-                    const bool got_p = mbar_wait(part_full(pb), (nsel >> 1) & 1u, abort_flag);
-                    n0 += (g == 0) ? 1u : 0u;
-                    n1 += (g == 1) ? 1u : 0u;
-                    if (!__all_sync(0xffffffffu, got_p)) {
-                        if (lane == 0) {
-                            report_timeout(p.status, 0x1700u | (unsigned)pb);
-                        }
-                        *abort_flag = 1;
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
+                    const int pb = 2 * q + g;
+                    const int gs = (kb & 3) * 2 + g;  // group index inside the scale slot
                     const float  sa_s = sas[gs * kBM + trow];
                     const float2 sa_v = make_float2(sa_s, sa_s);
                     const uint32_t t_addr = tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64);
@@ -610,11 +606,11 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                             acc[c * 8 + 2 * j + 1] = fma_f32x2(mul_f32x2(p1, sa_v), make_float2(s.z, s.w), acc[c * 8 + 2 * j + 1]);
                         }
                     }
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(part_empty(pb));
-                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(part_empty(q));
                 }
                 if (ok && ((kb & 3) == 3 || kb == num_kb - 1)) {
                     __syncwarp();
@@ -628,8 +624,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
             }
             if (ok && p.lora_act != nullptr) {
-                const int pb = 2 * (int)(n0 & 1u);
-                if (!__all_sync(0xffffffffu, mbar_wait(part_full(pb), (n0 >> 1) & 1u, abort_flag))) {
+                const int q  = (int)(n & 1u);
+                const int pb = 2 * q;
+                if (!__all_sync(0xffffffffu, mbar_wait(part_full(q), (n >> 1) & 1u, abort_flag))) {
                     if (lane == 0) {
                         report_timeout(p.status, 0x1b00u | (unsigned)pb);
                     }
@@ -650,9 +647,9 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) {
-                        mbar_arrive(part_empty(pb));
+                        mbar_arrive(part_empty(q));
                     }
-                    ++n0;
+                    ++n;
                 }
             }
             if (!ok) {
