@@ -12,14 +12,15 @@
 // occupies exactly 64 consecutive bytes (two K = 32 MMA steps).
 //
 // Each group's int32 partial must be rescaled in fp32 before the next group is added, so the
-// accumulator leaves tensor memory once per group: four partial buffers (128 columns each) are
-// cycled, the MMA warp runs up to four groups ahead, and eight drain warps convert / scale /
-// accumulate in registers.  That CUDA-core work, not the tensor pipe, bounds this kernel.
+// accumulator leaves tensor memory once per group: four partial buffers (128 columns each) form two
+// pairs, the two groups of a K block go into one pair behind one commit while the drain works on the
+// other, and eight drain warps convert / scale / accumulate in registers.  That CUDA-core work and the
+// hand-offs around it, not the tensor pipe, bound this kernel.
 //
 // 512 threads per CTA (sixteen warps, four per scheduler, hence at most 128 registers per thread), one persistent
 // CTA per SM:
 //   warp 0       TMA producer: packed A (128 x 64 B) and packed B (128 x 64 B) tiles, ring of 4 stages
-//   warps 1, 15  MMA issuers: warp 1 issues the first group of every K block, warp 15 the second
+//   warp 1       MMA issuer: both groups of a K block, one commit (warp 15 has no role)
 //   warp 2       scale loader: every four K blocks (8 groups) it transposes sa[m, g] and sb[n, g] of the tile into
 //                shared memory as [g][row] (ring of 3 slots), running ahead of the drain; also owns tensor memory
 //   warps 3, 12-14  expand nibbles -> swizzled int8 operand tiles (ring of 4 stages)
@@ -589,11 +590,16 @@ gemm_w4a4_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const float  sa_s = sas[gs * kBM + trow];
                     const float2 sa_v = make_float2(sa_s, sa_s);
                     const uint32_t t_addr = tmem_base + lane_addr + (uint32_t)(pb * kBN + half * 64);
+                    // the load of chunk c + 1 is in flight while chunk c is rescaled
+                    uint32_t pcs[2][16];
+                    tmem_ld_32x16(t_addr, pcs[0]);
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        uint32_t pc[16];
-                        tmem_ld_32x16(t_addr + (uint32_t)(c * 16), pc);
                         tmem_ld_wait();
+                        if (c + 1 < 4) {
+                            tmem_ld_32x16(t_addr + (uint32_t)((c + 1) * 16), pcs[(c + 1) & 1]);
+                        }
+                        const uint32_t* pc  = pcs[c & 1];
                         const float4*   sb4 = reinterpret_cast<const float4*>(sbs + gs * kBN + half * 64 + c * 16);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
