@@ -39,7 +39,7 @@ constexpr int kStoreBox    = 32 * 64;                       // one warp's stagin
 // per epilogue warp: one store box, then the (column scale, bias as fp32) pairs and the bias as stored (16-bit) of
 // the 128 columns the warp covers
 constexpr int kColParams   = 128 * 8 + 128 * 2;
-constexpr int kEpiSmem     = kEpiWarps * (kStoreBox + kColParams);
+constexpr int kStoreBoxWide = 32 * 128;                     // 32 rows x 128 bytes: two chunks of a 16-bit output behind one TMA store
 constexpr int kBarBytes    = 256;
 
 enum GemmKind { KIND_I8 = 0, KIND_F8 = 1 };
@@ -155,7 +155,11 @@ template<int BLOCK_N, int CTAS> struct GemmSmem {
     static constexpr int kABytes     = kASub * kSub;
     static constexpr int kBBytes     = kBSub * kSub;
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kStages     = (kSmemBudget - 1024 - kBarBytes - kEpiSmem) / kStageBytes;  // 4 (1 x 256), 6 (1 x 128) or 3 double stages (pair)
+    // One CTA with the 256-wide tile is what short-K problems get (the pair needs K >= 2048), and there the epilogue, not the
+    // main loop, sets the pace: its warps get boxes of two chunks (one TMA store per 64 columns) and the ring one stage less.
+    static constexpr int kBox        = (CTAS == 1 && BLOCK_N == 256) ? kStoreBoxWide : kStoreBox;
+    static constexpr int kEpiSmem    = kEpiWarps * (kBox + kColParams);
+    static constexpr int kStages     = (kSmemBudget - 1024 - kBarBytes - kEpiSmem) / kStageBytes;  // 3 (1 x 256), 6 (1 x 128) or 3 double stages (pair)
     static constexpr int kEpiOffset  = kStages * kStageBytes;           // 1024-aligned: stage sizes are multiples of 16 KB
     static constexpr int kBarOffset  = kEpiOffset + kEpiSmem;
     static constexpr int kTotal      = kBarOffset + kBarBytes + 1024;   // + alignment slack
@@ -558,11 +562,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
         const EpilogueParams& e  = p.epi;
         // this warp's private column parameters: no other warp reads or writes them, so __syncwarp is all they need
-        float2*        cp_tile   = reinterpret_cast<float2*>(gen_base + S::kEpiOffset + kEpiWarps * kStoreBox +
+        float2*        cp_tile   = reinterpret_cast<float2*>(gen_base + S::kEpiOffset + kEpiWarps * S::kBox +
                                                              (warp - kEpiWarp0) * kColParams);  // [128]
         uint16_t*      b16       = reinterpret_cast<uint16_t*>(cp_tile + 128);                  // [128]
-        uint8_t*       box       = gen_base + S::kEpiOffset + (warp - kEpiWarp0) * kStoreBox;
-        const uint32_t box_addr  = smem_base + S::kEpiOffset + (warp - kEpiWarp0) * kStoreBox;
+        uint8_t*       box       = gen_base + S::kEpiOffset + (warp - kEpiWarp0) * S::kBox;
+        const uint32_t box_addr  = smem_base + S::kEpiOffset + (warp - kEpiWarp0) * S::kBox;
         float fp8_scale = 0.0f;
         if (KIND == KIND_F8) {
             fp8_scale = e.alpha * ld_f32(e.s_a) * ld_f32(e.s_b);
@@ -725,6 +729,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                     }
                     qk_inv = rsqrtf(qk_sumsq_tree(part) / 128.0f + e.qk_eps);
                 }
+            }
+            if (CTAS == 1 && BLOCK_N == 256 && !RES && e.tma_store == 2) {
+                // Short-K problems, 16-bit output: 64 columns per step and ONE TMA store for them (the store box holds 32 rows x
+                // 128 bytes in the 128-byte swizzle).  A store costs its warp ~450 cycles (waiting for the box, two re-convergences,
+                // the proxy fence, the instruction itself) whatever its size, and with K this short the epilogue sets the pace.
+#pragma unroll 1
+                for (int c2 = 0; c2 < kHalfN / 64; ++c2) {
+                    uint32_t a64[64];
+                    tmem_ld_32x32(t_addr + (uint32_t)(c2 * 64), a64);
+                    tmem_ld_32x32(t_addr + (uint32_t)(c2 * 64 + 32), a64 + 32);
+                    tmem_ld_wait();
+                    const int col0  = n_blk * BLOCK_N + half * kHalfN + c2 * 64;
+                    const int valid = p.N - col0;
+                    uint32_t  o64[32];
+#pragma unroll
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const uint32_t* bias2 = reinterpret_cast<const uint32_t*>(b16 + c2 * 64 + h2 * 32);
+                        if (e.c_dtype == LYRAQ_BF16) {
+                            epilogue_math16<KIND, __nv_bfloat16, RES>(e, a64 + h2 * 32, cp_tile + c2 * 64 + h2 * 32, bias2, row_scale, fp8_scale, false, resb[0],
+                                                                      o64 + h2 * 16);
+                        } else {
+                            epilogue_math16<KIND, __half, RES>(e, a64 + h2 * 32, cp_tile + c2 * 64 + h2 * 32, bias2, row_scale, fp8_scale, false, resb[0],
+                                                               o64 + h2 * 16);
+                        }
+                    }
+                    if (lane == 0) {
+                        tma_store_wait_read();  // the previous store has drained the box
+                    }
+                    __syncwarp();
+                    uint8_t*  brow = box + lane * 128;
+                    const int sw   = lane & 7;   // 128-byte swizzle: 16-byte piece q of row r lies at piece q ^ (r & 7)
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        Vec16 w;
+                        w.w[0] = o64[4 * q]; w.w[1] = o64[4 * q + 1]; w.w[2] = o64[4 * q + 2]; w.w[3] = o64[4 * q + 3];
+                        *reinterpret_cast<Vec16*>(brow + ((q ^ sw) << 4)) = w;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0 && row0 < p.M && valid > 0) {
+                        tma_store_2d(&tmap_c, box_addr, col0, row0);
+                        tma_store_commit();
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(tmem_empty_bar(buf));
+                }
+                continue;
             }
             uint32_t acc[2][32];
             tmem_ld_32x32(t_addr, acc[0]);
@@ -1031,9 +1085,9 @@ int make_tmap_bytes_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64
 
 // Tensor map of a row-major [rows, cols] matrix of 1- or 2-byte elements for TMA stores of 32 x 32 boxes whose
 // shared-memory image uses the swizzle that matches the box's row size (32 or 64 bytes).
-int make_tmap_store(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int elem_bytes)
+int make_tmap_store(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, int elem_bytes, bool wide = false)
 {
-    const TmapKey key{base, cols, rows, ld * (uint64_t)elem_bytes, 32, 32, 16 + elem_bytes};
+    const TmapKey key{base, cols, rows, ld * (uint64_t)elem_bytes, wide ? 64u : 32u, 32, 16 + elem_bytes + (wide ? 8 : 0)};
     if (tmap_cache().find(key, map)) {
         return LYRAQ_OK;
     }
@@ -1043,11 +1097,12 @@ int make_tmap_store(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
     }
     const cuuint64_t dims[2]    = {cols, rows};
     const cuuint64_t strides[1] = {ld * (uint64_t)elem_bytes};  // row pitch: cols, or more when the output is a column window
-    const cuuint32_t box[2]     = {32, 32};
+    // 32 rows x 32 columns (64 or 32 bytes a row), or, wide (16-bit only), 32 rows x 64 columns = 128 bytes a row
+    const cuuint32_t box[2]     = {wide ? 64u : 32u, 32};
     const cuuint32_t estr[2]    = {1, 1};
     const CUresult   r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2,
                             const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                            elem_bytes == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B,
+                            wide ? CU_TENSOR_MAP_SWIZZLE_128B : elem_bytes == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B,
                             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         record_cuda_error(cudaErrorInvalidValue, "cuTensorMapEncodeTiled refused the output tensor map");
@@ -1130,11 +1185,13 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
             p.epi.tma_store = 1;
         }
     } else if ((p.epi.c_dtype == LYRAQ_BF16 || p.epi.c_dtype == LYRAQ_F16) && (p.N & 7) == 0) {
-        st = make_tmap_store(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N, (uint64_t)p.epi.ldc, 2);
+        // one CTA, 256-wide tile, no residual, no rope: the epilogue stores 64 columns at a time (tma_store == 2)
+        const bool wide = CTAS == 1 && BLOCK_N == 256 && !RES && p.epi.rope == nullptr;
+        st = make_tmap_store(&tc, p.epi.C, (uint64_t)p.M, (uint64_t)p.N, (uint64_t)p.epi.ldc, 2, wide);
         if (st != LYRAQ_OK) {
             return st;
         }
-        p.epi.tma_store = 1;
+        p.epi.tma_store = wide ? 2 : 1;
     }
     p.m_tiles = (p.M + kBlockM * CTAS - 1) / (kBlockM * CTAS);
     p.n_tiles = (p.N + BLOCK_N - 1) / BLOCK_N;
