@@ -17,7 +17,9 @@
 //                               shared memory (no barrier across warps), then streams 32-column chunks: tcgen05.ld of chunk
 //                               c+1 is in flight while chunk c gets its scales / bias / GELU / residual in registers;
 //                               16-bit results go through a 64-byte-swizzled shared-memory box and leave with one TMA
-//                               store per chunk (full 64-byte row segments, rows and columns clipped by the hardware).
+//                               store per chunk (full 64-byte row segments, rows and columns clipped by the hardware);
+//                               with one CTA per 256-wide tile (short-K problems, where the epilogue sets the pace) two
+//                               chunks share a 128-byte-swizzled box and one store.
 // The two accumulator buffers let the epilogue of tile i overlap the main loop of tile i+1.
 // Every mbarrier wait is bounded; on a timeout the role records it in the status word, raises the
 // block's abort flag and all roles fall through to the common exit, where tensor memory is freed.
