@@ -970,7 +970,7 @@ def run_reference(case, args, rank, world):
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": case.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # =================================================================================================== GPU arm
@@ -1185,14 +1185,29 @@ def run_ours(case, args, rank, world, local_rank):
                             "this run (configs.flux_fp8); the whole forward against the blended peak is in forward_roofline")
         line["roofline"] = roof
         line["cpu_baseline"] = time_cpu(case, min(case.tokens, CPU_ROWS), 3, 1)
-        print(json.dumps(line), flush=True)
+        emit(line)
     replicas.shutdown()
 
 
 DEFAULT_CASE = "flux_forward"
 
 
+# The process's standard output carries exactly one thing, the JSON line: file descriptor 1 is pointed at standard error for
+# the whole run (libraries such as NCCL print their banner to it), and the line goes to the descriptor saved here.
+_RESULT_FD = None
+
+
+def emit(line):
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def main():
+    global _RESULT_FD
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -1211,6 +1226,9 @@ def main():
     ap.add_argument("--no-dependent-launch", action="store_true",
                     help="launch the kernels as ordinary stream-ordered kernels (see lyraq_debug_set_dependent_launch)")
     args = ap.parse_args()
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
