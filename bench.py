@@ -246,7 +246,7 @@ class Int8Sdxl:
         self.gemm_bytes = T * self.K + self.N * self.K + 2.0 * T * self.N + 4.0 * (T + self.N) + 2.0 * self.N
         self.timed_work = [self.gemm_bytes]
         self.roof = {"bound": "hbm", "unit": "GB/s", "kernel": "gemm_tcgen05_kernel<i8> (1 launch per step)"}
-        self.traffic = 39.7e6 if T == 8192 else None  # profiles/gemm_tcgen05_int8_sdxl.md (most of the output is still in L2)
+        self.traffic = 33.6e6 if T == 8192 else None  # profiles/gemm_tcgen05_int8_sdxl.md (most of the output is still in L2)
 
     @staticmethod
     def _inputs(rows, k, n):
