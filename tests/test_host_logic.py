@@ -104,3 +104,24 @@ def test_unbuilt_quant_levels_are_refused_by_name():
             flux_blocks.FluxTransformerBlockOp("bf16", 3072, 24, 128, 6, level)
     with pytest.raises(NotImplementedError):
         flux_blocks.FluxSingleTransformerBlockOp()            # the reference's default arguments
+
+
+def test_bench_reference_arm_prints_exactly_one_json_line(tmp_path):
+    """What reads bench.py's output takes its standard output as one JSON line: nothing else may be written there (progress
+    and libraries' banners go to standard error).  The reference arm runs on the host cores, so this needs no GPU."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--case", "adaln_quant", "--steps", "1", "--warmup", "0"],
+                       capture_output=True, text=True, timeout=300, cwd=root)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = r.stdout.splitlines()
+    assert len(lines) == 1, lines
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["n_gpus"] == 1 and line["steps"] == 1
+    for key in ("metric", "value", "unit", "ms_per_step", "higher_is_better", "config", "e2e", "cpu_baseline"):
+        assert key in line, key
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
