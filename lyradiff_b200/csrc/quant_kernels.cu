@@ -373,6 +373,7 @@ template<typename K> static int launch_row_variant(K kernel, const RowParams& p,
 
 // Most 16-byte vectors a thread may hold before the team is doubled (4 or 6; sweepable through the debug hook).
 static int g_row_max_vpt = 6;
+static int g_adaln3072_on = 1;   // test hook: 0 sends AdaLN over rows of 3072 through the general row kernel
 
 // Picks the team size and launches.  dim is a multiple of 8 and <= 16384.  The smallest team (32..256 threads) that
 // keeps at most six 16-byte vectors per thread is used, so narrow rows need no cross-warp reduction and every thread
@@ -554,7 +555,7 @@ template<typename T, bool HAS_Y, bool HAS_B, bool HAS_Q8> static int launch_adal
 // so it steps aside when the debug hook has changed that shape.
 template<typename T> static bool adaln_fast_path(const RowParams& p, cudaStream_t stream, int& status)
 {
-    if (p.dim != 3072 || p.pre != nullptr || g_row_max_vpt != 6 || (p.qf8 != nullptr && p.f8_invert == 0)) {
+    if (g_adaln3072_on == 0 || p.dim != 3072 || p.pre != nullptr || g_row_max_vpt != 6 || (p.qf8 != nullptr && p.f8_invert == 0)) {
         return false;
     }
     if (p.q8 != nullptr) {
@@ -816,6 +817,12 @@ int lyraq_debug_set_row_vectors_per_thread(int max_vpt)
         return LYRAQ_ERR_INVALID_ARG;
     }
     g_row_max_vpt = max_vpt;
+    return LYRAQ_OK;
+}
+
+int lyraq_debug_set_adaln_row_kernel(int on)
+{
+    g_adaln3072_on = on != 0;
     return LYRAQ_OK;
 }
 

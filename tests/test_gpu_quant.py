@@ -271,6 +271,54 @@ def test_adaln_two_e4m3_outputs_equal_two_single_passes(ops):
     assert_bit_equal(qb2, rb.cpu())
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("b,s", [(1, 1), (1, 7), (2, 37), (3, 8), (1, 4608 + 3)])
+def test_adaln_3072_row_kernel_gives_the_general_kernel_bytes(ops, dtype, b, s):
+    """Rows of 3072 with a quantized output take a kernel of their own (one warp per row).  It sums in the general row
+    kernel's order, so every output form must be byte-identical to the general kernel's: y, the e4m3 codes of one or
+    two scales, and the dynamically scaled int8 codes with their per-token scales.  Row counts cover a lone row, a
+    block that is not full (8 rows per block) and the FLUX sequence plus a ragged tail; b > 1 covers the per-batch
+    scale / shift rows."""
+    from lyradiff_b200 import _lib
+
+    a = workloads.adaln_input(b=b, s=s, d=3072, seed=500 + b * 10 + s, dtype=dtype)
+    xd, sc, sh = cu(a["x"]), cu(a["scale"]), cu(a["shift"])
+    fa, fb = cu(torch.tensor([0.017])), cu(torch.tensor([0.031]))
+    rows = b * s
+
+    def run():
+        out = {}
+        for form in ("y+e4m3", "e4m3", "y+e4m3x2", "e4m3x2", "y+s8+e4m3", "s8"):
+            y = torch.full((b, s, 3072), float("nan"), dtype=dtype, device="cuda") if form.startswith("y") else None
+            qa = torch.zeros(rows, 3072, dtype=torch.uint8, device="cuda")
+            qb = torch.zeros_like(qa)
+            q8 = torch.zeros(rows, 3072, dtype=torch.int8, device="cuda")
+            s8 = torch.zeros(rows, dtype=torch.float32, device="cuda")
+            if "x2" in form:
+                ops.adaln_quant_fp8x2(y, qa, fa, qb, fb, xd, sc, sh)
+            elif "s8" in form:
+                if "e4m3" in form:
+                    ops.invoke_layer_norm_with_shift_and_scale(y, xd, sc, sh, 1e-6, q8=q8, q8_scale=s8, qf8=qa, f8_scale=fa)
+                else:
+                    ops.invoke_layer_norm_with_shift_and_scale(y, xd, sc, sh, 1e-6, q8=q8, q8_scale=s8)
+            else:
+                ops.invoke_layer_norm_with_shift_and_scale(y, xd, sc, sh, 1e-6, qf8=qa, f8_scale=fa)
+            check_status()
+            out[form] = [t.cpu() for t in (y, qa, qb, q8, s8) if t is not None]
+        return out
+
+    L = _lib.lib()
+    own = run()
+    assert L.lyraq_debug_set_adaln_row_kernel(0) == 0
+    try:
+        general = run()
+    finally:
+        L.lyraq_debug_set_adaln_row_kernel(1)
+    for form, tensors in own.items():
+        for i, (t, g) in enumerate(zip(tensors, general[form])):
+            assert t.dtype == g.dtype and torch.equal(t.view(torch.uint8), g.view(torch.uint8)), (form, i)
+
+
 def test_adaln_golden(ops, golden):
     z = golden("adaln")
     b, s, d = z["x"].shape
