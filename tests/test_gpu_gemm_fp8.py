@@ -109,7 +109,7 @@ def test_quantize_then_gemm_matches_unquantized_linear(ops):
 
 @pytest.mark.parametrize("name,k,n,gelu,residual", workloads.FLUX_FP8_LINEARS)
 def test_full_size_flux_linears(ops, name, k, n, gelu, residual):
-    """BASELINE configuration 2 at full size (M=4608): a strided sample of rows against the oracle, and the
+    """The FLUX FP8 linears at full size (M=4608): a strided sample of rows against the oracle, and the
     row-checksum property sum_n Y[m,n] == s * X[m,:] . sum_n W[n,:] (fp32 output, no epilogue)."""
     m = workloads.FLUX_TOKENS
     f = workloads.fp8_linear(m, k, n, seed=7, with_bias=True, with_residual=residual)

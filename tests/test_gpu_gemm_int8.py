@@ -128,7 +128,7 @@ def test_smoothquant_linear_end_to_end_small(ops):
 
 
 def test_full_size_config1(ops):
-    """BASELINE configuration 1 (M=8192, K=640, N=5120): accumulators checked bit-exactly on a strided sample
+    """The SDXL GEGLU feed-forward linear at full size (M=8192, K=640, N=5120): accumulators checked bit-exactly on a strided sample
     of rows and columns against the oracle, plus two size-independent properties: linearity in A
     (acc(A) + acc(-A) == 0) and a column checksum (sum_n acc[m,n] == A[m,:] . sum_n B[n,:])."""
     wl = workloads.int8_smoothquant_linear(seed=0)

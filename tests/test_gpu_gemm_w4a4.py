@@ -123,7 +123,7 @@ def test_quantize_then_gemm_end_to_end(ops):
 
 
 def test_full_size_config3(ops):
-    """BASELINE configuration 3 (M=4608, K=3072, N=21504): sampled rows bit-exact against the oracle, and the
+    """The fused FLUX W4A4 projection at full size (M=4608, K=3072, N=21504): sampled rows bit-exact against the oracle, and the
     exact-integer property with unit scales on the full problem via a column checksum."""
     w = workloads.w4a4_linear(seed=0)
     pa, sa, qa = quant.int4_quant_g64(w["x"], w["smooth"])

@@ -381,7 +381,7 @@ def test_ln_geglu_golden(ops, golden):
 
 
 def test_adaln_full_size_properties(ops):
-    """BASELINE configuration 4 at full size: dequantized int8 reproduces y within half a step per token,
+    """The FLUX AdaLN + quantize at full size ([4608, 3072]): dequantized int8 reproduces y within half a step per token,
     and the e4m3 output decodes to y within e4m3 spacing."""
     a = workloads.adaln_input(b=1, s=4608, d=3072, seed=0)
     xd, sc, sh = cu(a["x"]), cu(a["scale"]), cu(a["shift"])
