@@ -538,35 +538,21 @@ int launch_attention(void* out, int out_dtype, size_t out_ld, const float* out_s
     }
     const unsigned grid = (unsigned)(batch * (size_t)heads * (size_t)p.q_blocks);
     if (dtype == LYRAQ_BF16) {
-        static bool attr_set_dev[64] = {};
-        int         dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
-            return LYRAQ_ERR_CUDA;
-        }
-        bool& attr_set = attr_set_dev[dev];
-        if (!attr_set) {
-            const cudaError_t e = cudaFuncSetAttribute(attn::attention_fwd_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::kSmemTotal);
-            if (e != cudaSuccess) {
-                return cuda_status(e, "cudaFuncSetAttribute(attention_fwd_kernel<bf16>)");
-            }
-            attr_set = true;
+        static bool smem_raised[64] = {};
+        const int   attr_st = raise_dynamic_smem_once(attn::attention_fwd_kernel<__nv_bfloat16>, (int)attn::kSmemTotal, smem_raised,
+                                                      "cudaFuncSetAttribute(attention_fwd_kernel<bf16>)");
+        if (attr_st != LYRAQ_OK) {
+            return attr_st;
         }
         return cuda_status(launch_kernel(attn::attention_fwd_kernel<__nv_bfloat16>, grid, (unsigned)attn::kThreads, (size_t)attn::kSmemTotal,
                                          stream, 1u, tm, p),
                            "cudaLaunchKernelEx(attention_fwd_kernel<bf16>)");
     }
-    static bool attr_set_h_dev[64] = {};
-    int         dev_h = 0;
-    if (cudaGetDevice(&dev_h) != cudaSuccess || dev_h < 0 || dev_h >= 64) {
-        return LYRAQ_ERR_CUDA;
-    }
-    bool& attr_set_h = attr_set_h_dev[dev_h];
-    if (!attr_set_h) {
-        const cudaError_t e = cudaFuncSetAttribute(attn::attention_fwd_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::kSmemTotal);
-        if (e != cudaSuccess) {
-            return cuda_status(e, "cudaFuncSetAttribute(attention_fwd_kernel<f16>)");
-        }
-        attr_set_h = true;
+    static bool smem_raised_h[64] = {};
+    const int   attr_st = raise_dynamic_smem_once(attn::attention_fwd_kernel<__half>, (int)attn::kSmemTotal, smem_raised_h,
+                                                  "cudaFuncSetAttribute(attention_fwd_kernel<f16>)");
+    if (attr_st != LYRAQ_OK) {
+        return attr_st;
     }
     return cuda_status(launch_kernel(attn::attention_fwd_kernel<__half>, grid, (unsigned)attn::kThreads, (size_t)attn::kSmemTotal, stream,
                                      1u, tm, p),

@@ -413,6 +413,25 @@ inline int cuda_status(cudaError_t e, const char* where = "cuda call")
 
 inline int launch_status() { return cuda_status(cudaGetLastError(), "kernel launch"); }
 
+// Raises a kernel's dynamic shared-memory limit the first time its call site launches it on the current device: the
+// attribute stays with the function on that device, so launches after the first skip the driver call.  `done` is the call
+// site's own per-device record.
+template<typename Kern> inline int raise_dynamic_smem_once(Kern kern, int bytes, bool (&done)[64], const char* what)
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        return LYRAQ_ERR_CUDA;
+    }
+    if (!done[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+        if (e != cudaSuccess) {
+            return cuda_status(e, what);
+        }
+        done[dev] = true;
+    }
+    return LYRAQ_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Programmatic dependent launch.  Every kernel of the library tells the scheduler at its start that the next kernel
 // of the stream may begin launching (grid_launch_dependents), and waits for the kernels before it to have completed,

@@ -1202,17 +1202,11 @@ static int launch_gemm(const void* A, const void* B, GemmParams p, int sms, cuda
     const int  grid  = (int)(tiles < units ? tiles : units) * CTAS;
     auto       kern  = gemm_tcgen05_kernel<KIND, BLOCK_N, CTAS, RES>;
     // the dynamic shared-memory limit of this instance is raised once per device, not per launch
-    static bool attr_set[64] = {};
-    int         dev         = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
-        return LYRAQ_ERR_CUDA;
-    }
-    if (!attr_set[dev]) {
-        const cudaError_t attr_err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
-        if (attr_err != cudaSuccess) {
-            return cuda_status(attr_err, "cudaFuncSetAttribute(gemm_tcgen05_kernel, dynamic shared memory)");
-        }
-        attr_set[dev] = true;
+    static bool smem_raised[64] = {};
+    const int   attr_st = raise_dynamic_smem_once(kern, (int)S::kTotal, smem_raised,
+                                                  "cudaFuncSetAttribute(gemm_tcgen05_kernel, dynamic shared memory)");
+    if (attr_st != LYRAQ_OK) {
+        return attr_st;
     }
     return cuda_status(launch_kernel(kern, (unsigned)grid, (unsigned)kThreads, (size_t)S::kTotal, stream, (unsigned)CTAS, ta, tb, tc, p),
                        "cudaLaunchKernelEx(gemm_tcgen05_kernel)");

@@ -771,10 +771,11 @@ extern "C" int lyraq_gemm_w4a4(const uint8_t* A, const uint8_t* B, const float* 
     }
     const long tiles = (long)p.m_tiles * p.n_tiles;
     const int  grid  = (int)(tiles < sms ? tiles : sms);
-    const cudaError_t attr_err =
-        cudaFuncSetAttribute(w4::gemm_w4a4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, w4::kSmemTotal);
-    if (attr_err != cudaSuccess) {
-        return cuda_status(attr_err, "cudaFuncSetAttribute(gemm_w4a4_kernel, dynamic shared memory)");
+    static bool smem_raised[64] = {};
+    st = raise_dynamic_smem_once(w4::gemm_w4a4_kernel, (int)w4::kSmemTotal, smem_raised,
+                                 "cudaFuncSetAttribute(gemm_w4a4_kernel, dynamic shared memory)");
+    if (st != LYRAQ_OK) {
+        return st;
     }
     return cuda_status(launch_kernel(w4::gemm_w4a4_kernel, (unsigned)grid, (unsigned)w4::kThreads, (size_t)w4::kSmemTotal,
                                      (cudaStream_t)stream, 1u, ta, tb, p),

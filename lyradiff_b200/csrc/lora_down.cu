@@ -281,19 +281,21 @@ static int launch_lora_down_impl(float* act, const void* x, const void* down, in
     }
     const unsigned grid = (unsigned)((m + lora::kRows - 1) / lora::kRows);
     if (fused) {
-        const cudaError_t attr_err =
-            cudaFuncSetAttribute(lora::lora_down_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lora::kSmemTotal);
-        if (attr_err != cudaSuccess) {
-            return cuda_status(attr_err, "cudaFuncSetAttribute(lora_down_kernel<fused>, dynamic shared memory)");
+        static bool smem_raised_fused[64] = {};
+        st = raise_dynamic_smem_once(lora::lora_down_kernel<true>, (int)lora::kSmemTotal, smem_raised_fused,
+                                     "cudaFuncSetAttribute(lora_down_kernel<fused>, dynamic shared memory)");
+        if (st != LYRAQ_OK) {
+            return st;
         }
         return cuda_status(launch_kernel(lora::lora_down_kernel<true>, grid, (unsigned)lora::kThreadsFused, (size_t)lora::kSmemTotal,
                                          stream, 1u, tx, td, p),
                            "cudaLaunchKernelEx(lora_down_kernel<fused>)");
     }
-    const cudaError_t attr_err =
-        cudaFuncSetAttribute(lora::lora_down_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lora::kSmemTotal);
-    if (attr_err != cudaSuccess) {
-        return cuda_status(attr_err, "cudaFuncSetAttribute(lora_down_kernel, dynamic shared memory)");
+    static bool smem_raised[64] = {};
+    st = raise_dynamic_smem_once(lora::lora_down_kernel<false>, (int)lora::kSmemTotal, smem_raised,
+                                 "cudaFuncSetAttribute(lora_down_kernel, dynamic shared memory)");
+    if (st != LYRAQ_OK) {
+        return st;
     }
     return cuda_status(launch_kernel(lora::lora_down_kernel<false>, grid, (unsigned)lora::kThreads, (size_t)lora::kSmemTotal, stream, 1u,
                                      tx, td, p),
