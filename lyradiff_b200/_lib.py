@@ -23,7 +23,7 @@ SIGNATURES = {
     "lyraq_debug_attention_wait_test": (c_int, [c_int, ctypes.c_uint]),
     "lyraq_last_cuda_error": (ctypes.c_char_p, []),
     "lyraq_debug_set_row_vectors_per_thread": (c_int, [c_int]),
-    "lyraq_debug_set_adaln_row_kernel": (c_int, [c_int]),
+    "lyraq_debug_set_special_row_kernels": (c_int, [c_int]),
     "lyraq_quant_int8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_void_p]),
     "lyraq_quant_fp8": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_size_t, c_void_p]),
     "lyraq_fp8_amax_scale": (c_int, [c_void_p, c_void_p, c_int, c_size_t, c_void_p]),

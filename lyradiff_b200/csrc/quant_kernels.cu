@@ -80,6 +80,36 @@ template<bool IS_MAX> __device__ __forceinline__ float team_reduce(float v, int 
     return r;
 }
 
+// Bias + GEGLU on eight columns: h and g are the value and gate halves of the projection at columns c .. c + 7, bias
+// (or null) has 2 * dim entries.  Returns T(T(h + b_h) * T(g' * T(cdf(g')))) with g' = T(g + b_g): the products and the
+// cube in T, the cdf in fp32 and rounded to T, as GeluActivation<half2> does in the reference
+// (src/lyradiff/kernels/quant_kernels/ffn_kernels_int8.cu:189-290).  Both GEGLU kernels below call this, so they
+// leave the same bits.
+template<typename T> __device__ __forceinline__ Vec16 geglu_vec(Vec16 h, Vec16 g, const T* bias, int dim, int c)
+{
+    using P2 = Pair<T>;
+    if (bias != nullptr) {
+        const Vec16 bh = ld_nc_16_keep(bias + c);
+        const Vec16 bg = ld_nc_16_keep(bias + dim + c);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            h.w[j] = P2::add(h.w[j], bh.w[j]);
+            g.w[j] = P2::add(g.w[j], bg.w[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t cube = P2::mul(g.w[j], P2::mul(g.w[j], g.w[j]));
+        const float2   gf   = P2::to_f32(g.w[j]);
+        const float2   cf   = P2::to_f32(cube);
+        const float    c0   = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (gf.x + 0.044715f * cf.x)));
+        const float    c1   = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (gf.y + 0.044715f * cf.y)));
+        const uint32_t act  = P2::mul(g.w[j], P2::from_f32(c0, c1));
+        h.w[j]              = P2::mul(h.w[j], act);
+    }
+    return h;
+}
+
 // The row lives in registers as fp32 (f[i][0..7] = the i-th 16-byte vector of this thread); every step the
 // reference evaluates in T is done on packed pairs with the type's native single-rounding add / multiply.
 template<typename T, int VPT, int MODE>
@@ -169,27 +199,7 @@ row_quant_kernel(const RowParams p)
                 }
             }
             if (MODE == ROW_GEGLU) {
-                Vec16 g = cur2[kSecond ? i : 0];
-                if (p.bias != nullptr) {
-                    const Vec16 bh = ld_nc_16_keep(reinterpret_cast<const T*>(p.bias) + c);
-                    const Vec16 bg = ld_nc_16_keep(reinterpret_cast<const T*>(p.bias) + p.dim + c);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        h.w[j] = P2::add(h.w[j], bh.w[j]);
-                        g.w[j] = P2::add(g.w[j], bg.w[j]);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    // GeluActivation<half2>: cube and products in T, the cdf in fp32 and rounded to T
-                    const uint32_t cube = P2::mul(g.w[j], P2::mul(g.w[j], g.w[j]));
-                    const float2   gf   = P2::to_f32(g.w[j]);
-                    const float2   cf   = P2::to_f32(cube);
-                    const float    c0   = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (gf.x + 0.044715f * cf.x)));
-                    const float    c1   = 0.5f * (1.0f + tanh_approx(0.7978845608028654f * (gf.y + 0.044715f * cf.y)));
-                    const uint32_t act  = P2::mul(g.w[j], P2::from_f32(c0, c1));
-                    h.w[j]              = P2::mul(h.w[j], act);
-                }
+                h = geglu_vec<T>(h, cur2[kSecond ? i : 0], reinterpret_cast<const T*>(p.bias), p.dim, c);
             }
             if ((MODE == ROW_PLAIN || MODE == ROW_GEGLU) && p.y != nullptr) {
                 st_16(reinterpret_cast<T*>(p.y) + row * (size_t)p.dim + c, h);
@@ -373,7 +383,7 @@ template<typename K> static int launch_row_variant(K kernel, const RowParams& p,
 
 // Most 16-byte vectors a thread may hold before the team is doubled (4 or 6; sweepable through the debug hook).
 static int g_row_max_vpt = 6;
-static int g_adaln3072_on = 1;   // test hook: 0 sends AdaLN over rows of 3072 through the general row kernel
+static int g_special_rows_on = 1;   // test hook: 0 sends every call through the general row kernel
 
 // Picks the team size and launches.  dim is a multiple of 8 and <= 16384.  The smallest team (32..256 threads) that
 // keeps at most six 16-byte vectors per thread is used, so narrow rows need no cross-warp reduction and every thread
@@ -555,7 +565,7 @@ template<typename T, bool HAS_Y, bool HAS_B, bool HAS_Q8> static int launch_adal
 // so it steps aside when the debug hook has changed that shape.
 template<typename T> static bool adaln_fast_path(const RowParams& p, cudaStream_t stream, int& status)
 {
-    if (g_adaln3072_on == 0 || p.dim != 3072 || p.pre != nullptr || g_row_max_vpt != 6 || (p.qf8 != nullptr && p.f8_invert == 0)) {
+    if (g_special_rows_on == 0 || p.dim != 3072 || p.pre != nullptr || g_row_max_vpt != 6 || (p.qf8 != nullptr && p.f8_invert == 0)) {
         return false;
     }
     if (p.q8 != nullptr) {
@@ -576,6 +586,71 @@ template<typename T> static bool adaln_fast_path(const RowParams& p, cudaStream_
     return true;
 }
 
+// Bias + GEGLU -> int8 with a static scale has no row statistic, so it needs no team and no row loop: this kernel gives
+// every thread GEGLU_UNITS independent 8-column vectors (consecutive threads take consecutive vectors; all loads go out
+// before the first is used), with more warps resident than the row kernel can afford.  The per-vector arithmetic is the
+// row kernel's (geglu_vec, the smoothing multiply, quant8_s8), so the bytes are the same.
+constexpr int GEGLU_UNITS = 2;
+template<typename T> __global__ void __launch_bounds__(256, 4) geglu_int8_flat_kernel(const RowParams p, uint32_t total)
+{
+    using P2 = Pair<T>;
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const uint32_t nvec  = (uint32_t)p.dim >> 3;
+    const uint32_t first = blockIdx.x * (256u * GEGLU_UNITS) + threadIdx.x;
+    const T*       x     = reinterpret_cast<const T*>(p.x);
+    Vec16          h[GEGLU_UNITS], g[GEGLU_UNITS];
+    uint32_t       row[GEGLU_UNITS], col[GEGLU_UNITS];
+#pragma unroll
+    for (int u = 0; u < GEGLU_UNITS; ++u) {
+        const uint32_t idx = first + (uint32_t)u * 256u;
+        row[u]             = idx / nvec;
+        col[u]             = (idx - row[u] * nvec) << 3;
+        if (idx < total) {
+            const T* xr = x + (size_t)row[u] * (size_t)p.in_cols + col[u];
+            h[u]        = ld_nc_16(xr);
+            g[u]        = ld_nc_16(xr + p.dim);
+        }
+    }
+    const float s8 = ld_f32(p.q8_scale);
+    const float r8 = 1.0f / s8;
+#pragma unroll
+    for (int u = 0; u < GEGLU_UNITS; ++u) {
+        if (first + (uint32_t)u * 256u < total) {
+            const Vec16 a = geglu_vec<T>(h[u], g[u], reinterpret_cast<const T*>(p.bias), p.dim, (int)col[u]);
+            float2      f[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                f[j] = P2::to_f32(a.w[j]);
+            }
+            if (p.pre != nullptr) {
+                const float4 p0 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + col[u]));
+                const float4 p1 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + col[u] + 4));
+                f[0] = mul_f32x2(f[0], make_float2(p0.x, p0.y));
+                f[1] = mul_f32x2(f[1], make_float2(p0.z, p0.w));
+                f[2] = mul_f32x2(f[2], make_float2(p1.x, p1.y));
+                f[3] = mul_f32x2(f[3], make_float2(p1.z, p1.w));
+            }
+            uint32_t w0, w1;
+            quant8_s8(f, s8, r8, w0, w1);
+            st_8(p.q8 + (size_t)row[u] * (size_t)p.dim + col[u], w0, w1);
+        }
+    }
+}
+
+template<typename T> static bool geglu_fast_path(const RowParams& p, cudaStream_t stream, int& status)
+{
+    const size_t total = p.rows * (size_t)(p.dim >> 3);
+    if (g_special_rows_on == 0 || p.q8 == nullptr || p.y != nullptr || p.qf8 != nullptr || p.qf8b != nullptr ||
+        p.scale_mode != LYRAQ_SCALE_PER_TENSOR || total >= (1ull << 31)) {
+        return false;
+    }
+    const unsigned grid = (unsigned)((total + 256u * GEGLU_UNITS - 1) / (256u * GEGLU_UNITS));
+    status = cuda_status(launch_kernel(geglu_int8_flat_kernel<T>, grid, 256u, (size_t)0, stream, 1u, p, (uint32_t)total),
+                         "cudaLaunchKernelEx(geglu_int8_flat_kernel)");
+    return true;
+}
+
 template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaStream_t stream)
 {
     if (p.dim <= 0 || (p.dim & 7) != 0 || p.dim > 16384) {
@@ -585,6 +660,13 @@ template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaSt
         int status = LYRAQ_OK;
         if ((dtype == LYRAQ_F16 && adaln_fast_path<__half>(p, stream, status)) ||
             (dtype == LYRAQ_BF16 && adaln_fast_path<__nv_bfloat16>(p, stream, status))) {
+            return status;
+        }
+    }
+    if (MODE == ROW_GEGLU) {
+        int status = LYRAQ_OK;
+        if ((dtype == LYRAQ_F16 && geglu_fast_path<__half>(p, stream, status)) ||
+            (dtype == LYRAQ_BF16 && geglu_fast_path<__nv_bfloat16>(p, stream, status))) {
             return status;
         }
     }
@@ -820,9 +902,9 @@ int lyraq_debug_set_row_vectors_per_thread(int max_vpt)
     return LYRAQ_OK;
 }
 
-int lyraq_debug_set_adaln_row_kernel(int on)
+int lyraq_debug_set_special_row_kernels(int on)
 {
-    g_adaln3072_on = on != 0;
+    g_special_rows_on = on != 0;
     return LYRAQ_OK;
 }
 

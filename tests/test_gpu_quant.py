@@ -309,11 +309,11 @@ def test_adaln_3072_row_kernel_gives_the_general_kernel_bytes(ops, dtype, b, s):
 
     L = _lib.lib()
     own = run()
-    assert L.lyraq_debug_set_adaln_row_kernel(0) == 0
+    assert L.lyraq_debug_set_special_row_kernels(0) == 0
     try:
         general = run()
     finally:
-        L.lyraq_debug_set_adaln_row_kernel(1)
+        L.lyraq_debug_set_special_row_kernels(1)
     for form, tensors in own.items():
         for i, (t, g) in enumerate(zip(tensors, general[form])):
             assert t.dtype == g.dtype and torch.equal(t.view(torch.uint8), g.view(torch.uint8)), (form, i)
