@@ -370,6 +370,42 @@ def test_geglu_int8_against_oracle(ops, dtype, rows, dim):
     _close(q, norms.geglu_int8(h, None, pre, s), frac=2e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,dim", [(1, 8), (9, 64), (33, 1288), (8192, 2560), (3, 16384)])
+def test_geglu_flat_kernel_gives_the_row_kernel_bytes(ops, dtype, rows, dim):
+    """Bias + GEGLU -> int8 has no row statistic and runs as a flat kernel over 8-column vectors; the general row kernel
+    does the same arithmetic per vector, so the two must agree byte for byte: with and without the bias and the smoothing
+    vector, from one vector to the SDXL feed-forward size (8192 x 2560), whose last block is partly idle, and the
+    widest row."""
+    from lyradiff_b200 import _lib
+
+    g = torch.Generator().manual_seed(rows * 5 + dim)
+    h = cu((torch.randn(rows, 2 * dim, generator=g) * 1.5).to(dtype))
+    b2 = cu((torch.randn(2 * dim, generator=g) * 0.1).to(dtype))
+    pre = cu((0.5 + torch.rand(dim, generator=g)).float())
+    s = cu(torch.tensor([0.02], dtype=torch.float32))   # small enough that some codes saturate
+
+    def run():
+        out = []
+        for bias, smooth in ((b2, pre), (None, pre), (b2, None), (None, None)):
+            q = torch.zeros(rows, dim, dtype=torch.int8, device="cuda")
+            ops.invoke_fused_add_bias_geglu_int8o(q, h, bias, smooth, s)
+            check_status()
+            out.append(q.cpu())
+        return out
+
+    L = _lib.lib()
+    flat = run()
+    assert L.lyraq_debug_set_special_row_kernels(0) == 0
+    try:
+        general = run()
+    finally:
+        L.lyraq_debug_set_special_row_kernels(1)
+    for i, (a, b) in enumerate(zip(flat, general)):
+        assert torch.equal(a, b), i
+    assert int((flat[0] == 127).sum()) > 0 or rows * dim < 1000
+
+
 def test_ln_geglu_golden(ops, golden):
     z = golden("ln_geglu")
     rows, dim = z["x"].shape
