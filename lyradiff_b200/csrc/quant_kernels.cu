@@ -651,6 +651,114 @@ template<typename T> static bool geglu_fast_path(const RowParams& p, cudaStream_
     return true;
 }
 
+// LayerNorm -> int8 (static scale, no residual) for rows of 320 or 640 columns, the widths of the SDXL transformer
+// blocks whose rows do not fill a warp's 16-byte vectors evenly (640 columns = 80 vectors = 2.5 per lane).  8 or 16
+// lanes own a row with exactly five vectors each, so a warp works on four or two rows at once with every lane busy, the
+// two reductions are xor-butterflies inside the lane group, and with no row loop state to carry twice as many warps are
+// resident as in the general kernel.  Same formulas as the general kernel (mean and variance in fp32, x_hat rounded to T,
+// T(T(gamma * x_hat) + beta), smoothing multiply, quant8_s8); only the order of the fp32 sums differs.
+template<typename T, int LANES_LOG2>
+__global__ void __launch_bounds__(256, 4) ln_int8_short_kernel(const RowParams p)
+{
+    using P2 = Pair<T>;
+    constexpr int VPL   = 5;
+    constexpr int LANES = 1 << LANES_LOG2;
+    constexpr int RPW   = 32 / LANES;  // rows per warp
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int    lane   = threadIdx.x & 31;
+    const int    sub    = lane & (LANES - 1);
+    const size_t stride = (size_t)gridDim.x * 8 * RPW;
+    const T*     gamma  = reinterpret_cast<const T*>(p.gamma);
+    const T*     beta   = reinterpret_cast<const T*>(p.beta);
+    const float  s8     = ld_f32(p.q8_scale);
+    const float  r8     = 1.0f / s8;
+    for (size_t wrow = ((size_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW; wrow < p.rows; wrow += stride) {
+        const size_t row  = wrow + (size_t)(lane >> LANES_LOG2);
+        const bool   live = row < p.rows;  // the shuffles below need every lane, so a lane without a row works on zeros
+        const T*     xr   = reinterpret_cast<const T*>(p.x) + row * (size_t)p.dim;
+        Vec16        v[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            if (live) {
+                v[i] = ld_nc_16(xr + ((sub + LANES * i) << 3));
+            } else {
+                v[i].w[0] = v[i].w[1] = v[i].w[2] = v[i].w[3] = 0u;
+            }
+        }
+        // the row stays packed in T (20 registers); each of the three passes converts on the fly
+        float2 sa = make_float2(0.0f, 0.0f), sb = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            sa = add_f32x2(sa, add_f32x2(P2::to_f32(v[i].w[0]), P2::to_f32(v[i].w[2])));
+            sb = add_f32x2(sb, add_f32x2(P2::to_f32(v[i].w[1]), P2::to_f32(v[i].w[3])));
+        }
+        float sum = (sa.x + sa.y) + (sb.x + sb.y);
+#pragma unroll
+        for (int m = LANES / 2; m > 0; m >>= 1) {
+            sum += __shfl_xor_sync(0xffffffffu, sum, m);
+        }
+        const float  mean = sum / (float)p.dim;
+        const float2 nm   = make_float2(-mean, -mean);
+        float2       qa   = make_float2(0.0f, 0.0f), qb = make_float2(0.0f, 0.0f);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const float2 d0 = add_f32x2(P2::to_f32(v[i].w[0]), nm), d2 = add_f32x2(P2::to_f32(v[i].w[2]), nm);
+            const float2 d1 = add_f32x2(P2::to_f32(v[i].w[1]), nm), d3 = add_f32x2(P2::to_f32(v[i].w[3]), nm);
+            qa              = fma_f32x2(d0, d0, fma_f32x2(d2, d2, qa));
+            qb              = fma_f32x2(d1, d1, fma_f32x2(d3, d3, qb));
+        }
+        float m2 = (qa.x + qa.y) + (qb.x + qb.y);
+#pragma unroll
+        for (int m = LANES / 2; m > 0; m >>= 1) {
+            m2 += __shfl_xor_sync(0xffffffffu, m2, m);
+        }
+        const float  var  = fmaxf(m2 / (float)p.dim, 0.0f);
+        const float  rstd = 1.0f / sqrtf(var + p.eps);
+        const float2 rs   = make_float2(rstd, rstd);
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            const int   c = (sub + LANES * i) << 3;
+            const Vec16 a = ld_nc_16_keep(gamma + c);
+            const Vec16 b = ld_nc_16_keep(beta + c);
+            float2      y[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2   xn = mul_f32x2(add_f32x2(P2::to_f32(v[i].w[j]), nm), rs);
+                const uint32_t xh = P2::from_f32(xn.x, xn.y);
+                y[j]              = P2::to_f32(P2::add(P2::mul(a.w[j], xh), b.w[j]));
+            }
+            if (p.pre != nullptr) {
+                const float4 p0 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + c));
+                const float4 p1 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + c + 4));
+                y[0] = mul_f32x2(y[0], make_float2(p0.x, p0.y));
+                y[1] = mul_f32x2(y[1], make_float2(p0.z, p0.w));
+                y[2] = mul_f32x2(y[2], make_float2(p1.x, p1.y));
+                y[3] = mul_f32x2(y[3], make_float2(p1.z, p1.w));
+            }
+            uint32_t w0, w1;
+            quant8_s8(y, s8, r8, w0, w1);
+            if (live) {
+                st_8(p.q8 + row * (size_t)p.dim + c, w0, w1);
+            }
+        }
+    }
+}
+
+template<typename T> static bool ln_fast_path(const RowParams& p, cudaStream_t stream, int& status)
+{
+    if (g_special_rows_on == 0 || (p.dim != 320 && p.dim != 640) || p.residual != nullptr || p.q8 == nullptr || p.y != nullptr ||
+        p.qf8 != nullptr || p.qf8b != nullptr || p.scale_mode != LYRAQ_SCALE_PER_TENSOR) {
+        return false;
+    }
+    if (p.dim == 640) {
+        status = launch_row_variant(ln_int8_short_kernel<T, 4>, p, (p.rows + 15) / 16, stream);
+    } else {
+        status = launch_row_variant(ln_int8_short_kernel<T, 3>, p, (p.rows + 31) / 32, stream);
+    }
+    return true;
+}
+
 template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaStream_t stream)
 {
     if (p.dim <= 0 || (p.dim & 7) != 0 || p.dim > 16384) {
@@ -660,6 +768,13 @@ template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaSt
         int status = LYRAQ_OK;
         if ((dtype == LYRAQ_F16 && adaln_fast_path<__half>(p, stream, status)) ||
             (dtype == LYRAQ_BF16 && adaln_fast_path<__nv_bfloat16>(p, stream, status))) {
+            return status;
+        }
+    }
+    if (MODE == ROW_LN) {
+        int status = LYRAQ_OK;
+        if ((dtype == LYRAQ_F16 && ln_fast_path<__half>(p, stream, status)) ||
+            (dtype == LYRAQ_BF16 && ln_fast_path<__nv_bfloat16>(p, stream, status))) {
             return status;
         }
     }

@@ -355,6 +355,37 @@ def test_layernorm_int8_against_oracle(ops, dtype, rows, dim):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,dim", [(1, 320), (1, 640), (33, 640), (35, 320), (8192, 640), (4099, 320)])
+def test_layernorm_int8_short_row_kernel(ops, dtype, rows, dim):
+    """Rows of 320 and 640 columns take a kernel in which 8 or 16 lanes own a row (a warp works on 4 or 2 rows at once).
+    Its arithmetic is the general row kernel's except for the order of the two fp32 sums, so against the oracle it is
+    held to the general kernel's tolerance, and against the general kernel itself to a tighter one; row counts that
+    leave a warp's last rows empty are included."""
+    from lyradiff_b200 import _lib
+
+    g = torch.Generator().manual_seed(rows + dim)
+    x = (torch.randn(rows, dim, generator=g) * 2.0 + 0.3).to(dtype)
+    gamma = (1.0 + 0.1 * torch.randn(dim, generator=g)).to(dtype)
+    beta = (0.1 * torch.randn(dim, generator=g)).to(dtype)
+    pre = (0.5 + torch.rand(dim, generator=g)).float()
+    s = torch.tensor([0.03], dtype=torch.float32)
+    L = _lib.lib()
+    for smooth in (pre, None):
+        q = torch.full((rows, dim), 77, dtype=torch.int8, device="cuda")
+        ops.invoke_layer_norm_int8o(q, cu(x), cu(gamma), cu(beta), cu(smooth), cu(s), 1e-5)
+        check_status()
+        if rows <= 64:
+            _close(q, norms.layernorm_int8(x, gamma, beta, smooth, s)[0], frac=max(1e-3, 2.0 / (rows * dim)))
+        assert L.lyraq_debug_set_special_row_kernels(0) == 0
+        try:
+            q_row = torch.full((rows, dim), 78, dtype=torch.int8, device="cuda")
+            ops.invoke_layer_norm_int8o(q_row, cu(x), cu(gamma), cu(beta), cu(smooth), cu(s), 1e-5)
+        finally:
+            L.lyraq_debug_set_special_row_kernels(1)
+        _close(q, q_row.cpu(), frac=max(1e-4, 2.0 / (rows * dim)))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("rows,dim", [(9, 64), (33, 1280), (8, 2560), (3, 5120)])
 def test_geglu_int8_against_oracle(ops, dtype, rows, dim):
     g = torch.Generator().manual_seed(rows * 3 + dim)
