@@ -745,6 +745,107 @@ __global__ void __launch_bounds__(256, 4) ln_int8_short_kernel(const RowParams p
     }
 }
 
+// The SmoothQuant int8 quantize (static, given per-token, or dynamic per-token scale) in the same short-row form.  The
+// maximum of a row does not depend on the order it is taken in and the rest is per element, so the bytes and the scales
+// are the general kernel's.
+template<typename T, int LANES_LOG2>
+__global__ void __launch_bounds__(256, 4) quant_int8_short_kernel(const RowParams p)
+{
+    using P2 = Pair<T>;
+    constexpr int VPL   = 5;
+    constexpr int LANES = 1 << LANES_LOG2;
+    constexpr int RPW   = 32 / LANES;
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int    lane    = threadIdx.x & 31;
+    const int    sub     = lane & (LANES - 1);
+    const size_t stride  = (size_t)gridDim.x * 8 * RPW;
+    const bool   dynamic = (p.scale_mode == LYRAQ_SCALE_PER_TOKEN_DYNAMIC);
+    for (size_t wrow = ((size_t)blockIdx.x * 8 + (threadIdx.x >> 5)) * RPW; wrow < p.rows; wrow += stride) {
+        const size_t row  = wrow + (size_t)(lane >> LANES_LOG2);
+        const bool   live = row < p.rows;
+        const T*     xr   = reinterpret_cast<const T*>(p.x) + row * (size_t)p.dim;
+        // the row stays packed in T (20 registers); the maximum pass and the quantize pass each convert a vector and apply
+        // the smoothing factors as they go
+        Vec16 v[VPL];
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            if (live) {
+                v[i] = ld_nc_16(xr + ((sub + LANES * i) << 3));
+            } else {
+                v[i].w[0] = v[i].w[1] = v[i].w[2] = v[i].w[3] = 0u;
+            }
+        }
+        auto smoothed = [&](int i, float2 (&g)[4]) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                g[j] = P2::to_f32(v[i].w[j]);
+            }
+            if (p.pre != nullptr) {
+                const int    c  = (sub + LANES * i) << 3;
+                const float4 p0 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + c));
+                const float4 p1 = ld_f32x4(reinterpret_cast<const float4*>(p.pre + c + 4));
+                g[0] = mul_f32x2(g[0], make_float2(p0.x, p0.y));
+                g[1] = mul_f32x2(g[1], make_float2(p0.z, p0.w));
+                g[2] = mul_f32x2(g[2], make_float2(p1.x, p1.y));
+                g[3] = mul_f32x2(g[3], make_float2(p1.z, p1.w));
+            }
+        };
+        float s8;
+        if (dynamic) {
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                float2 g[4];
+                smoothed(i, g);
+                amax = fmaxf(amax, fmaxf(fmaxf(fmaxf(fabsf(g[0].x), fabsf(g[0].y)), fmaxf(fabsf(g[1].x), fabsf(g[1].y))),
+                                         fmaxf(fmaxf(fabsf(g[2].x), fabsf(g[2].y)), fmaxf(fabsf(g[3].x), fabsf(g[3].y)))));
+            }
+#pragma unroll
+            for (int m = LANES / 2; m > 0; m >>= 1) {
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+            }
+            s8 = (amax == 0.0f) ? 1.0f : amax / 127.0f;
+            if (live && sub == 0) {
+                p.q8_scale[row] = s8;
+            }
+        } else if (p.scale_mode == LYRAQ_SCALE_PER_TOKEN) {
+            s8 = live ? ld_f32(p.q8_scale + row) : 1.0f;
+        } else {
+            s8 = ld_f32(p.q8_scale);
+        }
+        const float r8 = 1.0f / s8;
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) {
+            float2 g[4];
+            smoothed(i, g);
+            uint32_t w0, w1;
+            if (dynamic) {
+                quant8_s8_inrange(g, s8, r8, w0, w1);
+            } else {
+                quant8_s8(g, s8, r8, w0, w1);
+            }
+            if (live) {
+                st_8(p.q8 + row * (size_t)p.dim + ((sub + LANES * i) << 3), w0, w1);
+            }
+        }
+    }
+}
+
+template<typename T> static bool quant_fast_path(const RowParams& p, cudaStream_t stream, int& status)
+{
+    if (g_special_rows_on == 0 || (p.dim != 320 && p.dim != 640) || p.q8 == nullptr || p.y != nullptr || p.qf8 != nullptr ||
+        p.qf8b != nullptr) {
+        return false;
+    }
+    if (p.dim == 640) {
+        status = launch_row_variant(quant_int8_short_kernel<T, 4>, p, (p.rows + 15) / 16, stream);
+    } else {
+        status = launch_row_variant(quant_int8_short_kernel<T, 3>, p, (p.rows + 31) / 32, stream);
+    }
+    return true;
+}
+
 template<typename T> static bool ln_fast_path(const RowParams& p, cudaStream_t stream, int& status)
 {
     if (g_special_rows_on == 0 || (p.dim != 320 && p.dim != 640) || p.residual != nullptr || p.q8 == nullptr || p.y != nullptr ||
@@ -768,6 +869,13 @@ template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaSt
         int status = LYRAQ_OK;
         if ((dtype == LYRAQ_F16 && adaln_fast_path<__half>(p, stream, status)) ||
             (dtype == LYRAQ_BF16 && adaln_fast_path<__nv_bfloat16>(p, stream, status))) {
+            return status;
+        }
+    }
+    if (MODE == ROW_PLAIN) {
+        int status = LYRAQ_OK;
+        if ((dtype == LYRAQ_F16 && quant_fast_path<__half>(p, stream, status)) ||
+            (dtype == LYRAQ_BF16 && quant_fast_path<__nv_bfloat16>(p, stream, status))) {
             return status;
         }
     }

@@ -25,7 +25,8 @@ def _x(rows, dim, dtype, seed, outliers=True):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("rows,dim", [(1, 8), (7, 64), (129, 640), (33, 3072), (5, 5120), (3, 16384), (260, 1280)])
+@pytest.mark.parametrize("rows,dim", [(1, 8), (7, 64), (129, 640), (33, 3072), (5, 5120), (3, 16384), (260, 1280), (1, 640),
+                                      (35, 320), (4099, 640)])
 def test_int8_quant_all_scale_modes_bit_exact(ops, dtype, rows, dim):
     x, pre = _x(rows, dim, dtype, seed=rows * 31 + dim)
     xd, pred = cu(x), cu(pre)
