@@ -651,13 +651,13 @@ template<typename T> static bool geglu_fast_path(const RowParams& p, cudaStream_
     return true;
 }
 
-// LayerNorm -> int8 (static scale, no residual) for rows of 320 or 640 columns, the widths of the SDXL transformer
-// blocks whose rows do not fill a warp's 16-byte vectors evenly (640 columns = 80 vectors = 2.5 per lane).  8 or 16
-// lanes own a row with exactly five vectors each, so a warp works on four or two rows at once with every lane busy, the
+// LayerNorm -> int8 (static scale; optionally x + residual + bias first, with the sum stored) for rows of 320, 640 or 1280 columns, the widths of the SDXL and SD 1.5
+// transformer blocks (640 columns = 80 vectors = 2.5 per lane of a warp: the general kernel leaves lanes idle).  8, 16 or
+// 32 lanes own a row with exactly five vectors each, so a warp works on four, two or one rows at once with every lane busy, the
 // two reductions are xor-butterflies inside the lane group, and with no row loop state to carry twice as many warps are
 // resident as in the general kernel.  Same formulas as the general kernel (mean and variance in fp32, x_hat rounded to T,
 // T(T(gamma * x_hat) + beta), smoothing multiply, quant8_s8); only the order of the fp32 sums differs.
-template<typename T, int LANES_LOG2>
+template<typename T, int LANES_LOG2, bool HAS_RES>
 __global__ void __launch_bounds__(256, 4) ln_int8_short_kernel(const RowParams p)
 {
     using P2 = Pair<T>;
@@ -684,6 +684,37 @@ __global__ void __launch_bounds__(256, 4) ln_int8_short_kernel(const RowParams p
                 v[i] = ld_nc_16(xr + ((sub + LANES * i) << 3));
             } else {
                 v[i].w[0] = v[i].w[1] = v[i].w[2] = v[i].w[3] = 0u;
+            }
+        }
+        if (HAS_RES) {
+            // h = T(T(x + residual) + bias), stored as the block's new hidden state and normalised in place of x
+            const T* rr = reinterpret_cast<const T*>(p.residual) + row * (size_t)p.dim;
+            Vec16    r[VPL];
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                if (live) {
+                    r[i] = ld_nc_16(rr + ((sub + LANES * i) << 3));
+                } else {
+                    r[i].w[0] = r[i].w[1] = r[i].w[2] = r[i].w[3] = 0u;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < VPL; ++i) {
+                const int c = (sub + LANES * i) << 3;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    v[i].w[j] = P2::add(v[i].w[j], r[i].w[j]);
+                }
+                if (p.bias != nullptr) {
+                    const Vec16 bv = ld_nc_16_keep(reinterpret_cast<const T*>(p.bias) + c);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        v[i].w[j] = P2::add(v[i].w[j], bv.w[j]);
+                    }
+                }
+                if (live && p.sum_out != nullptr) {
+                    st_16(reinterpret_cast<T*>(p.sum_out) + row * (size_t)p.dim + c, v[i]);
+                }
             }
         }
         // the row stays packed in T (20 registers); each of the three passes converts on the fly
@@ -834,11 +865,13 @@ __global__ void __launch_bounds__(256, 4) quant_int8_short_kernel(const RowParam
 
 template<typename T> static bool quant_fast_path(const RowParams& p, cudaStream_t stream, int& status)
 {
-    if (g_special_rows_on == 0 || (p.dim != 320 && p.dim != 640) || p.q8 == nullptr || p.y != nullptr || p.qf8 != nullptr ||
-        p.qf8b != nullptr) {
+    if (g_special_rows_on == 0 || (p.dim != 320 && p.dim != 640 && p.dim != 1280) || p.q8 == nullptr || p.y != nullptr ||
+        p.qf8 != nullptr || p.qf8b != nullptr) {
         return false;
     }
-    if (p.dim == 640) {
+    if (p.dim == 1280) {
+        status = launch_row_variant(quant_int8_short_kernel<T, 5>, p, (p.rows + 7) / 8, stream);
+    } else if (p.dim == 640) {
         status = launch_row_variant(quant_int8_short_kernel<T, 4>, p, (p.rows + 15) / 16, stream);
     } else {
         status = launch_row_variant(quant_int8_short_kernel<T, 3>, p, (p.rows + 31) / 32, stream);
@@ -848,14 +881,20 @@ template<typename T> static bool quant_fast_path(const RowParams& p, cudaStream_
 
 template<typename T> static bool ln_fast_path(const RowParams& p, cudaStream_t stream, int& status)
 {
-    if (g_special_rows_on == 0 || (p.dim != 320 && p.dim != 640) || p.residual != nullptr || p.q8 == nullptr || p.y != nullptr ||
+    if (g_special_rows_on == 0 || (p.dim != 320 && p.dim != 640 && p.dim != 1280) || p.q8 == nullptr || p.y != nullptr ||
         p.qf8 != nullptr || p.qf8b != nullptr || p.scale_mode != LYRAQ_SCALE_PER_TENSOR) {
         return false;
     }
-    if (p.dim == 640) {
-        status = launch_row_variant(ln_int8_short_kernel<T, 4>, p, (p.rows + 15) / 16, stream);
+    const bool res = p.residual != nullptr;
+    if (p.dim == 1280) {
+        status = res ? launch_row_variant(ln_int8_short_kernel<T, 5, true>, p, (p.rows + 7) / 8, stream)
+                     : launch_row_variant(ln_int8_short_kernel<T, 5, false>, p, (p.rows + 7) / 8, stream);
+    } else if (p.dim == 640) {
+        status = res ? launch_row_variant(ln_int8_short_kernel<T, 4, true>, p, (p.rows + 15) / 16, stream)
+                     : launch_row_variant(ln_int8_short_kernel<T, 4, false>, p, (p.rows + 15) / 16, stream);
     } else {
-        status = launch_row_variant(ln_int8_short_kernel<T, 3>, p, (p.rows + 31) / 32, stream);
+        status = res ? launch_row_variant(ln_int8_short_kernel<T, 3, true>, p, (p.rows + 31) / 32, stream)
+                     : launch_row_variant(ln_int8_short_kernel<T, 3, false>, p, (p.rows + 31) / 32, stream);
     }
     return true;
 }

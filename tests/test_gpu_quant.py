@@ -356,9 +356,10 @@ def test_layernorm_int8_against_oracle(ops, dtype, rows, dim):
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("rows,dim", [(1, 320), (1, 640), (33, 640), (35, 320), (8192, 640), (4099, 320)])
+@pytest.mark.parametrize("rows,dim", [(1, 320), (1, 640), (33, 640), (35, 320), (8192, 640), (4099, 320), (33, 1280), (2051, 1280)])
 def test_layernorm_int8_short_row_kernel(ops, dtype, rows, dim):
-    """Rows of 320 and 640 columns take a kernel in which 8 or 16 lanes own a row (a warp works on 4 or 2 rows at once).
+    """Rows of 320, 640 and 1280 columns take a kernel in which 8, 16 or 32 lanes own a row (a warp works on 4, 2 or 1 rows
+    at once).
     Its arithmetic is the general row kernel's except for the order of the two fp32 sums, so against the oracle it is
     held to the general kernel's tolerance, and against the general kernel itself to a tighter one; row counts that
     leave a warp's last rows empty are included."""
@@ -384,6 +385,24 @@ def test_layernorm_int8_short_row_kernel(ops, dtype, rows, dim):
         finally:
             L.lyraq_debug_set_special_row_kernels(1)
         _close(q, q_row.cpu(), frac=max(1e-4, 2.0 / (rows * dim)))
+    # the fused form: h = x + residual + bias is stored and normalised; the sum is element-wise, so it must be bit-equal
+    res = (torch.randn(rows, dim, generator=g) * 0.5).to(dtype)
+    bias = (torch.randn(dim, generator=g) * 0.1).to(dtype)
+    for b in (bias, None):
+        out = []
+        for on in (1, 0):
+            assert L.lyraq_debug_set_special_row_kernels(on) == 0
+            try:
+                q = torch.full((rows, dim), 79, dtype=torch.int8, device="cuda")
+                hsum = torch.full((rows, dim), float("nan"), dtype=dtype, device="cuda")
+                ops.invoke_layer_norm_int8o(q, cu(x), cu(gamma), cu(beta), cu(pre), cu(s), 1e-5, residual=cu(res), bias=cu(b),
+                                            sum_out=hsum)
+                check_status()
+                out.append((q.cpu(), hsum.cpu()))
+            finally:
+                L.lyraq_debug_set_special_row_kernels(1)
+        assert_bit_equal(out[0][1], out[1][1], "x + residual + bias")
+        _close(out[0][0], out[1][0], frac=max(1e-4, 2.0 / (rows * dim)))
 
 
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
