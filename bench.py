@@ -1172,7 +1172,7 @@ def run_ours(case, args, rank, world, local_rank):
             del case.op
             torch.cuda.empty_cache()
             subs = {}
-            for name in ("flux_fp8", "int8_sdxl", "w4a4", "adaln_quant", "attention"):
+            for name in ("flux_fp8", "int8_sdxl", "sdxl_ff", "w4a4", "adaln_quant", "attention"):
                 subs[name] = sub_record(name, dev, peaks, 20)
                 check_device()
             line["configs"] = subs
