@@ -101,10 +101,11 @@ LYRAQ_API int lyraq_debug_attention_wait_test(int skip_loads, unsigned int wait_
 LYRAQ_API int lyraq_debug_set_row_vectors_per_thread(int max_vpt);
 
 /* Test hook: some calls have kernels of their own beside the general row kernel -- AdaLN over rows of 3072 elements with
- * a quantized output (the FLUX form; one warp per row), bias + GEGLU -> int8 (no row statistic, so no row loop), and the
- * int8 quantize and LayerNorm -> int8 over rows of 320, 640 or 1280 columns (8, 16 or 32 lanes per row).  All give the general
- * kernel's bytes except the short-row LayerNorm, which differs in the order of its two fp32 sums.  on = 0 sends those calls through the general row kernel instead,
- * so that a test can compare the two; on = 1 (default) restores it.  Process-wide, not thread-safe.
+ * a quantized output (the FLUX form; one warp per row); bias + GEGLU -> int8 and the int8 quantize with a static or a
+ * given per-token scale (no row statistic, so no row loop); the dynamically scaled int8 quantize and LayerNorm -> int8
+ * over rows of 320, 640 or 1280 columns (8, 16 or 32 lanes per row).  All give the general kernel's bytes except the
+ * short-row LayerNorm, which differs in the order of its two fp32 sums.  on = 0 sends those calls through the general
+ * row kernel instead, so that a test can compare the two; on = 1 (default) restores it.  Process-wide, not thread-safe.
  * It has no counterpart in the reference (one kernel each: src/lyradiff/kernels/norms/layer_norm.cu:405-484,
  * src/lyradiff/kernels/quant_kernels/ffn_kernels_int8.cu:189-290). */
 LYRAQ_API int lyraq_debug_set_special_row_kernels(int on);

@@ -591,7 +591,8 @@ template<typename T> static bool adaln_fast_path(const RowParams& p, cudaStream_
 // before the first is used), with more warps resident than the row kernel can afford.  The per-vector arithmetic is the
 // row kernel's (geglu_vec, the smoothing multiply, quant8_s8), so the bytes are the same.
 constexpr int GEGLU_UNITS = 2;
-template<typename T> __global__ void __launch_bounds__(256, 4) geglu_int8_flat_kernel(const RowParams p, uint32_t total)
+template<typename T, bool GEGLU>
+__global__ void __launch_bounds__(256, 4) geglu_int8_flat_kernel(const RowParams p, uint32_t total)
 {
     using P2 = Pair<T>;
     grid_launch_dependents();
@@ -599,7 +600,7 @@ template<typename T> __global__ void __launch_bounds__(256, 4) geglu_int8_flat_k
     const uint32_t nvec  = (uint32_t)p.dim >> 3;
     const uint32_t first = blockIdx.x * (256u * GEGLU_UNITS) + threadIdx.x;
     const T*       x     = reinterpret_cast<const T*>(p.x);
-    Vec16          h[GEGLU_UNITS], g[GEGLU_UNITS];
+    Vec16          h[GEGLU_UNITS], g[GEGLU ? GEGLU_UNITS : 1];
     uint32_t       row[GEGLU_UNITS], col[GEGLU_UNITS];
 #pragma unroll
     for (int u = 0; u < GEGLU_UNITS; ++u) {
@@ -609,15 +610,19 @@ template<typename T> __global__ void __launch_bounds__(256, 4) geglu_int8_flat_k
         if (idx < total) {
             const T* xr = x + (size_t)row[u] * (size_t)p.in_cols + col[u];
             h[u]        = ld_nc_16(xr);
-            g[u]        = ld_nc_16(xr + p.dim);
+            if (GEGLU) {
+                g[GEGLU ? u : 0] = ld_nc_16(xr + p.dim);
+            }
         }
     }
-    const float s8 = ld_f32(p.q8_scale);
-    const float r8 = 1.0f / s8;
+    const bool  per_token = !GEGLU && p.scale_mode == LYRAQ_SCALE_PER_TOKEN;
+    const float s_tensor  = per_token ? 1.0f : ld_f32(p.q8_scale);
 #pragma unroll
     for (int u = 0; u < GEGLU_UNITS; ++u) {
         if (first + (uint32_t)u * 256u < total) {
-            const Vec16 a = geglu_vec<T>(h[u], g[u], reinterpret_cast<const T*>(p.bias), p.dim, (int)col[u]);
+            const float s8 = per_token ? ld_f32(p.q8_scale + row[u]) : s_tensor;
+            const float r8 = 1.0f / s8;
+            const Vec16 a  = GEGLU ? geglu_vec<T>(h[u], g[GEGLU ? u : 0], reinterpret_cast<const T*>(p.bias), p.dim, (int)col[u]) : h[u];
             float2      f[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -646,8 +651,23 @@ template<typename T> static bool geglu_fast_path(const RowParams& p, cudaStream_
         return false;
     }
     const unsigned grid = (unsigned)((total + 256u * GEGLU_UNITS - 1) / (256u * GEGLU_UNITS));
-    status = cuda_status(launch_kernel(geglu_int8_flat_kernel<T>, grid, 256u, (size_t)0, stream, 1u, p, (uint32_t)total),
+    status = cuda_status(launch_kernel(geglu_int8_flat_kernel<T, true>, grid, 256u, (size_t)0, stream, 1u, p, (uint32_t)total),
                          "cudaLaunchKernelEx(geglu_int8_flat_kernel)");
+    return true;
+}
+
+// The SmoothQuant quantize with a static or a given per-token scale has no row statistic either: the same flat kernel
+// without the GEGLU step, for any row width.
+template<typename T> static bool quant_flat_path(const RowParams& p, cudaStream_t stream, int& status)
+{
+    const size_t total = p.rows * (size_t)(p.dim >> 3);
+    if (g_special_rows_on == 0 || p.q8 == nullptr || p.y != nullptr || p.qf8 != nullptr || p.qf8b != nullptr ||
+        p.scale_mode == LYRAQ_SCALE_PER_TOKEN_DYNAMIC || total >= (1ull << 31)) {
+        return false;
+    }
+    const unsigned grid = (unsigned)((total + 256u * GEGLU_UNITS - 1) / (256u * GEGLU_UNITS));
+    status = cuda_status(launch_kernel(geglu_int8_flat_kernel<T, false>, grid, 256u, (size_t)0, stream, 1u, p, (uint32_t)total),
+                         "cudaLaunchKernelEx(geglu_int8_flat_kernel<plain>)");
     return true;
 }
 
@@ -913,6 +933,10 @@ template<int MODE> static int dispatch_row(int dtype, const RowParams& p, cudaSt
     }
     if (MODE == ROW_PLAIN) {
         int status = LYRAQ_OK;
+        if ((dtype == LYRAQ_F16 && quant_flat_path<__half>(p, stream, status)) ||
+            (dtype == LYRAQ_BF16 && quant_flat_path<__nv_bfloat16>(p, stream, status))) {
+            return status;
+        }
         if ((dtype == LYRAQ_F16 && quant_fast_path<__half>(p, stream, status)) ||
             (dtype == LYRAQ_BF16 && quant_fast_path<__nv_bfloat16>(p, stream, status))) {
             return status;

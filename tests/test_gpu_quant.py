@@ -52,6 +52,40 @@ def test_int8_quant_all_scale_modes_bit_exact(ops, dtype, rows, dim):
     assert_bit_equal(q, q_ref, "dynamic q, no pre")
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,dim", [(1, 8), (3, 640), (129, 2560), (4099, 3072), (5, 16384)])
+def test_int8_quant_special_kernels_give_the_row_kernel_bytes(ops, dtype, rows, dim):
+    """With a static or a given per-token scale the quantize has no row statistic and runs as a flat kernel over 8-column
+    vectors; with the dynamic scale rows of 320 / 640 / 1280 columns share a warp.  Either way the bytes (and the dynamic
+    scales) must be those of the general row kernel."""
+    from lyradiff_b200 import _lib
+
+    x, pre = _x(rows, dim, dtype, seed=rows * 13 + dim)
+    xd = cu(x)
+    s = cu(torch.tensor([0.043], dtype=torch.float32))
+    st = cu((0.01 + torch.rand(rows)).float())
+
+    def run():
+        out = []
+        for smooth in (cu(pre), None):
+            for kw, scale in (({}, s), ({"per_token": True}, st), ({"dynamic": True}, torch.zeros(rows, dtype=torch.float32, device="cuda"))):
+                q = torch.full((rows, dim), 55, dtype=torch.int8, device="cuda")
+                ops.invoke_sq_input_quant(q, xd, smooth, scale, **kw)
+                check_status()
+                out += [q.cpu(), scale.cpu().clone()]
+        return out
+
+    L = _lib.lib()
+    special = run()
+    assert L.lyraq_debug_set_special_row_kernels(0) == 0
+    try:
+        general = run()
+    finally:
+        L.lyraq_debug_set_special_row_kernels(1)
+    for i, (a, b) in enumerate(zip(special, general)):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8)), i
+
+
 def test_int8_quant_zero_rows_and_empty(ops):
     x = torch.zeros(4, 64, dtype=torch.float16)
     x[2] = torch.linspace(-2, 2, 64).half()
